@@ -1,0 +1,40 @@
+// BIR -> sm_100a PTX text. The role of `impl Backend for Ptx` in the reference
+// (crates/basalt-ptx/src/emit.rs:1973-1994): check, (here: optimise,) lower, return text.
+#pragma once
+#include <string>
+#include <vector>
+
+#include "bir.hpp"
+#include "passes.hpp"
+
+namespace basalt {
+
+struct EmitOptions {
+    int opt_level = 2;      // 0 = the reference's one-to-one lowering, >0 = run the BIR passes
+    int reg_budget = 64;    // 32-bit registers per thread the vectorisers may plan for
+    bool want_bir = false;  // also return the optimised BIR text
+};
+
+struct EmitResult {
+    std::string ptx;
+    std::string bir;   // optimised module, when requested
+    std::vector<OptReport> reports;
+};
+
+// Deterministic: the same (module, options) always yields the same bytes.
+bool emit_ptx(const Module& m, const EmitOptions& opts, EmitResult* out, Diag* d);
+
+// Lowerings of `mma` that use the whole CTA; defined in emit_mma.cpp. `lines` receives PTX
+// statements, `decls` register/shared declarations. Returns false when the op's shape is not one
+// the fast paths cover (the caller then emits the generic loop nest).
+struct MmaSite {
+    const Inst* inst;
+    std::string a, b, c, d;       // 64-bit registers holding the four operand addresses
+    Space sa, sb, sc, sd;         // their address spaces
+    bool c_is_null;               // operand c is the literal null pointer: D = A*B
+    int uid;                      // unique per function, for labels and symbols
+};
+bool emit_mma_fast(const MmaSite& site, const std::string& kernel, std::vector<std::string>* decls,
+                   std::vector<std::string>* lines, std::vector<std::string>* plan);
+
+}  // namespace basalt

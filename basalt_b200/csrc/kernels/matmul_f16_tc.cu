@@ -1,0 +1,244 @@
+// Hand-written fp16 matmul for sm_100a on the fifth-generation tensor cores.
+//
+//   C[M x N] (f16) = A[M x K] (f16) * B (f16), fp32 accumulation in tensor memory.
+//
+// One CTA of 128 threads computes one 128 x 128 tile of C (the BLOCK_M = BLOCK_N = 128,
+// BLOCK_K = 64 tiling of the Triton-style source kernel):
+//   * thread 0 of warp 0 is the TMA producer: per 64-deep K slab it issues tiled bulk-tensor
+//     loads of the A tile (128 rows x 128 bytes) and the B tile into a ring of shared-memory
+//     stages laid out with the 128-byte swizzle the tensor core's matrix descriptors expect;
+//   * thread 0 of warp 1 issues the MMAs: four tcgen05.mma (M128 N128 K16) per slab read A and B
+//     straight from shared memory through 64-bit matrix descriptors and accumulate into 128
+//     columns of TMEM; tcgen05.commit arrives on the stage's "empty" barrier when the MMAs that
+//     read it have finished, and on the "accumulator ready" barrier after the last slab;
+//   * all four warps then drain the accumulator: warp w owns TMEM lanes 32w..32w+31 (rows of the
+//     tile), reads 16 columns at a time with tcgen05.ld, converts to f16 and stores 32-byte runs.
+// Two CTAs fit on an SM (3 stages x 32 KB each, 128 TMEM columns each), so one CTA's epilogue
+// overlaps the other's main loop.
+//
+// Every wait on an mbarrier is bounded; when a wait gives up the kernel records a code in
+// `status`, carries on without the data (the result is then wrong, and the host reports it), and
+// still releases its tensor memory before it returns.
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../../include/basalt_b200_kernels.h"
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 64, UMMA_K = 16, THREADS = 128;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr uint32_t TMEM_COLS = 128;
+constexpr uint32_t WAIT_LIMIT = 1u << 24;   // try_wait calls before a wait gives up
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Bounded wait for the phase with the given parity. Returns false when it gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst), "l"(map),
+                 "r"(bar), "r"(x), "r"(y)
+                 : "memory");
+}
+// 64-bit shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor version 1.
+// Addresses and offsets are encoded in 16-byte units.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3FFF);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+template <int STAGES, bool B_IS_NK>
+__global__ void __launch_bounds__(THREADS) matmul_f16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                                                                __half* __restrict__ C, int N, int K, int32_t* status) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_bar;
+    __shared__ uint32_t tmem_slot;
+    // The swizzle pattern is a function of the absolute shared address: stages start on 1 KB.
+    const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int num_kb = K / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        mbar_init(smem_u32(&acc_bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {   // one warp allocates the accumulator's TMEM columns for the CTA
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_acc = tmem_slot;
+    bool ok = true;
+
+    if (warp == 0 && lane == 0) {
+        // ---- TMA producer ----
+        for (int kb = 0; kb < num_kb; kb++) {
+            const int s = kb % STAGES;
+            const uint32_t parity = ((kb / STAGES) & 1) ^ 1;   // a fresh barrier passes a wait on parity 1
+            ok &= mbar_wait(smem_u32(&empty_bar[s]), parity);
+            const uint32_t fb = smem_u32(&full_bar[s]), a_dst = tiles + s * STAGE_BYTES, b_dst = a_dst + A_BYTES;
+            mbar_expect_tx(fb, STAGE_BYTES);
+            tma_load_2d(a_dst, &map_a, fb, kb * BK, m0);               // box: 64 k (128 B) x 128 rows
+            if (B_IS_NK) tma_load_2d(b_dst, &map_b, fb, kb * BK, n0);  // box: 64 k (128 B) x 128 n
+            else {                                                     // box: 64 n (128 B) x 64 k, twice
+                tma_load_2d(b_dst, &map_b, fb, n0, kb * BK);
+                tma_load_2d(b_dst + B_BYTES / 2, &map_b, fb, n0 + 64, kb * BK);
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer ----
+        // Instruction descriptor: D = f32 (bits 4-5 = 1), A = B = f16 (0), A K-major, B K-major or
+        // MN-major (bit 16), N/8 in bits 17-22, M/16 in bits 24-28.
+        const uint32_t idesc = (1u << 4) | ((B_IS_NK ? 0u : 1u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+        for (int kb = 0; kb < num_kb; kb++) {
+            const int s = kb % STAGES;
+            ok &= mbar_wait(smem_u32(&full_bar[s]), (kb / STAGES) & 1);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t a_src = tiles + s * STAGE_BYTES, b_src = a_src + A_BYTES;
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; k++) {
+                // K-major tile: rows of 128 B, 8-row groups 1024 B apart; a K step of 16 halves is
+                // 32 B along the row.  MN-major B: 64-wide n halves 8192 B apart (leading offset),
+                // 8-row k groups 1024 B apart; a K step of 16 rows is 2048 B.
+                const uint64_t da = smem_desc(a_src + k * UMMA_K * 2, 16, 1024);
+                const uint64_t db = B_IS_NK ? smem_desc(b_src + k * UMMA_K * 2, 16, 1024) : smem_desc(b_src + k * UMMA_K * 128, B_BYTES / 2, 1024);
+                umma_f16(tmem_acc, da, db, idesc, (kb | k) != 0);
+            }
+            umma_commit(smem_u32(&empty_bar[s]));   // stage reusable once these MMAs have read it
+        }
+        umma_commit(smem_u32(&acc_bar));            // accumulator complete
+    }
+    __syncwarp();
+
+    // ---- epilogue: TMEM -> registers -> f16 -> global ----
+    ok &= mbar_wait(smem_u32(&acc_bar), 0);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    __half* crow = C + (size_t)(m0 + warp * 32 + lane) * N + n0;
+    const uint32_t lane_base = tmem_acc + ((uint32_t)(warp * 32) << 16);
+#pragma unroll 1
+    for (int c = 0; c < BN; c += 16) {
+        uint32_t r[16];
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+              "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+            : "r"(lane_base + (uint32_t)c));
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        uint32_t h[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            __half2 v = __floats2half2_rn(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+            h[i] = *reinterpret_cast<uint32_t*>(&v);
+        }
+        *reinterpret_cast<uint4*>(crow + c) = make_uint4(h[0], h[1], h[2], h[3]);
+        *reinterpret_cast<uint4*>(crow + c + 8) = make_uint4(h[4], h[5], h[6], h[7]);
+    }
+    if (!ok && status) atomicExch(status, 1);
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(TMEM_COLS) : "memory");
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess) fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// Row-major f16 matrix [rows x cols] -> tensor map with a (box_cols x box_rows) box, 128B swizzle.
+int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_cols, uint32_t box_rows) {
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return basalt_k::record_msg(1, "matmul_f16", "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {cols * 2};
+    cuuint32_t box[2] = {box_cols, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return basalt_k::record_msg((int)r, "matmul_f16", "cuTensorMapEncodeTiled failed");
+    return 0;
+}
+
+template <int STAGES, bool B_IS_NK>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, __half* C, int M, int N, int K, int32_t* status, cudaStream_t s) {
+    constexpr int smem = STAGES * STAGE_BYTES + 1024;
+    auto kern = matmul_f16_tc_kernel<STAGES, B_IS_NK>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return basalt_k::record(e, "matmul_f16 (shared memory size)");
+        configured = true;
+    }
+    dim3 grid(N / BN, M / BM);
+    kern<<<grid, THREADS, smem, s>>>(ma, mb, C, N, K, status);
+    return basalt_k::record(cudaGetLastError(), "matmul_f16");
+}
+
+}  // namespace
+
+extern "C" int basalt_k_matmul_f16(const void* A, const void* B, void* C, int M, int N, int K, int b_is_nk, int32_t* status, void* stream) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    if (M % BM || N % BN || K % BK) return basalt_k::record_msg(1, "matmul_f16", "M and N must be multiples of 128 and K of 64");
+    if (((uintptr_t)A | (uintptr_t)B | (uintptr_t)C) & 15) return basalt_k::record_msg(1, "matmul_f16", "matrices must be 16-byte aligned");
+    CUtensorMap ma, mb;
+    int rc = make_map(&ma, A, (uint64_t)M, (uint64_t)K, BK, BM);
+    if (rc) return rc;
+    rc = b_is_nk ? make_map(&mb, B, (uint64_t)N, (uint64_t)K, BK, BN) : make_map(&mb, B, (uint64_t)K, (uint64_t)N, 64, BK);
+    if (rc) return rc;
+    cudaStream_t s = (cudaStream_t)stream;
+    return b_is_nk ? launch<3, true>(ma, mb, (__half*)C, M, N, K, status, s) : launch<3, false>(ma, mb, (__half*)C, M, N, K, status, s);
+}

@@ -1,0 +1,96 @@
+// Hand-written fp32 SGEMM for sm_100a: C = A*B, row-major, FFMA only (no TF32 tensor cores).
+//
+// FP32-pipe bound: 128x128 CTA tile, K slab of 16, 256 threads each owning an 8x8 block of C as
+// four 4x4 quadrants so that every shared-memory read is a conflict-free 16-byte access; the next
+// K slab is fetched from global memory into registers while the current one is multiplied, then
+// stored into the other half of a double buffer.  Per K step a thread issues 4 LDS.128 for 64
+// FFMA.  Two CTAs are resident per SM (128 registers/thread, 32 KB shared each).
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../../include/basalt_b200_kernels.h"
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 16, THREADS = 256;
+
+__global__ void __launch_bounds__(THREADS, 2) sgemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C,
+                                                               int M, int N, int K) {
+    // As holds the A slab transposed ([k][m]) so a thread's 4 consecutive rows are one float4.
+    __shared__ __align__(16) float As[2][BK][BM];
+    __shared__ __align__(16) float Bs[2][BK][BN];
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    (void)M;
+
+    // global -> register staging: A slab is 128 rows x 16 floats (4 float4 per row), B slab is
+    // 16 rows x 128 floats (32 float4 per row); two float4 of each per thread.
+    const int a_row = tid >> 2, a_col = (tid & 3) * 4;   // rows a_row and a_row + 64
+    const int b_row = tid >> 5, b_col = (tid & 31) * 4;  // rows b_row and b_row + 8
+    const float* Ag = A + (size_t)(m0 + a_row) * K + a_col;
+    const float* Bg = B + (size_t)b_row * N + n0 + b_col;
+    float4 ra0, ra1, rb0, rb1;
+    auto fetch = [&](int k0) {
+        ra0 = *reinterpret_cast<const float4*>(Ag + k0);
+        ra1 = *reinterpret_cast<const float4*>(Ag + (size_t)64 * K + k0);
+        rb0 = *reinterpret_cast<const float4*>(Bg + (size_t)k0 * N);
+        rb1 = *reinterpret_cast<const float4*>(Bg + (size_t)(k0 + 8) * N);
+    };
+    auto stash = [&](int buf) {
+        As[buf][a_col + 0][a_row] = ra0.x; As[buf][a_col + 1][a_row] = ra0.y; As[buf][a_col + 2][a_row] = ra0.z; As[buf][a_col + 3][a_row] = ra0.w;
+        As[buf][a_col + 0][a_row + 64] = ra1.x; As[buf][a_col + 1][a_row + 64] = ra1.y; As[buf][a_col + 2][a_row + 64] = ra1.z; As[buf][a_col + 3][a_row + 64] = ra1.w;
+        *reinterpret_cast<float4*>(&Bs[buf][b_row][b_col]) = rb0;
+        *reinterpret_cast<float4*>(&Bs[buf][b_row + 8][b_col]) = rb1;
+    };
+
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[i][j] = 0.0f;
+
+    fetch(0);
+    stash(0);
+    __syncthreads();
+    const int nk = K / BK;
+    for (int kb = 0; kb < nk; kb++) {
+        const int buf = kb & 1;
+        if (kb + 1 < nk) fetch((kb + 1) * BK);
+#pragma unroll
+        for (int k = 0; k < BK; k++) {
+            const float4 a0 = *reinterpret_cast<const float4*>(&As[buf][k][ty * 4]);
+            const float4 a1 = *reinterpret_cast<const float4*>(&As[buf][k][ty * 4 + 64]);
+            const float4 b0 = *reinterpret_cast<const float4*>(&Bs[buf][k][tx * 4]);
+            const float4 b1 = *reinterpret_cast<const float4*>(&Bs[buf][k][tx * 4 + 64]);
+            const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+            const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+#pragma unroll
+                for (int j = 0; j < 8; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        if (kb + 1 < nk) {
+            stash(buf ^ 1);
+            __syncthreads();
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int row = m0 + ty * 4 + (i & 3) + (i >> 2) * 64;
+        float* crow = C + (size_t)row * N + n0 + tx * 4;
+        *reinterpret_cast<float4*>(crow) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+        *reinterpret_cast<float4*>(crow + 64) = make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
+    }
+}
+
+}  // namespace
+
+extern "C" int basalt_k_sgemm_f32(const float* A, const float* B, float* C, int M, int N, int K, void* stream) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    if (M % BM || N % BN || K % BK) return basalt_k::record_msg(1, "sgemm_f32", "M and N must be multiples of 128 and K of 16");
+    if (((uintptr_t)A | (uintptr_t)B | (uintptr_t)C) & 15) return basalt_k::record_msg(1, "sgemm_f32", "matrices must be 16-byte aligned");
+    dim3 grid(N / BN, M / BM);
+    sgemm_f32_kernel<<<grid, THREADS, 0, (cudaStream_t)stream>>>(A, B, C, M, N, K);
+    return basalt_k::record(cudaGetLastError(), "sgemm_f32");
+}

@@ -1,0 +1,1058 @@
+// Module checks and BIR-to-BIR passes; see passes.hpp.
+#include "passes.hpp"
+
+#include <algorithm>
+#include <functional>
+#include <map>
+#include <set>
+
+namespace basalt {
+
+// ---- refusal surface -----------------------------------------------------------------------
+static bool refuse(Diag* d, const char* code, const std::string& arg) {
+    if (d) { d->code = code; d->arg = arg; }
+    return false;
+}
+
+static bool check_inst(const Inst& in, Diag* d) {
+    // Vector-typed results: only ops with a per-lane meaning (crates/basalt-ptx/src/emit.rs:378-404).
+    if (in.ty.is_vec()) {
+        if (in.ty.lanes == 0) return refuse(d, "E091", "zero-lane vector type");
+        switch (in.op) {
+            case Opc::Bin: case Opc::Select: case Opc::Cast: case Opc::Phi: case Opc::Load: case Opc::VecBuild: break;
+            default: return refuse(d, "E091", "vector-typed result has no defined per-lane decomposition for this op");
+        }
+    }
+    if ((in.op == Opc::ICmp || in.op == Opc::FCmp) && in.aux.is_vec())
+        return refuse(d, "E091", "vector-operand compare has no scalar-reduction semantics in this backend");
+    if (in.op == Opc::Cast && (CastOp)in.sub == CastOp::Bitcast && (in.aux.is_sc(Scalar::I1) || in.ty.is_sc(Scalar::I1)))
+        return refuse(d, "E091", "bitcast on a predicate-typed value has no defined bit pattern");
+    if (in.op == Opc::Bin && in.ty.is_sc(Scalar::I1)) {
+        BinOp b = (BinOp)in.sub;
+        if (b != BinOp::And && b != BinOp::Or && b != BinOp::Xor)
+            return refuse(d, "E090", "only and/or/xor are defined on a predicate-typed Bin");
+    }
+    if (in.op == Opc::Atomic || in.op == Opc::AtomicCas) {
+        if (in.ty.is_sc(Scalar::I1) || in.ty.is_sc(Scalar::I8) || in.ty.is_sc(Scalar::I16) || in.ty.is_sc(Scalar::F16))
+            return refuse(d, "E091", "sub-32-bit atomic RMW/CAS: no distinct 8/16-bit register class in this backend");
+    }
+    if (in.op == Opc::Shuffle && (in.ty.is_sc(Scalar::I1) || in.ty.is_sc(Scalar::F16)))
+        return refuse(d, "E091", "shuffling a predicate- or half-typed value directly is not implemented");
+    if (in.op == Opc::KernelLaunch || in.op == Opc::CudaMalloc || in.op == Opc::CudaMemcpy || in.op == Opc::CudaFree || in.op == Opc::CudaSync)
+        return refuse(d, "E090", "kernel launch / CUDA Runtime API calls have no lowering in this backend");
+    if (in.op == Opc::Mma) {
+        bool fin = in.in_dt >= Scalar::F16, facc = in.acc_dt >= Scalar::F16;
+        // Same pairs the reference oracle accepts (oracle.rs "Supported (in_dtype, acc_dtype)
+        // pairs") plus f16 inputs, which this backend can lower.
+        if (fin != facc || in.in_dt == Scalar::I1 || in.acc_dt == Scalar::I1 || scalar_bits(in.acc_dt) < scalar_bits(in.in_dt) ||
+            in.acc_dt == Scalar::F16 || in.in_dt == Scalar::F64 || in.acc_dt == Scalar::F64 || in.in_dt == Scalar::I64 || in.acc_dt == Scalar::I64)
+            return refuse(d, "E091", "unsupported mma (in_dtype, acc_dtype) pair");
+        if (in.has_out && !(in.out_dt == in.acc_dt || (in.out_dt == Scalar::F16 && in.acc_dt == Scalar::F32)))
+            return refuse(d, "E091", "unsupported mma output type");
+        if (in.m == 0 || in.n == 0 || in.k == 0) return refuse(d, "E099", "empty mma tile");
+    }
+    if (in.op == Opc::WarpReduce && !in.ty.is_sc(Scalar::I32))
+        return refuse(d, "E091", "warp.reduce is defined on i32 only");
+    if (in.op == Opc::FCmp && in.aux.is_ptr()) return refuse(d, "E091", "fcmp on a pointer");
+    return true;
+}
+
+bool check_module(const Module& m, Diag* d) {
+    size_t nk = 0;
+    for (auto& f : m.funcs) nk += f.is_kernel;
+    if (m.funcs.empty()) return true;
+    if (nk == 0) return refuse(d, "E093", "host/non-kernel function compilation is not implemented");
+    for (auto& f : m.funcs)
+        for (auto& in : f.insts)
+            if (!check_inst(in, d)) return false;
+    // call graph
+    std::map<std::string, size_t> idx;
+    for (size_t i = 0; i < m.funcs.size(); i++) idx[m.funcs[i].name] = i;
+    std::vector<std::vector<size_t>> edges(m.funcs.size());
+    for (size_t i = 0; i < m.funcs.size(); i++)
+        for (auto& in : m.funcs[i].insts)
+            if (in.op == Opc::Call) {
+                auto it = idx.find(in.callee);
+                if (it == idx.end()) return refuse(d, "E093", "call to a function outside the module: " + in.callee);
+                const Function& cal = m.funcs[it->second];
+                if (it->second == i) return refuse(d, "E094", in.callee);
+                if (cal.is_kernel) return refuse(d, "E093", "a kernel is launched, never called: " + in.callee);
+                if (cal.params.size() != in.ops.size()) return refuse(d, "E093", "call arity mismatch: " + in.callee);
+                edges[i].push_back(it->second);
+            }
+    std::vector<int> color(m.funcs.size(), 0);
+    std::string cyc;
+    std::function<bool(size_t)> dfs = [&](size_t u) {
+        color[u] = 1;
+        for (size_t v : edges[u]) {
+            if (color[v] == 1) { cyc = m.funcs[v].name; return false; }
+            if (color[v] == 0 && !dfs(v)) return false;
+        }
+        color[u] = 2;
+        return true;
+    };
+    for (size_t i = 0; i < m.funcs.size(); i++)
+        if (color[i] == 0 && !dfs(i)) return refuse(d, "E094", cyc);
+    std::vector<char> reach(m.funcs.size(), 0);
+    std::function<void(size_t)> mark = [&](size_t u) {
+        if (reach[u]) return;
+        reach[u] = 1;
+        for (size_t v : edges[u]) mark(v);
+    };
+    for (size_t i = 0; i < m.funcs.size(); i++) if (m.funcs[i].is_kernel) mark(i);
+    for (size_t i = 0; i < m.funcs.size(); i++)
+        if (!reach[i]) return refuse(d, "E095", m.funcs[i].name);
+    return true;
+}
+
+// ---- small utilities -----------------------------------------------------------------------
+static void replace_uses(Function& f, Val from, Val to) {
+    for (auto& in : f.insts) for (Val& v : in.ops) if (v == from) v = to;
+    for (auto& b : f.blocks) if (b.term.has_val && b.term.val == from) b.term.val = to;
+}
+
+static bool has_side_effect(const Inst& in) {
+    switch (in.op) {
+        case Opc::Store: case Opc::Barrier: case Opc::Atomic: case Opc::AtomicCas: case Opc::Mma: case Opc::KernelLaunch:
+        case Opc::CudaMalloc: case Opc::CudaMemcpy: case Opc::CudaFree: case Opc::CudaSync: case Opc::Call:
+        case Opc::Shuffle: case Opc::Ballot: case Opc::VoteAny: case Opc::VoteAll: case Opc::WarpReduce:
+            return true;   // warp collectives stay: removing one changes which lanes synchronise
+        case Opc::Load: return in.vol;
+        default: return false;
+    }
+}
+
+void dce(Function& f) {
+    // Warp collectives whose result is unused are removable too, but only when every one in the
+    // function is dead-or-alive independently of control flow; keep it simple: shuffles and
+    // reductions without users are dropped (they have no memory effect), votes likewise.
+    auto removable = [&](const Inst& in) {
+        if (!has_side_effect(in)) return true;
+        return in.op == Opc::Shuffle || in.op == Opc::WarpReduce || in.op == Opc::Ballot || in.op == Opc::VoteAny || in.op == Opc::VoteAll;
+    };
+    for (;;) {
+        std::vector<uint32_t> uses(f.insts.size(), 0);
+        for (auto& b : f.blocks) {
+            for (uint32_t id : b.insts) for (Val v : f.insts[id].ops) if (!v.param) uses[v.idx]++;
+            if (b.term.has_val && !b.term.val.param) uses[b.term.val.idx]++;
+        }
+        bool changed = false;
+        for (auto& b : f.blocks) {
+            std::vector<uint32_t> keep;
+            for (uint32_t id : b.insts) {
+                if (uses[id] == 0 && removable(f.insts[id])) changed = true;
+                else keep.push_back(id);
+            }
+            b.insts.swap(keep);
+        }
+        if (!changed) break;
+    }
+}
+
+static void successors(const Term& t, std::vector<uint32_t>& out) {
+    out.clear();
+    if (t.kind == Term::Ret) return;
+    out.push_back(t.t);
+    if (t.kind == Term::CondBr) out.push_back(t.f);
+    for (auto& c : t.cases) out.push_back(c.second);
+}
+
+void simplify_cfg(Function& f) {
+    for (;;) {
+        bool changed = false;
+        std::vector<uint32_t> npred(f.blocks.size(), 0), succ;
+        std::vector<char> reach(f.blocks.size(), 0);
+        std::vector<uint32_t> stack{0};
+        reach[0] = 1;
+        while (!stack.empty()) {
+            uint32_t b = stack.back();
+            stack.pop_back();
+            successors(f.blocks[b].term, succ);
+            std::sort(succ.begin(), succ.end());
+            succ.erase(std::unique(succ.begin(), succ.end()), succ.end());
+            for (uint32_t s : succ) {
+                npred[s]++;
+                if (!reach[s]) { reach[s] = 1; stack.push_back(s); }
+            }
+        }
+        for (uint32_t b = 0; b < f.blocks.size() && !changed; b++) {
+            if (!reach[b]) continue;
+            Term& t = f.blocks[b].term;
+            if (t.kind != Term::Br) continue;
+            uint32_t s = t.t;
+            if (s == b || s == 0 || npred[s] != 1) continue;
+            // merge s into b
+            std::vector<uint32_t> moved;
+            for (uint32_t id : f.blocks[s].insts) {
+                Inst& in = f.insts[id];
+                if (in.op == Opc::Phi) {
+                    Val repl = in.ops.empty() ? Val::V(id) : in.ops[0];
+                    replace_uses(f, Val::V(id), repl);
+                } else moved.push_back(id);
+            }
+            for (uint32_t id : moved) f.blocks[b].insts.push_back(id);
+            f.blocks[b].term = f.blocks[s].term;
+            f.blocks[s].insts.clear();
+            f.blocks[s].term = Term{};
+            for (auto& in : f.insts) if (in.op == Opc::Phi) for (uint32_t& pb : in.phi_blocks) if (pb == s) pb = b;
+            changed = true;
+        }
+        if (changed) continue;
+        // drop unreachable blocks
+        bool any_dead = false;
+        for (uint32_t b = 0; b < f.blocks.size(); b++) any_dead |= !reach[b];
+        if (!any_dead) break;
+        std::vector<uint32_t> remap(f.blocks.size(), UINT32_MAX);
+        std::vector<Block> nb;
+        for (uint32_t b = 0; b < f.blocks.size(); b++)
+            if (reach[b]) { remap[b] = (uint32_t)nb.size(); nb.push_back(std::move(f.blocks[b])); }
+        for (auto& b : nb) {
+            Term& t = b.term;
+            if (t.kind != Term::Ret) t.t = remap[t.t];
+            if (t.kind == Term::CondBr) t.f = remap[t.f];
+            for (auto& c : t.cases) c.second = remap[c.second];
+        }
+        f.blocks = std::move(nb);
+        // phis: drop incomings from removed blocks, renumber the rest (only listed instructions matter)
+        for (auto& b : f.blocks)
+            for (uint32_t id : b.insts) {
+                Inst& in = f.insts[id];
+                if (in.op != Opc::Phi) continue;
+                std::vector<Val> ops;
+                std::vector<uint32_t> pbs;
+                for (size_t i = 0; i < in.ops.size(); i++)
+                    if (remap[in.phi_blocks[i]] != UINT32_MAX) { ops.push_back(in.ops[i]); pbs.push_back(remap[in.phi_blocks[i]]); }
+                in.ops = ops;
+                in.phi_blocks = pbs;
+            }
+    }
+}
+
+// ---- inliner -------------------------------------------------------------------------------
+static bool inline_one(Function& F, const Module& M) {
+    for (uint32_t bi = 0; bi < F.blocks.size(); bi++) {
+        for (size_t pos = 0; pos < F.blocks[bi].insts.size(); pos++) {
+            uint32_t call_id = F.blocks[bi].insts[pos];
+            if (F.insts[call_id].op != Opc::Call) continue;
+            const Function* cal = M.find(F.insts[call_id].callee);
+            std::vector<Val> args = F.insts[call_id].ops;
+            Ty rty = F.insts[call_id].ty;
+            // split the block after the call
+            Block cont;
+            cont.insts.assign(F.blocks[bi].insts.begin() + pos + 1, F.blocks[bi].insts.end());
+            cont.term = F.blocks[bi].term;
+            F.blocks[bi].insts.resize(pos);
+            uint32_t cont_idx = (uint32_t)F.blocks.size();
+            F.blocks.push_back(std::move(cont));
+            for (auto& in : F.insts) if (in.op == Opc::Phi) for (uint32_t& pb : in.phi_blocks) if (pb == bi) pb = cont_idx;
+            // clone the callee
+            uint32_t base_blk = (uint32_t)F.blocks.size(), base_inst = (uint32_t)F.insts.size();
+            auto mapv = [&](Val v) { return v.param ? args[v.idx] : Val::V(base_inst + v.idx); };
+            for (auto& cin : cal->insts) {
+                Inst in = cin;
+                for (Val& v : in.ops) v = mapv(v);
+                for (uint32_t& pb : in.phi_blocks) pb += base_blk;
+                F.insts.push_back(std::move(in));
+            }
+            std::vector<std::pair<uint32_t, Val>> rets;
+            for (size_t cb = 0; cb < cal->blocks.size(); cb++) {
+                Block nb;
+                for (uint32_t id : cal->blocks[cb].insts) nb.insts.push_back(base_inst + id);
+                Term t = cal->blocks[cb].term;
+                if (t.kind == Term::Ret) {
+                    if (t.has_val) rets.push_back({base_blk + (uint32_t)cb, mapv(t.val)});
+                    else rets.push_back({base_blk + (uint32_t)cb, Val{}});
+                    Term br;
+                    br.kind = Term::Br;
+                    br.t = cont_idx;
+                    t = br;
+                } else {
+                    if (t.has_val) t.val = mapv(t.val);
+                    t.t += base_blk;
+                    if (t.kind == Term::CondBr) t.f += base_blk;
+                    for (auto& c : t.cases) c.second += base_blk;
+                }
+                nb.term = t;
+                F.blocks.push_back(std::move(nb));
+            }
+            Term enter;
+            enter.kind = Term::Br;
+            enter.t = base_blk;
+            F.blocks[bi].term = enter;
+            if (!rty.is_void()) {
+                Val result;
+                if (rets.size() == 1) result = rets[0].second;
+                else {
+                    Inst phi;
+                    phi.op = Opc::Phi;
+                    phi.ty = rty;
+                    for (auto& r : rets) { phi.phi_blocks.push_back(r.first); phi.ops.push_back(r.second); }
+                    uint32_t pid = (uint32_t)F.insts.size();
+                    F.insts.push_back(std::move(phi));
+                    F.blocks[cont_idx].insts.insert(F.blocks[cont_idx].insts.begin(), pid);
+                    result = Val::V(pid);
+                }
+                replace_uses(F, Val::V(call_id), result);
+            }
+            return true;
+        }
+    }
+    return false;
+}
+
+void inline_calls(Module& m) {
+    for (auto& f : m.funcs) {
+        if (!f.is_kernel) continue;
+        while (inline_one(f, m)) {}
+    }
+    std::vector<Function> kernels;
+    for (auto& f : m.funcs) if (f.is_kernel) kernels.push_back(std::move(f));
+    m.funcs = std::move(kernels);
+}
+
+// ---- function builder ----------------------------------------------------------------------
+namespace {
+struct FB {
+    Function f;
+    uint32_t cur = 0;
+    uint32_t block() { f.blocks.emplace_back(); return (uint32_t)f.blocks.size() - 1; }
+    void at(uint32_t b) { cur = b; }
+    Val push(Inst in) {
+        uint32_t id = (uint32_t)f.insts.size();
+        f.insts.push_back(std::move(in));
+        f.blocks[cur].insts.push_back(id);
+        return Val::V(id);
+    }
+    Val ci(Ty ty, int64_t v) { Inst in; in.op = Opc::ConstI; in.ty = ty; in.imm = v; return push(in); }
+    Val bin(BinOp o, Ty ty, Val a, Val b) { Inst in; in.op = Opc::Bin; in.sub = (uint8_t)o; in.ty = ty; in.ops = {a, b}; return push(in); }
+    Val icmp(ICmp p, Ty oty, Val a, Val b) { Inst in; in.op = Opc::ICmp; in.sub = (uint8_t)p; in.ty = Ty::s(Scalar::I1); in.aux = oty; in.ops = {a, b}; return push(in); }
+    Val select(Ty ty, Val c, Val a, Val b) { Inst in; in.op = Opc::Select; in.ty = ty; in.ops = {c, a, b}; return push(in); }
+    Val cast(CastOp o, Ty dst, Ty src, Val v) { Inst in; in.op = Opc::Cast; in.sub = (uint8_t)o; in.ty = dst; in.aux = src; in.ops = {v}; return push(in); }
+    Val index(unsigned sub, Ty ty) { Inst in; in.op = Opc::Index; in.sub = (uint8_t)sub; in.ty = ty; return push(in); }
+    Val load(Ty ty, Space sp, Val p, uint32_t align) { Inst in; in.op = Opc::Load; in.ty = ty; in.space = sp; in.align = align; in.ops = {p}; return push(in); }
+    void store(Ty ty, Space sp, Val p, Val v, uint32_t align) { Inst in; in.op = Opc::Store; in.ty = Ty::v(); in.aux = ty; in.space = sp; in.align = align; in.ops = {p, v}; push(in); }
+    Val extract(Ty ty, Val v, unsigned lane) { Inst in; in.op = Opc::VecExtract; in.ty = ty; in.sub = (uint8_t)lane; in.ops = {v}; return push(in); }
+    Val build(Ty ty, std::vector<Val> lanes) { Inst in; in.op = Opc::VecBuild; in.ty = ty; in.ops = std::move(lanes); return push(in); }
+    // A phi is created empty and its incomings added once the predecessor values exist.
+    Val phi(Ty ty) { Inst in; in.op = Opc::Phi; in.ty = ty; return push(in); }
+    void phi_in(Val phi, uint32_t from, Val v) { f.insts[phi.idx].phi_blocks.push_back(from); f.insts[phi.idx].ops.push_back(v); }
+    void br(uint32_t t) { Term x; x.kind = Term::Br; x.t = t; f.blocks[cur].term = x; }
+    void condbr(Val c, uint32_t t, uint32_t e) { Term x; x.kind = Term::CondBr; x.has_val = true; x.val = c; x.t = t; x.f = e; f.blocks[cur].term = x; }
+    void ret() { f.blocks[cur].term = Term{}; }
+};
+
+const Ty I1 = Ty::s(Scalar::I1), I32 = Ty::s(Scalar::I32), I64 = Ty::s(Scalar::I64), PG = Ty::p(Space::Global);
+
+const Inst* def(const Function& f, Val v) { return v.param ? nullptr : &f.insts[v.idx]; }
+bool is_index(const Function& f, Val v, unsigned sub) {
+    const Inst* d = def(f, v);
+    return d && d->op == Opc::Index && d->sub == sub && d->ty == I32;
+}
+bool is_bin(const Function& f, Val v, BinOp o, Val* a, Val* b) {
+    const Inst* d = def(f, v);
+    if (!d || d->op != Opc::Bin || (BinOp)d->sub != o) return false;
+    *a = d->ops[0];
+    *b = d->ops[1];
+    return true;
+}
+bool const_int(const Function& f, Val v, int64_t* out) {
+    const Inst* d = def(f, v);
+    if (!d || d->op != Opc::ConstI || d->ty.is_ptr()) return false;
+    *out = d->imm;
+    return true;
+}
+// bid.x*bdim.x + tid.x in any operand order, all i32.
+bool is_linear_index(const Function& f, Val v) {
+    Val a, b, x, y;
+    if (!is_bin(f, v, BinOp::Add, &a, &b) || def(f, v)->ty != I32) return false;
+    for (int s = 0; s < 2; s++) {
+        if (is_index(f, b, 0) && is_bin(f, a, BinOp::Mul, &x, &y) &&
+            ((is_index(f, x, 3) && is_index(f, y, 6)) || (is_index(f, x, 6) && is_index(f, y, 3))))
+            return true;
+        std::swap(a, b);
+    }
+    return false;
+}
+// gdim.x*bdim.x in either order, i32.
+bool is_grid_stride(const Function& f, Val v) {
+    Val x, y;
+    if (!is_bin(f, v, BinOp::Mul, &x, &y) || def(f, v)->ty != I32) return false;
+    return (is_index(f, x, 9) && is_index(f, y, 6)) || (is_index(f, x, 6) && is_index(f, y, 9));
+}
+
+// A combining step r = op(x, y) on i32: add/and/or/xor directly, or max/min as
+// select(icmp, ., .).  `cmp_id` receives the compare's id for the select forms.
+bool match_combine(const Function& f, Val r, RedOp* op, Val* x, Val* y, uint32_t* cmp_id) {
+    const Inst* d = def(f, r);
+    if (!d || d->ty != I32) return false;
+    *cmp_id = UINT32_MAX;
+    if (d->op == Opc::Bin) {
+        switch ((BinOp)d->sub) {
+            case BinOp::Add: *op = RedOp::Add; break;
+            case BinOp::And: *op = RedOp::And; break;
+            case BinOp::Or: *op = RedOp::Or; break;
+            case BinOp::Xor: *op = RedOp::Xor; break;
+            default: return false;
+        }
+        *x = d->ops[0];
+        *y = d->ops[1];
+        return true;
+    }
+    if (d->op != Opc::Select) return false;
+    const Inst* c = def(f, d->ops[0]);
+    if (!c || c->op != Opc::ICmp || c->aux != I32) return false;
+    Val p = c->ops[0], q = c->ops[1], A = d->ops[1], B = d->ops[2];
+    bool gt = (ICmp)c->sub == ICmp::Sgt || (ICmp)c->sub == ICmp::Sge, lt = (ICmp)c->sub == ICmp::Slt || (ICmp)c->sub == ICmp::Sle;
+    if (!gt && !lt) return false;
+    bool straight = (A == p && B == q), crossed = (A == q && B == p);
+    if (!straight && !crossed) return false;
+    *op = (gt == straight) ? RedOp::Max : RedOp::Min;
+    *x = p;
+    *y = q;
+    *cmp_id = d->ops[0].idx;
+    return true;
+}
+
+Val emit_combine(FB& b, RedOp op, Val x, Val y) {
+    switch (op) {
+        case RedOp::Add: return b.bin(BinOp::Add, I32, x, y);
+        case RedOp::And: return b.bin(BinOp::And, I32, x, y);
+        case RedOp::Or: return b.bin(BinOp::Or, I32, x, y);
+        case RedOp::Xor: return b.bin(BinOp::Xor, I32, x, y);
+        case RedOp::Max: return b.select(I32, b.icmp(ICmp::Sgt, I32, x, y), x, y);
+        case RedOp::Min: return b.select(I32, b.icmp(ICmp::Slt, I32, x, y), x, y);
+    }
+    return x;
+}
+
+// Address pattern `base + ext(i)*esz` rooted at index value `i`; returns base and esz.
+struct Addr {
+    Val base;
+    int64_t esz = 0;
+};
+bool match_addr(const Function& f, Val v, Val i, Addr* out) {
+    const Inst* d = def(f, v);
+    if (!d || d->op != Opc::Bin || (BinOp)d->sub != BinOp::Add || d->ty != PG) return false;
+    for (int s = 0; s < 2; s++) {
+        Val base = d->ops[s], off = d->ops[1 - s];
+        const Inst* o = def(f, off);
+        if (!o || o->op != Opc::Bin || o->ty != I64) continue;
+        int64_t c = 0;
+        Val ext;
+        if ((BinOp)o->sub == BinOp::Mul) {
+            if (const_int(f, o->ops[1], &c)) ext = o->ops[0];
+            else if (const_int(f, o->ops[0], &c)) ext = o->ops[1];
+            else continue;
+        } else if ((BinOp)o->sub == BinOp::Shl && const_int(f, o->ops[1], &c) && c >= 0 && c < 8) {
+            c = (int64_t)1 << c;
+            ext = o->ops[0];
+        } else continue;
+        const Inst* e = def(f, ext);
+        if (!e || e->op != Opc::Cast || ((CastOp)e->sub != CastOp::SExt && (CastOp)e->sub != CastOp::ZExt) || e->ty != I64 || e->aux != I32 || e->ops[0] != i) continue;
+        const Inst* bd = def(f, base);
+        if (bd && !(f.val_ty(base) == PG)) continue;
+        out->base = base;
+        out->esz = c;
+        return true;
+    }
+    return false;
+}
+
+bool ret_only(const Function& f, uint32_t b) { return f.blocks[b].insts.empty() && f.blocks[b].term.kind == Term::Ret && !f.blocks[b].term.has_val; }
+
+int log2i(int64_t v) { int l = 0; while ((1ll << l) < v) l++; return l; }
+}  // namespace
+
+// ---- elementwise vectoriser ----------------------------------------------------------------
+bool vectorize_elementwise(Function& F, int max_unroll, OptReport* rep) {
+    if (!F.is_kernel || F.blocks.size() < 2 || F.blocks.size() > 3) return false;
+    const Term& et = F.blocks[0].term;
+    if (et.kind != Term::CondBr) return false;
+    uint32_t body = et.t, other = et.f;
+    if (body == 0 || other == 0 || body == other || !ret_only(F, other)) return false;
+    const Term& bt = F.blocks[body].term;
+    if (!(bt.kind == Term::Br && bt.t == other) && !(bt.kind == Term::Ret && !bt.has_val)) return false;
+    const Inst* c = def(F, et.val);
+    if (!c || c->op != Opc::ICmp || c->aux != I32) return false;
+    Val i, n;
+    if ((ICmp)c->sub == ICmp::Slt) { i = c->ops[0]; n = c->ops[1]; }
+    else if ((ICmp)c->sub == ICmp::Sgt) { i = c->ops[1]; n = c->ops[0]; }
+    else return false;
+    if (!is_linear_index(F, i) || !(n.param && F.params[n.idx] == I32)) return false;
+    for (uint32_t id : F.blocks[0].insts) {
+        Opc o = F.insts[id].op;
+        if (o != Opc::Index && o != Opc::ConstI && o != Opc::ConstF && o != Opc::Bin && o != Opc::ICmp && o != Opc::Cast) return false;
+        if (o == Opc::Index && F.insts[id].sub % 3 != 0) return false;   // 1-D kernels only
+    }
+    // Thread-dependent entry values other than the index itself must not leak into the body.
+    std::set<uint32_t> entry_ids(F.blocks[0].insts.begin(), F.blocks[0].insts.end());
+    std::set<uint32_t> tdep;
+    for (uint32_t id : F.blocks[0].insts) {
+        const Inst& in = F.insts[id];
+        bool t = in.op == Opc::Index && (in.sub == 0 || in.sub == 3);
+        for (Val v : in.ops) if (!v.param && tdep.count(v.idx)) t = true;
+        if (t) tdep.insert(id);
+    }
+    // Classify the body.
+    enum Kind { Skip, Uniform, Lane, LoadK, StoreK };
+    std::map<uint32_t, Kind> kind;
+    std::map<uint32_t, Addr> addr_of;   // load/store id -> address
+    std::set<uint32_t> idx_chain;       // ext / offset / address values
+    int64_t max_esz = 0, nloads = 0, nstores = 0;
+    for (uint32_t id : F.blocks[body].insts) {
+        const Inst& in = F.insts[id];
+        auto lane_or_uniform = [&](Val v, bool* lane) {
+            if (v == i) return false;
+            if (v.param) return true;
+            if (idx_chain.count(v.idx)) return false;
+            if (entry_ids.count(v.idx)) return !tdep.count(v.idx);
+            auto it = kind.find(v.idx);
+            if (it == kind.end()) return false;
+            if (it->second == Lane || it->second == LoadK) *lane = true;
+            return true;
+        };
+        Addr a;
+        if (in.op == Opc::Cast && in.ops[0] == i) {
+            if (((CastOp)in.sub != CastOp::SExt && (CastOp)in.sub != CastOp::ZExt) || in.ty != I64) return false;
+            idx_chain.insert(id); kind[id] = Skip; continue;
+        }
+        if (in.op == Opc::Bin && in.ty == I64 && ((!in.ops[0].param && idx_chain.count(in.ops[0].idx)) || (!in.ops[1].param && idx_chain.count(in.ops[1].idx)))) {
+            idx_chain.insert(id); kind[id] = Skip; continue;   // validated when the address is matched
+        }
+        if (in.op == Opc::Bin && in.ty == PG && match_addr(F, Val::V(id), i, &a)) {
+            bool lane = false;
+            if (!lane_or_uniform(a.base, &lane) || lane) return false;
+            idx_chain.insert(id); kind[id] = Skip; continue;
+        }
+        if (in.op == Opc::Load || in.op == Opc::Store) {
+            Ty ety = in.op == Opc::Load ? in.ty : in.aux;
+            if (in.vol || in.space != Space::Global || ety.kind != Ty::Sc) return false;
+            if (!match_addr(F, in.ops[0], i, &a)) return false;
+            int64_t esz = scalar_bytes(ety.sc);
+            if (a.esz != esz || (esz != 4 && esz != 8) || in.align < esz) return false;
+            max_esz = std::max(max_esz, esz);
+            addr_of[id] = a;
+            if (in.op == Opc::Load) { kind[id] = LoadK; nloads++; }
+            else {
+                bool lane = false;
+                if (!lane_or_uniform(in.ops[1], &lane)) return false;
+                kind[id] = StoreK; nstores++;
+            }
+            continue;
+        }
+        switch (in.op) {
+            case Opc::ConstI: if (in.ty.is_ptr() && in.ty.sp != Space::Global) return false; kind[id] = Uniform; continue;
+            case Opc::ConstF: kind[id] = Uniform; continue;
+            case Opc::Bin: case Opc::ICmp: case Opc::FCmp: case Opc::Select: case Opc::Cast: {
+                if (in.ty.is_vec()) return false;
+                bool lane = false;
+                for (Val v : in.ops) if (!lane_or_uniform(v, &lane)) return false;
+                kind[id] = lane ? Lane : Uniform;
+                continue;
+            }
+            default: return false;
+        }
+    }
+    if (nstores == 0 || nloads + nstores == 0) return false;
+    const int V = (int)(16 / max_esz);
+    int U = std::max<int64_t>(1, std::min<int64_t>(4, 64 / (std::max<int64_t>(nloads, 1) * 16)));
+    U = std::max(1, std::min(U, max_unroll));
+
+    FB b;
+    b.f.name = F.name; b.f.is_kernel = true; b.f.params = F.params; b.f.ret = F.ret;
+    uint32_t entry = b.block();
+    b.at(entry);
+    std::map<uint32_t, Val> E;   // old entry id -> new value
+    for (uint32_t id : F.blocks[0].insts) {
+        Inst in = F.insts[id];
+        for (Val& v : in.ops) if (!v.param) v = E.at(v.idx);
+        E[id] = b.push(in);
+    }
+    auto mapE = [&](Val v) { return v.param ? v : E.at(v.idx); };
+    Val g32 = mapE(i), guard = mapE(et.val);
+    Val g = b.cast(CastOp::SExt, I64, I32, g32);
+    Val T = b.bin(BinOp::Mul, I64, b.cast(CastOp::ZExt, I64, I32, b.index(9, I32)), b.cast(CastOp::ZExt, I64, I32, b.index(6, I32)));
+    Val n64 = b.cast(CastOp::SExt, I64, I32, n);
+    Val lim0 = b.select(I64, b.icmp(ICmp::Slt, I64, n64, T), n64, T);
+    Val zero = b.ci(I64, 0);
+    Val lim = b.select(I64, b.icmp(ICmp::Slt, I64, lim0, zero), zero, lim0);
+    Val nv = b.bin(BinOp::AShr, I64, lim, b.ci(I64, log2i(V)));
+    // alignment of every distinct base pointer
+    std::vector<Val> bases;
+    for (auto& kv : addr_of) if (std::find(bases.begin(), bases.end(), kv.second.base) == bases.end()) bases.push_back(kv.second.base);
+    Val bits = zero;
+    for (Val p : bases) bits = b.bin(BinOp::Or, I64, bits, b.cast(CastOp::Bitcast, I64, PG, mapE(p)));
+    Val aligned = b.icmp(ICmp::Eq, I64, b.bin(BinOp::And, I64, bits, b.ci(I64, 15)), zero);
+    uint32_t vhead = b.block(), uloop = b.block(), ubody = b.block(), vloop = b.block(), vbody = b.block(), tail = b.block(),
+             tbody = b.block(), sguard = b.block(), sbody = b.block(), exitb = b.block();
+    b.condbr(aligned, vhead, sguard);
+
+    // Clones the body for one scalar index value.
+    auto scalar_clone = [&](Val idx32) {
+        std::map<uint32_t, Val> M;
+        for (uint32_t id : F.blocks[body].insts) {
+            Inst in = F.insts[id];
+            for (Val& v : in.ops) {
+                if (v == i) v = idx32;
+                else if (!v.param) { auto it = M.find(v.idx); v = it != M.end() ? it->second : E.at(v.idx); }
+            }
+            Val r = b.push(in);
+            if (in.has_result()) M[id] = r;
+        }
+    };
+    // Emits `count` vector iterations at vector indices j, j+T, ...: all loads first, then the
+    // per-lane computation and the stores.
+    auto vector_iters = [&](Val j, int count) {
+        std::vector<std::map<uint32_t, std::vector<Val>>> lanes(count);   // [u][old id] -> per-lane values
+        std::vector<Val> js(count);
+        for (int u = 0; u < count; u++) js[u] = u == 0 ? j : b.bin(BinOp::Add, I64, js[u - 1], T);
+        auto vaddr = [&](int u, const Addr& a) {
+            Val off = b.bin(BinOp::Mul, I64, js[u], b.ci(I64, V * a.esz));
+            return b.bin(BinOp::Add, PG, mapE(a.base), off);
+        };
+        for (int u = 0; u < count; u++)
+            for (uint32_t id : F.blocks[body].insts) {
+                if (kind[id] != LoadK) continue;
+                const Inst& in = F.insts[id];
+                const Addr& a = addr_of[id];
+                Val vec = b.load(Ty::vec(in.ty.sc, (uint8_t)V), Space::Global, vaddr(u, a), (uint32_t)(V * a.esz));
+                std::vector<Val> ls;
+                for (int l = 0; l < V; l++) ls.push_back(b.extract(in.ty, vec, (unsigned)l));
+                lanes[u][id] = ls;
+            }
+        for (int u = 0; u < count; u++)
+            for (uint32_t id : F.blocks[body].insts) {
+                Kind k = kind[id];
+                if (k == Skip || k == LoadK) continue;
+                const Inst& in = F.insts[id];
+                auto lane_val = [&](Val v, int l) {
+                    if (v.param) return v;
+                    auto it = lanes[u].find(v.idx);
+                    if (it != lanes[u].end()) return it->second[l];
+                    return E.at(v.idx);
+                };
+                if (k == StoreK) {
+                    std::vector<Val> ls;
+                    for (int l = 0; l < V; l++) ls.push_back(lane_val(in.ops[1], l));
+                    const Addr& a = addr_of[id];
+                    Val vec = b.build(Ty::vec(in.aux.sc, (uint8_t)V), ls);
+                    b.store(Ty::vec(in.aux.sc, (uint8_t)V), Space::Global, vaddr(u, a), vec, (uint32_t)(V * a.esz));
+                    continue;
+                }
+                std::vector<Val> ls;
+                for (int l = 0; l < V; l++) {
+                    Inst cl = in;
+                    for (Val& v : cl.ops) v = lane_val(v, l);
+                    ls.push_back(b.push(cl));
+                }
+                lanes[u][id] = ls;
+            }
+    };
+
+    b.at(vhead); b.br(U > 1 ? uloop : vloop);
+    b.at(uloop);
+    Val ju = b.phi(I64);
+    Val last = b.bin(BinOp::Add, I64, ju, b.bin(BinOp::Mul, I64, T, b.ci(I64, U - 1)));
+    b.condbr(b.icmp(ICmp::Slt, I64, last, nv), ubody, vloop);
+    b.at(ubody);
+    vector_iters(ju, U);
+    Val ju2 = b.bin(BinOp::Add, I64, ju, b.bin(BinOp::Mul, I64, T, b.ci(I64, U)));
+    b.br(uloop);
+    b.phi_in(ju, vhead, g);
+    b.phi_in(ju, ubody, ju2);
+    b.at(vloop);
+    Val j = b.phi(I64);
+    b.condbr(b.icmp(ICmp::Slt, I64, j, nv), vbody, tail);
+    b.at(vbody);
+    vector_iters(j, 1);
+    Val j2 = b.bin(BinOp::Add, I64, j, T);
+    b.br(vloop);
+    if (U > 1) b.phi_in(j, uloop, ju); else b.phi_in(j, vhead, g);
+    b.phi_in(j, vbody, j2);
+    b.at(tail);
+    Val done = b.bin(BinOp::Shl, I64, nv, b.ci(I64, log2i(V)));
+    Val rem = b.bin(BinOp::Sub, I64, lim, done);
+    b.condbr(b.icmp(ICmp::Slt, I64, g, rem), tbody, exitb);
+    b.at(tbody);
+    scalar_clone(b.cast(CastOp::Trunc, I32, I64, b.bin(BinOp::Add, I64, done, g)));
+    b.br(exitb);
+    b.at(sguard); b.condbr(guard, sbody, exitb);
+    b.at(sbody); scalar_clone(g32); b.br(exitb);
+    b.at(exitb); b.ret();
+    if (U == 1) { /* uloop/ubody unreachable; simplify_cfg removes them */ }
+    F = std::move(b.f);
+    simplify_cfg(F);
+    dce(F);
+    if (rep) { rep->elementwise = true; rep->vec_lanes = V; rep->unroll = U; }
+    return true;
+}
+
+// ---- strided reduction loop vectoriser -----------------------------------------------------
+bool vectorize_reduction_loop(Function& F, int max_unroll, OptReport* rep) {
+    if (!F.is_kernel || F.blocks.size() < 4) return false;
+    const Term& t0 = F.blocks[0].term;
+    if (t0.kind != Term::Br) return false;
+    uint32_t H = t0.t;
+    if (H == 0) return false;
+    const Block& hb = F.blocks[H];
+    if (hb.term.kind != Term::CondBr || hb.insts.size() != 3) return false;
+    uint32_t L = hb.term.t, X = hb.term.f;
+    if (L == 0 || L == H || X == 0 || X == H || X == L) return false;
+    const Block& lb = F.blocks[L];
+    if (lb.term.kind != Term::Br || lb.term.t != H) return false;
+    for (uint32_t id : F.blocks[0].insts) {
+        Opc o = F.insts[id].op;
+        if (o != Opc::Index && o != Opc::ConstI && o != Opc::ConstF && o != Opc::Bin && o != Opc::ICmp && o != Opc::Cast) return false;
+    }
+    // header: two phis and the bound compare
+    uint32_t iphi = UINT32_MAX, aphi = UINT32_MAX, cmp = UINT32_MAX;
+    for (uint32_t id : hb.insts) {
+        const Inst& in = F.insts[id];
+        if (in.op == Opc::ICmp) cmp = id;
+        else if (in.op != Opc::Phi || in.ty != I32 || in.ops.size() != 2) return false;
+    }
+    if (cmp == UINT32_MAX || hb.term.val != Val::V(cmp)) return false;
+    const Inst& cin = F.insts[cmp];
+    if ((ICmp)cin.sub != ICmp::Slt || cin.aux != I32 || cin.ops[0].param) return false;
+    iphi = cin.ops[0].idx;
+    Val n = cin.ops[1];
+    if (F.insts[iphi].op != Opc::Phi) return false;
+    if (!n.param && std::find(F.blocks[0].insts.begin(), F.blocks[0].insts.end(), n.idx) == F.blocks[0].insts.end()) return false;
+    for (uint32_t id : hb.insts) if (F.insts[id].op == Opc::Phi && id != iphi) aphi = id;
+    if (aphi == UINT32_MAX) return false;
+    auto incoming = [&](uint32_t phi, uint32_t from, Val* out) {
+        const Inst& p = F.insts[phi];
+        for (size_t k = 0; k < p.ops.size(); k++) if (p.phi_blocks[k] == from) { *out = p.ops[k]; return true; }
+        return false;
+    };
+    Val i0, inext, a0, anext;
+    if (!incoming(iphi, 0, &i0) || !incoming(iphi, L, &inext) || !incoming(aphi, 0, &a0) || !incoming(aphi, L, &anext)) return false;
+    if (!is_linear_index(F, i0)) return false;
+    Val sx, sy;
+    if (!is_bin(F, inext, BinOp::Add, &sx, &sy)) return false;
+    Val stride = sx == Val::V(iphi) ? sy : sx;
+    if (!(sx == Val::V(iphi) || sy == Val::V(iphi)) || !is_grid_stride(F, stride)) return false;
+    RedOp op;
+    Val cx, cy;
+    uint32_t cmp2;
+    if (!match_combine(F, anext, &op, &cx, &cy, &cmp2)) return false;
+    Val loaded = cx == Val::V(aphi) ? cy : cx;
+    if (!(cx == Val::V(aphi) || cy == Val::V(aphi)) || loaded.param) return false;
+    const Inst& ld = F.insts[loaded.idx];
+    if (ld.op != Opc::Load || ld.ty != I32 || ld.vol || ld.space != Space::Global || ld.align < 4) return false;
+    Addr a;
+    if (!match_addr(F, ld.ops[0], Val::V(iphi), &a) || a.esz != 4) return false;
+    if (!a.base.param && std::find(F.blocks[0].insts.begin(), F.blocks[0].insts.end(), a.base.idx) == F.blocks[0].insts.end()) return false;
+    // the latch may contain nothing but the pieces matched above
+    std::set<uint32_t> allowed{loaded.idx, anext.idx, inext.idx};
+    if (cmp2 != UINT32_MAX) allowed.insert(cmp2);
+    {
+        const Inst& ad = F.insts[ld.ops[0].idx];
+        allowed.insert(ld.ops[0].idx);
+        for (Val v : ad.ops) if (!v.param && v != a.base) {
+            allowed.insert(v.idx);
+            for (Val w : F.insts[v.idx].ops) if (!w.param) { allowed.insert(w.idx); }
+        }
+    }
+    for (uint32_t id : lb.insts) {
+        if (allowed.count(id)) continue;
+        if (F.insts[id].op == Opc::ConstI) continue;
+        return false;
+    }
+    // Values defined in the loop must not be used after it, except the accumulator phi.
+    std::set<uint32_t> loop_ids(hb.insts.begin(), hb.insts.end());
+    loop_ids.insert(lb.insts.begin(), lb.insts.end());
+    std::set<uint32_t> entry_ids(F.blocks[0].insts.begin(), F.blocks[0].insts.end());
+    std::vector<uint32_t> rest;   // blocks other than 0, H, L
+    for (uint32_t bi = 1; bi < F.blocks.size(); bi++) if (bi != H && bi != L) rest.push_back(bi);
+    for (uint32_t bi : rest) {
+        auto bad = [&](Val v) { return !v.param && loop_ids.count(v.idx) && v.idx != aphi; };
+        for (uint32_t id : F.blocks[bi].insts) {
+            const Inst& in = F.insts[id];
+            for (Val v : in.ops) if (bad(v)) return false;
+            if (in.op == Opc::Phi) for (uint32_t pb : in.phi_blocks) if (pb == 0 || pb == L) return false;
+        }
+        if (F.blocks[bi].term.has_val && bad(F.blocks[bi].term.val)) return false;
+        std::vector<uint32_t> succ;
+        successors(F.blocks[bi].term, succ);
+        for (uint32_t s : succ) if (s == 0 || s == H || s == L) return false;
+    }
+    for (uint32_t id : F.blocks[X].insts) if (F.insts[id].op == Opc::Phi) return false;
+
+    const int V = 4;
+    int U = std::max(1, std::min(4, max_unroll));
+
+    FB b;
+    b.f.name = F.name; b.f.is_kernel = true; b.f.params = F.params; b.f.ret = F.ret;
+    uint32_t entry = b.block();
+    b.at(entry);
+    std::map<uint32_t, Val> E;
+    for (uint32_t id : F.blocks[0].insts) {
+        Inst in = F.insts[id];
+        for (Val& v : in.ops) if (!v.param) v = E.at(v.idx);
+        E[id] = b.push(in);
+    }
+    auto mapE = [&](Val v) { return v.param ? v : E.at(v.idx); };
+    Val base = mapE(a.base), init = mapE(a0);
+    Val g = b.cast(CastOp::SExt, I64, I32, mapE(i0));
+    Val T = b.cast(CastOp::SExt, I64, I32, mapE(stride));
+    Val n64 = b.cast(CastOp::SExt, I64, I32, mapE(n));
+    Val zero = b.ci(I64, 0);
+    Val nn = b.select(I64, b.icmp(ICmp::Slt, I64, n64, zero), zero, n64);
+    Val nv = b.bin(BinOp::AShr, I64, nn, b.ci(I64, 2));
+    Val aligned = b.icmp(ICmp::Eq, I64, b.bin(BinOp::And, I64, b.cast(CastOp::Bitcast, I64, PG, base), b.ci(I64, 15)), zero);
+    uint32_t vhead = b.block(), uloop = b.block(), ubody = b.block(), vloop = b.block(), vbody = b.block(), vexit = b.block(),
+             sloop = b.block(), sbody = b.block();
+    b.condbr(aligned, vhead, sloop);
+    auto vec_iters = [&](Val j, Val acc, int count) {
+        std::vector<Val> vecs;
+        Val jj = j;
+        for (int u = 0; u < count; u++) {
+            if (u) jj = b.bin(BinOp::Add, I64, jj, T);
+            Val p = b.bin(BinOp::Add, PG, base, b.bin(BinOp::Mul, I64, jj, b.ci(I64, 16)));
+            vecs.push_back(b.load(Ty::vec(Scalar::I32, V), Space::Global, p, 16));
+        }
+        for (Val vec : vecs) {
+            Val e0 = b.extract(I32, vec, 0), e1 = b.extract(I32, vec, 1), e2 = b.extract(I32, vec, 2), e3 = b.extract(I32, vec, 3);
+            Val t = emit_combine(b, op, emit_combine(b, op, e0, e1), emit_combine(b, op, e2, e3));
+            acc = emit_combine(b, op, acc, t);
+        }
+        return acc;
+    };
+    b.at(vhead); b.br(U > 1 ? uloop : vloop);
+    b.at(uloop);
+    Val ju = b.phi(I64), au = b.phi(I32);
+    Val last = b.bin(BinOp::Add, I64, ju, b.bin(BinOp::Mul, I64, T, b.ci(I64, U - 1)));
+    b.condbr(b.icmp(ICmp::Slt, I64, last, nv), ubody, vloop);
+    b.at(ubody);
+    Val au2 = vec_iters(ju, au, U);
+    Val ju2 = b.bin(BinOp::Add, I64, ju, b.bin(BinOp::Mul, I64, T, b.ci(I64, U)));
+    b.br(uloop);
+    b.phi_in(ju, vhead, g); b.phi_in(ju, ubody, ju2);
+    b.phi_in(au, vhead, init); b.phi_in(au, ubody, au2);
+    b.at(vloop);
+    Val j = b.phi(I64), av = b.phi(I32);
+    b.condbr(b.icmp(ICmp::Slt, I64, j, nv), vbody, vexit);
+    b.at(vbody);
+    Val av2 = vec_iters(j, av, 1);
+    Val j2 = b.bin(BinOp::Add, I64, j, T);
+    b.br(vloop);
+    if (U > 1) { b.phi_in(j, uloop, ju); b.phi_in(av, uloop, au); } else { b.phi_in(j, vhead, g); b.phi_in(av, vhead, init); }
+    b.phi_in(j, vbody, j2); b.phi_in(av, vbody, av2);
+    b.at(vexit);
+    Val tstart = b.bin(BinOp::Add, I64, b.bin(BinOp::Shl, I64, nv, b.ci(I64, 2)), g);
+    b.br(sloop);
+    b.at(sloop);
+    Val si = b.phi(I64), sa = b.phi(I32);
+    // remaining blocks are cloned after the loop; reserve their indices now
+    std::map<uint32_t, uint32_t> bmap;
+    for (uint32_t bi : rest) bmap[bi] = b.block();
+    b.at(sloop);
+    b.condbr(b.icmp(ICmp::Slt, I64, si, nn), sbody, bmap.at(X));
+    b.at(sbody);
+    Val sp = b.bin(BinOp::Add, PG, base, b.bin(BinOp::Mul, I64, si, b.ci(I64, 4)));
+    Val sa2 = emit_combine(b, op, sa, b.load(I32, Space::Global, sp, 4));
+    Val si2 = b.bin(BinOp::Add, I64, si, T);
+    b.br(sloop);
+    b.phi_in(si, entry, g); b.phi_in(si, vexit, tstart); b.phi_in(si, sbody, si2);
+    b.phi_in(sa, entry, init); b.phi_in(sa, vexit, av); b.phi_in(sa, sbody, sa2);
+    // clone the rest of the function
+    std::map<uint32_t, Val> M;
+    for (uint32_t bi : rest)
+        for (uint32_t id : F.blocks[bi].insts) {
+            if (!F.insts[id].has_result()) continue;
+            // reserve ids in order so forward references (phis) resolve
+        }
+    // two passes: first allocate instructions, then patch operands
+    std::vector<std::pair<uint32_t, uint32_t>> placed;   // (old id, new id)
+    for (uint32_t bi : rest) {
+        b.at(bmap.at(bi));
+        for (uint32_t id : F.blocks[bi].insts) {
+            Val r = b.push(F.insts[id]);
+            placed.push_back({id, r.idx});
+            M[id] = r;
+        }
+    }
+    auto mapR = [&](Val v) {
+        if (v.param) return v;
+        if (v.idx == aphi) return sa;
+        auto it = M.find(v.idx);
+        if (it != M.end()) return it->second;
+        return E.at(v.idx);
+    };
+    for (auto& pr : placed) {
+        Inst& in = b.f.insts[pr.second];
+        for (Val& v : in.ops) v = mapR(v);
+        for (uint32_t& pb : in.phi_blocks) pb = pb == H ? sloop : bmap.at(pb);
+    }
+    for (uint32_t bi : rest) {
+        Term t = F.blocks[bi].term;
+        if (t.has_val) t.val = mapR(t.val);
+        if (t.kind != Term::Ret) t.t = bmap.at(t.t);
+        if (t.kind == Term::CondBr) t.f = bmap.at(t.f);
+        for (auto& cs : t.cases) cs.second = bmap.at(cs.second);
+        b.f.blocks[bmap.at(bi)].term = t;
+    }
+    F = std::move(b.f);
+    simplify_cfg(F);
+    dce(F);
+    if (rep) { rep->reduction = true; rep->vec_lanes = V; rep->unroll = U; }
+    return true;
+}
+
+// ---- shuffle butterfly -> warp.reduce ------------------------------------------------------
+int fuse_warp_reductions(Function& F) {
+    int fused = 0;
+    for (auto& blk : F.blocks) {
+        bool again = true;
+        while (again) {
+            again = false;
+            std::set<uint32_t> in_block(blk.insts.begin(), blk.insts.end());
+            for (size_t pos = 0; pos < blk.insts.size() && !again; pos++) {
+                uint32_t s0 = blk.insts[pos];
+                const Inst& first = F.insts[s0];
+                if (first.op != Opc::Shuffle || (Shfl)first.sub != Shfl::Xor || first.ty != I32) continue;
+                Val v0 = first.ops[0], cur = v0;
+                unsigned seen = 0;
+                RedOp op = RedOp::Max;
+                bool ok = true;
+                for (int step = 0; step < 5 && ok; step++) {
+                    bool found = false;
+                    for (uint32_t sid : blk.insts) {
+                        const Inst& s = F.insts[sid];
+                        int64_t mask;
+                        if (s.op != Opc::Shuffle || (Shfl)s.sub != Shfl::Xor || s.ty != I32 || s.ops[0] != cur || !const_int(F, s.ops[1], &mask)) continue;
+                        if (mask != 1 && mask != 2 && mask != 4 && mask != 8 && mask != 16) continue;
+                        if (seen & (unsigned)mask) continue;
+                        for (uint32_t cid : blk.insts) {
+                            RedOp o2;
+                            Val x, y;
+                            uint32_t cmpid;
+                            if (!match_combine(F, Val::V(cid), &o2, &x, &y, &cmpid)) continue;
+                            if (!((x == cur && y == Val::V(sid)) || (y == cur && x == Val::V(sid)))) continue;
+                            if (cmpid != UINT32_MAX && !in_block.count(cmpid)) continue;
+                            if (step > 0 && o2 != op) continue;
+                            op = o2;
+                            seen |= (unsigned)mask;
+                            cur = Val::V(cid);
+                            found = true;
+                            break;
+                        }
+                        if (found) break;
+                    }
+                    ok = found;
+                }
+                if (!ok || seen != 31) continue;
+                // insert warp.reduce where the final combine stood
+                uint32_t fin = cur.idx;
+                Inst wr;
+                wr.op = Opc::WarpReduce;
+                wr.sub = (uint8_t)op;
+                wr.ty = I32;
+                wr.ops = {v0};
+                uint32_t wid = (uint32_t)F.insts.size();
+                F.insts.push_back(wr);
+                replace_uses(F, Val::V(fin), Val::V(wid));
+                F.insts[wid].ops[0] = v0;   // v0 itself is never the final combine
+                auto it = std::find(blk.insts.begin(), blk.insts.end(), fin);
+                blk.insts.insert(it, wid);
+                fused++;
+                again = true;
+            }
+            if (again) dce(F);
+        }
+    }
+    return fused;
+}
+
+// ---- liveness / register estimate ----------------------------------------------------------
+static int weight(Ty t) {
+    switch (t.kind) {
+        case Ty::Void: return 0;
+        case Ty::Ptr: return 2;
+        case Ty::Sc: return t.sc == Scalar::I1 ? 0 : (scalar_bits(t.sc) > 32 ? 2 : 1);
+        case Ty::Vec: return t.lanes * (scalar_bits(t.sc) > 32 ? 2 : 1);
+    }
+    return 0;
+}
+
+int estimate_registers(const Function& f) {
+    const size_t NP = f.params.size(), NV = NP + f.insts.size();
+    auto key = [&](Val v) { return v.param ? v.idx : NP + v.idx; };
+    const size_t NB = f.blocks.size();
+    std::vector<std::vector<char>> live_in(NB, std::vector<char>(NV, 0)), live_out(NB, std::vector<char>(NV, 0));
+    std::vector<uint32_t> succ;
+    bool changed = true;
+    while (changed) {
+        changed = false;
+        for (size_t bi = NB; bi-- > 0;) {
+            const Block& b = f.blocks[bi];
+            std::vector<char> out(NV, 0);
+            successors(b.term, succ);
+            for (uint32_t s : succ) {
+                for (size_t v = 0; v < NV; v++) if (live_in[s][v]) out[v] = 1;
+                // phi operands are live out of the matching predecessor only
+                for (uint32_t id : f.blocks[s].insts) {
+                    const Inst& in = f.insts[id];
+                    if (in.op != Opc::Phi) continue;
+                    out[NP + id] = 0;
+                    for (size_t k = 0; k < in.ops.size(); k++) if (in.phi_blocks[k] == bi) out[key(in.ops[k])] = 1;
+                }
+            }
+            std::vector<char> in = out;
+            if (b.term.has_val) in[key(b.term.val)] = 1;
+            for (size_t p = b.insts.size(); p-- > 0;) {
+                uint32_t id = b.insts[p];
+                const Inst& ins = f.insts[id];
+                in[NP + id] = 0;
+                if (ins.op != Opc::Phi) for (Val v : ins.ops) in[key(v)] = 1;
+            }
+            for (uint32_t id : b.insts) if (f.insts[id].op == Opc::Phi) in[NP + id] = 1;
+            if (in != live_in[bi] || out != live_out[bi]) { live_in[bi] = in; live_out[bi] = out; changed = true; }
+        }
+    }
+    auto wt = [&](size_t v) { return v < NP ? weight(f.params[v]) : weight(f.insts[v - NP].ty); };
+    int peak = 0;
+    for (size_t bi = 0; bi < NB; bi++) {
+        const Block& b = f.blocks[bi];
+        std::vector<char> live = live_out[bi];
+        if (b.term.has_val) live[key(b.term.val)] = 1;
+        int cur = 0;
+        for (size_t v = 0; v < NV; v++) if (live[v]) cur += wt(v);
+        peak = std::max(peak, cur);
+        for (size_t p = b.insts.size(); p-- > 0;) {
+            uint32_t id = b.insts[p];
+            const Inst& ins = f.insts[id];
+            if (live[NP + id]) { live[NP + id] = 0; cur -= wt(NP + id); }
+            if (ins.op != Opc::Phi)
+                for (Val v : ins.ops) if (!live[key(v)]) { live[key(v)] = 1; cur += wt(key(v)); }
+            peak = std::max(peak, cur);
+        }
+    }
+    return peak + 8;   // address temporaries, special registers, the ABI's reserved ones
+}
+
+void optimize_module(Module& m, int opt_level, int reg_budget, std::vector<OptReport>* reports) {
+    inline_calls(m);
+    for (auto& f : m.funcs) {
+        OptReport rep;
+        simplify_cfg(f);
+        dce(f);
+        if (opt_level > 0) {
+            rep.warp_reduces = fuse_warp_reductions(f);
+            bool done = false;
+            for (int U = 4; U >= 1 && !done; U >>= 1) {
+                Function cand = f;
+                OptReport r = rep;
+                if (!vectorize_elementwise(cand, U, &r) && !vectorize_reduction_loop(cand, U, &r)) break;
+                int est = estimate_registers(cand);
+                if (est <= reg_budget || U == 1) { f = std::move(cand); rep = r; rep.est_regs = est; done = true; }
+            }
+        }
+        if (!rep.est_regs) rep.est_regs = estimate_registers(f);
+        canonicalize(f);
+        if (reports) reports->push_back(rep);
+    }
+}
+
+}  // namespace basalt

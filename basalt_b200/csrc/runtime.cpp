@@ -1,0 +1,578 @@
+// Launch runtime over the CUDA Driver API, resolved with dlopen so the library loads on a
+// machine without a GPU. Stands in for crates/basalt-runtime/src/{dl,driver,context,module,
+// ffi,error}.rs of the reference; see include/basalt_b200.h for the entry-by-entry mapping.
+//
+// Differences from the reference runtime, all deliberate:
+//   * the device's primary context is retained instead of cuCtxCreate (driver.rs:143-159), so
+//     device memory, streams and NCCL communicators are shared with the CUDA runtime in-process;
+//   * launches take a stream and do not synchronise (module.rs:101-122 synchronises every launch);
+//   * cuModuleLoadDataEx captures the JIT log (context.rs:43-61 uses cuModuleLoadData);
+//   * kernels whose emitted PTX carries a `//!basalt.plan` line get their CUtensorMap
+//     parameters built and appended at launch.
+#include <cuda.h>
+#include <dlfcn.h>
+#include <nccl.h>
+
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <sstream>
+#include <string>
+#include <vector>
+
+#include "../../include/basalt_b200.h"
+
+namespace {
+
+thread_local basalt_rt_error g_err;
+
+int set_err(int kind, int code, const char* call, const std::string& msg) {
+    memset(&g_err, 0, sizeof g_err);
+    g_err.kind = kind;
+    g_err.code = code;
+    strncpy(g_err.call, call, sizeof g_err.call - 1);
+    strncpy(g_err.message, msg.c_str(), sizeof g_err.message - 1);
+    return kind;
+}
+
+struct Fns {
+    CUresult (*cuInit)(unsigned);
+    CUresult (*cuDeviceGetCount)(int*);
+    CUresult (*cuDeviceGet)(CUdevice*, int);
+    CUresult (*cuDeviceGetAttribute)(int*, CUdevice_attribute, CUdevice);
+    CUresult (*cuDevicePrimaryCtxRetain)(CUcontext*, CUdevice);
+    CUresult (*cuDevicePrimaryCtxRelease)(CUdevice);
+    CUresult (*cuCtxSetCurrent)(CUcontext);
+    CUresult (*cuCtxSynchronize)();
+    CUresult (*cuModuleLoadDataEx)(CUmodule*, const void*, unsigned, CUjit_option*, void**);
+    CUresult (*cuModuleUnload)(CUmodule);
+    CUresult (*cuModuleGetFunction)(CUfunction*, CUmodule, const char*);
+    CUresult (*cuFuncSetAttribute)(CUfunction, CUfunction_attribute, int);
+    CUresult (*cuLaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream, void**, void**);
+    CUresult (*cuMemAlloc)(CUdeviceptr*, size_t);
+    CUresult (*cuMemFree)(CUdeviceptr);
+    CUresult (*cuMemcpyHtoD)(CUdeviceptr, const void*, size_t);
+    CUresult (*cuMemcpyDtoH)(void*, CUdeviceptr, size_t);
+    CUresult (*cuMemcpyHtoDAsync)(CUdeviceptr, const void*, size_t, CUstream);
+    CUresult (*cuMemcpyDtoHAsync)(void*, CUdeviceptr, size_t, CUstream);
+    CUresult (*cuMemAllocHost)(void**, size_t);
+    CUresult (*cuMemFreeHost)(void*);
+    CUresult (*cuStreamCreate)(CUstream*, unsigned);
+    CUresult (*cuStreamDestroy)(CUstream);
+    CUresult (*cuStreamSynchronize)(CUstream);
+    CUresult (*cuEventCreate)(CUevent*, unsigned);
+    CUresult (*cuEventDestroy)(CUevent);
+    CUresult (*cuEventRecord)(CUevent, CUstream);
+    CUresult (*cuEventSynchronize)(CUevent);
+    CUresult (*cuEventElapsedTime)(float*, CUevent, CUevent);
+    CUresult (*cuGetErrorString)(CUresult, const char**);
+    CUresult (*cuTensorMapEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                       const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                       CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+};
+
+}  // namespace
+
+struct basalt_rt_driver {
+    void* lib = nullptr;
+    Fns f{};
+};
+struct basalt_rt_ctx {
+    basalt_rt_driver* drv = nullptr;
+    CUdevice dev = 0;
+    CUcontext ctx = nullptr;
+};
+namespace {
+struct TmapSpec {
+    int param = 0;          // index of the pointer parameter the map is built over
+    unsigned esz = 2;       // element bytes
+    uint64_t inner = 0;     // elements per row
+    uint64_t row_bytes = 0; // stride between rows
+    unsigned box_inner = 0, box_outer = 0;
+    unsigned swizzle = 0;   // bytes: 0, 32, 64, 128
+};
+struct Plan {
+    unsigned block[3] = {0, 0, 0};
+    unsigned grid[3] = {0, 0, 0};
+    unsigned smem = 0;
+    unsigned nparams = 0;   // number of BIR parameters (tensor maps follow them)
+    std::vector<TmapSpec> tmaps;
+};
+}  // namespace
+struct basalt_rt_module {
+    basalt_rt_ctx* ctx = nullptr;
+    CUmodule mod = nullptr;
+    std::map<std::string, Plan> plans;
+};
+struct basalt_rt_function {
+    basalt_rt_module* mod = nullptr;
+    CUfunction fn = nullptr;
+    bool has_plan = false;
+    Plan plan;
+};
+struct basalt_rt_buffer {
+    basalt_rt_ctx* ctx = nullptr;
+    CUdeviceptr ptr = 0;
+    size_t bytes = 0;
+};
+struct basalt_rt_comm {
+    basalt_rt_ctx* ctx = nullptr;
+    ncclComm_t comm = nullptr;
+};
+
+namespace {
+
+// check() of the reference (driver.rs:65-90): a failing CUresult becomes DriverCallFailed with
+// the driver's own message.
+int check(const Fns& f, const char* call, CUresult rc) {
+    if (rc == CUDA_SUCCESS) return 0;
+    const char* msg = nullptr;
+    std::string m;
+    if (f.cuGetErrorString && f.cuGetErrorString(rc, &msg) == CUDA_SUCCESS && msg) m = msg;
+    else m = "unknown CUDA error " + std::to_string((int)rc);
+    return set_err(3, (int)rc, call, m);
+}
+
+template <class F>
+bool resolve(void* lib, F* out, std::initializer_list<const char*> names) {
+    for (const char* n : names) {
+        void* p = dlsym(lib, n);
+        if (p) { *out = reinterpret_cast<F>(p); return true; }
+    }
+    set_err(2, 0, "dlsym", std::string("CUDA driver symbol not found: ") + *names.begin());
+    return false;
+}
+
+int make_current(basalt_rt_ctx* c) { return check(c->drv->f, "cuCtxSetCurrent", c->drv->f.cuCtxSetCurrent(c->ctx)); }
+
+// ---- NCCL, resolved lazily ------------------------------------------------------------------
+struct Nccl {
+    void* lib = nullptr;
+    ncclResult_t (*GetUniqueId)(ncclUniqueId*);
+    ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int);
+    ncclResult_t (*CommDestroy)(ncclComm_t);
+    ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t);
+    ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t);
+    const char* (*GetErrorString)(ncclResult_t);
+};
+Nccl* nccl() {
+    static Nccl n;
+    static bool tried = false, ok = false;
+    if (!tried) {
+        tried = true;
+        n.lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+        if (!n.lib) n.lib = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+        if (n.lib) {
+            ok = resolve(n.lib, &n.GetUniqueId, {"ncclGetUniqueId"}) && resolve(n.lib, &n.CommInitRank, {"ncclCommInitRank"}) &&
+                 resolve(n.lib, &n.CommDestroy, {"ncclCommDestroy"}) && resolve(n.lib, &n.AllReduce, {"ncclAllReduce"}) &&
+                 resolve(n.lib, &n.AllGather, {"ncclAllGather"}) && resolve(n.lib, &n.GetErrorString, {"ncclGetErrorString"});
+        }
+    }
+    if (!ok) { set_err(1, 0, "dlopen", "NCCL library not found (libnccl.so.2)"); return nullptr; }
+    return &n;
+}
+int nccl_check(Nccl* n, const char* call, ncclResult_t rc) {
+    if (rc == ncclSuccess) return 0;
+    return set_err(5, (int)rc, call, n->GetErrorString(rc));
+}
+
+// Parses the `//!basalt.plan <kernel> key=value ...` lines of an emitted module.
+void parse_plans(const char* ptx, std::map<std::string, Plan>* out) {
+    std::istringstream in(ptx);
+    std::string ln;
+    while (std::getline(in, ln)) {
+        if (ln.rfind("//!basalt.plan ", 0) != 0) continue;
+        std::istringstream ls(ln.substr(15));
+        std::string kernel, kv;
+        ls >> kernel;
+        Plan p;
+        while (ls >> kv) {
+            size_t eq = kv.find('=');
+            if (eq == std::string::npos) continue;
+            std::string k = kv.substr(0, eq), v = kv.substr(eq + 1);
+            if (k == "block") sscanf(v.c_str(), "%u,%u,%u", &p.block[0], &p.block[1], &p.block[2]);
+            else if (k == "grid") sscanf(v.c_str(), "%u,%u,%u", &p.grid[0], &p.grid[1], &p.grid[2]);
+            else if (k == "smem") p.smem = (unsigned)strtoul(v.c_str(), nullptr, 10);
+            else if (k == "params") p.nparams = (unsigned)strtoul(v.c_str(), nullptr, 10);
+            else if (k == "tmap") {
+                TmapSpec t;
+                unsigned long long inner = 0, rowb = 0;
+                if (sscanf(v.c_str(), "%d:%u:%llu:%llu:%u:%u:%u", &t.param, &t.esz, &inner, &rowb, &t.box_inner, &t.box_outer, &t.swizzle) == 7) {
+                    t.inner = inner;
+                    t.row_bytes = rowb;
+                    p.tmaps.push_back(t);
+                }
+            }
+        }
+        (*out)[kernel] = p;
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+void basalt_rt_last_error(basalt_rt_error* out) {
+    if (out) *out = g_err;
+}
+
+int basalt_rt_driver_load(basalt_rt_driver** out) {
+    if (!out) return set_err(4, 0, "basalt_rt_driver_load", "null output pointer");
+    *out = nullptr;
+    void* lib = dlopen("libcuda.so.1", RTLD_NOW);
+    if (!lib) lib = dlopen("libcuda.so", RTLD_NOW);
+    if (!lib) {
+        const char* e = dlerror();
+        return set_err(1, 0, "dlopen", std::string("CUDA driver library not found: ") + (e ? e : "libcuda.so.1"));
+    }
+    auto* d = new basalt_rt_driver;
+    d->lib = lib;
+    Fns& f = d->f;
+    bool ok = resolve(lib, &f.cuInit, {"cuInit"}) && resolve(lib, &f.cuDeviceGetCount, {"cuDeviceGetCount"}) &&
+              resolve(lib, &f.cuDeviceGet, {"cuDeviceGet"}) && resolve(lib, &f.cuDeviceGetAttribute, {"cuDeviceGetAttribute"}) &&
+              resolve(lib, &f.cuDevicePrimaryCtxRetain, {"cuDevicePrimaryCtxRetain"}) &&
+              resolve(lib, &f.cuDevicePrimaryCtxRelease, {"cuDevicePrimaryCtxRelease_v2", "cuDevicePrimaryCtxRelease"}) &&
+              resolve(lib, &f.cuCtxSetCurrent, {"cuCtxSetCurrent"}) && resolve(lib, &f.cuCtxSynchronize, {"cuCtxSynchronize"}) &&
+              resolve(lib, &f.cuModuleLoadDataEx, {"cuModuleLoadDataEx"}) && resolve(lib, &f.cuModuleUnload, {"cuModuleUnload"}) &&
+              resolve(lib, &f.cuModuleGetFunction, {"cuModuleGetFunction"}) && resolve(lib, &f.cuFuncSetAttribute, {"cuFuncSetAttribute"}) &&
+              resolve(lib, &f.cuLaunchKernel, {"cuLaunchKernel"}) && resolve(lib, &f.cuMemAlloc, {"cuMemAlloc_v2", "cuMemAlloc"}) &&
+              resolve(lib, &f.cuMemFree, {"cuMemFree_v2", "cuMemFree"}) && resolve(lib, &f.cuMemcpyHtoD, {"cuMemcpyHtoD_v2", "cuMemcpyHtoD"}) &&
+              resolve(lib, &f.cuMemcpyDtoH, {"cuMemcpyDtoH_v2", "cuMemcpyDtoH"}) &&
+              resolve(lib, &f.cuMemcpyHtoDAsync, {"cuMemcpyHtoDAsync_v2", "cuMemcpyHtoDAsync"}) &&
+              resolve(lib, &f.cuMemcpyDtoHAsync, {"cuMemcpyDtoHAsync_v2", "cuMemcpyDtoHAsync"}) &&
+              resolve(lib, &f.cuMemAllocHost, {"cuMemAllocHost_v2", "cuMemAllocHost"}) && resolve(lib, &f.cuMemFreeHost, {"cuMemFreeHost"}) &&
+              resolve(lib, &f.cuStreamCreate, {"cuStreamCreate"}) && resolve(lib, &f.cuStreamDestroy, {"cuStreamDestroy_v2", "cuStreamDestroy"}) &&
+              resolve(lib, &f.cuStreamSynchronize, {"cuStreamSynchronize"}) && resolve(lib, &f.cuEventCreate, {"cuEventCreate"}) &&
+              resolve(lib, &f.cuEventDestroy, {"cuEventDestroy_v2", "cuEventDestroy"}) && resolve(lib, &f.cuEventRecord, {"cuEventRecord"}) &&
+              resolve(lib, &f.cuEventSynchronize, {"cuEventSynchronize"}) && resolve(lib, &f.cuEventElapsedTime, {"cuEventElapsedTime"}) &&
+              resolve(lib, &f.cuGetErrorString, {"cuGetErrorString", "cuGetErrorName"}) &&
+              resolve(lib, &f.cuTensorMapEncodeTiled, {"cuTensorMapEncodeTiled"});
+    if (!ok) { dlclose(lib); delete d; return 2; }
+    int rc = check(f, "cuInit", f.cuInit(0));
+    if (rc) { dlclose(lib); delete d; return rc; }
+    *out = d;
+    return 0;
+}
+
+void basalt_rt_driver_unload(basalt_rt_driver* drv) {
+    if (!drv) return;
+    // The library handle is kept open: unloading libcuda under a live CUDA runtime is not safe.
+    delete drv;
+}
+
+int basalt_rt_device_count(basalt_rt_driver* drv, int* count) {
+    if (!drv || !count) return set_err(4, 0, "basalt_rt_device_count", "null argument");
+    return check(drv->f, "cuDeviceGetCount", drv->f.cuDeviceGetCount(count));
+}
+
+int basalt_rt_ctx_create(basalt_rt_driver* drv, int device_index, basalt_rt_ctx** out) {
+    if (!drv || !out) return set_err(4, 0, "basalt_rt_ctx_create", "null argument");
+    *out = nullptr;
+    CUdevice dev;
+    int rc = check(drv->f, "cuDeviceGet", drv->f.cuDeviceGet(&dev, device_index));
+    if (rc) return rc;
+    CUcontext ctx;
+    rc = check(drv->f, "cuDevicePrimaryCtxRetain", drv->f.cuDevicePrimaryCtxRetain(&ctx, dev));
+    if (rc) return rc;
+    auto* c = new basalt_rt_ctx;
+    c->drv = drv;
+    c->dev = dev;
+    c->ctx = ctx;
+    rc = make_current(c);
+    if (rc) { drv->f.cuDevicePrimaryCtxRelease(dev); delete c; return rc; }
+    *out = c;
+    return 0;
+}
+
+void basalt_rt_ctx_destroy(basalt_rt_ctx* ctx) {
+    if (!ctx) return;
+    ctx->drv->f.cuDevicePrimaryCtxRelease(ctx->dev);
+    delete ctx;
+}
+
+int basalt_rt_device_attr(basalt_rt_ctx* ctx, int attr, int* value) {
+    if (!ctx || !value) return set_err(4, 0, "basalt_rt_device_attr", "null argument");
+    return check(ctx->drv->f, "cuDeviceGetAttribute", ctx->drv->f.cuDeviceGetAttribute(value, (CUdevice_attribute)attr, ctx->dev));
+}
+
+int basalt_rt_module_load(basalt_rt_ctx* ctx, const char* ptx, basalt_rt_module** out) {
+    if (!ctx || !ptx || !out) return set_err(4, 0, "basalt_rt_module_load", "null argument");
+    *out = nullptr;
+    int rc = make_current(ctx);
+    if (rc) return rc;
+    static thread_local char log[8192];
+    log[0] = 0;
+    CUjit_option opt[] = {CU_JIT_ERROR_LOG_BUFFER, CU_JIT_ERROR_LOG_BUFFER_SIZE_BYTES};
+    void* val[] = {log, (void*)(uintptr_t)sizeof log};
+    CUmodule mod;
+    CUresult r = ctx->drv->f.cuModuleLoadDataEx(&mod, ptx, 2, opt, val);
+    if (r != CUDA_SUCCESS) {
+        check(ctx->drv->f, "cuModuleLoadData", r);
+        if (log[0]) {
+            std::string m = std::string(g_err.message) + ": " + log;
+            strncpy(g_err.message, m.c_str(), sizeof g_err.message - 1);
+        }
+        return 3;
+    }
+    auto* m = new basalt_rt_module;
+    m->ctx = ctx;
+    m->mod = mod;
+    parse_plans(ptx, &m->plans);
+    *out = m;
+    return 0;
+}
+
+void basalt_rt_module_unload(basalt_rt_module* mod) {
+    if (!mod) return;
+    mod->ctx->drv->f.cuModuleUnload(mod->mod);
+    delete mod;
+}
+
+int basalt_rt_get_function(basalt_rt_module* mod, const char* name, basalt_rt_function** out) {
+    if (!mod || !name || !out) return set_err(4, 0, "basalt_rt_get_function", "null argument");
+    *out = nullptr;
+    const Fns& f = mod->ctx->drv->f;
+    CUfunction fn;
+    int rc = check(f, "cuModuleGetFunction", f.cuModuleGetFunction(&fn, mod->mod, name));
+    if (rc) return rc;
+    auto* h = new basalt_rt_function;
+    h->mod = mod;
+    h->fn = fn;
+    auto it = mod->plans.find(name);
+    if (it != mod->plans.end()) {
+        h->has_plan = true;
+        h->plan = it->second;
+        if (h->plan.smem > 48 * 1024) {
+            rc = check(f, "cuFuncSetAttribute", f.cuFuncSetAttribute(fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)h->plan.smem));
+            if (rc) { delete h; return rc; }
+        }
+    }
+    *out = h;
+    return 0;
+}
+
+int basalt_rt_alloc(basalt_rt_ctx* ctx, size_t bytes, basalt_rt_buffer** out) {
+    if (!ctx || !out) return set_err(4, 0, "basalt_rt_alloc", "null argument");
+    *out = nullptr;
+    int rc = make_current(ctx);
+    if (rc) return rc;
+    CUdeviceptr p = 0;
+    rc = check(ctx->drv->f, "cuMemAlloc", ctx->drv->f.cuMemAlloc(&p, bytes ? bytes : 1));
+    if (rc) return rc;
+    auto* b = new basalt_rt_buffer;
+    b->ctx = ctx;
+    b->ptr = p;
+    b->bytes = bytes;
+    *out = b;
+    return 0;
+}
+
+void basalt_rt_buffer_free(basalt_rt_buffer* buf) {
+    if (!buf) return;
+    buf->ctx->drv->f.cuMemFree(buf->ptr);
+    delete buf;
+}
+
+uint64_t basalt_rt_buffer_ptr(const basalt_rt_buffer* buf) { return buf ? (uint64_t)buf->ptr : 0; }
+size_t basalt_rt_buffer_size(const basalt_rt_buffer* buf) { return buf ? buf->bytes : 0; }
+
+int basalt_rt_copy_from_host(basalt_rt_buffer* buf, const void* host, size_t bytes, void* stream) {
+    if (!buf || (!host && bytes)) return set_err(4, 0, "basalt_rt_copy_from_host", "null argument");
+    if (bytes > buf->bytes) return set_err(4, 0, "cuMemcpyHtoD", "host slice of " + std::to_string(bytes) + " bytes exceeds the device buffer of " + std::to_string(buf->bytes));
+    if (!bytes) return 0;
+    const Fns& f = buf->ctx->drv->f;
+    if (stream) return check(f, "cuMemcpyHtoDAsync", f.cuMemcpyHtoDAsync(buf->ptr, host, bytes, (CUstream)stream));
+    return check(f, "cuMemcpyHtoD", f.cuMemcpyHtoD(buf->ptr, host, bytes));
+}
+
+int basalt_rt_copy_to_host(const basalt_rt_buffer* buf, void* host, size_t bytes, void* stream) {
+    if (!buf || (!host && bytes)) return set_err(4, 0, "basalt_rt_copy_to_host", "null argument");
+    if (bytes > buf->bytes) return set_err(4, 0, "cuMemcpyDtoH", "host slice of " + std::to_string(bytes) + " bytes exceeds the device buffer of " + std::to_string(buf->bytes));
+    if (!bytes) return 0;
+    const Fns& f = buf->ctx->drv->f;
+    if (stream) return check(f, "cuMemcpyDtoHAsync", f.cuMemcpyDtoHAsync(host, buf->ptr, bytes, (CUstream)stream));
+    return check(f, "cuMemcpyDtoH", f.cuMemcpyDtoH(host, buf->ptr, bytes));
+}
+
+int basalt_rt_host_alloc(basalt_rt_ctx* ctx, size_t bytes, void** out) {
+    if (!ctx || !out) return set_err(4, 0, "basalt_rt_host_alloc", "null argument");
+    int rc = make_current(ctx);
+    if (rc) return rc;
+    return check(ctx->drv->f, "cuMemAllocHost", ctx->drv->f.cuMemAllocHost(out, bytes ? bytes : 1));
+}
+void basalt_rt_host_free(basalt_rt_ctx* ctx, void* p) {
+    if (ctx && p) ctx->drv->f.cuMemFreeHost(p);
+}
+
+int basalt_rt_planned_geometry(basalt_rt_function* fn, void** params, uint32_t grid[3], uint32_t block[3], uint32_t* smem) {
+    (void)params;
+    if (!fn) return set_err(4, 0, "basalt_rt_planned_geometry", "null argument");
+    for (int i = 0; i < 3; i++) {
+        if (grid) grid[i] = fn->has_plan ? fn->plan.grid[i] : 0;
+        if (block) block[i] = fn->has_plan ? fn->plan.block[i] : 0;
+    }
+    if (smem) *smem = fn->has_plan ? fn->plan.smem : 0;
+    return 0;
+}
+
+int basalt_rt_launch(basalt_rt_function* fn, const uint32_t grid[3], const uint32_t block[3], uint32_t shared_mem_bytes, void* stream, void** params) {
+    if (!fn || !grid || !block) return set_err(4, 0, "basalt_rt_launch", "null argument");
+    const Fns& f = fn->mod->ctx->drv->f;
+    if (!fn->has_plan || fn->plan.tmaps.empty()) {
+        if (fn->has_plan && fn->plan.block[0] && (block[0] != fn->plan.block[0] || block[1] != fn->plan.block[1] || block[2] != fn->plan.block[2]))
+            return set_err(4, 0, "cuLaunchKernel", "kernel was compiled for block (" + std::to_string(fn->plan.block[0]) + "," + std::to_string(fn->plan.block[1]) + "," + std::to_string(fn->plan.block[2]) + ")");
+        uint32_t sm = shared_mem_bytes ? shared_mem_bytes : (fn->has_plan ? fn->plan.smem : 0);
+        return check(f, "cuLaunchKernel", f.cuLaunchKernel(fn->fn, grid[0], grid[1], grid[2], block[0], block[1], block[2], sm, (CUstream)stream, params, nullptr));
+    }
+    const Plan& p = fn->plan;
+    if (block[0] != p.block[0] || block[1] != p.block[1] || block[2] != p.block[2])
+        return set_err(4, 0, "cuLaunchKernel", "kernel was compiled for block (" + std::to_string(p.block[0]) + "," + std::to_string(p.block[1]) + "," + std::to_string(p.block[2]) + ")");
+    if (!params) return set_err(4, 0, "cuLaunchKernel", "kernel takes parameters");
+    std::vector<CUtensorMap> maps(p.tmaps.size());
+    std::vector<void*> all(params, params + p.nparams);
+    for (size_t i = 0; i < p.tmaps.size(); i++) {
+        const TmapSpec& t = p.tmaps[i];
+        if ((unsigned)t.param >= p.nparams) return set_err(4, 0, "cuTensorMapEncodeTiled", "plan names a parameter the kernel does not have");
+        uint64_t base = *(uint64_t*)params[t.param];
+        if (base & 15) return set_err(4, 0, "cuTensorMapEncodeTiled", "matrix base address must be 16-byte aligned");
+        CUtensorMapDataType dt = t.esz == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : t.esz == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+        // The row count is not a kernel parameter; a kernel only requests boxes inside its own
+        // matrix, so the outer extent is left wide open.
+        cuuint64_t dims[2] = {t.inner, (cuuint64_t)1 << 24};
+        cuuint64_t strides[1] = {t.row_bytes};
+        cuuint32_t box[2] = {t.box_inner, t.box_outer};
+        cuuint32_t estr[2] = {1, 1};
+        CUtensorMapSwizzle sw = t.swizzle == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : t.swizzle == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : t.swizzle == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE;
+        int rc = check(f, "cuTensorMapEncodeTiled",
+                       f.cuTensorMapEncodeTiled(&maps[i], dt, 2, (void*)(uintptr_t)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
+        if (rc) return rc;
+        all.push_back(&maps[i]);
+    }
+    uint32_t sm = shared_mem_bytes ? shared_mem_bytes : p.smem;
+    return check(f, "cuLaunchKernel", f.cuLaunchKernel(fn->fn, grid[0], grid[1], grid[2], block[0], block[1], block[2], sm, (CUstream)stream, all.data(), nullptr));
+}
+
+int basalt_rt_ctx_sync(basalt_rt_ctx* ctx) {
+    if (!ctx) return set_err(4, 0, "basalt_rt_ctx_sync", "null argument");
+    int rc = make_current(ctx);
+    if (rc) return rc;
+    return check(ctx->drv->f, "cuCtxSynchronize", ctx->drv->f.cuCtxSynchronize());
+}
+
+int basalt_rt_stream_create(basalt_rt_ctx* ctx, void** out) {
+    if (!ctx || !out) return set_err(4, 0, "basalt_rt_stream_create", "null argument");
+    int rc = make_current(ctx);
+    if (rc) return rc;
+    return check(ctx->drv->f, "cuStreamCreate", ctx->drv->f.cuStreamCreate((CUstream*)out, CU_STREAM_NON_BLOCKING));
+}
+int basalt_rt_stream_destroy(basalt_rt_ctx* ctx, void* s) { return ctx ? check(ctx->drv->f, "cuStreamDestroy", ctx->drv->f.cuStreamDestroy((CUstream)s)) : 4; }
+int basalt_rt_stream_sync(basalt_rt_ctx* ctx, void* s) { return ctx ? check(ctx->drv->f, "cuStreamSynchronize", ctx->drv->f.cuStreamSynchronize((CUstream)s)) : 4; }
+int basalt_rt_event_create(basalt_rt_ctx* ctx, void** out) {
+    if (!ctx || !out) return set_err(4, 0, "basalt_rt_event_create", "null argument");
+    int rc = make_current(ctx);
+    if (rc) return rc;
+    return check(ctx->drv->f, "cuEventCreate", ctx->drv->f.cuEventCreate((CUevent*)out, CU_EVENT_DEFAULT));
+}
+int basalt_rt_event_destroy(basalt_rt_ctx* ctx, void* e) { return ctx ? check(ctx->drv->f, "cuEventDestroy", ctx->drv->f.cuEventDestroy((CUevent)e)) : 4; }
+int basalt_rt_event_record(basalt_rt_ctx* ctx, void* e, void* s) { return ctx ? check(ctx->drv->f, "cuEventRecord", ctx->drv->f.cuEventRecord((CUevent)e, (CUstream)s)) : 4; }
+int basalt_rt_event_sync(basalt_rt_ctx* ctx, void* e) { return ctx ? check(ctx->drv->f, "cuEventSynchronize", ctx->drv->f.cuEventSynchronize((CUevent)e)) : 4; }
+int basalt_rt_event_elapsed_ms(basalt_rt_ctx* ctx, void* a, void* b, float* ms) {
+    return ctx ? check(ctx->drv->f, "cuEventElapsedTime", ctx->drv->f.cuEventElapsedTime(ms, (CUevent)a, (CUevent)b)) : 4;
+}
+
+int basalt_rt_cpu_launch(basalt_rt_ctx* ctx, basalt_rt_function* fn, const basalt_rt_arg* args, int nargs, int64_t nthreads, uint32_t block) {
+    if (!ctx || !fn || (nargs && !args) || nthreads < 0 || block == 0) return set_err(4, 0, "basalt_rt_cpu_launch", "bad argument");
+    std::vector<basalt_rt_buffer*> bufs(nargs, nullptr);
+    std::vector<uint64_t> dptrs(nargs, 0);
+    std::vector<void*> params(nargs, nullptr);
+    int rc = 0;
+    auto cleanup = [&]() { for (auto* b : bufs) basalt_rt_buffer_free(b); };
+    for (int i = 0; i < nargs && !rc; i++) {
+        const basalt_rt_arg& a = args[i];
+        if (a.kind >= 4) {
+            rc = basalt_rt_alloc(ctx, a.bytes, &bufs[i]);
+            if (rc) break;
+            // written-only buffers are uploaded too: the kernel may leave part of them untouched
+            rc = basalt_rt_copy_from_host(bufs[i], a.host, a.bytes, nullptr);
+            dptrs[i] = basalt_rt_buffer_ptr(bufs[i]);
+            params[i] = &dptrs[i];
+        } else params[i] = (void*)&a.value;
+    }
+    if (!rc && nthreads > 0) {
+        uint32_t grid[3] = {(uint32_t)((nthreads + block - 1) / block), 1, 1};
+        uint32_t blk[3] = {(uint32_t)(nthreads < (int64_t)block ? nthreads : block), 1, 1};
+        rc = basalt_rt_launch(fn, grid, blk, 0, nullptr, params.data());
+        if (!rc) rc = basalt_rt_ctx_sync(ctx);
+    }
+    for (int i = 0; i < nargs && !rc; i++)
+        if (args[i].kind == 5 || args[i].kind == 6) rc = basalt_rt_copy_to_host(bufs[i], args[i].host, args[i].bytes, nullptr);
+    cleanup();
+    return rc;
+}
+
+void basalt_rt_shard_range(uint64_t total, int nranks, int rank, uint64_t align, uint64_t* begin, uint64_t* end) {
+    if (align == 0) align = 1;
+    if (nranks < 1) nranks = 1;
+    uint64_t units = (total + align - 1) / align;   // aligned chunks, the last possibly partial
+    uint64_t per = units / (uint64_t)nranks, extra = units % (uint64_t)nranks;
+    uint64_t r = (uint64_t)rank;
+    uint64_t b = r * per + (r < extra ? r : extra), e = b + per + (r < extra ? 1 : 0);
+    b *= align;
+    e *= align;
+    if (b > total) b = total;
+    if (e > total) e = total;
+    if (begin) *begin = b;
+    if (end) *end = e;
+}
+
+int basalt_rt_comm_unique_id(char id_out[128]) {
+    Nccl* n = nccl();
+    if (!n) return 1;
+    ncclUniqueId id;
+    int rc = nccl_check(n, "ncclGetUniqueId", n->GetUniqueId(&id));
+    if (rc) return rc;
+    static_assert(sizeof id == 128, "ncclUniqueId is 128 bytes");
+    memcpy(id_out, &id, 128);
+    return 0;
+}
+
+int basalt_rt_comm_init(basalt_rt_ctx* ctx, const char id[128], int nranks, int rank, basalt_rt_comm** out) {
+    if (!ctx || !id || !out) return set_err(4, 0, "basalt_rt_comm_init", "null argument");
+    *out = nullptr;
+    Nccl* n = nccl();
+    if (!n) return 1;
+    int rc = make_current(ctx);
+    if (rc) return rc;
+    ncclUniqueId uid;
+    memcpy(&uid, id, 128);
+    ncclComm_t c;
+    rc = nccl_check(n, "ncclCommInitRank", n->CommInitRank(&c, nranks, uid, rank));
+    if (rc) return rc;
+    auto* h = new basalt_rt_comm;
+    h->ctx = ctx;
+    h->comm = c;
+    *out = h;
+    return 0;
+}
+
+void basalt_rt_comm_destroy(basalt_rt_comm* comm) {
+    if (!comm) return;
+    if (Nccl* n = nccl()) n->CommDestroy(comm->comm);
+    delete comm;
+}
+
+int basalt_rt_allreduce_max_i32(basalt_rt_comm* comm, uint64_t send, uint64_t recv, size_t count, void* stream) {
+    Nccl* n = nccl();
+    if (!n || !comm) return set_err(4, 0, "basalt_rt_allreduce_max_i32", "no communicator");
+    return nccl_check(n, "ncclAllReduce", n->AllReduce((const void*)(uintptr_t)send, (void*)(uintptr_t)recv, count, ncclInt32, ncclMax, comm->comm, (cudaStream_t)stream));
+}
+
+int basalt_rt_allgather(basalt_rt_comm* comm, uint64_t send, uint64_t recv, size_t bytes_per_rank, void* stream) {
+    Nccl* n = nccl();
+    if (!n || !comm) return set_err(4, 0, "basalt_rt_allgather", "no communicator");
+    return nccl_check(n, "ncclAllGather", n->AllGather((const void*)(uintptr_t)send, (void*)(uintptr_t)recv, bytes_per_rank, ncclUint8, comm->comm, (cudaStream_t)stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,43 @@
+"""The hand-written sm_100a kernels of include/basalt_b200_kernels.h. Every argument is a device
+pointer (int) or DeviceBuffer; launches are asynchronous on `stream`."""
+from __future__ import annotations
+
+import ctypes as C
+
+from ._lib import lib
+from .runtime import DeviceBuffer
+
+
+class KernelError(Exception):
+    pass
+
+
+def _p(x) -> C.c_void_p:
+    return C.c_void_p(x.device_ptr() if isinstance(x, DeviceBuffer) else int(x))
+
+
+def _check(rc: int):
+    if rc:
+        raise KernelError(f"{lib.basalt_k_last_error().decode()} (code {rc})")
+
+
+def vadd_i32(a, b, c, n: int, stream=None):
+    _check(lib.basalt_k_vadd_i32(_p(a), _p(b), _p(c), n, C.c_void_p(stream)))
+
+
+def max_i32(x, n: int, out, stream=None):
+    """atomicMax(out, max(x[0..n))); out must already hold the running maximum."""
+    _check(lib.basalt_k_max_i32(_p(x), n, _p(out), C.c_void_p(stream)))
+
+
+def helper_chain_u32(inp, out, n: int, stream=None):
+    _check(lib.basalt_k_helper_chain_u32(_p(inp), _p(out), n, C.c_void_p(stream)))
+
+
+def sgemm_f32(A, B, Cm, M: int, N: int, K: int, stream=None):
+    _check(lib.basalt_k_sgemm_f32(_p(A), _p(B), _p(Cm), M, N, K, C.c_void_p(stream)))
+
+
+def matmul_f16(A, B, Cm, M: int, N: int, K: int, b_is_nk: bool = False, status=None, stream=None):
+    _check(lib.basalt_k_matmul_f16(_p(A), _p(B), _p(Cm), M, N, K, int(b_is_nk), _p(status) if status is not None else None,
+                                   C.c_void_p(stream)))

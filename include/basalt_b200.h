@@ -1,0 +1,189 @@
+/* C ABI of the Basalt sm_100a device path: the Backend boundary (BIR text in, PTX text out) and
+ * the launch runtime (CUDA Driver API, JIT load, streams, sharding, NCCL).
+ *
+ * Every entry point states the reference interface it stands in for (paths inside the reference
+ * project).  All functions are re-entrant unless noted; none keeps a pointer passed to it beyond
+ * the call.  Return value: 0 on success unless documented otherwise.
+ */
+#ifndef BASALT_B200_H
+#define BASALT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)
+#endif
+
+/* ------------------------------------------------------------------------------------------
+ * Backend: the `Backend` trait (crates/basalt-backend/src/backend.rs:144-157) as implemented by
+ * `Ptx` (crates/basalt-ptx/src/emit.rs:1973-1994).  `&Module` crosses as BIR text, the form the
+ * reference CLI itself accepts (crates/basalt-cli/src/main.rs:517-520).
+ * ---------------------------------------------------------------------------------------- */
+
+/* EmitOpts (backend.rs:123-137). target_variant: NULL or "sm_100a". opt_level: 0 lowers one to
+ * one like the reference, 1/2 run the vectorising passes (2 is the default when opts is NULL).
+ * out_name_hint and snap are accepted and ignored, as Ptx::emit ignores them (emit.rs:1988). */
+typedef struct basalt_emit_opts {
+    const char *target_variant;
+    int opt_level;
+    const char *out_name_hint;
+    int snap;
+} basalt_emit_opts;
+
+/* Diag (crates/basalt-diag/src/diag.rs:62-66): the stable E-code string (ecode.rs:148-181) and
+ * the argument the reference would render into the message template. */
+typedef struct basalt_diag {
+    char code[8];
+    char message[504];
+} basalt_diag;
+
+/* Backend::name (backend.rs:146). */
+const char *basalt_b200_name(void);
+
+/* Backend::supports (backend.rs:148-151; Ptx: emit.rs:1981-1986). Returns 1 when the module can
+ * be emitted, 0 when refused (ecode_out receives e.g. "E090"), -1 when the text is not BIR
+ * (ecode_out receives "E400", crates/basalt-cli/src/main.rs:308-309). */
+int basalt_b200_supports(const char *bir, size_t len, char ecode_out[8]);
+
+/* Backend::emit (backend.rs:152-156; Ptx: emit.rs:1988-1993). On success *ptx_out is a
+ * NUL-terminated, malloc'd PTX module (free with basalt_b200_free) and the result is 0; on
+ * refusal the result is 1 and diag_out is filled. Deterministic for a given (bir, opts). */
+int basalt_b200_emit(const char *bir, size_t len, const basalt_emit_opts *opts, char **ptx_out,
+                     size_t *ptx_len, basalt_diag *diag_out);
+
+/* The module as the emitter lowers it, after inlining and the vectorising passes, printed as BIR.
+ * No reference counterpart (the reference has no backend passes); exists so the passes can be
+ * checked against the CPU oracle. */
+int basalt_b200_optimize(const char *bir, size_t len, const basalt_emit_opts *opts, char **bir_out,
+                         size_t *bir_len, basalt_diag *diag_out);
+
+/* basalt_bir::parse followed by basalt_bir::print (crates/basalt-bir/src/lib.rs:79-85): the
+ * round-trip the reference tests in crates/basalt-bir/tests/roundtrip.rs. */
+int basalt_b200_roundtrip(const char *bir, size_t len, char **bir_out, size_t *bir_len,
+                          basalt_diag *diag_out);
+
+void basalt_b200_free(void *p);
+
+/* ------------------------------------------------------------------------------------------
+ * Runtime: crates/basalt-runtime/src/{driver,context,module,ffi,error}.rs.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct basalt_rt_driver basalt_rt_driver;     /* CudaDriver   (driver.rs:94-163)   */
+typedef struct basalt_rt_ctx basalt_rt_ctx;           /* CudaContext  (context.rs:30-91)   */
+typedef struct basalt_rt_module basalt_rt_module;     /* CudaModule   (module.rs:11-60)    */
+typedef struct basalt_rt_function basalt_rt_function; /* CudaFunction (module.rs:62-123)   */
+typedef struct basalt_rt_buffer basalt_rt_buffer;     /* DeviceBuffer (context.rs:95-168)  */
+typedef struct basalt_rt_comm basalt_rt_comm;         /* no counterpart: the reference is single-GPU */
+
+/* CudaError (error.rs:9-22). kind: 1 DriverNotFound, 2 SymbolNotFound, 3 DriverCallFailed,
+ * 4 a host-side check of this runtime (bounds, arguments), 5 NCCL. */
+typedef struct basalt_rt_error {
+    int kind;
+    int code;           /* CUresult / ncclResult_t */
+    char call[64];      /* e.g. "cuModuleLoadData" */
+    char message[440];
+} basalt_rt_error;
+/* The error of the calling thread's most recent failed runtime call. */
+void basalt_rt_last_error(basalt_rt_error *out);
+
+/* CudaDriver::load (driver.rs:104-133): dlopen libcuda.so.1 / libcuda.so, resolve entry points
+ * with their _v2 fallbacks, cuInit(0). */
+int basalt_rt_driver_load(basalt_rt_driver **out);
+void basalt_rt_driver_unload(basalt_rt_driver *drv);
+/* CudaDriver::device_count (driver.rs:136-141). */
+int basalt_rt_device_count(basalt_rt_driver *drv, int *count);
+/* CudaDriver::create_context (driver.rs:143-159). Retains the device's primary context instead
+ * of creating a new one, so memory and streams are shared with any CUDA runtime user (PyTorch,
+ * NCCL) in the process. */
+int basalt_rt_ctx_create(basalt_rt_driver *drv, int device_index, basalt_rt_ctx **out);
+void basalt_rt_ctx_destroy(basalt_rt_ctx *ctx);
+/* cuDeviceGetAttribute; attr is a CUdevice_attribute value. */
+int basalt_rt_device_attr(basalt_rt_ctx *ctx, int attr, int *value);
+
+/* CudaContext::load_module (context.rs:43-61): cuModuleLoadDataEx on the PTX text; the driver's
+ * JIT runs here. The JIT's error log is kept for basalt_rt_last_error. Also reads the
+ * `//!basalt.plan` lines the emitter writes for kernels that need tensor maps. */
+int basalt_rt_module_load(basalt_rt_ctx *ctx, const char *ptx, basalt_rt_module **out);
+void basalt_rt_module_unload(basalt_rt_module *mod);
+/* CudaModule::get_function (module.rs:22-44). */
+int basalt_rt_get_function(basalt_rt_module *mod, const char *name, basalt_rt_function **out);
+
+/* CudaContext::alloc (context.rs:64-76). */
+int basalt_rt_alloc(basalt_rt_ctx *ctx, size_t bytes, basalt_rt_buffer **out);
+void basalt_rt_buffer_free(basalt_rt_buffer *buf);
+/* DeviceBuffer::device_ptr / len (context.rs:142-150). */
+uint64_t basalt_rt_buffer_ptr(const basalt_rt_buffer *buf);
+size_t basalt_rt_buffer_size(const basalt_rt_buffer *buf);
+/* DeviceBuffer::copy_from_host / copy_to_host (context.rs:104-140): refuse (kind 4) when bytes
+ * exceeds the buffer. stream NULL = synchronous copy like the reference; otherwise asynchronous
+ * on that CUstream. */
+int basalt_rt_copy_from_host(basalt_rt_buffer *buf, const void *host, size_t bytes, void *stream);
+int basalt_rt_copy_to_host(const basalt_rt_buffer *buf, void *host, size_t bytes, void *stream);
+/* Page-locked host memory for asynchronous copies (no counterpart; the reference copies from
+ * pageable memory). */
+int basalt_rt_host_alloc(basalt_rt_ctx *ctx, size_t bytes, void **out);
+void basalt_rt_host_free(basalt_rt_ctx *ctx, void *p);
+
+/* CudaFunction::launch (module.rs:77-122): cuLaunchKernel with params[i] pointing at the i-th
+ * kernel parameter, in the BIR parameter order. Unlike the reference it takes a stream and does
+ * not synchronise; pass stream NULL and call basalt_rt_ctx_sync for the reference behaviour.
+ * For a kernel with a launch plan, the tensor-map parameters are built from the pointer and size
+ * parameters and appended here; the caller still passes only the BIR parameters. */
+int basalt_rt_launch(basalt_rt_function *fn, const uint32_t grid[3], const uint32_t block[3],
+                     uint32_t shared_mem_bytes, void *stream, void **params);
+/* Grid and block the emitter planned for this kernel (0 when the kernel has no plan and the
+ * caller chooses, as with the reference). */
+int basalt_rt_planned_geometry(basalt_rt_function *fn, void **params, uint32_t grid[3], uint32_t block[3],
+                               uint32_t *shared_mem_bytes);
+int basalt_rt_ctx_sync(basalt_rt_ctx *ctx);   /* cuCtxSynchronize (module.rs:120-121) */
+
+/* Streams and events (no counterpart: ffi.rs:38-42 "no multi-stream support yet"). */
+int basalt_rt_stream_create(basalt_rt_ctx *ctx, void **stream_out);
+int basalt_rt_stream_destroy(basalt_rt_ctx *ctx, void *stream);
+int basalt_rt_stream_sync(basalt_rt_ctx *ctx, void *stream);
+int basalt_rt_event_create(basalt_rt_ctx *ctx, void **event_out);
+int basalt_rt_event_destroy(basalt_rt_ctx *ctx, void *event);
+int basalt_rt_event_record(basalt_rt_ctx *ctx, void *event, void *stream);
+int basalt_rt_event_sync(basalt_rt_ctx *ctx, void *event);
+int basalt_rt_event_elapsed_ms(basalt_rt_ctx *ctx, void *start, void *end, float *ms);
+
+/* The reference's CPU launch ABI run on the device (crates/basalt-x86/src/oracle.rs:75-83,
+ * examples/cpu_launch_*.c): host pointers in, results in host memory out. For each argument:
+ * kind 0 = i32, 1 = i64, 2 = f32, 3 = f64 (value read from `value`), 4 = pointer read by the
+ * kernel, 5 = pointer written, 6 = both (host address in `host`, extent in `bytes`). The call
+ * allocates device buffers, copies inputs, launches ceil(nthreads/block) blocks of `block`
+ * threads (the reference's grid for a flat launch), copies outputs back and frees. */
+typedef struct basalt_rt_arg {
+    int kind;
+    union { int32_t i32; int64_t i64; float f32; double f64; } value;
+    void *host;
+    size_t bytes;
+} basalt_rt_arg;
+int basalt_rt_cpu_launch(basalt_rt_ctx *ctx, basalt_rt_function *fn, const basalt_rt_arg *args, int nargs,
+                         int64_t nthreads, uint32_t block);
+
+/* Contiguous range [begin,end) of `total` units owned by `rank` of `nranks`, boundaries rounded
+ * to multiples of `align` units. The grid-range sharding of the multi-GPU configurations. */
+void basalt_rt_shard_range(uint64_t total, int nranks, int rank, uint64_t align, uint64_t *begin,
+                           uint64_t *end);
+
+/* NCCL over NVLink, one communicator rank per process (no counterpart in the reference). The id
+ * made on rank 0 is distributed by the caller. */
+int basalt_rt_comm_unique_id(char id_out[128]);
+int basalt_rt_comm_init(basalt_rt_ctx *ctx, const char id[128], int nranks, int rank, basalt_rt_comm **out);
+void basalt_rt_comm_destroy(basalt_rt_comm *comm);
+/* ncclAllReduce(ncclInt32, ncclMax): combines the per-GPU partial maxima. */
+int basalt_rt_allreduce_max_i32(basalt_rt_comm *comm, uint64_t send, uint64_t recv, size_t count, void *stream);
+/* ncclAllGather of bytes_per_rank bytes: gathers the row-sharded matmul output. */
+int basalt_rt_allgather(basalt_rt_comm *comm, uint64_t send, uint64_t recv, size_t bytes_per_rank, void *stream);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+#endif /* BASALT_B200_H */

@@ -1,0 +1,55 @@
+/* Hand-written sm_100a CUDA kernels for the five benchmark workloads: the comparators that every
+ * emitted kernel is measured against.  The reference ships no CUDA kernels at all (its .cu files
+ * are compiler inputs, tests/kernels/ in the reference project); each entry below names the
+ * reference example whose kernel signature and result it reproduces at benchmark scale.
+ *
+ * All pointers are device pointers; `stream` is a cudaStream_t / CUstream (NULL = default
+ * stream).  Launches are asynchronous.  Return value: 0, or a cudaError_t / CUresult code
+ * (basalt_k_last_error() gives the text).
+ */
+#ifndef BASALT_B200_KERNELS_H
+#define BASALT_B200_KERNELS_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)
+#endif
+
+const char *basalt_k_last_error(void);
+
+/* c[i] = a[i] + b[i], wrapping int32, for i < n: the vector_add kernel of
+ * examples/cpu_launch_vadd.c (there f32, N = 1024) at int32. */
+int basalt_k_vadd_i32(const int32_t *a, const int32_t *b, int32_t *c, int64_t n, void *stream);
+
+/* atomicMax(out, max_i x[i]) signed: out must hold the running maximum on entry (INT32_MIN for
+ * a fresh reduction).  Named after examples/cpu_launch_max_i32.c, which in the reference is a
+ * two-argument scalar max; the reduction is this benchmark's workload. */
+int basalt_k_max_i32(const int32_t *x, int64_t n, int32_t *out, void *stream);
+
+/* out[i] = step_0(in[i]) with step_j(x) = step_{j+1}(x*x + 2654435761*j mod 2^32), 32 levels:
+ * tests/kernels/device_helper_chain.cu (there 3 levels) at depth 32. */
+int basalt_k_helper_chain_u32(const uint32_t *in, uint32_t *out, int64_t n, void *stream);
+
+/* C[MxN] = A[MxK] * B[KxN], row-major fp32, FFMA only (no TF32): the workload of
+ * examples/cpu_launch_tiled_sgemm.c (there 32^3 with a C addend). M, N multiples of 128, K of 16. */
+int basalt_k_sgemm_f32(const float *A, const float *B, float *C, int M, int N, int K, void *stream);
+
+/* C[MxN] (fp16) = A[MxK] (fp16) * B (fp16) with fp32 accumulation on tcgen05 tensor cores, TMA
+ * loads, TMEM accumulator: the workload of examples/cpu_launch_triton_matmul.c (there f32 4x5x3).
+ * b_is_nk = 0: B is [K x N] row-major; 1: B is stored transposed, [N x K] row-major.
+ * M, N multiples of 128, K of 64.  `status` (device int32, may be NULL) receives a non-zero code
+ * if a bounded wait inside the kernel expired. */
+int basalt_k_matmul_f16(const void *A, const void *B, void *C, int M, int N, int K, int b_is_nk,
+                        int32_t *status, void *stream);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+#endif /* BASALT_B200_KERNELS_H */
