@@ -1036,9 +1036,9 @@ void optimize_module(Module& m, int opt_level, int reg_budget, std::vector<OptRe
     inline_calls(m);
     for (auto& f : m.funcs) {
         OptReport rep;
-        simplify_cfg(f);
-        dce(f);
         if (opt_level > 0) {
+            simplify_cfg(f);
+            dce(f);
             rep.warp_reduces = fuse_warp_reductions(f);
             bool done = false;
             for (int U = 4; U >= 1 && !done; U >>= 1) {

@@ -1,0 +1,83 @@
+"""The emitter's BIR-to-BIR passes preserve results under the CPU oracle's execution model: the
+optimised module (inlined calls, 16-byte vector accesses, scalar tails) is run through the oracle
+interpreter beside the original on the same inputs, including ragged and under-sized launches."""
+import numpy as np
+import pytest
+
+import basalt_b200 as b
+from basalt_b200 import kernels_bir as kb
+from oracle.bir_interp import run_kernel
+
+LAUNCHES = [(1000, 1024), (1003, 1024), (7, 8), (0, 4), (100, 40), (37, 64), (64, 16), (5, 1), (33, 33)]
+
+
+@pytest.mark.parametrize("name, kernel, nin", [("vadd_i32", "vadd_i32", 2), ("vector_add_f32", "vector_add", 2),
+                                               ("chain_vector", "chain_vector", 1), ("square_vector", "square_vector", 1)])
+def test_elementwise_vectoriser(ptx, name, kernel, nin):
+    src = kb.load(name)
+    opt = ptx.optimized_bir(src)
+    assert "load v4" in opt and "vec.build" in opt and "call" not in opt
+    rng = np.random.default_rng(11)
+    for n, threads in LAUNCHES:
+        size = max(n, 1) + 8
+        if name == "vector_add_f32":
+            ins = [rng.uniform(-1e3, 1e3, size).astype(np.float32) for _ in range(nin)]
+            poison = np.full(size, -1.0, np.float32)
+        else:
+            ins = [rng.integers(-2**30, 2**30, size, dtype=np.int64).astype(np.int32) for _ in range(nin)]
+            poison = np.full(size, 0x7fffffff, np.int32)
+        o0, o1 = poison.copy(), poison.copy()
+        run_kernel(src, kernel, ins + [o0, n], threads)
+        run_kernel(opt, kernel, ins + [o1, n], threads)
+        assert np.array_equal(o0.view(np.uint32), o1.view(np.uint32)), (n, threads)
+        assert np.array_equal(o0[min(n, threads):], poison[min(n, threads):])   # nothing past min(n, threads) is touched
+
+
+def test_helper_chain_inlining_and_vectorising(ptx, orc):
+    import ctypes
+    from _util import vp
+    src = kb.helper_chain()
+    opt = ptx.optimized_bir(src)
+    assert "call" not in opt and opt.count("func @") == 1 and "load v4i32" in opt
+    x = np.random.default_rng(5).integers(0, 2**32, 300, dtype=np.uint64).astype(np.uint32)
+    want = np.zeros(300, np.uint32)
+    orc.orc_helper_chain_u32(vp(x), vp(want), ctypes.c_int32(297), ctypes.c_int64(320))
+    for text in (src, opt):
+        got = np.zeros(300, np.uint32)
+        run_kernel(text, "helper_chain", [x, got, 297], 320)
+        assert np.array_equal(got, want)
+
+
+def test_reduction_loop_vectoriser(ptx):
+    src = kb.load("max_i32_strided")
+    opt = ptx.optimized_bir(src)
+    assert "load v4i32" in opt
+    rng = np.random.default_rng(13)
+    for n, threads in [(1000, 64), (1003, 32), (5, 8), (0, 4), (64, 64), (999, 1), (17, 3), (4096, 128)]:
+        x = rng.integers(-2**31, 2**31, max(n, 1), dtype=np.int64).astype(np.int32)
+        for plant in (None, 0, n - 1, n // 2):
+            if plant is not None and n:
+                x[:] = np.minimum(x, 2**31 - 2)
+                x[plant] = 2**31 - 1
+            o0 = np.array([-2**31], np.int32); o1 = o0.copy()
+            run_kernel(src, "max_i32_strided", [x, o0, n], threads)
+            run_kernel(opt, "max_i32_strided", [x, o1, n], threads)
+            assert o0[0] == o1[0] == (x[:n].max() if n else -2**31), (n, threads, plant)
+
+
+def test_butterfly_becomes_one_warp_reduce_per_stage(ptx):
+    opt = ptx.optimized_bir(kb.load("max_i32"))
+    assert opt.count("warp.reduce.max i32") == 2 and "shuffle" not in opt
+    assert "atomic.max i32 ptr.global" in opt and "barrier" in opt and "load v4i32" in opt
+
+
+def test_opt_level_zero_keeps_the_module_shape(ptx):
+    opt0 = ptx.optimized_bir(kb.load("max_i32"), b.EmitOpts(opt_level=0))
+    assert opt0.count("shuffle.xor") == 10 and "v4" not in opt0
+
+
+def test_register_estimate_bounds_the_unroll(ptx):
+    text = ptx.emit(kb.load("vadd_i32")).text
+    line = next(l for l in text.splitlines() if l.startswith("// kernel vadd_i32"))
+    est = int(line.split("est_regs=")[1].split()[0])
+    assert est <= 64 and "unroll=2" in line
