@@ -18,7 +18,7 @@
 //
 // Every wait on an mbarrier is bounded; when a wait gives up the kernel records a code in
 // `status`, carries on without the data (the result is then wrong, and the host reports it), and
-// still releases its tensor memory before it returns.
+// still releases its tensor memory before it returns; CTAs that start after that return at once.
 #include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -32,7 +32,7 @@ namespace {
 constexpr int BM = 128, BN = 128, BK = 64, UMMA_K = 16, THREADS = 128;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr uint32_t TMEM_COLS = 128;
-constexpr uint32_t WAIT_LIMIT = 1u << 24;   // try_wait calls before a wait gives up
+constexpr uint64_t WAIT_LIMIT_NS = 200ull * 1000 * 1000;   // a wait gives up after 200 ms
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -42,9 +42,16 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-// Bounded wait for the phase with the given parity. Returns false when it gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
+__device__ __forceinline__ uint64_t global_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait for the phase with the given parity. Gives up after WAIT_LIMIT_NS, or at once when
+// another wait of this CTA has already given up (`*gave_up`, in shared memory); returns false then.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* gave_up) {
+    uint64_t t0 = 0;
+    for (uint32_t i = 0;; i++) {
         uint32_t done;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
@@ -54,8 +61,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
             : "r"(bar), "r"(parity)
             : "memory");
         if (done) return true;
+        if (*gave_up) return false;
+        if ((i & 63) == 63) {
+            const uint64_t now = global_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > WAIT_LIMIT_NS) { *gave_up = 1; return false; }
+        }
     }
-    return false;
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst), "l"(map),
@@ -91,13 +103,16 @@ __global__ void __launch_bounds__(THREADS) matmul_f16_tc_kernel(const __grid_con
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_bar;
     __shared__ uint32_t tmem_slot;
+    __shared__ volatile uint32_t gave_up;
     // The swizzle pattern is a function of the absolute shared address: stages start on 1 KB.
     const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int num_kb = K / BK;
 
+    if (status && *reinterpret_cast<volatile int32_t*>(status) != 0) return;   // an earlier CTA gave up: do not pile on
     if (threadIdx.x == 0) {
+        gave_up = 0;
         for (int s = 0; s < STAGES; s++) {
             mbar_init(smem_u32(&full_bar[s]), 1);
             mbar_init(smem_u32(&empty_bar[s]), 1);
@@ -121,7 +136,8 @@ __global__ void __launch_bounds__(THREADS) matmul_f16_tc_kernel(const __grid_con
         for (int kb = 0; kb < num_kb; kb++) {
             const int s = kb % STAGES;
             const uint32_t parity = ((kb / STAGES) & 1) ^ 1;   // a fresh barrier passes a wait on parity 1
-            ok &= mbar_wait(smem_u32(&empty_bar[s]), parity);
+            ok &= mbar_wait(smem_u32(&empty_bar[s]), parity, &gave_up);
+            if (!ok) break;   // issue nothing more; the copies already in flight land long before the CTA exits
             const uint32_t fb = smem_u32(&full_bar[s]), a_dst = tiles + s * STAGE_BYTES, b_dst = a_dst + A_BYTES;
             mbar_expect_tx(fb, STAGE_BYTES);
             tma_load_2d(a_dst, &map_a, fb, kb * BK, m0);               // box: 64 k (128 B) x 128 rows
@@ -138,7 +154,8 @@ __global__ void __launch_bounds__(THREADS) matmul_f16_tc_kernel(const __grid_con
         const uint32_t idesc = (1u << 4) | ((B_IS_NK ? 0u : 1u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
         for (int kb = 0; kb < num_kb; kb++) {
             const int s = kb % STAGES;
-            ok &= mbar_wait(smem_u32(&full_bar[s]), (kb / STAGES) & 1);
+            ok &= mbar_wait(smem_u32(&full_bar[s]), (kb / STAGES) & 1, &gave_up);
+            if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t a_src = tiles + s * STAGE_BYTES, b_src = a_src + A_BYTES;
 #pragma unroll
@@ -157,7 +174,7 @@ __global__ void __launch_bounds__(THREADS) matmul_f16_tc_kernel(const __grid_con
     __syncwarp();
 
     // ---- epilogue: TMEM -> registers -> f16 -> global ----
-    ok &= mbar_wait(smem_u32(&acc_bar), 0);
+    ok &= mbar_wait(smem_u32(&acc_bar), 0, &gave_up);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     __half* crow = C + (size_t)(m0 + warp * 32 + lane) * N + n0;
     const uint32_t lane_base = tmem_acc + ((uint32_t)(warp * 32) << 16);

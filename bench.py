@@ -1,0 +1,346 @@
+#!/usr/bin/env python
+"""Benchmark of the Basalt sm_100a device path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+Headline workload (N=1 and per rank at N>1): the max_i32 reduction over 2^28 int32 (1 GiB), the
+benchmark configuration the metric is quoted on.  A step is one pass over the rank's batch: one
+launch of the emitted sm_100a kernel through the C-ABI runtime, plus, at N>1, the 4-byte
+allreduce(max) of the partial maxima over this library's NCCL communicator.  Scaling is weak: every
+rank owns a 2^28-element contiguous shard of an N*2^28-element array.
+
+One JSON line is printed by rank 0; see DESIGN.md for the meaning of each key.  `--impl reference`
+times the reference's CPU launch path (the C restatement under oracle/, one thread, like the
+reference's emitted x86 loop) on the same workload instead.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_MAX = 1 << 28          # elements per rank: 1 GiB of int32, far larger than the 126 MB L2
+METRIC = "max_i32 reduction throughput (HBM GB/s)"
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), float(p.get("bf16_tflops", 1590.0)), "measured"
+    except Exception:
+        return 6650.0, 1590.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock, power and throttle reasons with nvidia-smi every 200 ms."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows, self.proc = [], None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200", "-i", str(index)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def stop(self, t0: float, t1: float) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        rows = [r for t, r in self.rows if t0 - 0.1 <= t <= t1 + 0.3 and len(r) >= 7] or [r for _, r in self.rows if len(r) >= 7]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        reasons = [n for k, n in enumerate(names) if any(r[3 + k] == "Active" for r in rows)]
+        num = lambda s: float(s) if s.replace(".", "", 1).isdigit() else float("nan")
+        return {"sm_mhz": statistics.median(num(r[0]) for r in rows), "sm_max_mhz": num(rows[0][1]),
+                "power_w_max": max(num(r[2]) for r in rows), "reasons": reasons, "samples": len(rows)}
+
+
+def load_oracle():
+    from oracle import build as oracle_build
+    lib = ctypes.CDLL(oracle_build.build())
+    lib.orc_time_max_i32.restype = ctypes.c_double
+    return lib
+
+
+def time_oracle_max(x: np.ndarray, reps: int):
+    """Seconds for one pass of the oracle's max_i32 over x (best of reps), and its result."""
+    lib = load_oracle()
+    res = ctypes.c_int32()
+    t = lib.orc_time_max_i32(x.ctypes.data_as(ctypes.c_void_p), ctypes.c_int32(len(x)), reps, ctypes.byref(res))
+    return t, res.value
+
+
+def reference_arm(args):
+    """The reference's CPU launch path for this workload: one native thread looping over the
+    elements (crates/basalt-x86/src/oracle.rs:1058-1098), restated in oracle/basalt_oracle.c."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from basalt_b200 import workloads as w
+    n = N_MAX
+    x = w.u32(w.SEEDS["max_i32"], n).view(np.int32)
+    for _ in range(min(args.warmup, 1)):
+        time_oracle_max(x, 1)
+    steps = max(1, min(args.steps, 20))      # each step is one full pass (about 0.2 s): bounded
+    times = [time_oracle_max(x, 1)[0] for _ in range(steps)]
+    ms = 1e3 * sum(times) / len(times)
+    value = 4.0 * n / (ms * 1e-3) / 1e9
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 1),
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "i32", "data": "synthetic",
+            "config": {"workload": "max_i32 N=2^28 int32 uniform full range, one pass per step", "l2": "input (1 GiB) larger than any cache"},
+            "cpu_baseline": {"value": value, "unit": "GB/s", "cores": 1, "kind": "port",
+                             "sample": f"{steps} full passes over 2^28 int32; the reference's CPU launch path is single-threaded by construction"},
+            "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def others_summary(ctx, torch, stream, peaks_hbm, peaks_tf):
+    """Short device-resident timings of the other four configurations (emitted and hand-written),
+    on device-generated synthetic data of the configured shapes; parity for them is in tests/."""
+    import basalt_b200 as b
+    from basalt_b200 import kernels, kernels_bir as kb
+    out = {}
+
+    def timed(fn, reps):
+        for _ in range(3):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        e1.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    def emitted(src, name):
+        mod = ctx.load_module(b.Ptx().emit(src).text)
+        return mod.get_function(name)
+
+    dp = lambda t: b.ptr(t.data_ptr())
+    # vadd_i32 at the configured N = 2^20 (12.6 MB: L2-resident, launch-latency bound) and at 2^28 (HBM)
+    for n, label in ((1 << 20, "vadd_i32_n2^20_L2_resident"), (1 << 28, "vadd_i32_n2^28_hbm")):
+        a = torch.randint(-2**30, 2**30, (n,), dtype=torch.int32, device="cuda"); bb = torch.randint(-2**30, 2**30, (n,), dtype=torch.int32, device="cuda")
+        c = torch.empty_like(a)
+        fn = emitted(kb.load("vadd_i32"), "vadd_i32")
+        ms_e = timed(lambda: fn.launch((n + 255) // 256, 256, 0, [dp(a), dp(bb), dp(c), b.i32(n)], stream=stream), 50)
+        ok = bool(torch.equal(c, a + bb))
+        ms_h = timed(lambda: kernels.vadd_i32(a.data_ptr(), bb.data_ptr(), c.data_ptr(), n, stream), 50)
+        out[label] = {"emitted_gbs": 12.0 * n / ms_e / 1e6, "handwritten_gbs": 12.0 * n / ms_h / 1e6, "frac_of_hbm_peak": 12.0 * n / ms_e / 1e6 / peaks_hbm, "ok": ok}
+        del a, bb, c
+    # helper chain, N = 2^26
+    n = 1 << 26
+    x = torch.randint(-2**31, 2**31 - 1, (n,), dtype=torch.int32, device="cuda"); y = torch.empty_like(x)
+    fn = emitted(kb.helper_chain(), "helper_chain")
+    ms_e = timed(lambda: fn.launch((n + 255) // 256, 256, 0, [dp(x), dp(y), b.i32(n)], stream=stream), 20)
+    ms_h = timed(lambda: kernels.helper_chain_u32(x.data_ptr(), y.data_ptr(), n, stream), 20)
+    out["helper_chain_n2^26"] = {"emitted_gops": 64.0 * n / ms_e / 1e6, "handwritten_gops": 64.0 * n / ms_h / 1e6,
+                                 "emitted_gbs": 8.0 * n / ms_e / 1e6, "handwritten_gbs": 8.0 * n / ms_h / 1e6}
+    del x, y
+    # SGEMM 4096^3
+    M = N = K = 4096
+    A = torch.rand(M, K, device="cuda") * 2 - 1; B = torch.rand(K, N, device="cuda") * 2 - 1; C = torch.empty(M, N, device="cuda")
+    ms_h = timed(lambda: kernels.sgemm_f32(A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K, stream), 5)
+    fl = 2.0 * M * N * K
+    out["sgemm_f32_4096"] = {"handwritten_tflops": fl / ms_h / 1e9}
+    try:
+        fn = emitted(kb.sgemm_cta128(M, N, K), "sgemm_f32")
+        ms_e = timed(lambda: fn.launch((N // 128, M // 128), 256, 0, [dp(A), dp(B), dp(C)], stream=stream), 3)
+        out["sgemm_f32_4096"]["emitted_tflops"] = fl / ms_e / 1e9
+    except Exception as e:   # noqa: BLE001 - reported, not hidden
+        out["sgemm_f32_4096"]["emitted_error"] = str(e)[:200]
+    del A, B, C
+    # fp16 matmul 8192^3 on tcgen05
+    M = N = K = 8192
+    A = (torch.randn(M, K, device="cuda") * 0.1).half(); B = (torch.randn(K, N, device="cuda") * 0.1).half(); C = torch.empty(M, N, device="cuda", dtype=torch.float16)
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    fl = 2.0 * M * N * K
+    try:
+        ms_h = timed(lambda: kernels.matmul_f16(A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K, False, st.data_ptr(), stream), 5)
+        out["matmul_f16_8192"] = {"handwritten_tflops": fl / ms_h / 1e9, "frac_of_bf16_peak": fl / ms_h / 1e9 / peaks_tf, "status": int(st.item())}
+    except Exception as e:   # noqa: BLE001
+        out["matmul_f16_8192"] = {"handwritten_error": str(e)[:200]}
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="basalt_b200", choices=["basalt_b200", "reference"])
+    ap.add_argument("--no-others", action="store_true", help="skip the short timings of the other four configurations")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import torch
+
+    import basalt_b200 as b
+    from basalt_b200 import kernels, kernels_bir as kb, sharding, workloads as w
+
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    group = sharding.RankGroup.from_env("nccl")
+    rank, world = group.rank, group.world
+    if world != args.gpus and rank == 0:
+        print(f"warning: --gpus {args.gpus} but WORLD_SIZE is {world}", file=sys.stderr)
+    ctx = b.CudaDriver.load().create_context(local_rank)
+    comm = group.nccl(ctx)
+    stream = torch.cuda.current_stream().cuda_stream
+    peak_hbm, peak_tf, peak_kind = measured_peaks()
+
+    # ---- inputs: this rank's contiguous shard, generated on the host into pinned memory ----
+    n = N_MAX
+    host_x = ctx.pinned_array((n,), np.uint32)
+    w.u32(w.SEEDS["max_i32"] + rank, n, out=host_x)
+    host_x = host_x.view(np.int32)
+    expect_local = int(host_x.max())
+    x = torch.empty(n, dtype=torch.int32, device="cuda")
+    x.copy_(torch.from_numpy(host_x))
+    host_in = host_x.view()
+    host_in.flags.writeable = False      # an input of the launch: copied to the device, never back
+    partial = torch.empty(1, dtype=torch.int32, device="cuda")
+    result = torch.empty(1, dtype=torch.int32, device="cuda")
+    lowest = torch.full((1,), -2**31, dtype=torch.int32, device="cuda")
+
+    fn = ctx.load_module(b.Ptx().emit(kb.load("max_i32")).text).get_function("max_i32")
+    blocks = ctx.sm_count() * 8
+    params = [b.ptr(x.data_ptr()), b.ptr(partial.data_ptr()), b.i32(n)]
+
+    def step_emitted():
+        partial.copy_(lowest)                                  # a 4-byte device copy resets the running maximum
+        fn.launch(blocks, 256, 0, params, stream=stream)       # basalt_rt_launch: the emitted sm_100a kernel
+        if comm is not None:
+            comm.allreduce_max_i32(partial.data_ptr(), result.data_ptr(), 1, stream)
+
+    def step_hand():
+        partial.copy_(lowest)
+        kernels.max_i32(x.data_ptr(), n, partial.data_ptr(), stream)
+        if comm is not None:
+            comm.allreduce_max_i32(partial.data_ptr(), result.data_ptr(), 1, stream)
+
+    def timed_loop(step, steps):
+        group.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        group.barrier()
+        return group.max_float(e0.elapsed_time(e1))
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    for _ in range(args.warmup):
+        step_emitted()
+    torch.cuda.synchronize()
+    t_begin = time.time()
+    total_ms = timed_loop(step_emitted, args.steps)
+    got = int((result if comm is not None else partial).item())
+    # kernel-only time of the dominant kernel, measured live with events around each launch
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(min(args.steps, 200))]
+    for e0, e1 in ev:
+        partial.copy_(lowest)
+        e0.record(); fn.launch(blocks, 256, 0, params, stream=stream); e1.record()
+    torch.cuda.synchronize()
+    kernel_ms = statistics.mean(e0.elapsed_time(e1) for e0, e1 in ev)
+    for _ in range(args.warmup):
+        step_hand()
+    hand_ms = timed_loop(step_hand, args.steps) / args.steps
+    t_end = time.time()
+
+    # ---- end to end: host buffers through the reference's CPU launch ABI on the device ----
+    out_host = np.empty(1, np.int32)
+    e2e_steps = max(3, min(args.steps, 10))
+
+    def step_e2e():
+        out_host[0] = -2**31
+        ctx.cpu_launch(fn, [host_in, out_host, b.i32(n)], nthreads=blocks * 256, block=256)   # H2D 1 GiB, launch, D2H 4 B
+        return group.max_i32_host(int(out_host[0])) if world > 1 else int(out_host[0])
+
+    step_e2e()
+    group.barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        got_e2e = step_e2e()
+    e2e_ms = group.max_float((time.perf_counter() - t0) * 1e3) / e2e_steps
+
+    expect = group.max_i32_host(expect_local)
+    parity = bool(got == expect and got_e2e == expect)
+
+    clocks = sampler.stop(t_begin, t_end) if sampler else None
+    cpu = None
+    others = None
+    if rank == 0:
+        sample_n = n
+        t_cpu, r_cpu = time_oracle_max(host_x[:sample_n], 3)
+        parity = parity and (world > 1 or r_cpu == expect)
+        cpu = {"value": 4.0 * sample_n / t_cpu / 1e9, "unit": "GB/s", "cores": 1, "kind": "port",
+               "sample": "3 full passes over this rank's 2^28 int32 (best), the oracle's sequential atomic-max loop, one thread as in the reference"}
+        if world == 1 and not args.no_others:
+            try:
+                others = others_summary(ctx, torch, stream, peak_hbm, peak_tf)
+            except Exception as e:   # noqa: BLE001
+                others = {"error": str(e)[:300]}
+    ms_per_step = total_ms / args.steps
+    total_bytes = 4.0 * n * world
+    if rank == 0:
+        achieved = 4.0 * n / (kernel_ms * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": total_bytes / (ms_per_step * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "i32", "data": "synthetic",
+            "config": {"workload": "max_i32: signed max over 2^28 int32 per GPU (uniform over the full range, SplitMix64 seed per rank), "
+                                   "emitted sm_100a kernel launched through the C-ABI runtime" + (", NCCL allreduce(max) of 1 int32 per step" if world > 1 else ""),
+                       "elements_per_gpu": n, "grid": blocks, "block": 256, "l2": "input (1 GiB per GPU) is larger than the 126 MB L2; no flush needed",
+                       "parallelism": f"contiguous shards x{world}"},
+            "parity": parity,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak_hbm, "unit": "GB/s", "frac": achieved / peak_hbm, "peak_source": peak_kind,
+                         "traffic": None, "kernel": "max_i32 (emitted)", "kernel_ms": kernel_ms, "algorithmic_bytes_per_launch": 4 * n},
+            "handwritten": {"value": total_bytes / (hand_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": hand_ms},
+            "cpu_baseline": cpu,
+            "e2e": {"value": total_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": 4 * n + 4, "d2h_bytes_per_step": 4,
+                    "ms_per_step": e2e_ms, "steps": e2e_steps, "api": "basalt_rt_cpu_launch (kernel parameters as host pointers, then nthreads)"},
+            "gpu_launches": args.steps,
+            "clocks": clocks,
+        }
+        if others is not None:
+            line["others"] = others
+        print(json.dumps(line), flush=True)
+    if comm is not None:
+        comm.destroy()
+    if group.dist is not None:
+        group.barrier()
+        group.dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,63 @@
+"""The launch runtime on a real device: the behaviours the reference's own runtime tests pin
+(crates/basalt-runtime/tests/cuda_driver.rs) plus streams, events and error reporting. Failures
+are provoked on the host only (bad PTX text, a missing symbol, an oversized copy)."""
+import numpy as np
+import pytest
+
+import basalt_b200 as b
+from basalt_b200 import kernels_bir as kb
+from _gpu import emitted
+
+pytestmark = pytest.mark.gpu
+
+
+def test_device_and_round_trip(gpu):
+    assert gpu.driver.device_count() >= 1
+    assert gpu.sm_count() > 0
+    x = np.arange(100003, dtype=np.int32)
+    buf = gpu.upload(x)
+    assert len(buf) == x.nbytes and buf.device_ptr() % 256 == 0
+    assert np.array_equal(buf.to_numpy(np.int32), x)
+
+
+def test_copies_are_bounds_checked(gpu):
+    buf = gpu.alloc(64)
+    with pytest.raises(b.CudaError) as e:
+        buf.copy_from_host(np.zeros(17, np.int32))
+    assert e.value.kind == 4 and "exceeds the device buffer" in e.value.message
+    with pytest.raises(b.CudaError) as e:
+        buf.copy_to_host(np.zeros(17, np.int32))
+    assert e.value.kind == 4
+
+
+def test_jit_failure_is_reported_not_fatal(gpu):
+    with pytest.raises(b.CudaError) as e:
+        gpu.load_module(".version 8.7\n.target sm_100a\n.address_size 64\n.visible .entry broken() { this is not ptx; }\n")
+    assert e.value.kind == 3 and e.value.call == "cuModuleLoadData" and e.value.code != 0
+    # the context is still usable
+    assert np.array_equal(gpu.upload(np.arange(8, dtype=np.int32)).to_numpy(np.int32), np.arange(8))
+
+
+def test_missing_function_is_reported(gpu):
+    mod = gpu.load_module(b.Ptx().emit(kb.load("vadd_i32")).text)
+    with pytest.raises(b.CudaError) as e:
+        mod.get_function("no_such_kernel")
+    assert e.value.kind == 3 and e.value.call == "cuModuleGetFunction"
+
+
+def test_async_launch_streams_events_and_pinned_memory(gpu):
+    n = 1 << 20
+    fn = emitted(gpu, kb.load("vadd_i32"), "vadd_i32")
+    a = gpu.pinned_array((n,), np.int32); bb = gpu.pinned_array((n,), np.int32); c = gpu.pinned_array((n,), np.int32)
+    a[:] = np.arange(n); bb[:] = 7; c[:] = 0
+    da, db, dc = gpu.alloc(a.nbytes), gpu.alloc(a.nbytes), gpu.alloc(a.nbytes)
+    s = gpu.create_stream(); e0 = gpu.create_event(); e1 = gpu.create_event()
+    gpu.record(e0, s)
+    da.copy_from_host(a, s); db.copy_from_host(bb, s)
+    fn.launch(n // 256, 256, 0, [da, db, dc, b.i32(n)], stream=s)
+    dc.copy_to_host(c, s)
+    gpu.record(e1, s)
+    gpu.stream_sync(s)
+    assert gpu.elapsed_ms(e0, e1) > 0
+    assert np.array_equal(c, a + 7)
+    gpu.destroy_event(e0); gpu.destroy_event(e1); gpu.destroy_stream(s)
