@@ -846,6 +846,8 @@ bool emit_ptx(const Module& in, const EmitOptions& opts, EmitResult* out, Diag* 
         if (r.vec_lanes) text += " lanes=" + std::to_string(r.vec_lanes) + " unroll=" + std::to_string(r.unroll);
         if (r.warp_reduces) text += " warp_reduces=" + std::to_string(r.warp_reduces);
         text += "\n";
+        if (!r.coarse_of.empty())
+            text += "//!basalt.plan " + r.coarse_of + " coarse=" + f.name + " params=" + std::to_string(f.params.size() - 1) + "\n";
         FnEmitter fe(m, f);
         std::string fn_text;
         if (!fe.run(&fn_text)) {

@@ -14,10 +14,11 @@ namespace {
 constexpr int kThreads = 256;
 
 // c = a + b over n4 int4 vectors, grid-stride, two vectors per array in flight per thread.
-__global__ void __launch_bounds__(kThreads) vadd_i32_kernel(const int4* __restrict__ a, const int4* __restrict__ b, int4* __restrict__ c,
+__global__ void __launch_bounds__(kThreads, 6) vadd_i32_kernel(const int4* __restrict__ a, const int4* __restrict__ b, int4* __restrict__ c,
                                                             int64_t n4, const int32_t* as, const int32_t* bs, int32_t* cs, int64_t n) {
     const int64_t T = (int64_t)gridDim.x * blockDim.x, g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     int64_t j = g;
+#pragma unroll 1
     for (; j + T < n4; j += 2 * T) {
         int4 a0 = a[j], b0 = b[j], a1 = a[j + T], b1 = b[j + T];
         c[j] = make_int4(a0.x + b0.x, a0.y + b0.y, a0.z + b0.z, a0.w + b0.w);
@@ -53,10 +54,11 @@ __device__ __forceinline__ int block_max(int v) {
 }
 
 // Signed max of x[0..n): four 16-byte loads in flight per thread, one red.global.max per CTA.
-__global__ void __launch_bounds__(kThreads) max_i32_kernel(const int4* __restrict__ x4, int64_t n4, const int32_t* __restrict__ xs, int64_t n, int32_t* out) {
+__global__ void __launch_bounds__(kThreads, 8) max_i32_kernel(const int4* __restrict__ x4, int64_t n4, const int32_t* __restrict__ xs, int64_t n, int32_t* out) {
     const int64_t T = (int64_t)gridDim.x * blockDim.x, g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     int m = INT32_MIN;
     int64_t j = g;
+#pragma unroll 1
     for (; j + 3 * T < n4; j += 4 * T) {
         int4 v0 = x4[j], v1 = x4[j + T], v2 = x4[j + 2 * T], v3 = x4[j + 3 * T];
         m = max(m, max(max(max4(v0), max4(v1)), max(max4(v2), max4(v3))));
@@ -81,10 +83,11 @@ __device__ __forceinline__ uint32_t chain_step(uint32_t x) {
     if constexpr (J == 31) return y;
     else return chain_step<J + 1>(y);
 }
-__global__ void __launch_bounds__(kThreads) helper_chain_kernel(const uint4* __restrict__ in4, uint4* __restrict__ out4, int64_t n4,
+__global__ void __launch_bounds__(kThreads, 8) helper_chain_kernel(const uint4* __restrict__ in4, uint4* __restrict__ out4, int64_t n4,
                                                                 const uint32_t* ins, uint32_t* outs, int64_t n) {
     const int64_t T = (int64_t)gridDim.x * blockDim.x, g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     int64_t j = g;
+#pragma unroll 1
     for (; j + T < n4; j += 2 * T) {
         uint4 v0 = in4[j], v1 = in4[j + T];
         out4[j] = make_uint4(chain_step<0>(v0.x), chain_step<0>(v0.y), chain_step<0>(v0.z), chain_step<0>(v0.w));

@@ -464,7 +464,7 @@ int log2i(int64_t v) { int l = 0; while ((1ll << l) < v) l++; return l; }
 }  // namespace
 
 // ---- elementwise vectoriser ----------------------------------------------------------------
-bool vectorize_elementwise(Function& F, int max_unroll, OptReport* rep) {
+bool vectorize_elementwise(Function& F, int max_unroll, OptReport* rep, Function* coarse_out) {
     if (!F.is_kernel || F.blocks.size() < 2 || F.blocks.size() > 3) return false;
     const Term& et = F.blocks[0].term;
     if (et.kind != Term::CondBr) return false;
@@ -558,8 +558,13 @@ bool vectorize_elementwise(Function& F, int max_unroll, OptReport* rep) {
     int U = std::max<int64_t>(1, std::min<int64_t>(4, 64 / (std::max<int64_t>(nloads, 1) * 16)));
     U = std::max(1, std::min(U, max_unroll));
 
+    // Builds the rewritten kernel. In the coarse form one more i64 parameter carries the number of
+    // threads of the launch the caller asked for, so that the same elements are processed when the
+    // runtime launches fewer, longer-running threads.
+    auto build_variant = [&](bool coarse) -> Function {
     FB b;
-    b.f.name = F.name; b.f.is_kernel = true; b.f.params = F.params; b.f.ret = F.ret;
+    b.f.name = coarse ? F.name + "__coarse" : F.name; b.f.is_kernel = true; b.f.params = F.params; b.f.ret = F.ret;
+    if (coarse) b.f.params.push_back(I64);
     uint32_t entry = b.block();
     b.at(entry);
     std::map<uint32_t, Val> E;   // old entry id -> new value
@@ -572,8 +577,9 @@ bool vectorize_elementwise(Function& F, int max_unroll, OptReport* rep) {
     Val g32 = mapE(i), guard = mapE(et.val);
     Val g = b.cast(CastOp::SExt, I64, I32, g32);
     Val T = b.bin(BinOp::Mul, I64, b.cast(CastOp::ZExt, I64, I32, b.index(9, I32)), b.cast(CastOp::ZExt, I64, I32, b.index(6, I32)));
+    Val Tlog = coarse ? Val::P((uint32_t)F.params.size()) : T;
     Val n64 = b.cast(CastOp::SExt, I64, I32, n);
-    Val lim0 = b.select(I64, b.icmp(ICmp::Slt, I64, n64, T), n64, T);
+    Val lim0 = b.select(I64, b.icmp(ICmp::Slt, I64, n64, Tlog), n64, Tlog);
     Val zero = b.ci(I64, 0);
     Val lim = b.select(I64, b.icmp(ICmp::Slt, I64, lim0, zero), zero, lim0);
     Val nv = b.bin(BinOp::AShr, I64, lim, b.ci(I64, log2i(V)));
@@ -585,6 +591,7 @@ bool vectorize_elementwise(Function& F, int max_unroll, OptReport* rep) {
     Val aligned = b.icmp(ICmp::Eq, I64, b.bin(BinOp::And, I64, bits, b.ci(I64, 15)), zero);
     uint32_t vhead = b.block(), uloop = b.block(), ubody = b.block(), vloop = b.block(), vbody = b.block(), tail = b.block(),
              tbody = b.block(), sguard = b.block(), sbody = b.block(), exitb = b.block();
+    (void)guard;
     b.condbr(aligned, vhead, sguard);
 
     // Clones the body for one scalar index value.
@@ -676,13 +683,24 @@ bool vectorize_elementwise(Function& F, int max_unroll, OptReport* rep) {
     b.at(tbody);
     scalar_clone(b.cast(CastOp::Trunc, I32, I64, b.bin(BinOp::Add, I64, done, g)));
     b.br(exitb);
-    b.at(sguard); b.condbr(guard, sbody, exitb);
-    b.at(sbody); scalar_clone(g32); b.br(exitb);
+    // unaligned pointers: the original scalar body, as a loop over this thread's elements
+    b.at(sguard);
+    Val si = b.phi(I64);
+    b.condbr(b.icmp(ICmp::Slt, I64, si, lim), sbody, exitb);
+    b.at(sbody);
+    scalar_clone(b.cast(CastOp::Trunc, I32, I64, si));
+    Val si2 = b.bin(BinOp::Add, I64, si, T);
+    b.br(sguard);
+    b.phi_in(si, entry, g);
+    b.phi_in(si, sbody, si2);
     b.at(exitb); b.ret();
-    if (U == 1) { /* uloop/ubody unreachable; simplify_cfg removes them */ }
-    F = std::move(b.f);
-    simplify_cfg(F);
-    dce(F);
+    Function out = std::move(b.f);
+    simplify_cfg(out);
+    dce(out);
+    return out;
+    };
+    if (coarse_out) *coarse_out = build_variant(true);
+    F = build_variant(false);
     if (rep) { rep->elementwise = true; rep->vec_lanes = V; rep->unroll = U; }
     return true;
 }
@@ -1034,6 +1052,8 @@ int estimate_registers(const Function& f) {
 
 void optimize_module(Module& m, int opt_level, int reg_budget, std::vector<OptReport>* reports) {
     inline_calls(m);
+    std::vector<Function> extra;
+    std::vector<OptReport> extra_reports;
     for (auto& f : m.funcs) {
         OptReport rep;
         if (opt_level > 0) {
@@ -1042,16 +1062,27 @@ void optimize_module(Module& m, int opt_level, int reg_budget, std::vector<OptRe
             rep.warp_reduces = fuse_warp_reductions(f);
             bool done = false;
             for (int U = 4; U >= 1 && !done; U >>= 1) {
-                Function cand = f;
+                Function cand = f, coarse;
                 OptReport r = rep;
-                if (!vectorize_elementwise(cand, U, &r) && !vectorize_reduction_loop(cand, U, &r)) break;
-                int est = estimate_registers(cand);
-                if (est <= reg_budget || U == 1) { f = std::move(cand); rep = r; rep.est_regs = est; done = true; }
+                bool ew = vectorize_elementwise(cand, U, &r, &coarse);
+                if (!ew && !vectorize_reduction_loop(cand, U, &r)) break;
+                int est = estimate_registers(ew ? coarse : cand);
+                if (est <= reg_budget || U == 1) {
+                    f = std::move(cand);
+                    rep = r;
+                    rep.est_regs = est;
+                    done = true;
+                    if (ew) { canonicalize(coarse); extra.push_back(std::move(coarse)); OptReport cr = r; cr.est_regs = est; cr.coarse_of = f.name; extra_reports.push_back(cr); }
+                }
             }
         }
         if (!rep.est_regs) rep.est_regs = estimate_registers(f);
         canonicalize(f);
         if (reports) reports->push_back(rep);
+    }
+    for (size_t i = 0; i < extra.size(); i++) {
+        m.funcs.push_back(std::move(extra[i]));
+        if (reports) reports->push_back(extra_reports[i]);
     }
 }
 

@@ -43,13 +43,17 @@ struct OptReport {
     int vec_lanes = 0;
     int unroll = 0;
     int est_regs = 0;           // liveness-based estimate of 32-bit registers per thread
+    std::string coarse_of;      // set on a `<name>__coarse` variant: the kernel it stands in for
 };
 
 // Rewrites a kernel of the shape `i = bid.x*bdim.x + tid.x; if (i < n) { body(i) }`, whose body
 // touches global memory only at `param + i*esz`, into a grid-stride loop over 16-byte vectors with
 // a scalar tail and an unaligned fallback.  The set of elements processed is exactly the set the
-// original processes under the same launch: [0, min(n, gdim.x*bdim.x)).
-bool vectorize_elementwise(Function& f, int unroll, OptReport* rep);
+// original processes under the same launch: [0, min(n, gdim.x*bdim.x)).  `coarse_out` receives a
+// second entry, `<name>__coarse`, with one more i64 parameter: the thread count of the launch the
+// caller asked for.  The runtime launches it with one wave of resident CTAs instead, so each thread
+// loops over many vectors with several loads in flight; the elements processed are the same.
+bool vectorize_elementwise(Function& f, int unroll, OptReport* rep, Function* coarse_out = nullptr);
 // Rewrites `for (i = g; i < n; i += gdim.x*bdim.x) acc = op(acc, x[i])` (op = signed max/min, add,
 // and, or, xor on i32) into the same loop over 16-byte vectors plus a scalar tail loop.
 bool vectorize_reduction_loop(Function& f, int unroll, OptReport* rep);

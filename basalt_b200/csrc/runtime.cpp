@@ -67,6 +67,7 @@ struct Fns {
     CUresult (*cuEventSynchronize)(CUevent);
     CUresult (*cuEventElapsedTime)(float*, CUevent, CUevent);
     CUresult (*cuGetErrorString)(CUresult, const char**);
+    CUresult (*cuOccupancyMaxActiveBlocksPerMultiprocessor)(int*, CUfunction, int, size_t);
     CUresult (*cuTensorMapEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                        const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                        CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -82,6 +83,7 @@ struct basalt_rt_ctx {
     basalt_rt_driver* drv = nullptr;
     CUdevice dev = 0;
     CUcontext ctx = nullptr;
+    int sm_count = 0;
 };
 namespace {
 struct TmapSpec {
@@ -98,6 +100,7 @@ struct Plan {
     unsigned smem = 0;
     unsigned nparams = 0;   // number of BIR parameters (tensor maps follow them)
     std::vector<TmapSpec> tmaps;
+    std::string coarse;     // entry taking one more u64 parameter: the thread count the caller asked for
 };
 }  // namespace
 struct basalt_rt_module {
@@ -108,6 +111,7 @@ struct basalt_rt_module {
 struct basalt_rt_function {
     basalt_rt_module* mod = nullptr;
     CUfunction fn = nullptr;
+    CUfunction coarse = nullptr;   // see Plan::coarse
     bool has_plan = false;
     Plan plan;
 };
@@ -195,6 +199,7 @@ void parse_plans(const char* ptx, std::map<std::string, Plan>* out) {
             else if (k == "grid") sscanf(v.c_str(), "%u,%u,%u", &p.grid[0], &p.grid[1], &p.grid[2]);
             else if (k == "smem") p.smem = (unsigned)strtoul(v.c_str(), nullptr, 10);
             else if (k == "params") p.nparams = (unsigned)strtoul(v.c_str(), nullptr, 10);
+            else if (k == "coarse") p.coarse = v;
             else if (k == "tmap") {
                 TmapSpec t;
                 unsigned long long inner = 0, rowb = 0;
@@ -247,7 +252,8 @@ int basalt_rt_driver_load(basalt_rt_driver** out) {
               resolve(lib, &f.cuEventDestroy, {"cuEventDestroy_v2", "cuEventDestroy"}) && resolve(lib, &f.cuEventRecord, {"cuEventRecord"}) &&
               resolve(lib, &f.cuEventSynchronize, {"cuEventSynchronize"}) && resolve(lib, &f.cuEventElapsedTime, {"cuEventElapsedTime"}) &&
               resolve(lib, &f.cuGetErrorString, {"cuGetErrorString", "cuGetErrorName"}) &&
-              resolve(lib, &f.cuTensorMapEncodeTiled, {"cuTensorMapEncodeTiled"});
+              resolve(lib, &f.cuTensorMapEncodeTiled, {"cuTensorMapEncodeTiled"}) &&
+              resolve(lib, &f.cuOccupancyMaxActiveBlocksPerMultiprocessor, {"cuOccupancyMaxActiveBlocksPerMultiprocessor"});
     if (!ok) { dlclose(lib); delete d; return 2; }
     int rc = check(f, "cuInit", f.cuInit(0));
     if (rc) { dlclose(lib); delete d; return rc; }
@@ -281,6 +287,7 @@ int basalt_rt_ctx_create(basalt_rt_driver* drv, int device_index, basalt_rt_ctx*
     c->ctx = ctx;
     rc = make_current(c);
     if (rc) { drv->f.cuDevicePrimaryCtxRelease(dev); delete c; return rc; }
+    if (drv->f.cuDeviceGetAttribute(&c->sm_count, CU_DEVICE_ATTRIBUTE_MULTIPROCESSOR_COUNT, dev) != CUDA_SUCCESS || c->sm_count < 1) c->sm_count = 1;
     *out = c;
     return 0;
 }
@@ -343,6 +350,10 @@ int basalt_rt_get_function(basalt_rt_module* mod, const char* name, basalt_rt_fu
     if (it != mod->plans.end()) {
         h->has_plan = true;
         h->plan = it->second;
+        if (!h->plan.coarse.empty()) {
+            rc = check(f, "cuModuleGetFunction", f.cuModuleGetFunction(&h->coarse, mod->mod, h->plan.coarse.c_str()));
+            if (rc) { delete h; return rc; }
+        }
         if (h->plan.smem > 48 * 1024) {
             rc = check(f, "cuFuncSetAttribute", f.cuFuncSetAttribute(fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)h->plan.smem));
             if (rc) { delete h; return rc; }
@@ -419,6 +430,18 @@ int basalt_rt_planned_geometry(basalt_rt_function* fn, void** params, uint32_t g
 int basalt_rt_launch(basalt_rt_function* fn, const uint32_t grid[3], const uint32_t block[3], uint32_t shared_mem_bytes, void* stream, void** params) {
     if (!fn || !grid || !block) return set_err(4, 0, "basalt_rt_launch", "null argument");
     const Fns& f = fn->mod->ctx->drv->f;
+    if (fn->coarse && params && grid[1] == 1 && grid[2] == 1 && block[1] == 1 && block[2] == 1 && block[0] >= 32) {
+        // One-element-per-thread kernel: the caller's launch names the logical threads; run them on
+        // one wave of resident CTAs, each thread looping with several 16-byte accesses in flight.
+        uint64_t logical = (uint64_t)grid[0] * block[0];
+        int resident = 0;
+        if (f.cuOccupancyMaxActiveBlocksPerMultiprocessor(&resident, fn->coarse, (int)block[0], shared_mem_bytes) != CUDA_SUCCESS || resident < 1) resident = 1;
+        uint32_t wave = (uint32_t)fn->mod->ctx->sm_count * (uint32_t)resident;
+        uint32_t phys = grid[0] < wave ? grid[0] : wave;
+        std::vector<void*> all(params, params + fn->plan.nparams);
+        all.push_back(&logical);
+        return check(f, "cuLaunchKernel", f.cuLaunchKernel(fn->coarse, phys, 1, 1, block[0], 1, 1, shared_mem_bytes, (CUstream)stream, all.data(), nullptr));
+    }
     if (!fn->has_plan || fn->plan.tmaps.empty()) {
         if (fn->has_plan && fn->plan.block[0] && (block[0] != fn->plan.block[0] || block[1] != fn->plan.block[1] || block[2] != fn->plan.block[2]))
             return set_err(4, 0, "cuLaunchKernel", "kernel was compiled for block (" + std::to_string(fn->plan.block[0]) + "," + std::to_string(fn->plan.block[1]) + "," + std::to_string(fn->plan.block[2]) + ")");

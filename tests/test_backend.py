@@ -125,7 +125,7 @@ def test_optimised_lowering_uses_the_blackwell_forms(ptx):
     assert "redux.sync.max.s32" in m and "red.global.max.s32" in m and "ld.global.v4.u32" in m and "shfl" not in m
     assert ".maxntid 256, 1, 1" in m
     h = ptx.emit(kb.helper_chain()).text
-    assert "call" not in h and h.count(".entry") == 1 and "ld.global.v4.u32" in h
+    assert "call" not in h and h.count(".entry") == 2 and "helper_chain__coarse" in h and "ld.global.v4.u32" in h
     h0 = emit0(ptx, kb.helper_chain())
     assert h0.count("mul.lo.s32") == 33 and "v4" not in h0   # 32 squarings plus the index product
 

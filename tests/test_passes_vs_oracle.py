@@ -38,7 +38,7 @@ def test_helper_chain_inlining_and_vectorising(ptx, orc):
     from _util import vp
     src = kb.helper_chain()
     opt = ptx.optimized_bir(src)
-    assert "call" not in opt and opt.count("func @") == 1 and "load v4i32" in opt
+    assert "call" not in opt and opt.count("func @") == 2 and "@helper_chain__coarse" in opt and "load v4i32" in opt
     x = np.random.default_rng(5).integers(0, 2**32, 300, dtype=np.uint64).astype(np.uint32)
     want = np.zeros(300, np.uint32)
     orc.orc_helper_chain_u32(vp(x), vp(want), ctypes.c_int32(297), ctypes.c_int64(320))
@@ -46,6 +46,21 @@ def test_helper_chain_inlining_and_vectorising(ptx, orc):
         got = np.zeros(300, np.uint32)
         run_kernel(text, "helper_chain", [x, got, 297], 320)
         assert np.array_equal(got, want)
+
+
+def test_coarse_variant_processes_the_same_elements_with_fewer_threads(ptx):
+    # `<name>__coarse` takes the caller's thread count as a last i64 parameter and may be launched
+    # with fewer, longer-running threads; results must equal the original under the caller's launch.
+    src = kb.load("vadd_i32")
+    opt = ptx.optimized_bir(src)
+    rng = np.random.default_rng(17)
+    for n, physical, logical in [(1000, 64, 1024), (1003, 32, 2000), (100, 8, 40), (37, 4, 64), (4099, 128, 4099), (9, 1, 9), (0, 2, 8)]:
+        a = rng.integers(-2**30, 2**30, max(n, 1) + 8, dtype=np.int64).astype(np.int32)
+        bb = a[::-1].copy()
+        c0 = np.full(max(n, 1) + 8, 0x7fffffff, np.int32); c1 = c0.copy()
+        run_kernel(src, "vadd_i32", [a, bb, c0, n], logical)
+        run_kernel(opt, "vadd_i32__coarse", [a, bb, c1, n, logical], physical)
+        assert np.array_equal(c0, c1), (n, physical, logical)
 
 
 def test_reduction_loop_vectoriser(ptx):
