@@ -16,6 +16,7 @@
 //   * phi moves go through temporaries when one phi of a block feeds another (swap problem).
 #include "emit.hpp"
 
+#include <algorithm>
 #include <cmath>
 #include <cstdio>
 #include <cstring>
@@ -77,7 +78,7 @@ const char* space_word(Space s) {
 struct FnEmitter {
     const Module& mod;
     const Function& f;
-    std::vector<std::string> body, decls, plan;
+    std::vector<std::string> body, decls, plan, extra_params, module_decls;
     int counts[NCLS] = {0, 0, 0, 0, 0, 0};
     std::map<uint32_t, std::vector<std::string>> regs;    // inst id -> registers (one per lane)
     std::vector<std::vector<std::string>> param_regs;
@@ -589,6 +590,19 @@ struct FnEmitter {
         line(std::string("redux.sync.") + m[in.sub] + " " + reg(Val::V(id)) + ", " + reg(in.ops[0]) + ", 0xffffffff;");
     }
 
+    // The pointer parameter a value is derived from through pointer additions, or -1.
+    int base_param(Val v) const {
+        for (int depth = 0; depth < 64; depth++) {
+            if (v.param) return f.params[v.idx].is_ptr() ? (int)v.idx : -1;
+            const Inst& d = f.insts[v.idx];
+            if (d.op != Opc::Bin || (BinOp)d.sub != BinOp::Add || !d.ty.is_ptr()) return -1;
+            if (f.val_ty(d.ops[0]).is_ptr()) v = d.ops[0];
+            else if (f.val_ty(d.ops[1]).is_ptr()) v = d.ops[1];
+            else return -1;
+        }
+        return -1;
+    }
+
     // `mma` as a CTA-collective op: every thread of the CTA reaches it, the tile product is
     // computed once.  This generic form spreads the m*n outputs over the CTA's threads and
     // follows the oracle's arithmetic exactly: acc = 0; acc = acc + a*b (two roundings);
@@ -601,7 +615,19 @@ struct FnEmitter {
         const Inst* cd = in.ops[2].param ? nullptr : &f.insts[in.ops[2].idx];
         site.c_is_null = cd && cd->op == Opc::ConstI && cd->ty.is_ptr() && cd->ty.sp == Space::Global && cd->imm == 0;
         site.uid = mma_n++;
-        if (emit_mma_fast(site, f.name, &decls, &body, &plan)) return;
+        site.kernel = f.name;
+        site.nparams = (unsigned)f.params.size();
+        site.max_threads = mod.has_launch_bounds ? mod.max_threads : 0;
+        size_t n_mma = 0;
+        for (auto& b : f.blocks) for (uint32_t id : b.insts) n_mma += f.insts[id].op == Opc::Mma;
+        site.sole_mma = n_mma == 1;
+        site.a_param = base_param(in.ops[0]);
+        site.b_param = base_param(in.ops[1]);
+        if (site.a_param >= 0) site.a_base = param_regs[site.a_param][0];
+        if (site.b_param >= 0) site.b_base = param_regs[site.b_param][0];
+        site.extra_params = &extra_params;
+        site.module_decls = &module_decls;
+        if (emit_mma_fast(site, &decls, &body, &plan)) return;
 
         const int64_t lda = in.has_ld && in.ld[0] ? in.ld[0] : (in.a_col ? in.m : in.k);
         const int64_t ldb = in.has_ld && in.ld[1] ? in.ld[1] : (in.b_col ? in.k : in.n);
@@ -805,8 +831,11 @@ struct FnEmitter {
             if (failed) return false;
         }
         std::string o = ".visible .entry " + f.name + "(";
-        for (size_t i = 0; i < f.params.size(); i++) o += (i ? ",\n\t" : "\n\t") + param_decl(i);
-        o += f.params.empty() ? ")\n" : "\n)\n";
+        std::vector<std::string> pd;
+        for (size_t i = 0; i < f.params.size(); i++) pd.push_back(param_decl(i));
+        for (auto& e : extra_params) pd.push_back(e);
+        for (size_t i = 0; i < pd.size(); i++) o += (i ? ",\n\t" : "\n\t") + pd[i];
+        o += pd.empty() ? ")\n" : "\n)\n";
         if (mod.has_launch_bounds) {
             o += ".maxntid " + std::to_string(mod.max_threads) + ", 1, 1\n";
             if (mod.min_blocks) o += ".minnctapersm " + std::to_string(mod.min_blocks) + "\n";
@@ -836,7 +865,8 @@ bool emit_ptx(const Module& in, const EmitOptions& opts, EmitResult* out, Diag* 
     }
     if (opts.want_bir) out->bir = print_module(m);
     std::string text = "//\n// Generated by basalt-b200 (nvidia-ptx-sm100)\n//\n.version 8.7\n.target sm_100a\n.address_size 64\n\n";
-    std::vector<std::string> plans;
+    std::string bodies;
+    std::vector<std::string> module_decls;
     for (size_t i = 0; i < m.funcs.size(); i++) {
         const Function& f = m.funcs[i];
         const OptReport& r = out->reports[i];
@@ -855,9 +885,13 @@ bool emit_ptx(const Module& in, const EmitOptions& opts, EmitResult* out, Diag* 
             return false;
         }
         for (auto& p : fe.plan) text += p + "\n";
-        text += fn_text + "\n";
+        for (auto& md : fe.module_decls)
+            if (std::find(module_decls.begin(), module_decls.end(), md) == module_decls.end()) module_decls.push_back(md);
+        bodies += fn_text + "\n";
     }
-    out->ptx = text;
+    text += "\n";
+    for (auto& md : module_decls) text += md + "\n";
+    out->ptx = text + bodies;
     return true;
 }
 

@@ -33,8 +33,16 @@ struct MmaSite {
     Space sa, sb, sc, sd;         // their address spaces
     bool c_is_null;               // operand c is the literal null pointer: D = A*B
     int uid;                      // unique per function, for labels and symbols
+    std::string kernel;           // entry name
+    unsigned nparams;             // number of BIR parameters of the entry
+    unsigned max_threads;         // the module's launch_bounds max_threads, 0 when absent
+    bool sole_mma;                // the function's only mma
+    int a_param, b_param;         // parameter each operand pointer is derived from by pointer adds, or -1
+    std::string a_base, b_base;   // registers holding those parameters
+    std::vector<std::string>* extra_params;   // receives .param declarations appended to the entry
+    std::vector<std::string>* module_decls;   // receives module-scope declarations
 };
-bool emit_mma_fast(const MmaSite& site, const std::string& kernel, std::vector<std::string>* decls,
-                   std::vector<std::string>* lines, std::vector<std::string>* plan);
+bool emit_mma_fast(const MmaSite& site, std::vector<std::string>* decls, std::vector<std::string>* lines,
+                   std::vector<std::string>* plan);
 
 }  // namespace basalt

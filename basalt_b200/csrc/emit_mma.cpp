@@ -1,10 +1,439 @@
-// CTA-wide lowerings of `mma` (register-tiled FFMA for f32, TMA + tcgen05 for f16).
+// CTA-wide lowerings of `mma` for sm_100a.
+//
+// In this backend `mma` is a CTA-collective tile operation (every thread of the CTA reaches it,
+// the product is computed once), so a kernel whose CTA computes one output tile is a few address
+// computations and one `mma` over strided tiles of the full matrices.  Two shapes get a dedicated
+// lowering; everything else takes the generic loop nest in emit.cpp.
+//
+//  * f32 x f32 -> f32, 128x128 tile, 256 threads: register-tiled FFMA.  K slabs of 16 are staged
+//    through a double-buffered shared-memory tile pair (A transposed so that a thread's four rows
+//    are one 16-byte read); each thread owns 8x8 outputs as four 4x4 quadrants; per K step it
+//    issues 4 ld.shared.v4 for 64 fma.rn.f32; the next slab's global loads are in flight while the
+//    current one is multiplied.  The same design as the hand-written comparator kernel
+//    (kernels/sgemm.cu).
+//  * f16 x f16 -> f32 accumulate -> f16, 128x128 tile, 128 threads: TMA + tcgen05.  One thread
+//    issues cp.async.bulk.tensor loads of 64-deep K slabs into a ring of 128-byte-swizzled shared
+//    stages, one thread issues tcgen05.mma (M128 N128 K16) from shared-memory matrix descriptors
+//    into a TMEM accumulator, mbarriers (tcgen05.commit) hand stages back; all four warps drain the
+//    accumulator with tcgen05.ld, convert and store.  The tensor maps are kernel parameters the
+//    launch runtime appends (the `//!basalt.plan` line says how to build them).  Every mbarrier
+//    wait is bounded by %globaltimer; a wait that gives up sets the kernel's status word, the
+//    kernel stops issuing copies, still frees its TMEM and returns.
+#include <cstdarg>
+#include <cstdio>
+
 #include "emit.hpp"
 
 namespace basalt {
+namespace {
 
-bool emit_mma_fast(const MmaSite&, const std::string&, std::vector<std::string>*, std::vector<std::string>*, std::vector<std::string>*) {
-    return false;
+struct Out {
+    std::vector<std::string>* lines;
+    void operator()(const char* fmt, ...) {
+        char buf[1024];
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(buf, sizeof buf, fmt, ap);
+        va_end(ap);
+        lines->push_back(std::string("\t") + buf);
+    }
+    void label(const std::string& l) { lines->push_back(l + ":"); }
+};
+
+bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<std::string>* lines, std::vector<std::string>* plan) {
+    const Inst& in = *s.inst;
+    if (in.in_dt != Scalar::F32 || in.acc_dt != Scalar::F32 || in.out_dt != Scalar::F32 || in.a_col || in.b_col) return false;
+    if (in.m != 128 || in.n != 128 || in.k % 16 != 0 || !s.c_is_null || !in.has_ld) return false;
+    if (s.sa != Space::Global || s.sb != Space::Global || s.sd != Space::Global || s.max_threads != 256) return false;
+    const long long lda = in.ld[0] ? in.ld[0] : in.k, ldb = in.ld[1] ? in.ld[1] : in.n, ldd = in.ld[3] ? in.ld[3] : in.n;
+    if (lda % 4 || ldb % 4 || ldd % 4 || lda * 4 >= (1ll << 31) || ldb * 4 >= (1ll << 31) || ldd * 4 >= (1ll << 31)) return false;
+    const int u = s.uid, nk = (int)(in.k / 16);
+    char nm[64];
+    auto R = [&](const char* stem, int i = -1) {
+        if (i < 0) snprintf(nm, sizeof nm, "%%mm%d_%s", u, stem);
+        else snprintf(nm, sizeof nm, "%%mm%d_%s%d", u, stem, i);
+        return std::string(nm);
+    };
+    char d[256];
+    snprintf(d, sizeof d, "\t.reg .f32 %%mm%d_acc<64>, %%mm%d_fa<8>, %%mm%d_fb<8>, %%mm%d_st<16>;", u, u, u, u);
+    decls->push_back(d);
+    snprintf(d, sizeof d, "\t.reg .b32 %%mm%d_tid, %%mm%d_tx, %%mm%d_ty, %%mm%d_t, %%mm%d_arow, %%mm%d_acol, %%mm%d_brow, %%mm%d_bcol, %%mm%d_asst, %%mm%d_bsst, %%mm%d_asrd, %%mm%d_bsrd, %%mm%d_as, %%mm%d_bs, %%mm%d_kb, %%mm%d_kb1, %%mm%d_off, %%mm%d_x, %%mm%d_y;",
+             u, u, u, u, u, u, u, u, u, u, u, u, u, u, u, u, u, u, u);
+    decls->push_back(d);
+    snprintf(d, sizeof d, "\t.reg .b64 %%mm%d_ag, %%mm%d_ag2, %%mm%d_bg, %%mm%d_bg2, %%mm%d_w, %%mm%d_c;", u, u, u, u, u, u);
+    decls->push_back(d);
+    snprintf(d, sizeof d, "\t.reg .pred %%mm%d_more, %%mm%d_bad;", u, u);
+    decls->push_back(d);
+    snprintf(d, sizeof d, "\t.shared .align 16 .b8 __mm%d_as[16384];", u);
+    decls->push_back(d);
+    snprintf(d, sizeof d, "\t.shared .align 16 .b8 __mm%d_bs[16384];", u);
+    decls->push_back(d);
+    std::string l_loop = "$mm" + std::to_string(u) + "_loop", l_done = "$mm" + std::to_string(u) + "_done", l_skip = "$mm" + std::to_string(u) + "_skip";
+    Out o{lines};
+    const std::string tid = R("tid"), tx = R("tx"), ty = R("ty"), t = R("t"), arow = R("arow"), acol = R("acol"), brow = R("brow"), bcol = R("bcol");
+    const std::string asst = R("asst"), bsst = R("bsst"), asrd = R("asrd"), bsrd = R("bsrd"), as = R("as"), bs = R("bs"), kb = R("kb"), kb1 = R("kb1"), off = R("off");
+    const std::string x = R("x"), y = R("y"), ag = R("ag"), ag2 = R("ag2"), bg = R("bg"), bg2 = R("bg2"), w = R("w"), cp = R("c"), more = R("more"), bad = R("bad");
+    auto acc = [&](int i) { return R("acc", i); };
+    auto st = [&](int i) { return R("st", i); };
+    auto fa = [&](int i) { return R("fa", i); };
+    auto fb = [&](int i) { return R("fb", i); };
+
+    o("// mma f32 128x128x%u: register-tiled FFMA, lda=%lld ldb=%lld ldd=%lld", in.k, lda, ldb, ldd);
+    o("mov.u32 %s, %%ntid.x;", t.c_str());
+    o("setp.ne.u32 %s, %s, 256;", bad.c_str(), t.c_str());
+    o("@%s bra %s;", bad.c_str(), l_skip.c_str());   // wrong block size: leave the output untouched rather than misbehave
+    o("mov.u32 %s, %%tid.x;", tid.c_str());
+    o("and.b32 %s, %s, 15;", tx.c_str(), tid.c_str());
+    o("shr.u32 %s, %s, 4;", ty.c_str(), tid.c_str());
+    o("shr.u32 %s, %s, 2;", arow.c_str(), tid.c_str());
+    o("and.b32 %s, %s, 3;", t.c_str(), tid.c_str());
+    o("shl.b32 %s, %s, 2;", acol.c_str(), t.c_str());
+    o("shr.u32 %s, %s, 5;", brow.c_str(), tid.c_str());
+    o("and.b32 %s, %s, 31;", t.c_str(), tid.c_str());
+    o("shl.b32 %s, %s, 2;", bcol.c_str(), t.c_str());
+    o("mul.wide.u32 %s, %s, %lld;", w.c_str(), arow.c_str(), lda * 4);
+    o("add.u64 %s, %s, %s;", ag.c_str(), s.a.c_str(), w.c_str());
+    o("mul.wide.u32 %s, %s, 4;", w.c_str(), acol.c_str());
+    o("add.u64 %s, %s, %s;", ag.c_str(), ag.c_str(), w.c_str());
+    o("add.u64 %s, %s, %lld;", ag2.c_str(), ag.c_str(), 64 * lda * 4);
+    o("mul.wide.u32 %s, %s, %lld;", w.c_str(), brow.c_str(), ldb * 4);
+    o("add.u64 %s, %s, %s;", bg.c_str(), s.b.c_str(), w.c_str());
+    o("mul.wide.u32 %s, %s, 4;", w.c_str(), bcol.c_str());
+    o("add.u64 %s, %s, %s;", bg.c_str(), bg.c_str(), w.c_str());
+    o("add.u64 %s, %s, %lld;", bg2.c_str(), bg.c_str(), 8 * ldb * 4);
+    o("mov.u64 %s, __mm%d_as;", w.c_str(), u);
+    o("cvt.u32.u64 %s, %s;", as.c_str(), w.c_str());
+    o("mov.u64 %s, __mm%d_bs;", w.c_str(), u);
+    o("cvt.u32.u64 %s, %s;", bs.c_str(), w.c_str());
+    o("mad.lo.u32 %s, %s, 512, %s;", t.c_str(), acol.c_str(), as.c_str());
+    o("mad.lo.u32 %s, %s, 4, %s;", asst.c_str(), arow.c_str(), t.c_str());
+    o("mad.lo.u32 %s, %s, 512, %s;", t.c_str(), brow.c_str(), bs.c_str());
+    o("mad.lo.u32 %s, %s, 4, %s;", bsst.c_str(), bcol.c_str(), t.c_str());
+    o("mad.lo.u32 %s, %s, 16, %s;", asrd.c_str(), ty.c_str(), as.c_str());
+    o("mad.lo.u32 %s, %s, 16, %s;", bsrd.c_str(), tx.c_str(), bs.c_str());
+    for (int i = 0; i < 64; i++) o("mov.f32 %s, 0f00000000;", acc(i).c_str());
+    auto fetch = [&](const char* pred) {
+        o("%sld.global.v4.f32 {%s, %s, %s, %s}, [%s];", pred, st(0).c_str(), st(1).c_str(), st(2).c_str(), st(3).c_str(), ag.c_str());
+        o("%sld.global.v4.f32 {%s, %s, %s, %s}, [%s];", pred, st(4).c_str(), st(5).c_str(), st(6).c_str(), st(7).c_str(), ag2.c_str());
+        o("%sld.global.v4.f32 {%s, %s, %s, %s}, [%s];", pred, st(8).c_str(), st(9).c_str(), st(10).c_str(), st(11).c_str(), bg.c_str());
+        o("%sld.global.v4.f32 {%s, %s, %s, %s}, [%s];", pred, st(12).c_str(), st(13).c_str(), st(14).c_str(), st(15).c_str(), bg2.c_str());
+    };
+    auto stash = [&]() {   // into the buffer at byte offset `off`
+        o("add.u32 %s, %s, %s;", x.c_str(), asst.c_str(), off.c_str());
+        for (int c = 0; c < 4; c++) {
+            o("st.shared.f32 [%s+%d], %s;", x.c_str(), c * 512, st(c).c_str());
+            o("st.shared.f32 [%s+%d], %s;", x.c_str(), c * 512 + 256, st(4 + c).c_str());
+        }
+        o("add.u32 %s, %s, %s;", y.c_str(), bsst.c_str(), off.c_str());
+        o("st.shared.v4.f32 [%s], {%s, %s, %s, %s};", y.c_str(), st(8).c_str(), st(9).c_str(), st(10).c_str(), st(11).c_str());
+        o("st.shared.v4.f32 [%s+4096], {%s, %s, %s, %s};", y.c_str(), st(12).c_str(), st(13).c_str(), st(14).c_str(), st(15).c_str());
+    };
+    o("mov.u32 %s, 0;", off.c_str());
+    o("mov.u32 %s, 0;", kb.c_str());
+    fetch("");
+    stash();
+    o("bar.sync 0;");
+    o.label(l_loop);
+    o("add.u32 %s, %s, 1;", kb1.c_str(), kb.c_str());
+    o("setp.lt.u32 %s, %s, %d;", more.c_str(), kb1.c_str(), nk);
+    o("add.u64 %s, %s, 64;", ag.c_str(), ag.c_str());
+    o("add.u64 %s, %s, 64;", ag2.c_str(), ag2.c_str());
+    o("add.u64 %s, %s, %lld;", bg.c_str(), bg.c_str(), 16 * ldb * 4);
+    o("add.u64 %s, %s, %lld;", bg2.c_str(), bg2.c_str(), 16 * ldb * 4);
+    fetch(("@" + more + " ").c_str());
+    o("add.u32 %s, %s, %s;", x.c_str(), asrd.c_str(), off.c_str());
+    o("add.u32 %s, %s, %s;", y.c_str(), bsrd.c_str(), off.c_str());
+    for (int k = 0; k < 16; k++) {
+        o("ld.shared.v4.f32 {%s, %s, %s, %s}, [%s+%d];", fa(0).c_str(), fa(1).c_str(), fa(2).c_str(), fa(3).c_str(), x.c_str(), k * 512);
+        o("ld.shared.v4.f32 {%s, %s, %s, %s}, [%s+%d];", fa(4).c_str(), fa(5).c_str(), fa(6).c_str(), fa(7).c_str(), x.c_str(), k * 512 + 256);
+        o("ld.shared.v4.f32 {%s, %s, %s, %s}, [%s+%d];", fb(0).c_str(), fb(1).c_str(), fb(2).c_str(), fb(3).c_str(), y.c_str(), k * 512);
+        o("ld.shared.v4.f32 {%s, %s, %s, %s}, [%s+%d];", fb(4).c_str(), fb(5).c_str(), fb(6).c_str(), fb(7).c_str(), y.c_str(), k * 512 + 256);
+        for (int i = 0; i < 8; i++)
+            for (int j = 0; j < 8; j++) o("fma.rn.f32 %s, %s, %s, %s;", acc(i * 8 + j).c_str(), fa(i).c_str(), fb(j).c_str(), acc(i * 8 + j).c_str());
+    }
+    o("@!%s bra %s;", more.c_str(), l_done.c_str());
+    o("xor.b32 %s, %s, 8192;", off.c_str(), off.c_str());
+    stash();
+    o("bar.sync 0;");
+    o("mov.u32 %s, %s;", kb.c_str(), kb1.c_str());
+    o("bra %s;", l_loop.c_str());
+    o.label(l_done);
+    // rows ty*4 + (i&3) + (i>>2)*64, columns tx*4 and tx*4 + 64
+    o("shl.b32 %s, %s, 2;", t.c_str(), ty.c_str());
+    o("mul.wide.u32 %s, %s, %lld;", w.c_str(), t.c_str(), ldd * 4);
+    o("add.u64 %s, %s, %s;", cp.c_str(), s.d.c_str(), w.c_str());
+    o("mul.wide.u32 %s, %s, 16;", w.c_str(), tx.c_str());
+    o("add.u64 %s, %s, %s;", cp.c_str(), cp.c_str(), w.c_str());
+    for (int i = 0; i < 8; i++) {
+        long long rowoff = ((i & 3) + (i >> 2) * 64) * ldd * 4;
+        o("st.global.v4.f32 [%s+%lld], {%s, %s, %s, %s};", cp.c_str(), rowoff, acc(i * 8).c_str(), acc(i * 8 + 1).c_str(), acc(i * 8 + 2).c_str(), acc(i * 8 + 3).c_str());
+        o("st.global.v4.f32 [%s+%lld], {%s, %s, %s, %s};", cp.c_str(), rowoff + 256, acc(i * 8 + 4).c_str(), acc(i * 8 + 5).c_str(), acc(i * 8 + 6).c_str(), acc(i * 8 + 7).c_str());
+    }
+    o.label(l_skip);
+    o("bar.sync 0;");
+    char pl[256];
+    snprintf(pl, sizeof pl, "//!basalt.plan %s block=256,1,1 params=%u", s.kernel.c_str(), s.nparams);
+    plan->push_back(pl);
+    return true;
+}
+
+bool matmul_tcgen05(const MmaSite& s, std::vector<std::string>* decls, std::vector<std::string>* lines, std::vector<std::string>* plan) {
+    const Inst& in = *s.inst;
+    if (in.in_dt != Scalar::F16 || in.acc_dt != Scalar::F32 || in.out_dt != Scalar::F16 || in.a_col) return false;
+    if (in.m != 128 || in.n != 128 || in.k % 64 != 0 || !s.c_is_null || !in.has_ld || !s.sole_mma) return false;
+    if (s.sa != Space::Global || s.sb != Space::Global || s.sd != Space::Global || s.max_threads != 128) return false;
+    if (s.a_param < 0 || s.b_param < 0 || !s.extra_params || !s.module_decls) return false;
+    const bool b_nk = in.b_col;   // B stored [N x K]: K-major like A; otherwise [K x N]: MN-major
+    const long long lda = in.ld[0] ? in.ld[0] : in.k, ldb = in.ld[1] ? in.ld[1] : (b_nk ? in.k : in.n), ldd = in.ld[3] ? in.ld[3] : in.n;
+    if (lda % 8 || ldb % 8 || ldd % 8) return false;   // 16-byte rows for TMA and for the 16-byte stores
+    const int u = s.uid, num_kb = (int)(in.k / 64), STAGES = 3, STAGE_BYTES = 32768;
+    const unsigned smem = STAGES * STAGE_BYTES + 1024;
+    const std::string P = "%mt" + std::to_string(u) + "_";
+    auto r = [&](const char* n) { return P + n; };
+    char d[512];
+    snprintf(d, sizeof d, "\t.reg .b32 %stid, %swarp, %slane, %st, %stiles, %sbars, %sfull, %sempty, %saccb, %sslot, %sgu, %stmem, %sok, %skb, %ss, %sph, %spar, %sadst, %sbdst, %sm0, %sn0, %sx, %sit, %sg, %sidesc, %slb, %sh<8>, %sv<16>;",
+             P.c_str(), P.c_str(), P.c_str(), P.c_str(), P.c_str(), P.c_str(), P.c_str(), P.c_str(), P.c_str(), P.c_str(), P.c_str(), P.c_str(), P.c_str(), P.c_str(),
+             P.c_str(), P.c_str(), P.c_str(), P.c_str(), P.c_str(), P.c_str(), P.c_str(), P.c_str(), P.c_str(), P.c_str(), P.c_str(), P.c_str(), P.c_str(), P.c_str());
+    decls->push_back(d);
+    snprintf(d, sizeof d, "\t.reg .b64 %sw, %soff, %srow, %scol, %sda, %sdb, %st0, %snow, %sdt, %scrow, %sstatus, %sma, %smb;", P.c_str(), P.c_str(), P.c_str(), P.c_str(), P.c_str(),
+             P.c_str(), P.c_str(), P.c_str(), P.c_str(), P.c_str(), P.c_str(), P.c_str(), P.c_str());
+    decls->push_back(d);
+    snprintf(d, sizeof d, "\t.reg .pred %sp, %sq, %sprod, %smma, %sw1, %sacc, %sdone;", P.c_str(), P.c_str(), P.c_str(), P.c_str(), P.c_str(), P.c_str(), P.c_str());
+    decls->push_back(d);
+    snprintf(d, sizeof d, "\t.shared .align 8 .b8 __mt%d_bars[%d];", u, 8 * (2 * STAGES + 1));
+    decls->push_back(d);
+    snprintf(d, sizeof d, "\t.shared .align 4 .b8 __mt%d_misc[8];", u);   // [0]: TMEM base column, [4]: a wait gave up
+    decls->push_back(d);
+    s.module_decls->push_back(".extern .shared .align 1024 .b8 __basalt_dyn_smem[];");
+    const std::string ta = s.kernel + "_tmap_a", tb = s.kernel + "_tmap_b", stp = s.kernel + "_status";
+    s.extra_params->push_back(".param .align 64 .b8 " + ta + "[128]");
+    s.extra_params->push_back(".param .align 64 .b8 " + tb + "[128]");
+    s.extra_params->push_back(".param .u64 " + stp);
+    const std::string L = "$mt" + std::to_string(u) + "_";
+    Out o{lines};
+    int wait_n = 0;
+    // Bounded wait on the mbarrier at shared address `bar` for phase parity `par`; on give-up
+    // clears %ok and jumps to `fail`.
+    auto wait = [&](const std::string& bar, const std::string& par, const std::string& fail) {
+        std::string lw = L + "w" + std::to_string(wait_n) + "_loop", ld = L + "w" + std::to_string(wait_n) + "_done", lf = L + "w" + std::to_string(wait_n) + "_fail",
+                    lt = L + "w" + std::to_string(wait_n) + "_t";
+        wait_n++;
+        o("mov.u64 %s, 0;", r("t0").c_str());
+        o("mov.u32 %s, 0;", r("it").c_str());
+        o.label(lw);
+        o("mbarrier.try_wait.parity.shared::cta.b64 %s, [%s], %s;", r("done").c_str(), bar.c_str(), par.c_str());
+        o("@%s bra %s;", r("done").c_str(), ld.c_str());
+        o("ld.volatile.shared.u32 %s, [%s];", r("g").c_str(), r("gu").c_str());
+        o("setp.ne.u32 %s, %s, 0;", r("q").c_str(), r("g").c_str());
+        o("@%s bra %s;", r("q").c_str(), lf.c_str());
+        o("add.u32 %s, %s, 1;", r("it").c_str(), r("it").c_str());
+        o("and.b32 %s, %s, 63;", r("g").c_str(), r("it").c_str());
+        o("setp.ne.u32 %s, %s, 0;", r("q").c_str(), r("g").c_str());
+        o("@%s bra %s;", r("q").c_str(), lw.c_str());
+        o("mov.u64 %s, %%globaltimer;", r("now").c_str());
+        o("setp.ne.u64 %s, %s, 0;", r("q").c_str(), r("t0").c_str());
+        o("@%s bra %s;", r("q").c_str(), lt.c_str());
+        o("mov.u64 %s, %s;", r("t0").c_str(), r("now").c_str());
+        o("bra %s;", lw.c_str());
+        o.label(lt);
+        o("sub.u64 %s, %s, %s;", r("dt").c_str(), r("now").c_str(), r("t0").c_str());
+        o("setp.lt.u64 %s, %s, 200000000;", r("q").c_str(), r("dt").c_str());   // 200 ms
+        o("@%s bra %s;", r("q").c_str(), lw.c_str());
+        o("st.volatile.shared.u32 [%s], 1;", r("gu").c_str());
+        o.label(lf);
+        o("mov.u32 %s, 0;", r("ok").c_str());
+        o("bra %s;", fail.c_str());
+        o.label(ld);
+    };
+
+    o("// mma f16->f32->f16 128x128x%u: TMA + tcgen05, %s B, lda=%lld ldb=%lld ldd=%lld", in.k, b_nk ? "K-major" : "MN-major", lda, ldb, ldd);
+    o("mov.u32 %s, %%ntid.x;", r("t").c_str());
+    o("setp.ne.u32 %s, %s, 128;", r("p").c_str(), r("t").c_str());
+    o("@%s bra %sskip;", r("p").c_str(), L.c_str());
+    o("ld.param.u64 %s, [%s];", r("status").c_str(), stp.c_str());
+    o("ld.volatile.global.u32 %s, [%s];", r("t").c_str(), r("status").c_str());
+    o("setp.ne.u32 %s, %s, 0;", r("p").c_str(), r("t").c_str());
+    o("@%s bra %sskip;", r("p").c_str(), L.c_str());   // an earlier CTA gave up: do not pile on
+    o("mov.b64 %s, %s;", r("ma").c_str(), ta.c_str());   // generic addresses of the two tensor-map parameters
+    o("cvta.param.u64 %s, %s;", r("ma").c_str(), r("ma").c_str());
+    o("mov.b64 %s, %s;", r("mb").c_str(), tb.c_str());
+    o("cvta.param.u64 %s, %s;", r("mb").c_str(), r("mb").c_str());
+    o("mov.u32 %s, %%tid.x;", r("tid").c_str());
+    o("shr.u32 %s, %s, 5;", r("warp").c_str(), r("tid").c_str());
+    o("and.b32 %s, %s, 31;", r("lane").c_str(), r("tid").c_str());
+    o("mov.u64 %s, __basalt_dyn_smem;", r("w").c_str());
+    o("cvt.u32.u64 %s, %s;", r("tiles").c_str(), r("w").c_str());
+    o("add.u32 %s, %s, 1023;", r("tiles").c_str(), r("tiles").c_str());
+    o("and.b32 %s, %s, 0xFFFFFC00;", r("tiles").c_str(), r("tiles").c_str());
+    o("mov.u64 %s, __mt%d_bars;", r("w").c_str(), u);
+    o("cvt.u32.u64 %s, %s;", r("bars").c_str(), r("w").c_str());
+    o("add.u32 %s, %s, %d;", r("accb").c_str(), r("bars").c_str(), 16 * STAGES);
+    o("mov.u64 %s, __mt%d_misc;", r("w").c_str(), u);
+    o("cvt.u32.u64 %s, %s;", r("slot").c_str(), r("w").c_str());
+    o("add.u32 %s, %s, 4;", r("gu").c_str(), r("slot").c_str());
+    // tile coordinates from the operand pointers: offset from the matrix base, split by the row pitch
+    o("sub.u64 %s, %s, %s;", r("off").c_str(), s.a.c_str(), s.a_base.c_str());
+    o("div.u64 %s, %s, %lld;", r("row").c_str(), r("off").c_str(), lda * 2);
+    o("cvt.u32.u64 %s, %s;", r("m0").c_str(), r("row").c_str());
+    o("sub.u64 %s, %s, %s;", r("off").c_str(), s.b.c_str(), s.b_base.c_str());
+    if (b_nk) {
+        o("div.u64 %s, %s, %lld;", r("row").c_str(), r("off").c_str(), ldb * 2);
+        o("cvt.u32.u64 %s, %s;", r("n0").c_str(), r("row").c_str());
+    } else {
+        o("shr.u64 %s, %s, 1;", r("col").c_str(), r("off").c_str());
+        o("cvt.u32.u64 %s, %s;", r("n0").c_str(), r("col").c_str());   // the B tile pointer sits in row 0
+    }
+    o("setp.ne.u32 %s, %s, 0;", r("p").c_str(), r("tid").c_str());
+    o("@%s bra %sinit_done;", r("p").c_str(), L.c_str());
+    o("st.volatile.shared.u32 [%s], 0;", r("gu").c_str());
+    for (int i = 0; i < 2 * STAGES + 1; i++) o("mbarrier.init.shared::cta.b64 [%s+%d], 1;", r("bars").c_str(), 8 * i);
+    o("fence.mbarrier_init.release.cluster;");
+    o("fence.proxy.async.shared::cta;");
+    o.label(L + "init_done");
+    o("setp.eq.u32 %s, %s, 1;", r("w1").c_str(), r("warp").c_str());
+    o("@!%s bra %salloc_done;", r("w1").c_str(), L.c_str());
+    o("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%s], 128;", r("slot").c_str());
+    o("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+    o.label(L + "alloc_done");
+    o("tcgen05.fence::before_thread_sync;");
+    o("bar.sync 0;");
+    o("tcgen05.fence::after_thread_sync;");
+    o("ld.shared.u32 %s, [%s];", r("tmem").c_str(), r("slot").c_str());
+    o("mov.u32 %s, 1;", r("ok").c_str());
+    o("setp.eq.u32 %s, %s, 0;", r("p").c_str(), r("lane").c_str());
+    o("setp.eq.u32 %s, %s, 0;", r("q").c_str(), r("warp").c_str());
+    o("and.pred %s, %s, %s;", r("prod").c_str(), r("p").c_str(), r("q").c_str());
+    o("and.pred %s, %s, %s;", r("mma").c_str(), r("p").c_str(), r("w1").c_str());
+    o("@%s bra %sproducer;", r("prod").c_str(), L.c_str());
+    o("@%s bra %sissuer;", r("mma").c_str(), L.c_str());
+    o("bra %sjoin;", L.c_str());
+
+    // ---- TMA producer: one thread ----
+    o.label(L + "producer");
+    o("mov.u32 %s, 0;", r("kb").c_str());
+    o("mov.u32 %s, 0;", r("s").c_str());
+    o("mov.u32 %s, 0;", r("ph").c_str());
+    o.label(L + "p_loop");
+    o("mad.lo.u32 %s, %s, 8, %s;", r("full").c_str(), r("s").c_str(), r("bars").c_str());
+    o("add.u32 %s, %s, %d;", r("empty").c_str(), r("full").c_str(), 8 * STAGES);
+    o("xor.b32 %s, %s, 1;", r("par").c_str(), r("ph").c_str());   // a fresh barrier passes a wait on parity 1
+    wait(r("empty"), r("par"), L + "join");
+    o("mad.lo.u32 %s, %s, %d, %s;", r("adst").c_str(), r("s").c_str(), STAGE_BYTES, r("tiles").c_str());
+    o("add.u32 %s, %s, 16384;", r("bdst").c_str(), r("adst").c_str());
+    o("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%s], %d;", r("full").c_str(), STAGE_BYTES);
+    o("shl.b32 %s, %s, 6;", r("x").c_str(), r("kb").c_str());   // k coordinate of this slab
+    o("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%s], [%s, {%s, %s}], [%s];", r("adst").c_str(), r("ma").c_str(), r("x").c_str(),
+      r("m0").c_str(), r("full").c_str());
+    if (b_nk) {
+        o("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%s], [%s, {%s, %s}], [%s];", r("bdst").c_str(), r("mb").c_str(), r("x").c_str(),
+          r("n0").c_str(), r("full").c_str());
+    } else {
+        o("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%s], [%s, {%s, %s}], [%s];", r("bdst").c_str(), r("mb").c_str(), r("n0").c_str(),
+          r("x").c_str(), r("full").c_str());
+        o("add.u32 %s, %s, 8192;", r("bdst").c_str(), r("bdst").c_str());
+        o("add.u32 %s, %s, 64;", r("t").c_str(), r("n0").c_str());
+        o("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%s], [%s, {%s, %s}], [%s];", r("bdst").c_str(), r("mb").c_str(), r("t").c_str(),
+          r("x").c_str(), r("full").c_str());
+    }
+    o("add.u32 %s, %s, 1;", r("s").c_str(), r("s").c_str());
+    o("setp.eq.u32 %s, %s, %d;", r("p").c_str(), r("s").c_str(), STAGES);
+    o("@%s mov.u32 %s, 0;", r("p").c_str(), r("s").c_str());
+    o("@%s xor.b32 %s, %s, 1;", r("p").c_str(), r("ph").c_str(), r("ph").c_str());
+    o("add.u32 %s, %s, 1;", r("kb").c_str(), r("kb").c_str());
+    o("setp.lt.u32 %s, %s, %d;", r("p").c_str(), r("kb").c_str(), num_kb);
+    o("@%s bra %sp_loop;", r("p").c_str(), L.c_str());
+    o("bra %sjoin;", L.c_str());
+
+    // ---- MMA issuer: one thread ----
+    // Instruction descriptor: D f32 (bits 4-5 = 1), A and B f16 (0), B major-ness in bit 16, N/8 in
+    // bits 17-22, M/16 in bits 24-28.  Matrix descriptors: address/16 in bits 0-13, leading offset/16
+    // in 16-29, stride offset/16 in 32-45, version 1 in 46-47, 128-byte swizzle (2) in 61-63.
+    const unsigned idesc = (1u << 4) | ((b_nk ? 0u : 1u) << 16) | (16u << 17) | (8u << 24);
+    const unsigned long long desc_a_hi = (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+    const unsigned long long desc_b_hi = b_nk ? desc_a_hi : ((512ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61));
+    o.label(L + "issuer");
+    o("mov.u32 %s, 0;", r("kb").c_str());
+    o("mov.u32 %s, 0;", r("s").c_str());
+    o("mov.u32 %s, 0;", r("ph").c_str());
+    o("mov.u32 %s, %u;", r("idesc").c_str(), idesc);
+    o.label(L + "m_loop");
+    o("mad.lo.u32 %s, %s, 8, %s;", r("full").c_str(), r("s").c_str(), r("bars").c_str());
+    o("add.u32 %s, %s, %d;", r("empty").c_str(), r("full").c_str(), 8 * STAGES);
+    wait(r("full"), r("ph"), L + "m_end");
+    o("tcgen05.fence::after_thread_sync;");
+    o("mad.lo.u32 %s, %s, %d, %s;", r("adst").c_str(), r("s").c_str(), STAGE_BYTES, r("tiles").c_str());
+    o("add.u32 %s, %s, 16384;", r("bdst").c_str(), r("adst").c_str());
+    for (int k = 0; k < 4; k++) {
+        // K-major: a K step of 16 halves is 32 bytes along the 128-byte row; MN-major B: 16 k rows = 2048 bytes
+        o("add.u32 %s, %s, %d;", r("x").c_str(), r("adst").c_str(), k * 32);
+        o("shr.u32 %s, %s, 4;", r("x").c_str(), r("x").c_str());
+        o("and.b32 %s, %s, 0x3FFF;", r("x").c_str(), r("x").c_str());
+        o("cvt.u64.u32 %s, %s;", r("da").c_str(), r("x").c_str());
+        o("or.b64 %s, %s, 0x%llX;", r("da").c_str(), r("da").c_str(), desc_a_hi);
+        o("add.u32 %s, %s, %d;", r("x").c_str(), r("bdst").c_str(), b_nk ? k * 32 : k * 2048);
+        o("shr.u32 %s, %s, 4;", r("x").c_str(), r("x").c_str());
+        o("and.b32 %s, %s, 0x3FFF;", r("x").c_str(), r("x").c_str());
+        o("cvt.u64.u32 %s, %s;", r("db").c_str(), r("x").c_str());
+        o("or.b64 %s, %s, 0x%llX;", r("db").c_str(), r("db").c_str(), desc_b_hi);
+        if (k == 0) o("setp.ne.u32 %s, %s, 0;", r("acc").c_str(), r("kb").c_str());   // the very first MMA overwrites the accumulator
+        else o("setp.ne.u32 %s, %s, 0;", r("acc").c_str(), r("idesc").c_str());   // always true
+        o("tcgen05.mma.cta_group::1.kind::f16 [%s], %s, %s, %s, %s;", r("tmem").c_str(), r("da").c_str(), r("db").c_str(), r("idesc").c_str(), r("acc").c_str());
+    }
+    o("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%s];", r("empty").c_str());
+    o("add.u32 %s, %s, 1;", r("s").c_str(), r("s").c_str());
+    o("setp.eq.u32 %s, %s, %d;", r("p").c_str(), r("s").c_str(), STAGES);
+    o("@%s mov.u32 %s, 0;", r("p").c_str(), r("s").c_str());
+    o("@%s xor.b32 %s, %s, 1;", r("p").c_str(), r("ph").c_str(), r("ph").c_str());
+    o("add.u32 %s, %s, 1;", r("kb").c_str(), r("kb").c_str());
+    o("setp.lt.u32 %s, %s, %d;", r("p").c_str(), r("kb").c_str(), num_kb);
+    o("@%s bra %sm_loop;", r("p").c_str(), L.c_str());
+    o.label(L + "m_end");
+    o("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%s];", r("accb").c_str());
+
+    // ---- epilogue: all four warps ----
+    o.label(L + "join");
+    o("bar.warp.sync 0xffffffff;");
+    o("mov.u32 %s, 0;", r("par").c_str());
+    wait(r("accb"), r("par"), L + "drain");
+    o.label(L + "drain");
+    o("tcgen05.fence::after_thread_sync;");
+    o("mad.lo.u32 %s, %s, 32, %s;", r("t").c_str(), r("warp").c_str(), r("lane").c_str());   // row of the tile
+    o("mul.wide.u32 %s, %s, %lld;", r("w").c_str(), r("t").c_str(), ldd * 2);
+    o("add.u64 %s, %s, %s;", r("crow").c_str(), s.d.c_str(), r("w").c_str());
+    o("shl.b32 %s, %s, 21;", r("lb").c_str(), r("warp").c_str());   // (warp*32) << 16: the warp's TMEM lanes
+    o("add.u32 %s, %s, %s;", r("lb").c_str(), r("lb").c_str(), r("tmem").c_str());
+    for (int c = 0; c < 128; c += 16) {
+        std::string list;
+        for (int i = 0; i < 16; i++) list += (i ? ", " : "") + P + "v" + std::to_string(i);
+        o("add.u32 %s, %s, %d;", r("x").c_str(), r("lb").c_str(), c);
+        o("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%s}, [%s];", list.c_str(), r("x").c_str());
+        o("tcgen05.wait::ld.sync.aligned;");
+        for (int i = 0; i < 8; i++) o("cvt.rn.f16x2.f32 %sh%d, %sv%d, %sv%d;", P.c_str(), i, P.c_str(), 2 * i + 1, P.c_str(), 2 * i);
+        o("st.global.v4.b32 [%s+%d], {%sh0, %sh1, %sh2, %sh3};", r("crow").c_str(), c * 2, P.c_str(), P.c_str(), P.c_str(), P.c_str());
+        o("st.global.v4.b32 [%s+%d], {%sh4, %sh5, %sh6, %sh7};", r("crow").c_str(), c * 2 + 16, P.c_str(), P.c_str(), P.c_str(), P.c_str());
+    }
+    o("setp.ne.u32 %s, %s, 0;", r("p").c_str(), r("ok").c_str());
+    o("@%s bra %sstatus_done;", r("p").c_str(), L.c_str());
+    o("mov.u32 %s, 1;", r("t").c_str());
+    o("atom.global.exch.b32 %s, [%s], %s;", r("g").c_str(), r("status").c_str(), r("t").c_str());
+    o.label(L + "status_done");
+    o("tcgen05.fence::before_thread_sync;");
+    o("bar.sync 0;");
+    o("@!%s bra %sskip;", r("w1").c_str(), L.c_str());
+    o("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %s, 128;", r("tmem").c_str());
+    o.label(L + "skip");
+    char pl[512];
+    // tmap=<param>:<element bytes>:<row elements>:<row pitch bytes>:<box inner>:<box outer>:<swizzle bytes>
+    snprintf(pl, sizeof pl, "//!basalt.plan %s block=128,1,1 smem=%u params=%u tmap=%d:2:%lld:%lld:64:128:128 tmap=%d:2:%lld:%lld:64:%d:128 status=1", s.kernel.c_str(), smem, s.nparams,
+             s.a_param, lda, lda * 2, s.b_param, ldb, ldb * 2, b_nk ? 128 : 64);
+    plan->push_back(pl);
+    return true;
+}
+
+}  // namespace
+
+bool emit_mma_fast(const MmaSite& site, std::vector<std::string>* decls, std::vector<std::string>* lines, std::vector<std::string>* plan) {
+    return sgemm_ffma(site, decls, lines, plan) || matmul_tcgen05(site, decls, lines, plan);
 }
 
 }  // namespace basalt

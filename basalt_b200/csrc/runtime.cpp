@@ -101,6 +101,7 @@ struct Plan {
     unsigned nparams = 0;   // number of BIR parameters (tensor maps follow them)
     std::vector<TmapSpec> tmaps;
     std::string coarse;     // entry taking one more u64 parameter: the thread count the caller asked for
+    bool status = false;    // the entry takes a last u64 parameter: a device int32 set when a bounded wait gave up
 };
 }  // namespace
 struct basalt_rt_module {
@@ -112,6 +113,7 @@ struct basalt_rt_function {
     basalt_rt_module* mod = nullptr;
     CUfunction fn = nullptr;
     CUfunction coarse = nullptr;   // see Plan::coarse
+    CUdeviceptr status = 0;        // see Plan::status
     bool has_plan = false;
     Plan plan;
 };
@@ -200,6 +202,7 @@ void parse_plans(const char* ptx, std::map<std::string, Plan>* out) {
             else if (k == "smem") p.smem = (unsigned)strtoul(v.c_str(), nullptr, 10);
             else if (k == "params") p.nparams = (unsigned)strtoul(v.c_str(), nullptr, 10);
             else if (k == "coarse") p.coarse = v;
+            else if (k == "status") p.status = v != "0";
             else if (k == "tmap") {
                 TmapSpec t;
                 unsigned long long inner = 0, rowb = 0;
@@ -354,6 +357,12 @@ int basalt_rt_get_function(basalt_rt_module* mod, const char* name, basalt_rt_fu
             rc = check(f, "cuModuleGetFunction", f.cuModuleGetFunction(&h->coarse, mod->mod, h->plan.coarse.c_str()));
             if (rc) { delete h; return rc; }
         }
+        if (h->plan.status) {
+            rc = check(f, "cuMemAlloc", f.cuMemAlloc(&h->status, 4));
+            int32_t zero = 0;
+            if (!rc) rc = check(f, "cuMemcpyHtoD", f.cuMemcpyHtoD(h->status, &zero, 4));
+            if (rc) { delete h; return rc; }
+        }
         if (h->plan.smem > 48 * 1024) {
             rc = check(f, "cuFuncSetAttribute", f.cuFuncSetAttribute(fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)h->plan.smem));
             if (rc) { delete h; return rc; }
@@ -473,8 +482,18 @@ int basalt_rt_launch(basalt_rt_function* fn, const uint32_t grid[3], const uint3
         if (rc) return rc;
         all.push_back(&maps[i]);
     }
+    uint64_t status_ptr = (uint64_t)fn->status;
+    if (p.status) all.push_back(&status_ptr);
     uint32_t sm = shared_mem_bytes ? shared_mem_bytes : p.smem;
     return check(f, "cuLaunchKernel", f.cuLaunchKernel(fn->fn, grid[0], grid[1], grid[2], block[0], block[1], block[2], sm, (CUstream)stream, all.data(), nullptr));
+}
+
+int basalt_rt_kernel_status(basalt_rt_function* fn, int32_t* out) {
+    if (!fn || !out) return set_err(4, 0, "basalt_rt_kernel_status", "null argument");
+    *out = 0;
+    if (!fn->status) return 0;
+    const Fns& f = fn->mod->ctx->drv->f;
+    return check(f, "cuMemcpyDtoH", f.cuMemcpyDtoH(out, fn->status, 4));
 }
 
 int basalt_rt_ctx_sync(basalt_rt_ctx* ctx) {

@@ -237,6 +237,13 @@ class CudaFunction:
         _check(lib.basalt_rt_planned_geometry(self._h, None, g, b, C.byref(s)))
         return tuple(g), tuple(b), s.value
 
+    def status(self) -> int:
+        """The kernel's device status word (synchronous read): non-zero when a bounded wait inside
+        the kernel gave up and the last output is not valid. Always 0 for kernels without waits."""
+        v = C.c_int32()
+        _check(lib.basalt_rt_kernel_status(self._h, C.byref(v)))
+        return v.value
+
     def launch(self, grid, block, shared_mem_bytes: int, params: list, stream=None, sync: bool | None = None):
         """cuLaunchKernel. With stream=None and sync unset this behaves like the reference: launch
         on the NULL stream, then cuCtxSynchronize (module.rs:101-122). Pass a stream, or sync=False,

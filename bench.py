@@ -195,6 +195,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="basalt_b200", choices=["basalt_b200", "reference"])
     ap.add_argument("--no-others", action="store_true", help="skip the short timings of the other four configurations")
+    ap.add_argument("--elements", type=int, default=N_MAX, help="int32 elements per GPU (profiling runs use a smaller case)")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer and CPU-baseline legs (profiling runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
@@ -217,7 +219,7 @@ def main():
     peak_hbm, peak_tf, peak_kind = measured_peaks()
 
     # ---- inputs: this rank's contiguous shard, generated on the host into pinned memory ----
-    n = N_MAX
+    n = args.elements
     host_x = ctx.pinned_array((n,), np.uint32)
     w.u32(w.SEEDS["max_i32"] + rank, n, out=host_x)
     host_x = host_x.view(np.int32)
@@ -286,12 +288,15 @@ def main():
         ctx.cpu_launch(fn, [host_in, out_host, b.i32(n)], nthreads=blocks * 256, block=256)   # H2D 1 GiB, launch, D2H 4 B
         return group.max_i32_host(int(out_host[0])) if world > 1 else int(out_host[0])
 
-    step_e2e()
-    group.barrier()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        got_e2e = step_e2e()
-    e2e_ms = group.max_float((time.perf_counter() - t0) * 1e3) / e2e_steps
+    if args.no_e2e:
+        got_e2e, e2e_ms = got, float("nan")
+    else:
+        step_e2e()
+        group.barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            got_e2e = step_e2e()
+        e2e_ms = group.max_float((time.perf_counter() - t0) * 1e3) / e2e_steps
 
     expect = group.max_i32_host(expect_local)
     parity = bool(got == expect and got_e2e == expect)
@@ -299,12 +304,15 @@ def main():
     clocks = sampler.stop(t_begin, t_end) if sampler else None
     cpu = None
     others = None
-    if rank == 0:
+    if rank == 0 and args.no_e2e:
+        cpu = None
+    elif rank == 0:
         sample_n = n
         t_cpu, r_cpu = time_oracle_max(host_x[:sample_n], 3)
         parity = parity and (world > 1 or r_cpu == expect)
         cpu = {"value": 4.0 * sample_n / t_cpu / 1e9, "unit": "GB/s", "cores": 1, "kind": "port",
-               "sample": "3 full passes over this rank's 2^28 int32 (best), the oracle's sequential atomic-max loop, one thread as in the reference"}
+               "sample": "3 full passes over this rank's int32 shard (best), the oracle's sequential atomic-max loop, one thread as in the reference"}
+    if rank == 0:
         if world == 1 and not args.no_others:
             try:
                 others = others_summary(ctx, torch, stream, peak_hbm, peak_tf)
@@ -318,9 +326,9 @@ def main():
             "metric": METRIC, "value": total_bytes / (ms_per_step * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "i32", "data": "synthetic",
-            "config": {"workload": "max_i32: signed max over 2^28 int32 per GPU (uniform over the full range, SplitMix64 seed per rank), "
+            "config": {"workload": f"max_i32: signed max over {n} int32 per GPU (uniform over the full range, SplitMix64 seed per rank), "
                                    "emitted sm_100a kernel launched through the C-ABI runtime" + (", NCCL allreduce(max) of 1 int32 per step" if world > 1 else ""),
-                       "elements_per_gpu": n, "grid": blocks, "block": 256, "l2": "input (1 GiB per GPU) is larger than the 126 MB L2; no flush needed",
+                       "elements_per_gpu": n, "grid": blocks, "block": 256, "l2": f"input ({4 * n >> 20} MiB per GPU) is larger than the 126 MB L2; no flush needed",
                        "parallelism": f"contiguous shards x{world}"},
             "parity": parity,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak_hbm, "unit": "GB/s", "frac": achieved / peak_hbm, "peak_source": peak_kind,

@@ -138,6 +138,10 @@ int basalt_rt_launch(basalt_rt_function *fn, const uint32_t grid[3], const uint3
  * caller chooses, as with the reference). */
 int basalt_rt_planned_geometry(basalt_rt_function *fn, void **params, uint32_t grid[3], uint32_t block[3],
                                uint32_t *shared_mem_bytes);
+/* Kernels with bounded device-side waits (the tcgen05 matmul) own a device status word; this
+ * reads it after synchronising: 0 = every wait was satisfied, non-zero = a wait gave up and the
+ * output of that launch is not valid. No counterpart: the reference's kernels never wait. */
+int basalt_rt_kernel_status(basalt_rt_function *fn, int32_t *out);
 int basalt_rt_ctx_sync(basalt_rt_ctx *ctx);   /* cuCtxSynchronize (module.rs:120-121) */
 
 /* Streams and events (no counterpart: ffi.rs:38-42 "no multi-stream support yet"). */

@@ -82,7 +82,9 @@ def run_matmul_f16(gpu, how, A, B, N, b_is_nk):
         gpu.synchronize()
         assert status.to_numpy(np.int32)[0] == 0, "a bounded wait inside the kernel expired"
     else:
-        emitted(gpu, kb.matmul_f16(M, N, K, b_is_nk), "matmul_kernel").launch((N // 128, M // 128), 128, 0, [dA, dB, dC])
+        fn = emitted(gpu, kb.matmul_f16(M, N, K, b_is_nk), "matmul_kernel")
+        fn.launch((N // 128, M // 128), 128, 0, [dA, dB, dC])
+        assert fn.status() == 0, "a bounded wait inside the emitted kernel expired"
     return dC.to_numpy(np.float16).reshape(M, N)
 
 
@@ -112,7 +114,7 @@ def test_matmul_f16_vs_oracle(gpu, orc, how, b_is_nk):
     assert rel_fro(got, want) <= F16_TOL
 
 
-@pytest.mark.parametrize("how", ["hand"])
+@pytest.mark.parametrize("how", ["hand", "emitted"])
 def test_matmul_f16_full_size(gpu, orc, how):
     M = N = K = 8192
     A = np.empty(M * K, np.float16); B = np.empty(K * N, np.float16)
