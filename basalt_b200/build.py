@@ -17,6 +17,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libbasalt_b200.so")
+CLI = os.path.join(HERE, "basalt-b200")
 CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 
 CXX_SOURCES = ["bir.cpp", "passes.cpp", "emit.cpp", "emit_mma.cpp", "capi.cpp", "runtime.cpp"]
@@ -69,6 +70,9 @@ def build(force: bool = False, verbose: bool = False) -> str:
         list(ex.map(run, jobs))
     if force or jobs or _stale(LIB, objs):
         run([nvcc, "-shared", "-o", LIB, *objs, "-cudart", "static", "-Xlinker", "--no-undefined", "-ldl", "-lpthread", "-lrt"])
+    cli_src = os.path.join(CSRC, "cli.cpp")
+    if force or _stale(CLI, [cli_src, LIB]):
+        run(["g++", "-std=c++17", "-O2", "-o", CLI, cli_src, f"-L{HERE}", "-lbasalt_b200", "-Wl,-rpath,$ORIGIN"])
     return LIB
 
 

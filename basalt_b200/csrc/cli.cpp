@@ -1,0 +1,58 @@
+// basalt-b200: the `basalt --nvidia-ptx <file.bir> [-o out.ptx]` arm of the reference CLI
+// (crates/basalt-cli/src/main.rs:511-559) for the sm_100a backend.  Reads BIR text, writes PTX to
+// stdout or to the -o path (main.rs:553-558); a refusal prints "<E-code>: <message>" on stderr and
+// exits 1, as the reference renders a Diag (main.rs:894-900).  Only .bir input: the CUDA-C and
+// Triton front ends are not part of this project.
+#include <cstdio>
+#include <cstring>
+#include <fstream>
+#include <iostream>
+#include <sstream>
+#include <string>
+
+#include "../../include/basalt_b200.h"
+
+static int usage() {
+    std::cerr << "usage: basalt-b200 --nvidia-ptx <file.bir> [-o <out.ptx>] [-O0|-O2]\n"
+                 "       basalt-b200 --ir <file.bir>        (print the module as the backend lowers it)\n";
+    return 2;
+}
+
+int main(int argc, char** argv) {
+    std::string mode, in, out;
+    basalt_emit_opts opts{nullptr, 2, nullptr, 0};
+    for (int i = 1; i < argc; i++) {
+        std::string a = argv[i];
+        if (a == "--nvidia-ptx" || a == "--ir") {
+            if (!mode.empty()) { std::cerr << "E103: conflicting flags: " << mode << " and " << a << "\n"; return 1; }
+            mode = a;
+        } else if (a == "-o") {
+            if (i + 1 >= argc) { std::cerr << "E101: missing argument for flag: -o\n"; return 1; }
+            out = argv[++i];
+        } else if (a == "-O0") opts.opt_level = 0;
+        else if (a == "-O2") opts.opt_level = 2;
+        else if (!a.empty() && a[0] == '-') { std::cerr << "E100: unknown flag: " << a << "\n"; return 1; }
+        else in = a;
+    }
+    if (mode.empty() || in.empty()) return usage();
+    if (in.size() < 4 || in.substr(in.size() - 4) != ".bir") { std::cerr << "E102: invalid argument for flag " << mode << ": only .bir input is supported\n"; return 1; }
+    std::ifstream f(in, std::ios::binary);
+    if (!f) { std::cerr << "E500: I/O error reading " << in << ": cannot open\n"; return 1; }
+    std::stringstream ss;
+    ss << f.rdbuf();
+    std::string text = ss.str();
+    char* result = nullptr;
+    size_t len = 0;
+    basalt_diag d;
+    int rc = mode == "--ir" ? basalt_b200_optimize(text.data(), text.size(), &opts, &result, &len, &d)
+                            : basalt_b200_emit(text.data(), text.size(), &opts, &result, &len, &d);
+    if (rc != 0) { std::cerr << d.code << ": " << d.message << "\n"; return 1; }
+    if (out.empty()) std::cout.write(result, (std::streamsize)len);
+    else {
+        std::ofstream o(out, std::ios::binary);
+        if (!o) { std::cerr << "E500: I/O error reading " << out << ": cannot open for writing\n"; basalt_b200_free(result); return 1; }
+        o.write(result, (std::streamsize)len);
+    }
+    basalt_b200_free(result);
+    return 0;
+}

@@ -84,6 +84,9 @@ struct basalt_rt_ctx {
     CUdevice dev = 0;
     CUcontext ctx = nullptr;
     int sm_count = 0;
+    // Device buffers kept between basalt_rt_cpu_launch calls, keyed by size: cuMemAlloc and
+    // cuMemFree of a gigabyte cost more than the kernel they serve. Released with the context.
+    std::multimap<size_t, CUdeviceptr> staging;
 };
 namespace {
 struct TmapSpec {
@@ -297,6 +300,7 @@ int basalt_rt_ctx_create(basalt_rt_driver* drv, int device_index, basalt_rt_ctx*
 
 void basalt_rt_ctx_destroy(basalt_rt_ctx* ctx) {
     if (!ctx) return;
+    for (auto& kv : ctx->staging) ctx->drv->f.cuMemFree(kv.second);
     ctx->drv->f.cuDevicePrimaryCtxRelease(ctx->dev);
     delete ctx;
 }
@@ -488,6 +492,14 @@ int basalt_rt_launch(basalt_rt_function* fn, const uint32_t grid[3], const uint3
     return check(f, "cuLaunchKernel", f.cuLaunchKernel(fn->fn, grid[0], grid[1], grid[2], block[0], block[1], block[2], sm, (CUstream)stream, all.data(), nullptr));
 }
 
+int basalt_rt_occupancy(basalt_rt_function* fn, uint32_t block_threads, uint32_t shared_mem_bytes, int* ctas_per_sm, int* sm_count) {
+    if (!fn || !ctas_per_sm) return set_err(4, 0, "basalt_rt_occupancy", "null argument");
+    const Fns& f = fn->mod->ctx->drv->f;
+    if (sm_count) *sm_count = fn->mod->ctx->sm_count;
+    uint32_t sm = shared_mem_bytes ? shared_mem_bytes : (fn->has_plan ? fn->plan.smem : 0);
+    return check(f, "cuOccupancyMaxActiveBlocksPerMultiprocessor", f.cuOccupancyMaxActiveBlocksPerMultiprocessor(ctas_per_sm, fn->fn, (int)block_threads, sm));
+}
+
 int basalt_rt_kernel_status(basalt_rt_function* fn, int32_t* out) {
     if (!fn || !out) return set_err(4, 0, "basalt_rt_kernel_status", "null argument");
     *out = 0;
@@ -526,19 +538,28 @@ int basalt_rt_event_elapsed_ms(basalt_rt_ctx* ctx, void* a, void* b, float* ms) 
 
 int basalt_rt_cpu_launch(basalt_rt_ctx* ctx, basalt_rt_function* fn, const basalt_rt_arg* args, int nargs, int64_t nthreads, uint32_t block) {
     if (!ctx || !fn || (nargs && !args) || nthreads < 0 || block == 0) return set_err(4, 0, "basalt_rt_cpu_launch", "bad argument");
-    std::vector<basalt_rt_buffer*> bufs(nargs, nullptr);
+    const Fns& f = ctx->drv->f;
+    int rc = make_current(ctx);
+    if (rc) return rc;
+    std::vector<std::pair<size_t, CUdeviceptr>> held(nargs, {0, 0});
     std::vector<uint64_t> dptrs(nargs, 0);
     std::vector<void*> params(nargs, nullptr);
-    int rc = 0;
-    auto cleanup = [&]() { for (auto* b : bufs) basalt_rt_buffer_free(b); };
+    auto release = [&]() {
+        for (auto& h : held) if (h.second) ctx->staging.insert(h);
+    };
     for (int i = 0; i < nargs && !rc; i++) {
         const basalt_rt_arg& a = args[i];
         if (a.kind >= 4) {
-            rc = basalt_rt_alloc(ctx, a.bytes, &bufs[i]);
+            size_t bytes = a.bytes ? a.bytes : 1;
+            auto it = ctx->staging.find(bytes);
+            CUdeviceptr p = 0;
+            if (it != ctx->staging.end()) { p = it->second; ctx->staging.erase(it); }
+            else rc = check(f, "cuMemAlloc", f.cuMemAlloc(&p, bytes));
             if (rc) break;
+            held[i] = {bytes, p};
             // written-only buffers are uploaded too: the kernel may leave part of them untouched
-            rc = basalt_rt_copy_from_host(bufs[i], a.host, a.bytes, nullptr);
-            dptrs[i] = basalt_rt_buffer_ptr(bufs[i]);
+            if (a.bytes) rc = check(f, "cuMemcpyHtoD", f.cuMemcpyHtoD(p, a.host, a.bytes));
+            dptrs[i] = (uint64_t)p;
             params[i] = &dptrs[i];
         } else params[i] = (void*)&a.value;
     }
@@ -549,8 +570,9 @@ int basalt_rt_cpu_launch(basalt_rt_ctx* ctx, basalt_rt_function* fn, const basal
         if (!rc) rc = basalt_rt_ctx_sync(ctx);
     }
     for (int i = 0; i < nargs && !rc; i++)
-        if (args[i].kind == 5 || args[i].kind == 6) rc = basalt_rt_copy_to_host(bufs[i], args[i].host, args[i].bytes, nullptr);
-    cleanup();
+        if ((args[i].kind == 5 || args[i].kind == 6) && args[i].bytes)
+            rc = check(f, "cuMemcpyDtoH", f.cuMemcpyDtoH(args[i].host, (CUdeviceptr)dptrs[i], args[i].bytes));
+    release();
     return rc;
 }
 

@@ -237,6 +237,28 @@ class CudaFunction:
         _check(lib.basalt_rt_planned_geometry(self._h, None, g, b, C.byref(s)))
         return tuple(g), tuple(b), s.value
 
+    def one_wave(self, block_threads: int, shared_mem_bytes: int = 0) -> int:
+        """Number of CTAs that are resident at once on the whole device for this kernel: the grid
+        for a grid-stride (persistent) launch."""
+        per_sm, sms = C.c_int(), C.c_int()
+        _check(lib.basalt_rt_occupancy(self._h, block_threads, shared_mem_bytes, C.byref(per_sm), C.byref(sms)))
+        return max(1, per_sm.value) * sms.value
+
+    def bind(self, grid, block, shared_mem_bytes: int, params: list, stream=None):
+        """Pre-marshals a launch; the returned callable issues it with a single foreign call
+        (asynchronous). Use for launch-latency-sensitive loops."""
+        vals = [C.c_uint64(p.device_ptr()) if isinstance(p, DeviceBuffer) else p for p in params]
+        arr = (C.c_void_p * max(len(vals), 1))(*[C.cast(C.pointer(v), C.c_void_p) for v in vals])
+        g = (C.c_uint32 * 3)(*_dim3(grid))
+        b = (C.c_uint32 * 3)(*_dim3(block))
+        s = C.c_void_p(stream)
+        h, fn = self._h, lib.basalt_rt_launch
+
+        def go(_keep=(vals, arr, g, b)):
+            if fn(h, g, b, shared_mem_bytes, s, arr):
+                _check(1)
+        return go
+
     def status(self) -> int:
         """The kernel's device status word (synchronous read): non-zero when a bounded wait inside
         the kernel gave up and the last output is not valid. Always 0 for kernels without waits."""

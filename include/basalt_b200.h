@@ -138,6 +138,11 @@ int basalt_rt_launch(basalt_rt_function *fn, const uint32_t grid[3], const uint3
  * caller chooses, as with the reference). */
 int basalt_rt_planned_geometry(basalt_rt_function *fn, void **params, uint32_t grid[3], uint32_t block[3],
                                uint32_t *shared_mem_bytes);
+/* Resident CTAs per SM for this kernel at the given block size (cuOccupancyMaxActiveBlocksPer-
+ * Multiprocessor) and the device's SM count: a grid of their product is exactly one wave. No
+ * counterpart in the reference, which leaves grid sizing to its tests. */
+int basalt_rt_occupancy(basalt_rt_function *fn, uint32_t block_threads, uint32_t shared_mem_bytes, int *ctas_per_sm,
+                        int *sm_count);
 /* Kernels with bounded device-side waits (the tcgen05 matmul) own a device status word; this
  * reads it after synchronising: 0 = every wait was satisfied, non-zero = a wait gave up and the
  * output of that launch is not valid. No counterpart: the reference's kernels never wait. */
@@ -158,8 +163,9 @@ int basalt_rt_event_elapsed_ms(basalt_rt_ctx *ctx, void *start, void *end, float
  * examples/cpu_launch_*.c): host pointers in, results in host memory out. For each argument:
  * kind 0 = i32, 1 = i64, 2 = f32, 3 = f64 (value read from `value`), 4 = pointer read by the
  * kernel, 5 = pointer written, 6 = both (host address in `host`, extent in `bytes`). The call
- * allocates device buffers, copies inputs, launches ceil(nthreads/block) blocks of `block`
- * threads (the reference's grid for a flat launch), copies outputs back and frees. */
+ * takes device buffers (kept with the context between calls and reused by size), copies inputs,
+ * launches ceil(nthreads/block) blocks of `block` threads (the reference's grid for a flat launch)
+ * and copies outputs back. */
 typedef struct basalt_rt_arg {
     int kind;
     union { int32_t i32; int64_t i64; float f32; double f64; } value;

@@ -1,0 +1,91 @@
+"""One rank of the multi-GPU parity run (launched by test_gpu_multi.py under torch.distributed.run).
+
+Each rank owns a contiguous shard of the work on its own GPU and runs the emitted kernels through
+the C-ABI runtime; the only exchanges are the ones the workloads need: allreduce(max) of one int32
+for the reduction, allgather of the row-sharded C for the two matmuls, both over this library's
+NCCL communicator.  Results are compared with the CPU oracle on every rank."""
+import ctypes
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+import basalt_b200 as b  # noqa: E402
+from basalt_b200 import kernels_bir as kb, sharding, workloads as w  # noqa: E402
+from _util import orc_matmul_f16_rows, orc_sgemm_rows, rel_fro, vp  # noqa: E402
+
+
+def main():
+    import torch
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    group = sharding.RankGroup.from_env("gloo")     # host rendezvous only; data moves over our NCCL communicator
+    ctx = b.CudaDriver.load().create_context(local)
+    comm = group.nccl(ctx)
+    orc = ctypes.CDLL(os.path.join(ROOT, "oracle", "liborc.so"))
+    ptx = b.Ptx()
+
+    # ---- max_i32: contiguous shards, planted maxima on both sides of every shard boundary ----
+    n = (1 << 22) + 37
+    x = w.u32(w.SEEDS["max_i32"], n).view(np.int32).copy()
+    np.minimum(x, 2**31 - 2, out=x)
+    fn = ctx.load_module(ptx.emit(kb.load("max_i32")).text).get_function("max_i32")
+    lo, hi = group.shard(n, 4)
+    plants = [None, 0, n - 1] + [p for r in range(1, group.world) for p in (group_bound(n, group.world, r) - 1, group_bound(n, group.world, r))]
+    for plant in plants:
+        y = x.copy()
+        if plant is not None:
+            y[plant] = 2**31 - 1
+        want = np.array([-2**31], np.int32)
+        orc.orc_max_i32(vp(y), vp(want), ctypes.c_int32(n), ctypes.c_int64(n))
+        dshard = ctx.upload(y[lo:hi])
+        partial = ctx.upload(np.array([-2**31], np.int32)); result = ctx.alloc(4)
+        if hi > lo:
+            fn.launch(min(fn.one_wave(256), (hi - lo + 255) // 256), 256, 0, [dshard, partial, b.i32(hi - lo)])
+        comm.allreduce_max_i32(partial.device_ptr(), result.device_ptr(), 1)
+        ctx.synchronize()
+        got = int(result.to_numpy(np.int32)[0])
+        assert got == int(want[0]), (plant, got, int(want[0]))
+
+    # ---- SGEMM: rows of A and C sharded, B replicated, allgather of C ----
+    M, N, K = 128 * 2 * group.world, 256, 128
+    A = w.f32_pm1(w.SEEDS["sgemm_f32"], M * K).reshape(M, K); B = w.f32_pm1(w.SEEDS["sgemm_f32"] + 1, K * N).reshape(K, N)
+    r0, r1 = group.shard(M, 128)
+    Ml = r1 - r0
+    dA, dB, dCl, dC = ctx.upload(A[r0:r1]), ctx.upload(B), ctx.alloc(Ml * N * 4), ctx.alloc(M * N * 4)
+    fn = ctx.load_module(ptx.emit(kb.sgemm_cta128(Ml, N, K)).text).get_function("sgemm_f32")
+    fn.launch((N // 128, Ml // 128), 256, 0, [dA, dB, dCl])
+    comm.allgather(dCl.device_ptr(), dC.device_ptr(), Ml * N * 4)
+    ctx.synchronize()
+    got = dC.to_numpy(np.float32).reshape(M, N)
+    assert rel_fro(got, orc_sgemm_rows(orc, A, B, 0, M)) <= 1e-4
+
+    # ---- fp16 matmul: the same sharding, tensor-core kernel ----
+    M, N, K = 128 * group.world, 256, 256
+    A = w.f16_normal01(w.SEEDS["matmul_f16"], M * K).reshape(M, K); B = w.f16_normal01(w.SEEDS["matmul_f16"] + 1, K * N).reshape(K, N)
+    r0, r1 = group.shard(M, 128)
+    Ml = r1 - r0
+    dA, dB, dCl, dC = ctx.upload(A[r0:r1]), ctx.upload(B), ctx.alloc(Ml * N * 2), ctx.alloc(M * N * 2)
+    fn = ctx.load_module(ptx.emit(kb.matmul_f16(Ml, N, K)).text).get_function("matmul_kernel")
+    fn.launch((N // 128, Ml // 128), 128, 0, [dA, dB, dCl])
+    assert fn.status() == 0
+    comm.allgather(dCl.device_ptr(), dC.device_ptr(), Ml * N * 2)
+    ctx.synchronize()
+    got = dC.to_numpy(np.float16).reshape(M, N)
+    assert rel_fro(got, orc_matmul_f16_rows(orc, A, B, N, False, 0, M)) <= 2e-3
+
+    comm.destroy()
+    group.barrier()
+    print(f"rank {group.rank}/{group.world} ok", flush=True)
+
+
+def group_bound(n, world, r):
+    return b.shard_range(n, world, r, 4)[0]
+
+
+if __name__ == "__main__":
+    main()

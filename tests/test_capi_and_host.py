@@ -96,3 +96,25 @@ print("rank", g.rank, "ok", lo, hi)
                         "--master-port", "29617", str(script)], capture_output=True, text=True, env=env, timeout=240)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
     assert r.stdout.count("ok") == 2
+
+
+def test_cli_follows_the_reference_conventions(tmp_path):
+    # crates/basalt-cli/tests/nvidia_ptx_flag.rs:22-85: PTX on stdout or at -o, non-zero exit with the E-code on stderr
+    from basalt_b200 import kernels_bir as kb
+    cli = os.path.join(ROOT, "basalt_b200", "basalt-b200")
+    src = tmp_path / "k.bir"
+    src.write_text(kb.load("vadd_i32"))
+    r = subprocess.run([cli, "--nvidia-ptx", str(src)], capture_output=True, text=True)
+    assert r.returncode == 0 and ".target sm_100a" in r.stdout and ".visible .entry vadd_i32(" in r.stdout
+    assert r.stdout == b.Ptx().emit(kb.load("vadd_i32")).text
+    out = tmp_path / "k.ptx"
+    r = subprocess.run([cli, "--nvidia-ptx", str(src), "-o", str(out), "-O0"], capture_output=True, text=True)
+    assert r.returncode == 0 and r.stdout == "" and "v4" not in out.read_text()
+    bad = tmp_path / "bad.bir"
+    bad.write_text("module {")
+    r = subprocess.run([cli, "--nvidia-ptx", str(bad)], capture_output=True, text=True)
+    assert r.returncode == 1 and r.stderr.startswith("E400: ")
+    r = subprocess.run([cli, "--nvidia-ptx", str(src), "--frobnicate"], capture_output=True, text=True)
+    assert r.returncode == 1 and r.stderr.startswith("E100: ")
+    r = subprocess.run([cli, "--ir", str(src)], capture_output=True, text=True)
+    assert r.returncode == 0 and "load v4i32" in r.stdout

@@ -81,8 +81,8 @@ def gpu_max(gpu, how, dx, n, level=2):
     elif how == "atomic":
         emitted(gpu, kb.load("max_i32_atomic"), "max_i32_atomic", level).launch(grid_for(n), 256, 0, [dx, out, b.i32(n)])
     else:
-        blocks = min(gpu.sm_count() * 8, grid_for(n))
-        emitted(gpu, kb.load("max_i32"), "max_i32", level).launch(blocks, 256, 0, [dx, out, b.i32(n)])
+        fn = emitted(gpu, kb.load("max_i32"), "max_i32", level)
+        fn.launch(min(fn.one_wave(256), grid_for(n)), 256, 0, [dx, out, b.i32(n)])
     return int(out.to_numpy(np.int32)[0])
 
 
