@@ -203,6 +203,161 @@ __global__ void __launch_bounds__(THREADS) matmul_f16_tc_kernel(const __grid_con
     if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(TMEM_COLS) : "memory");
 }
 
+// ---- persistent, warp-specialised kernel: 128 x 256 tiles ---------------------------------------
+//
+// One CTA per SM (192 threads) walks a list of 128 x 256 output tiles:
+//   warp 0 (one lane)  TMA producer, four 48 KB stages (A 128x64, B 64x256 per stage);
+//   warp 1 (one lane)  tcgen05.mma M128 N256 K16 into one of two 256-column TMEM accumulators;
+//   warps 2-5          epilogue: drain the other accumulator (tcgen05.ld), convert, store.
+// The epilogue of tile i therefore overlaps the main loop of tile i+1, and a 256-wide tile reads
+// 12 KB of shared memory per 128x256x16 MMA instead of 16 KB for two 128-wide ones.  Tiles are
+// visited in bands of 16 tile rows so that the tiles in flight share A and B panels in L2.
+namespace v2 {
+constexpr int BN2 = 256, STAGES = 4, THREADS2 = 192, B_BYTES2 = BN2 * BK * 2, STAGE_BYTES2 = A_BYTES + B_BYTES2;
+constexpr int GROUP_M = 16;
+constexpr uint32_t TMEM_COLS2 = 512;
+
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int* m_idx, int* n_idx) {
+    const int per_band = GROUP_M * tiles_n, band = t / per_band, first = band * GROUP_M;
+    const int rows = min(GROUP_M, tiles_m - first), r = t - band * per_band;
+    *m_idx = first + r % rows;
+    *n_idx = r / rows;
+}
+
+template <bool B_IS_NK>
+__global__ void __launch_bounds__(THREADS2, 1) matmul_f16_tc_persistent(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                                                                        __half* __restrict__ C, int M, int N, int K, int32_t* status) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], tfull_bar[2], tempty_bar[2];
+    __shared__ uint32_t tmem_slot;
+    __shared__ volatile uint32_t gave_up;
+    const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_m = M / BM, tiles_n = N / BN2, num_tiles = tiles_m * tiles_n, num_kb = K / BK;
+
+    if (status && *reinterpret_cast<volatile int32_t*>(status) != 0) return;
+    if (threadIdx.x == 0) {
+        gave_up = 0;
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(smem_u32(&tfull_bar[b]), 1);
+            mbar_init(smem_u32(&tempty_bar[b]), 4);   // one arrival per epilogue warp
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS2) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_slot;
+    bool ok = true;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t it = 0;   // running k-slab count across tiles: stage = it % STAGES, phase = (it / STAGES) & 1
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                int mi, ni;
+                tile_coords(t, tiles_m, tiles_n, &mi, &ni);
+                const int m0 = mi * BM, n0 = ni * BN2;
+                for (int kb = 0; kb < num_kb; kb++, it++) {
+                    const uint32_t s = it % STAGES, parity = ((it / STAGES) & 1) ^ 1;
+                    ok &= mbar_wait(smem_u32(&empty_bar[s]), parity, &gave_up);
+                    if (!ok) break;
+                    const uint32_t fb = smem_u32(&full_bar[s]), a_dst = tiles + s * STAGE_BYTES2, b_dst = a_dst + A_BYTES;
+                    mbar_expect_tx(fb, STAGE_BYTES2);
+                    tma_load_2d(a_dst, &map_a, fb, kb * BK, m0);
+                    if (B_IS_NK) tma_load_2d(b_dst, &map_b, fb, kb * BK, n0);   // box 64 k x 256 n
+                    else {
+#pragma unroll
+                        for (int h = 0; h < 4; h++) tma_load_2d(b_dst + h * 8192, &map_b, fb, n0 + 64 * h, kb * BK);   // box 64 n x 64 k
+                    }
+                }
+            }
+            if (!ok) {   // let the copies already issued land before the CTA can exit
+                const uint64_t t0 = global_ns();
+                while (global_ns() - t0 < 2000000ull) {}
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = (1u << 4) | ((B_IS_NK ? 0u : 1u) << 16) | ((uint32_t)(BN2 >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            uint32_t it = 0, local = 0;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, local++) {
+                const uint32_t buf = local & 1, use = local >> 1;
+                ok &= mbar_wait(smem_u32(&tempty_bar[buf]), (use & 1) ^ 1, &gave_up);   // epilogue has drained this accumulator
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t acc = tmem_base + buf * BN2;
+                for (int kb = 0; kb < num_kb; kb++, it++) {
+                    const uint32_t s = it % STAGES;
+                    ok &= mbar_wait(smem_u32(&full_bar[s]), (it / STAGES) & 1, &gave_up);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_src = tiles + s * STAGE_BYTES2, b_src = a_src + A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; k++) {
+                        const uint64_t da = smem_desc(a_src + k * UMMA_K * 2, 16, 1024);
+                        const uint64_t db = B_IS_NK ? smem_desc(b_src + k * UMMA_K * 2, 16, 1024) : smem_desc(b_src + k * UMMA_K * 128, 8192, 1024);
+                        umma_f16(acc, da, db, idesc, (kb | k) != 0);
+                    }
+                    umma_commit(smem_u32(&empty_bar[s]));
+                }
+                umma_commit(smem_u32(&tfull_bar[buf]));
+            }
+        }
+    } else {
+        const int ew = warp & 3;   // this warp may touch TMEM lanes 32*ew .. 32*ew+31
+        uint32_t local = 0;
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, local++) {
+            int mi, ni;
+            tile_coords(t, tiles_m, tiles_n, &mi, &ni);
+            const uint32_t buf = local & 1, use = local >> 1;
+            ok &= mbar_wait(smem_u32(&tfull_bar[buf]), use & 1, &gave_up);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            __half* crow = C + (size_t)(mi * BM + ew * 32 + lane) * N + (size_t)ni * BN2;
+            const uint32_t src = tmem_base + buf * BN2 + ((uint32_t)(ew * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < BN2; c += 32) {
+                uint32_t r[32];
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                    "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+                      "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+                      "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
+                      "=r"(r[31])
+                    : "r"(src + (uint32_t)c));
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                uint32_t h[16];
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    __half2 v = __floats2half2_rn(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+                    h[i] = *reinterpret_cast<uint32_t*>(&v);
+                }
+#pragma unroll
+                for (int q = 0; q < 4; q++) *reinterpret_cast<uint4*>(crow + c + 8 * q) = make_uint4(h[4 * q], h[4 * q + 1], h[4 * q + 2], h[4 * q + 3]);
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&tempty_bar[buf])) : "memory");
+        }
+    }
+    if (!ok && status) atomicExch(status, 1);
+    __syncwarp();
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS2) : "memory");
+}
+}  // namespace v2
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
@@ -245,6 +400,21 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, __half* C, int M, int N
     return basalt_k::record(cudaGetLastError(), "matmul_f16");
 }
 
+template <bool B_IS_NK>
+int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, __half* C, int M, int N, int K, int32_t* status, cudaStream_t s) {
+    constexpr int smem = v2::STAGES * v2::STAGE_BYTES2 + 1024;
+    auto kern = v2::matmul_f16_tc_persistent<B_IS_NK>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return basalt_k::record(e, "matmul_f16 (shared memory size)");
+        configured = true;
+    }
+    const int tiles = (M / BM) * (N / v2::BN2), sms = basalt_k::sm_count();
+    kern<<<tiles < sms ? tiles : sms, v2::THREADS2, smem, s>>>(ma, mb, C, M, N, K, status);
+    return basalt_k::record(cudaGetLastError(), "matmul_f16");
+}
+
 }  // namespace
 
 extern "C" int basalt_k_matmul_f16(const void* A, const void* B, void* C, int M, int N, int K, int b_is_nk, int32_t* status, void* stream) {
@@ -254,8 +424,13 @@ extern "C" int basalt_k_matmul_f16(const void* A, const void* B, void* C, int M,
     CUtensorMap ma, mb;
     int rc = make_map(&ma, A, (uint64_t)M, (uint64_t)K, BK, BM);
     if (rc) return rc;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (N % v2::BN2 == 0) {   // 128 x 256 tiles, persistent
+        rc = b_is_nk ? make_map(&mb, B, (uint64_t)N, (uint64_t)K, BK, v2::BN2) : make_map(&mb, B, (uint64_t)K, (uint64_t)N, 64, BK);
+        if (rc) return rc;
+        return b_is_nk ? launch_persistent<true>(ma, mb, (__half*)C, M, N, K, status, s) : launch_persistent<false>(ma, mb, (__half*)C, M, N, K, status, s);
+    }
     rc = b_is_nk ? make_map(&mb, B, (uint64_t)N, (uint64_t)K, BK, BN) : make_map(&mb, B, (uint64_t)K, (uint64_t)N, 64, BK);
     if (rc) return rc;
-    cudaStream_t s = (cudaStream_t)stream;
     return b_is_nk ? launch<3, true>(ma, mb, (__half*)C, M, N, K, status, s) : launch<3, false>(ma, mb, (__half*)C, M, N, K, status, s);
 }

@@ -28,14 +28,19 @@ __global__ void __launch_bounds__(THREADS, 2) sgemm_f32_kernel(const float* __re
     // 16 rows x 128 floats (32 float4 per row); two float4 of each per thread.
     const int a_row = tid >> 2, a_col = (tid & 3) * 4;   // rows a_row and a_row + 64
     const int b_row = tid >> 5, b_col = (tid & 31) * 4;  // rows b_row and b_row + 8
-    const float* Ag = A + (size_t)(m0 + a_row) * K + a_col;
-    const float* Bg = B + (size_t)b_row * N + n0 + b_col;
+    // four running pointers, advanced by one K slab per iteration
+    const float* Ag0 = A + (size_t)(m0 + a_row) * K + a_col;
+    const float* Ag1 = Ag0 + (size_t)64 * K;
+    const float* Bg0 = B + (size_t)b_row * N + n0 + b_col;
+    const float* Bg1 = Bg0 + (size_t)8 * N;
+    const size_t b_step = (size_t)BK * N;
     float4 ra0, ra1, rb0, rb1;
-    auto fetch = [&](int k0) {
-        ra0 = *reinterpret_cast<const float4*>(Ag + k0);
-        ra1 = *reinterpret_cast<const float4*>(Ag + (size_t)64 * K + k0);
-        rb0 = *reinterpret_cast<const float4*>(Bg + (size_t)k0 * N);
-        rb1 = *reinterpret_cast<const float4*>(Bg + (size_t)(k0 + 8) * N);
+    auto fetch = [&]() {
+        ra0 = *reinterpret_cast<const float4*>(Ag0);
+        ra1 = *reinterpret_cast<const float4*>(Ag1);
+        rb0 = *reinterpret_cast<const float4*>(Bg0);
+        rb1 = *reinterpret_cast<const float4*>(Bg1);
+        Ag0 += BK; Ag1 += BK; Bg0 += b_step; Bg1 += b_step;
     };
     auto stash = [&](int buf) {
         As[buf][a_col + 0][a_row] = ra0.x; As[buf][a_col + 1][a_row] = ra0.y; As[buf][a_col + 2][a_row] = ra0.z; As[buf][a_col + 3][a_row] = ra0.w;
@@ -50,13 +55,13 @@ __global__ void __launch_bounds__(THREADS, 2) sgemm_f32_kernel(const float* __re
 #pragma unroll
         for (int j = 0; j < 8; j++) acc[i][j] = 0.0f;
 
-    fetch(0);
+    fetch();
     stash(0);
     __syncthreads();
     const int nk = K / BK;
     for (int kb = 0; kb < nk; kb++) {
         const int buf = kb & 1;
-        if (kb + 1 < nk) fetch((kb + 1) * BK);
+        if (kb + 1 < nk) fetch();
 #pragma unroll
         for (int k = 0; k < BK; k++) {
             const float4 a0 = *reinterpret_cast<const float4*>(&As[buf][k][ty * 4]);

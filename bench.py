@@ -217,6 +217,53 @@ def others_summary(ctx, torch, stream, peaks_hbm, peaks_tf):
     return out
 
 
+def profile_one(args):
+    """A few launches of one workload's two kernels on a small case, for ncu captures."""
+    import torch
+
+    import basalt_b200 as b
+    from basalt_b200 import kernels, kernels_bir as kb
+    torch.cuda.set_device(0)
+    ctx = b.CudaDriver.load().create_context(0)
+    stream = torch.cuda.current_stream().cuda_stream
+    dp = lambda t: b.ptr(t.data_ptr())
+    reps = max(1, min(args.steps, 5))
+    name = args.profile
+    if name in ("vadd_i32", "helper_chain"):
+        n = args.size or (1 << 26)
+        x = torch.randint(-2**30, 2**30, (n,), dtype=torch.int32, device="cuda"); y = torch.randint(-2**30, 2**30, (n,), dtype=torch.int32, device="cuda")
+        z = torch.empty_like(x)
+        if name == "vadd_i32":
+            fn = ctx.load_module(b.Ptx().emit(kb.load("vadd_i32")).text).get_function("vadd_i32")
+            em = lambda: fn.launch((n + 255) // 256, 256, 0, [dp(x), dp(y), dp(z), b.i32(n)], stream=stream)
+            hw = lambda: kernels.vadd_i32(x.data_ptr(), y.data_ptr(), z.data_ptr(), n, stream)
+        else:
+            fn = ctx.load_module(b.Ptx().emit(kb.helper_chain()).text).get_function("helper_chain")
+            em = lambda: fn.launch((n + 255) // 256, 256, 0, [dp(x), dp(z), b.i32(n)], stream=stream)
+            hw = lambda: kernels.helper_chain_u32(x.data_ptr(), z.data_ptr(), n, stream)
+        size = {"elements": n}
+    elif name == "sgemm_f32":
+        m = args.size or 2048
+        A = torch.rand(m, m, device="cuda") * 2 - 1; B = torch.rand(m, m, device="cuda") * 2 - 1; C = torch.empty(m, m, device="cuda")
+        fn = ctx.load_module(b.Ptx().emit(kb.sgemm_cta128(m, m, m)).text).get_function("sgemm_f32")
+        em = lambda: fn.launch((m // 128, m // 128), 256, 0, [dp(A), dp(B), dp(C)], stream=stream)
+        hw = lambda: kernels.sgemm_f32(A.data_ptr(), B.data_ptr(), C.data_ptr(), m, m, m, stream)
+        size = {"M=N=K": m}
+    else:
+        m = args.size or 4096
+        A = (torch.randn(m, m, device="cuda") * 0.1).half(); B = (torch.randn(m, m, device="cuda") * 0.1).half(); C = torch.empty(m, m, device="cuda", dtype=torch.float16)
+        st = torch.zeros(1, dtype=torch.int32, device="cuda")
+        fn = ctx.load_module(b.Ptx().emit(kb.matmul_f16(m, m, m)).text).get_function("matmul_kernel")
+        em = lambda: fn.launch((m // 128, m // 128), 128, 0, [dp(A), dp(B), dp(C)], stream=stream)
+        hw = lambda: kernels.matmul_f16(A.data_ptr(), B.data_ptr(), C.data_ptr(), m, m, m, False, st.data_ptr(), stream)
+        size = {"M=N=K": m}
+    for f in (em, hw):
+        for _ in range(reps):
+            f()
+    torch.cuda.synchronize()
+    print(json.dumps({"profiling": name, "size": size, "launches_each": reps}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -226,10 +273,15 @@ def main():
     ap.add_argument("--no-others", action="store_true", help="skip the short timings of the other four configurations")
     ap.add_argument("--elements", type=int, default=N_MAX, help="int32 elements per GPU (profiling runs use a smaller case)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer and CPU-baseline legs (profiling runs)")
+    ap.add_argument("--profile", default=None, choices=["vadd_i32", "helper_chain", "sgemm_f32", "matmul_f16"],
+                    help="run only this workload's emitted and hand-written kernels a few times on a small case (for ncu) and exit")
+    ap.add_argument("--size", type=int, default=0, help="problem size for --profile (elements, or the matrix dimension)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         return reference_arm(args)
+    if args.profile:
+        return profile_one(args)
 
     import torch
 

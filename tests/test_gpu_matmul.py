@@ -90,7 +90,7 @@ def run_matmul_f16(gpu, how, A, B, N, b_is_nk):
 
 @pytest.mark.parametrize("how", ["hand", "emitted"])
 @pytest.mark.parametrize("b_is_nk", [True, False])
-@pytest.mark.parametrize("shape", [(128, 128, 64), (128, 128, 256), (256, 384, 192)])
+@pytest.mark.parametrize("shape", [(128, 128, 64), (128, 128, 256), (256, 384, 192), (256, 512, 192), (384, 256, 64), (2304, 512, 64)])
 def test_matmul_f16_exact_on_small_integers(gpu, how, b_is_nk, shape):
     M, N, K = shape
     A, B, _ = sgemm_fixture(M, N, K)
