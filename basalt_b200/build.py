@@ -43,6 +43,30 @@ def _stale(out: str, deps: list[str]) -> bool:
     return any(os.path.getmtime(d) > t for d in deps if os.path.exists(d))
 
 
+SHIM_KERNELS = ("vector_add_f32", "chain_vector", "square_vector", "mma2x2", "tiled_sgemm_f32", "tri_vadd", "tri_matmul")
+
+
+def _build_shims(force: bool, run) -> None:
+    """libbasalt_cpu_launch_{cuda,triton}.so: the reference's example kernels under their own symbols."""
+    src = os.path.join(CSRC, "shims", "cpu_launch_shims.cpp")
+    inc = os.path.join(OBJ, "shim_bir.inc")
+    bir_dir = os.path.join(HERE, "bir")
+    deps = [os.path.join(bir_dir, k + ".bir") for k in SHIM_KERNELS] + [os.path.join(HERE, "kernels_bir.py"), os.path.abspath(__file__)]
+    if force or _stale(inc, deps):
+        sys.path.insert(0, os.path.dirname(HERE))
+        from basalt_b200 import kernels_bir   # pure Python; the package resolves native names lazily
+        texts = {k: kernels_bir.load(k) for k in SHIM_KERNELS}
+        texts["stress"] = kernels_bir.stress()
+        with open(inc, "w") as f:
+            for k, t in texts.items():
+                f.write(f'static const char kBir_{k}[] = R"BIR({t})BIR";\n')
+    for flavour, flag in (("cuda", []), ("triton", ["-DBASALT_SHIMS_TRITON"])):
+        out = os.path.join(HERE, f"libbasalt_cpu_launch_{flavour}.so")
+        if force or _stale(out, [src, inc, LIB]):
+            run(["g++", "-std=c++17", "-O2", "-fPIC", "-shared", "-fvisibility=hidden", *flag, f"-I{OBJ}", "-o", out, src, f"-L{HERE}", "-lbasalt_b200",
+                 "-Wl,-rpath,$ORIGIN", "-lpthread"])
+
+
 def build(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(OBJ, exist_ok=True)
     hdrs = [os.path.join(CSRC, h) for h in HEADERS] + [os.path.abspath(__file__)]
@@ -70,6 +94,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         list(ex.map(run, jobs))
     if force or jobs or _stale(LIB, objs):
         run([nvcc, "-shared", "-o", LIB, *objs, "-cudart", "static", "-Xlinker", "--no-undefined", "-ldl", "-lpthread", "-lrt"])
+    _build_shims(force, run)
     cli_src = os.path.join(CSRC, "cli.cpp")
     if force or _stale(CLI, [cli_src, LIB]):
         run(["g++", "-std=c++17", "-O2", "-o", CLI, cli_src, f"-L{HERE}", "-lbasalt_b200", "-Wl,-rpath,$ORIGIN"])

@@ -174,7 +174,7 @@ __global__ void __launch_bounds__(THREADS) matmul_f16_tc_kernel(const __grid_con
     __syncwarp();
 
     // ---- epilogue: TMEM -> registers -> f16 -> global ----
-    ok &= mbar_wait(smem_u32(&acc_bar), 0, &gave_up);
+    ok &= mbar_wait(smem_u32(&acc_bar), 0, &gave_up);   // on give-up the drain still runs (warp-uniformly) on whatever TMEM holds
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     __half* crow = C + (size_t)(m0 + warp * 32 + lane) * N + n0;
     const uint32_t lane_base = tmem_acc + ((uint32_t)(warp * 32) << 16);
@@ -320,6 +320,7 @@ __global__ void __launch_bounds__(THREADS2, 1) matmul_f16_tc_persistent(const __
             tile_coords(t, tiles_m, tiles_n, &mi, &ni);
             const uint32_t buf = local & 1, use = local >> 1;
             ok &= mbar_wait(smem_u32(&tfull_bar[buf]), use & 1, &gave_up);
+            ok = __all_sync(0xffffffffu, ok);   // the warp stays together: tcgen05.ld below is warp-collective
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             __half* crow = C + (size_t)(mi * BM + ew * 32 + lane) * N + (size_t)ni * BN2;

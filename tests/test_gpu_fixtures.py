@@ -75,3 +75,22 @@ def test_triton_masked_vadd_leaves_poison(gpu, level):
     gpu.cpu_launch(emitted(gpu, kb.load("tri_vadd"), "vector_add", level), [a, bb, c, b.i64(n), b.i64(block)], 1)
     assert np.array_equal(c[:n], a + bb)
     assert np.all(c[n:] == -1.0)
+
+
+@pytest.mark.parametrize("flavour", ["cuda", "triton"])
+def test_c_drivers_link_against_the_shim_libraries(gpu, tmp_path, flavour):
+    """A C host program written against the reference's CPU-launch signatures (tests/drivers/*.c,
+    the checks of examples/cpu_launch_*.c) links against libbasalt_cpu_launch_<flavour>.so in place
+    of the x86 object file and passes on the GPU."""
+    import os
+    import shutil
+    import subprocess
+    if shutil.which("gcc") is None:
+        pytest.skip("no C compiler on this box")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    pkg = os.path.join(root, "basalt_b200")
+    exe = tmp_path / f"{flavour}_fixtures"
+    subprocess.run(["gcc", "-O1", "-o", str(exe), os.path.join(root, "tests", "drivers", f"{flavour}_fixtures.c"), f"-L{pkg}",
+                    f"-lbasalt_cpu_launch_{flavour}", f"-Wl,-rpath,{pkg}"], check=True)
+    r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and r.stdout.startswith("PASS"), r.stdout + r.stderr
