@@ -85,6 +85,7 @@ struct FnEmitter {
     std::map<std::pair<int, int64_t>, std::string> cells; // (space, key) -> symbol
     std::vector<uint32_t> uses;
     int label_n = 0, mma_n = 0;
+    unsigned maxntid = 0;
     Diag diag;
     bool failed = false;
 
@@ -603,6 +604,72 @@ struct FnEmitter {
         return -1;
     }
 
+    // value = parameter (or none) + c0 + cx*bid.x + cy*bid.y, when the value is such a function.
+    struct Aff {
+        bool ok = false;
+        int param = -1;
+        long long c0 = 0, cx = 0, cy = 0;
+    };
+    Aff affine(Val v, int depth = 0) const {
+        Aff r;
+        if (depth > 64) return r;
+        if (v.param) {
+            r.ok = f.params[v.idx].is_ptr();
+            r.param = (int)v.idx;
+            return r;
+        }
+        const Inst& d = f.insts[v.idx];
+        if (d.ty.is_vec()) return r;
+        switch (d.op) {
+            case Opc::ConstI:
+                if (d.ty.is_ptr() && d.ty.sp != Space::Global) return r;
+                r.ok = true;
+                r.c0 = d.imm;
+                return r;
+            case Opc::Index:
+                r.ok = d.sub == 3 || d.sub == 4;
+                r.cx = d.sub == 3;
+                r.cy = d.sub == 4;
+                return r;
+            case Opc::Cast: {
+                CastOp c = (CastOp)d.sub;
+                if (c != CastOp::SExt && c != CastOp::ZExt && c != CastOp::Trunc && c != CastOp::Bitcast) return r;
+                if (d.aux.is_float() || d.ty.is_float()) return r;
+                return affine(d.ops[0], depth + 1);
+            }
+            case Opc::Bin: {
+                BinOp b = (BinOp)d.sub;
+                Aff x = affine(d.ops[0], depth + 1), y = affine(d.ops[1], depth + 1);
+                if (!x.ok || !y.ok) return r;
+                if (b == BinOp::Add || b == BinOp::Sub) {
+                    if (x.param >= 0 && y.param >= 0) return r;
+                    if (b == BinOp::Sub && y.param >= 0) return r;
+                    long long sgn = b == BinOp::Add ? 1 : -1;
+                    r.ok = true;
+                    r.param = x.param >= 0 ? x.param : y.param;
+                    r.c0 = x.c0 + sgn * y.c0; r.cx = x.cx + sgn * y.cx; r.cy = x.cy + sgn * y.cy;
+                    return r;
+                }
+                if (b == BinOp::Mul || b == BinOp::Shl) {
+                    if (x.param >= 0 || y.param >= 0) return r;
+                    bool yc = y.cx == 0 && y.cy == 0, xc = x.cx == 0 && x.cy == 0;
+                    if (b == BinOp::Shl) {
+                        if (!yc || y.c0 < 0 || y.c0 > 40) return r;
+                        r.ok = true; r.c0 = x.c0 << y.c0; r.cx = x.cx << y.c0; r.cy = x.cy << y.c0;
+                        return r;
+                    }
+                    if (!yc && !xc) return r;
+                    const Aff& k = yc ? y : x;
+                    const Aff& t = yc ? x : y;
+                    r.ok = true; r.c0 = t.c0 * k.c0; r.cx = t.cx * k.c0; r.cy = t.cy * k.c0;
+                    return r;
+                }
+                return r;
+            }
+            default: return r;
+        }
+    }
+
     // `mma` as a CTA-collective op: every thread of the CTA reaches it, the tile product is
     // computed once.  This generic form spreads the m*n outputs over the CTA's threads and
     // follows the oracle's arithmetic exactly: acc = 0; acc = acc + a*b (two roundings);
@@ -625,6 +692,19 @@ struct FnEmitter {
         site.b_param = base_param(in.ops[1]);
         if (site.a_param >= 0) site.a_base = param_regs[site.a_param][0];
         if (site.b_param >= 0) site.b_base = param_regs[site.b_param][0];
+        Aff fa = affine(in.ops[0]), fb = affine(in.ops[1]), fd = affine(in.ops[3]);
+        site.affine = fa.ok && fb.ok && fd.ok && fa.param >= 0 && fb.param >= 0 && fd.param >= 0;
+        site.a_c0 = fa.c0; site.a_cx = fa.cx; site.a_cy = fa.cy;
+        site.b_c0 = fb.c0; site.b_cx = fb.cx; site.b_cy = fb.cy;
+        site.d_c0 = fd.c0; site.d_cx = fd.cx; site.d_cy = fd.cy;
+        site.d_param = fd.param;
+        if (site.affine) { site.a_param = fa.param; site.b_param = fb.param; site.a_base = param_regs[fa.param][0]; site.b_base = param_regs[fb.param][0]; site.d_base = param_regs[fd.param][0]; }
+        site.pure_kernel = f.blocks.size() == 1 && f.blocks[0].term.kind == Term::Ret;
+        for (uint32_t id : f.blocks[0].insts) {
+            Opc o = f.insts[id].op;
+            if (o != Opc::Mma && o != Opc::ConstI && o != Opc::Index && o != Opc::Bin && o != Opc::Cast) site.pure_kernel = false;
+        }
+        site.maxntid = &maxntid;
         site.extra_params = &extra_params;
         site.module_decls = &module_decls;
         if (emit_mma_fast(site, &decls, &body, &plan)) return;
@@ -837,8 +917,8 @@ struct FnEmitter {
         for (size_t i = 0; i < pd.size(); i++) o += (i ? ",\n\t" : "\n\t") + pd[i];
         o += pd.empty() ? ")\n" : "\n)\n";
         if (mod.has_launch_bounds) {
-            o += ".maxntid " + std::to_string(mod.max_threads) + ", 1, 1\n";
-            if (mod.min_blocks) o += ".minnctapersm " + std::to_string(mod.min_blocks) + "\n";
+            o += ".maxntid " + std::to_string(maxntid ? maxntid : mod.max_threads) + ", 1, 1\n";
+            if (mod.min_blocks) o += ".minnctapersm " + std::to_string(maxntid ? 1u : mod.min_blocks) + "\n";
         }
         o += "{\n";
         for (int c = 0; c < NCLS; c++)

@@ -39,6 +39,14 @@ struct MmaSite {
     bool sole_mma;                // the function's only mma
     int a_param, b_param;         // parameter each operand pointer is derived from by pointer adds, or -1
     std::string a_base, b_base;   // registers holding those parameters
+    // Operand pointers as affine functions of the block index: pointer = parameter + c0 + cx*bid.x + cy*bid.y.
+    // Valid when `affine` is set; then a/b/d derive from parameters a_param/b_param/d_param.
+    bool affine;
+    long long a_c0, a_cx, a_cy, b_c0, b_cx, b_cy, d_c0, d_cx, d_cy;
+    int d_param;
+    std::string d_base;
+    bool pure_kernel;             // one block, nothing but index arithmetic, this mma and `ret`
+    unsigned* maxntid;            // the entry's .maxntid, which a lowering may raise
     std::vector<std::string>* extra_params;   // receives .param declarations appended to the entry
     std::vector<std::string>* module_decls;   // receives module-scope declarations
 };

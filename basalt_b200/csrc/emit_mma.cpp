@@ -430,10 +430,352 @@ bool matmul_tcgen05(const MmaSite& s, std::vector<std::string>* decls, std::vect
     return true;
 }
 
+
+// The fp16 kernel whose CTAs each compute one 128x128 tile addressed as
+//   a = A + bid.y*128 rows, b = B + bid.x*128 columns, d = D + (bid.y*128 rows, bid.x*128 columns)
+// and do nothing else.  Such a grid is re-scheduled: one persistent CTA per SM (192 threads) walks
+// pairs of horizontally adjacent logical CTAs as 128x256 tiles (a 128-wide tile when the logical
+// grid is odd in x), in bands of 16 tile rows.  Warp 0 is the TMA producer (four 48 KB stages),
+// warp 1 issues tcgen05.mma M128 N256 K16 into one of two 256-column TMEM accumulators, warps 2-5
+// drain the other accumulator, so the epilogue of a tile overlaps the main loop of the next.  The
+// runtime passes the logical grid as two trailing u32 parameters and launches min(SMs, tiles) CTAs.
+bool matmul_tcgen05_persistent(const MmaSite& s, std::vector<std::string>* decls, std::vector<std::string>* lines, std::vector<std::string>* plan) {
+    const Inst& in = *s.inst;
+    if (in.in_dt != Scalar::F16 || in.acc_dt != Scalar::F32 || in.out_dt != Scalar::F16 || in.a_col) return false;
+    if (in.m != 128 || in.n != 128 || in.k % 64 != 0 || !s.c_is_null || !in.has_ld || !s.sole_mma || !s.pure_kernel || !s.affine) return false;
+    if (s.sa != Space::Global || s.sb != Space::Global || s.sd != Space::Global || s.max_threads != 128) return false;
+    if (!s.extra_params || !s.module_decls || !s.maxntid) return false;
+    const bool b_nk = in.b_col;
+    const long long lda = in.ld[0] ? in.ld[0] : in.k, ldb = in.ld[1] ? in.ld[1] : (b_nk ? in.k : in.n), ldd = in.ld[3] ? in.ld[3] : in.n;
+    if (lda % 8 || ldb % 8 || ldd % 8) return false;
+    // the tiling the re-scheduling relies on
+    if (s.a_c0 || s.a_cx || s.a_cy != 128 * lda * 2) return false;
+    if (s.b_c0 || s.b_cy || s.b_cx != (b_nk ? 128 * ldb * 2 : 256)) return false;
+    if (s.d_c0 || s.d_cx != 256 || s.d_cy != 128 * ldd * 2) return false;
+    const int u = s.uid, num_kb = (int)(in.k / 64), STAGE_BYTES = 49152;
+    const unsigned smem = 4 * STAGE_BYTES + 1024;
+    const std::string P = "%mp" + std::to_string(u) + "_", L = "$mp" + std::to_string(u) + "_";
+    auto r = [&](const char* n) { return P + n; };
+    std::string b32 = "\t.reg .b32 ";
+    for (const char* n : {"tid", "warp", "lane", "t", "u", "tiles", "bars", "slot", "gu", "tmem", "ok", "kb", "s", "ph", "par", "full", "empty", "adst", "bdst", "m0", "n0",
+                          "x", "it", "g", "idesc", "lgx", "lgy", "tn2", "ntiles", "perband", "band", "first", "rows", "rr", "mi", "nj", "width", "tile", "gstep", "local",
+                          "buf", "use", "bar2", "acc", "bytes", "ew", "c", "src", "spin"})
+        b32 += P + n + ", ";
+    b32 += P + "h<16>, " + P + "v<32>;";
+    decls->push_back(b32);
+    std::string b64 = "\t.reg .b64 ";
+    for (const char* n : {"w", "da", "db", "t0", "now", "dt", "crow", "status", "ma", "mb"}) b64 += P + n + ", ";
+    b64 += P + "z;";
+    decls->push_back(b64);
+    std::string pr = "\t.reg .pred ";
+    for (const char* n : {"p", "q", "w0", "w1", "l0", "prod", "mma", "epi", "accp", "done", "wide", "all"}) pr += P + n + ", ";
+    pr += P + "bx<4>;";
+    decls->push_back(pr);
+    char d[256];
+    snprintf(d, sizeof d, "\t.shared .align 8 .b8 __mp%d_bars[96];", u);   // full[4] @0, empty[4] @32, tfull[2] @64, tempty[2] @80
+    decls->push_back(d);
+    snprintf(d, sizeof d, "\t.shared .align 4 .b8 __mp%d_misc[8];", u);
+    decls->push_back(d);
+    s.module_decls->push_back(".extern .shared .align 1024 .b8 __basalt_dyn_smem[];");
+    const std::string ta = s.kernel + "_tmap_a", tb = s.kernel + "_tmap_b", stp = s.kernel + "_status", pgx = s.kernel + "_lgrid_x", pgy = s.kernel + "_lgrid_y";
+    s.extra_params->push_back(".param .align 64 .b8 " + ta + "[128]");
+    s.extra_params->push_back(".param .align 64 .b8 " + tb + "[128]");
+    s.extra_params->push_back(".param .u64 " + stp);
+    s.extra_params->push_back(".param .u32 " + pgx);
+    s.extra_params->push_back(".param .u32 " + pgy);
+    *s.maxntid = 192;
+    Out o{lines};
+    int wait_n = 0;
+    auto wait = [&](const std::string& bar, const std::string& par, const std::string& fail) {
+        std::string base = L + "w" + std::to_string(wait_n++);
+        o("mov.u64 %s, 0;", r("t0").c_str());
+        o("mov.u32 %s, 0;", r("spin").c_str());
+        o.label(base + "_loop");
+        o("mbarrier.try_wait.parity.shared::cta.b64 %s, [%s], %s;", r("done").c_str(), bar.c_str(), par.c_str());
+        o("@%s bra %s_done;", r("done").c_str(), base.c_str());
+        o("ld.volatile.shared.u32 %s, [%s];", r("g").c_str(), r("gu").c_str());
+        o("setp.ne.u32 %s, %s, 0;", r("q").c_str(), r("g").c_str());
+        o("@%s bra %s_fail;", r("q").c_str(), base.c_str());
+        o("add.u32 %s, %s, 1;", r("spin").c_str(), r("spin").c_str());
+        o("and.b32 %s, %s, 63;", r("g").c_str(), r("spin").c_str());
+        o("setp.ne.u32 %s, %s, 0;", r("q").c_str(), r("g").c_str());
+        o("@%s bra %s_loop;", r("q").c_str(), base.c_str());
+        o("mov.u64 %s, %%globaltimer;", r("now").c_str());
+        o("setp.ne.u64 %s, %s, 0;", r("q").c_str(), r("t0").c_str());
+        o("@%s bra %s_t;", r("q").c_str(), base.c_str());
+        o("mov.u64 %s, %s;", r("t0").c_str(), r("now").c_str());
+        o("bra %s_loop;", base.c_str());
+        o.label(base + "_t");
+        o("sub.u64 %s, %s, %s;", r("dt").c_str(), r("now").c_str(), r("t0").c_str());
+        o("setp.lt.u64 %s, %s, 200000000;", r("q").c_str(), r("dt").c_str());
+        o("@%s bra %s_loop;", r("q").c_str(), base.c_str());
+        o("st.volatile.shared.u32 [%s], 1;", r("gu").c_str());
+        o.label(base + "_fail");
+        o("mov.u32 %s, 0;", r("ok").c_str());
+        o("bra %s;", fail.c_str());
+        o.label(base + "_done");
+    };
+    // tile -> (m0, n0, width): bands of 16 tile rows, row-fastest inside a band
+    auto coords = [&]() {
+        o("div.u32 %s, %s, %s;", r("band").c_str(), r("tile").c_str(), r("perband").c_str());
+        o("shl.b32 %s, %s, 4;", r("first").c_str(), r("band").c_str());
+        o("sub.u32 %s, %s, %s;", r("rows").c_str(), r("lgy").c_str(), r("first").c_str());
+        o("min.u32 %s, %s, 16;", r("rows").c_str(), r("rows").c_str());
+        o("mul.lo.u32 %s, %s, %s;", r("t").c_str(), r("band").c_str(), r("perband").c_str());
+        o("sub.u32 %s, %s, %s;", r("rr").c_str(), r("tile").c_str(), r("t").c_str());
+        o("rem.u32 %s, %s, %s;", r("mi").c_str(), r("rr").c_str(), r("rows").c_str());
+        o("add.u32 %s, %s, %s;", r("mi").c_str(), r("mi").c_str(), r("first").c_str());
+        o("div.u32 %s, %s, %s;", r("nj").c_str(), r("rr").c_str(), r("rows").c_str());
+        o("shl.b32 %s, %s, 7;", r("m0").c_str(), r("mi").c_str());
+        o("shl.b32 %s, %s, 8;", r("n0").c_str(), r("nj").c_str());
+        o("shl.b32 %s, %s, 1;", r("t").c_str(), r("nj").c_str());
+        o("add.u32 %s, %s, 1;", r("t").c_str(), r("t").c_str());
+        o("setp.lt.u32 %s, %s, %s;", r("wide").c_str(), r("t").c_str(), r("lgx").c_str());   // the pair's second logical CTA exists
+        o("selp.u32 %s, 256, 128, %s;", r("width").c_str(), r("wide").c_str());
+    };
+
+    o("// mma f16->f32->f16 128x128x%u over a tiled grid: persistent TMA + tcgen05, 128x256 tiles, %s B", in.k, b_nk ? "K-major" : "MN-major");
+    o("mov.u32 %s, %%ntid.x;", r("t").c_str());
+    o("setp.ne.u32 %s, %s, 192;", r("p").c_str(), r("t").c_str());
+    o("@%s bra %sskip;", r("p").c_str(), L.c_str());
+    o("ld.param.u64 %s, [%s];", r("status").c_str(), stp.c_str());
+    o("ld.volatile.global.u32 %s, [%s];", r("t").c_str(), r("status").c_str());
+    o("setp.ne.u32 %s, %s, 0;", r("p").c_str(), r("t").c_str());
+    o("@%s bra %sskip;", r("p").c_str(), L.c_str());
+    o("ld.param.u32 %s, [%s];", r("lgx").c_str(), pgx.c_str());
+    o("ld.param.u32 %s, [%s];", r("lgy").c_str(), pgy.c_str());
+    o("mov.b64 %s, %s;", r("ma").c_str(), ta.c_str());
+    o("cvta.param.u64 %s, %s;", r("ma").c_str(), r("ma").c_str());
+    o("mov.b64 %s, %s;", r("mb").c_str(), tb.c_str());
+    o("cvta.param.u64 %s, %s;", r("mb").c_str(), r("mb").c_str());
+    o("mov.u32 %s, %%tid.x;", r("tid").c_str());
+    o("shr.u32 %s, %s, 5;", r("warp").c_str(), r("tid").c_str());
+    o("and.b32 %s, %s, 31;", r("lane").c_str(), r("tid").c_str());
+    o("mov.u64 %s, __basalt_dyn_smem;", r("w").c_str());
+    o("cvt.u32.u64 %s, %s;", r("tiles").c_str(), r("w").c_str());
+    o("add.u32 %s, %s, 1023;", r("tiles").c_str(), r("tiles").c_str());
+    o("and.b32 %s, %s, 0xFFFFFC00;", r("tiles").c_str(), r("tiles").c_str());
+    o("mov.u64 %s, __mp%d_bars;", r("w").c_str(), u);
+    o("cvt.u32.u64 %s, %s;", r("bars").c_str(), r("w").c_str());
+    o("mov.u64 %s, __mp%d_misc;", r("w").c_str(), u);
+    o("cvt.u32.u64 %s, %s;", r("slot").c_str(), r("w").c_str());
+    o("add.u32 %s, %s, 4;", r("gu").c_str(), r("slot").c_str());
+    o("add.u32 %s, %s, 1;", r("tn2").c_str(), r("lgx").c_str());
+    o("shr.u32 %s, %s, 1;", r("tn2").c_str(), r("tn2").c_str());
+    o("mul.lo.u32 %s, %s, %s;", r("ntiles").c_str(), r("tn2").c_str(), r("lgy").c_str());
+    o("shl.b32 %s, %s, 4;", r("perband").c_str(), r("tn2").c_str());
+    o("setp.ne.u32 %s, %s, 0;", r("p").c_str(), r("tid").c_str());
+    o("@%s bra %sinit_done;", r("p").c_str(), L.c_str());
+    o("st.volatile.shared.u32 [%s], 0;", r("gu").c_str());
+    for (int i = 0; i < 10; i++) o("mbarrier.init.shared::cta.b64 [%s+%d], 1;", r("bars").c_str(), 8 * i);
+    for (int i = 10; i < 12; i++) o("mbarrier.init.shared::cta.b64 [%s+%d], 4;", r("bars").c_str(), 8 * i);   // one arrival per epilogue warp
+    o("fence.mbarrier_init.release.cluster;");
+    o("fence.proxy.async.shared::cta;");
+    o.label(L + "init_done");
+    o("setp.eq.u32 %s, %s, 1;", r("w1").c_str(), r("warp").c_str());
+    o("@!%s bra %salloc_done;", r("w1").c_str(), L.c_str());
+    o("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%s], 512;", r("slot").c_str());
+    o("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+    o.label(L + "alloc_done");
+    o("tcgen05.fence::before_thread_sync;");
+    o("bar.sync 0;");
+    o("tcgen05.fence::after_thread_sync;");
+    o("ld.shared.u32 %s, [%s];", r("tmem").c_str(), r("slot").c_str());
+    o("mov.u32 %s, 1;", r("ok").c_str());
+    o("mov.u32 %s, %%ctaid.x;", r("tile").c_str());
+    o("mov.u32 %s, %%nctaid.x;", r("gstep").c_str());
+    o("mov.u32 %s, 0;", r("local").c_str());
+    o("mov.u32 %s, 0;", r("it").c_str());
+    o("setp.eq.u32 %s, %s, 0;", r("l0").c_str(), r("lane").c_str());
+    o("setp.eq.u32 %s, %s, 0;", r("w0").c_str(), r("warp").c_str());
+    o("and.pred %s, %s, %s;", r("prod").c_str(), r("w0").c_str(), r("l0").c_str());
+    o("and.pred %s, %s, %s;", r("mma").c_str(), r("w1").c_str(), r("l0").c_str());
+    o("setp.ge.u32 %s, %s, 2;", r("epi").c_str(), r("warp").c_str());
+    o("@%s bra %sp_tile;", r("prod").c_str(), L.c_str());
+    o("@%s bra %sm_tile;", r("mma").c_str(), L.c_str());
+    o("@%s bra %se_tile;", r("epi").c_str(), L.c_str());
+    o("bra %send;", L.c_str());
+
+    // ---- producer ----
+    o.label(L + "p_tile");
+    o("setp.ge.u32 %s, %s, %s;", r("p").c_str(), r("tile").c_str(), r("ntiles").c_str());
+    o("@%s bra %send;", r("p").c_str(), L.c_str());
+    coords();
+    o("shl.b32 %s, %s, 7;", r("bytes").c_str(), r("width").c_str());   // B slab: width x 64 halves
+    o("add.u32 %s, %s, 16384;", r("bytes").c_str(), r("bytes").c_str());
+    o("mov.u32 %s, 0;", r("kb").c_str());
+    o.label(L + "p_kb");
+    o("and.b32 %s, %s, 3;", r("s").c_str(), r("it").c_str());
+    o("shr.u32 %s, %s, 2;", r("ph").c_str(), r("it").c_str());
+    o("and.b32 %s, %s, 1;", r("ph").c_str(), r("ph").c_str());
+    o("xor.b32 %s, %s, 1;", r("par").c_str(), r("ph").c_str());
+    o("mad.lo.u32 %s, %s, 8, %s;", r("full").c_str(), r("s").c_str(), r("bars").c_str());
+    o("add.u32 %s, %s, 32;", r("empty").c_str(), r("full").c_str());
+    wait(r("empty"), r("par"), L + "p_fail");
+    o("mad.lo.u32 %s, %s, %d, %s;", r("adst").c_str(), r("s").c_str(), STAGE_BYTES, r("tiles").c_str());
+    o("add.u32 %s, %s, 16384;", r("bdst").c_str(), r("adst").c_str());
+    o("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%s], %s;", r("full").c_str(), r("bytes").c_str());
+    o("shl.b32 %s, %s, 6;", r("x").c_str(), r("kb").c_str());
+    const char* tma = "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes";
+    o("%s [%s], [%s, {%s, %s}], [%s];", tma, r("adst").c_str(), r("ma").c_str(), r("x").c_str(), r("m0").c_str(), r("full").c_str());
+    if (b_nk) {   // boxes of 64 k x 128 n rows
+        o("%s [%s], [%s, {%s, %s}], [%s];", tma, r("bdst").c_str(), r("mb").c_str(), r("x").c_str(), r("n0").c_str(), r("full").c_str());
+        o("add.u32 %s, %s, 128;", r("t").c_str(), r("n0").c_str());
+        o("add.u32 %s, %s, 16384;", r("u").c_str(), r("bdst").c_str());
+        o("@%s %s [%s], [%s, {%s, %s}], [%s];", r("wide").c_str(), tma, r("u").c_str(), r("mb").c_str(), r("x").c_str(), r("t").c_str(), r("full").c_str());
+    } else {      // boxes of 64 n x 64 k rows
+        for (int h = 0; h < 4; h++) {
+            o("add.u32 %s, %s, %d;", r("t").c_str(), r("n0").c_str(), 64 * h);
+            o("add.u32 %s, %s, %d;", r("u").c_str(), r("bdst").c_str(), 8192 * h);
+            if (h < 2) o("%s [%s], [%s, {%s, %s}], [%s];", tma, r("u").c_str(), r("mb").c_str(), r("t").c_str(), r("x").c_str(), r("full").c_str());
+            else o("@%s %s [%s], [%s, {%s, %s}], [%s];", r("wide").c_str(), tma, r("u").c_str(), r("mb").c_str(), r("t").c_str(), r("x").c_str(), r("full").c_str());
+        }
+    }
+    o("add.u32 %s, %s, 1;", r("it").c_str(), r("it").c_str());
+    o("add.u32 %s, %s, 1;", r("kb").c_str(), r("kb").c_str());
+    o("setp.lt.u32 %s, %s, %d;", r("p").c_str(), r("kb").c_str(), num_kb);
+    o("@%s bra %sp_kb;", r("p").c_str(), L.c_str());
+    o("add.u32 %s, %s, %s;", r("tile").c_str(), r("tile").c_str(), r("gstep").c_str());
+    o("bra %sp_tile;", L.c_str());
+    o.label(L + "p_fail");   // let the copies already issued land (2 ms, bounded) before the CTA can exit
+    o("mov.u64 %s, %%globaltimer;", r("t0").c_str());
+    o.label(L + "p_spin");
+    o("mov.u64 %s, %%globaltimer;", r("now").c_str());
+    o("sub.u64 %s, %s, %s;", r("dt").c_str(), r("now").c_str(), r("t0").c_str());
+    o("setp.lt.u64 %s, %s, 2000000;", r("q").c_str(), r("dt").c_str());
+    o("@%s bra %sp_spin;", r("q").c_str(), L.c_str());
+    o("bra %send;", L.c_str());
+
+    // ---- MMA issuer ----
+    const unsigned idesc128 = (1u << 4) | ((b_nk ? 0u : 1u) << 16) | (16u << 17) | (8u << 24), idesc256 = (1u << 4) | ((b_nk ? 0u : 1u) << 16) | (32u << 17) | (8u << 24);
+    const unsigned long long desc_a_hi = (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+    const unsigned long long desc_b_hi = b_nk ? desc_a_hi : ((512ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61));
+    o.label(L + "m_tile");
+    o("setp.ge.u32 %s, %s, %s;", r("p").c_str(), r("tile").c_str(), r("ntiles").c_str());
+    o("@%s bra %send;", r("p").c_str(), L.c_str());
+    coords();
+    o("selp.u32 %s, %u, %u, %s;", r("idesc").c_str(), idesc256, idesc128, r("wide").c_str());
+    o("and.b32 %s, %s, 1;", r("buf").c_str(), r("local").c_str());
+    o("shr.u32 %s, %s, 1;", r("use").c_str(), r("local").c_str());
+    o("and.b32 %s, %s, 1;", r("par").c_str(), r("use").c_str());
+    o("xor.b32 %s, %s, 1;", r("par").c_str(), r("par").c_str());
+    o("mad.lo.u32 %s, %s, 8, %s;", r("bar2").c_str(), r("buf").c_str(), r("bars").c_str());
+    o("add.u32 %s, %s, 80;", r("bar2").c_str(), r("bar2").c_str());   // tempty[buf]: the epilogue has drained this accumulator
+    wait(r("bar2"), r("par"), L + "end");
+    o("tcgen05.fence::after_thread_sync;");
+    o("mad.lo.u32 %s, %s, 256, %s;", r("acc").c_str(), r("buf").c_str(), r("tmem").c_str());
+    o("mov.u32 %s, 0;", r("kb").c_str());
+    o.label(L + "m_kb");
+    o("and.b32 %s, %s, 3;", r("s").c_str(), r("it").c_str());
+    o("shr.u32 %s, %s, 2;", r("ph").c_str(), r("it").c_str());
+    o("and.b32 %s, %s, 1;", r("ph").c_str(), r("ph").c_str());
+    o("mad.lo.u32 %s, %s, 8, %s;", r("full").c_str(), r("s").c_str(), r("bars").c_str());
+    o("add.u32 %s, %s, 32;", r("empty").c_str(), r("full").c_str());
+    wait(r("full"), r("ph"), L + "end");
+    o("tcgen05.fence::after_thread_sync;");
+    o("mad.lo.u32 %s, %s, %d, %s;", r("adst").c_str(), r("s").c_str(), STAGE_BYTES, r("tiles").c_str());
+    o("add.u32 %s, %s, 16384;", r("bdst").c_str(), r("adst").c_str());
+    for (int k = 0; k < 4; k++) {
+        o("add.u32 %s, %s, %d;", r("x").c_str(), r("adst").c_str(), k * 32);
+        o("shr.u32 %s, %s, 4;", r("x").c_str(), r("x").c_str());
+        o("and.b32 %s, %s, 0x3FFF;", r("x").c_str(), r("x").c_str());
+        o("cvt.u64.u32 %s, %s;", r("da").c_str(), r("x").c_str());
+        o("or.b64 %s, %s, 0x%llX;", r("da").c_str(), r("da").c_str(), desc_a_hi);
+        o("add.u32 %s, %s, %d;", r("x").c_str(), r("bdst").c_str(), b_nk ? k * 32 : k * 2048);
+        o("shr.u32 %s, %s, 4;", r("x").c_str(), r("x").c_str());
+        o("and.b32 %s, %s, 0x3FFF;", r("x").c_str(), r("x").c_str());
+        o("cvt.u64.u32 %s, %s;", r("db").c_str(), r("x").c_str());
+        o("or.b64 %s, %s, 0x%llX;", r("db").c_str(), r("db").c_str(), desc_b_hi);
+        if (k == 0) o("setp.ne.u32 %s, %s, 0;", r("accp").c_str(), r("kb").c_str());   // the tile's first MMA overwrites the accumulator
+        else o("setp.ne.u32 %s, %s, 0;", r("accp").c_str(), r("idesc").c_str());
+        o("tcgen05.mma.cta_group::1.kind::f16 [%s], %s, %s, %s, %s;", r("acc").c_str(), r("da").c_str(), r("db").c_str(), r("idesc").c_str(), r("accp").c_str());
+    }
+    o("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%s];", r("empty").c_str());
+    o("add.u32 %s, %s, 1;", r("it").c_str(), r("it").c_str());
+    o("add.u32 %s, %s, 1;", r("kb").c_str(), r("kb").c_str());
+    o("setp.lt.u32 %s, %s, %d;", r("p").c_str(), r("kb").c_str(), num_kb);
+    o("@%s bra %sm_kb;", r("p").c_str(), L.c_str());
+    o("sub.u32 %s, %s, 16;", r("bar2").c_str(), r("bar2").c_str());   // tfull[buf]
+    o("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%s];", r("bar2").c_str());
+    o("add.u32 %s, %s, %s;", r("tile").c_str(), r("tile").c_str(), r("gstep").c_str());
+    o("add.u32 %s, %s, 1;", r("local").c_str(), r("local").c_str());
+    o("bra %sm_tile;", L.c_str());
+
+    // ---- epilogue warps ----
+    o.label(L + "e_tile");
+    o("setp.ge.u32 %s, %s, %s;", r("p").c_str(), r("tile").c_str(), r("ntiles").c_str());
+    o("@%s bra %send;", r("p").c_str(), L.c_str());
+    coords();
+    o("and.b32 %s, %s, 1;", r("buf").c_str(), r("local").c_str());
+    o("shr.u32 %s, %s, 1;", r("use").c_str(), r("local").c_str());
+    o("and.b32 %s, %s, 1;", r("par").c_str(), r("use").c_str());
+    o("mad.lo.u32 %s, %s, 8, %s;", r("bar2").c_str(), r("buf").c_str(), r("bars").c_str());
+    o("add.u32 %s, %s, 64;", r("bar2").c_str(), r("bar2").c_str());   // tfull[buf]
+    wait(r("bar2"), r("par"), L + "e_after" + std::to_string(0));
+    o.label(L + "e_after0");
+    o("setp.ne.u32 %s, %s, 0;", r("p").c_str(), r("ok").c_str());
+    o("vote.sync.all.pred %s, %s, 0xffffffff;", r("all").c_str(), r("p").c_str());   // the warp stays together: tcgen05.ld is warp-collective
+    o("@!%s bra %send;", r("all").c_str(), L.c_str());
+    o("tcgen05.fence::after_thread_sync;");
+    o("and.b32 %s, %s, 3;", r("ew").c_str(), r("warp").c_str());   // this warp may touch TMEM lanes 32*ew .. 32*ew+31
+    o("mad.lo.u32 %s, %s, 32, %s;", r("t").c_str(), r("ew").c_str(), r("lane").c_str());
+    o("add.u32 %s, %s, %s;", r("t").c_str(), r("t").c_str(), r("m0").c_str());
+    o("mul.wide.u32 %s, %s, %lld;", r("w").c_str(), r("t").c_str(), ldd * 2);
+    o("add.u64 %s, %s, %s;", r("crow").c_str(), s.d_base.c_str(), r("w").c_str());
+    o("mul.wide.u32 %s, %s, 2;", r("w").c_str(), r("n0").c_str());
+    o("add.u64 %s, %s, %s;", r("crow").c_str(), r("crow").c_str(), r("w").c_str());
+    o("mad.lo.u32 %s, %s, 256, %s;", r("src").c_str(), r("buf").c_str(), r("tmem").c_str());
+    o("shl.b32 %s, %s, 21;", r("t").c_str(), r("ew").c_str());
+    o("add.u32 %s, %s, %s;", r("src").c_str(), r("src").c_str(), r("t").c_str());
+    o("mov.u32 %s, 0;", r("c").c_str());
+    o.label(L + "e_c");
+    {
+        std::string list;
+        for (int i = 0; i < 32; i++) list += (i ? ", " : "") + P + "v" + std::to_string(i);
+        o("add.u32 %s, %s, %s;", r("x").c_str(), r("src").c_str(), r("c").c_str());
+        o("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%s}, [%s];", list.c_str(), r("x").c_str());
+        o("tcgen05.wait::ld.sync.aligned;");
+        for (int i = 0; i < 16; i++) o("cvt.rn.f16x2.f32 %sh%d, %sv%d, %sv%d;", P.c_str(), i, P.c_str(), 2 * i + 1, P.c_str(), 2 * i);
+        o("mul.wide.u32 %s, %s, 2;", r("z").c_str(), r("c").c_str());
+        o("add.u64 %s, %s, %s;", r("z").c_str(), r("z").c_str(), r("crow").c_str());
+        for (int q = 0; q < 4; q++)
+            o("st.global.v4.b32 [%s+%d], {%sh%d, %sh%d, %sh%d, %sh%d};", r("z").c_str(), 16 * q, P.c_str(), 4 * q, P.c_str(), 4 * q + 1, P.c_str(), 4 * q + 2, P.c_str(), 4 * q + 3);
+    }
+    o("add.u32 %s, %s, 32;", r("c").c_str(), r("c").c_str());
+    o("setp.lt.u32 %s, %s, %s;", r("p").c_str(), r("c").c_str(), r("width").c_str());
+    o("@%s bra %se_c;", r("p").c_str(), L.c_str());
+    o("tcgen05.fence::before_thread_sync;");
+    o("bar.warp.sync 0xffffffff;");
+    o("add.u32 %s, %s, 16;", r("bar2").c_str(), r("bar2").c_str());   // tempty[buf]
+    o("@%s mbarrier.arrive.shared::cta.b64 _, [%s];", r("l0").c_str(), r("bar2").c_str());
+    o("add.u32 %s, %s, %s;", r("tile").c_str(), r("tile").c_str(), r("gstep").c_str());
+    o("add.u32 %s, %s, 1;", r("local").c_str(), r("local").c_str());
+    o("bra %se_tile;", L.c_str());
+
+    o.label(L + "end");
+    o("setp.ne.u32 %s, %s, 0;", r("p").c_str(), r("ok").c_str());
+    o("@%s bra %sstatus_done;", r("p").c_str(), L.c_str());
+    o("mov.u32 %s, 1;", r("t").c_str());
+    o("atom.global.exch.b32 %s, [%s], %s;", r("g").c_str(), r("status").c_str(), r("t").c_str());
+    o.label(L + "status_done");
+    o("bar.warp.sync 0xffffffff;");
+    o("tcgen05.fence::before_thread_sync;");
+    o("bar.sync 0;");
+    o("@!%s bra %sskip;", r("w1").c_str(), L.c_str());
+    o("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %s, 512;", r("tmem").c_str());
+    o.label(L + "skip");
+    char pl[640];
+    snprintf(pl, sizeof pl,
+             "//!basalt.plan %s logical_block=128,1,1 block=192,1,1 smem=%u params=%u tmap=%d:2:%lld:%lld:64:128:128 tmap=%d:2:%lld:%lld:64:%d:128 status=1 lgrid=2",
+             s.kernel.c_str(), smem, s.nparams, s.a_param, lda, lda * 2, s.b_param, ldb, ldb * 2, b_nk ? 128 : 64);
+    plan->push_back(pl);
+    return true;
+}
+
 }  // namespace
 
 bool emit_mma_fast(const MmaSite& site, std::vector<std::string>* decls, std::vector<std::string>* lines, std::vector<std::string>* plan) {
-    return sgemm_ffma(site, decls, lines, plan) || matmul_tcgen05(site, decls, lines, plan);
+    return sgemm_ffma(site, decls, lines, plan) || matmul_tcgen05_persistent(site, decls, lines, plan) || matmul_tcgen05(site, decls, lines, plan);
 }
 
 }  // namespace basalt

@@ -104,7 +104,10 @@ struct Plan {
     unsigned nparams = 0;   // number of BIR parameters (tensor maps follow them)
     std::vector<TmapSpec> tmaps;
     std::string coarse;     // entry taking one more u64 parameter: the thread count the caller asked for
-    bool status = false;    // the entry takes a last u64 parameter: a device int32 set when a bounded wait gave up
+    bool status = false;    // the entry takes a u64 parameter: a device int32 set when a bounded wait gave up
+    unsigned logical_block[3] = {0, 0, 0};   // block the caller must ask for when it differs from the block launched
+    unsigned lgrid = 0;     // persistent kernel: the caller's grid goes in two trailing u32 parameters; lgrid logical CTAs
+                            // along x form one tile, and min(SM count, tiles) CTAs are launched
 };
 }  // namespace
 struct basalt_rt_module {
@@ -206,6 +209,8 @@ void parse_plans(const char* ptx, std::map<std::string, Plan>* out) {
             else if (k == "params") p.nparams = (unsigned)strtoul(v.c_str(), nullptr, 10);
             else if (k == "coarse") p.coarse = v;
             else if (k == "status") p.status = v != "0";
+            else if (k == "logical_block") sscanf(v.c_str(), "%u,%u,%u", &p.logical_block[0], &p.logical_block[1], &p.logical_block[2]);
+            else if (k == "lgrid") p.lgrid = (unsigned)strtoul(v.c_str(), nullptr, 10);
             else if (k == "tmap") {
                 TmapSpec t;
                 unsigned long long inner = 0, rowb = 0;
@@ -462,8 +467,9 @@ int basalt_rt_launch(basalt_rt_function* fn, const uint32_t grid[3], const uint3
         return check(f, "cuLaunchKernel", f.cuLaunchKernel(fn->fn, grid[0], grid[1], grid[2], block[0], block[1], block[2], sm, (CUstream)stream, params, nullptr));
     }
     const Plan& p = fn->plan;
-    if (block[0] != p.block[0] || block[1] != p.block[1] || block[2] != p.block[2])
-        return set_err(4, 0, "cuLaunchKernel", "kernel was compiled for block (" + std::to_string(p.block[0]) + "," + std::to_string(p.block[1]) + "," + std::to_string(p.block[2]) + ")");
+    const unsigned* want = p.logical_block[0] ? p.logical_block : p.block;
+    if (block[0] != want[0] || block[1] != want[1] || block[2] != want[2])
+        return set_err(4, 0, "cuLaunchKernel", "kernel was compiled for block (" + std::to_string(want[0]) + "," + std::to_string(want[1]) + "," + std::to_string(want[2]) + ")");
     if (!params) return set_err(4, 0, "cuLaunchKernel", "kernel takes parameters");
     std::vector<CUtensorMap> maps(p.tmaps.size());
     std::vector<void*> all(params, params + p.nparams);
@@ -489,7 +495,18 @@ int basalt_rt_launch(basalt_rt_function* fn, const uint32_t grid[3], const uint3
     uint64_t status_ptr = (uint64_t)fn->status;
     if (p.status) all.push_back(&status_ptr);
     uint32_t sm = shared_mem_bytes ? shared_mem_bytes : p.smem;
-    return check(f, "cuLaunchKernel", f.cuLaunchKernel(fn->fn, grid[0], grid[1], grid[2], block[0], block[1], block[2], sm, (CUstream)stream, all.data(), nullptr));
+    uint32_t g[3] = {grid[0], grid[1], grid[2]}, lgx = grid[0], lgy = grid[1];
+    if (p.lgrid) {
+        if (grid[2] != 1) return set_err(4, 0, "cuLaunchKernel", "kernel was compiled for a two-dimensional grid");
+        uint64_t tiles = (uint64_t)((lgx + p.lgrid - 1) / p.lgrid) * lgy;
+        uint64_t sms = (uint64_t)fn->mod->ctx->sm_count;
+        g[0] = (uint32_t)(tiles < sms ? tiles : sms);
+        g[1] = 1;
+        if (g[0] == 0) return 0;
+        all.push_back(&lgx);
+        all.push_back(&lgy);
+    }
+    return check(f, "cuLaunchKernel", f.cuLaunchKernel(fn->fn, g[0], g[1], g[2], p.block[0], p.block[1], p.block[2], sm, (CUstream)stream, all.data(), nullptr));
 }
 
 int basalt_rt_occupancy(basalt_rt_function* fn, uint32_t block_threads, uint32_t shared_mem_bytes, int* ctas_per_sm, int* sm_count) {

@@ -141,11 +141,12 @@ def sgemm_cta128(M: int, N: int, K: int) -> str:
     return assemble(text)
 
 
-def matmul_f16(M: int, N: int, K: int, b_is_nk: bool = False) -> str:
+def matmul_f16(M: int, N: int, K: int, b_is_nk: bool = False, per_cta: bool = False) -> str:
     """C[MxN] (f16) = A[MxK] (f16) * B (f16), f32 accumulation: the tile-level form of a Triton
     matmul with BLOCK_M = BLOCK_N = 128 (the K loop over BLOCK_K = 64 slabs is inside the `mma`).
     B is [K x N] row-major, or with b_is_nk stored transposed as [N x K].  Launch with grid
-    (N/128, M/128) and 128 threads."""
+    (N/128, M/128) and 128 threads.  per_cta adds a trailing barrier, which keeps the emitter from
+    re-scheduling the grid as a persistent kernel (each CTA then runs its own TMA + tcgen05 pipeline)."""
     assert M % 128 == 0 and N % 128 == 0 and K % 64 == 0
     if b_is_nk:
         lb, ldb, bstep = "col", K, 128 * K * 2
@@ -174,6 +175,7 @@ def matmul_f16(M: int, N: int, K: int, b_is_nk: bool = False) -> str:
     %d = add ptr.global %arg2, %coff
     %null = const.i ptr.global 0
     mma f16 f32 row {lb} m 128 n 128 k {K} ld {K} {ldb} {N} {N} out f16 %a, %b, %null, %d
+{"    barrier" if per_cta else ""}
     ret
   }}
 }}

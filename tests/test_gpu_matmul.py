@@ -82,13 +82,13 @@ def run_matmul_f16(gpu, how, A, B, N, b_is_nk):
         gpu.synchronize()
         assert status.to_numpy(np.int32)[0] == 0, "a bounded wait inside the kernel expired"
     else:
-        fn = emitted(gpu, kb.matmul_f16(M, N, K, b_is_nk), "matmul_kernel")
+        fn = emitted(gpu, kb.matmul_f16(M, N, K, b_is_nk, per_cta=(how == "emitted_per_cta")), "matmul_kernel")
         fn.launch((N // 128, M // 128), 128, 0, [dA, dB, dC])
         assert fn.status() == 0, "a bounded wait inside the emitted kernel expired"
     return dC.to_numpy(np.float16).reshape(M, N)
 
 
-@pytest.mark.parametrize("how", ["hand", "emitted"])
+@pytest.mark.parametrize("how", ["hand", "emitted", "emitted_per_cta"])
 @pytest.mark.parametrize("b_is_nk", [True, False])
 @pytest.mark.parametrize("shape", [(128, 128, 64), (128, 128, 256), (256, 384, 192), (256, 512, 192), (384, 256, 64), (2304, 512, 64)])
 def test_matmul_f16_exact_on_small_integers(gpu, how, b_is_nk, shape):
