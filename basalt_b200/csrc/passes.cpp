@@ -310,6 +310,212 @@ void inline_calls(Module& m) {
     m.funcs = std::move(kernels);
 }
 
+
+// ---- SSA construction ----------------------------------------------------------------------
+// Promotes the front end's "locals are stack slots" pattern to SSA values and phis, the job of
+// construct_ssa in the reference (crates/basalt-passes/src/ssa.rs:1-29, called from Ptx::emit,
+// crates/basalt-ptx/src/emit.rs:1990).  A slot is one `const.i ptr.<space> K` address; it is
+// promotable when every use of that constant is the address operand of a non-volatile scalar
+// load or store and all of them agree on one type (ssa.rs:4-10).  Following Braun et al.: the
+// value reaching a block's entry is found by recursing into the predecessors, with a placeholder
+// phi at every multi-predecessor block to break cycles, then trivial phis are removed.  A read of
+// a never-written slot yields zero, as in the reference.  Deliberate difference: `shared`-space
+// slots are left in memory (on the GPU they are visible to the whole CTA, not per thread).
+namespace {
+struct SlotInfo {
+    Ty ty;
+    bool typed = false, ok = true;
+};
+}  // namespace
+
+void construct_ssa(Function& f) {
+    using Key = std::pair<int, int64_t>;
+    std::map<uint32_t, Key> slot_const;   // const instruction id -> slot
+    std::map<Key, SlotInfo> slots;
+    for (auto& b : f.blocks)
+        for (uint32_t id : b.insts) {
+            const Inst& in = f.insts[id];
+            if (in.op == Opc::ConstI && in.ty.is_ptr() && (in.ty.sp == Space::Local || in.ty.sp == Space::Param || in.ty.sp == Space::Constant)) {
+                Key k{(int)in.ty.sp, in.imm};
+                slot_const[id] = k;
+                slots[k];
+            }
+        }
+    if (slots.empty()) return;
+    auto slot_of = [&](Val v) -> const Key* {
+        if (v.param) return nullptr;
+        auto it = slot_const.find(v.idx);
+        return it == slot_const.end() ? nullptr : &it->second;
+    };
+    for (auto& b : f.blocks) {
+        for (uint32_t id : b.insts) {
+            const Inst& in = f.insts[id];
+            for (size_t oi = 0; oi < in.ops.size(); oi++) {
+                const Key* k = slot_of(in.ops[oi]);
+                if (!k) continue;
+                SlotInfo& si = slots[*k];
+                bool addr = oi == 0 && (in.op == Opc::Load || in.op == Opc::Store) && !in.vol;
+                Ty t = in.op == Opc::Load ? in.ty : in.aux;
+                if (!addr || t.kind == Ty::Vec || t.kind == Ty::Void) { si.ok = false; continue; }
+                if (!si.typed) { si.ty = t; si.typed = true; }
+                else if (si.ty != t) si.ok = false;
+            }
+        }
+        if (b.term.has_val) if (const Key* k = slot_of(b.term.val)) slots[*k].ok = false;
+    }
+    bool any = false;
+    for (auto& kv : slots) any |= kv.second.ok && kv.second.typed;
+    if (!any) return;
+    auto promotable = [&](Val v) -> const Key* {
+        const Key* k = slot_of(v);
+        return k && slots[*k].ok && slots[*k].typed ? k : nullptr;
+    };
+
+    const size_t NB = f.blocks.size();
+    std::vector<std::vector<uint32_t>> preds(NB);
+    {
+        std::vector<uint32_t> succ;
+        for (uint32_t b = 0; b < NB; b++) {
+            successors(f.blocks[b].term, succ);
+            std::sort(succ.begin(), succ.end());
+            succ.erase(std::unique(succ.begin(), succ.end()), succ.end());
+            for (uint32_t s2 : succ) preds[s2].push_back(b);
+        }
+    }
+    // local scan: what each promoted load reads, and what each block leaves in each slot
+    const Val ENTRY = Val::P(UINT32_MAX);   // marker: "the value at this block's entry"
+    std::map<uint32_t, Val> load_src;                 // load id -> stored value, or ENTRY
+    std::map<uint32_t, std::pair<Key, uint32_t>> load_at;   // load id -> (slot, block)
+    std::vector<std::map<Key, Val>> last_store(NB);
+    std::set<uint32_t> dead;   // promoted loads, stores and slot constants
+    for (uint32_t b = 0; b < NB; b++) {
+        std::map<Key, Val> cur;
+        for (uint32_t id : f.blocks[b].insts) {
+            const Inst& in = f.insts[id];
+            if (in.op == Opc::Load) {
+                if (const Key* k = promotable(in.ops[0])) {
+                    auto it = cur.find(*k);
+                    load_src[id] = it != cur.end() ? it->second : ENTRY;
+                    load_at[id] = {*k, b};
+                    dead.insert(id);
+                }
+            } else if (in.op == Opc::Store) {
+                if (const Key* k = promotable(in.ops[0])) {
+                    cur[*k] = in.ops[1];
+                    dead.insert(id);
+                }
+            }
+        }
+        last_store[b] = cur;
+    }
+    for (auto& kv : slot_const) if (slots[kv.second].ok && slots[kv.second].typed) dead.insert(kv.first);
+
+    // entry values, with placeholder phis
+    std::map<std::pair<uint32_t, Key>, Val> entry_val;
+    std::vector<std::vector<uint32_t>> new_phis(NB);
+    std::map<Key, Val> zero_of;
+    std::vector<uint32_t> zero_ids;
+    auto zero = [&](const Key& k) {
+        auto it = zero_of.find(k);
+        if (it != zero_of.end()) return it->second;
+        Inst z;
+        z.ty = slots[k].ty;
+        if (z.ty.is_float()) { z.op = Opc::ConstF; z.fimm = 0; } else { z.op = Opc::ConstI; z.imm = 0; }
+        if (z.ty.is_ptr()) z.ty = Ty::p(Space::Global);
+        uint32_t id = (uint32_t)f.insts.size();
+        f.insts.push_back(z);
+        zero_ids.push_back(id);
+        return zero_of[k] = Val::V(id);
+    };
+    std::function<Val(const Key&, uint32_t)> at_entry, at_exit;
+    at_exit = [&](const Key& k, uint32_t b) -> Val {
+        auto it = last_store[b].find(k);
+        return it != last_store[b].end() ? it->second : at_entry(k, b);
+    };
+    at_entry = [&](const Key& k, uint32_t b) -> Val {
+        auto key = std::make_pair(b, k);
+        auto it = entry_val.find(key);
+        if (it != entry_val.end()) return it->second;
+        if (b == 0 || preds[b].empty()) return entry_val[key] = zero(k);
+        if (preds[b].size() == 1 && preds[b][0] != b) {
+            Val v = at_exit(k, preds[b][0]);
+            return entry_val[key] = v;
+        }
+        Inst phi;
+        phi.op = Opc::Phi;
+        phi.ty = slots[k].ty;
+        uint32_t pid = (uint32_t)f.insts.size();
+        f.insts.push_back(phi);
+        new_phis[b].push_back(pid);
+        entry_val[key] = Val::V(pid);
+        for (uint32_t p : preds[b]) {
+            Val v = at_exit(k, p);
+            f.insts[pid].phi_blocks.push_back(p);
+            f.insts[pid].ops.push_back(v);
+        }
+        return Val::V(pid);
+    };
+    for (auto& kv : load_at)
+        if (load_src[kv.first] == ENTRY) load_src[kv.first] = at_entry(kv.second.first, kv.second.second);
+    // a value may be a promoted load: follow to what it reads
+    std::map<uint32_t, Val> phi_repl;
+    std::function<Val(Val)> fin = [&](Val v) -> Val {
+        for (int guard = 0; guard < 1 << 20; guard++) {
+            if (v.param) return v;
+            auto l = load_src.find(v.idx);
+            if (l != load_src.end()) { v = l->second; continue; }
+            auto r = phi_repl.find(v.idx);
+            if (r != phi_repl.end()) { v = r->second; continue; }
+            return v;
+        }
+        return v;
+    };
+    // trivial phis: all operands (other than the phi itself) are one value
+    for (bool changed = true; changed;) {
+        changed = false;
+        for (uint32_t b = 0; b < NB; b++)
+            for (uint32_t pid : new_phis[b]) {
+                if (phi_repl.count(pid)) continue;
+                Val uniq;
+                bool have = false, trivial = true;
+                for (Val o : f.insts[pid].ops) {
+                    Val v = fin(o);
+                    if (v == Val::V(pid)) continue;
+                    if (!have) { uniq = v; have = true; }
+                    else if (v != uniq) { trivial = false; break; }
+                }
+                if (trivial) {
+                    const Key* any_key = nullptr;
+                    for (auto& ev : entry_val) if (ev.second == Val::V(pid)) any_key = &ev.first.second;
+                    phi_repl[pid] = have ? uniq : (any_key ? zero(*any_key) : Val::V(pid));
+                    changed = true;
+                }
+            }
+    }
+    // rewrite
+    for (auto& in : f.insts) for (Val& v : in.ops) v = fin(v);
+    for (auto& b : f.blocks) if (b.term.has_val) b.term.val = fin(b.term.val);
+    for (uint32_t b = 0; b < NB; b++) {
+        std::vector<uint32_t> out;
+        if (b == 0) for (uint32_t z : zero_ids) out.push_back(z);
+        for (uint32_t pid : new_phis[b]) if (!phi_repl.count(pid)) out.push_back(pid);
+        // existing phis stay first, ahead of the zero constants only in block 0 where there are none
+        std::vector<uint32_t> old_phis, rest;
+        for (uint32_t id : f.blocks[b].insts) {
+            if (dead.count(id)) continue;
+            (f.insts[id].op == Opc::Phi ? old_phis : rest).push_back(id);
+        }
+        std::vector<uint32_t> merged;
+        for (uint32_t id : old_phis) merged.push_back(id);
+        for (uint32_t id : out) if (f.insts[id].op == Opc::Phi) merged.push_back(id);
+        for (uint32_t id : out) if (f.insts[id].op != Opc::Phi) merged.push_back(id);
+        for (uint32_t id : rest) merged.push_back(id);
+        f.blocks[b].insts = merged;
+    }
+    dce(f);
+    canonicalize(f);
+}
+
 // ---- function builder ----------------------------------------------------------------------
 namespace {
 struct FB {
@@ -1051,6 +1257,7 @@ int estimate_registers(const Function& f) {
 }
 
 void optimize_module(Module& m, int opt_level, int reg_budget, std::vector<OptReport>* reports) {
+    for (auto& f : m.funcs) construct_ssa(f);
     inline_calls(m);
     std::vector<Function> extra;
     std::vector<OptReport> extra_reports;

@@ -29,6 +29,9 @@ struct Diag {
 // kernel E093.  Host ops stay E090.
 bool check_module(const Module& m, Diag* d);
 
+// Promotes promotable local/param slots to SSA values and phis (the reference's construct_ssa,
+// crates/basalt-passes/src/ssa.rs), so that slot-form BIR straight from the front end is accepted.
+void construct_ssa(Function& f);
 // Inlines every call (the graph is acyclic after check_module) and drops the helper functions.
 void inline_calls(Module& m);
 // Merges straight-line block chains, removes unreachable blocks.

@@ -16,7 +16,7 @@ from .birasm import assemble
 _DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "bir")
 
 STATIC = ("vadd_i32", "vector_add_f32", "max_i32", "max_i32_atomic", "chain_vector", "square_vector", "mma2x2",
-          "tiled_sgemm_f32", "tri_matmul", "tri_vadd", "sgemm_tile16", "max_i32_strided")
+          "tiled_sgemm_f32", "tri_matmul", "tri_vadd", "sgemm_tile16", "max_i32_strided", "slot_form_sum")
 
 
 def load(name: str) -> str:

@@ -61,10 +61,11 @@ def test_compares_and_casts(ptx):
 
 
 def test_load_store_cover_every_address_space(ptx):
+    # volatile keeps the local/param/constant cells in memory (non-volatile ones are promoted to SSA values)
     for space, word in (("global", "global"), ("shared", "shared"), ("local", "local"), ("constant", "local"), ("param", "local")):
-        body = f"    %p = const.i ptr.{space} 65536\n    %v = load i32 ptr.{space} %p, align 4\n    store i32 ptr.{space} %p, %v, align 4"
+        body = f"    %p = const.i ptr.{space} 65536\n    %v = load i32 ptr.{space} %p, align 4, volatile\n    store i32 ptr.{space} %p, %v, align 4, volatile"
         text = emit0(ptx, kernel(body))
-        assert f"ld.{word}.u32" in text and f"st.{word}.u32" in text, space
+        assert f"ld.volatile.{word}.u32" in text and f"st.volatile.{word}.u32" in text, space
 
 
 def test_sized_shared_object_becomes_an_array(ptx):

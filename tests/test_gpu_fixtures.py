@@ -94,3 +94,11 @@ def test_c_drivers_link_against_the_shim_libraries(gpu, tmp_path, flavour):
                     f"-lbasalt_cpu_launch_{flavour}", f"-Wl,-rpath,{pkg}"], check=True)
     r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0 and r.stdout.startswith("PASS"), r.stdout + r.stderr
+
+
+@pytest.mark.parametrize("level", LEVELS)
+def test_slot_form_kernel_runs_after_ssa_construction(gpu, level):
+    n = 1000
+    out = np.full(n + 8, -7, np.int32)
+    gpu.cpu_launch(emitted(gpu, kb.load("slot_form_sum"), "slot_form_sum", level), [out, b.i32(n)], 1024)
+    assert np.array_equal(out[:n], np.arange(n) + n * (n - 1) // 2) and np.all(out[n:] == -7)

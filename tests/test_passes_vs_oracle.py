@@ -96,3 +96,45 @@ def test_register_estimate_bounds_the_unroll(ptx):
     line = next(l for l in text.splitlines() if l.startswith("// kernel vadd_i32"))
     est = int(line.split("est_regs=")[1].split()[0])
     assert est <= 64 and "unroll=2" in line
+
+
+def test_construct_ssa_promotes_front_end_slots(ptx):
+    # crates/basalt-passes/src/ssa.rs:4-10: local and param slots used only as load/store addresses
+    # become SSA values and phis; results under the oracle model are unchanged.
+    src = kb.load("slot_form_sum")
+    for level in (0, 2):
+        opt = ptx.optimized_bir(src, b.EmitOpts(opt_level=level))
+        assert "ptr.local" not in opt and "ptr.param" not in opt and opt.count("phi i32") == 3
+        for n, threads in [(10, 16), (0, 4), (-3, 4), (5, 3), (33, 64)]:
+            o0 = np.full(70, -7, np.int32); o1 = o0.copy()
+            run_kernel(src, "slot_form_sum", [o0, n], threads)
+            run_kernel(opt, "slot_form_sum", [o1, n], threads)
+            assert np.array_equal(o0, o1), (level, n, threads)
+    text = ptx.emit(src).text
+    assert ".local" not in text
+
+
+def test_shared_slots_and_address_taken_slots_stay_in_memory(ptx):
+    from basalt_b200.birasm import assemble
+    src = assemble("""module {
+  shared_mem_bytes 0
+  target_dtypes i32
+
+  func @k(ptr.global, i32) -> void {
+  entry:
+    %s = const.i ptr.shared 0
+    store i32 ptr.shared %s, %arg1, align 4
+    barrier
+    %v = load i32 ptr.shared %s, align 4
+    %l = const.i ptr.local 65536
+    %eight = const.i i64 0
+    %l2 = add ptr.local %l, %eight
+    store i32 ptr.local %l2, %v, align 4
+    %w = load i32 ptr.local %l, align 4
+    store i32 ptr.global %arg0, %w, align 4
+    ret
+  }
+}
+""")
+    opt = ptx.optimized_bir(src, b.EmitOpts(opt_level=0))
+    assert "ptr.shared" in opt and "ptr.local" in opt   # CTA-visible memory and an indexed local are not SSA values
