@@ -2,9 +2,9 @@
 //
 // FP32-pipe bound: 128x128 CTA tile, K slab of 16, 256 threads each owning an 8x8 block of C as
 // four 4x4 quadrants so that every shared-memory read is a conflict-free 16-byte access; the next
-// K slab is fetched from global memory into registers while the current one is multiplied, then
-// stored into the other half of a double buffer.  Per K step a thread issues 4 LDS.128 for 64
-// FFMA.  Two CTAs are resident per SM (128 registers/thread, 32 KB shared each).
+// K slab is copied from global memory straight into the other half of a shared-memory double
+// buffer with cp.async while the current one is multiplied (no staging registers).  Per K step a
+// thread issues 4 LDS.128 for 64 FFMA.  Two CTAs are resident per SM (32 KB shared each).
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -12,6 +12,13 @@
 #include "common.cuh"
 
 namespace {
+
+template <int BYTES>
+__device__ __forceinline__ void cp_async(void* smem_dst, const void* gmem_src) {
+    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    if constexpr (BYTES == 16) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(gmem_src) : "memory");
+    else asm volatile("cp.async.ca.shared.global [%0], [%1], %2;" ::"r"(dst), "l"(gmem_src), "n"(BYTES) : "memory");
+}
 
 constexpr int BM = 128, BN = 128, BK = 16, THREADS = 256;
 
@@ -34,19 +41,18 @@ __global__ void __launch_bounds__(THREADS, 2) sgemm_f32_kernel(const float* __re
     const float* Bg0 = B + (size_t)b_row * N + n0 + b_col;
     const float* Bg1 = Bg0 + (size_t)8 * N;
     const size_t b_step = (size_t)BK * N;
-    float4 ra0, ra1, rb0, rb1;
-    auto fetch = [&]() {
-        ra0 = *reinterpret_cast<const float4*>(Ag0);
-        ra1 = *reinterpret_cast<const float4*>(Ag1);
-        rb0 = *reinterpret_cast<const float4*>(Bg0);
-        rb1 = *reinterpret_cast<const float4*>(Bg1);
+    // global -> shared with cp.async, no staging registers: A lands transposed as eight 4-byte
+    // copies per thread, B as two 16-byte copies; one commit group per K slab.
+    auto copy_slab = [&](int buf) {
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            cp_async<4>(&As[buf][a_col + c][a_row], Ag0 + c);
+            cp_async<4>(&As[buf][a_col + c][a_row + 64], Ag1 + c);
+        }
+        cp_async<16>(&Bs[buf][b_row][b_col], Bg0);
+        cp_async<16>(&Bs[buf][b_row + 8][b_col], Bg1);
+        asm volatile("cp.async.commit_group;" ::: "memory");
         Ag0 += BK; Ag1 += BK; Bg0 += b_step; Bg1 += b_step;
-    };
-    auto stash = [&](int buf) {
-        As[buf][a_col + 0][a_row] = ra0.x; As[buf][a_col + 1][a_row] = ra0.y; As[buf][a_col + 2][a_row] = ra0.z; As[buf][a_col + 3][a_row] = ra0.w;
-        As[buf][a_col + 0][a_row + 64] = ra1.x; As[buf][a_col + 1][a_row + 64] = ra1.y; As[buf][a_col + 2][a_row + 64] = ra1.z; As[buf][a_col + 3][a_row + 64] = ra1.w;
-        *reinterpret_cast<float4*>(&Bs[buf][b_row][b_col]) = rb0;
-        *reinterpret_cast<float4*>(&Bs[buf][b_row + 8][b_col]) = rb1;
     };
 
     float acc[8][8];
@@ -55,13 +61,13 @@ __global__ void __launch_bounds__(THREADS, 2) sgemm_f32_kernel(const float* __re
 #pragma unroll
         for (int j = 0; j < 8; j++) acc[i][j] = 0.0f;
 
-    fetch();
-    stash(0);
+    copy_slab(0);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
     const int nk = K / BK;
     for (int kb = 0; kb < nk; kb++) {
         const int buf = kb & 1;
-        if (kb + 1 < nk) fetch();
+        if (kb + 1 < nk) copy_slab(buf ^ 1);   // lands while this slab is multiplied
 #pragma unroll
         for (int k = 0; k < BK; k++) {
             const float4 a0 = *reinterpret_cast<const float4*>(&As[buf][k][ty * 4]);
@@ -75,10 +81,8 @@ __global__ void __launch_bounds__(THREADS, 2) sgemm_f32_kernel(const float* __re
 #pragma unroll
                 for (int j = 0; j < 8; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
         }
-        if (kb + 1 < nk) {
-            stash(buf ^ 1);
-            __syncthreads();
-        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
     }
 #pragma unroll
     for (int i = 0; i < 8; i++) {

@@ -1,7 +1,8 @@
 #!/usr/bin/env python
 """Benchmark of the Basalt sm_100a device path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--no-others]
+    python bench.py --profile {vadd_i32,helper_chain,sgemm_f32,matmul_f16} [--size S]     (small cases for ncu)
 
 Headline workload (N=1 and per rank at N>1): the max_i32 reduction over 2^28 int32 (1 GiB), the
 benchmark configuration the metric is quoted on.  A step is one pass over the rank's batch: one
