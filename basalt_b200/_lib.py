@@ -87,6 +87,7 @@ def _load() -> C.CDLL:
         "basalt_k_vadd_i32": (C.c_int, [vp, vp, vp, i64, vp]),
         "basalt_k_max_i32": (C.c_int, [vp, i64, vp, vp]),
         "basalt_k_helper_chain_u32": (C.c_int, [vp, vp, i64, vp]),
+        "basalt_k_imad_peak": (C.c_int, [vp, i64, C.c_int, P(C.c_int64), vp]),
         "basalt_k_sgemm_f32": (C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, vp]),
         "basalt_k_matmul_f16": (C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, vp, vp]),
     }

@@ -105,6 +105,24 @@ __global__ void __launch_bounds__(kThreads) helper_chain_scalar_kernel(const uin
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += T) out[i] = chain_step<0>(in[i]);
 }
 
+// INT32 pipe peak: eight independent multiply-add chains per thread, nothing else in the loop.
+__global__ void __launch_bounds__(kThreads) imad_peak_kernel(uint32_t* out, int iters) {
+    uint32_t x[8];
+    const uint32_t m = 2654435761u + threadIdx.x, a = blockIdx.x * 977u + 12345u;
+#pragma unroll
+    for (int k = 0; k < 8; k++) x[k] = threadIdx.x * 31u + k;
+    for (int i = 0; i < iters; i++) {
+#pragma unroll
+        for (int r = 0; r < 4; r++)
+#pragma unroll
+            for (int k = 0; k < 8; k++) x[k] = x[k] * m + a;
+    }
+    uint32_t s = 0;
+#pragma unroll
+    for (int k = 0; k < 8; k++) s ^= x[k];
+    out[(size_t)blockIdx.x * blockDim.x + threadIdx.x] = s;
+}
+
 bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
 
 // CTAs: enough to cover `work` thread-steps, at most one full wave of resident CTAs (SM count x
@@ -149,6 +167,15 @@ int basalt_k_helper_chain_u32(const uint32_t* in, uint32_t* out, int64_t n, void
         helper_chain_kernel<<<grid_for(helper_chain_kernel, (n4 + 1) / 2 + 4), kThreads, 0, s>>>((const uint4*)in, (uint4*)out, n4, in, out, n);
     } else helper_chain_scalar_kernel<<<grid_for(helper_chain_scalar_kernel, n), kThreads, 0, s>>>(in, out, n);
     return basalt_k::record(cudaGetLastError(), "helper_chain_u32");
+}
+
+int basalt_k_imad_peak(uint32_t* out, int64_t out_elems, int iters, int64_t* imads, void* stream) {
+    int grid = basalt_k::sm_count() * basalt_k::resident_ctas(imad_peak_kernel, kThreads);
+    if ((int64_t)grid * kThreads > out_elems) grid = (int)(out_elems / kThreads);
+    if (grid < 1 || iters < 1) return basalt_k::record_msg(1, "imad_peak", "output buffer too small");
+    imad_peak_kernel<<<grid, kThreads, 0, (cudaStream_t)stream>>>(out, iters);
+    if (imads) *imads = (int64_t)grid * kThreads * iters * 32;
+    return basalt_k::record(cudaGetLastError(), "imad_peak");
 }
 
 }  // extern "C"

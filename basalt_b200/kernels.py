@@ -34,6 +34,13 @@ def helper_chain_u32(inp, out, n: int, stream=None):
     _check(lib.basalt_k_helper_chain_u32(_p(inp), _p(out), n, C.c_void_p(stream)))
 
 
+def imad_peak(out, out_elems: int, iters: int, stream=None) -> int:
+    """Launches the INT32-pipe microbenchmark; returns the number of multiply-adds it executes."""
+    n = C.c_int64()
+    _check(lib.basalt_k_imad_peak(_p(out), out_elems, iters, C.byref(n), C.c_void_p(stream)))
+    return n.value
+
+
 def sgemm_f32(A, B, Cm, M: int, N: int, K: int, stream=None):
     _check(lib.basalt_k_sgemm_f32(_p(A), _p(B), _p(Cm), M, N, K, C.c_void_p(stream)))
 

@@ -182,8 +182,17 @@ def others_summary(ctx, torch, stream, peaks_hbm, peaks_tf):
     fn = emitted(kb.helper_chain(), "helper_chain")
     ms_e = timed(lambda: fn.launch((n + 255) // 256, 256, 0, [dp(x), dp(y), b.i32(n)], stream=stream), 20)
     ms_h = timed(lambda: kernels.helper_chain_u32(x.data_ptr(), y.data_ptr(), n, stream), 20)
+    scratch = torch.empty(1 << 22, dtype=torch.int32, device="cuda")
+    imads = [0]
+
+    def peak():
+        imads[0] = kernels.imad_peak(scratch.data_ptr(), scratch.numel(), 2000, stream)
+    ms_p = timed(peak, 5)
+    imad_peak_gops = 2.0 * imads[0] / ms_p / 1e6
     out["helper_chain_n2^26"] = {"emitted_gops": 64.0 * n / ms_e / 1e6, "handwritten_gops": 64.0 * n / ms_h / 1e6,
-                                 "emitted_gbs": 8.0 * n / ms_e / 1e6, "handwritten_gbs": 8.0 * n / ms_h / 1e6}
+                                 "emitted_gbs": 8.0 * n / ms_e / 1e6, "handwritten_gbs": 8.0 * n / ms_h / 1e6,
+                                 "int32_pipe_peak_gops_measured": imad_peak_gops, "emitted_frac_of_int32_peak": 64.0 * n / ms_e / 1e6 / imad_peak_gops,
+                                 "emitted_frac_of_hbm_peak": 8.0 * n / ms_e / 1e6 / peaks_hbm}
     del x, y
     # SGEMM 4096^3
     M = N = K = 4096

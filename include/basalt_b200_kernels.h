@@ -34,6 +34,12 @@ int basalt_k_max_i32(const int32_t *x, int64_t n, int32_t *out, void *stream);
  * tests/kernels/device_helper_chain.cu (there 3 levels) at depth 32. */
 int basalt_k_helper_chain_u32(const uint32_t *in, uint32_t *out, int64_t n, void *stream);
 
+/* Measures the INT32 pipe: one wave of CTAs, each thread running `iters` x 32 independent
+ * multiply-adds (mod 2^32). *imads receives the number of multiply-adds executed; `out` (at least
+ * out_elems uint32) receives one word per thread so the work cannot be optimised away. The
+ * roofline denominator for the helper-chain workload; no counterpart in the reference. */
+int basalt_k_imad_peak(uint32_t *out, int64_t out_elems, int iters, int64_t *imads, void *stream);
+
 /* C[MxN] = A[MxK] * B[KxN], row-major fp32, FFMA only (no TF32): the workload of
  * examples/cpu_launch_tiled_sgemm.c (there 32^3 with a C addend). M, N multiples of 128, K of 16. */
 int basalt_k_sgemm_f32(const float *A, const float *B, float *C, int M, int N, int K, void *stream);
