@@ -68,14 +68,23 @@ __global__ void __launch_bounds__(THREADS, 2) sgemm_f32_kernel(const float* __re
     for (int kb = 0; kb < nk; kb++) {
         const int buf = kb & 1;
         if (kb + 1 < nk) copy_slab(buf ^ 1);   // lands while this slab is multiplied
+        // register double buffer for the fragments: step k+1 is read from shared memory while step k is multiplied
+        float4 fa[2][2], fb[2][2];
+        fa[0][0] = *reinterpret_cast<const float4*>(&As[buf][0][ty * 4]);
+        fa[0][1] = *reinterpret_cast<const float4*>(&As[buf][0][ty * 4 + 64]);
+        fb[0][0] = *reinterpret_cast<const float4*>(&Bs[buf][0][tx * 4]);
+        fb[0][1] = *reinterpret_cast<const float4*>(&Bs[buf][0][tx * 4 + 64]);
 #pragma unroll
         for (int k = 0; k < BK; k++) {
-            const float4 a0 = *reinterpret_cast<const float4*>(&As[buf][k][ty * 4]);
-            const float4 a1 = *reinterpret_cast<const float4*>(&As[buf][k][ty * 4 + 64]);
-            const float4 b0 = *reinterpret_cast<const float4*>(&Bs[buf][k][tx * 4]);
-            const float4 b1 = *reinterpret_cast<const float4*>(&Bs[buf][k][tx * 4 + 64]);
-            const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-            const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+            const int cur = k & 1, nxt = cur ^ 1;
+            if (k + 1 < BK) {
+                fa[nxt][0] = *reinterpret_cast<const float4*>(&As[buf][k + 1][ty * 4]);
+                fa[nxt][1] = *reinterpret_cast<const float4*>(&As[buf][k + 1][ty * 4 + 64]);
+                fb[nxt][0] = *reinterpret_cast<const float4*>(&Bs[buf][k + 1][tx * 4]);
+                fb[nxt][1] = *reinterpret_cast<const float4*>(&Bs[buf][k + 1][tx * 4 + 64]);
+            }
+            const float a[8] = {fa[cur][0].x, fa[cur][0].y, fa[cur][0].z, fa[cur][0].w, fa[cur][1].x, fa[cur][1].y, fa[cur][1].z, fa[cur][1].w};
+            const float b[8] = {fb[cur][0].x, fb[cur][0].y, fb[cur][0].z, fb[cur][0].w, fb[cur][1].x, fb[cur][1].y, fb[cur][1].z, fb[cur][1].w};
 #pragma unroll
             for (int i = 0; i < 8; i++)
 #pragma unroll
