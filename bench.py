@@ -10,7 +10,7 @@ launch of the emitted sm_100a kernel through the C-ABI runtime, plus, at N>1, th
 allreduce(max) of the partial maxima over this library's NCCL communicator.  Scaling is weak: every
 rank owns a 2^28-element contiguous shard of an N*2^28-element array.
 
-One JSON line is printed by rank 0; see DESIGN.md for the meaning of each key.  `--impl reference`
+One JSON line is printed by rank 0 (keys are described beside the code that fills them).  `--impl reference`
 times the reference's CPU launch path (the C restatement under oracle/, one thread, like the
 reference's emitted x86 loop) on the same workload instead.
 """
@@ -415,7 +415,7 @@ def main():
     if rank == 0:
         achieved = 4.0 * n / (kernel_ms * 1e-3) / 1e9
         # DRAM bytes per launch from the ncu capture of this kernel on a 2^26-element case
-        # (profiles/max_i32_emitted_n2p26.md): reads 268.443 MB for 268.435 MB algorithmic, plus about
+        # (summary kept under profiles/): reads 268.443 MB for 268.435 MB algorithmic, plus about
         # 4.5 MB of unrelated write-back; reads grow in proportion to the elements, so scale them.
         traffic = 4.0 * n * (268.443 / 268.435) + 4.5e6
         line = {
