@@ -274,6 +274,41 @@ def profile_one(args):
     print(json.dumps({"profiling": name, "size": size, "launches_each": reps}), flush=True)
 
 
+def sharded_matmul(ctx, torch, group, comm, stream, peak_tf):
+    """Config 5 across the ranks (strong scaling): each rank owns M/world rows of A and C, B is
+    replicated; the emitted tcgen05 kernel computes the local rows, then the row blocks are
+    allgathered over this library's NCCL communicator. Device-resident, CUDA events, max over ranks."""
+    import basalt_b200 as b
+    from basalt_b200 import kernels_bir as kb
+    M = N = K = 8192
+    r0, r1 = group.shard(M, 128)
+    Ml = r1 - r0
+    A = (torch.randn(Ml, K, device="cuda") * 0.1).half(); B = (torch.randn(K, N, device="cuda") * 0.1).half()
+    Cl = torch.empty(Ml, N, device="cuda", dtype=torch.float16); C = torch.empty(M, N, device="cuda", dtype=torch.float16)
+    fn = ctx.load_module(b.Ptx().emit(kb.matmul_f16(Ml, N, K)).text).get_function("matmul_kernel")
+    go = fn.bind((N // 128, Ml // 128), 128, 0, [b.ptr(A.data_ptr()), b.ptr(B.data_ptr()), b.ptr(Cl.data_ptr())], stream=stream)
+
+    def timed(step, reps):
+        for _ in range(3):
+            step()
+        group.barrier(); torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            step()
+        e1.record(); torch.cuda.synchronize(); group.barrier()
+        return group.max_float(e0.elapsed_time(e1)) / reps
+
+    def both():
+        go()
+        comm.allgather(Cl.data_ptr(), C.data_ptr(), Ml * N * 2, stream)
+    ms_compute = timed(go, 10)
+    ms_both = timed(both, 10)
+    fl = 2.0 * M * N * K
+    return {"rows_per_gpu": Ml, "compute_ms": ms_compute, "compute_plus_allgather_ms": ms_both, "tflops_total_compute_only": fl / ms_compute / 1e9,
+            "tflops_total_with_allgather": fl / ms_both / 1e9, "status": fn.status(), "scaling": "strong (8192^3 split by rows)"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -404,6 +439,12 @@ def main():
         parity = parity and (world > 1 or r_cpu == expect)
         cpu = {"value": 4.0 * sample_n / t_cpu / 1e9, "unit": "GB/s", "cores": 1, "kind": "port",
                "sample": "3 full passes over this rank's int32 shard (best), the oracle's sequential atomic-max loop, one thread as in the reference"}
+    sharded = None
+    if world > 1 and not args.no_others and 8192 % (128 * world) == 0:
+        try:
+            sharded = sharded_matmul(ctx, torch, group, comm, stream, peak_tf)
+        except Exception as e:   # noqa: BLE001
+            sharded = {"error": str(e)[:300]}
     if rank == 0:
         if world == 1 and not args.no_others:
             try:
@@ -439,6 +480,8 @@ def main():
         }
         if others is not None:
             line["others"] = others
+        if sharded is not None:
+            line["matmul_f16_8192_sharded"] = sharded
         print(json.dumps(line), flush=True)
     if comm is not None:
         comm.destroy()
