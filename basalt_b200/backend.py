@@ -88,3 +88,10 @@ class Ptx:
 def roundtrip(bir: str) -> str:
     """parse then print (crates/basalt-bir/src/lib.rs:79-85)."""
     return _text_call(lib.basalt_b200_roundtrip, bir, False)
+
+
+def compile_cuda(source: str) -> str:
+    """CUDA-C subset -> slot-form BIR text: the front half of the reference CLI's CUDA-C lane
+    (crates/basalt-cli/src/main.rs:286-327; crates/basalt-frontend-c, crates/basalt-sema/src/lower.rs).
+    Raises Diag with the reference's front-end codes (E200-E202, E300-E304, E308)."""
+    return _text_call(lib.basalt_b200_compile_cuda, source, False)

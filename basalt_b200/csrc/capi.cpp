@@ -5,6 +5,7 @@
 
 #include "../../include/basalt_b200.h"
 #include "emit.hpp"
+#include "frontend_c.hpp"
 
 using namespace basalt;
 
@@ -92,6 +93,16 @@ int basalt_b200_roundtrip(const char* bir, size_t len, char** bir_out, size_t* b
     if (bir_out) *bir_out = nullptr;
     Module m;
     if (!parse_or_diag(bir, len, &m, diag_out)) return 1;
+    if (bir_out) *bir_out = dup_out(print_module(m), bir_len);
+    return 0;
+}
+
+int basalt_b200_compile_cuda(const char* src, size_t len, char** bir_out, size_t* bir_len, basalt_diag* diag_out) {
+    if (bir_out) *bir_out = nullptr;
+    if (!src) { fill_diag(diag_out, "E500", "null input"); return 1; }
+    Module m;
+    Diag dg;
+    if (!compile_cuda_c(src, len, &m, &dg)) { fill_diag(diag_out, dg.code, dg.arg); return 1; }
     if (bir_out) *bir_out = dup_out(print_module(m), bir_len);
     return 0;
 }

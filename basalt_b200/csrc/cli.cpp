@@ -1,8 +1,9 @@
-// basalt-b200: the `basalt --nvidia-ptx <file.bir> [-o out.ptx]` arm of the reference CLI
-// (crates/basalt-cli/src/main.rs:511-559) for the sm_100a backend.  Reads BIR text, writes PTX to
-// stdout or to the -o path (main.rs:553-558); a refusal prints "<E-code>: <message>" on stderr and
-// exits 1, as the reference renders a Diag (main.rs:894-900).  Only .bir input: the CUDA-C and
-// Triton front ends are not part of this project.
+// basalt-b200: the `basalt --nvidia-ptx <file> [-o out.ptx]` arm of the reference CLI
+// (crates/basalt-cli/src/main.rs:511-559) for the sm_100a backend.  Reads BIR text (.bir) or a
+// CUDA-C source in the supported subset (.cu), writes PTX to stdout or to the -o path
+// (main.rs:553-558); a refusal prints "<E-code>: <message>" on stderr and exits 1, as the reference
+// renders a Diag (main.rs:894-900).  `--emit-bir file.cu` stops after the front end, like the
+// reference's flag of that name (main.rs:286-327).  There is no Triton front end here.
 #include <cstdio>
 #include <cstring>
 #include <fstream>
@@ -14,7 +15,9 @@
 
 static int usage() {
     std::cerr << "usage: basalt-b200 --nvidia-ptx <file.bir> [-o <out.ptx>] [-O0|-O2]\n"
-                 "       basalt-b200 --ir <file.bir>        (print the module as the backend lowers it)\n";
+                 "       basalt-b200 --nvidia-ptx <file.cu>  [-o <out.ptx>] [-O0|-O2]\n"
+                 "       basalt-b200 --emit-bir <file.cu>   (front end only: slot-form BIR)\n"
+                 "       basalt-b200 --ir <file.bir|file.cu> (print the module as the backend lowers it)\n";
     return 2;
 }
 
@@ -23,7 +26,7 @@ int main(int argc, char** argv) {
     basalt_emit_opts opts{nullptr, 2, nullptr, 0};
     for (int i = 1; i < argc; i++) {
         std::string a = argv[i];
-        if (a == "--nvidia-ptx" || a == "--ir") {
+        if (a == "--nvidia-ptx" || a == "--ir" || a == "--emit-bir") {
             if (!mode.empty()) { std::cerr << "E103: conflicting flags: " << mode << " and " << a << "\n"; return 1; }
             mode = a;
         } else if (a == "-o") {
@@ -35,7 +38,10 @@ int main(int argc, char** argv) {
         else in = a;
     }
     if (mode.empty() || in.empty()) return usage();
-    if (in.size() < 4 || in.substr(in.size() - 4) != ".bir") { std::cerr << "E102: invalid argument for flag " << mode << ": only .bir input is supported\n"; return 1; }
+    const bool is_bir = in.size() >= 4 && in.substr(in.size() - 4) == ".bir";
+    const bool is_cu = in.size() >= 3 && in.substr(in.size() - 3) == ".cu";
+    if (!is_bir && !is_cu) { std::cerr << "E102: invalid argument for flag " << mode << ": input must be .bir or .cu\n"; return 1; }
+    if (mode == "--emit-bir" && !is_cu) { std::cerr << "E102: invalid argument for flag --emit-bir: input must be .cu\n"; return 1; }
     std::ifstream f(in, std::ios::binary);
     if (!f) { std::cerr << "E500: I/O error reading " << in << ": cannot open\n"; return 1; }
     std::stringstream ss;
@@ -44,6 +50,22 @@ int main(int argc, char** argv) {
     char* result = nullptr;
     size_t len = 0;
     basalt_diag d;
+    if (is_cu) {
+        char* bir = nullptr;
+        size_t blen = 0;
+        if (basalt_b200_compile_cuda(text.data(), text.size(), &bir, &blen, &d) != 0) { std::cerr << d.code << ": " << d.message << "\n"; return 1; }
+        text.assign(bir, blen);
+        basalt_b200_free(bir);
+        if (mode == "--emit-bir") {
+            if (out.empty()) std::cout << text;
+            else {
+                std::ofstream o(out, std::ios::binary);
+                if (!o) { std::cerr << "E500: I/O error reading " << out << ": cannot open for writing\n"; return 1; }
+                o << text;
+            }
+            return 0;
+        }
+    }
     int rc = mode == "--ir" ? basalt_b200_optimize(text.data(), text.size(), &opts, &result, &len, &d)
                             : basalt_b200_emit(text.data(), text.size(), &opts, &result, &len, &d);
     if (rc != 0) { std::cerr << d.code << ": " << d.message << "\n"; return 1; }

@@ -2,6 +2,9 @@
 #include "passes.hpp"
 
 #include <algorithm>
+#include <climits>
+#include <cstdio>
+#include <cstring>
 #include <functional>
 #include <map>
 #include <set>
@@ -198,6 +201,102 @@ void simplify_cfg(Function& f) {
             changed = true;
         }
         if (changed) continue;
+        // if-convert a diamond whose two arms are empty: the phis of the join become selects
+        for (uint32_t b = 0; b < f.blocks.size() && !changed; b++) {
+            if (!reach[b]) continue;
+            Term& t = f.blocks[b].term;
+            if (t.kind != Term::CondBr || t.t == t.f) continue;
+            const uint32_t T = t.t, E = t.f;
+            if (T == 0 || E == 0 || T == b || E == b) continue;
+            const Block &tb = f.blocks[T], &eb = f.blocks[E];
+            if (!tb.insts.empty() || !eb.insts.empty() || tb.term.kind != Term::Br || eb.term.kind != Term::Br || tb.term.t != eb.term.t) continue;
+            if (npred[T] != 1 || npred[E] != 1) continue;
+            const uint32_t m = tb.term.t;
+            if (m == T || m == E || m == b) continue;
+            bool ok = true;
+            for (uint32_t id : f.blocks[m].insts) {
+                const Inst& in = f.insts[id];
+                if (in.op != Opc::Phi) continue;
+                int nt = 0, ne = 0;
+                for (uint32_t pb : in.phi_blocks) { nt += pb == T; ne += pb == E; if (pb == b) ok = false; }
+                if (nt != 1 || ne != 1) ok = false;
+            }
+            if (!ok) continue;
+            const Val cond = t.val;
+            std::vector<uint32_t> phis;
+            for (uint32_t id : f.blocks[m].insts) if (f.insts[id].op == Opc::Phi) phis.push_back(id);
+            for (uint32_t id : phis) {
+                Val vt, ve;
+                std::vector<Val> ops;
+                std::vector<uint32_t> pbs;
+                for (size_t i = 0; i < f.insts[id].ops.size(); i++) {
+                    uint32_t pb = f.insts[id].phi_blocks[i];
+                    if (pb == T) vt = f.insts[id].ops[i];
+                    else if (pb == E) ve = f.insts[id].ops[i];
+                    else { ops.push_back(f.insts[id].ops[i]); pbs.push_back(pb); }
+                }
+                Val chosen = vt;
+                if (vt != ve) {
+                    Inst sel;
+                    sel.op = Opc::Select;
+                    sel.ty = f.insts[id].ty;
+                    sel.ops = {cond, vt, ve};
+                    uint32_t sid = (uint32_t)f.insts.size();
+                    f.insts.push_back(sel);
+                    f.blocks[b].insts.push_back(sid);
+                    chosen = Val::V(sid);
+                }
+                ops.push_back(chosen);
+                pbs.push_back(b);
+                f.insts[id].ops = ops;
+                f.insts[id].phi_blocks = pbs;
+            }
+            Term& bt = f.blocks[b].term;
+            bt.kind = Term::Br;
+            bt.has_val = false;
+            bt.t = m;
+            changed = true;
+        }
+        if (changed) continue;
+        // thread empty forwarding blocks: p -> e -> s becomes p -> s
+        for (uint32_t e = 1; e < f.blocks.size() && !changed; e++) {
+            if (!reach[e] || !f.blocks[e].insts.empty()) continue;
+            const Term et = f.blocks[e].term;
+            if (et.kind != Term::Br || et.t == e) continue;
+            const uint32_t s = et.t;
+            bool s_has_phi = false;
+            for (uint32_t id : f.blocks[s].insts) s_has_phi |= f.insts[id].op == Opc::Phi;
+            std::vector<uint32_t> preds;
+            bool ok = true;
+            for (uint32_t p = 0; p < f.blocks.size(); p++) {
+                if (!reach[p]) continue;
+                successors(f.blocks[p].term, succ);
+                if (std::find(succ.begin(), succ.end(), e) == succ.end()) continue;
+                if (s_has_phi && std::find(succ.begin(), succ.end(), s) != succ.end()) ok = false;   // p would reach s twice
+                preds.push_back(p);
+            }
+            if (!ok || preds.empty()) continue;
+            for (uint32_t p : preds) {
+                Term& t = f.blocks[p].term;
+                if (t.kind != Term::Ret && t.t == e) t.t = s;
+                if (t.kind == Term::CondBr && t.f == e) t.f = s;
+                for (auto& c : t.cases) if (c.second == e) c.second = s;
+                if (t.kind == Term::CondBr && t.t == t.f) { t.kind = Term::Br; t.has_val = false; }
+            }
+            for (uint32_t id : f.blocks[s].insts) {
+                Inst& in = f.insts[id];
+                if (in.op != Opc::Phi) continue;
+                for (size_t i = 0; i < in.phi_blocks.size(); i++) {
+                    if (in.phi_blocks[i] != e) continue;
+                    Val v = in.ops[i];
+                    in.phi_blocks[i] = preds[0];
+                    for (size_t k = 1; k < preds.size(); k++) { in.phi_blocks.push_back(preds[k]); in.ops.push_back(v); }
+                    break;
+                }
+            }
+            changed = true;
+        }
+        if (changed) continue;
         // drop unreachable blocks
         bool any_dead = false;
         for (uint32_t b = 0; b < f.blocks.size(); b++) any_dead |= !reach[b];
@@ -226,6 +325,279 @@ void simplify_cfg(Function& f) {
                 in.phi_blocks = pbs;
             }
     }
+}
+
+// ---- constant folding ------------------------------------------------------------------------
+// Folds with the arithmetic of the CPU oracle (crates/basalt-x86/src/oracle.rs:1530-1653): integers
+// wrap at their declared width, division and remainder are signed, floats round to nearest at
+// their own width and are never fused.  A fold that the oracle and the device could disagree on
+// (division by zero, INT_MIN / -1, a shift count outside [0, width), anything on f16) is left alone.
+namespace {
+int64_t wrap_to(Scalar sc, int64_t v) {
+    switch (sc) {
+        case Scalar::I1: return v & 1;
+        case Scalar::I8: return (int64_t)(int8_t)(uint8_t)v;
+        case Scalar::I16: return (int64_t)(int16_t)(uint16_t)v;
+        case Scalar::I32: return (int64_t)(int32_t)(uint32_t)v;
+        default: return v;
+    }
+}
+uint64_t zext_of(Scalar sc, int64_t v) {
+    unsigned b = scalar_bits(sc);
+    return b >= 64 ? (uint64_t)v : ((uint64_t)v & ((1ull << b) - 1));
+}
+double round_to(Scalar sc, double v) { return sc == Scalar::F32 ? (double)(float)v : v; }
+const Inst* const_def(const Function& f, Val v) {
+    if (v.param) return nullptr;
+    const Inst& in = f.insts[v.idx];
+    return in.op == Opc::ConstI || in.op == Opc::ConstF ? &in : nullptr;
+}
+void make_const_i(Inst& in, int64_t v) {
+    Ty t = in.ty;
+    in = Inst{};
+    in.op = Opc::ConstI;
+    in.ty = t;
+    in.imm = t.kind == Ty::Sc ? wrap_to(t.sc, v) : v;
+}
+void make_const_f(Inst& in, double v) {
+    Ty t = in.ty;
+    in = Inst{};
+    in.op = Opc::ConstF;
+    in.ty = t;
+    in.fimm = v;
+}
+}  // namespace
+
+int fold_constants(Function& f) {
+    int folded = 0;
+    for (bool again = true; again;) {
+        again = false;
+        for (auto& blk : f.blocks) {
+            for (uint32_t id : blk.insts) {
+                Inst& in = f.insts[id];
+                if (in.ty.is_vec()) continue;
+                if (in.op == Opc::Bin && in.ty.kind == Ty::Sc) {
+                    const Inst *a = const_def(f, in.ops[0]), *b = const_def(f, in.ops[1]);
+                    BinOp op = (BinOp)in.sub;
+                    Scalar sc = in.ty.sc;
+                    if (in.ty.is_float()) {
+                        if (!a || !b || sc == Scalar::F16 || a->op != Opc::ConstF || b->op != Opc::ConstF) continue;
+                        double x = round_to(sc, a->fimm), y = round_to(sc, b->fimm), r;
+                        if (op == BinOp::FAdd) r = sc == Scalar::F32 ? (double)((float)x + (float)y) : x + y;
+                        else if (op == BinOp::FSub) r = sc == Scalar::F32 ? (double)((float)x - (float)y) : x - y;
+                        else if (op == BinOp::FMul) r = sc == Scalar::F32 ? (double)((float)x * (float)y) : x * y;
+                        else if (op == BinOp::FDiv) r = sc == Scalar::F32 ? (double)((float)x / (float)y) : x / y;
+                        else continue;
+                        make_const_f(in, r);
+                        folded++; again = true;
+                        continue;
+                    }
+                    if (a && b && a->op == Opc::ConstI && b->op == Opc::ConstI) {
+                        int64_t x = wrap_to(sc, a->imm), y = wrap_to(sc, b->imm), r;
+                        const int bits = (int)scalar_bits(sc);
+                        const int64_t min = bits >= 64 ? INT64_MIN : -(1ll << (bits - 1));
+                        switch (op) {
+                            case BinOp::Add: r = (int64_t)((uint64_t)x + (uint64_t)y); break;
+                            case BinOp::Sub: r = (int64_t)((uint64_t)x - (uint64_t)y); break;
+                            case BinOp::Mul: r = (int64_t)((uint64_t)x * (uint64_t)y); break;
+                            case BinOp::Div: if (y == 0 || (x == min && y == -1)) continue; r = x / y; break;
+                            case BinOp::Rem: if (y == 0 || (x == min && y == -1)) continue; r = x % y; break;
+                            case BinOp::And: r = x & y; break;
+                            case BinOp::Or: r = x | y; break;
+                            case BinOp::Xor: r = x ^ y; break;
+                            case BinOp::Shl: if (y < 0 || y >= bits) continue; r = (int64_t)(zext_of(sc, x) << y); break;
+                            case BinOp::LShr: if (y < 0 || y >= bits) continue; r = (int64_t)(zext_of(sc, x) >> y); break;
+                            case BinOp::AShr: if (y < 0 || y >= bits) continue; r = x >> y; break;
+                            default: continue;
+                        }
+                        make_const_i(in, r);
+                        folded++; again = true;
+                        continue;
+                    }
+                    // identities with one constant operand (integers only: x + 0.0 is not x for x = -0.0)
+                    auto is_k = [&](const Inst* c, int64_t k) { return c && c->op == Opc::ConstI && wrap_to(sc, c->imm) == k; };
+                    Val keep;
+                    bool have = false;
+                    if ((op == BinOp::Add || op == BinOp::Or || op == BinOp::Xor) && is_k(a, 0)) { keep = in.ops[1]; have = true; }
+                    else if ((op == BinOp::Add || op == BinOp::Sub || op == BinOp::Or || op == BinOp::Xor || op == BinOp::Shl || op == BinOp::LShr || op == BinOp::AShr) && is_k(b, 0)) { keep = in.ops[0]; have = true; }
+                    else if (op == BinOp::Mul && is_k(b, 1)) { keep = in.ops[0]; have = true; }
+                    else if (op == BinOp::Mul && is_k(a, 1)) { keep = in.ops[1]; have = true; }
+                    else if (op == BinOp::Div && is_k(b, 1)) { keep = in.ops[0]; have = true; }
+                    if (have && f.val_ty(keep) == in.ty) {
+                        replace_uses(f, Val::V(id), keep);
+                        folded++;   // the instruction itself is now dead; dce removes it
+                    }
+                    continue;
+                }
+                if (in.op == Opc::ICmp && in.aux.kind == Ty::Sc) {
+                    const Inst *a = const_def(f, in.ops[0]), *b = const_def(f, in.ops[1]);
+                    Scalar sc = in.aux.sc;
+                    if (a && b && a->op == Opc::ConstI && b->op == Opc::ConstI) {
+                        int64_t x = wrap_to(sc, a->imm), y = wrap_to(sc, b->imm);
+                        uint64_t ux = zext_of(sc, x), uy = zext_of(sc, y);
+                        bool r;
+                        switch ((ICmp)in.sub) {
+                            case ICmp::Eq: r = x == y; break;
+                            case ICmp::Ne: r = x != y; break;
+                            case ICmp::Slt: r = x < y; break;
+                            case ICmp::Sle: r = x <= y; break;
+                            case ICmp::Sgt: r = x > y; break;
+                            case ICmp::Sge: r = x >= y; break;
+                            case ICmp::Ult: r = ux < uy; break;
+                            case ICmp::Ule: r = ux <= uy; break;
+                            case ICmp::Ugt: r = ux > uy; break;
+                            default: r = ux >= uy; break;
+                        }
+                        make_const_i(in, r);
+                        folded++; again = true;
+                        continue;
+                    }
+                    // `(zext b) != 0` is b: the shape the reference's sema gives every condition
+                    // (crates/basalt-sema/src/lower.rs:1894-1910)
+                    if ((ICmp)in.sub == ICmp::Ne && b && b->op == Opc::ConstI && b->imm == 0 && !in.ops[0].param) {
+                        const Inst& z = f.insts[in.ops[0].idx];
+                        if (z.op == Opc::Cast && (CastOp)z.sub == CastOp::ZExt && z.aux.is_sc(Scalar::I1)) {
+                            replace_uses(f, Val::V(id), z.ops[0]);
+                            folded++;
+                        }
+                    }
+                    continue;
+                }
+                if (in.op == Opc::Cast && in.ty.kind == Ty::Sc && in.aux.kind == Ty::Sc) {
+                    const Inst* a = const_def(f, in.ops[0]);
+                    if (!a || in.ty.sc == Scalar::F16 || in.aux.sc == Scalar::F16) continue;
+                    CastOp op = (CastOp)in.sub;
+                    if (a->op == Opc::ConstI) {
+                        int64_t x = wrap_to(in.aux.sc, a->imm);
+                        if (op == CastOp::SExt || op == CastOp::Trunc) { make_const_i(in, x); folded++; again = true; }
+                        else if (op == CastOp::ZExt) { make_const_i(in, (int64_t)zext_of(in.aux.sc, x)); folded++; again = true; }
+                        else if (op == CastOp::SIToFP && in.aux.sc != Scalar::I1) { make_const_f(in, in.ty.sc == Scalar::F32 ? (double)(float)x : (double)x); folded++; again = true; }
+                    } else if (op == CastOp::FPExt && in.aux.sc == Scalar::F32) { make_const_f(in, round_to(Scalar::F32, a->fimm)); folded++; again = true; }
+                    continue;
+                }
+                if (in.op == Opc::Select) {
+                    const Inst* c = const_def(f, in.ops[0]);
+                    if (c && c->op == Opc::ConstI) { replace_uses(f, Val::V(id), (c->imm & 1) ? in.ops[1] : in.ops[2]); folded++; }
+                    else if (in.ops[1] == in.ops[2]) { replace_uses(f, Val::V(id), in.ops[1]); folded++; }
+                    continue;
+                }
+            }
+        }
+        // a conditional branch on a constant becomes a branch; the edge not taken leaves the phis
+        for (uint32_t b = 0; b < f.blocks.size(); b++) {
+            Term& t = f.blocks[b].term;
+            if (t.kind != Term::CondBr) continue;
+            const Inst* c = const_def(f, t.val);
+            if (!c || c->op != Opc::ConstI) continue;
+            uint32_t taken = (c->imm & 1) ? t.t : t.f, dropped = (c->imm & 1) ? t.f : t.t;
+            t.kind = Term::Br;
+            t.has_val = false;
+            t.t = taken;
+            if (dropped != taken)
+                for (uint32_t id : f.blocks[dropped].insts) {
+                    Inst& in = f.insts[id];
+                    if (in.op != Opc::Phi) continue;
+                    for (size_t i = 0; i < in.phi_blocks.size(); i++)
+                        if (in.phi_blocks[i] == b) { in.phi_blocks.erase(in.phi_blocks.begin() + (long)i); in.ops.erase(in.ops.begin() + (long)i); break; }
+                }
+            folded++; again = true;
+        }
+    }
+    return folded;
+}
+
+// ---- common subexpressions -------------------------------------------------------------------
+// A pure instruction identical to one in a dominating position is replaced by it.  Walks the
+// dominator tree (immediate dominators by the iterative algorithm of Cooper, Harvey and Kennedy)
+// with a scoped table, so availability never crosses into a sibling subtree.
+int eliminate_common_subexpressions(Function& f) {
+    const uint32_t nb = (uint32_t)f.blocks.size();
+    if (!nb) return 0;
+    std::vector<std::vector<uint32_t>> preds(nb);
+    std::vector<uint32_t> succ, rpo, order(nb, UINT32_MAX);
+    {   // reverse post-order from the entry
+        std::vector<char> seen(nb, 0);
+        std::vector<std::pair<uint32_t, size_t>> st{{0, 0}};
+        std::vector<std::vector<uint32_t>> sx(nb);
+        for (uint32_t b = 0; b < nb; b++) { successors(f.blocks[b].term, succ); sx[b] = succ; }
+        seen[0] = 1;
+        std::vector<uint32_t> post;
+        while (!st.empty()) {
+            auto& [b, i] = st.back();
+            if (i < sx[b].size()) {
+                uint32_t s = sx[b][i++];
+                if (!seen[s]) { seen[s] = 1; st.push_back({s, 0}); }
+            } else { post.push_back(b); st.pop_back(); }
+        }
+        rpo.assign(post.rbegin(), post.rend());
+        for (uint32_t i = 0; i < rpo.size(); i++) order[rpo[i]] = i;
+        for (uint32_t b : rpo) for (uint32_t s : sx[b]) preds[s].push_back(b);
+    }
+    std::vector<uint32_t> idom(nb, UINT32_MAX);
+    idom[0] = 0;
+    for (bool changed = true; changed;) {
+        changed = false;
+        for (uint32_t b : rpo) {
+            if (b == 0) continue;
+            uint32_t nd = UINT32_MAX;
+            for (uint32_t p : preds[b]) {
+                if (idom[p] == UINT32_MAX) continue;
+                if (nd == UINT32_MAX) { nd = p; continue; }
+                uint32_t x = p, y = nd;
+                while (x != y) {
+                    while (order[x] > order[y]) x = idom[x];
+                    while (order[y] > order[x]) y = idom[y];
+                }
+                nd = x;
+            }
+            if (nd != idom[b]) { idom[b] = nd; changed = true; }
+        }
+    }
+    std::vector<std::vector<uint32_t>> kids(nb);
+    for (uint32_t b : rpo) if (b != 0 && idom[b] != UINT32_MAX) kids[idom[b]].push_back(b);
+
+    auto key_of = [&](const Inst& in, std::string* k) {
+        switch (in.op) {
+            case Opc::ConstI: case Opc::ConstF: case Opc::Bin: case Opc::ICmp: case Opc::FCmp: case Opc::Select: case Opc::Cast: case Opc::Index:
+            case Opc::VecExtract: case Opc::VecBuild: break;
+            default: return false;
+        }
+        char buf[96];
+        uint64_t fb;
+        memcpy(&fb, &in.fimm, 8);
+        snprintf(buf, sizeof buf, "%d.%d.%s.%s.%lld.%llx", (int)in.op, (int)in.sub, ty_text(in.ty).c_str(), ty_text(in.aux).c_str(), (long long)in.imm, (unsigned long long)fb);
+        *k = buf;
+        for (Val v : in.ops) { *k += v.param ? ":p" : ":v"; *k += std::to_string(v.idx); }
+        return true;
+    };
+    int removed = 0;
+    std::map<std::string, uint32_t> avail;
+    struct Frame { uint32_t b; size_t kid; std::vector<std::string> added; };
+    std::vector<Frame> st;
+    auto enter = [&](uint32_t b) {
+        Frame fr{b, 0, {}};
+        std::vector<uint32_t> keep;
+        for (uint32_t id : f.blocks[b].insts) {
+            std::string k;
+            if (key_of(f.insts[id], &k)) {
+                auto it = avail.find(k);
+                if (it != avail.end()) { replace_uses(f, Val::V(id), Val::V(it->second)); removed++; continue; }
+                avail[k] = id;
+                fr.added.push_back(k);
+            }
+            keep.push_back(id);
+        }
+        f.blocks[b].insts = keep;
+        st.push_back(std::move(fr));
+    };
+    enter(0);
+    while (!st.empty()) {
+        Frame& fr = st.back();
+        if (fr.kid < kids[fr.b].size()) { uint32_t c = kids[fr.b][fr.kid++]; enter(c); continue; }
+        for (auto& k : fr.added) avail.erase(k);
+        st.pop_back();
+    }
+    return removed;
 }
 
 // ---- inliner -------------------------------------------------------------------------------
@@ -1265,7 +1637,10 @@ void optimize_module(Module& m, int opt_level, int reg_budget, std::vector<OptRe
         OptReport rep;
         if (opt_level > 0) {
             simplify_cfg(f);
+            fold_constants(f);
+            eliminate_common_subexpressions(f);
             dce(f);
+            simplify_cfg(f);
             rep.warp_reduces = fuse_warp_reductions(f);
             bool done = false;
             for (int U = 4; U >= 1 && !done; U >>= 1) {

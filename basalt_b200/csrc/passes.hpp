@@ -38,6 +38,12 @@ void inline_calls(Module& m);
 void simplify_cfg(Function& f);
 // Removes instructions without side effects whose results are unused.
 void dce(Function& f);
+// Evaluates instructions whose operands are constants, with the CPU oracle's arithmetic, applies
+// integer identities, and turns a conditional branch on a constant into a branch (the reference's
+// constant_fold, crates/basalt-passes/src/constfold.rs).  Returns the number of rewrites.
+int fold_constants(Function& f);
+// Replaces a pure instruction by an identical one that dominates it.  Returns the number removed.
+int eliminate_common_subexpressions(Function& f);
 
 struct OptReport {
     bool elementwise = false;   // one-element-per-thread kernel rewritten to vector accesses

@@ -323,6 +323,9 @@ def main():
     ap.add_argument("--size", type=int, default=0, help="problem size for --profile (elements, or the matrix dimension)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if int(os.environ.get("LOCAL_RANK", "0")) == 0:
+        from basalt_b200 import build as native_build
+        native_build.build()          # no-op when libbasalt_b200.so is up to date; needs nvcc otherwise
     if args.impl == "reference":
         return reference_arm(args)
     if args.profile:

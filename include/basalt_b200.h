@@ -66,6 +66,15 @@ int basalt_b200_optimize(const char *bir, size_t len, const basalt_emit_opts *op
 int basalt_b200_roundtrip(const char *bir, size_t len, char **bir_out, size_t *bir_len,
                           basalt_diag *diag_out);
 
+/* The front half of the reference CLI's CUDA-C lane (crates/basalt-cli/src/main.rs:286-327:
+ * preprocess, parse, type-check, lower to BIR) for the subset of the language device kernels are
+ * written in: crates/basalt-frontend-c plus crates/basalt-sema/src/{checker,lower}.rs.  On success
+ * *bir_out is the slot-form BIR text of the translation unit (the form sema hands to the passes,
+ * lower.rs:882-898, 992-1063), ready for basalt_b200_emit.  A refusal carries the reference's
+ * front-end codes: E200/E201/E202 lexical and syntax, E300-E304 and E308 semantic. */
+int basalt_b200_compile_cuda(const char *src, size_t len, char **bir_out, size_t *bir_len,
+                             basalt_diag *diag_out);
+
 void basalt_b200_free(void *p);
 
 /* ------------------------------------------------------------------------------------------
