@@ -7,8 +7,10 @@
 Headline workload (N=1 and per rank at N>1): the max_i32 reduction over 2^28 int32 (1 GiB), the
 benchmark configuration the metric is quoted on.  A step is one pass over the rank's batch: one
 launch of the emitted sm_100a kernel through the C-ABI runtime, plus, at N>1, the 4-byte
-allreduce(max) of the partial maxima over this library's NCCL communicator.  Scaling is weak: every
-rank owns a 2^28-element contiguous shard of an N*2^28-element array.
+allreduce(max) of the partial maxima over this library's NCCL communicator, issued on a second
+stream so that it overlaps the next step's kernel (every step's allreduce completes inside the
+timed region).  Scaling is weak: every rank owns a 2^28-element contiguous shard of an
+N*2^28-element array.
 
 One JSON line is printed by rank 0 (keys are described beside the code that fills them).  `--impl reference`
 times the reference's CPU launch path (the C restatement under oracle/, one thread, like the
@@ -118,7 +120,7 @@ def reference_arm(args):
             "cpu_baseline": {"value": value, "unit": "GB/s", "cores": 1, "kind": "port",
                              "sample": f"{steps} full passes over 2^28 int32; the reference's CPU launch path is single-threaded by construction"},
             "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-    print(json.dumps(line), flush=True)
+    emit_line(line)
 
 
 def others_summary(ctx, torch, stream, peaks_hbm, peaks_tf):
@@ -271,7 +273,7 @@ def profile_one(args):
         for _ in range(reps):
             f()
     torch.cuda.synchronize()
-    print(json.dumps({"profiling": name, "size": size, "launches_each": reps}), flush=True)
+    emit_line({"profiling": name, "size": size, "launches_each": reps})
 
 
 def sharded_matmul(ctx, torch, group, comm, stream, peak_tf):
@@ -309,6 +311,20 @@ def sharded_matmul(ctx, torch, group, comm, stream, peak_tf):
             "tflops_total_with_allgather": fl / ms_both / 1e9, "status": fn.status(), "scaling": "strong (8192^3 split by rows)"}
 
 
+_REAL_STDOUT = None
+
+
+def emit_line(obj) -> None:
+    """Prints the one JSON line on the process's real stdout."""
+    text = json.dumps(obj) + "\n"
+    sys.stdout.flush()
+    if _REAL_STDOUT is None:
+        sys.stdout.write(text)
+        sys.stdout.flush()
+    else:
+        os.write(_REAL_STDOUT, text.encode())
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -323,6 +339,12 @@ def main():
     ap.add_argument("--size", type=int, default=0, help="problem size for --profile (elements, or the matrix dimension)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    # Libraries (NCCL's version banner, build tools) write to file descriptor 1; the contract is one
+    # JSON line on stdout, so everything else goes to stderr until that line is printed.
+    sys.stdout.flush()
+    global _REAL_STDOUT
+    _REAL_STDOUT = os.dup(1)
+    os.dup2(2, 1)
     if int(os.environ.get("LOCAL_RANK", "0")) == 0:
         from basalt_b200 import build as native_build
         native_build.build()          # no-op when libbasalt_b200.so is up to date; needs nvcc otherwise
@@ -357,34 +379,61 @@ def main():
     x.copy_(torch.from_numpy(host_x))
     host_in = host_x.view()
     host_in.flags.writeable = False      # an input of the launch: copied to the device, never back
-    partial = torch.empty(1, dtype=torch.int32, device="cuda")
-    result = torch.empty(1, dtype=torch.int32, device="cuda")
+    # A ring of partial/result words: at N > 1 the 4-byte allreduce of step k runs on its own stream
+    # while the kernel of step k+1 streams its shard, so the collective's latency is hidden.
+    RING = 4 if comm is not None else 1
+    partials = torch.empty(RING, dtype=torch.int32, device="cuda")
+    results = torch.empty(RING, dtype=torch.int32, device="cuda")
     lowest = torch.full((1,), -2**31, dtype=torch.int32, device="cuda")
+    main_stream = torch.cuda.current_stream()
+    comm_stream = torch.cuda.Stream() if comm is not None else None
+    ready = [torch.cuda.Event() for _ in range(RING)]
+    reduced = [torch.cuda.Event() for _ in range(RING)]
+    issued = [0]
 
     fn = ctx.load_module(b.Ptx().emit(kb.load("max_i32")).text).get_function("max_i32")
     blocks = fn.one_wave(256)          # SM count x resident CTAs of this kernel: exactly one wave
-    params = [b.ptr(x.data_ptr()), b.ptr(partial.data_ptr()), b.i32(n)]
-    launch_emitted = fn.bind(blocks, 256, 0, params, stream=stream)
+    launch_emitted_slot = [fn.bind(blocks, 256, 0, [b.ptr(x.data_ptr()), b.ptr(partials[i].data_ptr()), b.i32(n)], stream=stream) for i in range(RING)]
+    launch_emitted = launch_emitted_slot[0]
+    partial = partials[0:1]
+
+    def step(launch_slot):
+        k = issued[0]
+        slot = k % RING
+        issued[0] = k + 1
+        if comm is not None and k >= RING:
+            main_stream.wait_event(reduced[slot])              # the slot's previous allreduce has read it
+        partials[slot:slot + 1].copy_(lowest)                  # a 4-byte device copy resets the running maximum
+        launch_slot(slot)
+        if comm is not None:
+            ready[slot].record(main_stream)
+            comm_stream.wait_event(ready[slot])
+            comm.allreduce_max_i32(partials[slot].data_ptr(), results[slot].data_ptr(), 1, comm_stream.cuda_stream)
+            reduced[slot].record(comm_stream)
+
+    def drain():
+        if comm is not None:
+            for e in reduced[:min(RING, issued[0])]:
+                main_stream.wait_event(e)
 
     def step_emitted():
-        partial.copy_(lowest)                                  # a 4-byte device copy resets the running maximum
-        launch_emitted()                                       # basalt_rt_launch: the emitted sm_100a kernel
-        if comm is not None:
-            comm.allreduce_max_i32(partial.data_ptr(), result.data_ptr(), 1, stream)
+        step(lambda slot: launch_emitted_slot[slot]())         # basalt_rt_launch: the emitted sm_100a kernel
 
     def step_hand():
-        partial.copy_(lowest)
-        kernels.max_i32(x.data_ptr(), n, partial.data_ptr(), stream)
-        if comm is not None:
-            comm.allreduce_max_i32(partial.data_ptr(), result.data_ptr(), 1, stream)
+        step(lambda slot: kernels.max_i32(x.data_ptr(), n, partials[slot].data_ptr(), stream))
 
-    def timed_loop(step, steps):
+    def last_result():
+        slot = (issued[0] - 1) % RING
+        return int((results if comm is not None else partials)[slot].item())
+
+    def timed_loop(step_fn, steps):
         group.barrier()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(steps):
-            step()
+            step_fn()
+        drain()                                                # the last allreduces are inside the timed region
         e1.record()
         torch.cuda.synchronize()
         group.barrier()
@@ -396,7 +445,7 @@ def main():
     torch.cuda.synchronize()
     t_begin = time.time()
     total_ms = timed_loop(step_emitted, args.steps)
-    got = int((result if comm is not None else partial).item())
+    got = last_result()
     # kernel-only time of the dominant kernel, measured live with events around each launch
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(min(args.steps, 200))]
     for e0, e1 in ev:
@@ -467,7 +516,7 @@ def main():
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "i32", "data": "synthetic",
             "config": {"workload": f"max_i32: signed max over {n} int32 per GPU (uniform over the full range, SplitMix64 seed per rank), "
-                                   "emitted sm_100a kernel launched through the C-ABI runtime" + (", NCCL allreduce(max) of 1 int32 per step" if world > 1 else ""),
+                                   "emitted sm_100a kernel launched through the C-ABI runtime" + (", NCCL allreduce(max) of 1 int32 per step on a second stream, overlapping the next step's kernel" if world > 1 else ""),
                        "elements_per_gpu": n, "grid": blocks, "block": 256, "l2": f"input ({4 * n >> 20} MiB per GPU) is larger than the 126 MB L2; no flush needed",
                        "parallelism": f"contiguous shards x{world}"},
             "parity": parity,
@@ -485,7 +534,7 @@ def main():
             line["others"] = others
         if sharded is not None:
             line["matmul_f16_8192_sharded"] = sharded
-        print(json.dumps(line), flush=True)
+        emit_line(line)
     if comm is not None:
         comm.destroy()
     if group.dist is not None:
