@@ -22,6 +22,7 @@
 #include <vector>
 
 #include "../../include/basalt_b200.h"
+#include "../../include/basalt_b200_kernels.h"
 
 namespace {
 
@@ -68,6 +69,9 @@ struct Fns {
     CUresult (*cuEventElapsedTime)(float*, CUevent, CUevent);
     CUresult (*cuGetErrorString)(CUresult, const char**);
     CUresult (*cuOccupancyMaxActiveBlocksPerMultiprocessor)(int*, CUfunction, int, size_t);
+    CUresult (*cuIpcGetMemHandle)(CUipcMemHandle*, CUdeviceptr);
+    CUresult (*cuIpcOpenMemHandle)(CUdeviceptr*, CUipcMemHandle, unsigned);
+    CUresult (*cuIpcCloseMemHandle)(CUdeviceptr);
     CUresult (*cuTensorMapEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                        const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                        CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -131,6 +135,14 @@ struct basalt_rt_buffer {
 struct basalt_rt_comm {
     basalt_rt_ctx* ctx = nullptr;
     ncclComm_t comm = nullptr;
+};
+struct basalt_rt_peer_group {
+    basalt_rt_ctx* ctx = nullptr;
+    int nranks = 0, rank = 0;
+    CUdeviceptr own = 0;                 // this rank's inbox; the status word sits kPeerStatusOffset bytes in
+    uint64_t inbox[8] = {0};             // every rank's inbox as mapped on this device
+    bool connected = false;
+    uint32_t epoch = 0;
 };
 
 namespace {
@@ -264,6 +276,9 @@ int basalt_rt_driver_load(basalt_rt_driver** out) {
               resolve(lib, &f.cuEventSynchronize, {"cuEventSynchronize"}) && resolve(lib, &f.cuEventElapsedTime, {"cuEventElapsedTime"}) &&
               resolve(lib, &f.cuGetErrorString, {"cuGetErrorString", "cuGetErrorName"}) &&
               resolve(lib, &f.cuTensorMapEncodeTiled, {"cuTensorMapEncodeTiled"}) &&
+              resolve(lib, &f.cuIpcGetMemHandle, {"cuIpcGetMemHandle"}) &&
+              resolve(lib, &f.cuIpcOpenMemHandle, {"cuIpcOpenMemHandle_v2", "cuIpcOpenMemHandle"}) &&
+              resolve(lib, &f.cuIpcCloseMemHandle, {"cuIpcCloseMemHandle"}) &&
               resolve(lib, &f.cuOccupancyMaxActiveBlocksPerMultiprocessor, {"cuOccupancyMaxActiveBlocksPerMultiprocessor"});
     if (!ok) { dlclose(lib); delete d; return 2; }
     int rc = check(f, "cuInit", f.cuInit(0));
@@ -654,6 +669,106 @@ int basalt_rt_allgather(basalt_rt_comm* comm, uint64_t send, uint64_t recv, size
     Nccl* n = nccl();
     if (!n || !comm) return set_err(4, 0, "basalt_rt_allgather", "no communicator");
     return nccl_check(n, "ncclAllGather", n->AllGather((const void*)(uintptr_t)send, (void*)(uintptr_t)recv, bytes_per_rank, ncclUint8, comm->comm, (cudaStream_t)stream));
+}
+
+// ---- peer-memory exchange group ---------------------------------------------------------------
+static const size_t kPeerInboxBytes = 2u << 20;      // its own allocation granule, so the IPC mapping covers nothing else
+static const size_t kPeerStatusOffset = 4096;
+static const uint64_t kPeerTimeoutNs = 2000000000ull;
+
+int basalt_rt_peer_group_create(basalt_rt_ctx* ctx, int nranks, int rank, basalt_rt_peer_group** out) {
+    if (!ctx || !out) return set_err(4, 0, "basalt_rt_peer_group_create", "null argument");
+    *out = nullptr;
+    if (nranks < 1 || nranks > 8 || rank < 0 || rank >= nranks) return set_err(4, 0, "basalt_rt_peer_group_create", "rank or world size out of range (at most 8 ranks)");
+    int rc = make_current(ctx);
+    if (rc) return rc;
+    const Fns& f = ctx->drv->f;
+    CUdeviceptr p = 0;
+    rc = check(f, "cuMemAlloc", f.cuMemAlloc(&p, kPeerInboxBytes));
+    if (rc) return rc;
+    std::vector<unsigned char> zeros(8192, 0);
+    rc = check(f, "cuMemcpyHtoD", f.cuMemcpyHtoD(p, zeros.data(), zeros.size()));
+    if (rc) { f.cuMemFree(p); return rc; }
+    auto* g = new basalt_rt_peer_group;
+    g->ctx = ctx;
+    g->nranks = nranks;
+    g->rank = rank;
+    g->own = p;
+    g->inbox[rank] = (uint64_t)p;
+    g->connected = nranks == 1;
+    *out = g;
+    return 0;
+}
+
+int basalt_rt_peer_group_handle(basalt_rt_peer_group* g, unsigned char handle_out[64]) {
+    if (!g || !handle_out) return set_err(4, 0, "basalt_rt_peer_group_handle", "null argument");
+    static_assert(sizeof(CUipcMemHandle) == 64, "CUDA IPC handles are 64 bytes");
+    int rc = make_current(g->ctx);
+    if (rc) return rc;
+    CUipcMemHandle h;
+    rc = check(g->ctx->drv->f, "cuIpcGetMemHandle", g->ctx->drv->f.cuIpcGetMemHandle(&h, g->own));
+    if (rc) return rc;
+    memcpy(handle_out, &h, 64);
+    return 0;
+}
+
+int basalt_rt_peer_group_connect(basalt_rt_peer_group* g, const unsigned char* handles, size_t nbytes) {
+    if (!g || !handles) return set_err(4, 0, "basalt_rt_peer_group_connect", "null argument");
+    if (nbytes != (size_t)g->nranks * 64) return set_err(4, 0, "basalt_rt_peer_group_connect", "expected one 64-byte handle per rank");
+    if (g->connected) return set_err(4, 0, "basalt_rt_peer_group_connect", "already connected");
+    int rc = make_current(g->ctx);
+    if (rc) return rc;
+    const Fns& f = g->ctx->drv->f;
+    for (int r = 0; r < g->nranks; r++) {
+        if (r == g->rank) continue;
+        CUipcMemHandle h;
+        memcpy(&h, handles + (size_t)r * 64, 64);
+        CUdeviceptr p = 0;
+        rc = check(f, "cuIpcOpenMemHandle", f.cuIpcOpenMemHandle(&p, h, CU_IPC_MEM_LAZY_ENABLE_PEER_ACCESS));
+        if (rc) {
+            for (int q = 0; q < r; q++) if (q != g->rank && g->inbox[q]) { f.cuIpcCloseMemHandle((CUdeviceptr)g->inbox[q]); g->inbox[q] = 0; }
+            return rc;
+        }
+        g->inbox[r] = (uint64_t)p;
+    }
+    g->connected = true;
+    return 0;
+}
+
+int basalt_rt_peer_allreduce_max_i32(basalt_rt_peer_group* g, uint64_t partial, uint64_t result, void* stream) {
+    if (!g || !partial || !result) return set_err(4, 0, "basalt_rt_peer_allreduce_max_i32", "null argument");
+    if (!g->connected) return set_err(4, 0, "basalt_rt_peer_allreduce_max_i32", "the group is not connected");
+    int rc = make_current(g->ctx);
+    if (rc) return rc;
+    if (++g->epoch == 0) g->epoch = 1;
+    int krc = basalt_k_peer_allreduce_max_i32(g->inbox, g->nranks, g->rank, g->epoch, (const int32_t*)(uintptr_t)partial, (int32_t*)(uintptr_t)result,
+                                              (uint32_t*)(uintptr_t)(g->own + kPeerStatusOffset), kPeerTimeoutNs, stream);
+    if (krc != 0) return set_err(3, krc, "basalt_k_peer_allreduce_max_i32", basalt_k_last_error());
+    return 0;
+}
+
+int basalt_rt_peer_group_status(basalt_rt_peer_group* g, uint32_t* status_out) {
+    if (!g || !status_out) return set_err(4, 0, "basalt_rt_peer_group_status", "null argument");
+    int rc = make_current(g->ctx);
+    if (rc) return rc;
+    const Fns& f = g->ctx->drv->f;
+    rc = check(f, "cuCtxSynchronize", f.cuCtxSynchronize());
+    if (rc) return rc;
+    return check(f, "cuMemcpyDtoH", f.cuMemcpyDtoH(status_out, g->own + kPeerStatusOffset, 4));
+}
+
+int basalt_rt_peer_group_destroy(basalt_rt_peer_group* g) {
+    if (!g) return 0;
+    int rc = make_current(g->ctx);
+    const Fns& f = g->ctx->drv->f;
+    if (!rc) {
+        f.cuCtxSynchronize();
+        for (int r = 0; r < g->nranks; r++)
+            if (r != g->rank && g->inbox[r]) f.cuIpcCloseMemHandle((CUdeviceptr)g->inbox[r]);
+        f.cuMemFree(g->own);
+    }
+    delete g;
+    return rc;
 }
 
 }  // extern "C"

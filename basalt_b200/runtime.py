@@ -329,3 +329,45 @@ class Communicator:
         if self._h:
             lib.basalt_rt_comm_destroy(self._h)
             self._h = None
+
+
+class PeerGroup:
+    """The sharded max_i32's exchange step over peer-mapped memory instead of a library collective
+    (basalt_rt_peer_group_*): each rank's inbox is exported as a CUDA IPC handle, every rank maps
+    every other rank's inbox, and `allreduce_max_i32` is one small kernel of release stores to the
+    peers and acquire loads of its own inbox."""
+
+    def __init__(self, ctx: CudaContext, handle, nranks: int, rank: int):
+        self.ctx, self._h, self.nranks, self.rank = ctx, handle, nranks, rank
+
+    @staticmethod
+    def create(ctx: CudaContext, nranks: int, rank: int) -> "PeerGroup":
+        h = C.c_void_p()
+        _check(lib.basalt_rt_peer_group_create(ctx._h, nranks, rank, C.byref(h)))
+        return PeerGroup(ctx, h, nranks, rank)
+
+    def handle(self) -> bytes:
+        buf = (C.c_char * 64)()
+        _check(lib.basalt_rt_peer_group_handle(self._h, buf))
+        return bytes(buf.raw)
+
+    def connect(self, handles: list[bytes]):
+        """`handles[r]` is rank r's `handle()`; the entry of this rank is ignored."""
+        if len(handles) != self.nranks or any(len(x) != 64 for x in handles):
+            raise ValueError("expected one 64-byte handle per rank")
+        blob = b"".join(handles)
+        _check(lib.basalt_rt_peer_group_connect(self._h, blob, len(blob)))
+
+    def allreduce_max_i32(self, partial_ptr: int, result_ptr: int, stream=None):
+        _check(lib.basalt_rt_peer_allreduce_max_i32(self._h, partial_ptr, result_ptr, C.c_void_p(stream)))
+
+    def status(self) -> int:
+        """Synchronises the context; non-zero bits name ranks that did not answer within the bound."""
+        out = C.c_uint32(0)
+        _check(lib.basalt_rt_peer_group_status(self._h, C.byref(out)))
+        return int(out.value)
+
+    def destroy(self):
+        if self._h:
+            lib.basalt_rt_peer_group_destroy(self._h)
+            self._h = None

@@ -16,7 +16,7 @@ from dataclasses import dataclass
 
 import numpy as np
 
-from .runtime import Communicator, CudaContext, shard_range
+from .runtime import Communicator, CudaContext, PeerGroup, shard_range
 
 
 @dataclass
@@ -75,6 +75,24 @@ class RankGroup:
         uid = Communicator.unique_id() if self.rank == 0 else None
         uid = self.broadcast_bytes(uid, 0)
         return Communicator.create(ctx, uid, self.world, self.rank)
+
+    def all_gather_bytes(self, payload: bytes) -> list[bytes]:
+        if self.dist is None:
+            return [payload]
+        box = [None] * self.world
+        self.dist.all_gather_object(box, payload)
+        return box
+
+    def peers(self, ctx: CudaContext) -> PeerGroup | None:
+        """The peer-memory exchange group over the ranks of the group (None for one rank): every
+        rank exports its inbox, the handles travel through torch.distributed, every rank maps the
+        others.  Needs one process per GPU on GPUs that can map each other's memory."""
+        if self.world <= 1:
+            return None
+        g = PeerGroup.create(ctx, self.world, self.rank)
+        g.connect(self.all_gather_bytes(g.handle()))
+        self.barrier()
+        return g
 
     def shard(self, total: int, align: int = 1) -> tuple[int, int]:
         return shard_range(total, self.world, self.rank, align)

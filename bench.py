@@ -7,10 +7,9 @@
 Headline workload (N=1 and per rank at N>1): the max_i32 reduction over 2^28 int32 (1 GiB), the
 benchmark configuration the metric is quoted on.  A step is one pass over the rank's batch: one
 launch of the emitted sm_100a kernel through the C-ABI runtime, plus, at N>1, the 4-byte
-allreduce(max) of the partial maxima over this library's NCCL communicator, issued on a second
-stream so that it overlaps the next step's kernel (every step's allreduce completes inside the
-timed region).  Scaling is weak: every rank owns a 2^28-element contiguous shard of an
-N*2^28-element array.
+allreduce(max) of the partial maxima: one small kernel of stores to and loads from peer-mapped
+memory (basalt_rt_peer_allreduce_max_i32; --nccl-exchange uses ncclAllReduce instead).  Scaling is
+weak: every rank owns a 2^28-element contiguous shard of an N*2^28-element array.
 
 One JSON line is printed by rank 0 (keys are described beside the code that fills them).  `--impl reference`
 times the reference's CPU launch path (the C restatement under oracle/, one thread, like the
@@ -333,6 +332,7 @@ def main():
     ap.add_argument("--impl", default="basalt_b200", choices=["basalt_b200", "reference"])
     ap.add_argument("--no-others", action="store_true", help="skip the short timings of the other four configurations")
     ap.add_argument("--elements", type=int, default=N_MAX, help="int32 elements per GPU (profiling runs use a smaller case)")
+    ap.add_argument("--nccl-exchange", action="store_true", help="at N > 1 use ncclAllReduce for the 4-byte exchange instead of the peer-memory kernel")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer and CPU-baseline legs (profiling runs)")
     ap.add_argument("--profile", default=None, choices=["vadd_i32", "helper_chain", "sgemm_f32", "matmul_f16"],
                     help="run only this workload's emitted and hand-written kernels a few times on a small case (for ncu) and exit")
@@ -366,6 +366,15 @@ def main():
         print(f"warning: --gpus {args.gpus} but WORLD_SIZE is {world}", file=sys.stderr)
     ctx = b.CudaDriver.load().create_context(local_rank)
     comm = group.nccl(ctx)
+    peers, exchange_kind = None, "none"
+    if world > 1:
+        exchange_kind = "ncclAllReduce(max) of 1 int32"
+        if not args.nccl_exchange:
+            try:
+                peers = group.peers(ctx)
+                exchange_kind = "allreduce(max) of 1 int32 over peer-mapped memory (release stores / acquire loads across NVLink)"
+            except b.CudaError as e:
+                print(f"peer-memory exchange unavailable ({e}); using NCCL", file=sys.stderr)
     stream = torch.cuda.current_stream().cuda_stream
     peak_hbm, peak_tf, peak_kind = measured_peaks()
 
@@ -379,52 +388,38 @@ def main():
     x.copy_(torch.from_numpy(host_x))
     host_in = host_x.view()
     host_in.flags.writeable = False      # an input of the launch: copied to the device, never back
-    # A ring of partial/result words: at N > 1 the 4-byte allreduce of step k runs on its own stream
-    # while the kernel of step k+1 streams its shard, so the collective's latency is hidden.
-    RING = 4 if comm is not None else 1
-    partials = torch.empty(RING, dtype=torch.int32, device="cuda")
-    results = torch.empty(RING, dtype=torch.int32, device="cuda")
+    partial = torch.empty(1, dtype=torch.int32, device="cuda")
+    result = torch.empty(1, dtype=torch.int32, device="cuda")
     lowest = torch.full((1,), -2**31, dtype=torch.int32, device="cuda")
-    main_stream = torch.cuda.current_stream()
-    comm_stream = torch.cuda.Stream() if comm is not None else None
-    ready = [torch.cuda.Event() for _ in range(RING)]
-    reduced = [torch.cuda.Event() for _ in range(RING)]
-    issued = [0]
 
     fn = ctx.load_module(b.Ptx().emit(kb.load("max_i32")).text).get_function("max_i32")
     blocks = fn.one_wave(256)          # SM count x resident CTAs of this kernel: exactly one wave
-    launch_emitted_slot = [fn.bind(blocks, 256, 0, [b.ptr(x.data_ptr()), b.ptr(partials[i].data_ptr()), b.i32(n)], stream=stream) for i in range(RING)]
-    launch_emitted = launch_emitted_slot[0]
-    partial = partials[0:1]
+    launch_emitted = fn.bind(blocks, 256, 0, [b.ptr(x.data_ptr()), b.ptr(partial.data_ptr()), b.i32(n)], stream=stream)
 
-    def step(launch_slot):
-        k = issued[0]
-        slot = k % RING
-        issued[0] = k + 1
-        if comm is not None and k >= RING:
-            main_stream.wait_event(reduced[slot])              # the slot's previous allreduce has read it
-        partials[slot:slot + 1].copy_(lowest)                  # a 4-byte device copy resets the running maximum
-        launch_slot(slot)
-        if comm is not None:
-            ready[slot].record(main_stream)
-            comm_stream.wait_event(ready[slot])
-            comm.allreduce_max_i32(partials[slot].data_ptr(), results[slot].data_ptr(), 1, comm_stream.cuda_stream)
-            reduced[slot].record(comm_stream)
-
-    def drain():
-        if comm is not None:
-            for e in reduced[:min(RING, issued[0])]:
-                main_stream.wait_event(e)
+    # The exchange step at N > 1: allreduce(max) of the 4-byte partials.  Over peer-mapped memory
+    # (one small kernel of release stores and acquire loads across NVLink) when the GPUs can map
+    # each other, else ncclAllReduce; both on the launching stream, so a step ends when its result
+    # is in `result`.  (Issuing the collective on a second stream to overlap it with the next
+    # step's kernel was measured and is slower: the collective's CTA takes a slot of the one-wave
+    # grid and the displaced CTA runs as a second wave.)
+    def exchange():
+        if peers is not None:
+            peers.allreduce_max_i32(partial.data_ptr(), result.data_ptr(), stream)
+        elif comm is not None:
+            comm.allreduce_max_i32(partial.data_ptr(), result.data_ptr(), 1, stream)
 
     def step_emitted():
-        step(lambda slot: launch_emitted_slot[slot]())         # basalt_rt_launch: the emitted sm_100a kernel
+        partial.copy_(lowest)                                  # a 4-byte device copy resets the running maximum
+        launch_emitted()                                       # basalt_rt_launch: the emitted sm_100a kernel
+        exchange()
 
     def step_hand():
-        step(lambda slot: kernels.max_i32(x.data_ptr(), n, partials[slot].data_ptr(), stream))
+        partial.copy_(lowest)
+        kernels.max_i32(x.data_ptr(), n, partial.data_ptr(), stream)
+        exchange()
 
     def last_result():
-        slot = (issued[0] - 1) % RING
-        return int((results if comm is not None else partials)[slot].item())
+        return int((result if world > 1 else partial).item())
 
     def timed_loop(step_fn, steps):
         group.barrier()
@@ -433,7 +428,6 @@ def main():
         e0.record()
         for _ in range(steps):
             step_fn()
-        drain()                                                # the last allreduces are inside the timed region
         e1.record()
         torch.cuda.synchronize()
         group.barrier()
@@ -516,7 +510,7 @@ def main():
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "i32", "data": "synthetic",
             "config": {"workload": f"max_i32: signed max over {n} int32 per GPU (uniform over the full range, SplitMix64 seed per rank), "
-                                   "emitted sm_100a kernel launched through the C-ABI runtime" + (", NCCL allreduce(max) of 1 int32 per step on a second stream, overlapping the next step's kernel" if world > 1 else ""),
+                                   "emitted sm_100a kernel launched through the C-ABI runtime" + ((", then " + exchange_kind + " per step") if world > 1 else ""),
                        "elements_per_gpu": n, "grid": blocks, "block": 256, "l2": f"input ({4 * n >> 20} MiB per GPU) is larger than the 126 MB L2; no flush needed",
                        "parallelism": f"contiguous shards x{world}"},
             "parity": parity,
@@ -527,7 +521,7 @@ def main():
             "cpu_baseline": cpu,
             "e2e": {"value": total_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": 4 * n + 4, "d2h_bytes_per_step": 4,
                     "ms_per_step": e2e_ms, "steps": e2e_steps, "api": "basalt_rt_cpu_launch (kernel parameters as host pointers, then nthreads)"},
-            "gpu_launches": args.steps,
+            "gpu_launches": args.steps * (2 if peers is not None else 1),
             "clocks": clocks,
         }
         if others is not None:
@@ -535,6 +529,12 @@ def main():
         if sharded is not None:
             line["matmul_f16_8192_sharded"] = sharded
         emit_line(line)
+    if peers is not None:
+        bad = peers.status()
+        if bad:
+            print(f"rank {rank}: peer exchange gave up waiting for ranks with bits {bad:#x}", file=sys.stderr)
+        group.barrier()
+        peers.destroy()
     if comm is not None:
         comm.destroy()
     if group.dist is not None:

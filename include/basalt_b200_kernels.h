@@ -52,6 +52,20 @@ int basalt_k_sgemm_f32(const float *A, const float *B, float *C, int M, int N, i
 int basalt_k_matmul_f16(const void *A, const void *B, void *C, int M, int N, int K, int b_is_nk,
                         int32_t *status, void *stream);
 
+/* The exchange step of the sharded max_i32 (one process per GPU): allreduce(max) of one int32 over
+ * inboxes in peer-mapped device memory, in place of ncclAllReduce(count 1, ncclInt32, ncclMax).
+ * inboxes[r] is the device address, valid on this GPU, of rank r's inbox: 2 x BASALT_K_MAX_PEERS
+ * uint64 words, zeroed before the first call (inboxes[rank] is this rank's own).  `epoch` counts
+ * the calls from 1 and must be the same on every rank; all ranks must make the same calls in the
+ * same order.  *partial is this rank's value, *result receives the maximum over all ranks; both
+ * are device pointers and the call is ordered on `stream`.  A peer that has not answered after
+ * timeout_ns sets bit r of *status (device uint32) and is left out of the result.  No counterpart
+ * in the reference, which has no multi-GPU path. */
+#define BASALT_K_MAX_PEERS 8
+int basalt_k_peer_allreduce_max_i32(const uint64_t *inboxes, int nranks, int rank, uint32_t epoch,
+                                    const int32_t *partial, int32_t *result, uint32_t *status,
+                                    uint64_t timeout_ns, void *stream);
+
 #if defined(__GNUC__)
 #pragma GCC visibility pop
 #endif

@@ -2,8 +2,8 @@
 
 Each rank owns a contiguous shard of the work on its own GPU and runs the emitted kernels through
 the C-ABI runtime; the only exchanges are the ones the workloads need: allreduce(max) of one int32
-for the reduction, allgather of the row-sharded C for the two matmuls, both over this library's
-NCCL communicator.  Results are compared with the CPU oracle on every rank."""
+for the reduction (over this library's NCCL communicator and, beside it, over peer-mapped memory),
+allgather of the row-sharded C for the two matmuls.  Results are compared with the CPU oracle on every rank."""
 import ctypes
 import os
 import sys
@@ -26,6 +26,7 @@ def main():
     group = sharding.RankGroup.from_env("gloo")     # host rendezvous only; data moves over our NCCL communicator
     ctx = b.CudaDriver.load().create_context(local)
     comm = group.nccl(ctx)
+    peers = group.peers(ctx)
     orc = ctypes.CDLL(os.path.join(ROOT, "oracle", "liborc.so"))
     ptx = b.Ptx()
 
@@ -50,6 +51,22 @@ def main():
         ctx.synchronize()
         got = int(result.to_numpy(np.int32)[0])
         assert got == int(want[0]), (plant, got, int(want[0]))
+        # the same exchange over peer-mapped memory instead of NCCL
+        result2 = ctx.upload(np.array([12345], np.int32))
+        peers.allreduce_max_i32(partial.device_ptr(), result2.device_ptr())
+        assert peers.status() == 0
+        assert int(result2.to_numpy(np.int32)[0]) == int(want[0]), (plant, "peer exchange")
+
+    # ---- peer exchange: many back-to-back epochs with values that change every call ----
+    calls = 300
+    table = lambda r: (np.arange(calls, dtype=np.int64) * 2654435761 * (r + 1) % (1 << 32)).astype(np.uint32).view(np.int32)
+    mine = ctx.upload(table(group.rank))
+    outs = ctx.upload(np.zeros(calls, np.int32))
+    for i in range(calls):
+        peers.allreduce_max_i32(mine.device_ptr() + 4 * i, outs.device_ptr() + 4 * i)
+    assert peers.status() == 0
+    want_all = np.max(np.stack([table(r) for r in range(group.world)]), axis=0)
+    assert np.array_equal(outs.to_numpy(np.int32), want_all)
 
     # ---- SGEMM: rows of A and C sharded, B replicated, allgather of C ----
     M, N, K = 128 * 2 * group.world, 256, 128
@@ -78,6 +95,8 @@ def main():
     got = dC.to_numpy(np.float16).reshape(M, N)
     assert rel_fro(got, orc_matmul_f16_rows(orc, A, B, N, False, 0, M)) <= 2e-3
 
+    group.barrier()
+    peers.destroy()
     comm.destroy()
     group.barrier()
     print(f"rank {group.rank}/{group.world} ok", flush=True)
