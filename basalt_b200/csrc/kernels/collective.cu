@@ -29,8 +29,8 @@ __device__ __forceinline__ unsigned long long global_ns() {
     return t;
 }
 
-__global__ void __launch_bounds__(32, 1) peer_allreduce_max_i32_kernel(PeerTable peers, int nranks, int rank, unsigned epoch, const int* __restrict__ partial,
-                                                                       int* __restrict__ result, unsigned* status, unsigned long long timeout_ns) {
+__global__ void __launch_bounds__(32, 1) peer_allreduce_max_i32_kernel(PeerTable peers, int nranks, int rank, unsigned epoch, int* partial,
+                                                                       int* __restrict__ result, unsigned* status, unsigned long long timeout_ns, int reset, int reset_value) {
     const int lane = threadIdx.x;
     const unsigned parity = epoch & 1u;
     int v = INT32_MIN;
@@ -56,13 +56,16 @@ __global__ void __launch_bounds__(32, 1) peer_allreduce_max_i32_kernel(PeerTable
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v = max(v, __shfl_xor_sync(0xffffffffu, v, o));
-    if (lane == 0) *result = v;
+    if (lane == 0) {
+        *result = v;
+        if (reset) *partial = reset_value;   // every lane has read it: ready for the next accumulation
+    }
 }
 
 }  // namespace
 
-extern "C" int basalt_k_peer_allreduce_max_i32(const uint64_t* inboxes, int nranks, int rank, uint32_t epoch, const int32_t* partial, int32_t* result,
-                                               uint32_t* status, uint64_t timeout_ns, void* stream) {
+extern "C" int basalt_k_peer_allreduce_max_i32(const uint64_t* inboxes, int nranks, int rank, uint32_t epoch, int32_t* partial, int32_t* result,
+                                               uint32_t* status, uint64_t timeout_ns, int reset, int32_t reset_value, void* stream) {
     if (!inboxes || !partial || !result || !status) return basalt_k::record_msg(1, "peer_allreduce_max_i32", "null argument");
     if (nranks < 1 || nranks > BASALT_K_MAX_PEERS || rank < 0 || rank >= nranks) return basalt_k::record_msg(1, "peer_allreduce_max_i32", "rank or world size out of range");
     if (epoch == 0) return basalt_k::record_msg(1, "peer_allreduce_max_i32", "epochs start at 1");
@@ -71,6 +74,6 @@ extern "C" int basalt_k_peer_allreduce_max_i32(const uint64_t* inboxes, int nran
         if (!inboxes[r] || (inboxes[r] & 7)) return basalt_k::record_msg(1, "peer_allreduce_max_i32", "an inbox pointer is null or misaligned");
         t.inbox[r] = (unsigned long long*)(uintptr_t)inboxes[r];
     }
-    peer_allreduce_max_i32_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(t, nranks, rank, epoch, partial, result, status, timeout_ns);
+    peer_allreduce_max_i32_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(t, nranks, rank, epoch, partial, result, status, timeout_ns, reset, reset_value);
     return basalt_k::record(cudaGetLastError(), "peer_allreduce_max_i32");
 }

@@ -23,6 +23,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "../../../include/basalt_b200_kernels.h"
 #include "common.cuh"
@@ -359,6 +360,215 @@ __global__ void __launch_bounds__(THREADS2, 1) matmul_f16_tc_persistent(const __
 }
 }  // namespace v2
 
+
+// ---- v3: a pair of CTAs (a cluster of two SMs) per 256 x 256 tile, tcgen05.mma.cta_group::2 ----
+//
+// CTA r of the pair owns rows 128r..128r+127 of the tile: it loads that half of A and columns
+// 128r..128r+127 of B (so each SM stages 32 KB per K slab instead of 48 KB for the same math),
+// and its tensor memory receives its 128 rows of the accumulator.  The even CTA (the leader)
+// issues every MMA; the instruction reads both CTAs' shared memory at the same offsets.
+//   * both producers signal the LEADER's "full" barrier (the bulk-tensor load names it through its
+//     shared::cluster address, no multicast); the leader's producer posts the expected byte count
+//     of both halves;
+//   * the MMA warp's commit arrives on the "empty" barrier of both CTAs (commit with a CTA mask),
+//     and, after a tile's last slab, on both CTAs' "accumulator full" barriers;
+//   * the epilogue warps of both CTAs arrive on the leader's "accumulator empty" barrier.
+// Every wait is bounded as in the other kernels; the pair meets at a cluster barrier before tensor
+// memory is released, so neither CTA leaves while the other may still name its barriers or memory.
+namespace v3 {
+constexpr int TM = 256, TN = 256, HALF_N = 128, STAGES = 6, THREADS3 = 192;
+constexpr int B_HALF_BYTES = HALF_N * BK * 2, STAGE_BYTES3 = A_BYTES + B_HALF_BYTES;   // 16 KB + 16 KB
+constexpr int GROUP_M = 8;
+constexpr uint32_t TMEM_COLS3 = 512;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// shared::cluster address of the same variable in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t cta_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(cta_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// bulk-tensor load into this CTA's shared memory whose completion bytes go to a barrier that may
+// live in the peer CTA (`bar_cluster` is a shared::cluster address)
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+                 "l"(map), "r"(bar_cluster), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+// arrives (once the MMAs issued so far have finished) on the barrier at this offset in both CTAs
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"((uint16_t)3)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
+}
+
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int* m_idx, int* n_idx) {
+    const int per_band = GROUP_M * tiles_n, band = t / per_band, first = band * GROUP_M;
+    const int rows = min(GROUP_M, tiles_m - first), r = t - band * per_band;
+    *m_idx = first + r % rows;
+    *n_idx = r / rows;
+}
+
+template <bool B_IS_NK>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS3, 1)
+    matmul_f16_tc_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, __half* __restrict__ C, int M, int N, int K,
+                       int32_t* status) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], tfull_bar[2], tempty_bar[2];
+    __shared__ uint32_t tmem_slot;
+    __shared__ volatile uint32_t gave_up;
+    const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+    const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+    const int tiles_m = M / TM, tiles_n = N / TN, num_tiles = tiles_m * tiles_n, num_kb = K / BK;
+
+    if (threadIdx.x == 0) {
+        gave_up = 0;
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(smem_u32(&full_bar[s]), 1);    // the leader's producer; bytes arrive from both CTAs
+            mbar_init(smem_u32(&empty_bar[s]), 1);   // one commit from the leader's MMA warp
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(smem_u32(&tfull_bar[b]), 1);
+            mbar_init(smem_u32(&tempty_bar[b]), 8);  // four epilogue warps in each CTA (used in the leader only)
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {   // the same warp of both CTAs allocates for the pair
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS3) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();   // the peer's barriers are initialised before anything can signal them
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_slot;
+    bool ok = true;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (int t = pair; t < num_tiles && ok; t += pairs) {
+                int mi, ni;
+                tile_coords(t, tiles_m, tiles_n, &mi, &ni);
+                const int m0 = mi * TM + (int)rank * BM, n0 = ni * TN + (int)rank * HALF_N;
+                for (int kb = 0; kb < num_kb; kb++, it++) {
+                    const uint32_t s = it % STAGES, parity = ((it / STAGES) & 1) ^ 1;
+                    ok &= mbar_wait(smem_u32(&empty_bar[s]), parity, &gave_up);
+                    if (!ok) break;
+                    const uint32_t fb_local = smem_u32(&full_bar[s]), fb = map_to_cta(fb_local, 0);
+                    const uint32_t a_dst = tiles + s * STAGE_BYTES3, b_dst = a_dst + A_BYTES;
+                    if (leader) mbar_expect_tx(fb_local, 2 * STAGE_BYTES3);
+                    tma_load_2d_pair(a_dst, &map_a, fb, kb * BK, m0);
+                    if (B_IS_NK) tma_load_2d_pair(b_dst, &map_b, fb, kb * BK, n0);   // box 64 k x 128 n
+                    else {
+#pragma unroll
+                        for (int h = 0; h < 2; h++) tma_load_2d_pair(b_dst + h * 8192, &map_b, fb, n0 + 64 * h, kb * BK);   // box 64 n x 64 k
+                    }
+                }
+            }
+            if (!ok) {   // let the copies already issued land before the CTA can exit
+                const uint64_t t0 = global_ns();
+                while (global_ns() - t0 < 2000000ull) {}
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && leader) {
+            const uint32_t idesc = (1u << 4) | ((B_IS_NK ? 0u : 1u) << 16) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(TM >> 4) << 24);
+            uint32_t it = 0, local = 0;
+            for (int t = pair; t < num_tiles && ok; t += pairs, local++) {
+                const uint32_t buf = local & 1, use = local >> 1;
+                ok &= mbar_wait(smem_u32(&tempty_bar[buf]), (use & 1) ^ 1, &gave_up);   // both epilogues have drained this accumulator
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t acc = tmem_base + buf * TN;
+                for (int kb = 0; kb < num_kb; kb++, it++) {
+                    const uint32_t s = it % STAGES;
+                    ok &= mbar_wait(smem_u32(&full_bar[s]), (it / STAGES) & 1, &gave_up);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_src = tiles + s * STAGE_BYTES3, b_src = a_src + A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; k++) {
+                        const uint64_t da = smem_desc(a_src + k * UMMA_K * 2, 16, 1024);
+                        const uint64_t db = B_IS_NK ? smem_desc(b_src + k * UMMA_K * 2, 16, 1024) : smem_desc(b_src + k * UMMA_K * 128, 8192, 1024);
+                        umma_f16_pair(acc, da, db, idesc, (kb | k) != 0);
+                    }
+                    umma_commit_pair(smem_u32(&empty_bar[s]));
+                }
+                umma_commit_pair(smem_u32(&tfull_bar[buf]));
+            }
+        }
+    } else {
+        const int ew = warp & 3;
+        uint32_t local = 0;
+        for (int t = pair; t < num_tiles && ok; t += pairs, local++) {
+            int mi, ni;
+            tile_coords(t, tiles_m, tiles_n, &mi, &ni);
+            const uint32_t buf = local & 1, use = local >> 1;
+            ok &= mbar_wait(smem_u32(&tfull_bar[buf]), use & 1, &gave_up);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            __half* crow = C + (size_t)(mi * TM + (int)rank * BM + ew * 32 + lane) * N + (size_t)ni * TN;
+            const uint32_t src = tmem_base + buf * TN + ((uint32_t)(ew * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < TN; c += 32) {
+                uint32_t r[32];
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                    "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+                      "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+                      "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
+                      "=r"(r[31])
+                    : "r"(src + (uint32_t)c));
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                uint32_t h[16];
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    __half2 v = __floats2half2_rn(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+                    h[i] = *reinterpret_cast<uint32_t*>(&v);
+                }
+#pragma unroll
+                for (int q = 0; q < 4; q++) *reinterpret_cast<uint4*>(crow + c + 8 * q) = make_uint4(h[4 * q], h[4 * q + 1], h[4 * q + 2], h[4 * q + 3]);
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[buf]), 0));
+        }
+    }
+    if (!ok && status) atomicExch(status, 1);
+    __syncwarp();
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();   // the peer has stopped naming this CTA's barriers, shared and tensor memory
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS3) : "memory");
+}
+}  // namespace v3
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
@@ -416,6 +626,30 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, __half* C, i
     return basalt_k::record(cudaGetLastError(), "matmul_f16");
 }
 
+
+template <bool B_IS_NK>
+int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, __half* C, int M, int N, int K, int32_t* status, cudaStream_t s) {
+    constexpr int smem = v3::STAGES * v3::STAGE_BYTES3 + 1024;
+    auto kern = v3::matmul_f16_tc_pair<B_IS_NK>;
+    static int max_pairs = 0;
+    if (!max_pairs) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return basalt_k::record(e, "matmul_f16 (shared memory size)");
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * basalt_k::sm_count());
+        cfg.blockDim = dim3(v3::THREADS3);
+        cfg.dynamicSmemBytes = smem;
+        int n = 0;
+        e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);   // the kernel's own __cluster_dims__ (2,1,1) applies
+        if (e != cudaSuccess || n < 1) { (void)cudaGetLastError(); n = basalt_k::sm_count() / 2; }
+        max_pairs = n;
+    }
+    const int tiles = (M / v3::TM) * (N / v3::TN);
+    const int pairs = tiles < max_pairs ? tiles : max_pairs;
+    kern<<<2 * pairs, v3::THREADS3, smem, s>>>(ma, mb, C, M, N, K, status);
+    return basalt_k::record(cudaGetLastError(), "matmul_f16");
+}
+
 }  // namespace
 
 extern "C" int basalt_k_matmul_f16(const void* A, const void* B, void* C, int M, int N, int K, int b_is_nk, int32_t* status, void* stream) {
@@ -426,6 +660,11 @@ extern "C" int basalt_k_matmul_f16(const void* A, const void* B, void* C, int M,
     int rc = make_map(&ma, A, (uint64_t)M, (uint64_t)K, BK, BM);
     if (rc) return rc;
     cudaStream_t s = (cudaStream_t)stream;
+    if (M % v3::TM == 0 && N % v3::TN == 0 && !getenv("BASALT_K_MATMUL_NO_PAIR")) {   // 256 x 256 tiles on pairs of SMs
+        rc = b_is_nk ? make_map(&mb, B, (uint64_t)N, (uint64_t)K, BK, v3::HALF_N) : make_map(&mb, B, (uint64_t)K, (uint64_t)N, 64, BK);
+        if (rc) return rc;
+        return b_is_nk ? launch_pair<true>(ma, mb, (__half*)C, M, N, K, status, s) : launch_pair<false>(ma, mb, (__half*)C, M, N, K, status, s);
+    }
     if (N % v2::BN2 == 0) {   // 128 x 256 tiles, persistent
         rc = b_is_nk ? make_map(&mb, B, (uint64_t)N, (uint64_t)K, BK, v2::BN2) : make_map(&mb, B, (uint64_t)K, (uint64_t)N, 64, BK);
         if (rc) return rc;

@@ -735,14 +735,14 @@ int basalt_rt_peer_group_connect(basalt_rt_peer_group* g, const unsigned char* h
     return 0;
 }
 
-int basalt_rt_peer_allreduce_max_i32(basalt_rt_peer_group* g, uint64_t partial, uint64_t result, void* stream) {
+int basalt_rt_peer_allreduce_max_i32(basalt_rt_peer_group* g, uint64_t partial, uint64_t result, int reset, int32_t reset_value, void* stream) {
     if (!g || !partial || !result) return set_err(4, 0, "basalt_rt_peer_allreduce_max_i32", "null argument");
     if (!g->connected) return set_err(4, 0, "basalt_rt_peer_allreduce_max_i32", "the group is not connected");
     int rc = make_current(g->ctx);
     if (rc) return rc;
     if (++g->epoch == 0) g->epoch = 1;
-    int krc = basalt_k_peer_allreduce_max_i32(g->inbox, g->nranks, g->rank, g->epoch, (const int32_t*)(uintptr_t)partial, (int32_t*)(uintptr_t)result,
-                                              (uint32_t*)(uintptr_t)(g->own + kPeerStatusOffset), kPeerTimeoutNs, stream);
+    int krc = basalt_k_peer_allreduce_max_i32(g->inbox, g->nranks, g->rank, g->epoch, (int32_t*)(uintptr_t)partial, (int32_t*)(uintptr_t)result,
+                                              (uint32_t*)(uintptr_t)(g->own + kPeerStatusOffset), kPeerTimeoutNs, reset, reset_value, stream);
     if (krc != 0) return set_err(3, krc, "basalt_k_peer_allreduce_max_i32", basalt_k_last_error());
     return 0;
 }

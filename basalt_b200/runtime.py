@@ -358,8 +358,10 @@ class PeerGroup:
         blob = b"".join(handles)
         _check(lib.basalt_rt_peer_group_connect(self._h, blob, len(blob)))
 
-    def allreduce_max_i32(self, partial_ptr: int, result_ptr: int, stream=None):
-        _check(lib.basalt_rt_peer_allreduce_max_i32(self._h, partial_ptr, result_ptr, C.c_void_p(stream)))
+    def allreduce_max_i32(self, partial_ptr: int, result_ptr: int, stream=None, reset_to: int | None = None):
+        """`reset_to`: value stored into the partial word once it has been read (None leaves it)."""
+        _check(lib.basalt_rt_peer_allreduce_max_i32(self._h, partial_ptr, result_ptr, 0 if reset_to is None else 1,
+                                                    0 if reset_to is None else reset_to, C.c_void_p(stream)))
 
     def status(self) -> int:
         """Synchronises the context; non-zero bits name ranks that did not answer within the bound."""

@@ -402,19 +402,25 @@ def main():
     # is in `result`.  (Issuing the collective on a second stream to overlap it with the next
     # step's kernel was measured and is slower: the collective's CTA takes a slot of the one-wave
     # grid and the displaced CTA runs as a second wave.)
+    def reset():
+        if peers is None:
+            partial.copy_(lowest)                              # a 4-byte device copy resets the running maximum
+
     def exchange():
-        if peers is not None:
-            peers.allreduce_max_i32(partial.data_ptr(), result.data_ptr(), stream)
+        if peers is not None:                                  # also resets `partial` for the next step
+            peers.allreduce_max_i32(partial.data_ptr(), result.data_ptr(), stream, reset_to=-2**31)
         elif comm is not None:
             comm.allreduce_max_i32(partial.data_ptr(), result.data_ptr(), 1, stream)
 
+    partial.copy_(lowest)
+
     def step_emitted():
-        partial.copy_(lowest)                                  # a 4-byte device copy resets the running maximum
+        reset()
         launch_emitted()                                       # basalt_rt_launch: the emitted sm_100a kernel
         exchange()
 
     def step_hand():
-        partial.copy_(lowest)
+        reset()
         kernels.max_i32(x.data_ptr(), n, partial.data_ptr(), stream)
         exchange()
 
@@ -447,6 +453,7 @@ def main():
         e0.record(); launch_emitted(); e1.record()
     torch.cuda.synchronize()
     kernel_ms = statistics.mean(e0.elapsed_time(e1) for e0, e1 in ev)
+    partial.copy_(lowest)
     for _ in range(args.warmup):
         step_hand()
     hand_ms = timed_loop(step_hand, args.steps) / args.steps

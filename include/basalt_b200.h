@@ -203,14 +203,16 @@ int basalt_rt_allgather(basalt_rt_comm *comm, uint64_t send, uint64_t recv, size
  * rank creates a group (which allocates and zeroes its inbox), exports the inbox as a CUDA IPC
  * handle (64 bytes), receives every rank's handle through whatever channel the host program has
  * (torch.distributed in bench.py and the tests), and connects.  basalt_rt_peer_allreduce_max_i32
- * then launches basalt_k_peer_allreduce_max_i32 on `stream` with the next epoch.  `status` reads
+ * then launches basalt_k_peer_allreduce_max_i32 on `stream` with the next epoch (`reset`: store
+ * reset_value into *partial after reading it).  `status` reads
  * the device word after synchronising: non-zero bits are ranks that did not answer within the
  * bound (2 s).  No counterpart in the reference (single GPU only). */
 typedef struct basalt_rt_peer_group basalt_rt_peer_group;
 int basalt_rt_peer_group_create(basalt_rt_ctx *ctx, int nranks, int rank, basalt_rt_peer_group **out);
 int basalt_rt_peer_group_handle(basalt_rt_peer_group *g, unsigned char handle_out[64]);
 int basalt_rt_peer_group_connect(basalt_rt_peer_group *g, const unsigned char *handles, size_t nbytes);
-int basalt_rt_peer_allreduce_max_i32(basalt_rt_peer_group *g, uint64_t partial, uint64_t result, void *stream);
+int basalt_rt_peer_allreduce_max_i32(basalt_rt_peer_group *g, uint64_t partial, uint64_t result, int reset,
+                                     int32_t reset_value, void *stream);
 int basalt_rt_peer_group_status(basalt_rt_peer_group *g, uint32_t *status_out);
 int basalt_rt_peer_group_destroy(basalt_rt_peer_group *g);
 

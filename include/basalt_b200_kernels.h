@@ -59,12 +59,14 @@ int basalt_k_matmul_f16(const void *A, const void *B, void *C, int M, int N, int
  * the calls from 1 and must be the same on every rank; all ranks must make the same calls in the
  * same order.  *partial is this rank's value, *result receives the maximum over all ranks; both
  * are device pointers and the call is ordered on `stream`.  A peer that has not answered after
- * timeout_ns sets bit r of *status (device uint32) and is left out of the result.  No counterpart
- * in the reference, which has no multi-GPU path. */
+ * timeout_ns sets bit r of *status (device uint32) and is left out of the result.  With `reset`
+ * non-zero, *partial is set to reset_value once it has been read, ready for the next accumulation
+ * (the reduction kernel folds into it with atomicMax).  No counterpart in the reference, which has
+ * no multi-GPU path. */
 #define BASALT_K_MAX_PEERS 8
 int basalt_k_peer_allreduce_max_i32(const uint64_t *inboxes, int nranks, int rank, uint32_t epoch,
-                                    const int32_t *partial, int32_t *result, uint32_t *status,
-                                    uint64_t timeout_ns, void *stream);
+                                    int32_t *partial, int32_t *result, uint32_t *status,
+                                    uint64_t timeout_ns, int reset, int32_t reset_value, void *stream);
 
 #if defined(__GNUC__)
 #pragma GCC visibility pop
