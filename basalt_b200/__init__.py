@@ -4,7 +4,7 @@ and 1/2/4/8-GPU sharding -- behind the reference's own Backend and runtime inter
 
 Names are resolved on first use, so `python -m basalt_b200.build` can run before the native
 library exists; anything else raises ImportError until it has been built."""
-_BACKEND = ("Artifact", "Diag", "EmitOpts", "Ptx", "Support", "roundtrip", "compile_cuda")
+_BACKEND = ("Artifact", "Diag", "EmitOpts", "Ptx", "Support", "roundtrip", "compile_cuda", "compile_triton")
 _RUNTIME = ("Communicator", "PeerGroup", "CudaContext", "CudaDriver", "CudaError", "CudaFunction", "CudaModule", "DeviceBuffer", "f32", "f64",
             "i32", "i64", "ptr", "shard_range")
 __all__ = list(_BACKEND + _RUNTIME)

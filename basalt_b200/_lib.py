@@ -45,6 +45,7 @@ def _load() -> C.CDLL:
         "basalt_b200_optimize": (C.c_int, [cp, sz, P(EmitOpts), P(vp), P(sz), P(DiagStruct)]),
         "basalt_b200_roundtrip": (C.c_int, [cp, sz, P(vp), P(sz), P(DiagStruct)]),
         "basalt_b200_compile_cuda": (C.c_int, [cp, sz, P(vp), P(sz), P(DiagStruct)]),
+        "basalt_b200_compile_triton": (C.c_int, [cp, sz, cp, P(vp), P(sz), P(DiagStruct)]),
         "basalt_b200_free": (None, [vp]),
         "basalt_rt_last_error": (None, [P(RtError)]),
         "basalt_rt_driver_load": (C.c_int, [P(vp)]),

@@ -95,3 +95,18 @@ def compile_cuda(source: str) -> str:
     (crates/basalt-cli/src/main.rs:286-327; crates/basalt-frontend-c, crates/basalt-sema/src/lower.rs).
     Raises Diag with the reference's front-end codes (E200-E202, E300-E304, E308)."""
     return _text_call(lib.basalt_b200_compile_cuda, source, False)
+
+
+def compile_triton(source: str, constexprs: dict | None = None, pointee: dict | None = None, num_warps: int | None = None,
+                   min_blocks: int | None = None) -> str:
+    """`@triton.jit` source -> tile-level BIR text: the front half of the reference CLI's Triton lane
+    (crates/basalt-cli/src/main.rs:329-372), with tl.dot lowered to `mma` and a program mapped to a
+    CTA.  `constexprs` binds tl.constexpr parameters that have no literal default, `pointee` names
+    the element type behind pointer parameters ("f16", "f32", "f64", "i64"; f32 when absent),
+    `num_warps` the CTA size the kernel is compiled for."""
+    items = [f"{k}={int(v)}" for k, v in (constexprs or {}).items()] + [f"{k}=*{v}" for k, v in (pointee or {}).items()]
+    if num_warps is not None:
+        items.append(f"num_warps={int(num_warps)}")
+    if min_blocks is not None:
+        items.append(f"min_blocks={int(min_blocks)}")
+    return _text_call(lib.basalt_b200_compile_triton, source, " ".join(items).encode())

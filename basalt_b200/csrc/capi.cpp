@@ -6,6 +6,7 @@
 #include "../../include/basalt_b200.h"
 #include "emit.hpp"
 #include "frontend_c.hpp"
+#include "frontend_triton.hpp"
 
 using namespace basalt;
 
@@ -103,6 +104,19 @@ int basalt_b200_compile_cuda(const char* src, size_t len, char** bir_out, size_t
     Module m;
     Diag dg;
     if (!compile_cuda_c(src, len, &m, &dg)) { fill_diag(diag_out, dg.code, dg.arg); return 1; }
+    if (bir_out) *bir_out = dup_out(print_module(m), bir_len);
+    return 0;
+}
+
+int basalt_b200_compile_triton(const char* src, size_t len, const char* bindings, char** bir_out, size_t* bir_len, basalt_diag* diag_out) {
+    if (bir_out) *bir_out = nullptr;
+    if (!src) { fill_diag(diag_out, "E500", "null input"); return 1; }
+    TritonOptions opts;
+    std::string why;
+    if (!parse_triton_bindings(bindings, &opts, &why)) { fill_diag(diag_out, "E102", "invalid bindings: " + why); return 1; }
+    Module m;
+    Diag dg;
+    if (!compile_triton(src, len, opts, &m, &dg)) { fill_diag(diag_out, dg.code, dg.arg); return 1; }
     if (bir_out) *bir_out = dup_out(print_module(m), bir_len);
     return 0;
 }

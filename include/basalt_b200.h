@@ -75,6 +75,20 @@ int basalt_b200_roundtrip(const char *bir, size_t len, char **bir_out, size_t *b
 int basalt_b200_compile_cuda(const char *src, size_t len, char **bir_out, size_t *bir_len,
                              basalt_diag *diag_out);
 
+/* The front half of the reference CLI's Triton lane (crates/basalt-cli/src/main.rs:329-372:
+ * parse, check_triton, lower_triton) for `@triton.jit` kernels, re-thought for a GPU: a program
+ * is a CTA, elementwise tile code is a loop over lanes strided by the CTA's thread count, and
+ * tl.dot is BIR's `mma` (the reference lowers it to a scalar triple loop because its back ends
+ * refuse `mma`, crates/basalt-sema/src/triton_lower.rs:9-31).  `bindings` is NULL or a
+ * space-separated list: `NAME=<int>` gives a tl.constexpr parameter without a literal default its
+ * compile-time value, `NAME=*f16|*f32|*f64|*i64` the element type behind a pointer parameter
+ * (f32 when absent, the reference's assumption, triton_lower.rs:72-84), `num_warps=<n>` the CTA
+ * size the kernel is compiled for (Triton's launch option).  The kernel ABI is the reference's
+ * (triton_lower.rs:517-551): parameters in source order, pointers as ptr.global, scalars as i64,
+ * constexpr parameters with a literal default dropped.  Refusals: E200/E201/E202, E300-E307. */
+int basalt_b200_compile_triton(const char *src, size_t len, const char *bindings, char **bir_out,
+                               size_t *bir_len, basalt_diag *diag_out);
+
 void basalt_b200_free(void *p);
 
 /* ------------------------------------------------------------------------------------------
