@@ -1,0 +1,65 @@
+"""Triton sources through the whole path on the device: front end -> BIR -> sm_100a PTX -> JIT ->
+launch, with a program per CTA.  The masked vector add is bit-exact against its definition (no
+lane at or past n is read or written); the tiled matmuls are checked against the CPU oracle with
+the benchmark's tolerances (SGEMM 1e-4, f16 2e-3 relative Frobenius) and exactly on small
+integers."""
+import numpy as np
+import pytest
+
+import basalt_b200 as b
+from basalt_b200 import kernels_triton as kt, workloads as w
+from _gpu import dev, emitted
+from _util import orc_matmul_f16_rows, orc_sgemm_rows, rel_fro, sgemm_fixture
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("level", [0, 2])
+@pytest.mark.parametrize("block_size, threads", [(1024, 256), (1024, 1024), (256, 64), (96, 128)])
+def test_masked_vector_add(gpu, level, block_size, threads):
+    fn = emitted(gpu, kt.vector_add(), "vector_add", level)
+    for n in [1, 1000, 4099, (1 << 18) + 5]:
+        a = w.f32_pm1(11, n); bb = w.f32_pm1(12, n)
+        programs = (n + block_size - 1) // block_size
+        # the buffers end exactly at n: a lane past n that loaded or stored would run off the allocation's data
+        da, db = dev(gpu, a), dev(gpu, bb)
+        dc = dev(gpu, np.full(programs * block_size + 8, -1.0, np.float32))
+        fn.launch(programs, threads, 0, [da, db, dc, b.i64(n), b.i64(block_size)])
+        got = dc.to_numpy(np.float32)
+        assert np.array_equal(got[:n], a + bb) and np.all(got[n:] == -1.0), (n, block_size, threads)
+
+
+def test_small_matmul_fixture(gpu):
+    # examples/cpu_launch_triton_matmul.c:39-89 on the device: one program, any CTA size
+    A, B, C = sgemm_fixture(4, 3, 5)
+    fn = emitted(gpu, kt.small_matmul(5), "matmul_kernel")
+    for threads in (1, 32, 128):
+        out = dev(gpu, np.full((4, 3), np.nan, np.float32))
+        fn.launch(1, threads, 0, [dev(gpu, A), dev(gpu, B), dev(gpu, C), out, b.i64(5)])
+        assert np.array_equal(out.to_numpy(np.float32).reshape(4, 3), A @ B + C), threads
+
+
+def test_tiled_sgemm(gpu, orc):
+    M, N, K = 256, 384, 128
+    A, B, _ = sgemm_fixture(M, N, K)
+    dC = dev(gpu, np.full((M, N), np.nan, np.float32))
+    emitted(gpu, kt.sgemm(M, N, K), "sgemm_f32").launch((N // 128, M // 128), 256, 0, [dev(gpu, A), dev(gpu, B), dC, b.i64(M), b.i64(N), b.i64(K)])
+    assert np.array_equal(dC.to_numpy(np.float32).reshape(M, N), (A.astype(np.int64) @ B.astype(np.int64)).astype(np.float32))
+    A = w.f32_pm1(w.SEEDS["sgemm_f32"], M * K).reshape(M, K)
+    B = w.f32_pm1(w.SEEDS["sgemm_f32"] + 1, K * N).reshape(K, N)
+    dC = dev(gpu, np.full((M, N), np.nan, np.float32))
+    emitted(gpu, kt.sgemm(M, N, K), "sgemm_f32").launch((N // 128, M // 128), 256, 0, [dev(gpu, A), dev(gpu, B), dC, b.i64(M), b.i64(N), b.i64(K)])
+    assert rel_fro(dC.to_numpy(np.float32).reshape(M, N), orc_sgemm_rows(orc, A, B, 0, M)) <= 1e-4
+
+
+@pytest.mark.parametrize("shape", [(128, 128, 64), (256, 512, 1024), (384, 256, 192)])
+def test_tiled_matmul_f16_on_tensor_cores(gpu, orc, shape):
+    M, N, K = shape
+    A = w.f16_normal01(w.SEEDS["matmul_f16"], M * K).reshape(M, K)
+    B = w.f16_normal01(w.SEEDS["matmul_f16"] + 1, K * N).reshape(K, N)
+    fn = emitted(gpu, kt.matmul_f16(M, N, K), "matmul_kernel")
+    dC = dev(gpu, np.full((M, N), np.nan, np.float16))
+    fn.launch((N // 128, M // 128), 128, 0, [dev(gpu, A), dev(gpu, B), dC, b.i64(M), b.i64(N), b.i64(K)])
+    assert fn.status() == 0, "a bounded wait inside the emitted kernel expired"
+    got = dC.to_numpy(np.float16).reshape(M, N)
+    assert rel_fro(got, orc_matmul_f16_rows(orc, A, B, N, False, 0, M)) <= 2e-3
