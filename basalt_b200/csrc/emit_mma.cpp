@@ -48,6 +48,13 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
     const long long lda = in.ld[0] ? in.ld[0] : in.k, ldb = in.ld[1] ? in.ld[1] : in.n, ldd = in.ld[3] ? in.ld[3] : in.n;
     if (lda % 4 || ldb % 4 || ldd % 4 || lda * 4 >= (1ll << 31) || ldb * 4 >= (1ll << 31) || ldd * 4 >= (1ll << 31)) return false;
     const int u = s.uid, nk = (int)(in.k / 16);
+    // Tail-wave form: when the kernel is nothing but this op on a tiled grid (operand pointers are the
+    // parameters plus constant multiples of the block indices), the CTA decodes its tile from a linear
+    // index instead, so that the launch runtime can issue whole tiles first and the tiles of a sparse
+    // last wave as K-parts that fill one wave (the parts are summed in index order by the part that
+    // finishes last; see kernels/sgemm.cu for the same scheme in CUDA).
+    const bool tail = s.affine && s.pure_kernel && s.sole_mma && s.extra_params && s.a_c0 == 0 && s.a_cx == 0 && s.a_cy == 128 * lda * 4 && s.b_c0 == 0 &&
+                      s.b_cy == 0 && s.b_cx == 512 && s.d_c0 == 0 && s.d_cx == 512 && s.d_cy == 128 * ldd * 4 && in.k < (1u << 30);
     char nm[64];
     auto R = [&](const char* stem, int i = -1) {
         if (i < 0) snprintf(nm, sizeof nm, "%%mm%d_%s", u, stem);
@@ -64,6 +71,25 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
     decls->push_back(d);
     snprintf(d, sizeof d, "\t.reg .pred %%mm%d_more, %%mm%d_bad;", u, u);
     decls->push_back(d);
+    if (tail) {
+        snprintf(d, sizeof d, "\t.reg .b32 %%mm%d_cid, %%mm%d_full, %%mm%d_split, %%mm%d_tile, %%mm%d_part, %%mm%d_parts, %%mm%d_lgx, %%mm%d_bx, %%mm%d_by, %%mm%d_klen, %%mm%d_kbeg, %%mm%d_nk, %%mm%d_tt, %%mm%d_tk, %%mm%d_p;",
+                 u, u, u, u, u, u, u, u, u, u, u, u, u, u, u);
+        decls->push_back(d);
+        snprintf(d, sizeof d, "\t.reg .b64 %%mm%d_ta, %%mm%d_tb, %%mm%d_td, %%mm%d_ws, %%mm%d_tkp, %%mm%d_pp;", u, u, u, u, u, u);
+        decls->push_back(d);
+        snprintf(d, sizeof d, "\t.reg .pred %%mm%d_whole, %%mm%d_one, %%mm%d_t0, %%mm%d_notlast, %%mm%d_pl;", u, u, u, u, u);
+        decls->push_back(d);
+        snprintf(d, sizeof d, "\t.reg .f32 %%mm%d_q<8>;", u);
+        decls->push_back(d);
+        snprintf(d, sizeof d, "\t.shared .align 4 .b8 __mm%d_tks[4];", u);
+        decls->push_back(d);
+        s.extra_params->push_back(".param .u32 " + s.kernel + "_lgrid_x");
+        s.extra_params->push_back(".param .u32 " + s.kernel + "_lgrid_y");
+        s.extra_params->push_back(".param .u32 " + s.kernel + "_full_tiles");
+        s.extra_params->push_back(".param .u32 " + s.kernel + "_split");
+        s.extra_params->push_back(".param .u64 " + s.kernel + "_workspace");
+        s.extra_params->push_back(".param .u64 " + s.kernel + "_tickets");
+    }
     snprintf(d, sizeof d, "\t.shared .align 16 .b8 __mm%d_as[16384];", u);
     decls->push_back(d);
     snprintf(d, sizeof d, "\t.shared .align 16 .b8 __mm%d_bs[16384];", u);
@@ -91,13 +117,49 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
     o("shr.u32 %s, %s, 5;", brow.c_str(), tid.c_str());
     o("and.b32 %s, %s, 31;", t.c_str(), tid.c_str());
     o("shl.b32 %s, %s, 2;", bcol.c_str(), t.c_str());
+    std::string abase = s.a, bbase = s.b, dbase = s.d;
+    if (tail) {
+        const std::string cid = R("cid"), full = R("full"), split = R("split"), tile = R("tile"), part = R("part"), parts = R("parts"), lgx = R("lgx"), bx = R("bx"), by = R("by");
+        const std::string klen = R("klen"), kbeg = R("kbeg"), nkr = R("nk"), whole = R("whole"), ta = R("ta"), tb = R("tb"), td = R("td");
+        o("ld.param.u32 %s, [%s_lgrid_x];", lgx.c_str(), s.kernel.c_str());
+        o("ld.param.u32 %s, [%s_full_tiles];", full.c_str(), s.kernel.c_str());
+        o("ld.param.u32 %s, [%s_split];", split.c_str(), s.kernel.c_str());
+        o("mov.u32 %s, %%ctaid.x;", cid.c_str());
+        o("setp.lt.u32 %s, %s, %s;", whole.c_str(), cid.c_str(), full.c_str());
+        o("sub.u32 %s, %s, %s;", t.c_str(), cid.c_str(), full.c_str());
+        o("div.u32 %s, %s, %s;", tile.c_str(), t.c_str(), split.c_str());
+        o("rem.u32 %s, %s, %s;", part.c_str(), t.c_str(), split.c_str());
+        o("add.u32 %s, %s, %s;", tile.c_str(), tile.c_str(), full.c_str());
+        o("selp.u32 %s, %s, %s, %s;", tile.c_str(), cid.c_str(), tile.c_str(), whole.c_str());
+        o("selp.u32 %s, 0, %s, %s;", part.c_str(), part.c_str(), whole.c_str());
+        o("selp.u32 %s, 1, %s, %s;", parts.c_str(), split.c_str(), whole.c_str());
+        o("div.u32 %s, %s, %s;", by.c_str(), tile.c_str(), lgx.c_str());
+        o("rem.u32 %s, %s, %s;", bx.c_str(), tile.c_str(), lgx.c_str());
+        o("mov.u32 %s, %u;", klen.c_str(), in.k);
+        o("div.u32 %s, %s, %s;", klen.c_str(), klen.c_str(), parts.c_str());
+        o("mul.lo.u32 %s, %s, %s;", kbeg.c_str(), part.c_str(), klen.c_str());
+        o("shr.u32 %s, %s, 4;", nkr.c_str(), klen.c_str());
+        // tile pointers: A + by*128*lda*4 + kbeg*4 ; B + bx*512 + kbeg*ldb*4 ; D + by*128*ldd*4 + bx*512
+        o("mul.wide.u32 %s, %s, %lld;", w.c_str(), by.c_str(), 128 * lda * 4);
+        o("add.u64 %s, %s, %s;", ta.c_str(), s.a_base.c_str(), w.c_str());
+        o("mul.wide.u32 %s, %s, 4;", w.c_str(), kbeg.c_str());
+        o("add.u64 %s, %s, %s;", ta.c_str(), ta.c_str(), w.c_str());
+        o("mul.wide.u32 %s, %s, 512;", w.c_str(), bx.c_str());
+        o("add.u64 %s, %s, %s;", tb.c_str(), s.b_base.c_str(), w.c_str());
+        o("add.u64 %s, %s, %s;", td.c_str(), s.d_base.c_str(), w.c_str());
+        o("mul.wide.u32 %s, %s, %lld;", w.c_str(), kbeg.c_str(), ldb * 4);
+        o("add.u64 %s, %s, %s;", tb.c_str(), tb.c_str(), w.c_str());
+        o("mul.wide.u32 %s, %s, %lld;", w.c_str(), by.c_str(), 128 * ldd * 4);
+        o("add.u64 %s, %s, %s;", td.c_str(), td.c_str(), w.c_str());
+        abase = ta; bbase = tb; dbase = td;
+    }
     o("mul.wide.u32 %s, %s, %lld;", w.c_str(), arow.c_str(), lda * 4);
-    o("add.u64 %s, %s, %s;", ag.c_str(), s.a.c_str(), w.c_str());
+    o("add.u64 %s, %s, %s;", ag.c_str(), abase.c_str(), w.c_str());
     o("mul.wide.u32 %s, %s, 4;", w.c_str(), acol.c_str());
     o("add.u64 %s, %s, %s;", ag.c_str(), ag.c_str(), w.c_str());
     o("add.u64 %s, %s, %lld;", ag2.c_str(), ag.c_str(), 64 * lda * 4);
     o("mul.wide.u32 %s, %s, %lld;", w.c_str(), brow.c_str(), ldb * 4);
-    o("add.u64 %s, %s, %s;", bg.c_str(), s.b.c_str(), w.c_str());
+    o("add.u64 %s, %s, %s;", bg.c_str(), bbase.c_str(), w.c_str());
     o("mul.wide.u32 %s, %s, 4;", w.c_str(), bcol.c_str());
     o("add.u64 %s, %s, %s;", bg.c_str(), bg.c_str(), w.c_str());
     o("add.u64 %s, %s, %lld;", bg2.c_str(), bg.c_str(), 8 * ldb * 4);
@@ -135,7 +197,8 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
     o("bar.sync 0;");
     o.label(l_loop);
     o("add.u32 %s, %s, 1;", kb1.c_str(), kb.c_str());
-    o("setp.lt.u32 %s, %s, %d;", more.c_str(), kb1.c_str(), nk);
+    if (tail) o("setp.lt.u32 %s, %s, %s;", more.c_str(), kb1.c_str(), R("nk").c_str());
+    else o("setp.lt.u32 %s, %s, %d;", more.c_str(), kb1.c_str(), nk);
     o("add.u64 %s, %s, 64;", ag.c_str(), ag.c_str());
     o("add.u64 %s, %s, 64;", ag2.c_str(), ag2.c_str());
     o("add.u64 %s, %s, %lld;", bg.c_str(), bg.c_str(), 16 * ldb * 4);
@@ -158,10 +221,68 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
     o("mov.u32 %s, %s;", kb.c_str(), kb1.c_str());
     o("bra %s;", l_loop.c_str());
     o.label(l_done);
+    if (tail) {
+        const std::string parts = R("parts"), part = R("part"), tile = R("tile"), full = R("full"), tt = R("tt"), tk = R("tk"), pv = R("p");
+        const std::string ws = R("ws"), tkp = R("tkp"), pp = R("pp"), one = R("one"), t0 = R("t0"), notlast = R("notlast"), pl = R("pl");
+        std::string l_store = "$mm" + std::to_string(u) + "_store", l_sum = "$mm" + std::to_string(u) + "_sum";
+        auto q = [&](int i) { return R("q", i); };
+        o("setp.eq.u32 %s, %s, 1;", one.c_str(), parts.c_str());
+        o("@%s bra %s;", one.c_str(), l_store.c_str());
+        // this part's partial sums: workspace + ((tile - full) * parts + part) * 64 KB, laid out [128][128]
+        o("ld.param.u64 %s, [%s_workspace];", ws.c_str(), s.kernel.c_str());
+        o("ld.param.u64 %s, [%s_tickets];", tkp.c_str(), s.kernel.c_str());
+        o("sub.u32 %s, %s, %s;", tt.c_str(), tile.c_str(), full.c_str());
+        o("mul.wide.u32 %s, %s, 4;", w.c_str(), tt.c_str());
+        o("add.u64 %s, %s, %s;", tkp.c_str(), tkp.c_str(), w.c_str());
+        o("mul.lo.u32 %s, %s, %s;", t.c_str(), tt.c_str(), parts.c_str());
+        o("mul.wide.u32 %s, %s, 65536;", w.c_str(), t.c_str());
+        o("add.u64 %s, %s, %s;", ws.c_str(), ws.c_str(), w.c_str());       // the tile's first part
+        o("mul.wide.u32 %s, %s, 2048;", w.c_str(), ty.c_str());             // row ty*4, 512 bytes per row
+        o("add.u64 %s, %s, %s;", ws.c_str(), ws.c_str(), w.c_str());
+        o("mul.wide.u32 %s, %s, 16;", w.c_str(), tx.c_str());
+        o("add.u64 %s, %s, %s;", ws.c_str(), ws.c_str(), w.c_str());       // + this thread's position inside a part
+        o("mul.wide.u32 %s, %s, 65536;", w.c_str(), part.c_str());
+        o("add.u64 %s, %s, %s;", pp.c_str(), ws.c_str(), w.c_str());
+        for (int i = 0; i < 8; i++) {
+            int off = ((i & 3) + (i >> 2) * 64) * 512;
+            o("st.global.v4.f32 [%s+%d], {%s, %s, %s, %s};", pp.c_str(), off, acc(i * 8).c_str(), acc(i * 8 + 1).c_str(), acc(i * 8 + 2).c_str(), acc(i * 8 + 3).c_str());
+            o("st.global.v4.f32 [%s+%d], {%s, %s, %s, %s};", pp.c_str(), off + 256, acc(i * 8 + 4).c_str(), acc(i * 8 + 5).c_str(), acc(i * 8 + 6).c_str(), acc(i * 8 + 7).c_str());
+        }
+        o("membar.gl;");
+        o("bar.sync 0;");
+        o("setp.eq.u32 %s, %s, 0;", t0.c_str(), tid.c_str());
+        o("mov.u64 %s, __mm%d_tks;", w.c_str(), u);
+        o("cvt.u32.u64 %s, %s;", x.c_str(), w.c_str());
+        o("@%s atom.global.add.u32 %s, [%s], 1;", t0.c_str(), tk.c_str(), tkp.c_str());
+        o("@%s st.shared.u32 [%s], %s;", t0.c_str(), x.c_str(), tk.c_str());
+        o("bar.sync 0;");
+        o("ld.shared.u32 %s, [%s];", tk.c_str(), x.c_str());
+        o("add.u32 %s, %s, 1;", tk.c_str(), tk.c_str());
+        o("setp.ne.u32 %s, %s, %s;", notlast.c_str(), tk.c_str(), parts.c_str());
+        o("@%s bra %s;", notlast.c_str(), l_skip.c_str());                  // another part finishes this tile
+        o("membar.gl;");
+        // the last part to arrive adds every part in index order, so the bits do not depend on who was last
+        for (int i = 0; i < 64; i++) o("mov.f32 %s, 0f00000000;", acc(i).c_str());
+        o("mov.u32 %s, 0;", pv.c_str());
+        o("mov.u64 %s, %s;", pp.c_str(), ws.c_str());
+        o.label(l_sum);
+        for (int i = 0; i < 8; i++) {
+            int off = ((i & 3) + (i >> 2) * 64) * 512;
+            o("ld.global.cg.v4.f32 {%s, %s, %s, %s}, [%s+%d];", q(0).c_str(), q(1).c_str(), q(2).c_str(), q(3).c_str(), pp.c_str(), off);
+            o("ld.global.cg.v4.f32 {%s, %s, %s, %s}, [%s+%d];", q(4).c_str(), q(5).c_str(), q(6).c_str(), q(7).c_str(), pp.c_str(), off + 256);
+            for (int j = 0; j < 8; j++) o("add.rn.f32 %s, %s, %s;", acc(i * 8 + j).c_str(), acc(i * 8 + j).c_str(), q(j).c_str());
+        }
+        o("add.u64 %s, %s, 65536;", pp.c_str(), pp.c_str());
+        o("add.u32 %s, %s, 1;", pv.c_str(), pv.c_str());
+        o("setp.lt.u32 %s, %s, %s;", pl.c_str(), pv.c_str(), parts.c_str());
+        o("@%s bra %s;", pl.c_str(), l_sum.c_str());
+        o("@%s st.global.u32 [%s], 0;", t0.c_str(), tkp.c_str());           // the ticket is back at zero for the next launch
+        o.label(l_store);
+    }
     // rows ty*4 + (i&3) + (i>>2)*64, columns tx*4 and tx*4 + 64
     o("shl.b32 %s, %s, 2;", t.c_str(), ty.c_str());
     o("mul.wide.u32 %s, %s, %lld;", w.c_str(), t.c_str(), ldd * 4);
-    o("add.u64 %s, %s, %s;", cp.c_str(), s.d.c_str(), w.c_str());
+    o("add.u64 %s, %s, %s;", cp.c_str(), dbase.c_str(), w.c_str());
     o("mul.wide.u32 %s, %s, 16;", w.c_str(), tx.c_str());
     o("add.u64 %s, %s, %s;", cp.c_str(), cp.c_str(), w.c_str());
     for (int i = 0; i < 8; i++) {
@@ -172,7 +293,8 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
     o.label(l_skip);
     o("bar.sync 0;");
     char pl[256];
-    snprintf(pl, sizeof pl, "//!basalt.plan %s block=256,1,1 params=%u", s.kernel.c_str(), s.nparams);
+    if (tail) snprintf(pl, sizeof pl, "//!basalt.plan %s block=256,1,1 params=%u tail=%u", s.kernel.c_str(), s.nparams, in.k);
+    else snprintf(pl, sizeof pl, "//!basalt.plan %s block=256,1,1 params=%u", s.kernel.c_str(), s.nparams);
     plan->push_back(pl);
     return true;
 }

@@ -5,6 +5,16 @@
 // K slab is copied from global memory straight into the other half of a shared-memory double
 // buffer with cp.async while the current one is multiplied (no staging registers).  Per K step a
 // thread issues 4 LDS.128 for 64 FFMA.  Two CTAs are resident per SM (32 KB shared each).
+//
+// Tail wave.  With R resident CTAs (2 per SM) and T tiles, the last T mod R tiles would run as a
+// mostly empty wave (4096^2 in 128x128 tiles: 1024 tiles on 296 slots is 3.46 waves, paid as 4).
+// When that tail is at most half a wave its tiles are split along K into s = min(4, R / tail)
+// parts, one CTA each, so the tail costs 1/s of a wave.  A part writes its 128x128 partial sums to
+// a workspace; the part that arrives last (a ticket counter per tile) adds the parts in index order
+// -- the result does not depend on arrival order -- stores the tile, and sets the counter back to
+// zero, so the workspace needs no clearing between launches.  The grid is one-dimensional: CTA c
+// below F (the full tiles) computes tile c over all of K; CTA F + s*t + p computes part p of tail
+// tile t.  CTAs are dispatched in index order, so the split parts form the last wave.
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -23,12 +33,23 @@ __device__ __forceinline__ void cp_async(void* smem_dst, const void* gmem_src) {
 constexpr int BM = 128, BN = 128, BK = 16, THREADS = 256;
 
 __global__ void __launch_bounds__(THREADS, 2) sgemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C,
-                                                               int M, int N, int K) {
+                                                               int M, int N, int K, int full_tiles, int split, float* __restrict__ workspace,
+                                                               unsigned* __restrict__ tickets) {
     // As holds the A slab transposed ([k][m]) so a thread's 4 consecutive rows are one float4.
     __shared__ __align__(16) float As[2][BK][BM];
     __shared__ __align__(16) float Bs[2][BK][BN];
+    __shared__ unsigned ticket_s;
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
-    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int tiles_n = N / BN;
+    int tile = blockIdx.x, part = 0, parts = 1;
+    if (tile >= full_tiles) {
+        const int r = tile - full_tiles;
+        tile = full_tiles + r / split;
+        part = r % split;
+        parts = split;
+    }
+    const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+    const int k_len = K / parts, k_begin = part * k_len;   // the launcher makes K / parts a multiple of BK
     (void)M;
 
     // global -> register staging: A slab is 128 rows x 16 floats (4 float4 per row), B slab is
@@ -36,9 +57,9 @@ __global__ void __launch_bounds__(THREADS, 2) sgemm_f32_kernel(const float* __re
     const int a_row = tid >> 2, a_col = (tid & 3) * 4;   // rows a_row and a_row + 64
     const int b_row = tid >> 5, b_col = (tid & 31) * 4;  // rows b_row and b_row + 8
     // four running pointers, advanced by one K slab per iteration
-    const float* Ag0 = A + (size_t)(m0 + a_row) * K + a_col;
+    const float* Ag0 = A + (size_t)(m0 + a_row) * K + k_begin + a_col;
     const float* Ag1 = Ag0 + (size_t)64 * K;
-    const float* Bg0 = B + (size_t)b_row * N + n0 + b_col;
+    const float* Bg0 = B + (size_t)(k_begin + b_row) * N + n0 + b_col;
     const float* Bg1 = Bg0 + (size_t)8 * N;
     const size_t b_step = (size_t)BK * N;
     // global -> shared with cp.async, no staging registers: A lands transposed as eight 4-byte
@@ -64,7 +85,7 @@ __global__ void __launch_bounds__(THREADS, 2) sgemm_f32_kernel(const float* __re
     copy_slab(0);
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
-    const int nk = K / BK;
+    const int nk = k_len / BK;
     for (int kb = 0; kb < nk; kb++) {
         const int buf = kb & 1;
         if (kb + 1 < nk) copy_slab(buf ^ 1);   // lands while this slab is multiplied
@@ -93,6 +114,38 @@ __global__ void __launch_bounds__(THREADS, 2) sgemm_f32_kernel(const float* __re
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
     }
+    if (parts > 1) {
+        // partial sums of this part: [tail tile][part][128][128]
+        const int t = tile - full_tiles;
+        float* mine = workspace + ((size_t)t * parts + part) * (BM * BN);
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            float* prow = mine + (ty * 4 + (i & 3) + (i >> 2) * 64) * BN + tx * 4;
+            *reinterpret_cast<float4*>(prow) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+            *reinterpret_cast<float4*>(prow + 64) = make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
+        }
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) ticket_s = atomicAdd(&tickets[t], 1u);
+        __syncthreads();
+        if (ticket_s != (unsigned)(parts - 1)) return;   // not the last part of this tile to finish
+        __threadfence();
+        const float* base = workspace + (size_t)t * parts * (BM * BN);
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const int off = (ty * 4 + (i & 3) + (i >> 2) * 64) * BN + tx * 4;
+            float4 lo = __ldcg(reinterpret_cast<const float4*>(base + off)), hi = __ldcg(reinterpret_cast<const float4*>(base + off + 64));
+            for (int p = 1; p < parts; p++) {   // parts are added in index order, whichever finished last
+                const float4 l2 = __ldcg(reinterpret_cast<const float4*>(base + (size_t)p * (BM * BN) + off));
+                const float4 h2 = __ldcg(reinterpret_cast<const float4*>(base + (size_t)p * (BM * BN) + off + 64));
+                lo.x += l2.x; lo.y += l2.y; lo.z += l2.z; lo.w += l2.w;
+                hi.x += h2.x; hi.y += h2.y; hi.z += h2.z; hi.w += h2.w;
+            }
+            acc[i][0] = lo.x; acc[i][1] = lo.y; acc[i][2] = lo.z; acc[i][3] = lo.w;
+            acc[i][4] = hi.x; acc[i][5] = hi.y; acc[i][6] = hi.z; acc[i][7] = hi.w;
+        }
+        if (tid == 0) tickets[t] = 0;   // ready for the next launch
+    }
 #pragma unroll
     for (int i = 0; i < 8; i++) {
         const int row = m0 + ty * 4 + (i & 3) + (i >> 2) * 64;
@@ -102,13 +155,63 @@ __global__ void __launch_bounds__(THREADS, 2) sgemm_f32_kernel(const float* __re
     }
 }
 
+// Split-K workspace of the tail wave, one per device, sized for the largest tail that is ever split
+// (half a wave of tiles times the parts that fill the wave: at most one partial tile per resident
+// CTA) plus one ticket per tail tile.  Allocated on first use and kept.
+struct TailWorkspace {
+    float* partials = nullptr;
+    unsigned* tickets = nullptr;
+    int slots = 0;
+};
+TailWorkspace* tail_workspace(int slots) {
+    static TailWorkspace per_device[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    TailWorkspace& w = per_device[dev];
+    if (w.slots >= slots) return &w;
+    if (w.partials) { cudaFree(w.partials); cudaFree(w.tickets); w = TailWorkspace{}; }
+    if (cudaMalloc(&w.partials, (size_t)slots * BM * BN * sizeof(float)) != cudaSuccess) { (void)cudaGetLastError(); return nullptr; }
+    if (cudaMalloc(&w.tickets, (size_t)slots * sizeof(unsigned)) != cudaSuccess || cudaMemset(w.tickets, 0, (size_t)slots * sizeof(unsigned)) != cudaSuccess) {
+        (void)cudaGetLastError();
+        cudaFree(w.partials);
+        w = TailWorkspace{};
+        return nullptr;
+    }
+    w.slots = slots;
+    return &w;
+}
+
+// Chooses the split of the tail wave: tiles [0, *full) run whole, the rest in *split parts each.
+void plan_tail(int tiles, int slots, int K, int* full, int* split) {
+    *full = tiles;
+    *split = 1;
+    const int tail = tiles % slots;
+    if (tiles < slots || tail == 0 || tail * 2 > slots) return;   // one wave or less, no tail, or a tail that is more than half full
+    int s = slots / tail;
+    if (s > 4) s = 4;
+    while (s > 1 && (K % (s * BK) != 0)) s--;
+    if (s < 2) return;
+    *full = tiles - tail;
+    *split = s;
+}
+
 }  // namespace
 
 extern "C" int basalt_k_sgemm_f32(const float* A, const float* B, float* C, int M, int N, int K, void* stream) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     if (M % BM || N % BN || K % BK) return basalt_k::record_msg(1, "sgemm_f32", "M and N must be multiples of 128 and K of 16");
     if (((uintptr_t)A | (uintptr_t)B | (uintptr_t)C) & 15) return basalt_k::record_msg(1, "sgemm_f32", "matrices must be 16-byte aligned");
-    dim3 grid(N / BN, M / BM);
-    sgemm_f32_kernel<<<grid, THREADS, 0, (cudaStream_t)stream>>>(A, B, C, M, N, K);
+    static int resident = 0;
+    if (!resident) resident = basalt_k::resident_ctas(sgemm_f32_kernel, THREADS);
+    const int tiles = (M / BM) * (N / BN), slots = resident * basalt_k::sm_count();
+    int full = tiles, split = 1;
+    plan_tail(tiles, slots, K, &full, &split);
+    TailWorkspace* w = nullptr;
+    if (split > 1) {
+        w = tail_workspace(slots);
+        if (!w) { full = tiles; split = 1; }   // no workspace: the plain schedule is still correct
+    }
+    const int grid = full + (tiles - full) * split;
+    sgemm_f32_kernel<<<grid, THREADS, 0, (cudaStream_t)stream>>>(A, B, C, M, N, K, full, split, w ? w->partials : nullptr, w ? w->tickets : nullptr);
     return basalt_k::record(cudaGetLastError(), "sgemm_f32");
 }

@@ -91,6 +91,10 @@ struct basalt_rt_ctx {
     // Device buffers kept between basalt_rt_cpu_launch calls, keyed by size: cuMemAlloc and
     // cuMemFree of a gigabyte cost more than the kernel they serve. Released with the context.
     std::multimap<size_t, CUdeviceptr> staging;
+    // Workspace of kernels whose plan says `tail=`: one 128x128 f32 partial tile per resident CTA and
+    // one ticket word per tile of a tail wave.  The kernels leave every ticket at zero.
+    CUdeviceptr tail_partials = 0, tail_tickets = 0;
+    unsigned tail_slots = 0;
 };
 namespace {
 struct TmapSpec {
@@ -110,6 +114,8 @@ struct Plan {
     std::string coarse;     // entry taking one more u64 parameter: the thread count the caller asked for
     bool status = false;    // the entry takes a u64 parameter: a device int32 set when a bounded wait gave up
     unsigned logical_block[3] = {0, 0, 0};   // block the caller must ask for when it differs from the block launched
+    unsigned tail_k = 0;    // FFMA matmul with a split-K tail wave (K extent): the caller's 2-D grid is re-issued as a 1-D grid of
+                            // whole tiles followed by K-parts of the tail tiles; six trailing parameters (see basalt_rt_launch)
     unsigned lgrid = 0;     // persistent kernel: the caller's grid goes in two trailing u32 parameters; lgrid logical CTAs
                             // along x form one tile, and min(SM count, tiles) CTAs are launched
 };
@@ -223,6 +229,7 @@ void parse_plans(const char* ptx, std::map<std::string, Plan>* out) {
             else if (k == "status") p.status = v != "0";
             else if (k == "logical_block") sscanf(v.c_str(), "%u,%u,%u", &p.logical_block[0], &p.logical_block[1], &p.logical_block[2]);
             else if (k == "lgrid") p.lgrid = (unsigned)strtoul(v.c_str(), nullptr, 10);
+            else if (k == "tail") p.tail_k = (unsigned)strtoul(v.c_str(), nullptr, 10);
             else if (k == "tmap") {
                 TmapSpec t;
                 unsigned long long inner = 0, rowb = 0;
@@ -321,6 +328,8 @@ int basalt_rt_ctx_create(basalt_rt_driver* drv, int device_index, basalt_rt_ctx*
 void basalt_rt_ctx_destroy(basalt_rt_ctx* ctx) {
     if (!ctx) return;
     for (auto& kv : ctx->staging) ctx->drv->f.cuMemFree(kv.second);
+    if (ctx->tail_partials) ctx->drv->f.cuMemFree(ctx->tail_partials);
+    if (ctx->tail_tickets) ctx->drv->f.cuMemFree(ctx->tail_tickets);
     ctx->drv->f.cuDevicePrimaryCtxRelease(ctx->dev);
     delete ctx;
 }
@@ -474,6 +483,54 @@ int basalt_rt_launch(basalt_rt_function* fn, const uint32_t grid[3], const uint3
         std::vector<void*> all(params, params + fn->plan.nparams);
         all.push_back(&logical);
         return check(f, "cuLaunchKernel", f.cuLaunchKernel(fn->coarse, phys, 1, 1, block[0], 1, 1, shared_mem_bytes, (CUstream)stream, all.data(), nullptr));
+    }
+    if (fn->has_plan && fn->plan.tail_k) {
+        // 128x128 tiles, one per logical CTA (grid x = tile column, y = tile row).  Whole tiles first,
+        // then the tiles of a sparse last wave split along K so that their parts fill one wave.
+        const Plan& p = fn->plan;
+        basalt_rt_ctx* ctx = fn->mod->ctx;
+        if (block[0] != p.block[0] || block[1] != p.block[1] || block[2] != p.block[2])
+            return set_err(4, 0, "cuLaunchKernel", "kernel was compiled for block (" + std::to_string(p.block[0]) + "," + std::to_string(p.block[1]) + "," + std::to_string(p.block[2]) + ")");
+        if (grid[2] != 1) return set_err(4, 0, "cuLaunchKernel", "kernel was compiled for a two-dimensional grid");
+        if (!params) return set_err(4, 0, "cuLaunchKernel", "kernel takes parameters");
+        uint32_t lgx = grid[0], lgy = grid[1];
+        const uint64_t tiles64 = (uint64_t)lgx * lgy;
+        if (tiles64 == 0) return 0;
+        if (tiles64 > 0x7fffffffull) return set_err(4, 0, "cuLaunchKernel", "grid too large");
+        const uint32_t tiles = (uint32_t)tiles64;
+        int resident = 0;
+        if (f.cuOccupancyMaxActiveBlocksPerMultiprocessor(&resident, fn->fn, (int)p.block[0], p.smem) != CUDA_SUCCESS || resident < 1) resident = 1;
+        const uint32_t slots = (uint32_t)ctx->sm_count * (uint32_t)resident;
+        uint32_t full = tiles, split = 1;
+        const uint32_t tail = tiles % slots;
+        if (tiles >= slots && tail != 0 && tail * 2 <= slots) {
+            uint32_t sp = slots / tail;
+            if (sp > 4) sp = 4;
+            while (sp > 1 && p.tail_k % (sp * 16) != 0) sp--;
+            if (sp >= 2) { full = tiles - tail; split = sp; }
+        }
+        if (split > 1 && ctx->tail_slots < slots) {
+            int rc = make_current(ctx);
+            if (rc) return rc;
+            if (ctx->tail_partials) { f.cuMemFree(ctx->tail_partials); f.cuMemFree(ctx->tail_tickets); ctx->tail_partials = ctx->tail_tickets = 0; ctx->tail_slots = 0; }
+            rc = check(f, "cuMemAlloc", f.cuMemAlloc(&ctx->tail_partials, (size_t)slots * 65536));
+            if (rc) return rc;
+            rc = check(f, "cuMemAlloc", f.cuMemAlloc(&ctx->tail_tickets, (size_t)slots * 4));
+            if (rc) { f.cuMemFree(ctx->tail_partials); ctx->tail_partials = 0; return rc; }
+            std::vector<uint32_t> zeros(slots, 0);
+            rc = check(f, "cuMemcpyHtoD", f.cuMemcpyHtoD(ctx->tail_tickets, zeros.data(), (size_t)slots * 4));
+            if (rc) return rc;
+            ctx->tail_slots = slots;
+        }
+        std::vector<void*> all(params, params + p.nparams);
+        uint64_t ws = (uint64_t)ctx->tail_partials, tk = (uint64_t)ctx->tail_tickets;
+        all.push_back(&lgx);
+        all.push_back(&lgy);
+        all.push_back(&full);
+        all.push_back(&split);
+        all.push_back(&ws);
+        all.push_back(&tk);
+        return check(f, "cuLaunchKernel", f.cuLaunchKernel(fn->fn, full + (tiles - full) * split, 1, 1, p.block[0], p.block[1], p.block[2], p.smem, (CUstream)stream, all.data(), nullptr));
     }
     if (!fn->has_plan || fn->plan.tmaps.empty()) {
         if (fn->has_plan && fn->plan.block[0] && (block[0] != fn->plan.block[0] || block[1] != fn->plan.block[1] || block[2] != fn->plan.block[2]))

@@ -72,6 +72,20 @@ def test_sgemm_full_size(gpu, orc, how):
     assert freivalds(A, B, got) <= SGEMM_TOL
 
 
+@pytest.mark.parametrize("how", ["hand", "cta128"])
+@pytest.mark.parametrize("shape", [(2560, 1920, 64), (2560, 1920, 48), (4096, 4736, 32), (2432, 2048, 16)])
+def test_sgemm_tail_wave(gpu, how, shape):
+    # More tiles than resident CTAs with a sparse last wave: 300 tiles (tail 4, split in 4 or, for
+    # K = 48, in 3 parts), 1184 tiles (no tail on 296 slots), 304 tiles with K too short to split.
+    # Small integers: every partial sum is exact, so any split of K must give the same bits; run
+    # twice, since a split tail leaves its tickets behind for the next launch.
+    M, N, K = shape
+    A, B, _ = sgemm_fixture(M, N, K)
+    want = (A.astype(np.int64) @ B.astype(np.int64)).astype(np.float32)
+    for _ in range(2):
+        assert np.array_equal(run_sgemm(gpu, how, A, B), want)
+
+
 def run_matmul_f16(gpu, how, A, B, N, b_is_nk):
     M, K = A.shape
     dA, dB = dev(gpu, A), dev(gpu, B)
