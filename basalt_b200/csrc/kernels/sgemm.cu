@@ -17,6 +17,7 @@
 // tile t.  CTAs are dispatched in index order, so the split parts form the last wave.
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "../../../include/basalt_b200_kernels.h"
 #include "common.cuh"
@@ -205,7 +206,8 @@ extern "C" int basalt_k_sgemm_f32(const float* A, const float* B, float* C, int 
     if (!resident) resident = basalt_k::resident_ctas(sgemm_f32_kernel, THREADS);
     const int tiles = (M / BM) * (N / BN), slots = resident * basalt_k::sm_count();
     int full = tiles, split = 1;
-    plan_tail(tiles, slots, K, &full, &split);
+    static const bool no_split = getenv("BASALT_K_SGEMM_NO_TAIL_SPLIT") != nullptr;   // for A/B timing of the tail-wave split
+    if (!no_split) plan_tail(tiles, slots, K, &full, &split);
     TailWorkspace* w = nullptr;
     if (split > 1) {
         w = tail_workspace(slots);

@@ -503,7 +503,8 @@ int basalt_rt_launch(basalt_rt_function* fn, const uint32_t grid[3], const uint3
         const uint32_t slots = (uint32_t)ctx->sm_count * (uint32_t)resident;
         uint32_t full = tiles, split = 1;
         const uint32_t tail = tiles % slots;
-        if (tiles >= slots && tail != 0 && tail * 2 <= slots) {
+        static const bool no_split = getenv("BASALT_RT_NO_TAIL_SPLIT") != nullptr;   // for A/B timing of the tail-wave split
+        if (!no_split && tiles >= slots && tail != 0 && tail * 2 <= slots) {
             uint32_t sp = slots / tail;
             if (sp > 4) sp = 4;
             while (sp > 1 && p.tail_k % (sp * 16) != 0) sp--;
