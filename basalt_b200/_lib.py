@@ -97,6 +97,7 @@ def _load() -> C.CDLL:
         "basalt_k_helper_chain_u32": (C.c_int, [vp, vp, i64, vp]),
         "basalt_k_imad_peak": (C.c_int, [vp, i64, C.c_int, P(C.c_int64), vp]),
         "basalt_k_sgemm_f32": (C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, vp]),
+        "basalt_k_sgemm_f32_static_workspace": (C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, vp]),
         "basalt_k_matmul_f16": (C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, vp, vp]),
         "basalt_k_peer_allreduce_max_i32": (C.c_int, [P(u64), C.c_int, C.c_int, C.c_uint32, vp, vp, vp, u64, C.c_int, C.c_int32, vp]),
     }

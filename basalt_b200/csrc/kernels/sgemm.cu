@@ -17,6 +17,7 @@
 // tile t.  CTAs are dispatched in index order, so the split parts form the last wave.
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdio.h>
 #include <stdlib.h>
 
 #include "../../../include/basalt_b200_kernels.h"
@@ -216,4 +217,56 @@ extern "C" int basalt_k_sgemm_f32(const float* A, const float* B, float* C, int 
     const int grid = full + (tiles - full) * split;
     sgemm_f32_kernel<<<grid, THREADS, 0, (cudaStream_t)stream>>>(A, B, C, M, N, K, full, split, w ? w->partials : nullptr, w ? w->tickets : nullptr);
     return basalt_k::record(cudaGetLastError(), "sgemm_f32");
+}
+
+// ---- the same SGEMM with its tail workspace in a static device array: allocates nothing ----------
+namespace {
+constexpr int STATIC_MAX_PARTS = 304;    // partial tiles: one per resident CTA of a 148-SM part (296), rounded up
+constexpr int STATIC_MAX_TICKETS = 256;  // tail tiles (at most half a wave)
+constexpr size_t STATIC_PARTIAL_BYTES = (size_t)STATIC_MAX_PARTS * BM * BN * sizeof(float);   // 19 MiB
+constexpr size_t STATIC_WS_BYTES = STATIC_PARTIAL_BYTES + STATIC_MAX_TICKETS * sizeof(unsigned);
+static __device__ __align__(256) unsigned char g_static_tail_ws[STATIC_WS_BYTES];
+
+struct StaticWs {
+    unsigned char* base = nullptr;   // device address of g_static_tail_ws on this device
+};
+}  // namespace
+
+extern "C" int basalt_k_sgemm_f32_static_workspace(const float* A, const float* B, float* C, int M, int N, int K, void* stream) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    if (M % BM || N % BN || K % BK) return basalt_k::record_msg(1, "sgemm_f32_static_workspace", "M and N must be multiples of 128 and K of 16");
+    if (((uintptr_t)A | (uintptr_t)B | (uintptr_t)C) & 15) return basalt_k::record_msg(1, "sgemm_f32_static_workspace", "matrices must be 16-byte aligned");
+    static StaticWs per_device[64];
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return basalt_k::record(e, "sgemm_f32_static_workspace (cudaGetDevice)");
+    if (dev < 0 || dev >= 64) return basalt_k::record_msg(1, "sgemm_f32_static_workspace", "device ordinal out of range");
+    StaticWs& w = per_device[dev];
+    if (!w.base) {   // set-up, once per device, with that device current
+        unsigned char* p = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, g_static_tail_ws);
+        if (e != cudaSuccess) return basalt_k::record(e, "sgemm_f32_static_workspace (cudaGetSymbolAddress)");
+        w.base = p;
+    }
+    static int resident = 0;
+    if (!resident) resident = basalt_k::resident_ctas(sgemm_f32_kernel, THREADS);
+    const int tiles = (M / BM) * (N / BN), slots = resident * basalt_k::sm_count();
+    int full = tiles, split = 1;
+    plan_tail(tiles, slots, K, &full, &split);
+    const int tail = tiles - full;
+    if (split > 1 && ((size_t)tail * split > (size_t)STATIC_MAX_PARTS || tail > STATIC_MAX_TICKETS)) {
+        char msg[200];
+        snprintf(msg, sizeof msg, "the tail wave needs %zu bytes of workspace (%d partial tiles); the static workspace holds %zu bytes (%d partial tiles)",
+                 (size_t)tail * split * BM * BN * sizeof(float), tail * split, STATIC_PARTIAL_BYTES, STATIC_MAX_PARTS);
+        return basalt_k::record_msg(1, "sgemm_f32_static_workspace", msg);
+    }
+    float* partials = reinterpret_cast<float*>(w.base);
+    unsigned* tickets = reinterpret_cast<unsigned*>(w.base + STATIC_PARTIAL_BYTES);
+    if (split > 1) {   // the tickets must start at zero; the kernel leaves them at zero again
+        e = cudaMemsetAsync(tickets, 0, (size_t)tail * sizeof(unsigned), (cudaStream_t)stream);
+        if (e != cudaSuccess) return basalt_k::record(e, "sgemm_f32_static_workspace (cudaMemsetAsync)");
+    }
+    const int grid = full + tail * split;
+    sgemm_f32_kernel<<<grid, THREADS, 0, (cudaStream_t)stream>>>(A, B, C, M, N, K, full, split, partials, tickets);
+    return basalt_k::record(cudaGetLastError(), "sgemm_f32_static_workspace");
 }

@@ -45,6 +45,11 @@ def sgemm_f32(A, B, Cm, M: int, N: int, K: int, stream=None):
     _check(lib.basalt_k_sgemm_f32(_p(A), _p(B), _p(Cm), M, N, K, C.c_void_p(stream)))
 
 
+def sgemm_f32_static_workspace(A, B, Cm, M: int, N: int, K: int, stream=None):
+    """sgemm_f32 with its tail-wave workspace in a static device array: the call allocates nothing."""
+    _check(lib.basalt_k_sgemm_f32_static_workspace(_p(A), _p(B), _p(Cm), M, N, K, C.c_void_p(stream)))
+
+
 def matmul_f16(A, B, Cm, M: int, N: int, K: int, b_is_nk: bool = False, status=None, stream=None):
     _check(lib.basalt_k_matmul_f16(_p(A), _p(B), _p(Cm), M, N, K, int(b_is_nk), _p(status) if status is not None else None,
                                    C.c_void_p(stream)))

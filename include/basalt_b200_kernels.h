@@ -44,6 +44,19 @@ int basalt_k_imad_peak(uint32_t *out, int64_t out_elems, int iters, int64_t *ima
  * examples/cpu_launch_tiled_sgemm.c (there 32^3 with a C addend). M, N multiples of 128, K of 16. */
 int basalt_k_sgemm_f32(const float *A, const float *B, float *C, int M, int N, int K, void *stream);
 
+/* basalt_k_sgemm_f32 with the split-K workspace of its tail wave in a static device array instead
+ * of device memory allocated on first use: this entry point allocates nothing (no cudaMalloc,
+ * cudaFree or allocating library call).  Same arguments and results.  The array holds 304 partial
+ * 128x128 f32 tiles (19 MiB) and 256 tickets; a problem whose tail wave needs more is refused with
+ * a message that says so (never on a 148-SM device, where a tail has at most 296 parts).  The first
+ * call on each device looks the array's address up (cudaGetSymbolAddress) with that device current;
+ * make that first call before any stream capture.  All calls on a device share the one array:
+ * calls that overlap in time (different streams) race; calls on one stream do not.  Every call
+ * zeroes the tickets it will use on `stream` before the kernel, and the kernel leaves them at zero.
+ * No counterpart in the reference. */
+int basalt_k_sgemm_f32_static_workspace(const float *A, const float *B, float *C, int M, int N, int K,
+                                        void *stream);
+
 /* C[MxN] (fp16) = A[MxK] (fp16) * B (fp16) with fp32 accumulation on tcgen05 tensor cores, TMA
  * loads, TMEM accumulator: the workload of examples/cpu_launch_triton_matmul.c (there f32 4x5x3).
  * b_is_nk = 0: B is [K x N] row-major; 1: B is stored transposed, [N x K] row-major.
