@@ -85,6 +85,11 @@ def _load() -> C.CDLL:
         "basalt_rt_comm_destroy": (None, [vp]),
         "basalt_rt_allreduce_max_i32": (C.c_int, [vp, u64, u64, sz, vp]),
         "basalt_rt_allgather": (C.c_int, [vp, u64, u64, sz, vp]),
+        "basalt_rt_ipc_export": (C.c_int, [vp, C.c_char * 64]),
+        "basalt_rt_ipc_open": (C.c_int, [vp, C.c_char_p, P(u64)]),
+        "basalt_rt_ipc_close": (C.c_int, [vp, u64]),
+        "basalt_rt_copy_device_async": (C.c_int, [vp, u64, u64, sz, vp]),
+        "basalt_rt_stream_wait_event": (C.c_int, [vp, vp, vp]),
         "basalt_rt_peer_group_create": (C.c_int, [vp, C.c_int, C.c_int, P(vp)]),
         "basalt_rt_peer_group_handle": (C.c_int, [vp, C.c_char * 64]),
         "basalt_rt_peer_group_connect": (C.c_int, [vp, C.c_char_p, sz]),

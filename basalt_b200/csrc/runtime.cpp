@@ -69,6 +69,8 @@ struct Fns {
     CUresult (*cuEventElapsedTime)(float*, CUevent, CUevent);
     CUresult (*cuGetErrorString)(CUresult, const char**);
     CUresult (*cuOccupancyMaxActiveBlocksPerMultiprocessor)(int*, CUfunction, int, size_t);
+    CUresult (*cuMemcpyDtoDAsync)(CUdeviceptr, CUdeviceptr, size_t, CUstream);
+    CUresult (*cuStreamWaitEvent)(CUstream, CUevent, unsigned);
     CUresult (*cuIpcGetMemHandle)(CUipcMemHandle*, CUdeviceptr);
     CUresult (*cuIpcOpenMemHandle)(CUdeviceptr*, CUipcMemHandle, unsigned);
     CUresult (*cuIpcCloseMemHandle)(CUdeviceptr);
@@ -283,6 +285,8 @@ int basalt_rt_driver_load(basalt_rt_driver** out) {
               resolve(lib, &f.cuEventSynchronize, {"cuEventSynchronize"}) && resolve(lib, &f.cuEventElapsedTime, {"cuEventElapsedTime"}) &&
               resolve(lib, &f.cuGetErrorString, {"cuGetErrorString", "cuGetErrorName"}) &&
               resolve(lib, &f.cuTensorMapEncodeTiled, {"cuTensorMapEncodeTiled"}) &&
+              resolve(lib, &f.cuMemcpyDtoDAsync, {"cuMemcpyDtoDAsync_v2", "cuMemcpyDtoDAsync"}) &&
+              resolve(lib, &f.cuStreamWaitEvent, {"cuStreamWaitEvent"}) &&
               resolve(lib, &f.cuIpcGetMemHandle, {"cuIpcGetMemHandle"}) &&
               resolve(lib, &f.cuIpcOpenMemHandle, {"cuIpcOpenMemHandle_v2", "cuIpcOpenMemHandle"}) &&
               resolve(lib, &f.cuIpcCloseMemHandle, {"cuIpcCloseMemHandle"}) &&
@@ -727,6 +731,49 @@ int basalt_rt_allgather(basalt_rt_comm* comm, uint64_t send, uint64_t recv, size
     Nccl* n = nccl();
     if (!n || !comm) return set_err(4, 0, "basalt_rt_allgather", "no communicator");
     return nccl_check(n, "ncclAllGather", n->AllGather((const void*)(uintptr_t)send, (void*)(uintptr_t)recv, bytes_per_rank, ncclUint8, comm->comm, (cudaStream_t)stream));
+}
+
+// ---- peer mappings of whole buffers, device-to-device copies, cross-stream ordering --------------
+int basalt_rt_ipc_export(const basalt_rt_buffer* buf, unsigned char handle_out[64]) {
+    if (!buf || !handle_out) return set_err(4, 0, "basalt_rt_ipc_export", "null argument");
+    int rc = make_current(buf->ctx);
+    if (rc) return rc;
+    CUipcMemHandle h;
+    rc = check(buf->ctx->drv->f, "cuIpcGetMemHandle", buf->ctx->drv->f.cuIpcGetMemHandle(&h, buf->ptr));
+    if (rc) return rc;
+    memcpy(handle_out, &h, 64);
+    return 0;
+}
+
+int basalt_rt_ipc_open(basalt_rt_ctx* ctx, const unsigned char handle[64], uint64_t* ptr_out) {
+    if (!ctx || !handle || !ptr_out) return set_err(4, 0, "basalt_rt_ipc_open", "null argument");
+    int rc = make_current(ctx);
+    if (rc) return rc;
+    CUipcMemHandle h;
+    memcpy(&h, handle, 64);
+    CUdeviceptr p = 0;
+    rc = check(ctx->drv->f, "cuIpcOpenMemHandle", ctx->drv->f.cuIpcOpenMemHandle(&p, h, CU_IPC_MEM_LAZY_ENABLE_PEER_ACCESS));
+    if (rc) return rc;
+    *ptr_out = (uint64_t)p;
+    return 0;
+}
+
+int basalt_rt_ipc_close(basalt_rt_ctx* ctx, uint64_t ptr) {
+    if (!ctx || !ptr) return set_err(4, 0, "basalt_rt_ipc_close", "null argument");
+    int rc = make_current(ctx);
+    if (rc) return rc;
+    return check(ctx->drv->f, "cuIpcCloseMemHandle", ctx->drv->f.cuIpcCloseMemHandle((CUdeviceptr)ptr));
+}
+
+int basalt_rt_copy_device_async(basalt_rt_ctx* ctx, uint64_t dst, uint64_t src, size_t bytes, void* stream) {
+    if (!ctx || ((!dst || !src) && bytes)) return set_err(4, 0, "basalt_rt_copy_device_async", "null argument");
+    if (!bytes) return 0;
+    return check(ctx->drv->f, "cuMemcpyDtoDAsync", ctx->drv->f.cuMemcpyDtoDAsync((CUdeviceptr)dst, (CUdeviceptr)src, bytes, (CUstream)stream));
+}
+
+int basalt_rt_stream_wait_event(basalt_rt_ctx* ctx, void* stream, void* event) {
+    if (!ctx || !event) return set_err(4, 0, "basalt_rt_stream_wait_event", "null argument");
+    return check(ctx->drv->f, "cuStreamWaitEvent", ctx->drv->f.cuStreamWaitEvent((CUstream)stream, (CUevent)event, 0));
 }
 
 // ---- peer-memory exchange group ---------------------------------------------------------------

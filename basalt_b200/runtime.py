@@ -135,6 +135,25 @@ class CudaContext:
     def event_sync(self, event: int):
         _check(lib.basalt_rt_event_sync(self._h, C.c_void_p(event)))
 
+    def stream_wait_event(self, stream, event: int):
+        """Work issued to `stream` after this call starts only when `event` (recorded on another stream) has happened."""
+        _check(lib.basalt_rt_stream_wait_event(self._h, C.c_void_p(stream), C.c_void_p(event)))
+
+    def copy_device_async(self, dst_ptr: int, src_ptr: int, nbytes: int, stream=None):
+        """Device-to-device copy by the copy engines; either address may be a peer mapping (ipc_open)."""
+        _check(lib.basalt_rt_copy_device_async(self._h, dst_ptr, src_ptr, nbytes, C.c_void_p(stream)))
+
+    def ipc_open(self, handle: bytes) -> int:
+        """Maps another process's exported buffer (DeviceBuffer.ipc_handle); returns its address on this device."""
+        if len(handle) != 64:
+            raise ValueError("a CUDA IPC handle is 64 bytes")
+        out = C.c_uint64(0)
+        _check(lib.basalt_rt_ipc_open(self._h, handle, C.byref(out)))
+        return int(out.value)
+
+    def ipc_close(self, ptr: int):
+        _check(lib.basalt_rt_ipc_close(self._h, ptr))
+
     def elapsed_ms(self, start: int, end: int) -> float:
         ms = C.c_float()
         _check(lib.basalt_rt_event_elapsed_ms(self._h, C.c_void_p(start), C.c_void_p(end), C.byref(ms)))
@@ -195,6 +214,12 @@ class DeviceBuffer:
         self.copy_to_host(out)
         return out
 
+    def ipc_handle(self) -> bytes:
+        """The 64-byte CUDA IPC handle of this allocation, for CudaContext.ipc_open in another process."""
+        buf = (C.c_char * 64)()
+        _check(lib.basalt_rt_ipc_export(self._h, buf))
+        return bytes(buf.raw)
+
     def free(self):
         if self._h:
             lib.basalt_rt_buffer_free(self._h)
@@ -246,7 +271,7 @@ class CudaFunction:
 
     def bind(self, grid, block, shared_mem_bytes: int, params: list, stream=None):
         """Pre-marshals a launch; the returned callable issues it with a single foreign call
-        (asynchronous). Use for launch-latency-sensitive loops."""
+        (asynchronous; `go(stream=...)` overrides the stream given here). Use for launch-latency-sensitive loops."""
         vals = [C.c_uint64(p.device_ptr()) if isinstance(p, DeviceBuffer) else p for p in params]
         arr = (C.c_void_p * max(len(vals), 1))(*[C.cast(C.pointer(v), C.c_void_p) for v in vals])
         g = (C.c_uint32 * 3)(*_dim3(grid))
@@ -254,8 +279,8 @@ class CudaFunction:
         s = C.c_void_p(stream)
         h, fn = self._h, lib.basalt_rt_launch
 
-        def go(_keep=(vals, arr, g, b)):
-            if fn(h, g, b, shared_mem_bytes, s, arr):
+        def go(stream=None, _keep=(vals, arr, g, b)):
+            if fn(h, g, b, shared_mem_bytes, s if stream is None else C.c_void_p(stream), arr):
                 _check(1)
         return go
 

@@ -94,6 +94,15 @@ class RankGroup:
         self.barrier()
         return g
 
+    def map_peers(self, ctx: CudaContext, buf) -> list[int]:
+        """Device addresses, valid on this rank's GPU, of every rank's copy of `buf` (a DeviceBuffer every
+        rank allocated with the same size); entry `rank` is this rank's own.  Close the others with
+        ctx.ipc_close before the owners free their buffers."""
+        if self.world <= 1:
+            return [buf.device_ptr()]
+        handles = self.all_gather_bytes(buf.ipc_handle())
+        return [buf.device_ptr() if r == self.rank else ctx.ipc_open(handles[r]) for r in range(self.world)]
+
     def shard(self, total: int, align: int = 1) -> tuple[int, int]:
         return shard_range(total, self.world, self.rank, align)
 
@@ -104,3 +113,54 @@ def reduce_max_sharded(group: RankGroup, local_slice: np.ndarray, reduce_local) 
     An empty shard contributes INT32_MIN, the identity."""
     partial = int(reduce_local(local_slice)) if len(local_slice) else -2**31
     return group.max_i32_host(partial)
+
+
+class PushGather:
+    """The gather of a row-sharded result, overlapped with the compute that produces it.
+
+    Every rank owns rows [row0, row0 + rows) of a result every rank wants whole.  The shard is
+    computed in `bands` row bands, band k by `launch_band(k, stream)` on one of two compute streams;
+    as soon as band k is done, the copy engines push its rows into every peer's result buffer (one
+    cuMemcpyDtoDAsync per peer on a copy stream) while band k + 1 computes.  `finish` orders the
+    caller's stream after the last push and runs the peer exchange as a barrier: when it returns in
+    stream order, every peer's pushes into this rank's buffer have landed (a peer's exchange word is
+    sent in stream order after that peer's copies).  An allgather does compute, then communication;
+    this does both at once and needs no SM for the transfer."""
+
+    def __init__(self, ctx: CudaContext, group: RankGroup, peers, result_ptrs: list[int], row_bytes: int, row0: int, rows: int, bands: int):
+        if rows % bands:
+            raise ValueError("the bands must divide the shard's rows")
+        self.ctx, self.group, self.peers, self.ptrs = ctx, group, peers, result_ptrs
+        self.row_bytes, self.row0, self.rows, self.bands = row_bytes, row0, rows, bands
+        self.compute = [ctx.create_stream(), ctx.create_stream()]
+        self.copy = ctx.create_stream()
+        self.band_done = [ctx.create_event() for _ in range(bands)]
+        self.start, self.copied = ctx.create_event(), ctx.create_event()
+        self.flag = ctx.upload(np.zeros(2, np.int32))
+
+    def run(self, launch_band, stream=None):
+        ctx, me = self.ctx, self.group.rank
+        ctx.record(self.start, stream)                          # the inputs are ready in the caller's stream order
+        band_rows = self.rows // self.bands
+        for k in range(self.bands):
+            cs = self.compute[k & 1]
+            if k < 2:
+                ctx.stream_wait_event(cs, self.start)
+            launch_band(k, cs)
+            ctx.record(self.band_done[k], cs)
+            ctx.stream_wait_event(self.copy, self.band_done[k])
+            off = (self.row0 + k * band_rows) * self.row_bytes
+            for step in range(1, self.group.world):              # start with the next rank, so the peers are not all written at once
+                r = (me + step) % self.group.world
+                ctx.copy_device_async(self.ptrs[r] + off, self.ptrs[me] + off, band_rows * self.row_bytes, self.copy)
+        if self.peers is not None:                               # barrier: every peer's pushes precede its word
+            self.peers.allreduce_max_i32(self.flag.device_ptr(), self.flag.device_ptr() + 4, self.copy)
+        ctx.record(self.copied, self.copy)
+        ctx.stream_wait_event(stream, self.copied)              # the next run's `start` is recorded after this: no band starts early
+
+    def close(self):
+        for s in self.compute + [self.copy]:
+            self.ctx.destroy_stream(s)
+        for e in self.band_done + [self.start, self.copied]:
+            self.ctx.destroy_event(e)
+        self.flag.free()

@@ -213,6 +213,19 @@ int basalt_rt_allreduce_max_i32(basalt_rt_comm *comm, uint64_t send, uint64_t re
 /* ncclAllGather of bytes_per_rank bytes: gathers the row-sharded matmul output. */
 int basalt_rt_allgather(basalt_rt_comm *comm, uint64_t send, uint64_t recv, size_t bytes_per_rank, void *stream);
 
+/* Whole-buffer peer mappings for the row-sharded matmuls, whose gather is overlapped with the
+ * compute by pushing finished row bands into every peer's result buffer with the copy engines:
+ * export a buffer allocated with basalt_rt_alloc as a 64-byte CUDA IPC handle, open another
+ * process's handle (the returned address is valid on this context's device, for kernels and for
+ * copies), close it again.  basalt_rt_copy_device_async is cuMemcpyDtoDAsync between any two such
+ * addresses, basalt_rt_stream_wait_event orders one stream after an event recorded on another.
+ * No counterpart in the reference (single GPU, synchronous copies only). */
+int basalt_rt_ipc_export(const basalt_rt_buffer *buf, unsigned char handle_out[64]);
+int basalt_rt_ipc_open(basalt_rt_ctx *ctx, const unsigned char handle[64], uint64_t *ptr_out);
+int basalt_rt_ipc_close(basalt_rt_ctx *ctx, uint64_t ptr);
+int basalt_rt_copy_device_async(basalt_rt_ctx *ctx, uint64_t dst, uint64_t src, size_t bytes, void *stream);
+int basalt_rt_stream_wait_event(basalt_rt_ctx *ctx, void *stream, void *event);
+
 /* Peer-memory exchange group: the sharded max_i32's allreduce without a library collective.  Each
  * rank creates a group (which allocates and zeroes its inbox), exports the inbox as a CUDA IPC
  * handle (64 bytes), receives every rank's handle through whatever channel the host program has

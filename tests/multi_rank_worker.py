@@ -95,6 +95,34 @@ def main():
     got = dC.to_numpy(np.float16).reshape(M, N)
     assert rel_fro(got, orc_matmul_f16_rows(orc, A, B, N, False, 0, M)) <= 2e-3
 
+    # ---- the same fp16 matmul with the gather pushed by the copy engines, band by band ----
+    M, N, K = 256 * group.world, 256, 256
+    A = w.f16_normal01(w.SEEDS["matmul_f16"] + 7, M * K).reshape(M, K); B = w.f16_normal01(w.SEEDS["matmul_f16"] + 8, K * N).reshape(K, N)
+    want = orc_matmul_f16_rows(orc, A, B, N, False, 0, M)
+    r0, r1 = group.shard(M, 128)
+    Ml = r1 - r0
+    dA, dB, dC = ctx.upload(A[r0:r1]), ctx.upload(B), ctx.upload(np.zeros((M, N), np.float16))
+    ptrs = group.map_peers(ctx, dC)
+    for bands in (1, 2):
+        rows_b = Ml // bands
+        fb = ctx.load_module(ptx.emit(kb.matmul_f16(rows_b, N, K)).text).get_function("matmul_kernel")
+        pg = sharding.PushGather(ctx, group, peers, ptrs, N * 2, r0, Ml, bands)
+        for _ in range(3):      # back-to-back runs reuse the streams and events
+            pg.run(lambda k, s: fb.launch((N // 128, rows_b // 128), 128, 0,
+                                          [b.ptr(dA.device_ptr() + k * rows_b * K * 2), dB, b.ptr(dC.device_ptr() + (r0 + k * rows_b) * N * 2)], stream=s), None)
+        ctx.synchronize()
+        assert fb.status() == 0 and peers.status() == 0
+        got = dC.to_numpy(np.float16).reshape(M, N)
+        assert rel_fro(got, want) <= 2e-3, ("pushed gather", bands)
+        group.barrier()
+        dC.copy_from_host(np.zeros((M, N), np.float16))
+        ctx.synchronize()
+        group.barrier()
+        pg.close()
+    for r, p in enumerate(ptrs):
+        if r != group.rank:
+            ctx.ipc_close(p)
+
     group.barrier()
     peers.destroy()
     comm.destroy()
