@@ -28,7 +28,9 @@
 #include <algorithm>
 #include <cmath>
 #include <cstdlib>
+#include <climits>
 #include <cstring>
+#include <functional>
 #include <memory>
 #include <set>
 #include <sstream>
@@ -543,10 +545,11 @@ private:
 // ---------------------------------------------------------------------------------------------
 // Symbolic tile values
 // ---------------------------------------------------------------------------------------------
-enum class El : uint8_t { I1, I64, F16, F32, F64 };
+enum class El : uint8_t { I1, I32, I64, F16, F32, F64 };
 Scalar scalar_of(El e) {
     switch (e) {
         case El::I1: return Scalar::I1;
+        case El::I32: return Scalar::I32;
         case El::I64: return Scalar::I64;
         case El::F16: return Scalar::F16;
         case El::F32: return Scalar::F32;
@@ -565,7 +568,7 @@ struct Dim {
 struct Node;
 using NP = std::shared_ptr<Node>;
 struct Node {
-    enum K { CInt, CFlt, PScalar, PPtr, Pid, NProg, Arange, Bin, Cmp, Neg, Not, Expand, Load, Dot, Zeros, Cast, Where } k = CInt;
+    enum K { CInt, CFlt, PScalar, PPtr, Pid, NProg, Arange, Bin, Cmp, Neg, Not, Expand, Load, Dot, Zeros, Cast, Where, Reduce } k = CInt;
     El el = El::I64;
     bool is_ptr = false;
     El pointee = El::F32;
@@ -633,8 +636,9 @@ private:
         if (!e) return;
         if (e->k == Expr::Call) {
             std::string callee = dotted(e->a);
-            if ((callee == "tl.load" || callee == "tl.store") && !e->args.empty()) additive_names(e->args[0], names);
-            for (auto& kw : e->kwargs) if ((callee == "tl.load" || callee == "tl.store") && (kw.first == "pointer" || kw.first == "ptr")) additive_names(kw.second, names);
+            const bool memory = callee == "tl.load" || callee == "tl.store" || callee.rfind("tl.atomic_", 0) == 0;
+            if (memory && !e->args.empty()) additive_names(e->args[0], names);
+            for (auto& kw : e->kwargs) if (memory && (kw.first == "pointer" || kw.first == "ptr")) additive_names(kw.second, names);
         }
         find_calls(e->a, names);
         find_calls(e->b, names);
@@ -687,8 +691,9 @@ private:
                 v.n->is_ptr = true;
                 auto it = opt_.pointee.find(p.name);
                 Scalar sc = it == opt_.pointee.end() ? Scalar::F32 : it->second;
-                v.n->pointee = sc == Scalar::F16 ? El::F16 : sc == Scalar::F64 ? El::F64 : sc == Scalar::I64 ? El::I64 : El::F32;
-                if (sc != Scalar::F16 && sc != Scalar::F32 && sc != Scalar::F64 && sc != Scalar::I64) fail("E300", k_.line, "pointee type of `" + p.name + "` must be f16, f32, f64 or i64");
+                v.n->pointee = sc == Scalar::F16 ? El::F16 : sc == Scalar::F64 ? El::F64 : sc == Scalar::I64 ? El::I64 : sc == Scalar::I32 ? El::I32 : El::F32;
+                if (sc != Scalar::F16 && sc != Scalar::F32 && sc != Scalar::F64 && sc != Scalar::I64 && sc != Scalar::I32)
+                    fail("E300", k_.line, "pointee type of `" + p.name + "` must be f16, f32, f64, i32 or i64");
                 v.n->param = (int)f_.params.size();
                 f_.params.push_back(Ty::p(Space::Global));
             } else {
@@ -759,6 +764,7 @@ private:
         if (n->is_ptr) fail("E300", line, "a pointer is used as a number");
         if (n->el == to) return n;
         if (n->k == Node::CInt && n->rank() == 0 && is_flt(to)) { NP c = cflt((double)n->iv, line); c->el = to; return c; }
+        if (n->k == Node::CInt && n->rank() == 0 && n->el == El::I64 && to == El::I32) { NP c = cint((int64_t)(int32_t)n->iv, line); c->el = El::I32; return c; }
         if (n->k == Node::CFlt && n->rank() == 0 && is_flt(to)) { NP c = cflt(n->fv, line); c->el = to; return c; }
         NP c = node(Node::Cast, line);
         c->el = to;
@@ -792,7 +798,12 @@ private:
             if (b->k == Node::CFlt && b->rank() == 0 && is_flt(a->el)) el = a->el;
             if (op == "/" && !is_flt(a->el) && !is_flt(b->el)) el = El::F32;
         } else if (op == "/") el = El::F32;   // true division of integers
-        else el = El::I64;
+        else {
+            // 32-bit data stays 32 bits wide (and wraps there) against itself and against integer literals
+            auto is32 = [](const NP& n) { return n->el == El::I32; };
+            auto lit = [](const NP& n) { return n->k == Node::CInt && n->rank() == 0 && n->iv >= INT32_MIN && n->iv <= INT32_MAX; };
+            el = (is32(a) && (is32(b) || lit(b))) || (is32(b) && lit(a)) ? El::I32 : El::I64;
+        }
         if (el == El::F16 && op != "min" && op != "max") fail("E304", line, "arithmetic on float16 tiles is outside the subset; convert with .to(tl.float32)");
         NP n = node(Node::Bin, line);
         n->op = op;
@@ -800,7 +811,7 @@ private:
         n->shape = broadcast(a, b, line);
         n->in = {convert(a, el, line), convert(b, el, line)};
         int64_t folded;
-        if (ceval(n, &folded)) return cint(folded, line);
+        if (el == El::I64 && ceval(n, &folded)) return cint(folded, line);
         return n;
     }
 
@@ -841,7 +852,7 @@ private:
             case Expr::Attr: {
                 std::string d = dotted(e);
                 static const struct { const char* n; El el; } dts[] = {{"tl.float16", El::F16}, {"tl.float32", El::F32}, {"tl.float64", El::F64}, {"tl.int64", El::I64},
-                                                                        {"tl.int32", El::I64}, {"tl.int1", El::I1}};
+                                                                        {"tl.int32", El::I32}, {"tl.int1", El::I1}};
                 for (auto& t : dts) if (d == t.n) { v.k = Value::DType; v.dt = t.el; return v; }
                 if (d == "tl.bfloat16") fail("E304", e->line, "bfloat16 has no BIR type");
                 fail("E301", e->line, "`" + d + "` is not known");
@@ -863,6 +874,7 @@ private:
                     n->el = a->el == El::I1 ? El::I64 : a->el;
                     n->shape = a->shape;
                     n->in = {convert(a, n->el, e->line)};
+                    if (a->k == Node::CInt) { v.n = cint(-a->iv, e->line); v.n->el = a->el; return v; }
                     v.n = n;
                     return v;
                 }
@@ -889,7 +901,8 @@ private:
             case Expr::Cmp: {
                 NP a = tile(eval(e->a), e->line, "the left operand"), b = tile(eval(e->b), e->line, "the right operand");
                 if (a->is_ptr || b->is_ptr) fail("E304", e->line, "pointer comparisons are outside the subset");
-                El el = (is_flt(a->el) || is_flt(b->el)) ? std::max(is_flt(a->el) ? a->el : El::F32, is_flt(b->el) ? b->el : El::F32) : El::I64;
+                El el = (is_flt(a->el) || is_flt(b->el)) ? std::max(is_flt(a->el) ? a->el : El::F32, is_flt(b->el) ? b->el : El::F32)
+                        : (a->el == El::I32 && (b->el == El::I32 || b->k == Node::CInt)) || (b->el == El::I32 && a->k == Node::CInt) ? El::I32 : El::I64;
                 NP n = node(Node::Cmp, e->line);
                 n->op = e->s;
                 n->el = El::I1;
@@ -1082,8 +1095,36 @@ private:
             if (e->args.empty()) fail("E300", line, callee + " takes a value");
             return eval(e->args[0]);   // compiler hints: the value itself
         }
-        for (const char* k : {"tl.sum", "tl.max", "tl.min", "tl.argmax", "tl.argmin", "tl.reshape", "tl.trans", "tl.view", "tl.broadcast_to", "tl.expand_dims", "tl.cumsum", "tl.sort", "tl.join",
-                              "tl.split", "tl.permute", "tl.make_block_ptr", "tl.advance", "tl.atomic_add", "tl.atomic_max", "tl.atomic_min", "tl.atomic_cas"})
+        if (callee == "tl.sum" || callee == "tl.max" || callee == "tl.min") {
+            EP in = arg_or_kw(e, 0, "input"), ax = arg_or_kw(e, 1, "axis");
+            if (!in) fail("E300", line, callee + " takes a tile");
+            NP x = tile(eval(in), line, "input");
+            if (x->rank() != 1) fail("E307", line, "reductions of rank-1 tiles only");
+            if (ax && ax->k != Expr::NoneLit && const_of(tile(eval(ax), line, "axis"), line, "the axis") != 0) fail("E300", line, "a rank-1 tile has only axis 0");
+            if (x->is_ptr || x->el == El::I1 || x->el == El::F16 || x->el == El::F64 || x->el == El::I64)
+                fail("E304", line, "reductions of int32 and float32 tiles only");
+            NP n = node(Node::Reduce, line);
+            n->op = callee.substr(3);
+            n->el = x->el;
+            n->in = {x};
+            v.n = n;
+            return v;
+        }
+        if (callee == "tl.atomic_add" || callee == "tl.atomic_max" || callee == "tl.atomic_min") {
+            EP p = arg_or_kw(e, 0, "pointer"), val = arg_or_kw(e, 1, "val"), m = arg_or_kw(e, 2, "mask");
+            if (!p || !val) fail("E300", line, callee + " needs a pointer and a value");
+            NP ptr = tile(eval(p), line, "pointer"), x = tile(eval(val), line, "value"), mask;
+            if (!ptr->is_ptr) fail("E300", line, callee + " on a value that is not a pointer");
+            if (m && m->k != Expr::NoneLit) {
+                mask = tile(eval(m), line, "mask");
+                if (mask->el != El::I1) fail("E300", line, "a mask must be a comparison result");
+            }
+            atomic(callee.substr(10), ptr, x, mask, line);
+            v.k = Value::None;     // the old value is not modelled
+            return v;
+        }
+        for (const char* k : {"tl.argmax", "tl.argmin", "tl.reshape", "tl.trans", "tl.view", "tl.broadcast_to", "tl.expand_dims", "tl.cumsum", "tl.sort", "tl.join",
+                              "tl.split", "tl.permute", "tl.make_block_ptr", "tl.advance", "tl.atomic_cas", "tl.atomic_xchg", "tl.atomic_and", "tl.atomic_or", "tl.atomic_xor"})
             if (callee == k) fail("E307", line, "`" + callee + "` is a tile construct this lowering does not model");
         for (const char* k : {"tl.exp", "tl.log", "tl.sqrt", "tl.sin", "tl.cos", "tl.sigmoid", "tl.softmax", "tl.abs", "tl.rand", "tl.randn", "tl.fma", "tl.exp2", "tl.log2", "tl.rsqrt",
                               "tl.device_print", "tl.static_print", "tl.static_assert", "tl.device_assert", "print"})
@@ -1253,13 +1294,17 @@ private:
                 Val a = gen(c, sub_idx(c, idx));
                 Ty from = Ty::s(scalar_of(c->el));
                 if (is_flt(c->el) && is_flt(n->el)) return cast(n->el > c->el ? CastOp::FPExt : CastOp::FPTrunc, ty, from, a);
-                if (is_flt(n->el)) return cast(c->el == El::I1 ? CastOp::UIToFP : CastOp::SIToFP, ty, c->el == El::I1 ? I64() : from, c->el == El::I1 ? cast(CastOp::ZExt, I64(), from, a) : a);
+                if (is_flt(n->el)) {
+                    if (c->el == El::I1) return cast(CastOp::UIToFP, ty, I64(), cast(CastOp::ZExt, I64(), from, a));
+                    return cast(CastOp::SIToFP, ty, from, a);
+                }
                 if (is_flt(c->el)) {
                     if (n->el == El::I1) return fcmp(FCmp::One, from, a, cf(from, 0.0));
                     return cast(CastOp::FPToSI, ty, from, a);
                 }
                 if (n->el == El::I1) return icmp(ICmp::Ne, from, a, ci(from, 0));
-                return cast(CastOp::ZExt, ty, from, a);   // i1 -> i64
+                if (c->el == El::I1) return cast(CastOp::ZExt, ty, from, a);
+                return cast(n->el > c->el ? CastOp::SExt : CastOp::Trunc, ty, from, a);   // i32 <-> i64
             }
             case Node::Cmp: {
                 const NP &x = n->in[0], &y = n->in[1];
@@ -1338,6 +1383,7 @@ private:
                 return phi(vt, {{from, other}, {t_end, lv}});
             }
             case Node::Dot: fail("E307", n->line, "a tl.dot result can only be stored (optionally plus a loaded tile, optionally converted)");
+            case Node::Reduce: fail("E307", n->line, "a reduction result can only be the value of tl.atomic_add / tl.atomic_max / tl.atomic_min on a scalar pointer");
         }
         fail("E304", n->line, "node outside the subset");
     }
@@ -1426,6 +1472,169 @@ private:
         scopes_.pop_back();
         scopes_.pop_back();
         cur_ = done;
+    }
+
+    // ---- atomics and CTA-wide reductions ----
+    // tl.atomic_<op>(ptr, tile): one atomic per lane of the tile.  tl.atomic_<op>(scalar_ptr, tl.<red>(x)):
+    // every thread folds the lanes it walks, a warp combines its 32 partial results (warp.reduce for
+    // int32, an xor butterfly of shuffles for float32), and lane 0 of each warp issues one atomic.
+    // The CTA must be whole warps, which Triton's num_warps guarantees.
+    void atomic(const std::string& op, const NP& ptr, const NP& value, const NP& mask, int line) {
+        AtomOp aop = op == "add" ? AtomOp::Add : op == "max" ? AtomOp::Max : AtomOp::Min;
+        El el = ptr->pointee;
+        if (el != El::I32 && el != El::F32 && el != El::I64) fail("E304", line, "atomics on int32, int64 and float32 only");
+        if (value->k == Node::Reduce) {
+            if (ptr->rank() != 0 || mask) fail("E307", line, "a reduction result goes to a scalar pointer, unmasked");
+            if (value->op != (op == "add" ? "sum" : op)) fail("E307", line, "tl.atomic_" + op + " of tl." + value->op + " is not one reduction");
+            if (value->el != el) fail("E300", line, "the reduced tile and the target have different element types");
+            reduce_to_atomic(aop, ptr, value->in[0], line);
+            return;
+        }
+        std::vector<Dim> shape = broadcast(ptr, value, line);
+        if (!(shape == ptr->shape)) fail("E305", line, "the value is larger than the pointer tile");
+        NP val = convert(value, el, line);
+        lane_loop(shape, line, [&](const std::vector<Val>& idx) {
+            auto emit = [&]() {
+                Val v = gen(val, sub_idx(val, idx)), addr = gen(ptr, sub_idx(ptr, idx));
+                Inst at;
+                at.op = Opc::Atomic;
+                at.sub = (uint8_t)aop;
+                at.ty = Ty::s(scalar_of(el));
+                at.space = Space::Global;
+                at.ops = {addr, v};
+                push(at);
+            };
+            if (mask) {
+                Val m = gen(mask, sub_idx(mask, idx));
+                uint32_t tb = new_block(), after = new_block();
+                condbr(m, tb, after);
+                cur_ = tb;
+                scopes_.emplace_back();
+                emit();
+                scopes_.pop_back();
+                br(after);
+                cur_ = after;
+            } else emit();
+        });
+    }
+
+    // for (l = tid.x; l < lanes; l += bdim.x) body(indices of lane l); `carried` values ride along as phis
+    void lane_loop(const std::vector<Dim>& shape, int line, const std::function<void(const std::vector<Val>&)>& body, std::vector<Val>* carried = nullptr,
+                   const std::function<std::vector<Val>(const std::vector<Val>&, const std::vector<Val>&)>* step = nullptr) {
+        scopes_.emplace_back();
+        Val lanes;
+        if (shape.empty()) lanes = ci(I64(), 1);
+        else if (shape.size() == 1) lanes = shape[0].sym >= 0 ? Val::P((uint32_t)shape[0].sym) : ci(I64(), shape[0].n);
+        else {
+            if (shape[0].sym >= 0 || shape[1].sym >= 0) fail("E306", line, "rank-2 tiles need compile-time extents");
+            lanes = ci(I64(), shape[0].n * shape[1].n);
+        }
+        Val tid = index(0), stride = index(6);
+        uint32_t pre = cur_, head = new_block(), bodyb = new_block(), done = new_block();
+        br(head);
+        cur_ = head;
+        Inst ph;
+        ph.op = Opc::Phi;
+        ph.ty = I64();
+        ph.ops = {tid};
+        ph.phi_blocks = {pre};
+        Val l = push(ph);
+        std::vector<Val> acc;
+        if (carried)
+            for (Val init : *carried) {
+                Inst pa;
+                pa.op = Opc::Phi;
+                pa.ty = f_.val_ty(init);
+                pa.ops = {init};
+                pa.phi_blocks = {pre};
+                acc.push_back(push(pa));
+            }
+        Val more = icmp(ICmp::Slt, I64(), l, lanes);
+        condbr(more, bodyb, done);
+        cur_ = bodyb;
+        scopes_.emplace_back();
+        std::vector<Val> idx;
+        if (shape.size() == 1) idx = {l};
+        else if (shape.size() == 2) {
+            Val n1 = ci(I64(), shape[1].n);
+            idx = {bin(BinOp::Div, I64(), l, n1), bin(BinOp::Rem, I64(), l, n1)};
+        }
+        std::vector<Val> next_acc;
+        if (step) next_acc = (*step)(idx, acc);
+        else body(idx);
+        Val next = bin(BinOp::Add, I64(), l, stride);
+        uint32_t latch_end = cur_;
+        br(head);
+        f_.insts[l.idx].ops.push_back(next);
+        f_.insts[l.idx].phi_blocks.push_back(latch_end);
+        for (size_t i = 0; i < acc.size(); i++) {
+            f_.insts[acc[i].idx].ops.push_back(next_acc[i]);
+            f_.insts[acc[i].idx].phi_blocks.push_back(latch_end);
+        }
+        scopes_.pop_back();
+        scopes_.pop_back();
+        cur_ = done;
+        if (carried) *carried = acc;   // the values the loop leaves with: the head's phis
+    }
+
+    Val combine(AtomOp op, El el, Val a, Val b) {
+        Ty t = Ty::s(scalar_of(el));
+        if (op == AtomOp::Add) return bin(is_flt(el) ? BinOp::FAdd : BinOp::Add, t, a, b);
+        Val c = is_flt(el) ? fcmp(op == AtomOp::Max ? FCmp::Ogt : FCmp::Olt, t, a, b) : icmp(op == AtomOp::Max ? ICmp::Sgt : ICmp::Slt, t, a, b);
+        return select(t, c, a, b);
+    }
+
+    void reduce_to_atomic(AtomOp op, const NP& ptr, const NP& x, int line) {
+        El el = x->el;
+        Ty t = Ty::s(scalar_of(el));
+        scopes_.emplace_back();
+        Val identity;
+        if (op == AtomOp::Add) identity = is_flt(el) ? cf(t, 0.0) : ci(t, 0);
+        else if (is_flt(el)) identity = cf(t, op == AtomOp::Max ? -INFINITY : INFINITY);
+        else identity = ci(t, op == AtomOp::Max ? (int64_t)INT32_MIN : (int64_t)INT32_MAX);
+        std::vector<Val> carried = {identity};
+        std::function<std::vector<Val>(const std::vector<Val>&, const std::vector<Val>&)> step = [&](const std::vector<Val>& idx, const std::vector<Val>& acc) {
+            Val v = gen(x, sub_idx(x, idx));
+            return std::vector<Val>{combine(op, el, v, acc[0])};
+        };
+        lane_loop(x->shape, line, nullptr, &carried, &step);
+        Val mine = carried[0], warp;
+        if (el == El::I32) {
+            Inst wr;
+            wr.op = Opc::WarpReduce;
+            wr.sub = (uint8_t)(op == AtomOp::Add ? RedOp::Add : op == AtomOp::Max ? RedOp::Max : RedOp::Min);
+            wr.ty = t;
+            wr.ops = {mine};
+            warp = push(wr);
+        } else {
+            warp = mine;
+            for (int m = 16; m >= 1; m >>= 1) {
+                Inst sh;
+                sh.op = Opc::Shuffle;
+                sh.sub = (uint8_t)Shfl::Xor;
+                sh.ty = t;
+                sh.ops = {warp, ci(Ty::s(Scalar::I32), m)};
+                Val other = push(sh);
+                warp = combine(op, el, other, warp);
+            }
+        }
+        Val lane = bin(BinOp::And, I64(), index(0), ci(I64(), 31));
+        Val first = icmp(ICmp::Eq, I64(), lane, ci(I64(), 0));
+        uint32_t tb = new_block(), after = new_block();
+        condbr(first, tb, after);
+        cur_ = tb;
+        scopes_.emplace_back();
+        Inst at;
+        at.op = Opc::Atomic;
+        at.sub = (uint8_t)op;
+        at.ty = t;
+        at.space = Space::Global;
+        at.ops = {gen(ptr, {}), warp};
+        push(at);
+        scopes_.pop_back();
+        br(after);
+        cur_ = after;
+        scopes_.pop_back();
     }
 
     // ---- tl.dot -> mma ----

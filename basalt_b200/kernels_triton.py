@@ -40,3 +40,13 @@ def matmul_f16(M: int, N: int, K: int, **blocks) -> str:
 def sgemm(M: int, N: int, K: int, **blocks) -> str:
     """The tiled f32 matmul; grid (N / BLOCK_N, M / BLOCK_M), compiled for 8 warps."""
     return backend.compile_triton(load("sgemm"), constexprs=dict(M=M, N=N, K=K, **blocks), num_warps=8, min_blocks=2)
+
+
+def vadd_i32() -> str:
+    """Masked c = a + b on int32 (wrapping); BLOCK is the run-time lane count of a program."""
+    return backend.compile_triton(load("vadd_i32"), pointee={"a_ptr": "i32", "b_ptr": "i32", "c_ptr": "i32"})
+
+
+def max_i32() -> str:
+    """Signed maximum folded into *out: tl.max over a program's BLOCK elements, one atomic per warp."""
+    return backend.compile_triton(load("max_i32"), pointee={"x_ptr": "i32", "out_ptr": "i32"})

@@ -101,6 +101,44 @@ def test_tiled_matmul_values_on_one_small_program(ptx):
     assert np.array_equal(out, (A @ B).astype(np.float16))
 
 
+def test_int32_sources_wrap_and_reduce(ptx, orc, tmp_path):
+    import ctypes
+    from _util import vp
+    from basalt_b200 import workloads as w
+    bir = checked(ptx, kt.vadd_i32())
+    assert "add i32" in bir and "load i32 ptr.global" in bir and "store i32 ptr.global" in bir       # 32-bit data stays 32 bits wide
+    n = 1000
+    a = w.i32_pm30(1, n) * 2; bb = w.i32_pm30(2, n) * 2                                             # sums overflow and must wrap
+    want = np.zeros(n, np.int32)
+    orc.orc_vadd_i32(vp(a), vp(bb), vp(want), ctypes.c_int32(n), ctypes.c_int64(n))
+    for threads in (1, 64):
+        c = np.full(1024, 0x7fffffff, np.int32)
+        run_kernel(bir, "vadd_i32", [a, bb, c, n, 1024], threads)
+        assert np.array_equal(c[:n], want) and np.all(c[n:] == 0x7fffffff)
+    # the reduction: per-thread fold in a lane loop, one warp.reduce, one atomic per warp (values are checked on the device:
+    # the CPU oracle's launch has no warps)
+    bir = checked(ptx, kt.max_i32())
+    assert bir.count("warp.reduce.max i32") == 1 and bir.count("atomic.max i32 ptr.global") == 1 and "shuffle" not in bir
+    assert "phi i32" in bir and "const.i i32 -2147483648" in bir
+    text = ptx.emit(bir).text
+    assert "redux.sync.max.s32" in text
+    ptxas(text, tmp_path)
+    # float32 sums use an xor butterfly of shuffles
+    src = "@triton.jit\ndef total(x_ptr, out_ptr, n, BLOCK: tl.constexpr):\n    offs = tl.program_id(0) * BLOCK + tl.arange(0, BLOCK)\n" \
+          "    tl.atomic_add(out_ptr, tl.sum(tl.load(x_ptr + offs, mask=offs < n, other=0.0), axis=0))\n"
+    bir = checked(ptx, b.compile_triton(src))
+    assert bir.count("shuffle.xor f32") == 5 and "atomic.add f32 ptr.global" in bir
+    ptxas(ptx.emit(bir).text, tmp_path)
+    # elementwise atomics run under the oracle: a histogram-like scatter with a mask
+    src = "@triton.jit\ndef scatter(idx_ptr, out_ptr, n, BLOCK: tl.constexpr = 16):\n    offs = tl.arange(0, BLOCK)\n    m = offs < n\n" \
+          "    i = tl.load(idx_ptr + offs, mask=m, other=0)\n    tl.atomic_add(out_ptr + i, offs + 1, mask=m)\n"
+    bir = checked(ptx, b.compile_triton(src, pointee={"idx_ptr": "i64", "out_ptr": "i64"}))
+    idx = np.array([0, 2, 2, 1, 0, 3, 3, 3, 9, 9, 9, 9, 9, 9, 9, 9], np.int64)
+    out = np.zeros(10, np.int64)
+    run_kernel(bir, "scatter", [idx, out, 8], 4)
+    assert out.tolist() == [1 + 5, 4, 2 + 3, 6 + 7 + 8, 0, 0, 0, 0, 0, 0]
+
+
 ELEMENTWISE = '''
 import triton
 import triton.language as tl
@@ -148,6 +186,8 @@ def test_rank2_elementwise_tile_code(ptx):
     ("E306", "@triton.jit\ndef k(x_ptr, n):\n    a = tl.arange(0, n + 1)\n    tl.store(x_ptr + a, 1.0)\n", {}),
     ("E306", kt.load("small_matmul"), {}),                                  # K left unbound: tl.dot needs constant extents
     ("E307", "@triton.jit\ndef k(x_ptr):\n    a = tl.arange(0, 4)\n    tl.store(x_ptr, tl.sum(tl.load(x_ptr + a)))\n", {}),
+    ("E307", "@triton.jit\ndef k(x_ptr):\n    a = tl.arange(0, 4)\n    tl.atomic_max(x_ptr, tl.sum(tl.load(x_ptr + a)))\n", {}),
+    ("E307", "@triton.jit\ndef k(x_ptr):\n    a = tl.arange(0, 4)\n    tl.atomic_xchg(x_ptr + a, 1.0)\n", {}),
     ("E307", "@triton.jit\ndef k(x_ptr):\n    a = tl.arange(0, 8)\n    tl.store(x_ptr + a[1:], 1.0)\n", {}),
     ("E307", kt.load("small_matmul").replace("acc + c)", "acc + c, mask=rows[:, None] < 3)"), {"constexprs": {"K": 5}}),
     ("E307", kt.load("small_matmul").replace("tl.load(a_ptr + rows[:, None] * K + depth[None, :])", "tl.load(a_ptr + rows[:, None] * K + depth[None, :]) * 2.0"),

@@ -52,6 +52,9 @@ def test_vadd_i32(gpu, label, level):
         emitted(gpu, bir, kernel, level).launch(grid_for(n), 256, 0, [da, db, dc, b.i32(n)])
         assert sha(dc.to_numpy(np.int32)) == g["sha256"], (form, level)
     dc = dev(gpu, np.full(n, 0x7fffffff, np.int32))
+    emitted(gpu, kt.vadd_i32(), "vadd_i32", level).launch((n + 1023) // 1024, 256, 0, [da, db, dc, b.i64(n), b.i64(1024)])      # programs of 1024 lanes
+    assert sha(dc.to_numpy(np.int32)) == g["sha256"], ("triton", level)
+    dc = dev(gpu, np.full(n, 0x7fffffff, np.int32))
     kernels.vadd_i32(da, db, dc, n)
     gpu.synchronize()
     assert sha(dc.to_numpy(np.int32)) == g["sha256"], "hand-written"
@@ -90,6 +93,9 @@ def test_max_i32(gpu, orc, label, level):
         out = dev(gpu, np.array([-2**31], np.int32))
         fn.launch(min(fn.one_wave(256), grid_for(n)), 256, 0, [dx, out, b.i32(n)])
         assert int(out.to_numpy(np.int32)[0]) == g["value"], (form, level)
+    out = dev(gpu, np.array([-2**31], np.int32))
+    emitted(gpu, kt.max_i32(), "max_i32", level).launch((n + 8191) // 8192, 256, 0, [dx, out, b.i64(n), b.i64(8192)])      # tl.max over 8192 lanes per program
+    assert int(out.to_numpy(np.int32)[0]) == g["value"], ("triton", level)
     out = dev(gpu, np.array([-2**31], np.int32))
     kernels.max_i32(dx, n, out)
     gpu.synchronize()

@@ -63,3 +63,23 @@ def test_tiled_matmul_f16_on_tensor_cores(gpu, orc, shape):
     assert fn.status() == 0, "a bounded wait inside the emitted kernel expired"
     got = dC.to_numpy(np.float16).reshape(M, N)
     assert rel_fro(got, orc_matmul_f16_rows(orc, A, B, N, False, 0, M)) <= 2e-3
+
+
+def test_reductions_and_atomics(gpu):
+    # tl.sum over float32 through the shuffle butterfly: small integers, so the order of the additions cannot matter
+    src = "@triton.jit\ndef total(x_ptr, out_ptr, n, BLOCK: tl.constexpr):\n    offs = tl.program_id(0) * BLOCK + tl.arange(0, BLOCK)\n" \
+          "    tl.atomic_add(out_ptr, tl.sum(tl.load(x_ptr + offs, mask=offs < n, other=0.0), axis=0))\n"
+    fn = emitted(gpu, b.compile_triton(src), "total")
+    for n, block, threads in [(1000, 1024, 256), (100003, 2048, 128), (5, 64, 32)]:
+        x = np.random.default_rng(n).integers(-8, 9, n).astype(np.float32)
+        out = dev(gpu, np.zeros(1, np.float32))
+        fn.launch((n + block - 1) // block, threads, 0, [dev(gpu, x), out, b.i64(n), b.i64(block)])
+        assert out.to_numpy(np.float32)[0] == x.sum(dtype=np.float64), (n, block, threads)
+    # tl.min over int32, one atomic per warp
+    src = "@triton.jit\ndef lowest(x_ptr, out_ptr, n, BLOCK: tl.constexpr):\n    offs = tl.program_id(0) * BLOCK + tl.arange(0, BLOCK)\n" \
+          "    tl.atomic_min(out_ptr, tl.min(tl.load(x_ptr + offs, mask=offs < n, other=2147483647), axis=0))\n"
+    fn = emitted(gpu, b.compile_triton(src, pointee={"x_ptr": "i32", "out_ptr": "i32"}), "lowest")
+    x = w.u32(5, 70001).view(np.int32)
+    out = dev(gpu, np.array([2**31 - 1], np.int32))
+    fn.launch((70001 + 4095) // 4096, 256, 0, [dev(gpu, x), out, b.i64(70001), b.i64(4096)])
+    assert int(out.to_numpy(np.int32)[0]) == int(x.min())
