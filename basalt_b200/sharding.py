@@ -19,6 +19,28 @@ import numpy as np
 from .runtime import Communicator, CudaContext, PeerGroup, shard_range
 
 
+def bind_to_gpu_cpus(device_index: int) -> list[int]:
+    """Restricts this process to the CPUs NVML reports as local to the GPU (its NUMA node), so that
+    pinned host buffers allocated afterwards sit on the memory closest to the GPU's PCIe root.  Only
+    reads NVML (nvmlDeviceGetCpuAffinity) and changes this process's own CPU affinity mask; returns
+    the CPUs chosen, or an empty list when NVML or the affinity call is unavailable."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        try:
+            handle = pynvml.nvmlDeviceGetHandleByIndex(device_index)
+            words = pynvml.nvmlDeviceGetCpuAffinity(handle, (os.cpu_count() + 63) // 64)
+        finally:
+            pynvml.nvmlShutdown()
+        cpus = [64 * w + bit for w, word in enumerate(words) for bit in range(64) if (int(word) >> bit) & 1]
+        allowed = sorted(set(cpus) & set(os.sched_getaffinity(0)))
+        if allowed:
+            os.sched_setaffinity(0, allowed)
+        return allowed
+    except Exception:   # noqa: BLE001 - an optimisation only
+        return []
+
+
 @dataclass
 class RankGroup:
     rank: int = 0

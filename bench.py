@@ -447,6 +447,7 @@ def main():
     from basalt_b200 import kernels, kernels_bir as kb, sharding, workloads as w
 
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    local_cpus = sharding.bind_to_gpu_cpus(local_rank)      # host buffers of the end-to-end leg land on the GPU's NUMA node
     torch.cuda.set_device(local_rank)
     group = sharding.RankGroup.from_env("nccl")
     rank, world = group.rank, group.world
@@ -606,7 +607,7 @@ def main():
             "dtype": "i32", "data": "synthetic",
             "config": {"workload": f"max_i32: signed max over {n} int32 per GPU (uniform over the full range, SplitMix64 seed per rank), "
                                    "emitted sm_100a kernel launched through the C-ABI runtime" + ((", then " + exchange_kind + " per step") if world > 1 else ""),
-                       "elements_per_gpu": n, "grid": blocks, "block": 256, "l2": f"input ({4 * n >> 20} MiB per GPU) is larger than the 126 MB L2; no flush needed",
+                       "elements_per_gpu": n, "grid": blocks, "block": 256, "host_cpus_bound_to_gpu_numa_node": len(local_cpus), "l2": f"input ({4 * n >> 20} MiB per GPU) is larger than the 126 MB L2; no flush needed",
                        "parallelism": f"contiguous shards x{world}"},
             "parity": parity,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak_hbm, "unit": "GB/s", "frac": achieved / peak_hbm, "peak_source": peak_kind,
