@@ -1368,8 +1368,13 @@ private:
                     in.ops = {addr};
                     return push(in);
                 };
-                if (!n->has_mask) return do_load();
-                Val m = gen(n->in[1], sub_idx(n->in[1], idx));
+                const bool guarded = lane_ && lane_->guarded;
+                if (!n->has_mask && !guarded) return do_load();
+                Val m;
+                if (n->has_mask) {
+                    m = gen(n->in[1], sub_idx(n->in[1], idx));
+                    if (guarded) m = bin(BinOp::And, Ty::s(Scalar::I1), m, lane_->guard);   // a lane past the tile loads nothing
+                } else m = lane_->guard;
                 Val other = n->has_other ? gen(n->in[2], sub_idx(n->in[2], idx)) : (is_flt(n->el) ? cf(vt, 0.0) : ci(vt, 0));
                 uint32_t from = cur_, tb = new_block(), mb = new_block();
                 condbr(m, tb, mb);
@@ -1403,15 +1408,24 @@ private:
         return false;
     }
 
-    void store(const NP& ptr, const NP& value, const NP& mask, int line) {
-        std::vector<Dim> shape = broadcast(ptr, value, line);
-        if (!(shape == ptr->shape)) fail("E305", line, "the stored value is larger than the pointer tile");
-        std::set<const Node*> seen;
-        if (has_dot(value, &seen)) { store_dot(ptr, value, mask, line); return; }
-        El el = ptr->pointee;
-        NP val = convert(value, el, line);
-        if (mask && !(broadcast(ptr, mask, line) == ptr->shape)) fail("E305", line, "the mask is larger than the pointer tile");
-        // lanes: the product of the extents; at most one of them may be symbolic, and only at rank 1
+    // ---- lane loops ----
+    // One lane of an unrolled iteration: its tile indices and, for every lane but the first, the
+    // predicate "this lane exists" (l + u * bdim.x < lanes), which guards its loads and its effects.
+    struct Lane {
+        std::vector<Val> idx;
+        bool guarded = false;
+        Val guard;
+    };
+    const Lane* lane_ = nullptr;   // the lane gen() is instantiating for, so that loads can honour its guard
+    static constexpr int kUnroll = 4;
+
+    // for (l = tid.x; l < lanes; l += kUnroll * bdim.x): lanes l, l + bdim.x, ... of one iteration are
+    // instantiated together -- first `values` for every lane (its loads), then `effects` for every lane
+    // -- so that a thread has kUnroll independent loads in flight and neighbouring threads still touch
+    // neighbouring addresses.  `carried` values ride along as phis; `fold` combines a lane's values into them.
+    void lane_loop(const std::vector<Dim>& shape, int line, const std::function<std::vector<Val>(const Lane&)>& values,
+                   const std::function<void(const Lane&, const std::vector<Val>&)>& effects, std::vector<Val>* carried = nullptr,
+                   const std::function<std::vector<Val>(const Lane&, const std::vector<Val>&, const std::vector<Val>&)>* fold = nullptr) {
         scopes_.emplace_back();
         Val lanes;
         if (shape.empty()) lanes = ci(I64(), 1);
@@ -1420,58 +1434,111 @@ private:
             if (shape[0].sym >= 0 || shape[1].sym >= 0) fail("E306", line, "rank-2 tiles need compile-time extents");
             lanes = ci(I64(), shape[0].n * shape[1].n);
         }
-        Val tid = index(0), step = index(6);
-        uint32_t pre = cur_, head = new_block(), body = new_block(), done = new_block();
+        const int unroll = shape.empty() ? 1 : kUnroll;
+        Val tid = index(0), stride = index(6);
+        uint32_t pre = cur_, head = new_block(), bodyb = new_block(), done = new_block();
         br(head);
         cur_ = head;
-        // the phi's second incoming value is patched in once the latch exists
-        Inst ph;
+        Inst ph;   // the second incoming value is patched in once the latch exists
         ph.op = Opc::Phi;
         ph.ty = I64();
         ph.ops = {tid};
         ph.phi_blocks = {pre};
         Val l = push(ph);
-        Val more = icmp(ICmp::Slt, I64(), l, lanes);
-        condbr(more, body, done);
-        cur_ = body;
+        std::vector<Val> acc;
+        if (carried)
+            for (Val init : *carried) {
+                Inst pa;
+                pa.op = Opc::Phi;
+                pa.ty = f_.val_ty(init);
+                pa.ops = {init};
+                pa.phi_blocks = {pre};
+                acc.push_back(push(pa));
+            }
+        condbr(icmp(ICmp::Slt, I64(), l, lanes), bodyb, done);
+        cur_ = bodyb;
         scopes_.emplace_back();
-        std::vector<Val> idx;
-        if (shape.size() == 1) idx = {l};
-        else if (shape.size() == 2) {
-            Val n1 = ci(I64(), shape[1].n);
-            idx = {bin(BinOp::Div, I64(), l, n1), bin(BinOp::Rem, I64(), l, n1)};
+        std::vector<Lane> ls((size_t)unroll);
+        Val lu = l;
+        for (int u = 0; u < unroll; u++) {
+            if (u) {
+                lu = bin(BinOp::Add, I64(), lu, stride);
+                ls[u].guarded = true;
+                ls[u].guard = icmp(ICmp::Slt, I64(), lu, lanes);
+            }
+            if (shape.size() == 1) ls[u].idx = {lu};
+            else if (shape.size() == 2) {
+                Val n1 = ci(I64(), shape[1].n);
+                ls[u].idx = {bin(BinOp::Div, I64(), lu, n1), bin(BinOp::Rem, I64(), lu, n1)};
+            }
         }
-        auto emit_store = [&]() {
-            Val v = gen(val, sub_idx(val, idx));
-            Val addr = gen(ptr, sub_idx(ptr, idx));
-            Inst st;
-            st.op = Opc::Store;
-            st.ty = Ty::v();
-            st.aux = Ty::s(scalar_of(el));
-            st.space = Space::Global;
-            st.align = scalar_bytes(scalar_of(el));
-            st.ops = {addr, v};
-            push(st);
-        };
-        if (mask) {
-            Val m = gen(mask, sub_idx(mask, idx));
-            uint32_t tb = new_block(), latch = new_block();
-            condbr(m, tb, latch);
-            cur_ = tb;
-            scopes_.emplace_back();
-            emit_store();
-            scopes_.pop_back();
-            br(latch);
-            cur_ = latch;
-        } else emit_store();
-        Val next = bin(BinOp::Add, I64(), l, step);
+        std::vector<std::vector<Val>> vals((size_t)unroll);
+        for (int u = 0; u < unroll; u++) { lane_ = &ls[u]; vals[u] = values(ls[u]); }
+        std::vector<Val> cur_acc = acc;
+        for (int u = 0; u < unroll; u++) {
+            lane_ = &ls[u];
+            if (fold) cur_acc = (*fold)(ls[u], vals[u], cur_acc);
+            else effects(ls[u], vals[u]);
+        }
+        lane_ = nullptr;
+        Val next = bin(BinOp::Add, I64(), lu, stride);
         uint32_t latch_end = cur_;
         br(head);
         f_.insts[l.idx].ops.push_back(next);
         f_.insts[l.idx].phi_blocks.push_back(latch_end);
+        for (size_t k = 0; k < acc.size(); k++) {
+            f_.insts[acc[k].idx].ops.push_back(cur_acc[k]);
+            f_.insts[acc[k].idx].phi_blocks.push_back(latch_end);
+        }
         scopes_.pop_back();
         scopes_.pop_back();
         cur_ = done;
+        if (carried) *carried = acc;   // the values the loop leaves with: the head's phis
+    }
+
+    // the predicate under which a lane's side effect happens: its mask and its guard, whichever exist
+    bool lane_condition(const Lane& lane, const NP& mask, Val* out) {
+        bool have = false;
+        if (mask) { *out = gen(mask, sub_idx(mask, lane.idx)); have = true; }
+        if (lane.guarded) { *out = have ? bin(BinOp::And, Ty::s(Scalar::I1), *out, lane.guard) : lane.guard; have = true; }
+        return have;
+    }
+    void under(bool have, Val cond, const std::function<void()>& emit) {
+        if (!have) { emit(); return; }
+        uint32_t tb = new_block(), after = new_block();
+        condbr(cond, tb, after);
+        cur_ = tb;
+        scopes_.emplace_back();
+        emit();
+        scopes_.pop_back();
+        br(after);
+        cur_ = after;
+    }
+
+    void store(const NP& ptr, const NP& value, const NP& mask, int line) {
+        std::vector<Dim> shape = broadcast(ptr, value, line);
+        if (!(shape == ptr->shape)) fail("E305", line, "the stored value is larger than the pointer tile");
+        std::set<const Node*> seen;
+        if (has_dot(value, &seen)) { store_dot(ptr, value, mask, line); return; }
+        El el = ptr->pointee;
+        NP val = convert(value, el, line);
+        if (mask && !(broadcast(ptr, mask, line) == ptr->shape)) fail("E305", line, "the mask is larger than the pointer tile");
+        lane_loop(shape, line,
+                  [&](const Lane& lane) { return std::vector<Val>{gen(val, sub_idx(val, lane.idx))}; },
+                  [&](const Lane& lane, const std::vector<Val>& v) {
+                      Val cond;
+                      bool have = lane_condition(lane, mask, &cond);
+                      under(have, cond, [&]() {
+                          Inst st;
+                          st.op = Opc::Store;
+                          st.ty = Ty::v();
+                          st.aux = Ty::s(scalar_of(el));
+                          st.space = Space::Global;
+                          st.align = scalar_bytes(scalar_of(el));
+                          st.ops = {gen(ptr, sub_idx(ptr, lane.idx)), v[0]};
+                          push(st);
+                      });
+                  });
     }
 
     // ---- atomics and CTA-wide reductions ----
@@ -1493,88 +1560,21 @@ private:
         std::vector<Dim> shape = broadcast(ptr, value, line);
         if (!(shape == ptr->shape)) fail("E305", line, "the value is larger than the pointer tile");
         NP val = convert(value, el, line);
-        lane_loop(shape, line, [&](const std::vector<Val>& idx) {
-            auto emit = [&]() {
-                Val v = gen(val, sub_idx(val, idx)), addr = gen(ptr, sub_idx(ptr, idx));
-                Inst at;
-                at.op = Opc::Atomic;
-                at.sub = (uint8_t)aop;
-                at.ty = Ty::s(scalar_of(el));
-                at.space = Space::Global;
-                at.ops = {addr, v};
-                push(at);
-            };
-            if (mask) {
-                Val m = gen(mask, sub_idx(mask, idx));
-                uint32_t tb = new_block(), after = new_block();
-                condbr(m, tb, after);
-                cur_ = tb;
-                scopes_.emplace_back();
-                emit();
-                scopes_.pop_back();
-                br(after);
-                cur_ = after;
-            } else emit();
-        });
-    }
-
-    // for (l = tid.x; l < lanes; l += bdim.x) body(indices of lane l); `carried` values ride along as phis
-    void lane_loop(const std::vector<Dim>& shape, int line, const std::function<void(const std::vector<Val>&)>& body, std::vector<Val>* carried = nullptr,
-                   const std::function<std::vector<Val>(const std::vector<Val>&, const std::vector<Val>&)>* step = nullptr) {
-        scopes_.emplace_back();
-        Val lanes;
-        if (shape.empty()) lanes = ci(I64(), 1);
-        else if (shape.size() == 1) lanes = shape[0].sym >= 0 ? Val::P((uint32_t)shape[0].sym) : ci(I64(), shape[0].n);
-        else {
-            if (shape[0].sym >= 0 || shape[1].sym >= 0) fail("E306", line, "rank-2 tiles need compile-time extents");
-            lanes = ci(I64(), shape[0].n * shape[1].n);
-        }
-        Val tid = index(0), stride = index(6);
-        uint32_t pre = cur_, head = new_block(), bodyb = new_block(), done = new_block();
-        br(head);
-        cur_ = head;
-        Inst ph;
-        ph.op = Opc::Phi;
-        ph.ty = I64();
-        ph.ops = {tid};
-        ph.phi_blocks = {pre};
-        Val l = push(ph);
-        std::vector<Val> acc;
-        if (carried)
-            for (Val init : *carried) {
-                Inst pa;
-                pa.op = Opc::Phi;
-                pa.ty = f_.val_ty(init);
-                pa.ops = {init};
-                pa.phi_blocks = {pre};
-                acc.push_back(push(pa));
-            }
-        Val more = icmp(ICmp::Slt, I64(), l, lanes);
-        condbr(more, bodyb, done);
-        cur_ = bodyb;
-        scopes_.emplace_back();
-        std::vector<Val> idx;
-        if (shape.size() == 1) idx = {l};
-        else if (shape.size() == 2) {
-            Val n1 = ci(I64(), shape[1].n);
-            idx = {bin(BinOp::Div, I64(), l, n1), bin(BinOp::Rem, I64(), l, n1)};
-        }
-        std::vector<Val> next_acc;
-        if (step) next_acc = (*step)(idx, acc);
-        else body(idx);
-        Val next = bin(BinOp::Add, I64(), l, stride);
-        uint32_t latch_end = cur_;
-        br(head);
-        f_.insts[l.idx].ops.push_back(next);
-        f_.insts[l.idx].phi_blocks.push_back(latch_end);
-        for (size_t i = 0; i < acc.size(); i++) {
-            f_.insts[acc[i].idx].ops.push_back(next_acc[i]);
-            f_.insts[acc[i].idx].phi_blocks.push_back(latch_end);
-        }
-        scopes_.pop_back();
-        scopes_.pop_back();
-        cur_ = done;
-        if (carried) *carried = acc;   // the values the loop leaves with: the head's phis
+        lane_loop(shape, line,
+                  [&](const Lane& lane) { return std::vector<Val>{gen(val, sub_idx(val, lane.idx))}; },
+                  [&](const Lane& lane, const std::vector<Val>& v) {
+                      Val cond;
+                      bool have = lane_condition(lane, mask, &cond);
+                      under(have, cond, [&]() {
+                          Inst at;
+                          at.op = Opc::Atomic;
+                          at.sub = (uint8_t)aop;
+                          at.ty = Ty::s(scalar_of(el));
+                          at.space = Space::Global;
+                          at.ops = {gen(ptr, sub_idx(ptr, lane.idx)), v[0]};
+                          push(at);
+                      });
+                  });
     }
 
     Val combine(AtomOp op, El el, Val a, Val b) {
@@ -1593,11 +1593,13 @@ private:
         else if (is_flt(el)) identity = cf(t, op == AtomOp::Max ? -INFINITY : INFINITY);
         else identity = ci(t, op == AtomOp::Max ? (int64_t)INT32_MIN : (int64_t)INT32_MAX);
         std::vector<Val> carried = {identity};
-        std::function<std::vector<Val>(const std::vector<Val>&, const std::vector<Val>&)> step = [&](const std::vector<Val>& idx, const std::vector<Val>& acc) {
-            Val v = gen(x, sub_idx(x, idx));
-            return std::vector<Val>{combine(op, el, v, acc[0])};
-        };
-        lane_loop(x->shape, line, nullptr, &carried, &step);
+        std::function<std::vector<Val>(const Lane&, const std::vector<Val>&, const std::vector<Val>&)> fold =
+            [&](const Lane& lane, const std::vector<Val>& v, const std::vector<Val>& acc) {
+                Val folded = combine(op, el, v[0], acc[0]);
+                if (lane.guarded) folded = select(t, lane.guard, folded, acc[0]);   // a lane past the tile contributes nothing
+                return std::vector<Val>{folded};
+            };
+        lane_loop(x->shape, line, [&](const Lane& lane) { return std::vector<Val>{gen(x, sub_idx(x, lane.idx))}; }, nullptr, &carried, &fold);
         Val mine = carried[0], warp;
         if (el == El::I32) {
             Inst wr;
@@ -1620,20 +1622,15 @@ private:
         }
         Val lane = bin(BinOp::And, I64(), index(0), ci(I64(), 31));
         Val first = icmp(ICmp::Eq, I64(), lane, ci(I64(), 0));
-        uint32_t tb = new_block(), after = new_block();
-        condbr(first, tb, after);
-        cur_ = tb;
-        scopes_.emplace_back();
-        Inst at;
-        at.op = Opc::Atomic;
-        at.sub = (uint8_t)op;
-        at.ty = t;
-        at.space = Space::Global;
-        at.ops = {gen(ptr, {}), warp};
-        push(at);
-        scopes_.pop_back();
-        br(after);
-        cur_ = after;
+        under(true, first, [&]() {
+            Inst at;
+            at.op = Opc::Atomic;
+            at.sub = (uint8_t)op;
+            at.ty = t;
+            at.space = Space::Global;
+            at.ops = {gen(ptr, {}), warp};
+            push(at);
+        });
         scopes_.pop_back();
     }
 

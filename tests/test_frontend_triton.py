@@ -38,7 +38,8 @@ def test_masked_vector_add_known_answer(ptx, tmp_path):
     # with -1; lanes at or past N must neither load (a and b are only N long) nor store.
     bir = checked(ptx, kt.vector_add())
     assert "func @vector_add(ptr.global, ptr.global, ptr.global, i64, i64) -> void" in bir      # pointers, then i64 scalars
-    assert bir.count("load f32 ptr.global") == 2 and "select" not in bir and bir.count("condbr") >= 4   # masks are branches
+    # four lanes per loop iteration, two masked loads and one masked store each; masks are branches, never selects
+    assert bir.count("load f32 ptr.global") == 8 and bir.count("store f32 ptr.global") == 4 and "select" not in bir and bir.count("condbr") >= 13
     n, block = 1000, 1024
     a = np.arange(n, dtype=np.float32)
     for text in (bir, ptx.optimized_bir(bir), kb.load("tri_vadd")):
@@ -119,6 +120,7 @@ def test_int32_sources_wrap_and_reduce(ptx, orc, tmp_path):
     # the CPU oracle's launch has no warps)
     bir = checked(ptx, kt.max_i32())
     assert bir.count("warp.reduce.max i32") == 1 and bir.count("atomic.max i32 ptr.global") == 1 and "shuffle" not in bir
+    assert bir.count("load i32 ptr.global") == 4      # four independent loads per loop iteration
     assert "phi i32" in bir and "const.i i32 -2147483648" in bir
     text = ptx.emit(bir).text
     assert "redux.sync.max.s32" in text
