@@ -595,7 +595,7 @@ struct Value {
 // ---------------------------------------------------------------------------------------------
 class KernelCompiler {
 public:
-    KernelCompiler(const Kernel& k, const TritonOptions& o) : k_(k), opt_(o) {}
+    KernelCompiler(const Kernel& k, const TritonOptions& o, Module* m) : k_(k), opt_(o), m_(m) {}
 
     Function run() {
         classify_params();
@@ -612,6 +612,8 @@ public:
 private:
     const Kernel& k_;
     const TritonOptions& opt_;
+    Module* m_;
+    int shared_cells_ = 0;
     Function f_;
     std::map<std::string, Value> env_;
     uint32_t cur_ = 0;
@@ -1544,8 +1546,9 @@ private:
     // ---- atomics and CTA-wide reductions ----
     // tl.atomic_<op>(ptr, tile): one atomic per lane of the tile.  tl.atomic_<op>(scalar_ptr, tl.<red>(x)):
     // every thread folds the lanes it walks, a warp combines its 32 partial results (warp.reduce for
-    // int32, an xor butterfly of shuffles for float32), and lane 0 of each warp issues one atomic.
-    // The CTA must be whole warps, which Triton's num_warps guarantees.
+    // int32, an xor butterfly of shuffles for float32), lane 0 of every warp parks the warp's value in
+    // shared memory, the first warp combines those after a barrier, and thread 0 issues the program's
+    // one atomic.  The CTA must be whole warps, which Triton's num_warps guarantees.
     void atomic(const std::string& op, const NP& ptr, const NP& value, const NP& mask, int line) {
         AtomOp aop = op == "add" ? AtomOp::Add : op == "max" ? AtomOp::Max : AtomOp::Min;
         El el = ptr->pointee;
@@ -1600,36 +1603,77 @@ private:
                 return std::vector<Val>{folded};
             };
         lane_loop(x->shape, line, [&](const Lane& lane) { return std::vector<Val>{gen(x, sub_idx(x, lane.idx))}; }, nullptr, &carried, &fold);
-        Val mine = carried[0], warp;
-        if (el == El::I32) {
-            Inst wr;
-            wr.op = Opc::WarpReduce;
-            wr.sub = (uint8_t)(op == AtomOp::Add ? RedOp::Add : op == AtomOp::Max ? RedOp::Max : RedOp::Min);
-            wr.ty = t;
-            wr.ops = {mine};
-            warp = push(wr);
-        } else {
-            warp = mine;
+        // warp step, then the warps of the CTA through shared memory, then one atomic per program
+        auto warp_combine = [&](Val v) {
+            if (el == El::I32) {
+                Inst wr;
+                wr.op = Opc::WarpReduce;
+                wr.sub = (uint8_t)(op == AtomOp::Add ? RedOp::Add : op == AtomOp::Max ? RedOp::Max : RedOp::Min);
+                wr.ty = t;
+                wr.ops = {v};
+                return push(wr);
+            }
             for (int m = 16; m >= 1; m >>= 1) {
                 Inst sh;
                 sh.op = Opc::Shuffle;
                 sh.sub = (uint8_t)Shfl::Xor;
                 sh.ty = t;
-                sh.ops = {warp, ci(Ty::s(Scalar::I32), m)};
+                sh.ops = {v, ci(Ty::s(Scalar::I32), m)};
                 Val other = push(sh);
-                warp = combine(op, el, other, warp);
+                v = combine(op, el, other, v);
             }
-        }
-        Val lane = bin(BinOp::And, I64(), index(0), ci(I64(), 31));
-        Val first = icmp(ICmp::Eq, I64(), lane, ci(I64(), 0));
-        under(true, first, [&]() {
-            Inst at;
-            at.op = Opc::Atomic;
-            at.sub = (uint8_t)op;
-            at.ty = t;
-            at.space = Space::Global;
-            at.ops = {gen(ptr, {}), warp};
-            push(at);
+            return v;
+        };
+        Val warp = warp_combine(carried[0]);
+        SharedObj so;   // one word per warp of the CTA (at most 32)
+        so.key = ((int64_t)m_->funcs.size() << 32) + 65536 * (int64_t)shared_cells_++;
+        so.bytes = 128;
+        so.align = 16;
+        m_->shared_objs.push_back(so);
+        const Ty ps = Ty::p(Space::Shared);
+        Val tid = index(0), c31 = ci(I64(), 31), c5 = ci(I64(), 5), c4 = ci(I64(), 4), zero64 = ci(I64(), 0);
+        Val lane = bin(BinOp::And, I64(), tid, c31), wid = bin(BinOp::LShr, I64(), tid, c5);
+        under(true, icmp(ICmp::Eq, I64(), lane, zero64), [&]() {
+            Inst st;
+            st.op = Opc::Store;
+            st.ty = Ty::v();
+            st.aux = t;
+            st.space = Space::Shared;
+            st.align = 4;
+            st.ops = {bin(BinOp::Add, ps, ci(ps, so.key), bin(BinOp::Mul, I64(), wid, c4)), warp};
+            push(st);
+        });
+        Inst bar;
+        bar.op = Opc::Barrier;
+        bar.ty = Ty::v();
+        push(bar);
+        under(true, icmp(ICmp::Slt, I64(), tid, ci(I64(), 32)), [&]() {
+            Val warps = bin(BinOp::LShr, I64(), bin(BinOp::Add, I64(), index(6), c31), c5);
+            Val have = icmp(ICmp::Slt, I64(), tid, warps);
+            uint32_t from = cur_, lb = new_block(), mb = new_block();
+            condbr(have, lb, mb);
+            cur_ = lb;
+            Inst ld;
+            ld.op = Opc::Load;
+            ld.ty = t;
+            ld.space = Space::Shared;
+            ld.align = 4;
+            ld.ops = {bin(BinOp::Add, ps, ci(ps, so.key), bin(BinOp::Mul, I64(), tid, c4))};
+            Val part = push(ld);
+            uint32_t l_end = cur_;
+            br(mb);
+            cur_ = mb;
+            Val v = phi(t, {{from, identity}, {l_end, part}});
+            Val all = warp_combine(v);
+            under(true, icmp(ICmp::Eq, I64(), tid, zero64), [&]() {
+                Inst at;
+                at.op = Opc::Atomic;
+                at.sub = (uint8_t)op;
+                at.ty = t;
+                at.space = Space::Global;
+                at.ops = {gen(ptr, {}), all};
+                push(at);
+            });
         });
         scopes_.pop_back();
     }
@@ -1856,8 +1900,9 @@ bool compile_triton(const char* src, size_t len, const TritonOptions& opts, Modu
         }
         for (auto& k : kernels) {
             for (auto& f : m.funcs) if (f.name == k.name) fail("E302", k.line, "`" + k.name + "` is defined twice");
-            KernelCompiler kc(k, opts);
-            m.funcs.push_back(kc.run());
+            KernelCompiler kc(k, opts, &m);
+            Function f = kc.run();
+            m.funcs.push_back(std::move(f));
         }
         std::string why;
         if (!verify_module(m, &why)) {

@@ -116,10 +116,11 @@ def test_int32_sources_wrap_and_reduce(ptx, orc, tmp_path):
         c = np.full(1024, 0x7fffffff, np.int32)
         run_kernel(bir, "vadd_i32", [a, bb, c, n, 1024], threads)
         assert np.array_equal(c[:n], want) and np.all(c[n:] == 0x7fffffff)
-    # the reduction: per-thread fold in a lane loop, one warp.reduce, one atomic per warp (values are checked on the device:
-    # the CPU oracle's launch has no warps)
+    # the reduction: per-thread fold in a lane loop, a warp step, the warps combined through shared memory, one atomic per
+    # program (values are checked on the device: the CPU oracle's launch has no warps)
     bir = checked(ptx, kt.max_i32())
-    assert bir.count("warp.reduce.max i32") == 1 and bir.count("atomic.max i32 ptr.global") == 1 and "shuffle" not in bir
+    assert bir.count("warp.reduce.max i32") == 2 and bir.count("atomic.max i32 ptr.global") == 1 and "shuffle" not in bir
+    assert "shared_obj 0 bytes 128 align 16" in bir and bir.count("barrier") == 1
     assert bir.count("load i32 ptr.global") == 4      # four independent loads per loop iteration
     assert "phi i32" in bir and "const.i i32 -2147483648" in bir
     text = ptx.emit(bir).text
@@ -129,7 +130,7 @@ def test_int32_sources_wrap_and_reduce(ptx, orc, tmp_path):
     src = "@triton.jit\ndef total(x_ptr, out_ptr, n, BLOCK: tl.constexpr):\n    offs = tl.program_id(0) * BLOCK + tl.arange(0, BLOCK)\n" \
           "    tl.atomic_add(out_ptr, tl.sum(tl.load(x_ptr + offs, mask=offs < n, other=0.0), axis=0))\n"
     bir = checked(ptx, b.compile_triton(src))
-    assert bir.count("shuffle.xor f32") == 5 and "atomic.add f32 ptr.global" in bir
+    assert bir.count("shuffle.xor f32") == 10 and bir.count("atomic.add f32 ptr.global") == 1
     ptxas(ptx.emit(bir).text, tmp_path)
     # elementwise atomics run under the oracle: a histogram-like scatter with a mask
     src = "@triton.jit\ndef scatter(idx_ptr, out_ptr, n, BLOCK: tl.constexpr = 16):\n    offs = tl.arange(0, BLOCK)\n    m = offs < n\n" \
