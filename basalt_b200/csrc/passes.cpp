@@ -510,49 +510,74 @@ int fold_constants(Function& f) {
 // A pure instruction identical to one in a dominating position is replaced by it.  Walks the
 // dominator tree (immediate dominators by the iterative algorithm of Cooper, Harvey and Kennedy)
 // with a scoped table, so availability never crosses into a sibling subtree.
-int eliminate_common_subexpressions(Function& f) {
-    const uint32_t nb = (uint32_t)f.blocks.size();
-    if (!nb) return 0;
-    std::vector<std::vector<uint32_t>> preds(nb);
-    std::vector<uint32_t> succ, rpo, order(nb, UINT32_MAX);
-    {   // reverse post-order from the entry
+namespace {
+// Reverse post-order from the entry, predecessors of the reachable blocks, and immediate dominators
+// (the iterative algorithm of Cooper, Harvey and Kennedy); idom is UINT32_MAX for unreachable blocks.
+struct Dominators {
+    std::vector<std::vector<uint32_t>> preds, succs;
+    std::vector<uint32_t> rpo, order, idom;
+    explicit Dominators(const Function& f) {
+        const uint32_t nb = (uint32_t)f.blocks.size();
+        preds.assign(nb, {});
+        succs.assign(nb, {});
+        order.assign(nb, UINT32_MAX);
+        idom.assign(nb, UINT32_MAX);
+        if (!nb) return;
+        std::vector<uint32_t> succ;
+        for (uint32_t b = 0; b < nb; b++) { successors(f.blocks[b].term, succ); succs[b] = succ; }
         std::vector<char> seen(nb, 0);
         std::vector<std::pair<uint32_t, size_t>> st{{0, 0}};
-        std::vector<std::vector<uint32_t>> sx(nb);
-        for (uint32_t b = 0; b < nb; b++) { successors(f.blocks[b].term, succ); sx[b] = succ; }
         seen[0] = 1;
         std::vector<uint32_t> post;
         while (!st.empty()) {
             auto& [b, i] = st.back();
-            if (i < sx[b].size()) {
-                uint32_t s = sx[b][i++];
+            if (i < succs[b].size()) {
+                uint32_t s = succs[b][i++];
                 if (!seen[s]) { seen[s] = 1; st.push_back({s, 0}); }
             } else { post.push_back(b); st.pop_back(); }
         }
         rpo.assign(post.rbegin(), post.rend());
         for (uint32_t i = 0; i < rpo.size(); i++) order[rpo[i]] = i;
-        for (uint32_t b : rpo) for (uint32_t s : sx[b]) preds[s].push_back(b);
-    }
-    std::vector<uint32_t> idom(nb, UINT32_MAX);
-    idom[0] = 0;
-    for (bool changed = true; changed;) {
-        changed = false;
-        for (uint32_t b : rpo) {
-            if (b == 0) continue;
-            uint32_t nd = UINT32_MAX;
-            for (uint32_t p : preds[b]) {
-                if (idom[p] == UINT32_MAX) continue;
-                if (nd == UINT32_MAX) { nd = p; continue; }
-                uint32_t x = p, y = nd;
-                while (x != y) {
-                    while (order[x] > order[y]) x = idom[x];
-                    while (order[y] > order[x]) y = idom[y];
+        for (uint32_t b : rpo) for (uint32_t s : succs[b]) preds[s].push_back(b);
+        idom[0] = 0;
+        for (bool changed = true; changed;) {
+            changed = false;
+            for (uint32_t b : rpo) {
+                if (b == 0) continue;
+                uint32_t nd = UINT32_MAX;
+                for (uint32_t p : preds[b]) {
+                    if (idom[p] == UINT32_MAX) continue;
+                    if (nd == UINT32_MAX) { nd = p; continue; }
+                    uint32_t x = p, y = nd;
+                    while (x != y) {
+                        while (order[x] > order[y]) x = idom[x];
+                        while (order[y] > order[x]) y = idom[y];
+                    }
+                    nd = x;
                 }
-                nd = x;
+                if (nd != idom[b]) { idom[b] = nd; changed = true; }
             }
-            if (nd != idom[b]) { idom[b] = nd; changed = true; }
         }
     }
+    bool dominates(uint32_t a, uint32_t b) const {   // a dominates b (both reachable)
+        while (b != a && b != 0) b = idom[b];
+        return b == a;
+    }
+};
+bool is_pure(const Inst& in) {
+    switch (in.op) {
+        case Opc::ConstI: case Opc::ConstF: case Opc::Bin: case Opc::ICmp: case Opc::FCmp: case Opc::Select: case Opc::Cast: case Opc::Index:
+        case Opc::VecExtract: case Opc::VecBuild: return true;
+        default: return false;
+    }
+}
+}  // namespace
+
+int eliminate_common_subexpressions(Function& f) {
+    const uint32_t nb = (uint32_t)f.blocks.size();
+    if (!nb) return 0;
+    Dominators dom(f);
+    const std::vector<uint32_t>&rpo = dom.rpo, &idom = dom.idom;
     std::vector<std::vector<uint32_t>> kids(nb);
     for (uint32_t b : rpo) if (b != 0 && idom[b] != UINT32_MAX) kids[idom[b]].push_back(b);
 
@@ -598,6 +623,75 @@ int eliminate_common_subexpressions(Function& f) {
         st.pop_back();
     }
     return removed;
+}
+
+
+// ---- loop-invariant code motion ----------------------------------------------------------------
+// A pure instruction inside a natural loop whose operands are all defined outside the loop (or are
+// themselves invariant) moves to the loop's preheader: the one predecessor of the header from outside
+// the loop, when it ends in an unconditional branch (the shape every front end here produces).
+// Division and remainder stay where they are: the CPU oracle's division traps on a zero divisor
+// (crates/basalt-x86/src/oracle.rs:1546-1610), so executing one that the loop would have skipped
+// could add a fault.  Loads are never moved.  The reference's licm (crates/basalt-passes/src/licm.rs).
+int hoist_loop_invariants(Function& f) {
+    int moved_total = 0;
+    for (bool again = true; again;) {
+        again = false;
+        Dominators dom(f);
+        const uint32_t nb = (uint32_t)f.blocks.size();
+        std::vector<uint32_t> def_block(f.insts.size(), UINT32_MAX);
+        for (uint32_t b = 0; b < nb; b++) for (uint32_t id : f.blocks[b].insts) def_block[id] = b;
+        for (uint32_t head : dom.rpo) {
+            std::vector<uint32_t> latches;
+            for (uint32_t p : dom.preds[head]) if (dom.idom[p] != UINT32_MAX && dom.dominates(head, p)) latches.push_back(p);
+            if (latches.empty()) continue;
+            std::vector<char> in_loop(nb, 0);
+            in_loop[head] = 1;
+            std::vector<uint32_t> work = latches;
+            while (!work.empty()) {
+                uint32_t b = work.back();
+                work.pop_back();
+                if (in_loop[b]) continue;
+                in_loop[b] = 1;
+                for (uint32_t p : dom.preds[b]) work.push_back(p);
+            }
+            uint32_t pre = UINT32_MAX;
+            int outside = 0;
+            for (uint32_t p : dom.preds[head]) if (!in_loop[p]) { pre = p; outside++; }
+            if (outside != 1 || f.blocks[pre].term.kind != Term::Br) continue;
+            std::vector<char> invariant(f.insts.size(), 0);
+            std::vector<uint32_t> hoist;
+            for (bool grew = true; grew;) {
+                grew = false;
+                for (uint32_t b : dom.rpo) {
+                    if (!in_loop[b]) continue;
+                    for (uint32_t id : f.blocks[b].insts) {
+                        const Inst& in = f.insts[id];
+                        if (invariant[id] || !is_pure(in)) continue;
+                        if (in.op == Opc::Bin && ((BinOp)in.sub == BinOp::Div || (BinOp)in.sub == BinOp::Rem)) continue;
+                        bool ok = true;
+                        for (Val v : in.ops)
+                            if (!v.param && !invariant[v.idx] && (def_block[v.idx] == UINT32_MAX || in_loop[def_block[v.idx]])) { ok = false; break; }
+                        if (!ok) continue;
+                        invariant[id] = 1;
+                        hoist.push_back(id);
+                        grew = true;
+                    }
+                }
+            }
+            if (hoist.empty()) continue;
+            for (uint32_t b = 0; b < nb; b++) {
+                if (!in_loop[b]) continue;
+                auto& v = f.blocks[b].insts;
+                v.erase(std::remove_if(v.begin(), v.end(), [&](uint32_t id) { return invariant[id] != 0; }), v.end());
+            }
+            for (uint32_t id : hoist) f.blocks[pre].insts.push_back(id);   // in discovery order: operands before their users
+            moved_total += (int)hoist.size();
+            again = true;   // block membership changed: recompute and look at the enclosing loops
+            break;
+        }
+    }
+    return moved_total;
 }
 
 // ---- inliner -------------------------------------------------------------------------------
@@ -1639,6 +1733,7 @@ void optimize_module(Module& m, int opt_level, int reg_budget, std::vector<OptRe
             simplify_cfg(f);
             fold_constants(f);
             eliminate_common_subexpressions(f);
+            hoist_loop_invariants(f);
             dce(f);
             simplify_cfg(f);
             rep.warp_reduces = fuse_warp_reductions(f);

@@ -44,6 +44,10 @@ void dce(Function& f);
 int fold_constants(Function& f);
 // Replaces a pure instruction by an identical one that dominates it.  Returns the number removed.
 int eliminate_common_subexpressions(Function& f);
+// Moves pure instructions whose operands do not change inside a natural loop to the loop's preheader
+// (the reference's licm, crates/basalt-passes/src/licm.rs); never a division, never a load.  Returns
+// the number moved.
+int hoist_loop_invariants(Function& f);
 
 struct OptReport {
     bool elementwise = false;   // one-element-per-thread kernel rewritten to vector accesses

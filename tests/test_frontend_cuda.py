@@ -302,3 +302,37 @@ def test_the_reference_tree_kernels_compile_and_give_their_known_answers(ptx):
         assert out[0] == 20
     with pytest.raises(b.Diag):
         b.compile_cuda(src("deliberate_errors.cu"))
+
+
+def test_loop_invariants_move_to_the_preheader(ptx):
+    # crates/basalt-passes/src/licm.rs: a pure computation on values that do not change in the loop is
+    # done once, before it; a division is left in place (it could trap where the loop would have skipped it).
+    src = """
+__global__ void weighted(const int *x, int *out, int n, int a, int b) {
+    int acc = 0;
+    for (int i = 0; i < n; i++) {
+        int scale = a * b + 7;
+        int risky = (x[i] != 0) ? a / b : 0;
+        acc += x[i] * scale + risky;
+    }
+    out[0] = acc;
+}
+"""
+    bir = b.compile_cuda(src)
+    opt = ptx.optimized_bir(bir)
+    blocks = opt.split("\n  bb")
+    entry = blocks[1]
+    assert "mul i32 %arg3, %arg4" in entry and "const.i i32 7" in entry            # hoisted into the block before the loop
+    assert "div i32" in opt and "div i32" not in entry                              # the division stays guarded inside the loop
+    x = np.array([3, 0, -2, 5, 0, 1], np.int32)
+    for n in (0, 1, 6):
+        o0, o1 = np.zeros(1, np.int32), np.zeros(1, np.int32)
+        run_kernel(bir, "weighted", [x, o0, n, 6, 4], 1)
+        run_kernel(opt, "weighted", [x, o1, n, 6, 4], 1)
+        want = sum(int(v) * (6 * 4 + 7) + (1 if v else 0) for v in x[:n])
+        assert o0[0] == o1[0] == want, n
+    # b = 0 with an all-zero input: the division must not run at all
+    z = np.zeros(4, np.int32)
+    o = np.zeros(1, np.int32)
+    run_kernel(opt, "weighted", [z, o, 4, 6, 0], 1)
+    assert o[0] == 0
