@@ -94,6 +94,7 @@ def _load() -> C.CDLL:
         "basalt_rt_peer_group_handle": (C.c_int, [vp, C.c_char * 64]),
         "basalt_rt_peer_group_connect": (C.c_int, [vp, C.c_char_p, sz]),
         "basalt_rt_peer_allreduce_max_i32": (C.c_int, [vp, u64, u64, C.c_int, C.c_int32, vp]),
+        "basalt_rt_peer_max_i32": (C.c_int, [vp, u64, i64, u64, vp]),
         "basalt_rt_peer_group_status": (C.c_int, [vp, P(C.c_uint32)]),
         "basalt_rt_peer_group_destroy": (C.c_int, [vp]),
         "basalt_k_last_error": (cp, []),
@@ -104,6 +105,7 @@ def _load() -> C.CDLL:
         "basalt_k_sgemm_f32": (C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, vp]),
         "basalt_k_sgemm_f32_static_workspace": (C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, vp]),
         "basalt_k_matmul_f16": (C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, vp, vp]),
+        "basalt_k_max_i32_allreduce": (C.c_int, [vp, i64, vp, P(u64), C.c_int, C.c_int, C.c_uint32, vp, vp, vp, u64, vp]),
         "basalt_k_peer_allreduce_max_i32": (C.c_int, [P(u64), C.c_int, C.c_int, C.c_uint32, vp, vp, vp, u64, C.c_int, C.c_int32, vp]),
     }
     for name, (res, args) in sig.items():

@@ -779,6 +779,8 @@ int basalt_rt_stream_wait_event(basalt_rt_ctx* ctx, void* stream, void* event) {
 // ---- peer-memory exchange group ---------------------------------------------------------------
 static const size_t kPeerInboxBytes = 2u << 20;      // its own allocation granule, so the IPC mapping covers nothing else
 static const size_t kPeerStatusOffset = 4096;
+static const size_t kPeerTicketOffset = 4096 + 64;    // ticket of the fused reduction + exchange kernel, starts at 0
+static const size_t kPeerPartialOffset = 4096 + 128;  // its running maximum, starts at INT32_MIN
 static const uint64_t kPeerTimeoutNs = 2000000000ull;
 
 int basalt_rt_peer_group_create(basalt_rt_ctx* ctx, int nranks, int rank, basalt_rt_peer_group** out) {
@@ -792,6 +794,8 @@ int basalt_rt_peer_group_create(basalt_rt_ctx* ctx, int nranks, int rank, basalt
     rc = check(f, "cuMemAlloc", f.cuMemAlloc(&p, kPeerInboxBytes));
     if (rc) return rc;
     std::vector<unsigned char> zeros(8192, 0);
+    const int32_t lowest = INT32_MIN;
+    memcpy(zeros.data() + kPeerPartialOffset, &lowest, 4);
     rc = check(f, "cuMemcpyHtoD", f.cuMemcpyHtoD(p, zeros.data(), zeros.size()));
     if (rc) { f.cuMemFree(p); return rc; }
     auto* g = new basalt_rt_peer_group;
@@ -849,6 +853,19 @@ int basalt_rt_peer_allreduce_max_i32(basalt_rt_peer_group* g, uint64_t partial, 
     int krc = basalt_k_peer_allreduce_max_i32(g->inbox, g->nranks, g->rank, g->epoch, (int32_t*)(uintptr_t)partial, (int32_t*)(uintptr_t)result,
                                               (uint32_t*)(uintptr_t)(g->own + kPeerStatusOffset), kPeerTimeoutNs, reset, reset_value, stream);
     if (krc != 0) return set_err(3, krc, "basalt_k_peer_allreduce_max_i32", basalt_k_last_error());
+    return 0;
+}
+
+int basalt_rt_peer_max_i32(basalt_rt_peer_group* g, uint64_t shard, int64_t n, uint64_t result, void* stream) {
+    if (!g || !shard || !result) return set_err(4, 0, "basalt_rt_peer_max_i32", "null argument");
+    if (!g->connected) return set_err(4, 0, "basalt_rt_peer_max_i32", "the group is not connected");
+    int rc = make_current(g->ctx);
+    if (rc) return rc;
+    if (++g->epoch == 0) g->epoch = 1;
+    int krc = basalt_k_max_i32_allreduce((const int32_t*)(uintptr_t)shard, n, (int32_t*)(uintptr_t)(g->own + kPeerPartialOffset), g->inbox, g->nranks, g->rank, g->epoch,
+                                         (int32_t*)(uintptr_t)result, (uint32_t*)(uintptr_t)(g->own + kPeerStatusOffset),
+                                         (uint32_t*)(uintptr_t)(g->own + kPeerTicketOffset), kPeerTimeoutNs, stream);
+    if (krc != 0) return set_err(3, krc, "basalt_k_max_i32_allreduce", basalt_k_last_error());
     return 0;
 }
 

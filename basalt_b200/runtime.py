@@ -388,6 +388,11 @@ class PeerGroup:
         _check(lib.basalt_rt_peer_allreduce_max_i32(self._h, partial_ptr, result_ptr, 0 if reset_to is None else 1,
                                                     0 if reset_to is None else reset_to, C.c_void_p(stream)))
 
+    def max_i32(self, shard_ptr: int, n: int, result_ptr: int, stream=None):
+        """The whole sharded step in one launch: the reduction of this rank's shard and the exchange
+        (basalt_rt_peer_max_i32); the running maximum and the ticket live in the group."""
+        _check(lib.basalt_rt_peer_max_i32(self._h, shard_ptr, n, result_ptr, C.c_void_p(stream)))
+
     def status(self) -> int:
         """Synchronises the context; non-zero bits name ranks that did not answer within the bound."""
         out = C.c_uint32(0)

@@ -531,6 +531,9 @@ def main():
         kernels.max_i32(x.data_ptr(), n, partial.data_ptr(), stream)
         exchange()
 
+    def step_fused():                                          # hand-written: reduction and exchange in one launch
+        peers.max_i32(x.data_ptr(), n, result.data_ptr(), stream)
+
     def last_result():
         return int((result if world > 1 else partial).item())
 
@@ -564,6 +567,13 @@ def main():
     for _ in range(args.warmup):
         step_hand()
     hand_ms = timed_loop(step_hand, args.steps) / args.steps
+    fused = None
+    if peers is not None:
+        for _ in range(args.warmup):
+            step_fused()
+        fused_ms = timed_loop(step_fused, args.steps) / args.steps
+        fused = {"ms_per_step": fused_ms, "gbs_all_ranks": 4.0 * n * world / fused_ms / 1e6, "ok": last_result() == group.max_i32_host(expect_local),
+                 "what": "hand-written kernel: the shard's reduction and, in its last CTA, the peer-memory exchange; one launch per step"}
     t_end = time.time()
 
     # ---- end to end: host buffers through the reference's CPU launch ABI on the device ----
@@ -642,6 +652,8 @@ def main():
             line["others"] = others
         if sharded is not None:
             line["matmul_f16_8192_sharded"] = sharded
+        if fused is not None:
+            line["handwritten_fused_reduce_exchange"] = fused
         emit_line(line)
     if peers is not None:
         bad = peers.status()

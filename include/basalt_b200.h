@@ -240,6 +240,9 @@ int basalt_rt_peer_group_handle(basalt_rt_peer_group *g, unsigned char handle_ou
 int basalt_rt_peer_group_connect(basalt_rt_peer_group *g, const unsigned char *handles, size_t nbytes);
 int basalt_rt_peer_allreduce_max_i32(basalt_rt_peer_group *g, uint64_t partial, uint64_t result, int reset,
                                      int32_t reset_value, void *stream);
+/* The whole sharded max_i32 step in one launch (basalt_k_max_i32_allreduce): reduction of the rank's
+ * shard and the exchange, with the group's own running-maximum and ticket words. */
+int basalt_rt_peer_max_i32(basalt_rt_peer_group *g, uint64_t shard, int64_t n, uint64_t result, void *stream);
 int basalt_rt_peer_group_status(basalt_rt_peer_group *g, uint32_t *status_out);
 int basalt_rt_peer_group_destroy(basalt_rt_peer_group *g);
 

@@ -81,6 +81,15 @@ int basalt_k_peer_allreduce_max_i32(const uint64_t *inboxes, int nranks, int ran
                                     int32_t *partial, int32_t *result, uint32_t *status,
                                     uint64_t timeout_ns, int reset, int32_t reset_value, void *stream);
 
+/* The sharded max_i32 step as ONE kernel: the reduction of this rank's shard x[0..n) (as
+ * basalt_k_max_i32) and, in the CTA that finishes last, the exchange of basalt_k_peer_allreduce_max_i32.
+ * *partial must hold INT32_MIN and *ticket 0 before the first call; the kernel leaves them so.
+ * *result receives the maximum over all ranks' shards.  x must be 16-byte aligned.  The other
+ * arguments are those of basalt_k_peer_allreduce_max_i32.  No counterpart in the reference. */
+int basalt_k_max_i32_allreduce(const int32_t *x, int64_t n, int32_t *partial, const uint64_t *inboxes, int nranks,
+                               int rank, uint32_t epoch, int32_t *result, uint32_t *status, uint32_t *ticket,
+                               uint64_t timeout_ns, void *stream);
+
 #if defined(__GNUC__)
 #pragma GCC visibility pop
 #endif

@@ -56,6 +56,12 @@ def main():
         peers.allreduce_max_i32(partial.device_ptr(), result2.device_ptr())
         assert peers.status() == 0
         assert int(result2.to_numpy(np.int32)[0]) == int(want[0]), (plant, "peer exchange")
+        # reduction and exchange in one kernel (hand-written), twice in a row: it must leave its own state ready
+        for again in range(2):
+            result3 = ctx.upload(np.array([54321], np.int32))
+            peers.max_i32(dshard.device_ptr(), hi - lo, result3.device_ptr())
+            assert peers.status() == 0
+            assert int(result3.to_numpy(np.int32)[0]) == int(want[0]), (plant, "fused", again)
 
     # ---- peer exchange: many back-to-back epochs with values that change every call ----
     calls = 300
