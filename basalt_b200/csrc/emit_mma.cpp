@@ -62,7 +62,11 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
         return std::string(nm);
     };
     char d[256];
-    snprintf(d, sizeof d, "\t.reg .f32 %%mm%d_acc<64>, %%mm%d_fa<8>, %%mm%d_fb<8>, %%mm%d_st<16>;", u, u, u, u);
+    snprintf(d, sizeof d, "\t.reg .f32 %%mm%d_fa<8>, %%mm%d_st<16>;", u, u);
+    decls->push_back(d);
+    // accumulators as packed pairs (columns 2p, 2p+1 of the thread's row i in acc2[4i+p]), the eight A values of a
+    // K step duplicated into both halves of a 64-bit register, the eight B values as four pairs
+    snprintf(d, sizeof d, "\t.reg .b64 %%mm%d_acc2_<32>, %%mm%d_ad<8>, %%mm%d_bp<4>;", u, u, u);
     decls->push_back(d);
     snprintf(d, sizeof d, "\t.reg .b32 %%mm%d_tid, %%mm%d_tx, %%mm%d_ty, %%mm%d_t, %%mm%d_arow, %%mm%d_acol, %%mm%d_brow, %%mm%d_bcol, %%mm%d_asst, %%mm%d_bsst, %%mm%d_asrd, %%mm%d_bsrd, %%mm%d_as, %%mm%d_bs, %%mm%d_kb, %%mm%d_kb1, %%mm%d_off, %%mm%d_x, %%mm%d_y;",
              u, u, u, u, u, u, u, u, u, u, u, u, u, u, u, u, u, u, u);
@@ -78,8 +82,6 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
         snprintf(d, sizeof d, "\t.reg .b64 %%mm%d_ta, %%mm%d_tb, %%mm%d_td, %%mm%d_ws, %%mm%d_tkp, %%mm%d_pp;", u, u, u, u, u, u);
         decls->push_back(d);
         snprintf(d, sizeof d, "\t.reg .pred %%mm%d_whole, %%mm%d_one, %%mm%d_t0, %%mm%d_notlast, %%mm%d_pl;", u, u, u, u, u);
-        decls->push_back(d);
-        snprintf(d, sizeof d, "\t.reg .f32 %%mm%d_q<8>;", u);
         decls->push_back(d);
         snprintf(d, sizeof d, "\t.shared .align 4 .b8 __mm%d_tks[4];", u);
         decls->push_back(d);
@@ -99,10 +101,11 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
     const std::string tid = R("tid"), tx = R("tx"), ty = R("ty"), t = R("t"), arow = R("arow"), acol = R("acol"), brow = R("brow"), bcol = R("bcol");
     const std::string asst = R("asst"), bsst = R("bsst"), asrd = R("asrd"), bsrd = R("bsrd"), as = R("as"), bs = R("bs"), kb = R("kb"), kb1 = R("kb1"), off = R("off");
     const std::string x = R("x"), y = R("y"), ag = R("ag"), ag2 = R("ag2"), bg = R("bg"), bg2 = R("bg2"), w = R("w"), cp = R("c"), more = R("more"), bad = R("bad");
-    auto acc = [&](int i) { return R("acc", i); };
+    auto acc2 = [&](int i) { return R("acc2_", i); };
     auto st = [&](int i) { return R("st", i); };
     auto fa = [&](int i) { return R("fa", i); };
-    auto fb = [&](int i) { return R("fb", i); };
+    auto ad = [&](int i) { return R("ad", i); };
+    auto bp = [&](int i) { return R("bp", i); };
 
     o("// mma f32 128x128x%u: register-tiled FFMA, lda=%lld ldb=%lld ldd=%lld", in.k, lda, ldb, ldd);
     o("mov.u32 %s, %%ntid.x;", t.c_str());
@@ -173,7 +176,7 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
     o("mad.lo.u32 %s, %s, 4, %s;", bsst.c_str(), bcol.c_str(), t.c_str());
     o("mad.lo.u32 %s, %s, 16, %s;", asrd.c_str(), ty.c_str(), as.c_str());
     o("mad.lo.u32 %s, %s, 16, %s;", bsrd.c_str(), tx.c_str(), bs.c_str());
-    for (int i = 0; i < 64; i++) o("mov.f32 %s, 0f00000000;", acc(i).c_str());
+    for (int i = 0; i < 32; i++) o("mov.b64 %s, 0;", acc2(i).c_str());
     auto fetch = [&](const char* pred) {
         o("%sld.global.v4.f32 {%s, %s, %s, %s}, [%s];", pred, st(0).c_str(), st(1).c_str(), st(2).c_str(), st(3).c_str(), ag.c_str());
         o("%sld.global.v4.f32 {%s, %s, %s, %s}, [%s];", pred, st(4).c_str(), st(5).c_str(), st(6).c_str(), st(7).c_str(), ag2.c_str());
@@ -206,13 +209,16 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
     fetch(("@" + more + " ").c_str());
     o("add.u32 %s, %s, %s;", x.c_str(), asrd.c_str(), off.c_str());
     o("add.u32 %s, %s, %s;", y.c_str(), bsrd.c_str(), off.c_str());
+    // Packed FP32: fma.rn.f32x2 does two IEEE fused multiply-adds per instruction (the same bits as two
+    // fma.rn.f32), so a K step is 32 FMA instructions plus 8 register pairings instead of 64 FMAs.
     for (int k = 0; k < 16; k++) {
         o("ld.shared.v4.f32 {%s, %s, %s, %s}, [%s+%d];", fa(0).c_str(), fa(1).c_str(), fa(2).c_str(), fa(3).c_str(), x.c_str(), k * 512);
         o("ld.shared.v4.f32 {%s, %s, %s, %s}, [%s+%d];", fa(4).c_str(), fa(5).c_str(), fa(6).c_str(), fa(7).c_str(), x.c_str(), k * 512 + 256);
-        o("ld.shared.v4.f32 {%s, %s, %s, %s}, [%s+%d];", fb(0).c_str(), fb(1).c_str(), fb(2).c_str(), fb(3).c_str(), y.c_str(), k * 512);
-        o("ld.shared.v4.f32 {%s, %s, %s, %s}, [%s+%d];", fb(4).c_str(), fb(5).c_str(), fb(6).c_str(), fb(7).c_str(), y.c_str(), k * 512 + 256);
+        o("ld.shared.v2.b64 {%s, %s}, [%s+%d];", bp(0).c_str(), bp(1).c_str(), y.c_str(), k * 512);
+        o("ld.shared.v2.b64 {%s, %s}, [%s+%d];", bp(2).c_str(), bp(3).c_str(), y.c_str(), k * 512 + 256);
+        for (int i = 0; i < 8; i++) o("mov.b64 %s, {%s, %s};", ad(i).c_str(), fa(i).c_str(), fa(i).c_str());
         for (int i = 0; i < 8; i++)
-            for (int j = 0; j < 8; j++) o("fma.rn.f32 %s, %s, %s, %s;", acc(i * 8 + j).c_str(), fa(i).c_str(), fb(j).c_str(), acc(i * 8 + j).c_str());
+            for (int q = 0; q < 4; q++) o("fma.rn.f32x2 %s, %s, %s, %s;", acc2(i * 4 + q).c_str(), ad(i).c_str(), bp(q).c_str(), acc2(i * 4 + q).c_str());
     }
     o("@!%s bra %s;", more.c_str(), l_done.c_str());
     o("xor.b32 %s, %s, 8192;", off.c_str(), off.c_str());
@@ -225,7 +231,6 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
         const std::string parts = R("parts"), part = R("part"), tile = R("tile"), full = R("full"), tt = R("tt"), tk = R("tk"), pv = R("p");
         const std::string ws = R("ws"), tkp = R("tkp"), pp = R("pp"), one = R("one"), t0 = R("t0"), notlast = R("notlast"), pl = R("pl");
         std::string l_store = "$mm" + std::to_string(u) + "_store", l_sum = "$mm" + std::to_string(u) + "_sum";
-        auto q = [&](int i) { return R("q", i); };
         o("setp.eq.u32 %s, %s, 1;", one.c_str(), parts.c_str());
         o("@%s bra %s;", one.c_str(), l_store.c_str());
         // this part's partial sums: workspace + ((tile - full) * parts + part) * 64 KB, laid out [128][128]
@@ -245,8 +250,8 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
         o("add.u64 %s, %s, %s;", pp.c_str(), ws.c_str(), w.c_str());
         for (int i = 0; i < 8; i++) {
             int off = ((i & 3) + (i >> 2) * 64) * 512;
-            o("st.global.v4.f32 [%s+%d], {%s, %s, %s, %s};", pp.c_str(), off, acc(i * 8).c_str(), acc(i * 8 + 1).c_str(), acc(i * 8 + 2).c_str(), acc(i * 8 + 3).c_str());
-            o("st.global.v4.f32 [%s+%d], {%s, %s, %s, %s};", pp.c_str(), off + 256, acc(i * 8 + 4).c_str(), acc(i * 8 + 5).c_str(), acc(i * 8 + 6).c_str(), acc(i * 8 + 7).c_str());
+            o("st.global.v2.b64 [%s+%d], {%s, %s};", pp.c_str(), off, acc2(i * 4).c_str(), acc2(i * 4 + 1).c_str());
+            o("st.global.v2.b64 [%s+%d], {%s, %s};", pp.c_str(), off + 256, acc2(i * 4 + 2).c_str(), acc2(i * 4 + 3).c_str());
         }
         o("membar.gl;");
         o("bar.sync 0;");
@@ -262,15 +267,15 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
         o("@%s bra %s;", notlast.c_str(), l_skip.c_str());                  // another part finishes this tile
         o("membar.gl;");
         // the last part to arrive adds every part in index order, so the bits do not depend on who was last
-        for (int i = 0; i < 64; i++) o("mov.f32 %s, 0f00000000;", acc(i).c_str());
+        for (int i = 0; i < 32; i++) o("mov.b64 %s, 0;", acc2(i).c_str());
         o("mov.u32 %s, 0;", pv.c_str());
         o("mov.u64 %s, %s;", pp.c_str(), ws.c_str());
         o.label(l_sum);
         for (int i = 0; i < 8; i++) {
             int off = ((i & 3) + (i >> 2) * 64) * 512;
-            o("ld.global.cg.v4.f32 {%s, %s, %s, %s}, [%s+%d];", q(0).c_str(), q(1).c_str(), q(2).c_str(), q(3).c_str(), pp.c_str(), off);
-            o("ld.global.cg.v4.f32 {%s, %s, %s, %s}, [%s+%d];", q(4).c_str(), q(5).c_str(), q(6).c_str(), q(7).c_str(), pp.c_str(), off + 256);
-            for (int j = 0; j < 8; j++) o("add.rn.f32 %s, %s, %s;", acc(i * 8 + j).c_str(), acc(i * 8 + j).c_str(), q(j).c_str());
+            o("ld.global.cg.v2.b64 {%s, %s}, [%s+%d];", bp(0).c_str(), bp(1).c_str(), pp.c_str(), off);
+            o("ld.global.cg.v2.b64 {%s, %s}, [%s+%d];", bp(2).c_str(), bp(3).c_str(), pp.c_str(), off + 256);
+            for (int j = 0; j < 4; j++) o("add.rn.f32x2 %s, %s, %s;", acc2(i * 4 + j).c_str(), acc2(i * 4 + j).c_str(), bp(j).c_str());
         }
         o("add.u64 %s, %s, 65536;", pp.c_str(), pp.c_str());
         o("add.u32 %s, %s, 1;", pv.c_str(), pv.c_str());
@@ -287,8 +292,8 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
     o("add.u64 %s, %s, %s;", cp.c_str(), cp.c_str(), w.c_str());
     for (int i = 0; i < 8; i++) {
         long long rowoff = ((i & 3) + (i >> 2) * 64) * ldd * 4;
-        o("st.global.v4.f32 [%s+%lld], {%s, %s, %s, %s};", cp.c_str(), rowoff, acc(i * 8).c_str(), acc(i * 8 + 1).c_str(), acc(i * 8 + 2).c_str(), acc(i * 8 + 3).c_str());
-        o("st.global.v4.f32 [%s+%lld], {%s, %s, %s, %s};", cp.c_str(), rowoff + 256, acc(i * 8 + 4).c_str(), acc(i * 8 + 5).c_str(), acc(i * 8 + 6).c_str(), acc(i * 8 + 7).c_str());
+        o("st.global.v2.b64 [%s+%lld], {%s, %s};", cp.c_str(), rowoff, acc2(i * 4).c_str(), acc2(i * 4 + 1).c_str());
+        o("st.global.v2.b64 [%s+%lld], {%s, %s};", cp.c_str(), rowoff + 256, acc2(i * 4 + 2).c_str(), acc2(i * 4 + 3).c_str());
     }
     o.label(l_skip);
     o("bar.sync 0;");
