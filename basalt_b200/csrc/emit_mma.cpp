@@ -68,6 +68,8 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
     // K step duplicated into both halves of a 64-bit register, the eight B values as four pairs
     snprintf(d, sizeof d, "\t.reg .b64 %%mm%d_acc2_<32>, %%mm%d_ad<8>, %%mm%d_bp<4>;", u, u, u);
     decls->push_back(d);
+    snprintf(d, sizeof d, "\t.reg .b32 %%mm%d_asq<4>, %%mm%d_xq<4>;", u, u);
+    decls->push_back(d);
     snprintf(d, sizeof d, "\t.reg .b32 %%mm%d_tid, %%mm%d_tx, %%mm%d_ty, %%mm%d_t, %%mm%d_arow, %%mm%d_acol, %%mm%d_brow, %%mm%d_bcol, %%mm%d_asst, %%mm%d_bsst, %%mm%d_asrd, %%mm%d_bsrd, %%mm%d_as, %%mm%d_bs, %%mm%d_kb, %%mm%d_kb1, %%mm%d_off, %%mm%d_x, %%mm%d_y;",
              u, u, u, u, u, u, u, u, u, u, u, u, u, u, u, u, u, u, u);
     decls->push_back(d);
@@ -170,11 +172,22 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
     o("cvt.u32.u64 %s, %s;", as.c_str(), w.c_str());
     o("mov.u64 %s, __mm%d_bs;", w.c_str(), u);
     o("cvt.u32.u64 %s, %s;", bs.c_str(), w.c_str());
+    // The A slab is stored transposed, As[k][m]; column m of row k lives at m ^ 8 * ((k >> 2) & 3), so that the four
+    // threads that stage the same row of A (k = 0-3, 4-7, 8-11, 12-15) hit different banks.  A thread's fragment is four
+    // consecutive m starting at a multiple of 4, which the swizzle keeps together.
+    o("and.b32 %s, %s, 3;", t.c_str(), tid.c_str());
+    o("shl.b32 %s, %s, 3;", t.c_str(), t.c_str());
+    o("xor.b32 %s, %s, %s;", x.c_str(), arow.c_str(), t.c_str());
     o("mad.lo.u32 %s, %s, 512, %s;", t.c_str(), acol.c_str(), as.c_str());
-    o("mad.lo.u32 %s, %s, 4, %s;", asst.c_str(), arow.c_str(), t.c_str());
+    o("mad.lo.u32 %s, %s, 4, %s;", asst.c_str(), x.c_str(), t.c_str());
     o("mad.lo.u32 %s, %s, 512, %s;", t.c_str(), brow.c_str(), bs.c_str());
     o("mad.lo.u32 %s, %s, 4, %s;", bsst.c_str(), bcol.c_str(), t.c_str());
     o("mad.lo.u32 %s, %s, 16, %s;", asrd.c_str(), ty.c_str(), as.c_str());
+    o("shl.b32 %s, %s, 4;", t.c_str(), ty.c_str());
+    for (int q = 0; q < 4; q++) {
+        o("xor.b32 %s, %s, %d;", x.c_str(), t.c_str(), q * 32);
+        o("add.u32 %s, %s, %s;", R("asq", q).c_str(), as.c_str(), x.c_str());
+    }
     o("mad.lo.u32 %s, %s, 16, %s;", bsrd.c_str(), tx.c_str(), bs.c_str());
     for (int i = 0; i < 32; i++) o("mov.b64 %s, 0;", acc2(i).c_str());
     auto fetch = [&](const char* pred) {
@@ -207,13 +220,13 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
     o("add.u64 %s, %s, %lld;", bg.c_str(), bg.c_str(), 16 * ldb * 4);
     o("add.u64 %s, %s, %lld;", bg2.c_str(), bg2.c_str(), 16 * ldb * 4);
     fetch(("@" + more + " ").c_str());
-    o("add.u32 %s, %s, %s;", x.c_str(), asrd.c_str(), off.c_str());
+    for (int q = 0; q < 4; q++) o("add.u32 %s, %s, %s;", R("xq", q).c_str(), R("asq", q).c_str(), off.c_str());
     o("add.u32 %s, %s, %s;", y.c_str(), bsrd.c_str(), off.c_str());
     // Packed FP32: fma.rn.f32x2 does two IEEE fused multiply-adds per instruction (the same bits as two
     // fma.rn.f32), so a K step is 32 FMA instructions plus 8 register pairings instead of 64 FMAs.
     for (int k = 0; k < 16; k++) {
-        o("ld.shared.v4.f32 {%s, %s, %s, %s}, [%s+%d];", fa(0).c_str(), fa(1).c_str(), fa(2).c_str(), fa(3).c_str(), x.c_str(), k * 512);
-        o("ld.shared.v4.f32 {%s, %s, %s, %s}, [%s+%d];", fa(4).c_str(), fa(5).c_str(), fa(6).c_str(), fa(7).c_str(), x.c_str(), k * 512 + 256);
+        o("ld.shared.v4.f32 {%s, %s, %s, %s}, [%s+%d];", fa(0).c_str(), fa(1).c_str(), fa(2).c_str(), fa(3).c_str(), R("xq", k >> 2).c_str(), k * 512);
+        o("ld.shared.v4.f32 {%s, %s, %s, %s}, [%s+%d];", fa(4).c_str(), fa(5).c_str(), fa(6).c_str(), fa(7).c_str(), R("xq", k >> 2).c_str(), k * 512 + 256);
         o("ld.shared.v2.b64 {%s, %s}, [%s+%d];", bp(0).c_str(), bp(1).c_str(), y.c_str(), k * 512);
         o("ld.shared.v2.b64 {%s, %s}, [%s+%d];", bp(2).c_str(), bp(3).c_str(), y.c_str(), k * 512 + 256);
         for (int i = 0; i < 8; i++) o("mov.b64 %s, {%s, %s};", ad(i).c_str(), fa(i).c_str(), fa(i).c_str());
