@@ -114,16 +114,8 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
     o("setp.ne.u32 %s, %s, 256;", bad.c_str(), t.c_str());
     o("@%s bra %s;", bad.c_str(), l_skip.c_str());   // wrong block size: leave the output untouched rather than misbehave
     o("mov.u32 %s, %%tid.x;", tid.c_str());
-    // a warp covers 8 columns x 4 rows of the 16 x 16 thread grid (warp w sits at columns 8(w & 1), rows 4(w >> 1)):
-    // per K step it then reads four distinct A fragments and eight adjacent B fragments (128 contiguous bytes)
-    o("and.b32 %s, %s, 7;", tx.c_str(), tid.c_str());
-    o("shr.u32 %s, %s, 5;", t.c_str(), tid.c_str());
-    o("and.b32 %s, %s, 1;", x.c_str(), t.c_str());
-    o("mad.lo.u32 %s, %s, 8, %s;", tx.c_str(), x.c_str(), tx.c_str());
-    o("shr.u32 %s, %s, 1;", t.c_str(), t.c_str());
-    o("shr.u32 %s, %s, 3;", x.c_str(), tid.c_str());
-    o("and.b32 %s, %s, 3;", x.c_str(), x.c_str());
-    o("mad.lo.u32 %s, %s, 4, %s;", ty.c_str(), t.c_str(), x.c_str());
+    o("and.b32 %s, %s, 15;", tx.c_str(), tid.c_str());
+    o("shr.u32 %s, %s, 4;", ty.c_str(), tid.c_str());
     o("shr.u32 %s, %s, 2;", arow.c_str(), tid.c_str());
     o("and.b32 %s, %s, 3;", t.c_str(), tid.c_str());
     o("shl.b32 %s, %s, 2;", acol.c_str(), t.c_str());
