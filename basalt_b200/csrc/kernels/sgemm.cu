@@ -4,7 +4,10 @@
 // four 4x4 quadrants so that every shared-memory read is a conflict-free 16-byte access; the next
 // K slab is copied from global memory straight into the other half of a shared-memory double
 // buffer with cp.async while the current one is multiplied (no staging registers).  Per K step a
-// thread issues 4 LDS.128 for 64 FFMA.  Two CTAs are resident per SM (32 KB shared each).
+// thread issues 4 LDS.128 for 32 packed FMAs (__ffma2_rn: two IEEE fused multiply-adds per
+// instruction, the same bits as two fmaf).  The transposed A slab is swizzled -- column m of row k
+// sits at m ^ 8 * ((k >> 2) & 3) -- so that the four threads staging one row of A hit different banks.
+// Two CTAs are resident per SM (32 KB shared each).
 //
 // Tail wave.  With R resident CTAs (2 per SM) and T tiles, the last T mod R tiles would run as a
 // mostly empty wave (4096^2 in 128x128 tiles: 1024 tiles on 296 slots is 3.46 waves, paid as 4).
@@ -57,6 +60,7 @@ __global__ void __launch_bounds__(THREADS, 2) sgemm_f32_kernel(const float* __re
     // global -> register staging: A slab is 128 rows x 16 floats (4 float4 per row), B slab is
     // 16 rows x 128 floats (32 float4 per row); two float4 of each per thread.
     const int a_row = tid >> 2, a_col = (tid & 3) * 4;   // rows a_row and a_row + 64
+    const int a_sw = a_row ^ ((tid & 3) << 3);           // swizzled column of the transposed slab: rows a_col .. a_col+3 all have (k >> 2) & 3 == tid & 3
     const int b_row = tid >> 5, b_col = (tid & 31) * 4;  // rows b_row and b_row + 8
     // four running pointers, advanced by one K slab per iteration
     const float* Ag0 = A + (size_t)(m0 + a_row) * K + k_begin + a_col;
@@ -69,8 +73,8 @@ __global__ void __launch_bounds__(THREADS, 2) sgemm_f32_kernel(const float* __re
     auto copy_slab = [&](int buf) {
 #pragma unroll
         for (int c = 0; c < 4; c++) {
-            cp_async<4>(&As[buf][a_col + c][a_row], Ag0 + c);
-            cp_async<4>(&As[buf][a_col + c][a_row + 64], Ag1 + c);
+            cp_async<4>(&As[buf][a_col + c][a_sw], Ag0 + c);
+            cp_async<4>(&As[buf][a_col + c][a_sw + 64], Ag1 + c);
         }
         cp_async<16>(&Bs[buf][b_row][b_col], Bg0);
         cp_async<16>(&Bs[buf][b_row + 8][b_col], Bg1);
@@ -78,11 +82,11 @@ __global__ void __launch_bounds__(THREADS, 2) sgemm_f32_kernel(const float* __re
         Ag0 += BK; Ag1 += BK; Bg0 += b_step; Bg1 += b_step;
     };
 
-    float acc[8][8];
+    float2 acc2[8][4];   // acc2[i][p] = (C[i][2p], C[i][2p+1]) of the thread's 8 x 8 block
 #pragma unroll
     for (int i = 0; i < 8; i++)
 #pragma unroll
-        for (int j = 0; j < 8; j++) acc[i][j] = 0.0f;
+        for (int p = 0; p < 4; p++) acc2[i][p] = make_float2(0.0f, 0.0f);
 
     copy_slab(0);
     asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -91,27 +95,21 @@ __global__ void __launch_bounds__(THREADS, 2) sgemm_f32_kernel(const float* __re
     for (int kb = 0; kb < nk; kb++) {
         const int buf = kb & 1;
         if (kb + 1 < nk) copy_slab(buf ^ 1);   // lands while this slab is multiplied
-        // register double buffer for the fragments: step k+1 is read from shared memory while step k is multiplied
-        float4 fa[2][2], fb[2][2];
-        fa[0][0] = *reinterpret_cast<const float4*>(&As[buf][0][ty * 4]);
-        fa[0][1] = *reinterpret_cast<const float4*>(&As[buf][0][ty * 4 + 64]);
-        fb[0][0] = *reinterpret_cast<const float4*>(&Bs[buf][0][tx * 4]);
-        fb[0][1] = *reinterpret_cast<const float4*>(&Bs[buf][0][tx * 4 + 64]);
 #pragma unroll
         for (int k = 0; k < BK; k++) {
-            const int cur = k & 1, nxt = cur ^ 1;
-            if (k + 1 < BK) {
-                fa[nxt][0] = *reinterpret_cast<const float4*>(&As[buf][k + 1][ty * 4]);
-                fa[nxt][1] = *reinterpret_cast<const float4*>(&As[buf][k + 1][ty * 4 + 64]);
-                fb[nxt][0] = *reinterpret_cast<const float4*>(&Bs[buf][k + 1][tx * 4]);
-                fb[nxt][1] = *reinterpret_cast<const float4*>(&Bs[buf][k + 1][tx * 4 + 64]);
+            const int m = (ty * 4) ^ (((k >> 2) & 3) << 3);
+            const float4 a0 = *reinterpret_cast<const float4*>(&As[buf][k][m]);
+            const float4 a1 = *reinterpret_cast<const float4*>(&As[buf][k][m + 64]);
+            const float4 b0 = *reinterpret_cast<const float4*>(&Bs[buf][k][tx * 4]);
+            const float4 b1 = *reinterpret_cast<const float4*>(&Bs[buf][k][tx * 4 + 64]);
+            const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+            const float2 b[4] = {make_float2(b0.x, b0.y), make_float2(b0.z, b0.w), make_float2(b1.x, b1.y), make_float2(b1.z, b1.w)};
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const float2 ai = make_float2(a[i], a[i]);
+#pragma unroll
+                for (int p = 0; p < 4; p++) acc2[i][p] = __ffma2_rn(ai, b[p], acc2[i][p]);
             }
-            const float a[8] = {fa[cur][0].x, fa[cur][0].y, fa[cur][0].z, fa[cur][0].w, fa[cur][1].x, fa[cur][1].y, fa[cur][1].z, fa[cur][1].w};
-            const float b[8] = {fb[cur][0].x, fb[cur][0].y, fb[cur][0].z, fb[cur][0].w, fb[cur][1].x, fb[cur][1].y, fb[cur][1].z, fb[cur][1].w};
-#pragma unroll
-            for (int i = 0; i < 8; i++)
-#pragma unroll
-                for (int j = 0; j < 8; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
@@ -123,8 +121,8 @@ __global__ void __launch_bounds__(THREADS, 2) sgemm_f32_kernel(const float* __re
 #pragma unroll
         for (int i = 0; i < 8; i++) {
             float* prow = mine + (ty * 4 + (i & 3) + (i >> 2) * 64) * BN + tx * 4;
-            *reinterpret_cast<float4*>(prow) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
-            *reinterpret_cast<float4*>(prow + 64) = make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
+            *reinterpret_cast<float4*>(prow) = make_float4(acc2[i][0].x, acc2[i][0].y, acc2[i][1].x, acc2[i][1].y);
+            *reinterpret_cast<float4*>(prow + 64) = make_float4(acc2[i][2].x, acc2[i][2].y, acc2[i][3].x, acc2[i][3].y);
         }
         __threadfence();
         __syncthreads();
@@ -143,8 +141,8 @@ __global__ void __launch_bounds__(THREADS, 2) sgemm_f32_kernel(const float* __re
                 lo.x += l2.x; lo.y += l2.y; lo.z += l2.z; lo.w += l2.w;
                 hi.x += h2.x; hi.y += h2.y; hi.z += h2.z; hi.w += h2.w;
             }
-            acc[i][0] = lo.x; acc[i][1] = lo.y; acc[i][2] = lo.z; acc[i][3] = lo.w;
-            acc[i][4] = hi.x; acc[i][5] = hi.y; acc[i][6] = hi.z; acc[i][7] = hi.w;
+            acc2[i][0] = make_float2(lo.x, lo.y); acc2[i][1] = make_float2(lo.z, lo.w);
+            acc2[i][2] = make_float2(hi.x, hi.y); acc2[i][3] = make_float2(hi.z, hi.w);
         }
         if (tid == 0) tickets[t] = 0;   // ready for the next launch
     }
@@ -152,8 +150,8 @@ __global__ void __launch_bounds__(THREADS, 2) sgemm_f32_kernel(const float* __re
     for (int i = 0; i < 8; i++) {
         const int row = m0 + ty * 4 + (i & 3) + (i >> 2) * 64;
         float* crow = C + (size_t)row * N + n0 + tx * 4;
-        *reinterpret_cast<float4*>(crow) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
-        *reinterpret_cast<float4*>(crow + 64) = make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
+        *reinterpret_cast<float4*>(crow) = make_float4(acc2[i][0].x, acc2[i][0].y, acc2[i][1].x, acc2[i][1].y);
+        *reinterpret_cast<float4*>(crow + 64) = make_float4(acc2[i][2].x, acc2[i][2].y, acc2[i][3].x, acc2[i][3].y);
     }
 }
 
