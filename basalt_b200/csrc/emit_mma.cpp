@@ -55,6 +55,11 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
     // finishes last; see kernels/sgemm.cu for the same scheme in CUDA).
     const bool tail = s.affine && s.pure_kernel && s.sole_mma && s.extra_params && s.a_c0 == 0 && s.a_cx == 0 && s.a_cy == 128 * lda * 4 && s.b_c0 == 0 &&
                       s.b_cy == 0 && s.b_cx == 512 && s.d_c0 == 0 && s.d_cx == 512 && s.d_cy == 128 * ldd * 4 && in.k < (1u << 30);
+    // In the tail-wave form nothing else in the kernel depends on the CTA's size, so the tile is computed by 128 threads
+    // that own 16 x 8 outputs each (four groups of four rows, 32 apart) instead of 256 threads with 8 x 8: six 16-byte
+    // fragment loads per 64 packed FMAs instead of eight, which is what the shared-memory pipe was short of.
+    const bool wide = tail;
+    const int NT = wide ? 128 : 256, RG = wide ? 4 : 2, SP = 128 / RG;   // threads, row groups per thread, rows between groups
     char nm[64];
     auto R = [&](const char* stem, int i = -1) {
         if (i < 0) snprintf(nm, sizeof nm, "%%mm%d_%s", u, stem);
@@ -62,11 +67,11 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
         return std::string(nm);
     };
     char d[256];
-    snprintf(d, sizeof d, "\t.reg .f32 %%mm%d_fa<8>, %%mm%d_st<16>;", u, u);
+    snprintf(d, sizeof d, "\t.reg .f32 %%mm%d_fa<%d>, %%mm%d_st<%d>;", u, 4 * RG, u, 8 * RG);
     decls->push_back(d);
     // accumulators as packed pairs (columns 2p, 2p+1 of the thread's row i in acc2[4i+p]), the eight A values of a
     // K step duplicated into both halves of a 64-bit register, the eight B values as four pairs
-    snprintf(d, sizeof d, "\t.reg .b64 %%mm%d_acc2_<32>, %%mm%d_ad<8>, %%mm%d_bp<4>;", u, u, u);
+    snprintf(d, sizeof d, "\t.reg .b64 %%mm%d_acc2_<%d>, %%mm%d_ad<%d>, %%mm%d_bp<4>;", u, 16 * RG, u, 4 * RG, u);
     decls->push_back(d);
     snprintf(d, sizeof d, "\t.reg .b32 %%mm%d_asq<4>, %%mm%d_xq<4>;", u, u);
     decls->push_back(d);
@@ -111,7 +116,7 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
 
     o("// mma f32 128x128x%u: register-tiled FFMA, lda=%lld ldb=%lld ldd=%lld", in.k, lda, ldb, ldd);
     o("mov.u32 %s, %%ntid.x;", t.c_str());
-    o("setp.ne.u32 %s, %s, 256;", bad.c_str(), t.c_str());
+    o("setp.ne.u32 %s, %s, %d;", bad.c_str(), t.c_str(), NT);
     o("@%s bra %s;", bad.c_str(), l_skip.c_str());   // wrong block size: leave the output untouched rather than misbehave
     o("mov.u32 %s, %%tid.x;", tid.c_str());
     o("and.b32 %s, %s, 15;", tx.c_str(), tid.c_str());
@@ -162,12 +167,10 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
     o("add.u64 %s, %s, %s;", ag.c_str(), abase.c_str(), w.c_str());
     o("mul.wide.u32 %s, %s, 4;", w.c_str(), acol.c_str());
     o("add.u64 %s, %s, %s;", ag.c_str(), ag.c_str(), w.c_str());
-    o("add.u64 %s, %s, %lld;", ag2.c_str(), ag.c_str(), 64 * lda * 4);
     o("mul.wide.u32 %s, %s, %lld;", w.c_str(), brow.c_str(), ldb * 4);
     o("add.u64 %s, %s, %s;", bg.c_str(), bbase.c_str(), w.c_str());
     o("mul.wide.u32 %s, %s, 4;", w.c_str(), bcol.c_str());
     o("add.u64 %s, %s, %s;", bg.c_str(), bg.c_str(), w.c_str());
-    o("add.u64 %s, %s, %lld;", bg2.c_str(), bg.c_str(), 8 * ldb * 4);
     o("mov.u64 %s, __mm%d_as;", w.c_str(), u);
     o("cvt.u32.u64 %s, %s;", as.c_str(), w.c_str());
     o("mov.u64 %s, __mm%d_bs;", w.c_str(), u);
@@ -189,22 +192,24 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
         o("add.u32 %s, %s, %s;", R("asq", q).c_str(), as.c_str(), x.c_str());
     }
     o("mad.lo.u32 %s, %s, 16, %s;", bsrd.c_str(), tx.c_str(), bs.c_str());
-    for (int i = 0; i < 32; i++) o("mov.b64 %s, 0;", acc2(i).c_str());
+    for (int i = 0; i < 16 * RG; i++) o("mov.b64 %s, 0;", acc2(i).c_str());
     auto fetch = [&](const char* pred) {
-        o("%sld.global.v4.f32 {%s, %s, %s, %s}, [%s];", pred, st(0).c_str(), st(1).c_str(), st(2).c_str(), st(3).c_str(), ag.c_str());
-        o("%sld.global.v4.f32 {%s, %s, %s, %s}, [%s];", pred, st(4).c_str(), st(5).c_str(), st(6).c_str(), st(7).c_str(), ag2.c_str());
-        o("%sld.global.v4.f32 {%s, %s, %s, %s}, [%s];", pred, st(8).c_str(), st(9).c_str(), st(10).c_str(), st(11).c_str(), bg.c_str());
-        o("%sld.global.v4.f32 {%s, %s, %s, %s}, [%s];", pred, st(12).c_str(), st(13).c_str(), st(14).c_str(), st(15).c_str(), bg2.c_str());
+        // rows arow + SP*h of the A slab and rows brow + (NT/32)*h of the B slab, one 16-byte load each
+        for (int h = 0; h < RG; h++)
+            o("%sld.global.v4.f32 {%s, %s, %s, %s}, [%s+%lld];", pred, st(4 * h).c_str(), st(4 * h + 1).c_str(), st(4 * h + 2).c_str(), st(4 * h + 3).c_str(), ag.c_str(),
+              (long long)h * SP * lda * 4);
+        for (int h = 0; h < RG; h++)
+            o("%sld.global.v4.f32 {%s, %s, %s, %s}, [%s+%lld];", pred, st(4 * RG + 4 * h).c_str(), st(4 * RG + 4 * h + 1).c_str(), st(4 * RG + 4 * h + 2).c_str(),
+              st(4 * RG + 4 * h + 3).c_str(), bg.c_str(), (long long)h * (NT / 32) * ldb * 4);
     };
     auto stash = [&]() {   // into the buffer at byte offset `off`
         o("add.u32 %s, %s, %s;", x.c_str(), asst.c_str(), off.c_str());
-        for (int c = 0; c < 4; c++) {
-            o("st.shared.f32 [%s+%d], %s;", x.c_str(), c * 512, st(c).c_str());
-            o("st.shared.f32 [%s+%d], %s;", x.c_str(), c * 512 + 256, st(4 + c).c_str());
-        }
+        for (int c = 0; c < 4; c++)
+            for (int h = 0; h < RG; h++) o("st.shared.f32 [%s+%d], %s;", x.c_str(), c * 512 + h * SP * 4, st(4 * h + c).c_str());
         o("add.u32 %s, %s, %s;", y.c_str(), bsst.c_str(), off.c_str());
-        o("st.shared.v4.f32 [%s], {%s, %s, %s, %s};", y.c_str(), st(8).c_str(), st(9).c_str(), st(10).c_str(), st(11).c_str());
-        o("st.shared.v4.f32 [%s+4096], {%s, %s, %s, %s};", y.c_str(), st(12).c_str(), st(13).c_str(), st(14).c_str(), st(15).c_str());
+        for (int h = 0; h < RG; h++)
+            o("st.shared.v4.f32 [%s+%d], {%s, %s, %s, %s};", y.c_str(), h * (NT / 32) * 512, st(4 * RG + 4 * h).c_str(), st(4 * RG + 4 * h + 1).c_str(),
+              st(4 * RG + 4 * h + 2).c_str(), st(4 * RG + 4 * h + 3).c_str());
     };
     o("mov.u32 %s, 0;", off.c_str());
     o("mov.u32 %s, 0;", kb.c_str());
@@ -216,21 +221,20 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
     if (tail) o("setp.lt.u32 %s, %s, %s;", more.c_str(), kb1.c_str(), R("nk").c_str());
     else o("setp.lt.u32 %s, %s, %d;", more.c_str(), kb1.c_str(), nk);
     o("add.u64 %s, %s, 64;", ag.c_str(), ag.c_str());
-    o("add.u64 %s, %s, 64;", ag2.c_str(), ag2.c_str());
     o("add.u64 %s, %s, %lld;", bg.c_str(), bg.c_str(), 16 * ldb * 4);
-    o("add.u64 %s, %s, %lld;", bg2.c_str(), bg2.c_str(), 16 * ldb * 4);
     fetch(("@" + more + " ").c_str());
     for (int q = 0; q < 4; q++) o("add.u32 %s, %s, %s;", R("xq", q).c_str(), R("asq", q).c_str(), off.c_str());
     o("add.u32 %s, %s, %s;", y.c_str(), bsrd.c_str(), off.c_str());
     // Packed FP32: fma.rn.f32x2 does two IEEE fused multiply-adds per instruction (the same bits as two
     // fma.rn.f32), so a K step is 32 FMA instructions plus 8 register pairings instead of 64 FMAs.
     for (int k = 0; k < 16; k++) {
-        o("ld.shared.v4.f32 {%s, %s, %s, %s}, [%s+%d];", fa(0).c_str(), fa(1).c_str(), fa(2).c_str(), fa(3).c_str(), R("xq", k >> 2).c_str(), k * 512);
-        o("ld.shared.v4.f32 {%s, %s, %s, %s}, [%s+%d];", fa(4).c_str(), fa(5).c_str(), fa(6).c_str(), fa(7).c_str(), R("xq", k >> 2).c_str(), k * 512 + 256);
+        for (int g = 0; g < RG; g++)
+            o("ld.shared.v4.f32 {%s, %s, %s, %s}, [%s+%d];", fa(4 * g).c_str(), fa(4 * g + 1).c_str(), fa(4 * g + 2).c_str(), fa(4 * g + 3).c_str(), R("xq", k >> 2).c_str(),
+              k * 512 + g * SP * 4);
         o("ld.shared.v2.b64 {%s, %s}, [%s+%d];", bp(0).c_str(), bp(1).c_str(), y.c_str(), k * 512);
         o("ld.shared.v2.b64 {%s, %s}, [%s+%d];", bp(2).c_str(), bp(3).c_str(), y.c_str(), k * 512 + 256);
-        for (int i = 0; i < 8; i++) o("mov.b64 %s, {%s, %s};", ad(i).c_str(), fa(i).c_str(), fa(i).c_str());
-        for (int i = 0; i < 8; i++)
+        for (int i = 0; i < 4 * RG; i++) o("mov.b64 %s, {%s, %s};", ad(i).c_str(), fa(i).c_str(), fa(i).c_str());
+        for (int i = 0; i < 4 * RG; i++)
             for (int q = 0; q < 4; q++) o("fma.rn.f32x2 %s, %s, %s, %s;", acc2(i * 4 + q).c_str(), ad(i).c_str(), bp(q).c_str(), acc2(i * 4 + q).c_str());
     }
     o("@!%s bra %s;", more.c_str(), l_done.c_str());
@@ -261,8 +265,8 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
         o("add.u64 %s, %s, %s;", ws.c_str(), ws.c_str(), w.c_str());       // + this thread's position inside a part
         o("mul.wide.u32 %s, %s, 65536;", w.c_str(), part.c_str());
         o("add.u64 %s, %s, %s;", pp.c_str(), ws.c_str(), w.c_str());
-        for (int i = 0; i < 8; i++) {
-            int off = ((i & 3) + (i >> 2) * 64) * 512;
+        for (int i = 0; i < 4 * RG; i++) {
+            int off = ((i & 3) + (i >> 2) * SP) * 512;
             o("st.global.v2.b64 [%s+%d], {%s, %s};", pp.c_str(), off, acc2(i * 4).c_str(), acc2(i * 4 + 1).c_str());
             o("st.global.v2.b64 [%s+%d], {%s, %s};", pp.c_str(), off + 256, acc2(i * 4 + 2).c_str(), acc2(i * 4 + 3).c_str());
         }
@@ -280,12 +284,12 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
         o("@%s bra %s;", notlast.c_str(), l_skip.c_str());                  // another part finishes this tile
         o("membar.gl;");
         // the last part to arrive adds every part in index order, so the bits do not depend on who was last
-        for (int i = 0; i < 32; i++) o("mov.b64 %s, 0;", acc2(i).c_str());
+        for (int i = 0; i < 16 * RG; i++) o("mov.b64 %s, 0;", acc2(i).c_str());
         o("mov.u32 %s, 0;", pv.c_str());
         o("mov.u64 %s, %s;", pp.c_str(), ws.c_str());
         o.label(l_sum);
-        for (int i = 0; i < 8; i++) {
-            int off = ((i & 3) + (i >> 2) * 64) * 512;
+        for (int i = 0; i < 4 * RG; i++) {
+            int off = ((i & 3) + (i >> 2) * SP) * 512;
             o("ld.global.cg.v2.b64 {%s, %s}, [%s+%d];", bp(0).c_str(), bp(1).c_str(), pp.c_str(), off);
             o("ld.global.cg.v2.b64 {%s, %s}, [%s+%d];", bp(2).c_str(), bp(3).c_str(), pp.c_str(), off + 256);
             for (int j = 0; j < 4; j++) o("add.rn.f32x2 %s, %s, %s;", acc2(i * 4 + j).c_str(), acc2(i * 4 + j).c_str(), bp(j).c_str());
@@ -303,15 +307,16 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
     o("add.u64 %s, %s, %s;", cp.c_str(), dbase.c_str(), w.c_str());
     o("mul.wide.u32 %s, %s, 16;", w.c_str(), tx.c_str());
     o("add.u64 %s, %s, %s;", cp.c_str(), cp.c_str(), w.c_str());
-    for (int i = 0; i < 8; i++) {
-        long long rowoff = ((i & 3) + (i >> 2) * 64) * ldd * 4;
+    for (int i = 0; i < 4 * RG; i++) {
+        long long rowoff = ((i & 3) + (i >> 2) * SP) * ldd * 4;
         o("st.global.v2.b64 [%s+%lld], {%s, %s};", cp.c_str(), rowoff, acc2(i * 4).c_str(), acc2(i * 4 + 1).c_str());
         o("st.global.v2.b64 [%s+%lld], {%s, %s};", cp.c_str(), rowoff + 256, acc2(i * 4 + 2).c_str(), acc2(i * 4 + 3).c_str());
     }
     o.label(l_skip);
     o("bar.sync 0;");
     char pl[256];
-    if (tail) snprintf(pl, sizeof pl, "//!basalt.plan %s block=256,1,1 params=%u tail=%u", s.kernel.c_str(), s.nparams, in.k);
+    if (wide && s.maxntid) *s.maxntid = (unsigned)NT;
+    if (tail) snprintf(pl, sizeof pl, "//!basalt.plan %s logical_block=256,1,1 block=%d,1,1 params=%u tail=%u", s.kernel.c_str(), NT, s.nparams, in.k);
     else snprintf(pl, sizeof pl, "//!basalt.plan %s block=256,1,1 params=%u", s.kernel.c_str(), s.nparams);
     plan->push_back(pl);
     return true;

@@ -493,8 +493,9 @@ int basalt_rt_launch(basalt_rt_function* fn, const uint32_t grid[3], const uint3
         // then the tiles of a sparse last wave split along K so that their parts fill one wave.
         const Plan& p = fn->plan;
         basalt_rt_ctx* ctx = fn->mod->ctx;
-        if (block[0] != p.block[0] || block[1] != p.block[1] || block[2] != p.block[2])
-            return set_err(4, 0, "cuLaunchKernel", "kernel was compiled for block (" + std::to_string(p.block[0]) + "," + std::to_string(p.block[1]) + "," + std::to_string(p.block[2]) + ")");
+        const unsigned* want = p.logical_block[0] ? p.logical_block : p.block;
+        if (block[0] != want[0] || block[1] != want[1] || block[2] != want[2])
+            return set_err(4, 0, "cuLaunchKernel", "kernel was compiled for block (" + std::to_string(want[0]) + "," + std::to_string(want[1]) + "," + std::to_string(want[2]) + ")");
         if (grid[2] != 1) return set_err(4, 0, "cuLaunchKernel", "kernel was compiled for a two-dimensional grid");
         if (!params) return set_err(4, 0, "cuLaunchKernel", "kernel takes parameters");
         uint32_t lgx = grid[0], lgy = grid[1];

@@ -143,7 +143,7 @@ class PushGather:
     Every rank owns rows [row0, row0 + rows) of a result every rank wants whole.  The shard is
     computed in `bands` row bands, band k by `launch_band(k, stream)` on one of two compute streams;
     as soon as band k is done, the copy engines push its rows into every peer's result buffer (one
-    cuMemcpyDtoDAsync per peer on a copy stream) while band k + 1 computes.  `finish` orders the
+    cuMemcpyDtoDAsync per peer, each peer on its own copy stream) while band k + 1 computes.  `finish` orders the
     caller's stream after the last push and runs the peer exchange as a barrier: when it returns in
     stream order, every peer's pushes into this rank's buffer have landed (a peer's exchange word is
     sent in stream order after that peer's copies).  An allgather does compute, then communication;
@@ -155,13 +155,15 @@ class PushGather:
         self.ctx, self.group, self.peers, self.ptrs = ctx, group, peers, result_ptrs
         self.row_bytes, self.row0, self.rows, self.bands = row_bytes, row0, rows, bands
         self.compute = [ctx.create_stream(), ctx.create_stream()]
-        self.copy = ctx.create_stream()
+        # one copy stream per peer: the pushes to different peers run on different copy engines and links at once
+        self.copies = [ctx.create_stream() for _ in range(max(1, group.world - 1))]
         self.band_done = [ctx.create_event() for _ in range(bands)]
+        self.pushed = [ctx.create_event() for _ in self.copies]
         self.start, self.copied = ctx.create_event(), ctx.create_event()
         self.flag = ctx.upload(np.zeros(2, np.int32))
 
     def run(self, launch_band, stream=None):
-        ctx, me = self.ctx, self.group.rank
+        ctx, me, world = self.ctx, self.group.rank, self.group.world
         ctx.record(self.start, stream)                          # the inputs are ready in the caller's stream order
         band_rows = self.rows // self.bands
         for k in range(self.bands):
@@ -170,19 +172,25 @@ class PushGather:
                 ctx.stream_wait_event(cs, self.start)
             launch_band(k, cs)
             ctx.record(self.band_done[k], cs)
-            ctx.stream_wait_event(self.copy, self.band_done[k])
             off = (self.row0 + k * band_rows) * self.row_bytes
-            for step in range(1, self.group.world):              # start with the next rank, so the peers are not all written at once
-                r = (me + step) % self.group.world
-                ctx.copy_device_async(self.ptrs[r] + off, self.ptrs[me] + off, band_rows * self.row_bytes, self.copy)
+            for step in range(1, world):                         # stream `step - 1` serves the rank `step` places after this one
+                r = (me + step) % world
+                ctx.stream_wait_event(self.copies[step - 1], self.band_done[k])
+                ctx.copy_device_async(self.ptrs[r] + off, self.ptrs[me] + off, band_rows * self.row_bytes, self.copies[step - 1])
+        last = self.copies[0]
+        if world == 1:
+            ctx.stream_wait_event(last, self.band_done[self.bands - 1])
+        for i in range(1, len(self.copies)):                     # gather the copy streams on the first one
+            ctx.record(self.pushed[i], self.copies[i])
+            ctx.stream_wait_event(last, self.pushed[i])
         if self.peers is not None:                               # barrier: every peer's pushes precede its word
-            self.peers.allreduce_max_i32(self.flag.device_ptr(), self.flag.device_ptr() + 4, self.copy)
-        ctx.record(self.copied, self.copy)
+            self.peers.allreduce_max_i32(self.flag.device_ptr(), self.flag.device_ptr() + 4, last)
+        ctx.record(self.copied, last)
         ctx.stream_wait_event(stream, self.copied)              # the next run's `start` is recorded after this: no band starts early
 
     def close(self):
-        for s in self.compute + [self.copy]:
+        for s in self.compute + self.copies:
             self.ctx.destroy_stream(s)
-        for e in self.band_done + [self.start, self.copied]:
+        for e in self.band_done + self.pushed + [self.start, self.copied]:
             self.ctx.destroy_event(e)
         self.flag.free()
