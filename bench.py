@@ -307,6 +307,13 @@ def others_summary(ctx, torch, stream, peaks_hbm, peaks_tf):
             lambda: fn.launch((N // 128, M // 128), 256, 0, [dp(A), dp(B), dp(C)], stream=stream), fl, seconds=1.5, flop_per_clock_per_sm=256.0)
     except Exception as e:   # noqa: BLE001 - reported, not hidden
         out["sgemm_f32_4096"]["emitted_error"] = str(e)[:200]
+    try:   # comparator only: the vendor library's fp32 (no TF32) GEMM on the same operands
+        was = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = False
+        out["sgemm_f32_4096"]["cublas_fp32_same_operands_tflops"] = fl / timed(lambda: torch.matmul(A, B, out=C), 5) / 1e9
+        torch.backends.cuda.matmul.allow_tf32 = was
+    except Exception as e:   # noqa: BLE001
+        out["sgemm_f32_4096"]["cublas_error"] = str(e)[:200]
     del A, B, C
     # fp16 matmul 8192^3 on tcgen05
     M = N = K = 8192
@@ -329,6 +336,18 @@ def others_summary(ctx, torch, stream, peaks_hbm, peaks_tf):
         out["matmul_f16_8192"]["peaks"] = {"bf16_tflops_burst_best_of_10": peaks_tf, "bf16_tflops_sustained": measured_sustained_tf()}
     except Exception as e:   # noqa: BLE001
         out["matmul_f16_8192"]["emitted_error"] = str(e)[:200]
+    # Comparator only, never on the product path: the vendor library on the SAME operands in the same
+    # regimes (the power a dense matmul draws, and so the clock it settles at, depends on the data).
+    try:
+        lib_mm = lambda: torch.matmul(A, B, out=C)
+        ms_l = timed(lib_mm, 5)
+        out["matmul_f16_8192"]["cublas_f16_same_operands"] = {"tflops": fl / ms_l / 1e9, **best_and_sustained(lib_mm, fl)}
+        Ab, Bb, Cb = A.bfloat16(), B.bfloat16(), torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        lib_bf = lambda: torch.matmul(Ab, Bb, out=Cb)
+        ms_b = timed(lib_bf, 5)
+        out["matmul_f16_8192"]["cublas_bf16_same_values"] = {"tflops": fl / ms_b / 1e9, **best_and_sustained(lib_bf, fl)}
+    except Exception as e:   # noqa: BLE001
+        out["matmul_f16_8192"]["cublas_error"] = str(e)[:200]
     return out
 
 
