@@ -85,11 +85,12 @@ struct FnEmitter {
     std::map<std::pair<int, int64_t>, std::string> cells; // (space, key) -> symbol
     std::vector<uint32_t> uses;
     int label_n = 0, mma_n = 0;
-    unsigned maxntid = 0;
+    unsigned maxntid = 0, cluster = 0;
+    bool pair_twin = false;   // emitting `<name>__pair`: the mma must take the two-SM lowering
     Diag diag;
     bool failed = false;
 
-    FnEmitter(const Module& m, const Function& fn) : mod(m), f(fn) {}
+    FnEmitter(const Module& m, const Function& fn, bool pair = false) : mod(m), f(fn), pair_twin(pair) {}
 
     std::string fresh(Cls c) { return kClsPrefix[c] + std::to_string(counts[c]++); }
     void line(const std::string& s) { body.push_back("\t" + s); }
@@ -707,7 +708,10 @@ struct FnEmitter {
         site.maxntid = &maxntid;
         site.extra_params = &extra_params;
         site.module_decls = &module_decls;
+        site.pair_twin = pair_twin;
+        site.cluster = &cluster;
         if (emit_mma_fast(site, &decls, &body, &plan)) return;
+        if (pair_twin) { fail("E099", "internal: the two-SM twin of " + f.name + " has no lowering"); return; }
 
         const int64_t lda = in.has_ld && in.ld[0] ? in.ld[0] : (in.a_col ? in.m : in.k);
         const int64_t ldb = in.has_ld && in.ld[1] ? in.ld[1] : (in.b_col ? in.k : in.n);
@@ -920,6 +924,7 @@ struct FnEmitter {
             o += ".maxntid " + std::to_string(maxntid ? maxntid : mod.max_threads) + ", 1, 1\n";
             if (mod.min_blocks) o += ".minnctapersm " + std::to_string(maxntid ? 1u : mod.min_blocks) + "\n";
         }
+        if (cluster) o += ".reqnctapercluster " + std::to_string(cluster) + ", 1, 1\n";
         o += "{\n";
         for (int c = 0; c < NCLS; c++)
             if (counts[c]) o += std::string("\t.reg ") + kClsDecl[c] + " " + kClsPrefix[c] + "<" + std::to_string(counts[c]) + ">;\n";
@@ -968,6 +973,22 @@ bool emit_ptx(const Module& in, const EmitOptions& opts, EmitResult* out, Diag* 
         for (auto& md : fe.module_decls)
             if (std::find(module_decls.begin(), module_decls.end(), md) == module_decls.end()) module_decls.push_back(md);
         bodies += fn_text + "\n";
+        // A plan that names a `pair=` entry asks for the same function once more, lowered for pairs of SMs.
+        for (auto& p : fe.plan) {
+            size_t at = p.find(" pair=");
+            if (at == std::string::npos) continue;
+            Function twin = f;
+            twin.name = p.substr(at + 6, p.find(' ', at + 6) == std::string::npos ? std::string::npos : p.find(' ', at + 6) - (at + 6));
+            FnEmitter fe2(m, twin, true);
+            std::string twin_text;
+            if (!fe2.run(&twin_text)) {
+                if (d) *d = fe2.diag;
+                return false;
+            }
+            for (auto& md : fe2.module_decls)
+                if (std::find(module_decls.begin(), module_decls.end(), md) == module_decls.end()) module_decls.push_back(md);
+            bodies += twin_text + "\n";
+        }
     }
     text += "\n";
     for (auto& md : module_decls) text += md + "\n";

@@ -49,6 +49,8 @@ struct MmaSite {
     unsigned* maxntid;            // the entry's .maxntid, which a lowering may raise
     std::vector<std::string>* extra_params;   // receives .param declarations appended to the entry
     std::vector<std::string>* module_decls;   // receives module-scope declarations
+    bool pair_twin = false;       // this is the `<name>__pair` twin of an entry: take the two-SM (cta_group::2) lowering or fail
+    unsigned* cluster = nullptr;  // the entry's .reqnctapercluster x extent, which a lowering may set
 };
 bool emit_mma_fast(const MmaSite& site, std::vector<std::string>* decls, std::vector<std::string>* lines,
                    std::vector<std::string>* plan);

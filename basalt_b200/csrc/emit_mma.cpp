@@ -19,6 +19,7 @@
 //    launch runtime appends (the `//!basalt.plan` line says how to build them).  Every mbarrier
 //    wait is bounded by %globaltimer; a wait that gives up sets the kernel's status word, the
 //    kernel stops issuing copies, still frees its TMEM and returns.
+#include <algorithm>
 #include <cstdarg>
 #include <cstdio>
 
@@ -820,19 +821,21 @@ bool matmul_tcgen05_persistent(const MmaSite& s, std::vector<std::string>* decls
     o("tcgen05.fence::after_thread_sync;");
     o("mad.lo.u32 %s, %s, %d, %s;", r("adst").c_str(), r("s").c_str(), STAGE_BYTES, r("tiles").c_str());
     o("add.u32 %s, %s, 16384;", r("bdst").c_str(), r("adst").c_str());
+    // One descriptor pair per slab, stepped by constant adds: the one issuing thread has about 500 clocks
+    // per slab, and a dependent chain of shifts, masks and ors per MMA is a large part of that.
+    o("shr.u32 %s, %s, 4;", r("x").c_str(), r("adst").c_str());      // stage addresses are 1 KB aligned and below 256 KB: no masking needed
+    o("cvt.u64.u32 %s, %s;", r("da").c_str(), r("x").c_str());
+    o("or.b64 %s, %s, 0x%llX;", r("da").c_str(), r("da").c_str(), desc_a_hi);
+    o("shr.u32 %s, %s, 4;", r("x").c_str(), r("bdst").c_str());
+    o("cvt.u64.u32 %s, %s;", r("db").c_str(), r("x").c_str());
+    o("or.b64 %s, %s, 0x%llX;", r("db").c_str(), r("db").c_str(), desc_b_hi);
+    o("setp.ne.u32 %s, %s, 0;", r("accp").c_str(), r("kb").c_str());   // the tile's first MMA overwrites the accumulator
     for (int k = 0; k < 4; k++) {
-        o("add.u32 %s, %s, %d;", r("x").c_str(), r("adst").c_str(), k * 32);
-        o("shr.u32 %s, %s, 4;", r("x").c_str(), r("x").c_str());
-        o("and.b32 %s, %s, 0x3FFF;", r("x").c_str(), r("x").c_str());
-        o("cvt.u64.u32 %s, %s;", r("da").c_str(), r("x").c_str());
-        o("or.b64 %s, %s, 0x%llX;", r("da").c_str(), r("da").c_str(), desc_a_hi);
-        o("add.u32 %s, %s, %d;", r("x").c_str(), r("bdst").c_str(), b_nk ? k * 32 : k * 2048);
-        o("shr.u32 %s, %s, 4;", r("x").c_str(), r("x").c_str());
-        o("and.b32 %s, %s, 0x3FFF;", r("x").c_str(), r("x").c_str());
-        o("cvt.u64.u32 %s, %s;", r("db").c_str(), r("x").c_str());
-        o("or.b64 %s, %s, 0x%llX;", r("db").c_str(), r("db").c_str(), desc_b_hi);
-        if (k == 0) o("setp.ne.u32 %s, %s, 0;", r("accp").c_str(), r("kb").c_str());   // the tile's first MMA overwrites the accumulator
-        else o("setp.ne.u32 %s, %s, 0;", r("accp").c_str(), r("idesc").c_str());
+        if (k) {   // 16 k: 32 bytes along a K-major row; 16 rows of 128 bytes in an MN-major slab
+            o("add.u64 %s, %s, 2;", r("da").c_str(), r("da").c_str());
+            o("add.u64 %s, %s, %d;", r("db").c_str(), r("db").c_str(), b_nk ? 2 : 128);
+        }
+        if (k == 1) o("setp.ne.u32 %s, %s, 0;", r("accp").c_str(), r("idesc").c_str());
         o("tcgen05.mma.cta_group::1.kind::f16 [%s], %s, %s, %s, %s;", r("acc").c_str(), r("da").c_str(), r("db").c_str(), r("idesc").c_str(), r("accp").c_str());
     }
     o("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%s];", r("empty").c_str());
@@ -911,15 +914,369 @@ bool matmul_tcgen05_persistent(const MmaSite& s, std::vector<std::string>* decls
     o.label(L + "skip");
     char pl[640];
     snprintf(pl, sizeof pl,
-             "//!basalt.plan %s logical_block=128,1,1 block=192,1,1 smem=%u params=%u tmap=%d:2:%lld:%lld:64:128:128 tmap=%d:2:%lld:%lld:64:%d:128 status=1 lgrid=2",
-             s.kernel.c_str(), smem, s.nparams, s.a_param, lda, lda * 2, s.b_param, ldb, ldb * 2, b_nk ? 128 : 64);
+             "//!basalt.plan %s logical_block=128,1,1 block=192,1,1 smem=%u params=%u tmap=%d:2:%lld:%lld:64:128:128 tmap=%d:2:%lld:%lld:64:%d:128 status=1 lgrid=2 pair=%s__pair",
+             s.kernel.c_str(), smem, s.nparams, s.a_param, lda, lda * 2, s.b_param, ldb, ldb * 2, b_nk ? 128 : 64, s.kernel.c_str());
     plan->push_back(pl);
+    return true;
+}
+
+
+// The same kernel as matmul_tcgen05_persistent, lowered for PAIRS of SMs (`<name>__pair`, launched by the
+// runtime instead of `<name>` when the logical grid is even in x and y, i.e. M and N are multiples of
+// 256).  A cluster of two CTAs owns one 256x256 tile: CTA r loads its 128 rows of A and its 128 columns of
+// B (32 KB per K slab per SM instead of 48 KB, so six stages fit), both producers signal the leader's
+// "full" barrier (a cta_group::2 bulk-tensor load names the barrier by its shared::cluster address; no
+// multicast), the leader's warp 1 issues tcgen05.mma.cta_group::2 M256 N256 K16 for both, its commits
+// (multicast to both CTAs' barriers) release the stage and publish the accumulator, the epilogue warps
+// of both CTAs drain their own 128 TMEM lanes and arrive on the leader's "accumulator empty" barrier,
+// and the pair meets at a cluster barrier before tensor memory is released.  Parameters, tensor maps and
+// shared-memory size are those of the one-SM form, so the runtime launches either with one argument list.
+bool matmul_tcgen05_pair(const MmaSite& s, std::vector<std::string>* decls, std::vector<std::string>* lines, std::vector<std::string>* plan) {
+    const Inst& in = *s.inst;
+    if (in.in_dt != Scalar::F16 || in.acc_dt != Scalar::F32 || in.out_dt != Scalar::F16 || in.a_col) return false;
+    if (in.m != 128 || in.n != 128 || in.k % 64 != 0 || !s.c_is_null || !in.has_ld || !s.sole_mma || !s.pure_kernel || !s.affine) return false;
+    if (s.sa != Space::Global || s.sb != Space::Global || s.sd != Space::Global || s.max_threads != 128) return false;
+    if (!s.extra_params || !s.module_decls || !s.maxntid || !s.cluster) return false;
+    const bool b_nk = in.b_col;
+    const long long lda = in.ld[0] ? in.ld[0] : in.k, ldb = in.ld[1] ? in.ld[1] : (b_nk ? in.k : in.n), ldd = in.ld[3] ? in.ld[3] : in.n;
+    if (lda % 8 || ldb % 8 || ldd % 8) return false;
+    if (s.a_c0 || s.a_cx || s.a_cy != 128 * lda * 2) return false;
+    if (s.b_c0 || s.b_cy || s.b_cx != (b_nk ? 128 * ldb * 2 : 256)) return false;
+    if (s.d_c0 || s.d_cx != 256 || s.d_cy != 128 * ldd * 2) return false;
+    const int u = s.uid, num_kb = (int)(in.k / 64), STAGES = 6, STAGE_BYTES = 32768;
+    const int FULL = 0, EMPTY = 8 * STAGES, TFULL = 16 * STAGES, TEMPTY = 16 * STAGES + 16;
+    const std::string P = "%mq" + std::to_string(u) + "_", L = "$mq" + std::to_string(u) + "_";
+    auto r = [&](const char* n) { return P + n; };
+    std::string b32 = "\t.reg .b32 ";
+    for (const char* n : {"tid", "warp", "lane", "t", "u", "tiles", "bars", "slot", "gu", "tmem", "ok", "kb", "s", "ph", "par", "full", "empty", "fb", "adst", "bdst", "m0", "n0",
+                          "x", "it", "g", "lgx", "lgy", "tm", "tn", "ntiles", "perband", "band", "first", "rows", "rr", "mi", "nj", "tile", "gstep", "local",
+                          "buf", "use", "bar2", "acc", "ew", "c", "src", "spin", "rank", "zero", "idesc"})
+        b32 += P + n + ", ";
+    b32 += P + "h<16>, " + P + "v<32>;";
+    decls->push_back(b32);
+    std::string b64 = "\t.reg .b64 ";
+    for (const char* n : {"w", "da", "db", "t0", "now", "dt", "crow", "status", "ma", "mb"}) b64 += P + n + ", ";
+    b64 += P + "z;";
+    decls->push_back(b64);
+    decls->push_back("\t.reg .b16 " + P + "both;");
+    std::string pr = "\t.reg .pred ";
+    for (const char* n : {"p", "q", "w0", "w1", "l0", "prod", "mma", "epi", "accp", "done", "all", "lead"}) pr += P + n + ", ";
+    pr += P + "unused;";
+    decls->push_back(pr);
+    char d[256];
+    snprintf(d, sizeof d, "\t.shared .align 8 .b8 __mq%d_bars[%d];", u, TEMPTY + 16);   // full[6], empty[6], tfull[2], tempty[2]
+    decls->push_back(d);
+    snprintf(d, sizeof d, "\t.shared .align 4 .b8 __mq%d_misc[8];", u);
+    decls->push_back(d);
+    const std::string dyn = ".extern .shared .align 1024 .b8 __basalt_dyn_smem[];";
+    if (std::find(s.module_decls->begin(), s.module_decls->end(), dyn) == s.module_decls->end()) s.module_decls->push_back(dyn);
+    const std::string ta = s.kernel + "_tmap_a", tb = s.kernel + "_tmap_b", stp = s.kernel + "_status", pgx = s.kernel + "_lgrid_x", pgy = s.kernel + "_lgrid_y";
+    s.extra_params->push_back(".param .align 64 .b8 " + ta + "[128]");
+    s.extra_params->push_back(".param .align 64 .b8 " + tb + "[128]");
+    s.extra_params->push_back(".param .u64 " + stp);
+    s.extra_params->push_back(".param .u32 " + pgx);
+    s.extra_params->push_back(".param .u32 " + pgy);
+    *s.maxntid = 192;
+    *s.cluster = 2;
+    Out o{lines};
+    int wait_n = 0;
+    // Bounded wait on a barrier of this CTA: 200 ms on %globaltimer, then the CTA-wide give-up flag.
+    auto wait = [&](const std::string& bar, const std::string& par, const std::string& fail) {
+        std::string base = L + "w" + std::to_string(wait_n++);
+        o("mov.u64 %s, 0;", r("t0").c_str());
+        o("mov.u32 %s, 0;", r("spin").c_str());
+        o.label(base + "_loop");
+        o("mbarrier.try_wait.parity.shared::cta.b64 %s, [%s], %s;", r("done").c_str(), bar.c_str(), par.c_str());
+        o("@%s bra %s_done;", r("done").c_str(), base.c_str());
+        o("ld.volatile.shared.u32 %s, [%s];", r("g").c_str(), r("gu").c_str());
+        o("setp.ne.u32 %s, %s, 0;", r("q").c_str(), r("g").c_str());
+        o("@%s bra %s_fail;", r("q").c_str(), base.c_str());
+        o("add.u32 %s, %s, 1;", r("spin").c_str(), r("spin").c_str());
+        o("and.b32 %s, %s, 63;", r("g").c_str(), r("spin").c_str());
+        o("setp.ne.u32 %s, %s, 0;", r("q").c_str(), r("g").c_str());
+        o("@%s bra %s_loop;", r("q").c_str(), base.c_str());
+        o("mov.u64 %s, %%globaltimer;", r("now").c_str());
+        o("setp.ne.u64 %s, %s, 0;", r("q").c_str(), r("t0").c_str());
+        o("@%s bra %s_t;", r("q").c_str(), base.c_str());
+        o("mov.u64 %s, %s;", r("t0").c_str(), r("now").c_str());
+        o("bra %s_loop;", base.c_str());
+        o.label(base + "_t");
+        o("sub.u64 %s, %s, %s;", r("dt").c_str(), r("now").c_str(), r("t0").c_str());
+        o("setp.lt.u64 %s, %s, 200000000;", r("q").c_str(), r("dt").c_str());
+        o("@%s bra %s_loop;", r("q").c_str(), base.c_str());
+        o("st.volatile.shared.u32 [%s], 1;", r("gu").c_str());
+        o.label(base + "_fail");
+        o("mov.u32 %s, 0;", r("ok").c_str());
+        o("bra %s;", fail.c_str());
+        o.label(base + "_done");
+    };
+    // tile -> (mi, nj): bands of 8 tile rows, row-fastest inside a band
+    auto coords = [&]() {
+        o("div.u32 %s, %s, %s;", r("band").c_str(), r("tile").c_str(), r("perband").c_str());
+        o("shl.b32 %s, %s, 3;", r("first").c_str(), r("band").c_str());
+        o("sub.u32 %s, %s, %s;", r("rows").c_str(), r("tm").c_str(), r("first").c_str());
+        o("min.u32 %s, %s, 8;", r("rows").c_str(), r("rows").c_str());
+        o("mul.lo.u32 %s, %s, %s;", r("t").c_str(), r("band").c_str(), r("perband").c_str());
+        o("sub.u32 %s, %s, %s;", r("rr").c_str(), r("tile").c_str(), r("t").c_str());
+        o("rem.u32 %s, %s, %s;", r("mi").c_str(), r("rr").c_str(), r("rows").c_str());
+        o("add.u32 %s, %s, %s;", r("mi").c_str(), r("mi").c_str(), r("first").c_str());
+        o("div.u32 %s, %s, %s;", r("nj").c_str(), r("rr").c_str(), r("rows").c_str());
+        o("shl.b32 %s, %s, 8;", r("m0").c_str(), r("mi").c_str());
+        o("mad.lo.u32 %s, %s, 128, %s;", r("m0").c_str(), r("rank").c_str(), r("m0").c_str());   // this CTA's 128 rows of the tile
+        o("shl.b32 %s, %s, 8;", r("n0").c_str(), r("nj").c_str());
+    };
+    // s and ph are kept as running counters (s = slab count mod STAGES, ph = its wrap parity): the one
+    // thread that issues the MMAs has about 500 clocks per slab, and a dependent chain of divisions,
+    // shifts and ors for every slab and every descriptor was most of that
+    auto stage = [&]() {
+        o("mad.lo.u32 %s, %s, 8, %s;", r("full").c_str(), r("s").c_str(), r("bars").c_str());
+        o("add.u32 %s, %s, %d;", r("empty").c_str(), r("full").c_str(), EMPTY);
+        o("mad.lo.u32 %s, %s, %d, %s;", r("adst").c_str(), r("s").c_str(), STAGE_BYTES, r("tiles").c_str());
+        o("add.u32 %s, %s, 16384;", r("bdst").c_str(), r("adst").c_str());
+    };
+
+    auto next_stage = [&]() {
+        o("add.u32 %s, %s, 1;", r("s").c_str(), r("s").c_str());
+        o("setp.eq.u32 %s, %s, %d;", r("q").c_str(), r("s").c_str(), STAGES);
+        o("@%s mov.u32 %s, 0;", r("q").c_str(), r("s").c_str());
+        o("@%s xor.b32 %s, %s, 1;", r("q").c_str(), r("ph").c_str(), r("ph").c_str());
+    };
+
+    o("// mma f16->f32->f16 128x128x%u over a tiled grid: TMA + tcgen05.cta_group::2, 256x256 tiles on pairs of SMs, %s B", in.k, b_nk ? "K-major" : "MN-major");
+    o("mov.u32 %s, %%ntid.x;", r("t").c_str());
+    o("setp.ne.u32 %s, %s, 192;", r("p").c_str(), r("t").c_str());
+    o("@%s bra %sskip;", r("p").c_str(), L.c_str());
+    o("ld.param.u64 %s, [%s];", r("status").c_str(), stp.c_str());
+    o("ld.param.u32 %s, [%s];", r("lgx").c_str(), pgx.c_str());
+    o("ld.param.u32 %s, [%s];", r("lgy").c_str(), pgy.c_str());
+    o("mov.b64 %s, %s;", r("ma").c_str(), ta.c_str());
+    o("cvta.param.u64 %s, %s;", r("ma").c_str(), r("ma").c_str());
+    o("mov.b64 %s, %s;", r("mb").c_str(), tb.c_str());
+    o("cvta.param.u64 %s, %s;", r("mb").c_str(), r("mb").c_str());
+    o("mov.u32 %s, %%tid.x;", r("tid").c_str());
+    o("shr.u32 %s, %s, 5;", r("warp").c_str(), r("tid").c_str());
+    o("and.b32 %s, %s, 31;", r("lane").c_str(), r("tid").c_str());
+    o("mov.u32 %s, %%cluster_ctarank;", r("rank").c_str());
+    o("setp.eq.u32 %s, %s, 0;", r("lead").c_str(), r("rank").c_str());
+    o("mov.u32 %s, 0;", r("zero").c_str());
+    o("mov.b16 %s, 3;", r("both").c_str());
+    o("mov.u64 %s, __basalt_dyn_smem;", r("w").c_str());
+    o("cvt.u32.u64 %s, %s;", r("tiles").c_str(), r("w").c_str());
+    o("add.u32 %s, %s, 1023;", r("tiles").c_str(), r("tiles").c_str());
+    o("and.b32 %s, %s, 0xFFFFFC00;", r("tiles").c_str(), r("tiles").c_str());
+    o("mov.u64 %s, __mq%d_bars;", r("w").c_str(), u);
+    o("cvt.u32.u64 %s, %s;", r("bars").c_str(), r("w").c_str());
+    o("mov.u64 %s, __mq%d_misc;", r("w").c_str(), u);
+    o("cvt.u32.u64 %s, %s;", r("slot").c_str(), r("w").c_str());
+    o("add.u32 %s, %s, 4;", r("gu").c_str(), r("slot").c_str());
+    o("shr.u32 %s, %s, 1;", r("tn").c_str(), r("lgx").c_str());
+    o("shr.u32 %s, %s, 1;", r("tm").c_str(), r("lgy").c_str());
+    o("mul.lo.u32 %s, %s, %s;", r("ntiles").c_str(), r("tn").c_str(), r("tm").c_str());
+    o("shl.b32 %s, %s, 3;", r("perband").c_str(), r("tn").c_str());
+    o("setp.ne.u32 %s, %s, 0;", r("p").c_str(), r("tid").c_str());
+    o("@%s bra %sinit_done;", r("p").c_str(), L.c_str());
+    o("st.volatile.shared.u32 [%s], 0;", r("gu").c_str());
+    for (int i = 0; i < 2 * STAGES + 2; i++) o("mbarrier.init.shared::cta.b64 [%s+%d], 1;", r("bars").c_str(), 8 * i);   // full, empty, tfull
+    for (int i = 0; i < 2; i++) o("mbarrier.init.shared::cta.b64 [%s+%d], 8;", r("bars").c_str(), TEMPTY + 8 * i);      // four epilogue warps in each CTA
+    o("fence.mbarrier_init.release.cluster;");
+    o("fence.proxy.async.shared::cta;");
+    o.label(L + "init_done");
+    o("setp.eq.u32 %s, %s, 1;", r("w1").c_str(), r("warp").c_str());
+    o("@!%s bra %salloc_done;", r("w1").c_str(), L.c_str());
+    o("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%s], 512;", r("slot").c_str());   // the same warp of both CTAs allocates for the pair
+    o("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;");
+    o.label(L + "alloc_done");
+    o("tcgen05.fence::before_thread_sync;");
+    o("bar.sync 0;");
+    o("barrier.cluster.arrive.release.aligned;");   // the peer's barriers are initialised before anything can signal them
+    o("barrier.cluster.wait.acquire.aligned;");
+    o("tcgen05.fence::after_thread_sync;");
+    o("ld.shared.u32 %s, [%s];", r("tmem").c_str(), r("slot").c_str());
+    o("mov.u32 %s, 1;", r("ok").c_str());
+    o("mov.u32 %s, %%ctaid.x;", r("tile").c_str());
+    o("shr.u32 %s, %s, 1;", r("tile").c_str(), r("tile").c_str());
+    o("mov.u32 %s, %%nctaid.x;", r("gstep").c_str());
+    o("shr.u32 %s, %s, 1;", r("gstep").c_str(), r("gstep").c_str());
+    o("mov.u32 %s, 0;", r("local").c_str());
+    o("mov.u32 %s, 0;", r("s").c_str());
+    o("mov.u32 %s, 0;", r("ph").c_str());
+    o("setp.eq.u32 %s, %s, 0;", r("l0").c_str(), r("lane").c_str());
+    o("setp.eq.u32 %s, %s, 0;", r("w0").c_str(), r("warp").c_str());
+    o("and.pred %s, %s, %s;", r("prod").c_str(), r("w0").c_str(), r("l0").c_str());
+    o("and.pred %s, %s, %s;", r("mma").c_str(), r("w1").c_str(), r("l0").c_str());
+    o("and.pred %s, %s, %s;", r("mma").c_str(), r("mma").c_str(), r("lead").c_str());
+    o("setp.ge.u32 %s, %s, 2;", r("epi").c_str(), r("warp").c_str());
+    o("@%s bra %sp_tile;", r("prod").c_str(), L.c_str());
+    o("@%s bra %sm_tile;", r("mma").c_str(), L.c_str());
+    o("@%s bra %se_tile;", r("epi").c_str(), L.c_str());
+    o("bra %send;", L.c_str());
+
+    // ---- producers (one thread in each CTA) ----
+    o.label(L + "p_tile");
+    o("setp.ge.u32 %s, %s, %s;", r("p").c_str(), r("tile").c_str(), r("ntiles").c_str());
+    o("@%s bra %send;", r("p").c_str(), L.c_str());
+    coords();
+    o("mad.lo.u32 %s, %s, 128, %s;", r("n0").c_str(), r("rank").c_str(), r("n0").c_str());   // this CTA's 128 columns of B
+    o("mov.u32 %s, 0;", r("kb").c_str());
+    o.label(L + "p_kb");
+    stage();
+    o("xor.b32 %s, %s, 1;", r("par").c_str(), r("ph").c_str());
+    wait(r("empty"), r("par"), L + "p_fail");
+    o("mapa.shared::cluster.u32 %s, %s, %s;", r("fb").c_str(), r("full").c_str(), r("zero").c_str());   // the leader's barrier collects both CTAs' bytes
+    o("@%s mbarrier.arrive.expect_tx.shared::cta.b64 _, [%s], %d;", r("lead").c_str(), r("full").c_str(), 2 * STAGE_BYTES);
+    o("shl.b32 %s, %s, 6;", r("x").c_str(), r("kb").c_str());
+    const char* tma = "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes";
+    o("%s [%s], [%s, {%s, %s}], [%s];", tma, r("adst").c_str(), r("ma").c_str(), r("x").c_str(), r("m0").c_str(), r("fb").c_str());
+    if (b_nk) {   // one box of 64 k x 128 n rows
+        o("%s [%s], [%s, {%s, %s}], [%s];", tma, r("bdst").c_str(), r("mb").c_str(), r("x").c_str(), r("n0").c_str(), r("fb").c_str());
+    } else {      // two boxes of 64 n x 64 k rows
+        for (int h = 0; h < 2; h++) {
+            o("add.u32 %s, %s, %d;", r("t").c_str(), r("n0").c_str(), 64 * h);
+            o("add.u32 %s, %s, %d;", r("u").c_str(), r("bdst").c_str(), 8192 * h);
+            o("%s [%s], [%s, {%s, %s}], [%s];", tma, r("u").c_str(), r("mb").c_str(), r("t").c_str(), r("x").c_str(), r("fb").c_str());
+        }
+    }
+    next_stage();
+    o("add.u32 %s, %s, 1;", r("kb").c_str(), r("kb").c_str());
+    o("setp.lt.u32 %s, %s, %d;", r("p").c_str(), r("kb").c_str(), num_kb);
+    o("@%s bra %sp_kb;", r("p").c_str(), L.c_str());
+    o("add.u32 %s, %s, %s;", r("tile").c_str(), r("tile").c_str(), r("gstep").c_str());
+    o("bra %sp_tile;", L.c_str());
+    o.label(L + "p_fail");   // let the copies already issued land (2 ms, bounded) before the CTA can exit
+    o("mov.u64 %s, %%globaltimer;", r("t0").c_str());
+    o.label(L + "p_spin");
+    o("mov.u64 %s, %%globaltimer;", r("now").c_str());
+    o("sub.u64 %s, %s, %s;", r("dt").c_str(), r("now").c_str(), r("t0").c_str());
+    o("setp.lt.u64 %s, %s, 2000000;", r("q").c_str(), r("dt").c_str());
+    o("@%s bra %sp_spin;", r("q").c_str(), L.c_str());
+    o("bra %send;", L.c_str());
+
+    // ---- MMA issuer (one thread of the leader) ----
+    const unsigned idesc = (1u << 4) | ((b_nk ? 0u : 1u) << 16) | (32u << 17) | (16u << 24);   // f32 accumulate, N = 256, M = 256
+    const unsigned long long desc_a_hi = (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+    const unsigned long long desc_b_hi = b_nk ? desc_a_hi : ((512ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61));
+    const char* commit = "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64";
+    o.label(L + "m_tile");
+    o("setp.ge.u32 %s, %s, %s;", r("p").c_str(), r("tile").c_str(), r("ntiles").c_str());
+    o("@%s bra %send;", r("p").c_str(), L.c_str());
+    o("mov.u32 %s, %u;", r("idesc").c_str(), idesc);
+    o("and.b32 %s, %s, 1;", r("buf").c_str(), r("local").c_str());
+    o("shr.u32 %s, %s, 1;", r("use").c_str(), r("local").c_str());
+    o("and.b32 %s, %s, 1;", r("par").c_str(), r("use").c_str());
+    o("xor.b32 %s, %s, 1;", r("par").c_str(), r("par").c_str());
+    o("mad.lo.u32 %s, %s, 8, %s;", r("bar2").c_str(), r("buf").c_str(), r("bars").c_str());
+    o("add.u32 %s, %s, %d;", r("bar2").c_str(), r("bar2").c_str(), TEMPTY);   // both epilogues have drained this accumulator
+    wait(r("bar2"), r("par"), L + "end");
+    o("tcgen05.fence::after_thread_sync;");
+    o("mad.lo.u32 %s, %s, 256, %s;", r("acc").c_str(), r("buf").c_str(), r("tmem").c_str());
+    o("mov.u32 %s, 0;", r("kb").c_str());
+    o.label(L + "m_kb");
+    stage();
+    o("shr.u32 %s, %s, 4;", r("x").c_str(), r("adst").c_str());      // stage addresses are 1 KB aligned and below 256 KB: no masking needed
+    o("cvt.u64.u32 %s, %s;", r("da").c_str(), r("x").c_str());
+    o("or.b64 %s, %s, 0x%llX;", r("da").c_str(), r("da").c_str(), desc_a_hi);
+    o("shr.u32 %s, %s, 4;", r("x").c_str(), r("bdst").c_str());
+    o("cvt.u64.u32 %s, %s;", r("db").c_str(), r("x").c_str());
+    o("or.b64 %s, %s, 0x%llX;", r("db").c_str(), r("db").c_str(), desc_b_hi);
+    o("setp.ne.u32 %s, %s, 0;", r("accp").c_str(), r("kb").c_str());   // the tile's first MMA overwrites the accumulator
+    wait(r("full"), r("ph"), L + "end");   // everything above is ready when the slab lands
+    o("tcgen05.fence::after_thread_sync;");
+    for (int k = 0; k < 4; k++) {
+        if (k) {   // 16 k: 32 bytes along a K-major row; 16 rows of 128 bytes in an MN-major slab
+            o("add.u64 %s, %s, 2;", r("da").c_str(), r("da").c_str());
+            o("add.u64 %s, %s, %d;", r("db").c_str(), r("db").c_str(), b_nk ? 2 : 128);
+        }
+        if (k == 1) o("setp.eq.u32 %s, %s, 0;", r("accp").c_str(), r("zero").c_str());
+        o("tcgen05.mma.cta_group::2.kind::f16 [%s], %s, %s, %s, {%s, %s, %s, %s, %s, %s, %s, %s}, %s;", r("acc").c_str(), r("da").c_str(), r("db").c_str(), r("idesc").c_str(),
+          r("zero").c_str(), r("zero").c_str(), r("zero").c_str(), r("zero").c_str(), r("zero").c_str(), r("zero").c_str(), r("zero").c_str(), r("zero").c_str(), r("accp").c_str());
+    }
+    o("%s [%s], %s;", commit, r("empty").c_str(), r("both").c_str());   // the stage is free in both CTAs once these MMAs have read it
+    next_stage();
+    o("add.u32 %s, %s, 1;", r("kb").c_str(), r("kb").c_str());
+    o("setp.lt.u32 %s, %s, %d;", r("p").c_str(), r("kb").c_str(), num_kb);
+    o("@%s bra %sm_kb;", r("p").c_str(), L.c_str());
+    o("sub.u32 %s, %s, 16;", r("bar2").c_str(), r("bar2").c_str());   // tfull[buf], in both CTAs
+    o("%s [%s], %s;", commit, r("bar2").c_str(), r("both").c_str());
+    o("add.u32 %s, %s, %s;", r("tile").c_str(), r("tile").c_str(), r("gstep").c_str());
+    o("add.u32 %s, %s, 1;", r("local").c_str(), r("local").c_str());
+    o("bra %sm_tile;", L.c_str());
+
+    // ---- epilogue warps (four in each CTA, each CTA drains its own 128 rows) ----
+    o.label(L + "e_tile");
+    o("setp.ge.u32 %s, %s, %s;", r("p").c_str(), r("tile").c_str(), r("ntiles").c_str());
+    o("@%s bra %send;", r("p").c_str(), L.c_str());
+    coords();
+    o("and.b32 %s, %s, 1;", r("buf").c_str(), r("local").c_str());
+    o("shr.u32 %s, %s, 1;", r("use").c_str(), r("local").c_str());
+    o("and.b32 %s, %s, 1;", r("par").c_str(), r("use").c_str());
+    o("mad.lo.u32 %s, %s, 8, %s;", r("bar2").c_str(), r("buf").c_str(), r("bars").c_str());
+    o("add.u32 %s, %s, %d;", r("bar2").c_str(), r("bar2").c_str(), TFULL);
+    wait(r("bar2"), r("par"), L + "e_after");
+    o.label(L + "e_after");
+    o("setp.ne.u32 %s, %s, 0;", r("p").c_str(), r("ok").c_str());
+    o("vote.sync.all.pred %s, %s, 0xffffffff;", r("all").c_str(), r("p").c_str());   // the warp stays together: tcgen05.ld is warp-collective
+    o("@!%s bra %send;", r("all").c_str(), L.c_str());
+    o("tcgen05.fence::after_thread_sync;");
+    o("and.b32 %s, %s, 3;", r("ew").c_str(), r("warp").c_str());   // this warp may touch TMEM lanes 32*ew .. 32*ew+31
+    o("mad.lo.u32 %s, %s, 32, %s;", r("t").c_str(), r("ew").c_str(), r("lane").c_str());
+    o("add.u32 %s, %s, %s;", r("t").c_str(), r("t").c_str(), r("m0").c_str());
+    o("mul.wide.u32 %s, %s, %lld;", r("w").c_str(), r("t").c_str(), ldd * 2);
+    o("add.u64 %s, %s, %s;", r("crow").c_str(), s.d_base.c_str(), r("w").c_str());
+    o("mul.wide.u32 %s, %s, 2;", r("w").c_str(), r("n0").c_str());
+    o("add.u64 %s, %s, %s;", r("crow").c_str(), r("crow").c_str(), r("w").c_str());
+    o("mad.lo.u32 %s, %s, 256, %s;", r("src").c_str(), r("buf").c_str(), r("tmem").c_str());
+    o("shl.b32 %s, %s, 21;", r("t").c_str(), r("ew").c_str());
+    o("add.u32 %s, %s, %s;", r("src").c_str(), r("src").c_str(), r("t").c_str());
+    o("mov.u32 %s, 0;", r("c").c_str());
+    o.label(L + "e_c");
+    {
+        std::string list;
+        for (int i = 0; i < 32; i++) list += (i ? ", " : "") + P + "v" + std::to_string(i);
+        o("add.u32 %s, %s, %s;", r("x").c_str(), r("src").c_str(), r("c").c_str());
+        o("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%s}, [%s];", list.c_str(), r("x").c_str());
+        o("tcgen05.wait::ld.sync.aligned;");
+        for (int i = 0; i < 16; i++) o("cvt.rn.f16x2.f32 %sh%d, %sv%d, %sv%d;", P.c_str(), i, P.c_str(), 2 * i + 1, P.c_str(), 2 * i);
+        o("mul.wide.u32 %s, %s, 2;", r("z").c_str(), r("c").c_str());
+        o("add.u64 %s, %s, %s;", r("z").c_str(), r("z").c_str(), r("crow").c_str());
+        for (int q = 0; q < 4; q++)
+            o("st.global.v4.b32 [%s+%d], {%sh%d, %sh%d, %sh%d, %sh%d};", r("z").c_str(), 16 * q, P.c_str(), 4 * q, P.c_str(), 4 * q + 1, P.c_str(), 4 * q + 2, P.c_str(), 4 * q + 3);
+    }
+    o("add.u32 %s, %s, 32;", r("c").c_str(), r("c").c_str());
+    o("setp.lt.u32 %s, %s, 256;", r("p").c_str(), r("c").c_str());
+    o("@%s bra %se_c;", r("p").c_str(), L.c_str());
+    o("tcgen05.fence::before_thread_sync;");
+    o("bar.warp.sync 0xffffffff;");
+    o("add.u32 %s, %s, %d;", r("bar2").c_str(), r("bar2").c_str(), TEMPTY - TFULL);   // tempty[buf] ...
+    o("mapa.shared::cluster.u32 %s, %s, %s;", r("fb").c_str(), r("bar2").c_str(), r("zero").c_str());      // ... of the leader
+    o("@%s mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%s];", r("l0").c_str(), r("fb").c_str());
+    o("add.u32 %s, %s, %s;", r("tile").c_str(), r("tile").c_str(), r("gstep").c_str());
+    o("add.u32 %s, %s, 1;", r("local").c_str(), r("local").c_str());
+    o("bra %se_tile;", L.c_str());
+
+    o.label(L + "end");
+    o("setp.ne.u32 %s, %s, 0;", r("p").c_str(), r("ok").c_str());
+    o("@%s bra %sstatus_done;", r("p").c_str(), L.c_str());
+    o("mov.u32 %s, 1;", r("t").c_str());
+    o("atom.global.exch.b32 %s, [%s], %s;", r("g").c_str(), r("status").c_str(), r("t").c_str());
+    o.label(L + "status_done");
+    o("bar.warp.sync 0xffffffff;");
+    o("tcgen05.fence::before_thread_sync;");
+    o("bar.sync 0;");
+    o("barrier.cluster.arrive.release.aligned;");   // the peer has stopped naming this CTA's barriers, shared and tensor memory
+    o("barrier.cluster.wait.acquire.aligned;");
+    o("tcgen05.fence::after_thread_sync;");
+    o("@!%s bra %sskip;", r("w1").c_str(), L.c_str());
+    o("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %s, 512;", r("tmem").c_str());
+    o.label(L + "skip");
+    (void)FULL;
+    (void)plan;   // launched through the plan of the one-SM entry, whose `pair=` key names this one
     return true;
 }
 
 }  // namespace
 
 bool emit_mma_fast(const MmaSite& site, std::vector<std::string>* decls, std::vector<std::string>* lines, std::vector<std::string>* plan) {
+    if (site.pair_twin) return matmul_tcgen05_pair(site, decls, lines, plan);
     return sgemm_ffma(site, decls, lines, plan) || matmul_tcgen05_persistent(site, decls, lines, plan) || matmul_tcgen05(site, decls, lines, plan);
 }
 

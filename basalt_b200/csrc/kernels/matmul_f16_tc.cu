@@ -302,12 +302,11 @@ __global__ void __launch_bounds__(THREADS2, 1) matmul_f16_tc_persistent(const __
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t a_src = tiles + s * STAGE_BYTES2, b_src = a_src + A_BYTES;
+                    const uint64_t da = smem_desc(a_src, 16, 1024);   // one descriptor pair per slab, stepped by constant adds
+                    const uint64_t db = B_IS_NK ? smem_desc(b_src, 16, 1024) : smem_desc(b_src, 8192, 1024);
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; k++) {
-                        const uint64_t da = smem_desc(a_src + k * UMMA_K * 2, 16, 1024);
-                        const uint64_t db = B_IS_NK ? smem_desc(b_src + k * UMMA_K * 2, 16, 1024) : smem_desc(b_src + k * UMMA_K * 128, 8192, 1024);
-                        umma_f16(acc, da, db, idesc, (kb | k) != 0);
-                    }
+                    for (int k = 0; k < BK / UMMA_K; k++)
+                        umma_f16(acc, da + (uint64_t)(2 * k), db + (uint64_t)((B_IS_NK ? 2 : 128) * k), idesc, (kb | k) != 0);
                     umma_commit(smem_u32(&empty_bar[s]));
                 }
                 umma_commit(smem_u32(&tfull_bar[buf]));
@@ -468,14 +467,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS3, 1)
 
     if (warp == 0) {
         if (lane == 0) {
-            uint32_t it = 0;
+            uint32_t s = 0, ph = 0;   // stage and its wrap parity, as running counters
             for (int t = pair; t < num_tiles && ok; t += pairs) {
                 int mi, ni;
                 tile_coords(t, tiles_m, tiles_n, &mi, &ni);
                 const int m0 = mi * TM + (int)rank * BM, n0 = ni * TN + (int)rank * HALF_N;
-                for (int kb = 0; kb < num_kb; kb++, it++) {
-                    const uint32_t s = it % STAGES, parity = ((it / STAGES) & 1) ^ 1;
-                    ok &= mbar_wait(smem_u32(&empty_bar[s]), parity, &gave_up);
+                for (int kb = 0; kb < num_kb; kb++) {
+                    ok &= mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, &gave_up);
                     if (!ok) break;
                     const uint32_t fb_local = smem_u32(&full_bar[s]), fb = map_to_cta(fb_local, 0);
                     const uint32_t a_dst = tiles + s * STAGE_BYTES3, b_dst = a_dst + A_BYTES;
@@ -486,6 +484,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS3, 1)
 #pragma unroll
                         for (int h = 0; h < 2; h++) tma_load_2d_pair(b_dst + h * 8192, &map_b, fb, n0 + 64 * h, kb * BK);   // box 64 n x 64 k
                     }
+                    if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
             }
             if (!ok) {   // let the copies already issued land before the CTA can exit
@@ -496,26 +495,28 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS3, 1)
     } else if (warp == 1) {
         if (lane == 0 && leader) {
             const uint32_t idesc = (1u << 4) | ((B_IS_NK ? 0u : 1u) << 16) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(TM >> 4) << 24);
-            uint32_t it = 0, local = 0;
+            // This one thread has about 500 clocks per K slab: the stage index is a running counter and the
+            // descriptors are built once per slab and stepped by constant adds (a 16-k step is 32 bytes along a
+            // K-major row, 16 rows of 128 bytes in an MN-major slab; descriptors count 16-byte units).
+            uint32_t s = 0, ph = 0, local = 0;
             for (int t = pair; t < num_tiles && ok; t += pairs, local++) {
                 const uint32_t buf = local & 1, use = local >> 1;
                 ok &= mbar_wait(smem_u32(&tempty_bar[buf]), (use & 1) ^ 1, &gave_up);   // both epilogues have drained this accumulator
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t acc = tmem_base + buf * TN;
-                for (int kb = 0; kb < num_kb; kb++, it++) {
-                    const uint32_t s = it % STAGES;
-                    ok &= mbar_wait(smem_u32(&full_bar[s]), (it / STAGES) & 1, &gave_up);
+                for (int kb = 0; kb < num_kb; kb++) {
+                    ok &= mbar_wait(smem_u32(&full_bar[s]), ph, &gave_up);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t a_src = tiles + s * STAGE_BYTES3, b_src = a_src + A_BYTES;
+                    const uint64_t da = smem_desc(a_src, 16, 1024);
+                    const uint64_t db = B_IS_NK ? smem_desc(b_src, 16, 1024) : smem_desc(b_src, 8192, 1024);
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; k++) {
-                        const uint64_t da = smem_desc(a_src + k * UMMA_K * 2, 16, 1024);
-                        const uint64_t db = B_IS_NK ? smem_desc(b_src + k * UMMA_K * 2, 16, 1024) : smem_desc(b_src + k * UMMA_K * 128, 8192, 1024);
-                        umma_f16_pair(acc, da, db, idesc, (kb | k) != 0);
-                    }
+                    for (int k = 0; k < BK / UMMA_K; k++)
+                        umma_f16_pair(acc, da + (uint64_t)(2 * k), db + (uint64_t)((B_IS_NK ? 2 : 128) * k), idesc, (kb | k) != 0);
                     umma_commit_pair(smem_u32(&empty_bar[s]));
+                    if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
                 umma_commit_pair(smem_u32(&tfull_bar[buf]));
             }

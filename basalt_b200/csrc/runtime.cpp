@@ -118,6 +118,8 @@ struct Plan {
     unsigned logical_block[3] = {0, 0, 0};   // block the caller must ask for when it differs from the block launched
     unsigned tail_k = 0;    // FFMA matmul with a split-K tail wave (K extent): the caller's 2-D grid is re-issued as a 1-D grid of
                             // whole tiles followed by K-parts of the tail tiles; six trailing parameters (see basalt_rt_launch)
+    std::string pair;       // persistent kernel only: the same kernel lowered for clusters of two CTAs that share a 2 x lgrid-wide,
+                            // two-row tile; launched instead when the caller's grid is even in x and y
     unsigned lgrid = 0;     // persistent kernel: the caller's grid goes in two trailing u32 parameters; lgrid logical CTAs
                             // along x form one tile, and min(SM count, tiles) CTAs are launched
 };
@@ -131,6 +133,7 @@ struct basalt_rt_function {
     basalt_rt_module* mod = nullptr;
     CUfunction fn = nullptr;
     CUfunction coarse = nullptr;   // see Plan::coarse
+    CUfunction pair = nullptr;     // see Plan::pair
     CUdeviceptr status = 0;        // see Plan::status
     bool has_plan = false;
     Plan plan;
@@ -228,6 +231,7 @@ void parse_plans(const char* ptx, std::map<std::string, Plan>* out) {
             else if (k == "smem") p.smem = (unsigned)strtoul(v.c_str(), nullptr, 10);
             else if (k == "params") p.nparams = (unsigned)strtoul(v.c_str(), nullptr, 10);
             else if (k == "coarse") p.coarse = v;
+            else if (k == "pair") p.pair = v;
             else if (k == "status") p.status = v != "0";
             else if (k == "logical_block") sscanf(v.c_str(), "%u,%u,%u", &p.logical_block[0], &p.logical_block[1], &p.logical_block[2]);
             else if (k == "lgrid") p.lgrid = (unsigned)strtoul(v.c_str(), nullptr, 10);
@@ -400,8 +404,13 @@ int basalt_rt_get_function(basalt_rt_module* mod, const char* name, basalt_rt_fu
             if (!rc) rc = check(f, "cuMemcpyHtoD", f.cuMemcpyHtoD(h->status, &zero, 4));
             if (rc) { delete h; return rc; }
         }
+        if (!h->plan.pair.empty() && !getenv("BASALT_RT_NO_PAIR")) {
+            rc = check(f, "cuModuleGetFunction", f.cuModuleGetFunction(&h->pair, mod->mod, h->plan.pair.c_str()));
+            if (rc) { delete h; return rc; }
+        }
         if (h->plan.smem > 48 * 1024) {
             rc = check(f, "cuFuncSetAttribute", f.cuFuncSetAttribute(fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)h->plan.smem));
+            if (!rc && h->pair) rc = check(f, "cuFuncSetAttribute", f.cuFuncSetAttribute(h->pair, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)h->plan.smem));
             if (rc) { delete h; return rc; }
         }
     }
@@ -574,17 +583,25 @@ int basalt_rt_launch(basalt_rt_function* fn, const uint32_t grid[3], const uint3
     if (p.status) all.push_back(&status_ptr);
     uint32_t sm = shared_mem_bytes ? shared_mem_bytes : p.smem;
     uint32_t g[3] = {grid[0], grid[1], grid[2]}, lgx = grid[0], lgy = grid[1];
+    CUfunction entry = fn->fn;
     if (p.lgrid) {
         if (grid[2] != 1) return set_err(4, 0, "cuLaunchKernel", "kernel was compiled for a two-dimensional grid");
         uint64_t tiles = (uint64_t)((lgx + p.lgrid - 1) / p.lgrid) * lgy;
         uint64_t sms = (uint64_t)fn->mod->ctx->sm_count;
         g[0] = (uint32_t)(tiles < sms ? tiles : sms);
         g[1] = 1;
+        if (fn->pair && p.lgrid == 2 && lgx % 2 == 0 && lgy % 2 == 0 && sms >= 2) {
+            // clusters of two CTAs (the entry's own .reqnctapercluster), each walking tiles of 2 x 2 logical CTAs
+            uint64_t pair_tiles = (uint64_t)(lgx / 2) * (lgy / 2);
+            uint64_t pairs = pair_tiles < sms / 2 ? pair_tiles : sms / 2;
+            g[0] = (uint32_t)(2 * pairs);
+            entry = fn->pair;
+        }
         if (g[0] == 0) return 0;
         all.push_back(&lgx);
         all.push_back(&lgy);
     }
-    return check(f, "cuLaunchKernel", f.cuLaunchKernel(fn->fn, g[0], g[1], g[2], p.block[0], p.block[1], p.block[2], sm, (CUstream)stream, all.data(), nullptr));
+    return check(f, "cuLaunchKernel", f.cuLaunchKernel(entry, g[0], g[1], g[2], p.block[0], p.block[1], p.block[2], sm, (CUstream)stream, all.data(), nullptr));
 }
 
 int basalt_rt_occupancy(basalt_rt_function* fn, uint32_t block_threads, uint32_t shared_mem_bytes, int* ctas_per_sm, int* sm_count) {

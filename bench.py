@@ -333,6 +333,13 @@ def others_summary(ctx, torch, stream, peaks_hbm, peaks_tf):
         ms_e = timed(go, 5)
         out["matmul_f16_8192"].update({"emitted_tflops": fl / ms_e / 1e9, "emitted_frac_of_bf16_peak": fl / ms_e / 1e9 / peaks_tf, "emitted_status": fn.status()})
         out["matmul_f16_8192"]["emitted_regimes"] = best_and_sustained(go, fl)
+        os.environ["BASALT_RT_NO_PAIR"] = "1"      # the same module's one-SM entry (128x256 tiles), for comparison
+        try:
+            fn1 = emitted(kb.matmul_f16(M, N, K), "matmul_kernel")
+        finally:
+            os.environ.pop("BASALT_RT_NO_PAIR", None)
+        go1 = fn1.bind((N // 128, M // 128), 128, 0, [dp(A), dp(B), dp(C)], stream=stream)
+        out["matmul_f16_8192"]["emitted_one_sm_entry_tflops"] = fl / timed(go1, 5) / 1e9
         out["matmul_f16_8192"]["peaks"] = {"bf16_tflops_burst_best_of_10": peaks_tf, "bf16_tflops_sustained": measured_sustained_tf()}
     except Exception as e:   # noqa: BLE001
         out["matmul_f16_8192"]["emitted_error"] = str(e)[:200]

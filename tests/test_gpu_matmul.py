@@ -7,6 +7,7 @@ sum is exactly representable, must match exactly.  At the benchmark's full sizes
 evaluated on sampled rows, and the whole result is checked with Freivalds' identity
 C*v == A*(B*v), a size-independent property."""
 import ctypes
+import os
 
 import numpy as np
 import pytest
@@ -96,15 +97,21 @@ def run_matmul_f16(gpu, how, A, B, N, b_is_nk):
         gpu.synchronize()
         assert status.to_numpy(np.int32)[0] == 0, "a bounded wait inside the kernel expired"
     else:
-        fn = emitted(gpu, kb.matmul_f16(M, N, K, b_is_nk, per_cta=(how == "emitted_per_cta")), "matmul_kernel")
+        # "emitted" takes the two-SM entry whenever the grid is even in x and y; "emitted_one_sm" keeps the one-SM entry
+        if how == "emitted_one_sm":
+            os.environ["BASALT_RT_NO_PAIR"] = "1"
+        try:
+            fn = emitted(gpu, kb.matmul_f16(M, N, K, b_is_nk, per_cta=(how == "emitted_per_cta")), "matmul_kernel")
+        finally:
+            os.environ.pop("BASALT_RT_NO_PAIR", None)
         fn.launch((N // 128, M // 128), 128, 0, [dA, dB, dC])
         assert fn.status() == 0, "a bounded wait inside the emitted kernel expired"
     return dC.to_numpy(np.float16).reshape(M, N)
 
 
-@pytest.mark.parametrize("how", ["hand", "emitted", "emitted_per_cta"])
+@pytest.mark.parametrize("how", ["hand", "emitted", "emitted_one_sm", "emitted_per_cta"])
 @pytest.mark.parametrize("b_is_nk", [True, False])
-@pytest.mark.parametrize("shape", [(128, 128, 64), (128, 128, 256), (256, 384, 192), (256, 512, 192), (384, 256, 64), (2304, 512, 64)])
+@pytest.mark.parametrize("shape", [(128, 128, 64), (128, 128, 256), (256, 384, 192), (256, 512, 192), (384, 256, 64), (2304, 512, 64), (256, 256, 1024)])
 def test_matmul_f16_exact_on_small_integers(gpu, how, b_is_nk, shape):
     M, N, K = shape
     A, B, _ = sgemm_fixture(M, N, K)
@@ -128,7 +135,22 @@ def test_matmul_f16_vs_oracle(gpu, orc, how, b_is_nk):
     assert rel_fro(got, want) <= F16_TOL
 
 
-@pytest.mark.parametrize("how", ["hand", "emitted"])
+@pytest.mark.parametrize("b_is_nk", [True, False])
+def test_matmul_f16_pairs_over_many_waves(gpu, b_is_nk):
+    # 4864 x 4096: 19 x 16 tiles of 256 x 256 on 74 pairs of SMs (4.1 waves: both accumulators and all six
+    # stages wrap several times, the last band has 3 tile rows); the two entries must agree bit for bit
+    M, N, K = 4864, 4096, 192
+    A = w.f16_normal01(w.SEEDS["matmul_f16"] + 7, M * K).reshape(M, K)
+    B = w.f16_normal01(w.SEEDS["matmul_f16"] + 8, K * N).reshape(K, N)
+    Bdev = np.ascontiguousarray(B.T) if b_is_nk else B
+    pair = run_matmul_f16(gpu, "emitted", A, Bdev, N, b_is_nk)
+    one = run_matmul_f16(gpu, "emitted_one_sm", A, Bdev, N, b_is_nk)
+    hand = run_matmul_f16(gpu, "hand", A, Bdev, N, b_is_nk)
+    assert np.isfinite(pair).all()
+    assert np.array_equal(pair.view(np.uint16), one.view(np.uint16)) and np.array_equal(pair.view(np.uint16), hand.view(np.uint16))
+
+
+@pytest.mark.parametrize("how", ["hand", "emitted", "emitted_one_sm"])
 def test_matmul_f16_full_size(gpu, orc, how):
     M = N = K = 8192
     A = np.empty(M * K, np.float16); B = np.empty(K * N, np.float16)
