@@ -105,6 +105,7 @@ def _load() -> C.CDLL:
         "basalt_k_sgemm_f32": (C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, vp]),
         "basalt_k_sgemm_f32_static_workspace": (C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, vp]),
         "basalt_k_matmul_f16": (C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, vp, vp]),
+        "basalt_k_matmul_f16_allgather": (C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, P(vp), C.c_int, vp, vp]),
         "basalt_k_max_i32_allreduce": (C.c_int, [vp, i64, vp, P(u64), C.c_int, C.c_int, C.c_uint32, vp, vp, vp, u64, vp]),
         "basalt_k_peer_allreduce_max_i32": (C.c_int, [P(u64), C.c_int, C.c_int, C.c_uint32, vp, vp, vp, u64, C.c_int, C.c_int32, vp]),
     }

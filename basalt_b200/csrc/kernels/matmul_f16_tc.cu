@@ -426,10 +426,23 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
     *n_idx = r / rows;
 }
 
-template <bool B_IS_NK>
+// The same rows of the result in the other ranks' buffers (peer-mapped device memory), for the fused
+// gather: the epilogue stores every 16-byte piece of a tile to this GPU's buffer and to each of these.
+struct PeerRows {
+    __half* c[BASALT_K_MAX_PEERS - 1];
+    int n;
+};
+
+constexpr int STAGING_BYTES = 4 * 32 * 128;   // STAGED: 32 rows x 64 columns of f16 for each of the four epilogue warps
+
+// STAGED: the epilogue transposes each 32-row x 64-column piece through shared memory so that a warp's store
+// instruction writes four whole 128-byte lines instead of 32 separate 16-byte pieces of 32 different rows.
+// Over NVLink that is the difference between a line-sized and a 16-byte write per request, which is why the
+// fused gather (PUSH) needs it.
+template <bool B_IS_NK, bool PUSH, bool STAGED>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS3, 1)
     matmul_f16_tc_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, __half* __restrict__ C, int M, int N, int K,
-                       int32_t* status) {
+                       int32_t* status, const PeerRows peers) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], tfull_bar[2], tempty_bar[2];
     __shared__ uint32_t tmem_slot;
@@ -532,8 +545,58 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS3, 1)
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            __half* crow = C + (size_t)(mi * TM + (int)rank * BM + ew * 32 + lane) * N + (size_t)ni * TN;
+            const size_t tile_off = (size_t)(mi * TM + (int)rank * BM + ew * 32 + lane) * N + (size_t)ni * TN;
+            __half* crow = C + tile_off;
             const uint32_t src = tmem_base + buf * TN + ((uint32_t)(ew * 32) << 16);
+            if (STAGED) {
+                uint8_t* stg = smem_raw + (tiles - smem_u32(smem_raw)) + STAGES * STAGE_BYTES3 + ew * (32 * 128);
+                const size_t warp_off = (size_t)(mi * TM + (int)rank * BM + ew * 32) * N + (size_t)ni * TN;   // the warp's first row
+                const int rrow = lane >> 3, piece = lane & 7;   // reading back: eight lanes cover one 128-byte row
+#pragma unroll 1
+                for (int c = 0; c < TN; c += 64) {
+#pragma unroll
+                    for (int half = 0; half < 2; half++) {
+                        uint32_t r[32];
+                        asm volatile(
+                            "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+                              "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+                              "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]),
+                              "=r"(r[30]), "=r"(r[31])
+                            : "r"(src + (uint32_t)(c + 32 * half)));
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                        for (int q = 0; q < 4; q++) {   // 16-byte piece 4*half + q of this lane's row, at a column rotated by the row: no bank conflicts
+                            uint32_t h[4];
+#pragma unroll
+                            for (int i = 0; i < 4; i++) {
+                                __half2 v = __floats2half2_rn(__uint_as_float(r[8 * q + 2 * i]), __uint_as_float(r[8 * q + 2 * i + 1]));
+                                h[i] = *reinterpret_cast<uint32_t*>(&v);
+                            }
+                            *reinterpret_cast<uint4*>(stg + lane * 128 + (((4 * half + q) ^ (lane & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+                        }
+                    }
+                    __syncwarp();
+                    uint4 v[8];
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        const int row = 4 * i + rrow;
+                        v[i] = *reinterpret_cast<const uint4*>(stg + row * 128 + ((piece ^ (row & 7)) << 4));
+                    }
+                    __syncwarp();   // the next piece may overwrite the staging rows
+                    __half* dst = C + warp_off + c + 8 * piece;
+#pragma unroll
+                    for (int i = 0; i < 8; i++) *reinterpret_cast<uint4*>(dst + (size_t)(4 * i + rrow) * N) = v[i];
+                    if (PUSH) {   // the same lines into every peer's buffer, over NVLink
+                        for (int p = 0; p < peers.n; p++) {
+                            __half* pdst = peers.c[p] + warp_off + c + 8 * piece;
+#pragma unroll
+                            for (int i = 0; i < 8; i++) *reinterpret_cast<uint4*>(pdst + (size_t)(4 * i + rrow) * N) = v[i];
+                        }
+                    }
+                }
+            } else {
 #pragma unroll 1
             for (int c = 0; c < TN; c += 32) {
                 uint32_t r[32];
@@ -554,11 +617,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS3, 1)
                 }
 #pragma unroll
                 for (int q = 0; q < 4; q++) *reinterpret_cast<uint4*>(crow + c + 8 * q) = make_uint4(h[4 * q], h[4 * q + 1], h[4 * q + 2], h[4 * q + 3]);
+                if (PUSH) {   // the same 64 bytes of this row into every peer's buffer, over NVLink
+                    for (int p = 0; p < peers.n; p++) {
+                        __half* prow = peers.c[p] + tile_off + c;
+#pragma unroll
+                        for (int q = 0; q < 4; q++) *reinterpret_cast<uint4*>(prow + 8 * q) = make_uint4(h[4 * q], h[4 * q + 1], h[4 * q + 2], h[4 * q + 3]);
+                    }
+                }
+            }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[buf]), 0));
         }
+        if (PUSH) __threadfence_system();   // this thread's peer stores are performed before the kernel can end
     }
     if (!ok && status) atomicExch(status, 1);
     __syncwarp();
@@ -628,10 +700,10 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, __half* C, i
 }
 
 
-template <bool B_IS_NK>
-int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, __half* C, int M, int N, int K, int32_t* status, cudaStream_t s) {
-    constexpr int smem = v3::STAGES * v3::STAGE_BYTES3 + 1024;
-    auto kern = v3::matmul_f16_tc_pair<B_IS_NK>;
+template <bool B_IS_NK, bool PUSH, bool STAGED>
+int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, __half* C, int M, int N, int K, int32_t* status, cudaStream_t s, const v3::PeerRows& peers) {
+    constexpr int smem = v3::STAGES * v3::STAGE_BYTES3 + 1024 + (STAGED ? v3::STAGING_BYTES : 0);
+    auto kern = v3::matmul_f16_tc_pair<B_IS_NK, PUSH, STAGED>;
     static int max_pairs = 0;
     if (!max_pairs) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -647,7 +719,7 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, __half* C, int M, 
     }
     const int tiles = (M / v3::TM) * (N / v3::TN);
     const int pairs = tiles < max_pairs ? tiles : max_pairs;
-    kern<<<2 * pairs, v3::THREADS3, smem, s>>>(ma, mb, C, M, N, K, status);
+    kern<<<2 * pairs, v3::THREADS3, smem, s>>>(ma, mb, C, M, N, K, status, peers);
     return basalt_k::record(cudaGetLastError(), "matmul_f16");
 }
 
@@ -664,7 +736,10 @@ extern "C" int basalt_k_matmul_f16(const void* A, const void* B, void* C, int M,
     if (M % v3::TM == 0 && N % v3::TN == 0 && !getenv("BASALT_K_MATMUL_NO_PAIR")) {   // 256 x 256 tiles on pairs of SMs
         rc = b_is_nk ? make_map(&mb, B, (uint64_t)N, (uint64_t)K, BK, v3::HALF_N) : make_map(&mb, B, (uint64_t)K, (uint64_t)N, 64, BK);
         if (rc) return rc;
-        return b_is_nk ? launch_pair<true>(ma, mb, (__half*)C, M, N, K, status, s) : launch_pair<false>(ma, mb, (__half*)C, M, N, K, status, s);
+        const v3::PeerRows none = {};
+        if (getenv("BASALT_K_MATMUL_DIRECT_EPILOGUE"))   // A/B switch: 16-byte pieces straight from the registers (1.3 % slower at 8192^3)
+            return b_is_nk ? launch_pair<true, false, false>(ma, mb, (__half*)C, M, N, K, status, s, none) : launch_pair<false, false, false>(ma, mb, (__half*)C, M, N, K, status, s, none);
+        return b_is_nk ? launch_pair<true, false, true>(ma, mb, (__half*)C, M, N, K, status, s, none) : launch_pair<false, false, true>(ma, mb, (__half*)C, M, N, K, status, s, none);
     }
     if (N % v2::BN2 == 0) {   // 128 x 256 tiles, persistent
         rc = b_is_nk ? make_map(&mb, B, (uint64_t)N, (uint64_t)K, BK, v2::BN2) : make_map(&mb, B, (uint64_t)K, (uint64_t)N, 64, BK);
@@ -674,4 +749,27 @@ extern "C" int basalt_k_matmul_f16(const void* A, const void* B, void* C, int M,
     rc = b_is_nk ? make_map(&mb, B, (uint64_t)N, (uint64_t)K, BK, BN) : make_map(&mb, B, (uint64_t)K, (uint64_t)N, 64, BK);
     if (rc) return rc;
     return b_is_nk ? launch<3, true>(ma, mb, (__half*)C, M, N, K, status, s) : launch<3, false>(ma, mb, (__half*)C, M, N, K, status, s);
+}
+
+// C = A * B for this rank's rows, every tile stored to this GPU's result buffer and to the same rows of
+// each peer's buffer from the epilogue of the tcgen05 kernel: compute and gather in one kernel.
+extern "C" int basalt_k_matmul_f16_allgather(const void* A, const void* B, void* C, int M, int N, int K, int b_is_nk, void* const* peer_c, int n_peers,
+                                             int32_t* status, void* stream) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    if (M % v3::TM || N % v3::TN || K % BK) return basalt_k::record_msg(1, "matmul_f16_allgather", "M and N must be multiples of 256 and K of 64");
+    if (n_peers < 0 || n_peers > BASALT_K_MAX_PEERS - 1 || (n_peers && !peer_c)) return basalt_k::record_msg(1, "matmul_f16_allgather", "bad peer list");
+    uintptr_t all = (uintptr_t)A | (uintptr_t)B | (uintptr_t)C;
+    v3::PeerRows peers = {};
+    peers.n = n_peers;
+    for (int i = 0; i < n_peers; i++) { peers.c[i] = (__half*)peer_c[i]; all |= (uintptr_t)peer_c[i]; }
+    if (all & 15) return basalt_k::record_msg(1, "matmul_f16_allgather", "matrices must be 16-byte aligned");
+    CUtensorMap ma, mb;
+    int rc = make_map(&ma, A, (uint64_t)M, (uint64_t)K, BK, BM);
+    if (rc) return rc;
+    rc = b_is_nk ? make_map(&mb, B, (uint64_t)N, (uint64_t)K, BK, v3::HALF_N) : make_map(&mb, B, (uint64_t)K, (uint64_t)N, 64, BK);
+    if (rc) return rc;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (getenv("BASALT_K_MATMUL_UNSTAGED_PUSH"))   // A/B switch: 16-byte pieces straight from the registers
+        return b_is_nk ? launch_pair<true, true, false>(ma, mb, (__half*)C, M, N, K, status, s, peers) : launch_pair<false, true, false>(ma, mb, (__half*)C, M, N, K, status, s, peers);
+    return b_is_nk ? launch_pair<true, true, true>(ma, mb, (__half*)C, M, N, K, status, s, peers) : launch_pair<false, true, true>(ma, mb, (__half*)C, M, N, K, status, s, peers);
 }

@@ -50,6 +50,15 @@ def sgemm_f32_static_workspace(A, B, Cm, M: int, N: int, K: int, stream=None):
     _check(lib.basalt_k_sgemm_f32_static_workspace(_p(A), _p(B), _p(Cm), M, N, K, C.c_void_p(stream)))
 
 
+def matmul_f16_allgather(A, B, Cm, M: int, N: int, K: int, peer_ptrs, b_is_nk: bool = False, status=None, stream=None):
+    """This rank's rows of C = A * B, stored to `Cm` and, from the same epilogue, to each address in
+    `peer_ptrs` (the same rows of the other ranks' result buffers, peer-mapped).  Follow it with the
+    peer exchange on the same stream: that is the barrier after which every rank holds all rows."""
+    arr = (C.c_void_p * max(1, len(peer_ptrs)))(*[C.c_void_p(int(p)) for p in peer_ptrs])
+    _check(lib.basalt_k_matmul_f16_allgather(_p(A), _p(B), _p(Cm), M, N, K, int(b_is_nk), arr, len(peer_ptrs),
+                                             _p(status) if status is not None else None, C.c_void_p(stream)))
+
+
 def matmul_f16(A, B, Cm, M: int, N: int, K: int, b_is_nk: bool = False, status=None, stream=None):
     _check(lib.basalt_k_matmul_f16(_p(A), _p(B), _p(Cm), M, N, K, int(b_is_nk), _p(status) if status is not None else None,
                                    C.c_void_p(stream)))

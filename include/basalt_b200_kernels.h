@@ -90,6 +90,17 @@ int basalt_k_max_i32_allreduce(const int32_t *x, int64_t n, int32_t *partial, co
                                int rank, uint32_t epoch, int32_t *result, uint32_t *status, uint32_t *ticket,
                                uint64_t timeout_ns, void *stream);
 
+/* The row-sharded fp16 matmul with its gather fused in: C = A * B for this rank's M rows as
+ * basalt_k_matmul_f16 (CTA pairs, tcgen05.mma.cta_group::2), and the epilogue stores every piece of
+ * every tile both to C and to the same position behind each of the n_peers pointers in peer_c (host
+ * array; each entry the address, in this process, of the same rows of another rank's result buffer,
+ * mapped with basalt_rt_ipc_open).  Each storing thread ends with a system-scope fence, so a
+ * stream-ordered basalt_k_peer_allreduce_max_i32 after this kernel is the barrier after which every
+ * rank holds the whole result.  M, N multiples of 256, K of 64, n_peers <= BASALT_K_MAX_PEERS - 1.
+ * No counterpart in the reference, which has no multi-GPU path. */
+int basalt_k_matmul_f16_allgather(const void *A, const void *B, void *C, int M, int N, int K, int b_is_nk,
+                                  void *const *peer_c, int n_peers, int32_t *status, void *stream);
+
 #if defined(__GNUC__)
 #pragma GCC visibility pop
 #endif

@@ -15,7 +15,7 @@ sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 import basalt_b200 as b  # noqa: E402
-from basalt_b200 import kernels_bir as kb, sharding, workloads as w  # noqa: E402
+from basalt_b200 import kernels, kernels_bir as kb, sharding, workloads as w  # noqa: E402
 from _util import orc_matmul_f16_rows, orc_sgemm_rows, rel_fro, vp  # noqa: E402
 
 
@@ -125,6 +125,30 @@ def main():
         ctx.synchronize()
         group.barrier()
         pg.close()
+    for r, p in enumerate(ptrs):
+        if r != group.rank:
+            ctx.ipc_close(p)
+
+    # ---- the same, gather fused into the tensor-core kernel: its epilogue stores every tile to every rank ----
+    M, N, K = 512 * group.world, 512, 192
+    A = w.f16_normal01(w.SEEDS["matmul_f16"] + 11, M * K).reshape(M, K); B = w.f16_normal01(w.SEEDS["matmul_f16"] + 12, K * N).reshape(K, N)
+    want = orc_matmul_f16_rows(orc, A, B, N, False, 0, M)
+    r0, r1 = group.shard(M, 256)
+    Ml = r1 - r0
+    dA, dB, dC = ctx.upload(A[r0:r1]), ctx.upload(B), ctx.upload(np.full((M, N), np.nan, np.float16))
+    st, flag = ctx.upload(np.zeros(1, np.int32)), ctx.upload(np.zeros(2, np.int32))
+    ptrs = group.map_peers(ctx, dC)
+    group.barrier()      # every rank's buffer holds its NaN fill before anyone stores into it
+    others = [ptrs[r] + r0 * N * 2 for r in range(group.world) if r != group.rank]
+    for _ in range(3):
+        kernels.matmul_f16_allgather(dA, dB, dC.device_ptr() + r0 * N * 2, Ml, N, K, others, status=st)
+        peers.allreduce_max_i32(flag.device_ptr(), flag.device_ptr() + 4, None)      # the barrier: all ranks' stores have landed
+        ctx.synchronize()
+        assert st.to_numpy(np.int32)[0] == 0 and peers.status() == 0
+        got = dC.to_numpy(np.float16).reshape(M, N)
+        assert np.isfinite(got).all(), "rows of some rank never arrived"
+        assert rel_fro(got, want) <= 2e-3, "fused gather"
+        group.barrier()
     for r, p in enumerate(ptrs):
         if r != group.rank:
             ctx.ipc_close(p)
