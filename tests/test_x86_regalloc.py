@@ -243,130 +243,58 @@ def test_cuda_c_sources_match_interpreter(ptx):
                 assert np.array_equal(a, b), name
 
 
-TYPES = ("i8", "i16", "i32", "i64")
-BINOPS = ("add", "sub", "mul", "and", "or", "xor", "shl", "lshr", "ashr", "div", "rem")
-NP = {"i8": np.int8, "i16": np.int16, "i32": np.int32, "i64": np.int64, "f32": np.float32, "f64": np.float64}
+import _opkernels as ops
 
 
-def _binop_kernel(ty: str, op: str) -> str:
-    sz = np.dtype(NP[ty]).itemsize
-    return module(f"""  func @k(ptr.global, ptr.global, ptr.global) -> void {{
-  bb0:
-    %0 = tid.x i64
-    %1 = const.i i64 {sz}
-    %2 = mul i64 %0, %1
-    %3 = add ptr.global %arg0, %2
-    %4 = load {ty} ptr.global %3, align {sz}
-    %5 = add ptr.global %arg1, %2
-    %6 = load {ty} ptr.global %5, align {sz}
-    %7 = {op} {ty} %4, %6
-    %8 = add ptr.global %arg2, %2
-    store {ty} ptr.global %8, %7, align {sz}
-    ret
-  }}
-""")
-
-
-@pytest.mark.parametrize("ty", TYPES)
+@pytest.mark.parametrize("ty", ops.INT_TYPES)
 def test_integer_binops_match_interpreter(ty):
-    rng = np.random.default_rng(7)
     n = 300
-    bits = np.dtype(NP[ty]).itemsize * 8
-    info = np.iinfo(NP[ty])
-    a = rng.integers(info.min, info.max, n, dtype=NP[ty], endpoint=True)
-    b = rng.integers(info.min, info.max, n, dtype=NP[ty], endpoint=True)
-    a[:4] = [info.min, info.max, -1, 0]
-    for op in BINOPS:
-        bb = b.copy()
-        if op in ("shl", "lshr", "ashr"):
-            bb = (bb.astype(np.int64) % bits).astype(NP[ty])      # in-range counts: wider ones differ by design per ISA
-        if op in ("div", "rem"):
-            bb[bb == 0] = 3
-            bb[(a == info.min) & (bb == -1)] = 5                 # overflow traps on x86
-        got = np.zeros(n, NP[ty]); want = np.zeros(n, NP[ty])
-        text = _binop_kernel(ty, op)
+    for op in ops.INT_BINOPS:
+        a, bb = ops.int_inputs(ty, op, n)
+        got = np.zeros(n, ops.NP[ty]); want = np.zeros(n, ops.NP[ty])
+        text = ops.binop_kernel(ty, op)
         x86.compile(text)(a, bb, got, n)
         run_kernel(text, "k", [a, bb, want], n)
         assert np.array_equal(got, want), (ty, op)
 
 
-@pytest.mark.parametrize("ty", ("f32", "f64"))
-def test_float_binops_and_compares_match_interpreter(ty):
-    rng = np.random.default_rng(11)
+@pytest.mark.parametrize("ty", ops.INT_TYPES + ("f32", "f64"))
+def test_compares_and_select_match_interpreter(ty):
     n = 200
-    a = (rng.standard_normal(n) * 100).astype(NP[ty]); b = (rng.standard_normal(n) * 10).astype(NP[ty])
-    a[:3] = [0.0, np.inf, np.nan]; b[:3] = [-0.0, 1.0, 2.0]; b[5] = np.nan
-    for op in ("fadd", "fsub", "fmul", "fdiv"):
-        got = np.zeros(n, NP[ty]); want = np.zeros(n, NP[ty])
-        text = _binop_kernel(ty, op)
-        x86.compile(text)(a, b, got, n)
-        run_kernel(text, "k", [a, b, want], n)
-        assert np.array_equal(got.view(np.uint8), want.view(np.uint8)), (ty, op)
-    sz = np.dtype(NP[ty]).itemsize
-    for pred in ("oeq", "one", "olt", "ole", "ogt", "oge", "ord", "uno"):
-        text = module(f"""  func @k(ptr.global, ptr.global, ptr.global) -> void {{
-  bb0:
-    %0 = tid.x i64
-    %1 = const.i i64 {sz}
-    %2 = mul i64 %0, %1
-    %3 = add ptr.global %arg0, %2
-    %4 = load {ty} ptr.global %3, align {sz}
-    %5 = add ptr.global %arg1, %2
-    %6 = load {ty} ptr.global %5, align {sz}
-    %7 = fcmp {pred} {ty} %4, %6
-    %8 = zext i32 i1 %7
-    %9 = const.i i64 4
-    %10 = mul i64 %0, %9
-    %11 = add ptr.global %arg2, %10
-    store i32 ptr.global %11, %8, align 4
-    ret
-  }}
-""")
+    a, bb = ops.float_inputs(ty, n) if ty.startswith("f") else ops.int_inputs(ty, "add", n)
+    if not ty.startswith("f"):
+        bb[8:12] = a[8:12]
+    for pred in (ops.FCMP_PREDS if ty.startswith("f") else ops.ICMP_PREDS):
         got = np.zeros(n, np.int32); want = np.zeros(n, np.int32)
-        x86.compile(text)(a, b, got, n)
-        run_kernel(text, "k", [a, b, want], n)
+        text = ops.compare_kernel(ty, pred)
+        x86.compile(text)(a, bb, got, n)
+        run_kernel(text, "k", [a, bb, want], n)
         assert np.array_equal(got, want), (ty, pred)
+    got = np.zeros(n, ops.NP[ty]); want = np.zeros(n, ops.NP[ty])
+    text = ops.select_kernel(ty)
+    x86.compile(text)(a, bb, got, n)
+    run_kernel(text, "k", [a, bb, want], n)
+    assert np.array_equal(got.view(np.uint8), want.view(np.uint8)), ty
 
 
-CASTS = [("sext", "i8", "i32"), ("zext", "i8", "i32"), ("sext", "i16", "i64"), ("zext", "i16", "i64"), ("sext", "i32", "i64"),
-         ("zext", "i32", "i64"), ("trunc", "i64", "i8"), ("trunc", "i32", "i16"), ("sitofp", "i32", "f32"), ("sitofp", "i64", "f64"),
-         ("sitofp", "i8", "f32"), ("uitofp", "i32", "f32"), ("uitofp", "i64", "f64"), ("uitofp", "i64", "f32"), ("uitofp", "i16", "f64"),
-         ("fptosi", "f32", "i32"), ("fptosi", "f64", "i64"), ("fptoui", "f32", "i32"), ("fptoui", "f64", "i64"), ("fptoui", "f32", "i64"),
-         ("fpext", "f32", "f64"), ("fptrunc", "f64", "f32"), ("bitcast", "f32", "i32"), ("bitcast", "i64", "f64")]
+@pytest.mark.parametrize("ty", ("f32", "f64"))
+def test_float_binops_match_interpreter(ty):
+    n = 200
+    a, bb = ops.float_inputs(ty, n)
+    for op in ops.FLOAT_BINOPS:
+        got = np.zeros(n, ops.NP[ty]); want = np.zeros(n, ops.NP[ty])
+        text = ops.binop_kernel(ty, op)
+        x86.compile(text)(a, bb, got, n)
+        run_kernel(text, "k", [a, bb, want], n)
+        assert np.array_equal(got.view(np.uint8), want.view(np.uint8)), (ty, op)
 
 
-@pytest.mark.parametrize("op,src,dst", CASTS)
+@pytest.mark.parametrize("op,src,dst", ops.CASTS)
 def test_casts_match_interpreter(op, src, dst):
-    rng = np.random.default_rng(13)
     n = 128
-    if src.startswith("f"):
-        lim = 2.0**31 - 256 if dst == "i32" else 2.0**62
-        a = (rng.random(n) * lim).astype(NP[src])
-        if op == "fptosi":
-            a[::2] *= -1
-        if op == "fptoui" and dst == "i64":
-            a[:8] = NP[src](2.0**63) + (np.arange(8) * 2.0**40).astype(NP[src])      # the high path
-    else:
-        info = np.iinfo(NP[src])
-        a = rng.integers(info.min, info.max, n, dtype=NP[src], endpoint=True)
-        a[:3] = [info.min, info.max, -1]
-    ssz, dsz = np.dtype(NP[src]).itemsize, np.dtype(NP[dst]).itemsize
-    text = module(f"""  func @k(ptr.global, ptr.global) -> void {{
-  bb0:
-    %0 = tid.x i64
-    %1 = const.i i64 {ssz}
-    %2 = mul i64 %0, %1
-    %3 = add ptr.global %arg0, %2
-    %4 = load {src} ptr.global %3, align {ssz}
-    %5 = {op} {dst} {src} %4
-    %6 = const.i i64 {dsz}
-    %7 = mul i64 %0, %6
-    %8 = add ptr.global %arg1, %7
-    store {dst} ptr.global %8, %5, align {dsz}
-    ret
-  }}
-""")
-    got = np.zeros(n, NP[dst]); want = np.zeros(n, NP[dst])
+    a = ops.cast_inputs(op, src, dst, n)
+    text = ops.cast_kernel(op, src, dst)
+    got = np.zeros(n, ops.NP[dst]); want = np.zeros(n, ops.NP[dst])
     x86.compile(text)(a, got, n)
     run_kernel(text, "k", [a, want], n)
     assert np.array_equal(got.view(np.uint8), want.view(np.uint8)), (op, src, dst)
