@@ -194,3 +194,105 @@ def test_float_atomic_add_exch_and_cas(gpu, level):
     # exch stores i+100 and returns i; the first cas sees i+100 and restores i; the second expects i+1, sees i, fails
     assert np.array_equal(dev[0], cells) and np.array_equal(dev[1], cells + 100 + cells)
     assert np.array_equal(dev[0], cpu[0]) and np.array_equal(dev[1], cpu[1])
+
+
+# ---- control flow: phis that read each other, a switch, a data-dependent loop ----
+SWAPPING_PHIS = ops.module("""  func @k(ptr.global, ptr.global) -> void {
+  bb0:
+    %0 = bid.x i64
+    %1 = bdim.x i64
+    %2 = mul i64 %0, %1
+    %3 = tid.x i64
+    %4 = add i64 %2, %3
+    %5 = const.i i64 4
+    %6 = mul i64 %4, %5
+    %7 = add ptr.global %arg0, %6
+    %8 = load i32 ptr.global %7, align 4
+    %9 = const.i i32 0
+    %10 = const.i i32 1
+    br bb1
+  bb1:
+    %11 = phi i32 [bb0 -> %9, bb2 -> %12]
+    %12 = phi i32 [bb0 -> %10, bb2 -> %11]
+    %13 = phi i32 [bb0 -> %9, bb2 -> %16]
+    %14 = icmp slt i32 %13, %8
+    condbr %14, bb2, bb3
+  bb2:
+    %15 = const.i i32 1
+    %16 = add i32 %13, %15
+    br bb1
+  bb3:
+    %17 = const.i i32 10
+    %18 = mul i32 %11, %17
+    %19 = add i32 %18, %12
+    %20 = add ptr.global %arg1, %6
+    store i32 ptr.global %20, %19, align 4
+    ret
+  }
+""")
+
+SWITCH_AND_LOOP = ops.module("""  func @k(ptr.global, ptr.global) -> void {
+  bb0:
+    %0 = bid.x i64
+    %1 = bdim.x i64
+    %2 = mul i64 %0, %1
+    %3 = tid.x i64
+    %4 = add i64 %2, %3
+    %5 = const.i i64 4
+    %6 = mul i64 %4, %5
+    %7 = add ptr.global %arg0, %6
+    %8 = load i32 ptr.global %7, align 4
+    %9 = const.i i32 5
+    %10 = rem i32 %8, %9
+    switch %10, default bb4 [0 -> bb1, 1 -> bb2, 3 -> bb3]
+  bb1:
+    %11 = const.i i32 1000
+    br bb5
+  bb2:
+    %12 = const.i i32 3
+    %13 = mul i32 %8, %12
+    br bb5
+  bb3:
+    %14 = const.i i32 0
+    %15 = sub i32 %14, %8
+    br bb5
+  bb4:
+    %16 = const.i i32 7
+    %17 = xor i32 %8, %16
+    br bb5
+  bb5:
+    %18 = phi i32 [bb1 -> %11, bb2 -> %13, bb3 -> %15, bb4 -> %17]
+    %19 = const.i i32 0
+    br bb6
+  bb6:
+    %20 = phi i32 [bb5 -> %18, bb7 -> %25]
+    %21 = phi i32 [bb5 -> %19, bb7 -> %27]
+    %22 = const.i i32 100
+    %23 = icmp sgt i32 %20, %22
+    condbr %23, bb7, bb8
+  bb7:
+    %24 = const.i i32 2
+    %25 = div i32 %20, %24
+    %26 = const.i i32 1
+    %27 = add i32 %21, %26
+    br bb6
+  bb8:
+    %28 = const.i i32 4096
+    %29 = mul i32 %21, %28
+    %30 = add i32 %29, %20
+    %31 = add ptr.global %arg1, %6
+    store i32 ptr.global %31, %30, align 4
+    ret
+  }
+""")
+
+
+@pytest.mark.parametrize("level", LEVELS)
+def test_control_flow(gpu, level):
+    rng = np.random.default_rng(21)
+    trips = rng.integers(0, 9, N).astype(np.int32)
+    got, want = both(gpu, SWAPPING_PHIS, [trips, np.zeros(N, np.int32)], level)
+    assert np.array_equal(got, want) and np.array_equal(got, np.where(trips % 2 == 0, 1, 10))
+    vals = rng.integers(0, 5000, N).astype(np.int32)
+    got, want = both(gpu, SWITCH_AND_LOOP, [vals, np.zeros(N, np.int32)], level)
+    assert np.array_equal(got, want)
