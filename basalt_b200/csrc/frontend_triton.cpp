@@ -595,7 +595,18 @@ struct Value {
 // ---------------------------------------------------------------------------------------------
 class KernelCompiler {
 public:
-    KernelCompiler(const Kernel& k, const TritonOptions& o, Module* m) : k_(k), opt_(o), m_(m) {}
+    KernelCompiler(const Kernel& k, const TritonOptions& o, Module* m, const std::vector<Kernel>* all = nullptr) : k_(k), opt_(o), m_(m), all_(all) {}
+
+    // Names of the @triton.jit functions this one calls (by plain name): those are helpers, inlined at the call.
+    static void callees(const std::vector<Stmt>& body, const std::vector<Kernel>& all, std::set<std::string>* out) {
+        for (auto& s : body) {
+            callees_in(s.value, all, out);
+            callees_in(s.cond, all, out);
+            for (auto& a : s.range_args) callees_in(a, all, out);
+            callees(s.body, all, out);
+            callees(s.orelse, all, out);
+        }
+    }
 
     Function run() {
         classify_params();
@@ -613,12 +624,47 @@ private:
     const Kernel& k_;
     const TritonOptions& opt_;
     Module* m_;
+    const std::vector<Kernel>* all_;   // every @triton.jit function of the source, for calls between them
+    int depth_ = 0;                    // nesting of inlined calls
+    Value ret_value_;                  // what the innermost inlined call returned
     int shared_cells_ = 0;
     Function f_;
     std::map<std::string, Value> env_;
     uint32_t cur_ = 0;
     std::vector<bool> closed_;
     bool returned_ = false;
+
+    static void callees_in(const EP& e, const std::vector<Kernel>& all, std::set<std::string>* out) {
+        if (!e) return;
+        if (e->k == Expr::Call && e->a && e->a->k == Expr::Name)
+            for (auto& g : all) if (g.name == e->a->s) out->insert(g.name);
+        callees_in(e->a, all, out);
+        callees_in(e->b, all, out);
+        for (auto& a : e->args) callees_in(a, all, out);
+        for (auto& kw : e->kwargs) callees_in(kw.second, all, out);
+    }
+    const Kernel* jit_function(const std::string& name) const {
+        if (!all_) return nullptr;
+        for (auto& g : *all_) if (g.name == name) return &g;
+        return nullptr;
+    }
+    // Which parameters of a helper are used as pointers (in its own body, or passed on to a helper that does).
+    std::set<std::string> pointer_params_of(const Kernel& g, int depth) {
+        std::set<std::string> names;
+        if (depth > 8) return names;
+        std::vector<const Stmt*> assigns;
+        pointer_positions(g.body, &names, &assigns, depth + 1);
+        for (bool grew = true; grew;) {
+            grew = false;
+            for (const Stmt* s : assigns) {
+                if (!names.count(s->target)) continue;
+                std::set<std::string> more;
+                additive_names(s->value, &more);
+                for (auto& m : more) if (names.insert(m).second) grew = true;
+            }
+        }
+        return names;
+    }
 
     // ---- parameters ----
     static void additive_names(const EP& e, std::set<std::string>* out) {
@@ -627,25 +673,65 @@ private:
         else if (e->k == Expr::Bin && (e->s == "+" || e->s == "-")) { additive_names(e->a, out); additive_names(e->b, out); }
         else if (e->k == Expr::Subscript) additive_names(e->a, out);
     }
-    void pointer_positions(const std::vector<Stmt>& body, std::set<std::string>* names, std::vector<const Stmt*>* assigns) {
+    void pointer_positions(const std::vector<Stmt>& body, std::set<std::string>* names, std::vector<const Stmt*>* assigns, int depth = 0) {
         for (auto& s : body) {
-            if (s.k == Stmt::For || s.k == Stmt::If) { pointer_positions(s.body, names, assigns); pointer_positions(s.orelse, names, assigns); }
+            if (s.k == Stmt::For || s.k == Stmt::If) { pointer_positions(s.body, names, assigns, depth); pointer_positions(s.orelse, names, assigns, depth); }
             if (s.k == Stmt::Assign || s.k == Stmt::AugAssign) assigns->push_back(&s);
-            if (s.value) find_calls(s.value, names);
+            if (s.value) find_calls(s.value, names, depth);
         }
     }
-    void find_calls(const EP& e, std::set<std::string>* names) {
+    void find_calls(const EP& e, std::set<std::string>* names, int depth = 0) {
         if (!e) return;
         if (e->k == Expr::Call) {
             std::string callee = dotted(e->a);
             const bool memory = callee == "tl.load" || callee == "tl.store" || callee.rfind("tl.atomic_", 0) == 0;
             if (memory && !e->args.empty()) additive_names(e->args[0], names);
             for (auto& kw : e->kwargs) if (memory && (kw.first == "pointer" || kw.first == "ptr")) additive_names(kw.second, names);
+            if (const Kernel* g = jit_function(callee)) {   // an argument bound to a helper's pointer parameter is a pointer here too
+                std::set<std::string> ptrs = pointer_params_of(*g, depth);
+                for (size_t i = 0; i < e->args.size() && i < g->params.size(); i++)
+                    if (ptrs.count(g->params[i].name)) additive_names(e->args[i], names);
+                for (auto& kw : e->kwargs) if (ptrs.count(kw.first)) additive_names(kw.second, names);
+            }
         }
-        find_calls(e->a, names);
-        find_calls(e->b, names);
-        for (auto& a : e->args) find_calls(a, names);
-        for (auto& kw : e->kwargs) find_calls(kw.second, names);
+        find_calls(e->a, names, depth);
+        find_calls(e->b, names, depth);
+        for (auto& a : e->args) find_calls(a, names, depth);
+        for (auto& kw : e->kwargs) find_calls(kw.second, names, depth);
+    }
+    // A call of another @triton.jit function of the same source: its body runs here, in a scope of its own,
+    // with the arguments bound to its parameters; `return` hands a value back.
+    Value call_jit(const Kernel& g, const EP& e) {
+        const int line = e->line;
+        if (depth_ >= 16) fail("E304", line, "calls between @triton.jit functions nest more than 16 deep (recursion has no lowering)");
+        if (e->args.size() > g.params.size()) fail("E300", line, "`" + g.name + "` takes " + std::to_string(g.params.size()) + " arguments");
+        std::map<std::string, Value> scope;
+        for (size_t i = 0; i < e->args.size(); i++) scope[g.params[i].name] = eval(e->args[i]);
+        for (auto& kw : e->kwargs) {
+            bool known = false;
+            for (auto& p : g.params) known |= p.name == kw.first;
+            if (!known) fail("E300", line, "`" + g.name + "` has no parameter `" + kw.first + "`");
+            if (scope.count(kw.first)) fail("E300", line, "`" + kw.first + "` is given twice");
+            scope[kw.first] = eval(kw.second);
+        }
+        for (auto& p : g.params) {
+            if (scope.count(p.name)) continue;
+            if (!p.def) fail("E300", line, "`" + g.name + "` needs an argument for `" + p.name + "`");
+            scope[p.name] = eval(p.def);
+        }
+        std::swap(env_, scope);
+        const bool was_returned = returned_;
+        Value was_value = ret_value_;
+        returned_ = false;
+        ret_value_ = Value();
+        depth_++;
+        exec(g.body);
+        depth_--;
+        Value out = ret_value_;
+        std::swap(env_, scope);
+        returned_ = was_returned;
+        ret_value_ = was_value;
+        return out;
     }
     static std::string dotted(const EP& e) {
         if (!e) return "";
@@ -952,6 +1038,7 @@ private:
             return v;
         }
         std::string callee = dotted(e->a);
+        if (const Kernel* g = jit_function(callee)) return call_jit(*g, e);
         if (callee == "tl.program_id" || callee == "tl.num_programs") {
             EP ax = arg_or_kw(e, 0, "axis");
             int64_t axis = ax ? const_of(tile(eval(ax), line, "axis"), line, "the axis") : 0;
@@ -1141,7 +1228,10 @@ private:
             switch (s.k) {
                 case Stmt::Pass: break;
                 case Stmt::Return:
-                    if (s.value && s.value->k != Expr::NoneLit) fail("E300", s.line, "a kernel returns nothing");
+                    if (depth_ > 0) {   // inside an inlined helper: the value goes back to the call
+                        if (s.value && s.value->k == Expr::Tuple) fail("E307", s.line, "a helper that returns several values is not modelled");
+                        ret_value_ = s.value && s.value->k != Expr::NoneLit ? eval(s.value) : Value();
+                    } else if (s.value && s.value->k != Expr::NoneLit) fail("E300", s.line, "a kernel returns nothing");
                     returned_ = true;
                     break;
                 case Stmt::ExprStmt:
@@ -1898,9 +1988,20 @@ bool compile_triton(const char* src, size_t len, const TritonOptions& opts, Modu
             auto mb = opts.constexprs.find("min_blocks");
             m.min_blocks = mb == opts.constexprs.end() ? 1 : (uint32_t)mb->second;
         }
+        // A @triton.jit function that another one calls is a helper: it is inlined at its calls and is no entry.
+        std::set<std::string> helpers;
+        for (size_t i = 0; i < kernels.size(); i++)
+            for (size_t j = 0; j < i; j++) if (kernels[i].name == kernels[j].name) fail("E302", kernels[i].line, "`" + kernels[i].name + "` is defined twice");
         for (auto& k : kernels) {
-            for (auto& f : m.funcs) if (f.name == k.name) fail("E302", k.line, "`" + k.name + "` is defined twice");
-            KernelCompiler kc(k, opts, &m);
+            std::set<std::string> called;
+            KernelCompiler::callees(k.body, kernels, &called);
+            called.erase(k.name);      // a function that calls itself is refused where the call is met
+            helpers.insert(called.begin(), called.end());
+        }
+        if (helpers.size() == kernels.size()) fail("E304", kernels[0].line, "every @triton.jit function is called by another one: no kernel is left");
+        for (auto& k : kernels) {
+            if (helpers.count(k.name)) continue;
+            KernelCompiler kc(k, opts, &m, &kernels);
             Function f = kc.run();
             m.funcs.push_back(std::move(f));
         }

@@ -26,6 +26,11 @@ def vector_add() -> str:
     return backend.compile_triton(load("vector_add"))
 
 
+def saxpy_helpers() -> str:
+    """out = 2.5 x + y written with four helper @triton.jit functions, all inlined into `saxpy_kernel`."""
+    return backend.compile_triton(load("saxpy_helpers"))
+
+
 def small_matmul(K: int = 5) -> str:
     """out = a @ b + c on one M x N tile (M = 4, N = 3 by default in the source), f32."""
     return backend.compile_triton(load("small_matmul"), constexprs={"K": K})

@@ -235,3 +235,47 @@ def test_the_reference_tree_triton_kernels(ptx):
     out = np.zeros((4, 3), np.float32)
     run_kernel(bir, "matmul_kernel", [A, B, C, out, 5], 1)
     assert np.array_equal(out, A @ B + C)
+
+
+# ---- calls between @triton.jit functions ----
+SAXPY_INLINE = '''
+import triton
+import triton.language as tl
+
+@triton.jit
+def saxpy_kernel(x_ptr, y_ptr, out_ptr, n, BLOCK: tl.constexpr):
+    pid = tl.program_id(0)
+    offs = pid * BLOCK + tl.arange(0, BLOCK)
+    x = tl.load(x_ptr + offs, mask=offs < n, other=0.0)
+    y = tl.load(y_ptr + offs, mask=offs < n, other=0.0)
+    t = x * 2.5
+    tl.store(out_ptr + offs, t + y, mask=offs < n)
+'''
+
+
+def test_helper_functions_are_inlined(ptx):
+    # four helpers (positional, keyword and defaulted arguments, a helper that only stores): one entry, and the
+    # same BIR as the kernel written in one piece; pointer-ness of x_ptr / y_ptr / out_ptr flows through the calls
+    bir = kt.saxpy_helpers()
+    assert bir.count("func @") == 1 and "func @saxpy_kernel(ptr.global, ptr.global, ptr.global, i64, i64)" in bir
+    assert bir == b.compile_triton(SAXPY_INLINE)
+    n = 100
+    x = np.arange(n, dtype=np.float32); y = np.ones(n, np.float32)
+    for text in (bir, ptx.optimized_bir(bir)):
+        out = np.full(128 + 4, -1.0, np.float32)
+        run_kernel(text, "saxpy_kernel", [x, y, out, n, 128], 1)
+        assert np.array_equal(out[:n], 2.5 * x + y) and np.all(out[n:] == -1.0)
+
+
+@pytest.mark.parametrize("code, body", [
+    ("E304", "@triton.jit\ndef f(x):\n    return f(x)\n@triton.jit\ndef k(p, n):\n    tl.store(p + tl.arange(0, 4), f(tl.load(p + tl.arange(0, 4))))\n"),
+    ("E300", "@triton.jit\ndef f(x, y):\n    return x + y\n@triton.jit\ndef k(p):\n    tl.store(p + tl.arange(0, 4), f(tl.load(p + tl.arange(0, 4))))\n"),
+    ("E300", "@triton.jit\ndef f(x):\n    return x\n@triton.jit\ndef k(p):\n    tl.store(p + tl.arange(0, 4), f(tl.load(p + tl.arange(0, 4)), z=1))\n"),
+    ("E300", "@triton.jit\ndef f(x):\n    return x\n@triton.jit\ndef k(p):\n    tl.store(p + tl.arange(0, 4), f(1, 2))\n"),
+    ("E307", "@triton.jit\ndef f(x):\n    return (x, x)\n@triton.jit\ndef k(p):\n    a = f(tl.load(p + tl.arange(0, 4)))\n"),
+    ("E304", "@triton.jit\ndef f(x):\n    return g(x)\n@triton.jit\ndef g(x):\n    return f(x)\n"),
+])
+def test_helper_call_refusals(code, body):
+    with pytest.raises(b.Diag) as e:
+        b.compile_triton("import triton\nimport triton.language as tl\n" + body)
+    assert e.value.code == code, e.value

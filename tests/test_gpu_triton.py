@@ -83,3 +83,17 @@ def test_reductions_and_atomics(gpu):
     out = dev(gpu, np.array([2**31 - 1], np.int32))
     fn.launch((70001 + 4095) // 4096, 256, 0, [dev(gpu, x), out, b.i64(70001), b.i64(4096)])
     assert int(out.to_numpy(np.int32)[0]) == int(x.min())
+
+
+@pytest.mark.parametrize("level", [0, 2])
+def test_kernel_written_with_helper_functions(gpu, level):
+    # four @triton.jit helpers inlined into one entry; many programs, ragged n, nothing past n touched
+    fn = emitted(gpu, kt.saxpy_helpers(), "saxpy_kernel", level)
+    block = 512
+    for n in (1, 777, (1 << 16) + 3):
+        x = w.f32_pm1(21, n); y = w.f32_pm1(22, n)
+        programs = (n + block - 1) // block
+        out = dev(gpu, np.full(programs * block + 8, -1.0, np.float32))
+        fn.launch(programs, 128, 0, [dev(gpu, x), dev(gpu, y), out, b.i64(n), b.i64(block)])
+        got = out.to_numpy(np.float32)
+        assert np.array_equal(got[:n], np.float32(2.5) * x + y) and np.all(got[n:] == -1.0), (n, level)
