@@ -837,19 +837,80 @@ private:
             }
             return;
         }
+        if (eat_id("switch")) {
+            // The dispatch block is filled in after the body, when every label is known: the scrutinee is evaluated
+            // before it, the body starts in an unreachable block (code before the first label never runs), a label
+            // opens a new block that the code before it falls into, `break` leaves for the block after the switch and
+            // `continue` still belongs to the enclosing loop.
+            need_p("(");
+            Ex sv = rval(expr());
+            if (!sv.ty.is_scalar() || !is_int(sv.ty.b)) fail("E300", line, "the value a `switch` selects on must be an integer");
+            sv = convert(sv, scalar_ct(promote(sv.ty.b)), line);
+            need_p(")");
+            if (!is_p("{")) fail("E304", line, "a `switch` body must be a block");
+            i_++;
+            const uint32_t dispatch = new_block(), after = new_block(), before_first_label = new_block();
+            br(dispatch);
+            at(before_first_label);
+            loops_.push_back({after, loops_.empty() ? UINT32_MAX : loops_.back().cont});
+            scopes_.emplace_back();
+            std::vector<std::pair<int64_t, uint32_t>> cases;
+            bool has_default = false;
+            uint32_t default_block = after;
+            while (!is_p("}")) {
+                if (at_eof()) fail("E202", line, "unterminated `switch`");
+                const int label_line = tok().line;
+                if (eat_id("case") || is_id("default")) {
+                    const bool is_default = is_id("default");
+                    int64_t value = 0;
+                    if (is_default) i_++;
+                    else value = const_int();
+                    need_p(":");
+                    const uint32_t lb = new_block();
+                    br(lb);   // the code above falls through into the label
+                    at(lb);
+                    if (is_default) {
+                        if (has_default) fail("E302", label_line, "a second `default` label");
+                        has_default = true;
+                        default_block = lb;
+                    } else {
+                        if (size_of(sv.ty.b) == 4) value = (int64_t)(int32_t)value;
+                        for (auto& c : cases) if (c.first == value) fail("E302", label_line, "the case value " + std::to_string(value) + " appears twice");
+                        cases.push_back({value, lb});
+                    }
+                    continue;
+                }
+                statement();
+            }
+            i_++;
+            scopes_.pop_back();
+            loops_.pop_back();
+            br(after);
+            at(dispatch);
+            Term& t = f_->blocks[cur_].term;
+            t.kind = Term::Switch;
+            t.has_val = true;
+            t.val = sv.v;
+            t.t = default_block;
+            t.cases = cases;
+            closed_[cur_] = true;
+            at(after);
+            return;
+        }
         if (eat_id("break")) {
-            if (loops_.empty()) fail("E201", line, "`break` outside a loop");
+            if (loops_.empty()) fail("E201", line, "`break` outside a loop or switch");
             need_p(";");
             br(loops_.back().brk);
             return;
         }
         if (eat_id("continue")) {
-            if (loops_.empty()) fail("E201", line, "`continue` outside a loop");
+            if (loops_.empty() || loops_.back().cont == UINT32_MAX) fail("E201", line, "`continue` outside a loop");
             need_p(";");
             br(loops_.back().cont);
             return;
         }
-        if (is_id("switch") || is_id("goto") || is_id("struct") || is_id("union") || is_id("enum") || is_id("typedef") || is_id("template") || is_id("asm"))
+        if (is_id("case") || is_id("default")) fail("E201", line, "`" + tok().s + "` outside a switch");
+        if (is_id("goto") || is_id("struct") || is_id("union") || is_id("enum") || is_id("typedef") || is_id("template") || is_id("asm"))
             fail("E304", line, "`" + tok().s + "` is outside the subset");
         if (type_start(tok())) { declaration(); return; }
         expr();

@@ -11,7 +11,7 @@ import os
 _DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "cu")
 
 STATIC = ("vadd_i32", "vector_add_f32", "max_i32", "max_i32_atomic", "chain_vector", "square_vector", "constant_math",
-          "control_flow")
+          "control_flow", "switch_cases")
 
 
 def path(name: str) -> str:

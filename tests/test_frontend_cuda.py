@@ -244,7 +244,12 @@ def test_matmul_sources_lower_to_the_same_tile_op_as_their_twins(ptx, shape, tmp
     ("E303", "__global__ int k(int *o) { return 0; }"),
     ("E303", "__global__ __device__ void k(int *o) { }"),
     ("E303", "__global__ void a(int *o) { } __global__ void k(int *o) { a(o); }"),
-    ("E304", "__global__ void k(int *o) { switch (o[0]) { default: break; } }"),
+    ("E304", "__global__ void k(int *o) { goto done; }"),
+    ("E302", "__global__ void k(int *o) { switch (o[0]) { case 1: case 1: o[0] = 2; } }"),
+    ("E302", "__global__ void k(int *o) { switch (o[0]) { default: o[0] = 1; default: o[0] = 2; } }"),
+    ("E300", "__global__ void k(float *o) { switch (o[0]) { case 1: o[0] = 2; } }"),
+    ("E201", "__global__ void k(int *o) { switch (o[0]) { case 1: continue; } }"),
+    ("E201", "__global__ void k(int *o) { case 1: o[0] = 2; }"),
     ("E304", "struct S { int a; }; __global__ void k(int *o) { }"),
     ("E304", "__global__ void k(unsigned *o, unsigned d) { o[0] = o[1] / d; }"),
     ("E304", "__global__ void k(float *o) { o[0] = sqrtf(o[1]); }"),
@@ -336,3 +341,34 @@ __global__ void weighted(const int *x, int *out, int n, int a, int b) {
     o = np.zeros(1, np.int32)
     run_kernel(opt, "weighted", [z, o, 4, 6, 0], 1)
     assert o[0] == 0
+
+
+def switch_cases_expected(x):
+    """basalt_b200/cu/switch_cases.cu restated in Python integers (C division and remainder truncate toward zero)."""
+    out = []
+    for v in map(int, x):
+        r = int(np.fmod(v, 6))
+        if r == 0: acc = 100
+        elif r == 1: acc = 17              # 10, then falls through into `acc += 7`
+        elif r == 2: acc = 7
+        elif r == 4: acc = 0
+        elif r == 5: acc = int(v / 6) - 1
+        else: acc = -3                     # default, then falls through into `acc *= 3`
+        for k in range(4):
+            if k == 1: continue
+            acc += 1000 if k == 2 else k
+            acc += 1
+        out.append(acc)
+    return np.array(out, np.int32)
+
+
+def test_switch_source(ptx):
+    # labels open blocks the code above falls into, `break` leaves the switch, `continue` the enclosing loop's body
+    bir, opt = _both(ptx, kc.load("switch_cases"))
+    assert "switch %" in bir and "default bb" in bir
+    n = 200
+    x = (np.arange(n) * 37 % 101 - 50).astype(np.int32)
+    for text in (bir, opt):
+        out = np.zeros(n, np.int32)
+        run_kernel(text, "switch_cases", [x, out, n], n)
+        assert np.array_equal(out, switch_cases_expected(x))

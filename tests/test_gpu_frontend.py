@@ -111,3 +111,13 @@ def test_matmul_f16_source(gpu, orc, b_is_nk):
     assert fn.status() == 0, "a bounded wait inside the emitted kernel expired"
     got = dC.to_numpy(np.float16).reshape(M, N)
     assert rel_fro(got, orc_matmul_f16_rows(orc, A, Bdev, N, b_is_nk, 0, M)) <= 2e-3
+
+
+@pytest.mark.parametrize("level", [0, 2])
+def test_switch_source(gpu, level):
+    from test_frontend_cuda import switch_cases_expected
+    n = 5000
+    x = (np.arange(n) * 37 % 1013 - 500).astype(np.int32)
+    out = np.zeros(n, np.int32)
+    gpu.cpu_launch(emitted(gpu, b.compile_cuda(kc.load("switch_cases")), "switch_cases", level), [x, out, b.i32(n)], n)
+    assert np.array_equal(out, switch_cases_expected(x))
