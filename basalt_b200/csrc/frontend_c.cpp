@@ -5,7 +5,7 @@
 // __global__/__device__ qualifiers, scalar and pointer parameters, scalar locals, __shared__
 // arrays with constant extents, if/for/while/do, the C expression operators with the usual
 // arithmetic conversions, threadIdx/blockIdx/blockDim/gridDim, __syncthreads, warp shuffles and
-// votes (with or without the _sync mask), atomics, min/max, object-like #define.  Anything else is
+// votes (with or without the _sync mask), atomics, min/max, object- and function-like #define.  Anything else is
 // refused with E304 rather than guessed at.
 //
 // Differences from the reference's lowering (crates/basalt-sema/src/lower.rs), each deliberate:
@@ -64,15 +64,8 @@ public:
             if (*p_ == '#' && line_start) { directive(); continue; }
             line_start = false;
             Token t = next();
-            if (t.k == Tk::Ident) {
-                auto it = macros_.find(t.s);
-                if (it != macros_.end()) {
-                    for (Token m : it->second) { m.line = t.line; out.push_back(m); }
-                    continue;
-                }
-                if (fn_macros_.count(t.s)) fail("E304", t.line, "function-like macro `" + t.s + "` is outside the subset");
-            }
-            out.push_back(t);
+            if (t.k == Tk::Ident) expand_into(t, &out, 0);
+            else out.push_back(t);
         }
         Token e;
         e.k = Tk::Eof;
@@ -84,8 +77,51 @@ public:
 private:
     const char *p_, *end_;
     int line_ = 1;
+    struct FnMacro {
+        std::vector<std::string> params;
+        std::vector<Token> body;
+    };
     std::map<std::string, std::vector<Token>> macros_;
-    std::map<std::string, bool> fn_macros_;
+    std::map<std::string, FnMacro> fn_macros_;
+
+    // Appends what the identifier `t` stands for: itself, the tokens of an object-like macro, or, when it names
+    // a function-like macro and a `(` follows, the macro's body with each parameter replaced by the tokens of
+    // its argument (arguments are expanded as they are read; a name not followed by `(` stays a name, as in C).
+    void expand_into(const Token& t, std::vector<Token>* out, int depth) {
+        auto obj = macros_.find(t.s);
+        if (obj != macros_.end()) {
+            for (Token m : obj->second) { m.line = t.line; out->push_back(m); }
+            return;
+        }
+        auto fn = fn_macros_.find(t.s);
+        if (fn == fn_macros_.end()) { out->push_back(t); return; }
+        bool line_start = false;
+        skip_space(&line_start);
+        if (p_ >= end_ || *p_ != '(') { out->push_back(t); return; }
+        if (depth > 32) fail("E304", t.line, "macro calls nest too deeply");
+        p_++;
+        std::vector<std::vector<Token>> args(1);
+        for (int parens = 0;;) {
+            skip_space(&line_start);
+            if (p_ >= end_) fail("E202", t.line, "unterminated call of macro `" + t.s + "`");
+            Token a = next();
+            if (a.k == Tk::Punct && a.s == "(") parens++;
+            else if (a.k == Tk::Punct && a.s == ")") { if (parens == 0) break; parens--; }
+            else if (a.k == Tk::Punct && a.s == "," && parens == 0) { args.emplace_back(); continue; }
+            if (a.k == Tk::Ident) expand_into(a, &args.back(), depth + 1);
+            else args.back().push_back(a);
+        }
+        const FnMacro& m = fn->second;
+        if (m.params.empty() && args.size() == 1 && args[0].empty()) args.clear();
+        if (args.size() != m.params.size())
+            fail("E300", t.line, "macro `" + t.s + "` takes " + std::to_string(m.params.size()) + " argument(s), " + std::to_string(args.size()) + " given");
+        for (const Token& b : m.body) {
+            size_t which = m.params.size();
+            if (b.k == Tk::Ident) for (size_t i = 0; i < m.params.size(); i++) if (m.params[i] == b.s) which = i;
+            if (which == m.params.size()) { Token c = b; c.line = t.line; out->push_back(c); }
+            else for (Token c : args[which]) { c.line = t.line; out->push_back(c); }
+        }
+    }
 
     void skip_space(bool* line_start) {
         while (p_ < end_) {
@@ -126,14 +162,35 @@ private:
         while (k < text.size() && (isalnum((unsigned char)text[k]) || text[k] == '_')) k++;
         std::string macro = text.substr(j, k - j);
         if (macro.empty()) fail("E201", line, "#define without a name");
-        if (k < text.size() && text[k] == '(') { fn_macros_[macro] = true; return; }
+        FnMacro fm;
+        const bool function_like = k < text.size() && text[k] == '(';
+        if (function_like) {   // the parameter list follows the name with no space in between
+            size_t q = k + 1;
+            for (;;) {
+                while (q < text.size() && isspace((unsigned char)text[q])) q++;
+                if (q < text.size() && text[q] == ')') { q++; break; }
+                size_t r = q;
+                while (r < text.size() && (isalnum((unsigned char)text[r]) || text[r] == '_')) r++;
+                if (r == q) fail(text.compare(q, 3, "...") == 0 ? "E304" : "E201", line, "#define " + macro + ": a parameter list of plain names is expected");
+                fm.params.push_back(text.substr(q, r - q));
+                q = r;
+                while (q < text.size() && isspace((unsigned char)text[q])) q++;
+                if (q < text.size() && text[q] == ',') { q++; continue; }
+                if (q < text.size() && text[q] == ')') { q++; break; }
+                fail("E201", line, "#define " + macro + ": `,` or `)` expected in the parameter list");
+            }
+            k = q;
+        }
         std::string body = text.substr(k);
         Lexer sub(body.data(), body.size());
         sub.macros_ = macros_;
+        sub.fn_macros_ = fn_macros_;
+        for (auto& prm : fm.params) { sub.macros_.erase(prm); sub.fn_macros_.erase(prm); }   // a parameter hides a macro of its name
         sub.line_ = line;
         std::vector<Token> toks = sub.run();
         toks.pop_back();
-        macros_[macro] = toks;
+        if (function_like) { fm.body = toks; fn_macros_[macro] = fm; macros_.erase(macro); }
+        else { macros_[macro] = toks; fn_macros_.erase(macro); }
     }
 
     Token next() {

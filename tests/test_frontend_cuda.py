@@ -372,3 +372,35 @@ def test_switch_source(ptx):
         out = np.zeros(n, np.int32)
         run_kernel(text, "switch_cases", [x, out, n], n)
         assert np.array_equal(out, switch_cases_expected(x))
+
+
+def test_function_like_macros():
+    # arguments are expanded as they are read, a macro may use earlier ones, `NAME (` with a space is still a call,
+    # an empty parameter list takes an empty argument list
+    src = """
+#define N 16
+#define IDX(i, j) ((i) * N + (j))
+#define SQ(x) ((x) * (x))
+#define CLAMP(v, lo, hi) ((v) < (lo) ? (lo) : ((v) > (hi) ? (hi) : (v)))
+#define TWICE(e) (SQ(e) + SQ(e))
+#define ZERO() 0
+__global__ void k(const int *in, int *out, int n) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    int r = i / N, c = i % N;
+    int v = in[IDX(r, c)];
+    out[IDX(r, c)] = CLAMP(TWICE(v + 1), ZERO(), 500) + SQ(c) - IDX (1, 2);
+}
+"""
+    bir = b.compile_cuda(src)
+    n = 256
+    x = (np.arange(n) % 23 - 11).astype(np.int32); out = np.zeros(n, np.int32)
+    run_kernel(bir, "k", [x, out, n], n)
+    c = np.arange(n) % 16
+    assert np.array_equal(out, np.clip(2 * (x + 1) ** 2, 0, 500) + c * c - 18)
+    for bad, code in (("#define F(a, b) ((a)+(b))\n__global__ void k(int*o){ o[0]=F(1); }", "E300"),
+                      ("#define F(a,...) (a)\n__global__ void k(int*o){ o[0]=F(1); }", "E304"),
+                      ("#define F(a) ((a)\n__global__ void k(int*o){ o[0]=F(1; }", "E202")):
+        with pytest.raises(b.Diag) as e:
+            b.compile_cuda(bad)
+        assert e.value.code == code, e.value
