@@ -274,8 +274,22 @@ def others_summary(ctx, torch, stream, peaks_hbm, peaks_tf):
         out["max_i32_n2^28_other_sources"] = {"from_cuda_c_gbs": 4.0 * n / ms_c / 1e6, "from_triton_gbs": 4.0 * n / ms_t / 1e6,
                                               "ok": int(acc.item()) == int(x.max().item())}
         del x
+        # the vector add from its CUDA-C and Triton sources (2^26 elements per operand, 768 MiB of traffic)
+        n = 1 << 26
+        a = torch.randint(-2**31, 2**31 - 1, (n,), dtype=torch.int32, device="cuda"); bb = torch.randint(-2**31, 2**31 - 1, (n,), dtype=torch.int32, device="cuda")
+        c = torch.empty_like(a)
+        fn = emitted(b.compile_cuda(kc.load("vadd_i32")), "vadd_i32")
+        ms_c = timed(lambda: fn.launch((n + 255) // 256, 256, 0, [dp(a), dp(bb), dp(c), b.i32(n)], stream=stream), 20)
+        ok_c = bool(torch.equal(c, a + bb))
+        c.zero_()
+        fn = emitted(kt.vadd_i32(), "vadd_i32")
+        block = 4096
+        ms_t = timed(lambda: fn.launch((n + block - 1) // block, 256, 0, [dp(a), dp(bb), dp(c), b.i64(n), b.i64(block)], stream=stream), 20)
+        out["vadd_i32_n2^26_other_sources"] = {"from_cuda_c_gbs": 12.0 * n / ms_c / 1e6, "from_triton_gbs": 12.0 * n / ms_t / 1e6,
+                                               "ok": ok_c and bool(torch.equal(c, a + bb))}
+        del a, bb, c
     except Exception as e:   # noqa: BLE001 - reported, not hidden
-        out["max_i32_n2^28_other_sources"] = {"error": str(e)[:200]}
+        out["other_sources_error"] = str(e)[:200]
     n = 1 << 26
     x = torch.randint(-2**31, 2**31 - 1, (n,), dtype=torch.int32, device="cuda"); y = torch.empty_like(x)
     fn = emitted(kb.helper_chain(), "helper_chain")
@@ -320,41 +334,43 @@ def others_summary(ctx, torch, stream, peaks_hbm, peaks_tf):
     A = (torch.randn(M, K, device="cuda") * 0.1).half(); B = (torch.randn(K, N, device="cuda") * 0.1).half(); C = torch.empty(M, N, device="cuda", dtype=torch.float16)
     st = torch.zeros(1, dtype=torch.int32, device="cuda")
     fl = 2.0 * M * N * K
+    # The kernels are timed INTERLEAVED (four rounds of five launches each, medians reported): under the 1 kW cap
+    # whichever kernel runs right after a cooler phase gains about 2 %, so back-to-back blocks per kernel would
+    # favour the first one.  The sustained regimes (2 s each) follow afterwards.
+    mm = out["matmul_f16_8192"] = {}
+    cands = {}
     try:
-        ms_h = timed(lambda: kernels.matmul_f16(A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K, False, st.data_ptr(), stream), 5)
-        out["matmul_f16_8192"] = {"handwritten_tflops": fl / ms_h / 1e9, "handwritten_frac_of_bf16_peak": fl / ms_h / 1e9 / peaks_tf, "status": int(st.item())}
-        out["matmul_f16_8192"]["handwritten_regimes"] = best_and_sustained(
-            lambda: kernels.matmul_f16(A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K, False, st.data_ptr(), stream), fl)
-    except Exception as e:   # noqa: BLE001
-        out["matmul_f16_8192"] = {"handwritten_error": str(e)[:200]}
-    try:
+        cands["handwritten"] = lambda: kernels.matmul_f16(A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K, False, st.data_ptr(), stream)
         fn = emitted(kb.matmul_f16(M, N, K), "matmul_kernel")
-        go = fn.bind((N // 128, M // 128), 128, 0, [dp(A), dp(B), dp(C)], stream=stream)
-        ms_e = timed(go, 5)
-        out["matmul_f16_8192"].update({"emitted_tflops": fl / ms_e / 1e9, "emitted_frac_of_bf16_peak": fl / ms_e / 1e9 / peaks_tf, "emitted_status": fn.status()})
-        out["matmul_f16_8192"]["emitted_regimes"] = best_and_sustained(go, fl)
+        cands["emitted"] = fn.bind((N // 128, M // 128), 128, 0, [dp(A), dp(B), dp(C)], stream=stream)
         os.environ["BASALT_RT_NO_PAIR"] = "1"      # the same module's one-SM entry (128x256 tiles), for comparison
         try:
             fn1 = emitted(kb.matmul_f16(M, N, K), "matmul_kernel")
         finally:
             os.environ.pop("BASALT_RT_NO_PAIR", None)
-        go1 = fn1.bind((N // 128, M // 128), 128, 0, [dp(A), dp(B), dp(C)], stream=stream)
-        out["matmul_f16_8192"]["emitted_one_sm_entry_tflops"] = fl / timed(go1, 5) / 1e9
-        out["matmul_f16_8192"]["peaks"] = {"bf16_tflops_burst_best_of_10": peaks_tf, "bf16_tflops_sustained": measured_sustained_tf()}
-    except Exception as e:   # noqa: BLE001
-        out["matmul_f16_8192"]["emitted_error"] = str(e)[:200]
-    # Comparator only, never on the product path: the vendor library on the SAME operands in the same
-    # regimes (the power a dense matmul draws, and so the clock it settles at, depends on the data).
-    try:
-        lib_mm = lambda: torch.matmul(A, B, out=C)
-        ms_l = timed(lib_mm, 5)
-        out["matmul_f16_8192"]["cublas_f16_same_operands"] = {"tflops": fl / ms_l / 1e9, **best_and_sustained(lib_mm, fl)}
+        cands["emitted_one_sm_entry"] = fn1.bind((N // 128, M // 128), 128, 0, [dp(A), dp(B), dp(C)], stream=stream)
+        # comparators only, never on the product path: the vendor library on the SAME operands (the power a dense
+        # matmul draws, and so the clock it settles at, depends on the data) and on the same values in bf16
+        cands["cublas_f16_same_operands"] = lambda: torch.matmul(A, B, out=C)
         Ab, Bb, Cb = A.bfloat16(), B.bfloat16(), torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
-        lib_bf = lambda: torch.matmul(Ab, Bb, out=Cb)
-        ms_b = timed(lib_bf, 5)
-        out["matmul_f16_8192"]["cublas_bf16_same_values"] = {"tflops": fl / ms_b / 1e9, **best_and_sustained(lib_bf, fl)}
-    except Exception as e:   # noqa: BLE001
-        out["matmul_f16_8192"]["cublas_error"] = str(e)[:200]
+        cands["cublas_bf16_same_values"] = lambda: torch.matmul(Ab, Bb, out=Cb)
+        rounds = {k: [] for k in cands}
+        for _ in range(4):
+            for k, f_ in cands.items():
+                rounds[k].append(fl / timed(f_, 5) / 1e9)
+        med = {k: statistics.median(v) for k, v in rounds.items()}
+        mm.update({"handwritten_tflops": med["handwritten"], "emitted_tflops": med["emitted"], "emitted_one_sm_entry_tflops": med["emitted_one_sm_entry"],
+                   "cublas_f16_same_operands_tflops": med["cublas_f16_same_operands"], "cublas_bf16_same_values_tflops": med["cublas_bf16_same_values"],
+                   "how": "medians of 4 interleaved rounds of 5 launches", "status": int(st.item()), "emitted_status": fn.status(),
+                   "emitted_over_handwritten": med["emitted"] / med["handwritten"], "emitted_over_cublas_f16_same_operands": med["emitted"] / med["cublas_f16_same_operands"],
+                   "emitted_frac_of_bf16_peak": med["emitted"] / peaks_tf, "handwritten_frac_of_bf16_peak": med["handwritten"] / peaks_tf,
+                   "emitted_frac_of_nominal_2250": med["emitted"] / 2250.0})
+        mm["emitted_regimes"] = best_and_sustained(cands["emitted"], fl)
+        mm["handwritten_regimes"] = best_and_sustained(cands["handwritten"], fl)
+        mm["cublas_f16_same_operands_regimes"] = best_and_sustained(cands["cublas_f16_same_operands"], fl)
+        mm["peaks"] = {"bf16_tflops_burst_best_of_10": peaks_tf, "bf16_tflops_sustained": measured_sustained_tf()}
+    except Exception as e:   # noqa: BLE001 - reported, not hidden
+        mm["error"] = str(e)[:300]
     return out
 
 
