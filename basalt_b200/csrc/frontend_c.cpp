@@ -1361,19 +1361,28 @@ private:
         return r;
     }
 
-    // BIR division is signed (crates/basalt-x86/src/oracle.rs:1546-1610); an unsigned divide is only
-    // expressible when the divisor is a power-of-two constant.
+    // BIR division is signed (crates/basalt-x86/src/oracle.rs:1546-1610).  An unsigned divide by a power-of-two
+    // constant is a shift or a mask; any other 32-bit one is done in 64 bits, where both operands, zero-extended,
+    // are non-negative and the signed quotient and remainder are the unsigned ones.  A 64-bit unsigned divide by
+    // anything else has no such widening and is refused.
     Ex unsigned_divrem(bool is_div, const Ex& a, const Ex& b, Ty t, const CT& ct, int line) {
-        const Inst* k = b.v.param ? nullptr : &f_->insts[b.v.idx];
-        if (!k || k->op != Opc::ConstI) fail("E304", line, "unsigned division by a non-constant is outside the subset (BIR division is signed)");
-        uint64_t d = (uint64_t)k->imm;
-        if (scalar_bits(t.sc) == 32) d &= 0xffffffffu;
-        if (d == 0 || (d & (d - 1))) fail("E304", line, "unsigned division by a constant that is not a power of two is outside the subset");
-        int sh = 0;
-        while ((d >> sh) != 1) sh++;
         Ex r;
         r.ty = ct;
-        r.v = is_div ? bin(BinOp::LShr, t, a.v, ci(t, sh)) : bin(BinOp::And, t, a.v, ci(t, (int64_t)(d - 1)));
+        const Inst* k = b.v.param ? nullptr : &f_->insts[b.v.idx];
+        if (k && k->op == Opc::ConstI) {
+            uint64_t d = (uint64_t)k->imm;
+            if (scalar_bits(t.sc) == 32) d &= 0xffffffffu;
+            if (d != 0 && !(d & (d - 1))) {
+                int sh = 0;
+                while ((d >> sh) != 1) sh++;
+                r.v = is_div ? bin(BinOp::LShr, t, a.v, ci(t, sh)) : bin(BinOp::And, t, a.v, ci(t, (int64_t)(d - 1)));
+                return r;
+            }
+        }
+        if (scalar_bits(t.sc) != 32) fail("E304", line, "64-bit unsigned division by anything but a power-of-two constant is outside the subset (BIR division is signed)");
+        const Ty wide = Ty::s(Scalar::I64);
+        Val q = bin(is_div ? BinOp::Div : BinOp::Rem, wide, cast(CastOp::ZExt, wide, t, a.v), cast(CastOp::ZExt, wide, t, b.v));
+        r.v = cast(CastOp::Trunc, t, wide, q);
         return r;
     }
 

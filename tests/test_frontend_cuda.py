@@ -251,7 +251,7 @@ def test_matmul_sources_lower_to_the_same_tile_op_as_their_twins(ptx, shape, tmp
     ("E201", "__global__ void k(int *o) { switch (o[0]) { case 1: continue; } }"),
     ("E201", "__global__ void k(int *o) { case 1: o[0] = 2; }"),
     ("E304", "struct S { int a; }; __global__ void k(int *o) { }"),
-    ("E304", "__global__ void k(unsigned *o, unsigned d) { o[0] = o[1] / d; }"),
+    ("E304", "__global__ void k(unsigned long *o, unsigned long d) { o[0] = o[1] / d; }"),
     ("E304", "__global__ void k(float *o) { o[0] = sqrtf(o[1]); }"),
     ("E304", "__global__ void k(int *o) { o[0] = __shfl_xor_sync(0xff, o[1], 1); }"),
     ("E304", "int table[4]; __global__ void k(int *o) { }"),
@@ -404,3 +404,28 @@ __global__ void k(const int *in, int *out, int n) {
         with pytest.raises(b.Diag) as e:
             b.compile_cuda(bad)
         assert e.value.code == code, e.value
+
+
+def test_unsigned_division_goes_through_64_bits():
+    # BIR division is signed: a 32-bit unsigned divide is done on the zero-extended operands in 64 bits,
+    # a power-of-two constant divisor stays a shift or a mask, a 64-bit unsigned divide is refused
+    src = """
+__global__ void k(const unsigned *a, const unsigned *d, unsigned *q, unsigned *r, int n) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    q[i] = a[i] / d[i] + a[i] / 7u;
+    r[i] = a[i] % d[i] + a[i] % 10u + (a[i] / 8u) + (a[i] % 16u);
+}
+"""
+    bir = b.compile_cuda(src)
+    assert bir.count(" div i64 ") == 2 and bir.count(" rem i64 ") == 2 and " lshr i32 " in bir
+    n = 512
+    rng = np.random.default_rng(1)
+    a = rng.integers(0, 2**32, n, dtype=np.uint64).astype(np.uint32); d = rng.integers(1, 2**32, n, dtype=np.uint64).astype(np.uint32)
+    a[:4] = [0, 2**32 - 1, 2**31, 2**31 - 1]; d[:4] = [2**32 - 1, 1, 3, 2**31]
+    q = np.zeros(n, np.uint32); r = np.zeros(n, np.uint32)
+    run_kernel(bir, "k", [a, d, q, r, n], n)
+    assert np.array_equal(q, (a // d + a // 7).astype(np.uint32)) and np.array_equal(r, (a % d + a % 10 + a // 8 + a % 16).astype(np.uint32))
+    with pytest.raises(b.Diag) as e:
+        b.compile_cuda("__global__ void k(unsigned long *o) { o[0] = o[1] / 3ul; }")
+    assert e.value.code == "E304"
