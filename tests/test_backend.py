@@ -198,3 +198,25 @@ def test_every_kernel_assembles_for_sm_100a(ptx, tmp_path, level):
         p.write_text(ptx.emit(src, b.EmitOpts(opt_level=level)).text)
         r = subprocess.run(["ptxas", "-arch=sm_100a", str(p), "-o", "/dev/null"], capture_output=True, text=True)
         assert r.returncode == 0, f"{name}: {r.stderr}"
+
+
+def test_tiled_fp16_matmul_gets_a_two_sm_twin(ptx):
+    # the persistent tcgen05 form is emitted twice: `<name>` for one SM per tile and `<name>__pair` for clusters
+    # of two (the plan's `pair=` key tells the runtime, which takes it on grids that are even in x and y)
+    for nk in (False, True):
+        text = ptx.emit(kb.matmul_f16(512, 512, 256, nk)).text
+        plans = [l for l in text.splitlines() if l.startswith("//!basalt.plan")]
+        assert len(plans) == 1 and " lgrid=2 " in plans[0] and plans[0].endswith("pair=matmul_kernel__pair")
+        one, two = text.split(".visible .entry matmul_kernel__pair")
+        assert ".visible .entry matmul_kernel(" in one and ".reqnctapercluster" not in one
+        assert ".reqnctapercluster 2, 1, 1" in two and two.count("tcgen05.mma.cta_group::2.kind::f16") == 4
+        assert "tcgen05.alloc.cta_group::2" in two and "tcgen05.dealloc.cta_group::2" in two and two.count("barrier.cluster.arrive") == 2
+        # both entries take the same argument list: the runtime launches either with one set of tensor maps
+        params = lambda t: [l.strip().rstrip(",").split()[-1].split("_", 2)[-1] for l in t.split(")")[0].splitlines() if ".param" in l]
+        assert params(one.split(".visible .entry matmul_kernel(")[1]) == [p.replace("_pair_", "", 1) if p.startswith("_pair_") else p for p in params(two)]
+        # bulk-tensor loads never multicast: a cta_group::2 load names the leader's barrier by address instead
+        for line in text.splitlines():
+            if "cp.async.bulk" in line:
+                assert "multicast" not in line, line
+        # every wait in the twin is bounded: each try_wait loop reads the clock and can leave through the give-up flag
+        assert two.count("mbarrier.try_wait.parity") == two.count("setp.lt.u64") - 1    # + the 2 ms drain of the producer
