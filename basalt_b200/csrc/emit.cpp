@@ -962,7 +962,16 @@ bool emit_ptx(const Module& in, const EmitOptions& opts, EmitResult* out, Diag* 
         if (r.warp_reduces) text += " warp_reduces=" + std::to_string(r.warp_reduces);
         text += "\n";
         if (!r.coarse_of.empty())
-            text += "//!basalt.plan " + r.coarse_of + " coarse=" + f.name + " params=" + std::to_string(f.params.size() - 1) + "\n";
+        {
+            // elements a thread should handle: one trip of the vectorised loop for a streaming body (many short CTAs stream
+            // fastest), four trips when the body is arithmetic-heavy (the 32-level helper chain: 31 to 33 T int-op/s on 2 to
+            // 8 waves, 22 on 128 -- there the per-CTA set-up is no longer hidden behind memory)
+            size_t arithmetic = 0;
+            for (auto& in : f.insts) arithmetic += in.op == Opc::Bin;
+            const int trips = arithmetic > 256 ? 4 : 1;
+            text += "//!basalt.plan " + r.coarse_of + " coarse=" + f.name + " params=" + std::to_string(f.params.size() - 1) + " per_thread=" +
+                    std::to_string(std::max(1, r.vec_lanes) * std::max(1, r.unroll) * trips) + "\n";
+        }
         FnEmitter fe(m, f);
         std::string fn_text;
         if (!fe.run(&fn_text)) {

@@ -1526,7 +1526,8 @@ private:
             if (shape[0].sym >= 0 || shape[1].sym >= 0) fail("E306", line, "rank-2 tiles need compile-time extents");
             lanes = ci(I64(), shape[0].n * shape[1].n);
         }
-        const int unroll = shape.empty() ? 1 : kUnroll;
+        // a reduction has one load per lane, so it takes twice the lanes per iteration to keep as many bytes in flight
+        const int unroll = shape.empty() ? 1 : (fold ? 2 * kUnroll : kUnroll);
         Val tid = index(0), stride = index(6);
         uint32_t pre = cur_, head = new_block(), bodyb = new_block(), done = new_block();
         br(head);

@@ -114,6 +114,7 @@ struct Plan {
     unsigned nparams = 0;   // number of BIR parameters (tensor maps follow them)
     std::vector<TmapSpec> tmaps;
     std::string coarse;     // entry taking one more u64 parameter: the thread count the caller asked for
+    unsigned per_thread = 0; // coarse entry: elements a thread handles in one trip of its loop (vector lanes x unroll)
     bool status = false;    // the entry takes a u64 parameter: a device int32 set when a bounded wait gave up
     unsigned logical_block[3] = {0, 0, 0};   // block the caller must ask for when it differs from the block launched
     unsigned tail_k = 0;    // FFMA matmul with a split-K tail wave (K extent): the caller's 2-D grid is re-issued as a 1-D grid of
@@ -231,6 +232,7 @@ void parse_plans(const char* ptx, std::map<std::string, Plan>* out) {
             else if (k == "smem") p.smem = (unsigned)strtoul(v.c_str(), nullptr, 10);
             else if (k == "params") p.nparams = (unsigned)strtoul(v.c_str(), nullptr, 10);
             else if (k == "coarse") p.coarse = v;
+            else if (k == "per_thread") p.per_thread = (unsigned)strtoul(v.c_str(), nullptr, 10);
             else if (k == "pair") p.pair = v;
             else if (k == "status") p.status = v != "0";
             else if (k == "logical_block") sscanf(v.c_str(), "%u,%u,%u", &p.logical_block[0], &p.logical_block[1], &p.logical_block[2]);
@@ -486,13 +488,20 @@ int basalt_rt_launch(basalt_rt_function* fn, const uint32_t grid[3], const uint3
     if (!fn || !grid || !block) return set_err(4, 0, "basalt_rt_launch", "null argument");
     const Fns& f = fn->mod->ctx->drv->f;
     if (fn->coarse && params && grid[1] == 1 && grid[2] == 1 && block[1] == 1 && block[2] == 1 && block[0] >= 32) {
-        // One-element-per-thread kernel: the caller's launch names the logical threads; run them on
-        // one wave of resident CTAs, each thread looping with several 16-byte accesses in flight.
+        // One-element-per-thread kernel: the caller's launch names the logical threads.  They are run by CTAs whose
+        // threads each make one trip of the vectorised loop (several 16-byte accesses in flight): many short CTAs
+        // stream faster than one resident wave of long-running ones (vadd_i32 at 2^28: 6.9 against 6.1 TB/s), the
+        // hardware scheduler evening out what the SMs and memory channels get.  Never fewer CTAs than would fill the
+        // device when the work allows it, never more than the caller asked for.
         uint64_t logical = (uint64_t)grid[0] * block[0];
         int resident = 0;
         if (f.cuOccupancyMaxActiveBlocksPerMultiprocessor(&resident, fn->coarse, (int)block[0], shared_mem_bytes) != CUDA_SUCCESS || resident < 1) resident = 1;
-        uint32_t wave = (uint32_t)fn->mod->ctx->sm_count * (uint32_t)resident;
-        uint32_t phys = grid[0] < wave ? grid[0] : wave;
+        uint64_t wave = (uint64_t)fn->mod->ctx->sm_count * (uint64_t)resident;
+        uint64_t per_cta = (uint64_t)block[0] * (fn->plan.per_thread ? fn->plan.per_thread : 16);
+        uint64_t want = (logical + per_cta - 1) / per_cta;
+        if (const char* w = getenv("BASALT_RT_COARSE_WAVES")) want = wave * (uint64_t)(atoi(w) > 0 ? atoi(w) : 1);   // A/B switch: a fixed number of waves
+        if (want < wave) want = wave;
+        uint32_t phys = grid[0] < want ? grid[0] : (uint32_t)want;
         std::vector<void*> all(params, params + fn->plan.nparams);
         all.push_back(&logical);
         return check(f, "cuLaunchKernel", f.cuLaunchKernel(fn->coarse, phys, 1, 1, block[0], 1, 1, shared_mem_bytes, (CUstream)stream, all.data(), nullptr));

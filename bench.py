@@ -265,7 +265,7 @@ def others_summary(ctx, torch, stream, peaks_hbm, peaks_tf):
         x = torch.randint(-2**31, 2**31 - 1, (n,), dtype=torch.int32, device="cuda")
         acc = torch.full((1,), -2**31, dtype=torch.int32, device="cuda")
         fn = emitted(b.compile_cuda(kc.load("max_i32")), "max_i32")
-        go = fn.bind(fn.one_wave(256), 256, 0, [dp(x), dp(acc), b.i32(n)], stream=stream)
+        go = fn.bind(fn.streaming_grid(256, n), 256, 0, [dp(x), dp(acc), b.i32(n)], stream=stream)
         ms_c = timed(go, 20)
         fn = emitted(kt.max_i32(), "max_i32")
         block = 32768                      # lanes per program: 128 per thread, one atomic per program
@@ -596,15 +596,15 @@ def main():
     lowest = torch.full((1,), -2**31, dtype=torch.int32, device="cuda")
 
     fn = ctx.load_module(b.Ptx().emit(kb.load("max_i32")).text).get_function("max_i32")
-    blocks = fn.one_wave(256)          # SM count x resident CTAs of this kernel: exactly one wave
+    blocks = fn.streaming_grid(256, n)   # about 64 elements per thread, at most 16 resident waves: measured faster than one wave
     launch_emitted = fn.bind(blocks, 256, 0, [b.ptr(x.data_ptr()), b.ptr(partial.data_ptr()), b.i32(n)], stream=stream)
 
     # The exchange step at N > 1: allreduce(max) of the 4-byte partials.  Over peer-mapped memory
     # (one small kernel of release stores and acquire loads across NVLink) when the GPUs can map
     # each other, else ncclAllReduce; both on the launching stream, so a step ends when its result
     # is in `result`.  (Issuing the collective on a second stream to overlap it with the next
-    # step's kernel was measured and is slower: the collective's CTA takes a slot of the one-wave
-    # grid and the displaced CTA runs as a second wave.)
+    # step's kernel was measured and is slower: the collective's CTA competes with the
+    # reduction's CTAs for the SMs.)
     def reset():
         if peers is None:
             partial.copy_(lowest)                              # a 4-byte device copy resets the running maximum

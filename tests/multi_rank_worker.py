@@ -46,7 +46,7 @@ def main():
         dshard = ctx.upload(y[lo:hi])
         partial = ctx.upload(np.array([-2**31], np.int32)); result = ctx.alloc(4)
         if hi > lo:
-            fn.launch(min(fn.one_wave(256), (hi - lo + 255) // 256), 256, 0, [dshard, partial, b.i32(hi - lo)])
+            fn.launch(fn.streaming_grid(256, hi - lo), 256, 0, [dshard, partial, b.i32(hi - lo)])
         comm.allreduce_max_i32(partial.device_ptr(), result.device_ptr(), 1)
         ctx.synchronize()
         got = int(result.to_numpy(np.int32)[0])

@@ -41,7 +41,7 @@ def test_block_max_source(gpu, orc, level):
         want = np.array([-2**31], np.int32)
         orc.orc_max_i32(vp(x), vp(want), ctypes.c_int32(n), ctypes.c_int64(n))
         out = dev(gpu, np.array([-2**31], np.int32))
-        fn.launch(min(fn.one_wave(256), grid_for(n)), 256, 0, [dev(gpu, x), out, b.i32(n)])
+        fn.launch(fn.streaming_grid(256, n), 256, 0, [dev(gpu, x), out, b.i32(n)])
         assert int(out.to_numpy(np.int32)[0]) == int(want[0]), n
     x = -np.abs(w.i32_pm30(9, 5000)) - 5          # all negative: the identity must not leak
     out = dev(gpu, np.array([-2**31], np.int32))

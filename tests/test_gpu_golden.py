@@ -91,7 +91,7 @@ def test_max_i32(gpu, orc, label, level):
     for form, bir, kernel in sources("max_i32"):
         fn = emitted(gpu, bir, kernel, level)
         out = dev(gpu, np.array([-2**31], np.int32))
-        fn.launch(min(fn.one_wave(256), grid_for(n)), 256, 0, [dx, out, b.i32(n)])
+        fn.launch(fn.streaming_grid(256, n), 256, 0, [dx, out, b.i32(n)])
         assert int(out.to_numpy(np.int32)[0]) == g["value"], (form, level)
     out = dev(gpu, np.array([-2**31], np.int32))
     emitted(gpu, kt.max_i32(), "max_i32", level).launch((n + 8191) // 8192, 256, 0, [dx, out, b.i64(n), b.i64(8192)])      # tl.max over 8192 lanes per program

@@ -82,7 +82,7 @@ def gpu_max(gpu, how, dx, n, level=2):
         emitted(gpu, kb.load("max_i32_atomic"), "max_i32_atomic", level).launch(grid_for(n), 256, 0, [dx, out, b.i32(n)])
     else:
         fn = emitted(gpu, kb.load("max_i32"), "max_i32", level)
-        fn.launch(min(fn.one_wave(256), grid_for(n)), 256, 0, [dx, out, b.i32(n)])
+        fn.launch(fn.streaming_grid(256, n), 256, 0, [dx, out, b.i32(n)])
     return int(out.to_numpy(np.int32)[0])
 
 
