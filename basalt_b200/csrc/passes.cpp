@@ -4,6 +4,7 @@
 #include <algorithm>
 #include <climits>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <functional>
 #include <map>
@@ -1738,7 +1739,8 @@ void optimize_module(Module& m, int opt_level, int reg_budget, std::vector<OptRe
             simplify_cfg(f);
             rep.warp_reduces = fuse_warp_reductions(f);
             bool done = false;
-            for (int U = 4; U >= 1 && !done; U >>= 1) {
+            const int max_unroll = getenv("BASALT_MAX_UNROLL") ? atoi(getenv("BASALT_MAX_UNROLL")) : 4;   // A/B switch
+            for (int U = max_unroll; U >= 1 && !done; U >>= 1) {
                 Function cand = f, coarse;
                 OptReport r = rep;
                 bool ew = vectorize_elementwise(cand, U, &r, &coarse);
