@@ -608,7 +608,7 @@ bool matmul_tcgen05_persistent(const MmaSite& s, std::vector<std::string>* decls
                           "x", "it", "g", "idesc", "lgx", "lgy", "tn2", "ntiles", "perband", "band", "first", "rows", "rr", "mi", "nj", "width", "tile", "gstep", "local",
                           "buf", "use", "bar2", "acc", "bytes", "ew", "c", "src", "spin"})
         b32 += P + n + ", ";
-    b32 += P + "h<16>, " + P + "v<32>;";
+    b32 += P + "h<16>, " + P + "v<32>, " + P + "wo<8>, " + P + "ro<8>, " + P + "rb<32>;";
     decls->push_back(b32);
     std::string b64 = "\t.reg .b64 ";
     for (const char* n : {"w", "da", "db", "t0", "now", "dt", "crow", "status", "ma", "mb"}) b64 += P + n + ", ";
@@ -866,13 +866,34 @@ bool matmul_tcgen05_persistent(const MmaSite& s, std::vector<std::string>* decls
     o("vote.sync.all.pred %s, %s, 0xffffffff;", r("all").c_str(), r("p").c_str());   // the warp stays together: tcgen05.ld is warp-collective
     o("@!%s bra %send;", r("all").c_str(), L.c_str());
     o("tcgen05.fence::after_thread_sync;");
+    // Line-sized stores, as in the two-SM form: each 32-row x 64-column piece of the warp's part of the accumulator is
+    // transposed through 4 KB of shared memory (16-byte units rotated by the row) and stored as whole 128-byte lines.
     o("and.b32 %s, %s, 3;", r("ew").c_str(), r("warp").c_str());   // this warp may touch TMEM lanes 32*ew .. 32*ew+31
-    o("mad.lo.u32 %s, %s, 32, %s;", r("t").c_str(), r("ew").c_str(), r("lane").c_str());
-    o("add.u32 %s, %s, %s;", r("t").c_str(), r("t").c_str(), r("m0").c_str());
+    o("mad.lo.u32 %s, %s, 32, %s;", r("t").c_str(), r("ew").c_str(), r("m0").c_str());       // the warp's first row
     o("mul.wide.u32 %s, %s, %lld;", r("w").c_str(), r("t").c_str(), ldd * 2);
     o("add.u64 %s, %s, %s;", r("crow").c_str(), s.d_base.c_str(), r("w").c_str());
     o("mul.wide.u32 %s, %s, 2;", r("w").c_str(), r("n0").c_str());
     o("add.u64 %s, %s, %s;", r("crow").c_str(), r("crow").c_str(), r("w").c_str());
+    o("shr.u32 %s, %s, 3;", r("t").c_str(), r("lane").c_str());                               // reading back: row 4i + lane/8 ...
+    o("and.b32 %s, %s, 7;", r("u").c_str(), r("lane").c_str());                               // ... 16-byte unit lane%8
+    o("mul.wide.u32 %s, %s, %lld;", r("w").c_str(), r("t").c_str(), ldd * 2);
+    o("add.u64 %s, %s, %s;", r("crow").c_str(), r("crow").c_str(), r("w").c_str());
+    o("mul.wide.u32 %s, %s, 16;", r("w").c_str(), r("u").c_str());
+    o("add.u64 %s, %s, %s;", r("crow").c_str(), r("crow").c_str(), r("w").c_str());
+    o("mad.lo.u32 %s, %s, 4096, %s;", r("x").c_str(), r("ew").c_str(), r("tiles").c_str());
+    o("add.u32 %s, %s, %d;", r("x").c_str(), r("x").c_str(), 4 * STAGE_BYTES);                 // this warp's staging rows, past the four stages
+    for (int j = 0; j < 8; j++) {
+        o("xor.b32 %s, %s, %d;", r("g").c_str(), r("u").c_str(), j);
+        o("shl.b32 %s, %s, 4;", r("g").c_str(), r("g").c_str());
+        o("mad.lo.u32 %swo%d, %s, 128, %s;", P.c_str(), j, r("lane").c_str(), r("g").c_str());
+        o("add.u32 %swo%d, %swo%d, %s;", P.c_str(), j, P.c_str(), j, r("x").c_str());
+        o("add.u32 %s, %s, %d;", r("g").c_str(), r("t").c_str(), 4 * j);
+        o("and.b32 %s, %s, 7;", r("c").c_str(), r("g").c_str());
+        o("xor.b32 %s, %s, %s;", r("c").c_str(), r("c").c_str(), r("u").c_str());
+        o("shl.b32 %s, %s, 4;", r("c").c_str(), r("c").c_str());
+        o("mad.lo.u32 %sro%d, %s, 128, %s;", P.c_str(), j, r("g").c_str(), r("c").c_str());
+        o("add.u32 %sro%d, %sro%d, %s;", P.c_str(), j, P.c_str(), j, r("x").c_str());
+    }
     o("mad.lo.u32 %s, %s, 256, %s;", r("src").c_str(), r("buf").c_str(), r("tmem").c_str());
     o("shl.b32 %s, %s, 21;", r("t").c_str(), r("ew").c_str());
     o("add.u32 %s, %s, %s;", r("src").c_str(), r("src").c_str(), r("t").c_str());
@@ -881,16 +902,25 @@ bool matmul_tcgen05_persistent(const MmaSite& s, std::vector<std::string>* decls
     {
         std::string list;
         for (int i = 0; i < 32; i++) list += (i ? ", " : "") + P + "v" + std::to_string(i);
-        o("add.u32 %s, %s, %s;", r("x").c_str(), r("src").c_str(), r("c").c_str());
-        o("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%s}, [%s];", list.c_str(), r("x").c_str());
-        o("tcgen05.wait::ld.sync.aligned;");
-        for (int i = 0; i < 16; i++) o("cvt.rn.f16x2.f32 %sh%d, %sv%d, %sv%d;", P.c_str(), i, P.c_str(), 2 * i + 1, P.c_str(), 2 * i);
+        for (int half = 0; half < 2; half++) {
+            o("add.u32 %s, %s, %s;", r("x").c_str(), r("src").c_str(), r("c").c_str());
+            if (half) o("add.u32 %s, %s, 32;", r("x").c_str(), r("x").c_str());
+            o("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%s}, [%s];", list.c_str(), r("x").c_str());
+            o("tcgen05.wait::ld.sync.aligned;");
+            for (int i = 0; i < 16; i++) o("cvt.rn.f16x2.f32 %sh%d, %sv%d, %sv%d;", P.c_str(), i, P.c_str(), 2 * i + 1, P.c_str(), 2 * i);
+            for (int q = 0; q < 4; q++)
+                o("st.shared.v4.b32 [%swo%d], {%sh%d, %sh%d, %sh%d, %sh%d};", P.c_str(), 4 * half + q, P.c_str(), 4 * q, P.c_str(), 4 * q + 1, P.c_str(), 4 * q + 2, P.c_str(), 4 * q + 3);
+        }
+        o("bar.warp.sync 0xffffffff;");
+        for (int i = 0; i < 8; i++)
+            o("ld.shared.v4.b32 {%srb%d, %srb%d, %srb%d, %srb%d}, [%sro%d];", P.c_str(), 4 * i, P.c_str(), 4 * i + 1, P.c_str(), 4 * i + 2, P.c_str(), 4 * i + 3, P.c_str(), i);
+        o("bar.warp.sync 0xffffffff;");   // the next piece may overwrite the staging rows
         o("mul.wide.u32 %s, %s, 2;", r("z").c_str(), r("c").c_str());
         o("add.u64 %s, %s, %s;", r("z").c_str(), r("z").c_str(), r("crow").c_str());
-        for (int q = 0; q < 4; q++)
-            o("st.global.v4.b32 [%s+%d], {%sh%d, %sh%d, %sh%d, %sh%d};", r("z").c_str(), 16 * q, P.c_str(), 4 * q, P.c_str(), 4 * q + 1, P.c_str(), 4 * q + 2, P.c_str(), 4 * q + 3);
+        for (int i = 0; i < 8; i++)
+            o("st.global.v4.b32 [%s+%lld], {%srb%d, %srb%d, %srb%d, %srb%d};", r("z").c_str(), 4ll * i * ldd * 2, P.c_str(), 4 * i, P.c_str(), 4 * i + 1, P.c_str(), 4 * i + 2, P.c_str(), 4 * i + 3);
     }
-    o("add.u32 %s, %s, 32;", r("c").c_str(), r("c").c_str());
+    o("add.u32 %s, %s, 64;", r("c").c_str(), r("c").c_str());
     o("setp.lt.u32 %s, %s, %s;", r("p").c_str(), r("c").c_str(), r("width").c_str());
     o("@%s bra %se_c;", r("p").c_str(), L.c_str());
     o("tcgen05.fence::before_thread_sync;");
