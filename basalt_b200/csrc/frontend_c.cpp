@@ -5,7 +5,7 @@
 // __global__/__device__ qualifiers, scalar and pointer parameters, scalar locals, __shared__
 // arrays with constant extents, if/for/while/do, the C expression operators with the usual
 // arithmetic conversions, threadIdx/blockIdx/blockDim/gridDim, __syncthreads, warp shuffles and
-// votes (with or without the _sync mask), atomics, min/max, object- and function-like #define.  Anything else is
+// votes (with or without the _sync mask), atomics, min/max, object- and function-like #define, #if/#ifdef groups.  Anything else is
 // refused with E304 rather than guessed at.
 //
 // Differences from the reference's lowering (crates/basalt-sema/src/lower.rs), each deliberate:
@@ -63,10 +63,15 @@ public:
             if (p_ >= end_) break;
             if (*p_ == '#' && line_start) { directive(); continue; }
             line_start = false;
+            if (!active()) {   // inside a conditional group that is not taken: the text is skipped, line by line
+                while (p_ < end_ && *p_ != '\n') p_++;
+                continue;
+            }
             Token t = next();
             if (t.k == Tk::Ident) expand_into(t, &out, 0);
             else out.push_back(t);
         }
+        if (!conds_.empty()) fail("E202", line_, "unterminated #if");
         Token e;
         e.k = Tk::Eof;
         e.line = line_;
@@ -83,6 +88,44 @@ private:
     };
     std::map<std::string, std::vector<Token>> macros_;
     std::map<std::string, FnMacro> fn_macros_;
+    // #if / #ifdef / #ifndef nesting: whether the group is being taken, whether one of its branches has been
+    struct Cond { bool taking, taken, parent_active; };
+    std::vector<Cond> conds_;
+    bool active() const { return conds_.empty() || conds_.back().taking; }
+    bool defined(const std::string& n) const { return macros_.count(n) || fn_macros_.count(n); }
+    // the controlling expression of #if / #elif: an integer literal, NAME (its value if it is a literal macro),
+    // defined(NAME) / defined NAME, with a leading `!`
+    bool condition(std::string e, int line) {
+        size_t i = 0;
+        auto space = [&]() { while (i < e.size() && isspace((unsigned char)e[i])) i++; };
+        auto word = [&]() { size_t b = i; while (i < e.size() && (isalnum((unsigned char)e[i]) || e[i] == '_')) i++; return e.substr(b, i - b); };
+        bool neg = false;
+        for (space(); i < e.size() && e[i] == '!'; space()) { neg = !neg; i++; }
+        bool v = false;
+        if (i < e.size() && isdigit((unsigned char)e[i])) {
+            char* endp = nullptr;
+            v = strtoll(e.c_str() + i, &endp, 0) != 0;
+            i = (size_t)(endp - e.c_str());
+            while (i < e.size() && strchr("uUlL", e[i])) i++;
+        } else if (i < e.size() && (isalpha((unsigned char)e[i]) || e[i] == '_')) {
+            std::string w = word();
+            if (w == "defined") {
+                space();
+                const bool paren = i < e.size() && e[i] == '(';
+                if (paren) { i++; space(); }
+                std::string n = word();
+                if (n.empty()) fail("E201", line, "defined needs a name");
+                if (paren) { space(); if (i >= e.size() || e[i] != ')') fail("E201", line, "`)` expected after defined(" + n); i++; }
+                v = defined(n);
+            } else {
+                auto it = macros_.find(w);   // an undefined name counts as 0
+                v = it != macros_.end() && it->second.size() == 1 && it->second[0].k == Tk::Int && it->second[0].u != 0;
+            }
+        } else fail("E304", line, "this #if expression is outside the subset (a literal, a name or defined(NAME), with `!`)");
+        space();
+        if (i < e.size()) fail("E304", line, "this #if expression is outside the subset (a literal, a name or defined(NAME), with `!`)");
+        return neg ? !v : v;
+    }
 
     // Appends what the identifier `t` stands for: itself, the tokens of an object-like macro, or, when it names
     // a function-like macro and a `(` follows, the macro's body with each parameter replaced by the tokens of
@@ -155,7 +198,43 @@ private:
         size_t j = i;
         while (j < text.size() && isalpha((unsigned char)text[j])) j++;
         std::string name = text.substr(i, j - i);
+        const std::string rest = text.substr(j);
+        if (name == "ifdef" || name == "ifndef" || name == "if") {
+            const bool parent = active();
+            bool take = false;
+            if (parent) {
+                if (name == "if") take = condition(rest, line);
+                else {
+                    std::string n = rest;
+                    while (!n.empty() && isspace((unsigned char)n.front())) n.erase(n.begin());
+                    while (!n.empty() && isspace((unsigned char)n.back())) n.pop_back();
+                    if (n.empty()) fail("E201", line, "#" + name + " needs a name");
+                    take = defined(n) == (name == "ifdef");
+                }
+            }
+            conds_.push_back({take, take, parent});
+            return;
+        }
+        if (name == "elif" || name == "else" || name == "endif") {
+            if (conds_.empty()) fail("E201", line, "#" + name + " without #if");
+            Cond& c = conds_.back();
+            if (name == "endif") { conds_.pop_back(); return; }
+            const bool take = c.parent_active && !c.taken && (name == "else" || condition(rest, line));
+            c.taking = take;
+            c.taken = c.taken || take;
+            return;
+        }
+        if (!active()) return;
         if (name == "include" || name == "pragma" || name.empty()) return;
+        if (name == "undef") {
+            std::string n = rest;
+            while (!n.empty() && isspace((unsigned char)n.front())) n.erase(n.begin());
+            while (!n.empty() && isspace((unsigned char)n.back())) n.pop_back();
+            macros_.erase(n);
+            fn_macros_.erase(n);
+            return;
+        }
+        if (name == "error") fail("E304", line, "#error" + rest);
         if (name != "define") fail("E304", line, "preprocessor directive `#" + name + "` is outside the subset");
         while (j < text.size() && isspace((unsigned char)text[j])) j++;
         size_t k = j;

@@ -429,3 +429,49 @@ __global__ void k(const unsigned *a, const unsigned *d, unsigned *q, unsigned *r
     with pytest.raises(b.Diag) as e:
         b.compile_cuda("__global__ void k(unsigned long *o) { o[0] = o[1] / 3ul; }")
     assert e.value.code == "E304"
+
+
+def test_conditional_groups():
+    # #ifdef / #ifndef / #if / #elif / #else / #endif / #undef: untaken groups are skipped as text (they need not lex)
+    src = """
+#ifndef SCALE
+#define SCALE 3
+#endif
+#define FAST 1
+#ifdef NEVER
+this is not C at all @@@
+#elif 0
+#define OFFSET 99
+#else
+#define OFFSET 10
+#endif
+#if FAST
+#define STEP(x) ((x) * SCALE)
+#else
+#define STEP(x) (x)
+#endif
+#if !defined(OFFSET)
+#error no offset
+#endif
+#undef FAST
+#ifdef FAST
+#define OFFSET2 1000
+#else
+#define OFFSET2 0
+#endif
+__global__ void k(const int *in, int *out, int n) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = STEP(in[i]) + OFFSET + OFFSET2;
+}
+"""
+    bir = b.compile_cuda(src)
+    n = 64
+    x = np.arange(n, dtype=np.int32); out = np.zeros(n, np.int32)
+    run_kernel(bir, "k", [x, out, n], n)
+    assert np.array_equal(out, x * 3 + 10)
+    for bad, code in (("#ifdef A\n__global__ void k(int*o){}\n", "E202"), ("#endif\n__global__ void k(int*o){}", "E201"),
+                      ("#if 1+1\n#endif\n__global__ void k(int*o){}", "E304"), ("#if defined(A) && 0\n#endif\n__global__ void k(int*o){}", "E304"),
+                      ("#ifndef A\n#error A is required\n#endif\n__global__ void k(int*o){}", "E304")):
+        with pytest.raises(b.Diag) as e:
+            b.compile_cuda(bad)
+        assert e.value.code == code, e.value
