@@ -1205,8 +1205,13 @@ bool vectorize_elementwise(Function& F, int max_unroll, OptReport* rep, Function
             if (a.esz != esz || (esz != 4 && esz != 8) || in.align < esz) return false;
             max_esz = std::max(max_esz, esz);
             addr_of[id] = a;
-            if (in.op == Opc::Load) { kind[id] = LoadK; nloads++; }
-            else {
+            if (in.op == Opc::Load) {
+                // The rewritten body issues every load before any store.  A load that follows a store
+                // may read what this thread just wrote (the same element in place, or through a second
+                // parameter naming the same buffer), so such a body keeps its scalar form.
+                if (nstores > 0) return false;
+                kind[id] = LoadK; nloads++;
+            } else {
                 bool lane = false;
                 if (!lane_or_uniform(in.ops[1], &lane)) return false;
                 kind[id] = StoreK; nstores++;

@@ -138,3 +138,37 @@ def test_shared_slots_and_address_taken_slots_stay_in_memory(ptx):
 """)
     opt = ptx.optimized_bir(src, b.EmitOpts(opt_level=0))
     assert "ptr.shared" in opt and "ptr.local" in opt   # CTA-visible memory and an indexed local are not SSA values
+
+
+IN_PLACE_SOURCE = """
+__global__ void in_place(int* a, int* c, int n) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) { a[i] = a[i] + a[i]; c[i] = a[i]; }
+}
+__global__ void two_names(const int* a, int* b, int* c, int n) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) { b[i] = 2 * a[i]; c[i] = a[i]; }
+}
+"""
+
+
+def test_a_load_after_a_store_is_not_hoisted_above_it(ptx):
+    # The vectorised body issues all loads first; a body that reads back what it has just stored
+    # (the same element, or the same buffer under a second parameter) must keep program order.
+    src = b.compile_cuda(IN_PLACE_SOURCE)
+    opt = ptx.optimized_bir(src)
+    for n, threads in [(4, 4), (1000, 1024), (37, 64), (100, 40)]:
+        a0 = np.arange(1, max(n, 1) + 9, dtype=np.int32); a1 = a0.copy()
+        c0 = np.full_like(a0, -1); c1 = c0.copy()
+        run_kernel(src, "in_place", [a0, c0, n], threads)
+        run_kernel(opt, "in_place", [a1, c1, n], threads)
+        assert np.array_equal(a0, a1) and np.array_equal(c0, c1), (n, threads)
+        m = min(n, threads)
+        assert np.array_equal(c0[:m], 2 * np.arange(1, m + 1))
+        # one buffer passed as input and as output
+        x0 = np.arange(1, max(n, 1) + 9, dtype=np.int32); x1 = x0.copy()
+        d0 = np.full_like(x0, -1); d1 = d0.copy()
+        run_kernel(src, "two_names", [x0, x0, d0, n], threads)
+        run_kernel(opt, "two_names", [x1, x1, d1, n], threads)
+        assert np.array_equal(x0, x1) and np.array_equal(d0, d1), (n, threads)
+        assert np.array_equal(d0[:m], 2 * np.arange(1, m + 1))
