@@ -66,6 +66,7 @@ def _load() -> C.CDLL:
         "basalt_rt_host_alloc": (C.c_int, [vp, sz, P(vp)]),
         "basalt_rt_host_free": (None, [vp, vp]),
         "basalt_rt_launch": (C.c_int, [vp, C.c_uint32 * 3, C.c_uint32 * 3, C.c_uint32, vp, P(vp)]),
+        "basalt_rt_launch_gather": (C.c_int, [vp, C.c_uint32 * 3, C.c_uint32 * 3, C.c_uint32, vp, P(vp), P(u64), C.c_int]),
         "basalt_rt_planned_geometry": (C.c_int, [vp, P(vp), C.c_uint32 * 3, C.c_uint32 * 3, P(C.c_uint32)]),
         "basalt_rt_ctx_sync": (C.c_int, [vp]),
         "basalt_rt_kernel_status": (C.c_int, [vp, i32p]),
@@ -106,6 +107,8 @@ def _load() -> C.CDLL:
         "basalt_k_sgemm_f32_static_workspace": (C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, vp]),
         "basalt_k_matmul_f16": (C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, vp, vp]),
         "basalt_k_matmul_f16_allgather": (C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, P(vp), C.c_int, vp, vp]),
+        "basalt_k_fill": (C.c_int, [C.c_int, u64, u64, i64, vp, vp]),
+        "basalt_k_matmul_f16_variant": (C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, P(vp), C.c_int, vp, vp]),
         "basalt_k_max_i32_allreduce": (C.c_int, [vp, i64, vp, P(u64), C.c_int, C.c_int, C.c_uint32, vp, vp, vp, u64, vp]),
         "basalt_k_peer_allreduce_max_i32": (C.c_int, [P(u64), C.c_int, C.c_int, C.c_uint32, vp, vp, vp, u64, C.c_int, C.c_int32, vp]),
     }

@@ -100,6 +100,15 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
         s.extra_params->push_back(".param .u32 " + s.kernel + "_split");
         s.extra_params->push_back(".param .u64 " + s.kernel + "_workspace");
         s.extra_params->push_back(".param .u64 " + s.kernel + "_tickets");
+        // the fused gather: the result matrix's base address on up to seven peers, and how many are set
+        s.extra_params->push_back(".param .align 8 .b8 " + s.kernel + "_peers[56]");
+        s.extra_params->push_back(".param .u32 " + s.kernel + "_npeers");
+        snprintf(d, sizeof d, "\t.reg .b32 %%mm%d_np, %%mm%d_pi;", u, u);
+        decls->push_back(d);
+        snprintf(d, sizeof d, "\t.reg .b64 %%mm%d_pb, %%mm%d_pz, %%mm%d_pq;", u, u, u);
+        decls->push_back(d);
+        snprintf(d, sizeof d, "\t.reg .pred %%mm%d_pk;", u);
+        decls->push_back(d);
     }
     snprintf(d, sizeof d, "\t.shared .align 16 .b8 __mm%d_as[16384];", u);
     decls->push_back(d);
@@ -314,11 +323,36 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
         o("st.global.v2.b64 [%s+%lld], {%s, %s};", cp.c_str(), rowoff, acc2(i * 4).c_str(), acc2(i * 4 + 1).c_str());
         o("st.global.v2.b64 [%s+%lld], {%s, %s};", cp.c_str(), rowoff + 256, acc2(i * 4 + 2).c_str(), acc2(i * 4 + 3).c_str());
     }
+    if (tail) {
+        // the fused gather: the finished tile goes to the same offset behind every peer's base address (256
+        // contiguous bytes per row and warp instruction), then a system-scope fence before the CTA can end
+        const std::string np = R("np"), pi = R("pi"), pb = R("pb"), pz = R("pz"), pq = R("pq"), pk = R("pk");
+        std::string l_peer = "$mm" + std::to_string(u) + "_peer";
+        o("ld.param.u32 %s, [%s_npeers];", np.c_str(), s.kernel.c_str());
+        o("setp.eq.u32 %s, %s, 0;", pk.c_str(), np.c_str());
+        o("@%s bra %s;", pk.c_str(), l_skip.c_str());
+        o("sub.u64 %s, %s, %s;", pq.c_str(), cp.c_str(), s.d_base.c_str());
+        o("mov.u32 %s, 0;", pi.c_str());
+        o("mov.b64 %s, %s_peers;", pb.c_str(), s.kernel.c_str());
+        o.label(l_peer);
+        o("ld.param.u64 %s, [%s];", pz.c_str(), pb.c_str());
+        o("add.u64 %s, %s, %s;", pz.c_str(), pz.c_str(), pq.c_str());
+        for (int i = 0; i < 4 * RG; i++) {
+            long long rowoff = ((i & 3) + (i >> 2) * SP) * ldd * 4;
+            o("st.global.v2.b64 [%s+%lld], {%s, %s};", pz.c_str(), rowoff, acc2(i * 4).c_str(), acc2(i * 4 + 1).c_str());
+            o("st.global.v2.b64 [%s+%lld], {%s, %s};", pz.c_str(), rowoff + 256, acc2(i * 4 + 2).c_str(), acc2(i * 4 + 3).c_str());
+        }
+        o("add.u64 %s, %s, 8;", pb.c_str(), pb.c_str());
+        o("add.u32 %s, %s, 1;", pi.c_str(), pi.c_str());
+        o("setp.lt.u32 %s, %s, %s;", pk.c_str(), pi.c_str(), np.c_str());
+        o("@%s bra %s;", pk.c_str(), l_peer.c_str());
+        o("fence.acq_rel.sys;");
+    }
     o.label(l_skip);
     o("bar.sync 0;");
     char pl[256];
     if (wide && s.maxntid) *s.maxntid = (unsigned)NT;
-    if (tail) snprintf(pl, sizeof pl, "//!basalt.plan %s logical_block=256,1,1 block=%d,1,1 params=%u tail=%u", s.kernel.c_str(), NT, s.nparams, in.k);
+    if (tail) snprintf(pl, sizeof pl, "//!basalt.plan %s logical_block=256,1,1 block=%d,1,1 params=%u tail=%u gather=%d", s.kernel.c_str(), NT, s.nparams, in.k, s.d_param);
     else snprintf(pl, sizeof pl, "//!basalt.plan %s block=256,1,1 params=%u", s.kernel.c_str(), s.nparams);
     plan->push_back(pl);
     return true;
@@ -611,7 +645,7 @@ bool matmul_tcgen05_persistent(const MmaSite& s, std::vector<std::string>* decls
     b32 += P + "h<16>, " + P + "v<32>, " + P + "wo<8>, " + P + "ro<8>, " + P + "rb<32>;";
     decls->push_back(b32);
     std::string b64 = "\t.reg .b64 ";
-    for (const char* n : {"w", "da", "db", "t0", "now", "dt", "crow", "status", "ma", "mb"}) b64 += P + n + ", ";
+    for (const char* n : {"w", "da", "db", "t0", "now", "dt", "crow", "status", "ma", "mb", "pb", "pz", "pq"}) b64 += P + n + ", ";
     b64 += P + "z;";
     decls->push_back(b64);
     std::string pr = "\t.reg .pred ";
@@ -945,8 +979,8 @@ bool matmul_tcgen05_persistent(const MmaSite& s, std::vector<std::string>* decls
     o.label(L + "skip");
     char pl[640];
     snprintf(pl, sizeof pl,
-             "//!basalt.plan %s logical_block=128,1,1 block=192,1,1 smem=%u params=%u tmap=%d:2:%lld:%lld:64:128:128 tmap=%d:2:%lld:%lld:64:%d:128 status=1 lgrid=2 pair=%s__pair",
-             s.kernel.c_str(), smem, s.nparams, s.a_param, lda, lda * 2, s.b_param, ldb, ldb * 2, b_nk ? 128 : 64, s.kernel.c_str());
+             "//!basalt.plan %s logical_block=128,1,1 block=192,1,1 smem=%u params=%u tmap=%d:2:%lld:%lld:64:128:128 tmap=%d:2:%lld:%lld:64:%d:128 status=1 lgrid=2 pair=%s__pair gather=%d",
+             s.kernel.c_str(), smem, s.nparams, s.a_param, lda, lda * 2, s.b_param, ldb, ldb * 2, b_nk ? 128 : 64, s.kernel.c_str(), s.d_param);
     plan->push_back(pl);
     return true;
 }
@@ -983,17 +1017,17 @@ bool matmul_tcgen05_pair(const MmaSite& s, std::vector<std::string>* decls, std:
     std::string b32 = "\t.reg .b32 ";
     for (const char* n : {"tid", "warp", "lane", "t", "u", "tiles", "bars", "slot", "gu", "tmem", "ok", "kb", "s", "ph", "par", "full", "empty", "fb", "adst", "bdst", "m0", "n0",
                           "x", "it", "g", "lgx", "lgy", "tm", "tn", "ntiles", "perband", "band", "first", "rows", "rr", "mi", "nj", "tile", "gstep", "local",
-                          "buf", "use", "bar2", "acc", "ew", "c", "src", "spin", "rank", "zero", "idesc"})
+                          "buf", "use", "bar2", "acc", "ew", "c", "src", "spin", "rank", "zero", "idesc", "np", "pi"})
         b32 += P + n + ", ";
     b32 += P + "h<16>, " + P + "v<32>, " + P + "wo<8>, " + P + "ro<8>, " + P + "rb<32>;";
     decls->push_back(b32);
     std::string b64 = "\t.reg .b64 ";
-    for (const char* n : {"w", "da", "db", "t0", "now", "dt", "crow", "status", "ma", "mb"}) b64 += P + n + ", ";
+    for (const char* n : {"w", "da", "db", "t0", "now", "dt", "crow", "status", "ma", "mb", "pb", "pz", "pq"}) b64 += P + n + ", ";
     b64 += P + "z;";
     decls->push_back(b64);
     decls->push_back("\t.reg .b16 " + P + "both;");
     std::string pr = "\t.reg .pred ";
-    for (const char* n : {"p", "q", "w0", "w1", "l0", "prod", "mma", "epi", "accp", "done", "all", "lead"}) pr += P + n + ", ";
+    for (const char* n : {"p", "q", "w0", "w1", "l0", "prod", "mma", "epi", "accp", "done", "all", "lead", "pk"}) pr += P + n + ", ";
     pr += P + "unused;";
     decls->push_back(pr);
     char d[256];
@@ -1009,6 +1043,11 @@ bool matmul_tcgen05_pair(const MmaSite& s, std::vector<std::string>* decls, std:
     s.extra_params->push_back(".param .u64 " + stp);
     s.extra_params->push_back(".param .u32 " + pgx);
     s.extra_params->push_back(".param .u32 " + pgy);
+    // the fused gather: base addresses of the same result matrix in up to seven peers' memory (the output
+    // parameter's value on each peer, mapped into this GPU's address space) and how many of them are set
+    const std::string ppeers = s.kernel + "_peers", pnpeers = s.kernel + "_npeers";
+    s.extra_params->push_back(".param .align 8 .b8 " + ppeers + "[56]");
+    s.extra_params->push_back(".param .u32 " + pnpeers);
     *s.maxntid = 192;
     *s.cluster = 2;
     Out o{lines};
@@ -1082,6 +1121,7 @@ bool matmul_tcgen05_pair(const MmaSite& s, std::vector<std::string>* decls, std:
     o("ld.param.u64 %s, [%s];", r("status").c_str(), stp.c_str());
     o("ld.param.u32 %s, [%s];", r("lgx").c_str(), pgx.c_str());
     o("ld.param.u32 %s, [%s];", r("lgy").c_str(), pgy.c_str());
+    o("ld.param.u32 %s, [%s];", r("np").c_str(), pnpeers.c_str());
     o("mov.b64 %s, %s;", r("ma").c_str(), ta.c_str());
     o("cvta.param.u64 %s, %s;", r("ma").c_str(), r("ma").c_str());
     o("mov.b64 %s, %s;", r("mb").c_str(), tb.c_str());
@@ -1305,6 +1345,23 @@ bool matmul_tcgen05_pair(const MmaSite& s, std::vector<std::string>* decls, std:
         o("add.u64 %s, %s, %s;", r("z").c_str(), r("z").c_str(), r("crow").c_str());
         for (int i = 0; i < 8; i++)
             o("st.global.v4.b32 [%s+%lld], {%srb%d, %srb%d, %srb%d, %srb%d};", r("z").c_str(), 4ll * i * ldd * 2, P.c_str(), 4 * i, P.c_str(), 4 * i + 1, P.c_str(), 4 * i + 2, P.c_str(), 4 * i + 3);
+        // the fused gather: the same lines at the same offset behind every peer's base address, over NVLink,
+        // while the next tile's main loop runs on the tensor pipe
+        o("setp.eq.u32 %s, %s, 0;", r("pk").c_str(), r("np").c_str());
+        o("@%s bra %se_peers_done;", r("pk").c_str(), L.c_str());
+        o("sub.u64 %s, %s, %s;", r("pq").c_str(), r("z").c_str(), s.d_base.c_str());   // offset of this lane's first line in the result
+        o("mov.u32 %s, 0;", r("pi").c_str());
+        o("mov.b64 %s, %s;", r("pb").c_str(), ppeers.c_str());
+        o.label(L + "e_peer");
+        o("ld.param.u64 %s, [%s];", r("pz").c_str(), r("pb").c_str());
+        o("add.u64 %s, %s, %s;", r("pz").c_str(), r("pz").c_str(), r("pq").c_str());
+        for (int i = 0; i < 8; i++)
+            o("st.global.v4.b32 [%s+%lld], {%srb%d, %srb%d, %srb%d, %srb%d};", r("pz").c_str(), 4ll * i * ldd * 2, P.c_str(), 4 * i, P.c_str(), 4 * i + 1, P.c_str(), 4 * i + 2, P.c_str(), 4 * i + 3);
+        o("add.u64 %s, %s, 8;", r("pb").c_str(), r("pb").c_str());
+        o("add.u32 %s, %s, 1;", r("pi").c_str(), r("pi").c_str());
+        o("setp.lt.u32 %s, %s, %s;", r("pk").c_str(), r("pi").c_str(), r("np").c_str());
+        o("@%s bra %se_peer;", r("pk").c_str(), L.c_str());
+        o.label(L + "e_peers_done");
     }
     o("add.u32 %s, %s, 64;", r("c").c_str(), r("c").c_str());
     o("setp.lt.u32 %s, %s, 256;", r("p").c_str(), r("c").c_str());
@@ -1324,6 +1381,8 @@ bool matmul_tcgen05_pair(const MmaSite& s, std::vector<std::string>* decls, std:
     o("mov.u32 %s, 1;", r("t").c_str());
     o("atom.global.exch.b32 %s, [%s], %s;", r("g").c_str(), r("status").c_str(), r("t").c_str());
     o.label(L + "status_done");
+    o("setp.ne.u32 %s, %s, 0;", r("pk").c_str(), r("np").c_str());
+    o("@%s fence.acq_rel.sys;", r("pk").c_str());   // this thread's stores into peer memory are performed before the kernel can end
     o("bar.warp.sync 0xffffffff;");
     o("tcgen05.fence::before_thread_sync;");
     o("bar.sync 0;");

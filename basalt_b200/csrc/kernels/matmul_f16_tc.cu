@@ -375,8 +375,20 @@ __global__ void __launch_bounds__(THREADS2, 1) matmul_f16_tc_persistent(const __
 // Every wait is bounded as in the other kernels; the pair meets at a cluster barrier before tensor
 // memory is released, so neither CTA leaves while the other may still name its barriers or memory.
 namespace v3 {
-constexpr int TM = 256, TN = 256, HALF_N = 128, STAGES = 6, THREADS3 = 192;
+constexpr int TM = 256, TN = 256, HALF_N = 128, THREADS3 = 192;
 constexpr int B_HALF_BYTES = HALF_N * BK * 2, STAGE_BYTES3 = A_BYTES + B_HALF_BYTES;   // 16 KB + 16 KB
+// How the epilogue leaves the SM.
+//   DIRECT  16-byte pieces straight from the registers tcgen05.ld filled (a lane holds one row);
+//   LINES   each 32-row x 64-column piece is transposed through shared memory and stored by the warp as
+//           whole 128-byte lines (and, in the fused gather, again into every peer's buffer);
+//   BULK    the piece is written to shared memory in the 128-byte-swizzled layout and one lane hands it
+//           to the copy engine of the SM as bulk-tensor stores (cp.async.bulk.tensor, shared -> global),
+//           one per destination: the warp goes straight back to tensor memory while the stores drain.
+enum Epilogue { DIRECT = 0, LINES = 1, BULK = 2 };
+constexpr int PIECE_BYTES = 32 * 128;   // 32 rows x 64 columns of f16
+// ring depth of the K-slab stages and staging pieces per epilogue warp: everything fits 227 KB
+__host__ __device__ constexpr int stages_of(int epi, bool deep) { return epi == BULK && deep ? 5 : 6; }
+__host__ __device__ constexpr int pieces_of(int epi, bool deep) { return epi == DIRECT ? 0 : epi == LINES ? 1 : deep ? 4 : 2; }
 constexpr int GROUP_M = 8;
 constexpr uint32_t TMEM_COLS3 = 512;
 
@@ -432,17 +444,26 @@ struct PeerRows {
     __half* c[BASALT_K_MAX_PEERS - 1];
     int n;
 };
+// BULK: tensor maps of the result rows, this GPU's first, then the same rows in each peer's buffer
+// (box: 64 columns x 32 rows, 128-byte swizzle)
+struct StoreMaps {
+    CUtensorMap c[BASALT_K_MAX_PEERS];
+    int n;
+};
 
-constexpr int STAGING_BYTES = 4 * 32 * 128;   // STAGED: 32 rows x 64 columns of f16 for each of the four epilogue warps
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+}
 
-// STAGED: the epilogue transposes each 32-row x 64-column piece through shared memory so that a warp's store
-// instruction writes four whole 128-byte lines instead of 32 separate 16-byte pieces of 32 different rows.
-// Over NVLink that is the difference between a line-sized and a 16-byte write per request, which is why the
-// fused gather (PUSH) needs it.
-template <bool B_IS_NK, bool PUSH, bool STAGED>
+// Over NVLink the difference between LINES and DIRECT is a line-sized against a 16-byte write per request,
+// which is why the fused gather needs at least LINES; BULK also takes the copies off the warps.
+template <bool B_IS_NK, int EPI, bool DEEP>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS3, 1)
     matmul_f16_tc_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, __half* __restrict__ C, int M, int N, int K,
-                       int32_t* status, const PeerRows peers) {
+                       int32_t* status, const PeerRows peers, const __grid_constant__ StoreMaps out) {
+    constexpr int STAGES = stages_of(EPI, DEEP), PIECES = pieces_of(EPI, DEEP);
+    constexpr bool STAGED = EPI == LINES;
+    const bool PUSH = peers.n > 0;
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], tfull_bar[2], tempty_bar[2];
     __shared__ uint32_t tmem_slot;
@@ -536,7 +557,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS3, 1)
         }
     } else {
         const int ew = warp & 3;
-        uint32_t local = 0;
+        uint32_t local = 0, piece = 0;
+        (void)piece;
         for (int t = pair; t < num_tiles && ok; t += pairs, local++) {
             int mi, ni;
             tile_coords(t, tiles_m, tiles_n, &mi, &ni);
@@ -548,6 +570,53 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS3, 1)
             const size_t tile_off = (size_t)(mi * TM + (int)rank * BM + ew * 32 + lane) * N + (size_t)ni * TN;
             __half* crow = C + tile_off;
             const uint32_t src = tmem_base + buf * TN + ((uint32_t)(ew * 32) << 16);
+            if constexpr (EPI == BULK) {
+                const uint32_t ring = tiles + STAGES * STAGE_BYTES3 + ew * (PIECES * PIECE_BYTES);   // 1 KB aligned: the swizzle is a function of the address
+                const int y = mi * TM + (int)rank * BM + ew * 32;
+#pragma unroll 1
+                for (int c = 0; c < TN; c += 64, piece++) {
+                    const uint32_t stg = ring + (piece % PIECES) * PIECE_BYTES;
+                    // the stores that last read this piece of the ring have finished reading it
+                    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(PIECES - 1) : "memory");
+                    __syncwarp();
+#pragma unroll
+                    for (int half = 0; half < 2; half++) {
+                        uint32_t r[32];
+                        asm volatile(
+                            "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+                              "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+                              "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]),
+                              "=r"(r[30]), "=r"(r[31])
+                            : "r"(src + (uint32_t)(c + 32 * half)));
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                        for (int q = 0; q < 4; q++) {   // 16-byte unit 4*half + q of row `lane`, where the 128-byte swizzle puts it
+                            uint32_t h[4];
+#pragma unroll
+                            for (int i = 0; i < 4; i++) {
+                                __half2 v = __floats2half2_rn(__uint_as_float(r[8 * q + 2 * i]), __uint_as_float(r[8 * q + 2 * i + 1]));
+                                h[i] = *reinterpret_cast<uint32_t*>(&v);
+                            }
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stg + lane * 128 + (((4 * half + q) ^ (lane & 7)) << 4)), "r"(h[0]), "r"(h[1]),
+                                         "r"(h[2]), "r"(h[3])
+                                         : "memory");
+                        }
+                    }
+                    if (c + 64 == TN) {   // the accumulator is drained: the MMA warp may overwrite it while the stores go out
+                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the copy engine reads what the warp wrote
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (c + 64 == TN) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[buf]), 0));
+                        for (int d = 0; d < out.n; d++) tma_store_2d(&out.c[d], stg, ni * TN + c, y);
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+                }
+                continue;
+            }
             if (STAGED) {
                 uint8_t* stg = smem_raw + (tiles - smem_u32(smem_raw)) + STAGES * STAGE_BYTES3 + ew * (32 * 128);
                 const size_t warp_off = (size_t)(mi * TM + (int)rank * BM + ew * 32) * N + (size_t)ni * TN;   // the warp's first row
@@ -630,6 +699,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS3, 1)
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[buf]), 0));
         }
+        if (EPI == BULK && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // every bulk store of this warp is complete
         if (PUSH) __threadfence_system();   // this thread's peer stores are performed before the kernel can end
     }
     if (!ok && status) atomicExch(status, 1);
@@ -700,10 +770,11 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, __half* C, i
 }
 
 
-template <bool B_IS_NK, bool PUSH, bool STAGED>
-int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, __half* C, int M, int N, int K, int32_t* status, cudaStream_t s, const v3::PeerRows& peers) {
-    constexpr int smem = v3::STAGES * v3::STAGE_BYTES3 + 1024 + (STAGED ? v3::STAGING_BYTES : 0);
-    auto kern = v3::matmul_f16_tc_pair<B_IS_NK, PUSH, STAGED>;
+template <bool B_IS_NK, int EPI, bool DEEP>
+int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, __half* C, int M, int N, int K, int32_t* status, cudaStream_t s, const v3::PeerRows& peers,
+                const v3::StoreMaps& out) {
+    constexpr int smem = v3::stages_of(EPI, DEEP) * v3::STAGE_BYTES3 + 1024 + 4 * v3::pieces_of(EPI, DEEP) * v3::PIECE_BYTES;
+    auto kern = v3::matmul_f16_tc_pair<B_IS_NK, EPI, DEEP>;
     static int max_pairs = 0;
     if (!max_pairs) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -719,29 +790,64 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, __half* C, int M, 
     }
     const int tiles = (M / v3::TM) * (N / v3::TN);
     const int pairs = tiles < max_pairs ? tiles : max_pairs;
-    kern<<<2 * pairs, v3::THREADS3, smem, s>>>(ma, mb, C, M, N, K, status, peers);
+    kern<<<2 * pairs, v3::THREADS3, smem, s>>>(ma, mb, C, M, N, K, status, peers, out);
     return basalt_k::record(cudaGetLastError(), "matmul_f16");
 }
 
-}  // namespace
+// Row-major f16 result rows -> tensor map for the BULK epilogue's stores (box 64 columns x 32 rows).
+int make_store_maps(v3::StoreMaps* out, void* C, void* const* peer_c, int n_peers, int M, int N) {
+    out->n = 1 + n_peers;
+    int rc = make_map(&out->c[0], C, (uint64_t)M, (uint64_t)N, 64, 32);
+    for (int i = 0; i < n_peers && !rc; i++) rc = make_map(&out->c[1 + i], peer_c[i], (uint64_t)M, (uint64_t)N, 64, 32);
+    return rc;
+}
 
-extern "C" int basalt_k_matmul_f16(const void* A, const void* B, void* C, int M, int N, int K, int b_is_nk, int32_t* status, void* stream) {
+template <bool B_IS_NK>
+int launch_pair_variant(int variant, const CUtensorMap& ma, const CUtensorMap& mb, void* C, int M, int N, int K, int32_t* status, cudaStream_t s,
+                        void* const* peer_c, int n_peers) {
+    v3::PeerRows peers = {};
+    peers.n = n_peers;
+    for (int i = 0; i < n_peers; i++) peers.c[i] = (__half*)peer_c[i];
+    if (variant == BASALT_K_MATMUL_PAIR_DIRECT) return launch_pair<B_IS_NK, v3::DIRECT, false>(ma, mb, (__half*)C, M, N, K, status, s, peers, v3::StoreMaps{});
+    if (variant == BASALT_K_MATMUL_PAIR_LINES) return launch_pair<B_IS_NK, v3::LINES, false>(ma, mb, (__half*)C, M, N, K, status, s, peers, v3::StoreMaps{});
+    v3::StoreMaps out = {};
+    int rc = make_store_maps(&out, C, peer_c, n_peers, M, N);
+    if (rc) return rc;
+    peers.n = 0;   // the bulk stores carry the peers' copies
+    if (variant == BASALT_K_MATMUL_PAIR_BULK) return launch_pair<B_IS_NK, v3::BULK, false>(ma, mb, (__half*)C, M, N, K, status, s, peers, out);
+    return launch_pair<B_IS_NK, v3::BULK, true>(ma, mb, (__half*)C, M, N, K, status, s, peers, out);
+}
+
+int matmul_f16_any(const void* A, const void* B, void* C, int M, int N, int K, int b_is_nk, int variant, void* const* peer_c, int n_peers, int32_t* status,
+                   void* stream, const char* who) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
-    if (M % BM || N % BN || K % BK) return basalt_k::record_msg(1, "matmul_f16", "M and N must be multiples of 128 and K of 64");
-    if (((uintptr_t)A | (uintptr_t)B | (uintptr_t)C) & 15) return basalt_k::record_msg(1, "matmul_f16", "matrices must be 16-byte aligned");
+    if (M % BM || N % BN || K % BK) return basalt_k::record_msg(1, who, "M and N must be multiples of 128 and K of 64");
+    if (n_peers < 0 || n_peers > BASALT_K_MAX_PEERS - 1 || (n_peers && !peer_c)) return basalt_k::record_msg(1, who, "bad peer list");
+    uintptr_t all = (uintptr_t)A | (uintptr_t)B | (uintptr_t)C;
+    for (int i = 0; i < n_peers; i++) all |= (uintptr_t)peer_c[i];
+    if (all & 15) return basalt_k::record_msg(1, who, "matrices must be 16-byte aligned");
+    const bool pair_shape = M % v3::TM == 0 && N % v3::TN == 0;
+    if (variant == BASALT_K_MATMUL_AUTO) {
+        if (n_peers) variant = BASALT_K_MATMUL_PAIR_BULK_DEEP;
+        else if (pair_shape) variant = BASALT_K_MATMUL_PAIR_LINES;
+        else variant = N % v2::BN2 == 0 ? BASALT_K_MATMUL_ONE_SM_256 : BASALT_K_MATMUL_ONE_CTA_128;
+    }
+    if (variant < BASALT_K_MATMUL_ONE_CTA_128 || variant > BASALT_K_MATMUL_PAIR_BULK_DEEP) return basalt_k::record_msg(1, who, "unknown variant");
+    const bool is_pair = variant >= BASALT_K_MATMUL_PAIR_DIRECT;
+    if (is_pair && !pair_shape) return basalt_k::record_msg(1, who, "the CTA-pair kernels need M and N to be multiples of 256");
+    if (!is_pair && n_peers) return basalt_k::record_msg(1, who, "only the CTA-pair kernels store to peers");
+    if (variant == BASALT_K_MATMUL_ONE_SM_256 && N % v2::BN2) return basalt_k::record_msg(1, who, "the 128x256 kernel needs N to be a multiple of 256");
     CUtensorMap ma, mb;
     int rc = make_map(&ma, A, (uint64_t)M, (uint64_t)K, BK, BM);
     if (rc) return rc;
     cudaStream_t s = (cudaStream_t)stream;
-    if (M % v3::TM == 0 && N % v3::TN == 0 && !getenv("BASALT_K_MATMUL_NO_PAIR")) {   // 256 x 256 tiles on pairs of SMs
+    if (is_pair) {   // 256 x 256 tiles on pairs of SMs
         rc = b_is_nk ? make_map(&mb, B, (uint64_t)N, (uint64_t)K, BK, v3::HALF_N) : make_map(&mb, B, (uint64_t)K, (uint64_t)N, 64, BK);
         if (rc) return rc;
-        const v3::PeerRows none = {};
-        if (getenv("BASALT_K_MATMUL_DIRECT_EPILOGUE"))   // A/B switch: 16-byte pieces straight from the registers (1.3 % slower at 8192^3)
-            return b_is_nk ? launch_pair<true, false, false>(ma, mb, (__half*)C, M, N, K, status, s, none) : launch_pair<false, false, false>(ma, mb, (__half*)C, M, N, K, status, s, none);
-        return b_is_nk ? launch_pair<true, false, true>(ma, mb, (__half*)C, M, N, K, status, s, none) : launch_pair<false, false, true>(ma, mb, (__half*)C, M, N, K, status, s, none);
+        return b_is_nk ? launch_pair_variant<true>(variant, ma, mb, C, M, N, K, status, s, peer_c, n_peers)
+                       : launch_pair_variant<false>(variant, ma, mb, C, M, N, K, status, s, peer_c, n_peers);
     }
-    if (N % v2::BN2 == 0) {   // 128 x 256 tiles, persistent
+    if (variant == BASALT_K_MATMUL_ONE_SM_256) {   // 128 x 256 tiles, persistent
         rc = b_is_nk ? make_map(&mb, B, (uint64_t)N, (uint64_t)K, BK, v2::BN2) : make_map(&mb, B, (uint64_t)K, (uint64_t)N, 64, BK);
         if (rc) return rc;
         return b_is_nk ? launch_persistent<true>(ma, mb, (__half*)C, M, N, K, status, s) : launch_persistent<false>(ma, mb, (__half*)C, M, N, K, status, s);
@@ -751,25 +857,21 @@ extern "C" int basalt_k_matmul_f16(const void* A, const void* B, void* C, int M,
     return b_is_nk ? launch<3, true>(ma, mb, (__half*)C, M, N, K, status, s) : launch<3, false>(ma, mb, (__half*)C, M, N, K, status, s);
 }
 
+}  // namespace
+
+extern "C" int basalt_k_matmul_f16(const void* A, const void* B, void* C, int M, int N, int K, int b_is_nk, int32_t* status, void* stream) {
+    return matmul_f16_any(A, B, C, M, N, K, b_is_nk, BASALT_K_MATMUL_AUTO, nullptr, 0, status, stream, "matmul_f16");
+}
+
 // C = A * B for this rank's rows, every tile stored to this GPU's result buffer and to the same rows of
 // each peer's buffer from the epilogue of the tcgen05 kernel: compute and gather in one kernel.
 extern "C" int basalt_k_matmul_f16_allgather(const void* A, const void* B, void* C, int M, int N, int K, int b_is_nk, void* const* peer_c, int n_peers,
                                              int32_t* status, void* stream) {
-    if (M <= 0 || N <= 0 || K <= 0) return 0;
-    if (M % v3::TM || N % v3::TN || K % BK) return basalt_k::record_msg(1, "matmul_f16_allgather", "M and N must be multiples of 256 and K of 64");
-    if (n_peers < 0 || n_peers > BASALT_K_MAX_PEERS - 1 || (n_peers && !peer_c)) return basalt_k::record_msg(1, "matmul_f16_allgather", "bad peer list");
-    uintptr_t all = (uintptr_t)A | (uintptr_t)B | (uintptr_t)C;
-    v3::PeerRows peers = {};
-    peers.n = n_peers;
-    for (int i = 0; i < n_peers; i++) { peers.c[i] = (__half*)peer_c[i]; all |= (uintptr_t)peer_c[i]; }
-    if (all & 15) return basalt_k::record_msg(1, "matmul_f16_allgather", "matrices must be 16-byte aligned");
-    CUtensorMap ma, mb;
-    int rc = make_map(&ma, A, (uint64_t)M, (uint64_t)K, BK, BM);
-    if (rc) return rc;
-    rc = b_is_nk ? make_map(&mb, B, (uint64_t)N, (uint64_t)K, BK, v3::HALF_N) : make_map(&mb, B, (uint64_t)K, (uint64_t)N, 64, BK);
-    if (rc) return rc;
-    cudaStream_t s = (cudaStream_t)stream;
-    if (getenv("BASALT_K_MATMUL_UNSTAGED_PUSH"))   // A/B switch: 16-byte pieces straight from the registers
-        return b_is_nk ? launch_pair<true, true, false>(ma, mb, (__half*)C, M, N, K, status, s, peers) : launch_pair<false, true, false>(ma, mb, (__half*)C, M, N, K, status, s, peers);
-    return b_is_nk ? launch_pair<true, true, true>(ma, mb, (__half*)C, M, N, K, status, s, peers) : launch_pair<false, true, true>(ma, mb, (__half*)C, M, N, K, status, s, peers);
+    if (M % v3::TM || N % v3::TN) return basalt_k::record_msg(1, "matmul_f16_allgather", "M and N must be multiples of 256 and K of 64");
+    return matmul_f16_any(A, B, C, M, N, K, b_is_nk, BASALT_K_MATMUL_AUTO, peer_c, n_peers, status, stream, "matmul_f16_allgather");
+}
+
+extern "C" int basalt_k_matmul_f16_variant(const void* A, const void* B, void* C, int M, int N, int K, int b_is_nk, int variant, void* const* peer_c,
+                                           int n_peers, int32_t* status, void* stream) {
+    return matmul_f16_any(A, B, C, M, N, K, b_is_nk, variant, peer_c, n_peers, status, stream, "matmul_f16_variant");
 }

@@ -123,6 +123,8 @@ struct Plan {
                             // two-row tile; launched instead when the caller's grid is even in x and y
     unsigned lgrid = 0;     // persistent kernel: the caller's grid goes in two trailing u32 parameters; lgrid logical CTAs
                             // along x form one tile, and min(SM count, tiles) CTAs are launched
+    int gather = -1;        // the kernel (its pair twin, for a persistent kernel) can also store its result behind peer base addresses:
+                            // index of the output pointer parameter; two trailing parameters, a table of seven u64 and a u32 count
 };
 }  // namespace
 struct basalt_rt_module {
@@ -238,6 +240,7 @@ void parse_plans(const char* ptx, std::map<std::string, Plan>* out) {
             else if (k == "logical_block") sscanf(v.c_str(), "%u,%u,%u", &p.logical_block[0], &p.logical_block[1], &p.logical_block[2]);
             else if (k == "lgrid") p.lgrid = (unsigned)strtoul(v.c_str(), nullptr, 10);
             else if (k == "tail") p.tail_k = (unsigned)strtoul(v.c_str(), nullptr, 10);
+            else if (k == "gather") p.gather = (int)strtol(v.c_str(), nullptr, 10);
             else if (k == "tmap") {
                 TmapSpec t;
                 unsigned long long inner = 0, rowb = 0;
@@ -484,9 +487,32 @@ int basalt_rt_planned_geometry(basalt_rt_function* fn, void** params, uint32_t g
     return 0;
 }
 
+namespace {
+int launch_impl(basalt_rt_function* fn, const uint32_t grid[3], const uint32_t block[3], uint32_t shared_mem_bytes, void* stream, void** params,
+                const uint64_t* peer_out, int n_peers);
+}
 int basalt_rt_launch(basalt_rt_function* fn, const uint32_t grid[3], const uint32_t block[3], uint32_t shared_mem_bytes, void* stream, void** params) {
     if (!fn || !grid || !block) return set_err(4, 0, "basalt_rt_launch", "null argument");
+    return launch_impl(fn, grid, block, shared_mem_bytes, stream, params, nullptr, 0);
+}
+
+int basalt_rt_launch_gather(basalt_rt_function* fn, const uint32_t grid[3], const uint32_t block[3], uint32_t shared_mem_bytes, void* stream, void** params,
+                            const uint64_t* peer_out, int n_peers) {
+    if (!fn || !grid || !block) return set_err(4, 0, "basalt_rt_launch_gather", "null argument");
+    if (n_peers < 0 || n_peers > 7 || (n_peers && !peer_out)) return set_err(4, 0, "basalt_rt_launch_gather", "between 0 and 7 peer addresses");
+    if (!fn->has_plan || fn->plan.gather < 0) return set_err(4, 0, "basalt_rt_launch_gather", "this kernel was not emitted with a gathering epilogue");
+    for (int i = 0; i < n_peers; i++)
+        if (!peer_out[i] || (peer_out[i] & 15)) return set_err(4, 0, "basalt_rt_launch_gather", "a peer address is null or not 16-byte aligned");
+    return launch_impl(fn, grid, block, shared_mem_bytes, stream, params, peer_out, n_peers);
+}
+
+namespace {
+int launch_impl(basalt_rt_function* fn, const uint32_t grid[3], const uint32_t block[3], uint32_t shared_mem_bytes, void* stream, void** params,
+                const uint64_t* peer_out, int n_peers) {
     const Fns& f = fn->mod->ctx->drv->f;
+    uint64_t peer_table[7] = {0, 0, 0, 0, 0, 0, 0};
+    uint32_t peer_count = (uint32_t)n_peers;
+    for (int i = 0; i < n_peers; i++) peer_table[i] = peer_out[i];
     if (fn->coarse && params && grid[1] == 1 && grid[2] == 1 && block[1] == 1 && block[2] == 1 && block[0] >= 32) {
         // One-element-per-thread kernel: the caller's launch names the logical threads.  They are run by CTAs whose
         // threads each make one trip of the vectorised loop (several 16-byte accesses in flight): many short CTAs
@@ -554,6 +580,10 @@ int basalt_rt_launch(basalt_rt_function* fn, const uint32_t grid[3], const uint3
         all.push_back(&split);
         all.push_back(&ws);
         all.push_back(&tk);
+        if (p.gather >= 0) {
+            all.push_back(peer_table);
+            all.push_back(&peer_count);
+        }
         return check(f, "cuLaunchKernel", f.cuLaunchKernel(fn->fn, full + (tiles - full) * split, 1, 1, p.block[0], p.block[1], p.block[2], p.smem, (CUstream)stream, all.data(), nullptr));
     }
     if (!fn->has_plan || fn->plan.tmaps.empty()) {
@@ -609,9 +639,16 @@ int basalt_rt_launch(basalt_rt_function* fn, const uint32_t grid[3], const uint3
         if (g[0] == 0) return 0;
         all.push_back(&lgx);
         all.push_back(&lgy);
+        if (entry == fn->pair && p.gather >= 0) {
+            all.push_back(peer_table);
+            all.push_back(&peer_count);
+        }
     }
+    if (n_peers && !(entry == fn->pair && p.gather >= 0))
+        return set_err(4, 0, "basalt_rt_launch_gather", "the gathering epilogue is in the two-SM entry: the grid must be even in x and y");
     return check(f, "cuLaunchKernel", f.cuLaunchKernel(entry, g[0], g[1], g[2], p.block[0], p.block[1], p.block[2], sm, (CUstream)stream, all.data(), nullptr));
 }
+}  // namespace
 
 int basalt_rt_occupancy(basalt_rt_function* fn, uint32_t block_threads, uint32_t shared_mem_bytes, int* ctas_per_sm, int* sm_count) {
     if (!fn || !ctas_per_sm) return set_err(4, 0, "basalt_rt_occupancy", "null argument");

@@ -59,6 +59,26 @@ def matmul_f16_allgather(A, B, Cm, M: int, N: int, K: int, peer_ptrs, b_is_nk: b
                                              _p(status) if status is not None else None, C.c_void_p(stream)))
 
 
+MATMUL_VARIANTS = {"auto": 0, "one_cta_128": 1, "one_sm_256": 2, "pair_direct": 3, "pair_lines": 4, "pair_bulk": 5, "pair_bulk_deep": 6}
+
+
+def matmul_f16_variant(A, B, Cm, M: int, N: int, K: int, variant: str, peer_ptrs=(), b_is_nk: bool = False, status=None, stream=None):
+    """basalt_k_matmul_f16_variant: the product through one named kernel form (MATMUL_VARIANTS), with
+    the result also stored behind each address of `peer_ptrs` (CTA-pair forms only)."""
+    arr = (C.c_void_p * max(1, len(peer_ptrs)))(*[C.c_void_p(int(p)) for p in peer_ptrs])
+    _check(lib.basalt_k_matmul_f16_variant(_p(A), _p(B), _p(Cm), M, N, K, int(b_is_nk), MATMUL_VARIANTS[variant], arr, len(peer_ptrs),
+                                           _p(status) if status is not None else None, C.c_void_p(stream)))
+
+
 def matmul_f16(A, B, Cm, M: int, N: int, K: int, b_is_nk: bool = False, status=None, stream=None):
     _check(lib.basalt_k_matmul_f16(_p(A), _p(B), _p(Cm), M, N, K, int(b_is_nk), _p(status) if status is not None else None,
                                    C.c_void_p(stream)))
+
+
+FILL_KINDS = {"u32": 0, "i32_pm30": 1, "f32_pm1": 2, "f16_normal01": 3}
+
+
+def fill(kind: str, seed: int, n: int, out, start: int = 0, stream=None):
+    """Draws start .. start+n-1 of the seeded stream into device memory, as workloads.{u32, i32_pm30,
+    f32_pm1, f16_normal01} produce them on the host (identical bytes)."""
+    _check(lib.basalt_k_fill(FILL_KINDS[kind], seed, start, n, _p(out), C.c_void_p(stream)))

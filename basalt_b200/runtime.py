@@ -292,6 +292,23 @@ class CudaFunction:
                 _check(1)
         return go
 
+    def bind_gather(self, grid, block, shared_mem_bytes: int, params: list, peer_out: list[int], stream=None):
+        """`bind` for basalt_rt_launch_gather: the kernel's epilogue also stores every tile of its result,
+        at the same offset, behind each address of `peer_out` (the output parameter's value on the other
+        ranks, mapped into this device's address space)."""
+        vals = [C.c_uint64(p.device_ptr()) if isinstance(p, DeviceBuffer) else p for p in params]
+        arr = (C.c_void_p * max(len(vals), 1))(*[C.cast(C.pointer(v), C.c_void_p) for v in vals])
+        g = (C.c_uint32 * 3)(*_dim3(grid))
+        b = (C.c_uint32 * 3)(*_dim3(block))
+        peers = (C.c_uint64 * max(len(peer_out), 1))(*[int(p) for p in peer_out])
+        s = C.c_void_p(stream)
+        h, fn, n = self._h, lib.basalt_rt_launch_gather, len(peer_out)
+
+        def go(stream=None, _keep=(vals, arr, g, b, peers)):
+            if fn(h, g, b, shared_mem_bytes, s if stream is None else C.c_void_p(stream), arr, peers, n):
+                _check(1)
+        return go
+
     def status(self) -> int:
         """The kernel's device status word (synchronous read): non-zero when a bounded wait inside
         the kernel gave up and the last output is not valid. Always 0 for kernels without waits."""

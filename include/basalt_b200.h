@@ -157,6 +157,20 @@ void basalt_rt_host_free(basalt_rt_ctx *ctx, void *p);
  * parameters and appended here; the caller still passes only the BIR parameters. */
 int basalt_rt_launch(basalt_rt_function *fn, const uint32_t grid[3], const uint32_t block[3],
                      uint32_t shared_mem_bytes, void *stream, void **params);
+/* basalt_rt_launch for one rank of a row-sharded matmul whose result every rank wants whole: compute
+ * and gather in ONE kernel.  peer_out[i] (0 <= n_peers <= 7) is the value the kernel's output pointer
+ * parameter has on another rank, as an address valid on this device (basalt_rt_ipc_open); the
+ * kernel's epilogue stores every tile of its result at its own output pointer and, at the same
+ * offset, behind each peer address over NVLink (plain line-sized stores from the SMs while the next
+ * tile is being computed; no copy engine, no library collective), and ends with a system-scope
+ * fence.  A stream-ordered basalt_rt_peer_allreduce_max_i32 afterwards is the barrier after which
+ * every rank holds every rank's rows.  Only kernels the emitter lowered with a gathering epilogue
+ * take it (the fp32 FFMA matmul; the fp16 tcgen05 matmul through its two-SM entry, so the grid must
+ * be even in x and y); any other kernel is refused (kind 4).  No counterpart in the reference, which
+ * has no multi-GPU path (crates/basalt-runtime/src/ffi.rs:38-42). */
+int basalt_rt_launch_gather(basalt_rt_function *fn, const uint32_t grid[3], const uint32_t block[3],
+                            uint32_t shared_mem_bytes, void *stream, void **params, const uint64_t *peer_out,
+                            int n_peers);
 /* Grid and block the emitter planned for this kernel (0 when the kernel has no plan and the
  * caller chooses, as with the reference). */
 int basalt_rt_planned_geometry(basalt_rt_function *fn, void **params, uint32_t grid[3], uint32_t block[3],
@@ -233,7 +247,9 @@ int basalt_rt_stream_wait_event(basalt_rt_ctx *ctx, void *stream, void *event);
  * then launches basalt_k_peer_allreduce_max_i32 on `stream` with the next epoch (`reset`: store
  * reset_value into *partial after reading it).  `status` reads
  * the device word after synchronising: non-zero bits are ranks that did not answer within the
- * bound (2 s).  No counterpart in the reference (single GPU only). */
+ * bound (2 s); a group that has reported a non-zero status must be destroyed and created again on
+ * every rank (a late word matches no later epoch).  No counterpart in the reference (single GPU
+ * only). */
 typedef struct basalt_rt_peer_group basalt_rt_peer_group;
 int basalt_rt_peer_group_create(basalt_rt_ctx *ctx, int nranks, int rank, basalt_rt_peer_group **out);
 int basalt_rt_peer_group_handle(basalt_rt_peer_group *g, unsigned char handle_out[64]);

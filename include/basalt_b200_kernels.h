@@ -72,7 +72,10 @@ int basalt_k_matmul_f16(const void *A, const void *B, void *C, int M, int N, int
  * the calls from 1 and must be the same on every rank; all ranks must make the same calls in the
  * same order.  *partial is this rank's value, *result receives the maximum over all ranks; both
  * are device pointers and the call is ordered on `stream`.  A peer that has not answered after
- * timeout_ns sets bit r of *status (device uint32) and is left out of the result.  With `reset`
+ * timeout_ns sets bit r of *status (device uint32) and is left out of the result; its word, should it
+ * arrive later, matches no later epoch either (a word is accepted only when it carries exactly the
+ * epoch being waited for), so after a non-zero status the group's inboxes must be zeroed and the
+ * epochs restarted on every rank (basalt_rt_peer_group_destroy / _create).  With `reset`
  * non-zero, *partial is set to reset_value once it has been read, ready for the next accumulation
  * (the reduction kernel folds into it with atomicMax).  No counterpart in the reference, which has
  * no multi-GPU path. */
@@ -100,6 +103,40 @@ int basalt_k_max_i32_allreduce(const int32_t *x, int64_t n, int32_t *partial, co
  * No counterpart in the reference, which has no multi-GPU path. */
 int basalt_k_matmul_f16_allgather(const void *A, const void *B, void *C, int M, int N, int K, int b_is_nk,
                                   void *const *peer_c, int n_peers, int32_t *status, void *stream);
+
+/* The same product through one named kernel form, for tests and A/B timing (basalt_k_matmul_f16 and
+ * basalt_k_matmul_f16_allgather choose for themselves: the CTA-pair kernel with line-sized stores
+ * when M and N are multiples of 256 and nothing is gathered, bulk-tensor stores for the gather).
+ * ONE_CTA_128: one 128x128 tile per CTA of 128 threads.  ONE_SM_256: persistent, 128x256 tiles, one
+ * SM each.  PAIR_*: 256x256 tiles on clusters of two SMs (tcgen05.mma.cta_group::2), differing in
+ * how the epilogue leaves the SM: DIRECT = 16-byte pieces straight from the registers; LINES = each
+ * 32-row x 64-column piece transposed through shared memory and stored as whole 128-byte lines;
+ * BULK = the piece handed to the SM's copy engine as one bulk-tensor store per destination
+ * (cp.async.bulk.tensor shared -> global; six K-slab stages and two staging pieces per warp);
+ * BULK_DEEP = the same with five stages and four staging pieces per warp.  peer_c / n_peers as in
+ * basalt_k_matmul_f16_allgather (PAIR_* only; NULL / 0 for a local product).  No counterpart in the
+ * reference. */
+enum {
+    BASALT_K_MATMUL_AUTO = 0,
+    BASALT_K_MATMUL_ONE_CTA_128 = 1,
+    BASALT_K_MATMUL_ONE_SM_256 = 2,
+    BASALT_K_MATMUL_PAIR_DIRECT = 3,
+    BASALT_K_MATMUL_PAIR_LINES = 4,
+    BASALT_K_MATMUL_PAIR_BULK = 5,
+    BASALT_K_MATMUL_PAIR_BULK_DEEP = 6
+};
+int basalt_k_matmul_f16_variant(const void *A, const void *B, void *C, int M, int N, int K, int b_is_nk, int variant,
+                                void *const *peer_c, int n_peers, int32_t *status, void *stream);
+
+/* Seeded synthetic inputs of the benchmark workloads, generated on the device: element i of the
+ * output is draw `start + i` of the SplitMix64 counter stream of `seed`, mapped as the host
+ * generator (basalt_b200/workloads.py) and the CPU oracle map it -- the three produce identical
+ * bytes.  U32: all 32-bit patterns (the max_i32 and helper-chain inputs).  I32_PM30: int32 uniform
+ * in [-2^30, 2^30) (vadd_i32).  F32_PM1: f32 uniform in [-1, 1) (SGEMM).  F16_NORMAL01: binary16
+ * N(0,1) * 0.1 as a twelve-term Irwin-Hall sum (fp16 matmul; three draws per element).  No
+ * counterpart in the reference, whose inputs are the closed-form arrays of examples/cpu_launch_*.c. */
+enum { BASALT_K_FILL_U32 = 0, BASALT_K_FILL_I32_PM30 = 1, BASALT_K_FILL_F32_PM1 = 2, BASALT_K_FILL_F16_NORMAL01 = 3 };
+int basalt_k_fill(int kind, uint64_t seed, uint64_t start, int64_t n, void *out, void *stream);
 
 #if defined(__GNUC__)
 #pragma GCC visibility pop

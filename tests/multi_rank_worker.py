@@ -153,6 +153,43 @@ def main():
         if r != group.rank:
             ctx.ipc_close(p)
 
+    # ---- the emitted kernels with their gathering epilogue (basalt_rt_launch_gather): fp16 on tcgen05, then fp32 FFMA ----
+    for what in ("f16", "f32"):
+        if what == "f16":
+            M, N, K, esz = 512 * group.world, 512, 192, 2
+            A = w.f16_normal01(w.SEEDS["matmul_f16"] + 31, M * K).reshape(M, K); B = w.f16_normal01(w.SEEDS["matmul_f16"] + 32, K * N).reshape(K, N)
+            want, tol, dt = orc_matmul_f16_rows(orc, A, B, N, False, 0, M), 2e-3, np.float16
+        else:
+            M, N, K, esz = 256 * group.world, 384, 96, 4
+            A = w.f32_pm1(w.SEEDS["sgemm_f32"] + 31, M * K).reshape(M, K); B = w.f32_pm1(w.SEEDS["sgemm_f32"] + 32, K * N).reshape(K, N)
+            want, tol, dt = orc_sgemm_rows(orc, A, B, 0, M), 1e-4, np.float32
+        r0, r1 = group.shard(M, 256)
+        Ml = r1 - r0
+        dA, dB, dC = ctx.upload(A[r0:r1]), ctx.upload(B), ctx.upload(np.full((M, N), np.nan, dt))
+        flag = ctx.upload(np.zeros(2, np.int32))
+        ptrs = group.map_peers(ctx, dC)
+        group.barrier()
+        if what == "f16":
+            fn = ctx.load_module(ptx.emit(kb.matmul_f16(Ml, N, K)).text).get_function("matmul_kernel")
+            block = 128
+        else:
+            fn = ctx.load_module(ptx.emit(kb.sgemm_cta128(Ml, N, K)).text).get_function("sgemm_f32")
+            block = 256
+        go = fn.bind_gather((N // 128, Ml // 128), block, 0, [dA, dB, b.ptr(dC.device_ptr() + r0 * N * esz)],
+                            [ptrs[r] + r0 * N * esz for r in range(group.world) if r != group.rank])
+        for _ in range(3):
+            go()
+            peers.allreduce_max_i32(flag.device_ptr(), flag.device_ptr() + 4, None)      # the barrier: all ranks' stores have landed
+            ctx.synchronize()
+            assert fn.status() == 0 and peers.status() == 0
+            got = dC.to_numpy(dt).reshape(M, N)
+            assert np.isfinite(got).all(), ("rows of some rank never arrived", what)
+            assert rel_fro(got, want) <= tol, ("emitted fused gather", what)
+            group.barrier()
+        for r, p in enumerate(ptrs):
+            if r != group.rank:
+                ctx.ipc_close(p)
+
     group.barrier()
     peers.destroy()
     comm.destroy()

@@ -17,7 +17,8 @@ from basalt_b200 import kernels_cu as kc
 from oracle.bir_interp import run_kernel
 from _util import vp
 
-REFERENCE_KERNELS = "/root/reference/tests/kernels"
+# A checkout of the reference project, when the environment names one (BASALT_REFERENCE_TREE=<its root>).
+REFERENCE_KERNELS = os.path.join(os.environ.get("BASALT_REFERENCE_TREE", ""), "tests", "kernels")
 
 
 def _both(ptx, source):
@@ -278,7 +279,7 @@ def test_cli_accepts_cuda_sources(tmp_path):
     assert out.returncode == 1 and out.stderr.startswith("E301: ")
 
 
-@pytest.mark.skipif(not os.path.isdir(REFERENCE_KERNELS), reason="the reference tree is only present on the development machine")
+@pytest.mark.skipif(not os.environ.get("BASALT_REFERENCE_TREE") or not os.path.isdir(REFERENCE_KERNELS), reason="BASALT_REFERENCE_TREE does not name a checkout of the reference")
 def test_the_reference_tree_kernels_compile_and_give_their_known_answers(ptx):
     """The reference's own device sources (tests/kernels/*.cu), read where they lie, through this
     front end, with the inputs and answers of the matching examples/cpu_launch_*.c drivers."""

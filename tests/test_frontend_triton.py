@@ -17,7 +17,8 @@ from basalt_b200 import kernels_triton as kt
 from oracle.bir_interp import run_kernel
 from _util import sgemm_fixture
 
-REFERENCE_KERNELS = "/root/reference/tests/kernels"
+# A checkout of the reference project, when the environment names one (BASALT_REFERENCE_TREE=<its root>).
+REFERENCE_KERNELS = os.path.join(os.environ.get("BASALT_REFERENCE_TREE", ""), "tests", "kernels")
 
 
 def checked(ptx, bir):
@@ -218,7 +219,7 @@ def test_cli_accepts_triton_sources(tmp_path):
     assert out.returncode == 1 and out.stderr.startswith("E306: ")
 
 
-@pytest.mark.skipif(not os.path.isdir(REFERENCE_KERNELS), reason="the reference tree is only present on the development machine")
+@pytest.mark.skipif(not os.environ.get("BASALT_REFERENCE_TREE") or not os.path.isdir(REFERENCE_KERNELS), reason="BASALT_REFERENCE_TREE does not name a checkout of the reference")
 def test_the_reference_tree_triton_kernels(ptx):
     """The reference's own Triton sources (tests/kernels/tri_*.py), read where they lie, with the
     inputs and answers of examples/cpu_launch_triton_{vadd,matmul}.c."""

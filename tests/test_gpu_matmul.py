@@ -168,3 +168,125 @@ def test_matmul_f16_full_size(gpu, orc, how):
     rhs = A[blk].astype(np.float64) @ (B.astype(np.float32) @ v.astype(np.float32)).astype(np.float64)
     lhs = got[blk].astype(np.float64) @ v
     assert np.linalg.norm(lhs - rhs) / np.linalg.norm(rhs) <= F16_TOL
+
+
+PAIR_VARIANTS = ["pair_direct", "pair_lines", "pair_bulk", "pair_bulk_deep"]
+
+
+@pytest.mark.parametrize("b_is_nk", [True, False])
+@pytest.mark.parametrize("shape", [(256, 256, 64), (512, 768, 192), (4864, 4096, 192)])
+def test_matmul_f16_kernel_forms_agree(gpu, b_is_nk, shape):
+    # Every hand-written form (one CTA per tile, one SM per 128x256 tile, CTA pairs with each of the
+    # four epilogues) accumulates in the same order, so the results must agree bit for bit; the large
+    # shape wraps the stage ring, both accumulators and the staging pieces many times.
+    M, N, K = shape
+    A = w.f16_normal01(w.SEEDS["matmul_f16"] + 11, M * K).reshape(M, K)
+    B = w.f16_normal01(w.SEEDS["matmul_f16"] + 12, K * N).reshape(K, N)
+    dA, dB = dev(gpu, A), dev(gpu, np.ascontiguousarray(B.T) if b_is_nk else B)
+    status = dev(gpu, np.zeros(1, np.int32))
+    results = {}
+    for variant in ["one_cta_128", "one_sm_256"] + PAIR_VARIANTS:
+        dC = dev(gpu, np.full((M, N), np.nan, np.float16))
+        kernels.matmul_f16_variant(dA, dB, dC, M, N, K, variant, b_is_nk=b_is_nk, status=status)
+        gpu.synchronize()
+        assert status.to_numpy(np.int32)[0] == 0, variant
+        results[variant] = dC.to_numpy(np.float16).reshape(M, N).view(np.uint16)
+        dC.free()
+    assert np.isfinite(results["one_cta_128"].view(np.float16)).all()
+    for variant, got in results.items():
+        assert np.array_equal(got, results["one_cta_128"]), variant
+
+
+@pytest.mark.parametrize("variant", ["pair_direct", "pair_lines", "pair_bulk", "pair_bulk_deep", "auto"])
+@pytest.mark.parametrize("n_peers", [1, 7])
+def test_fused_gather_into_loop_back_peers(gpu, orc, variant, n_peers):
+    # The fused matmul + gather on ONE GPU: the "peers" are further buffers of this GPU, so the peer
+    # stores of the epilogue are exercised without a second device.  The rank's rows must land at the
+    # same offset of every buffer, the other rows of every buffer must stay untouched.
+    M_all, N, K, rows, row0 = 1024, 512, 256, 256, 512
+    A = w.f16_normal01(w.SEEDS["matmul_f16"] + 21, rows * K).reshape(rows, K)
+    B = w.f16_normal01(w.SEEDS["matmul_f16"] + 22, K * N).reshape(K, N)
+    want = orc_matmul_f16_rows(orc, A, B, N, False, 0, rows)
+    dA, dB = dev(gpu, A), dev(gpu, B)
+    poison = np.full((M_all, N), -7.0, np.float16)
+    bufs = [dev(gpu, poison) for _ in range(1 + n_peers)]
+    status = dev(gpu, np.zeros(1, np.int32))
+    mine = bufs[0].device_ptr() + row0 * N * 2
+    others = [b_.device_ptr() + row0 * N * 2 for b_ in bufs[1:]]
+    for _ in range(2):
+        kernels.matmul_f16_variant(dA, dB, mine, rows, N, K, variant, peer_ptrs=others, status=status)
+    gpu.synchronize()
+    assert status.to_numpy(np.int32)[0] == 0
+    first = None
+    for b_ in bufs:
+        got = b_.to_numpy(np.float16).reshape(M_all, N)
+        assert np.array_equal(got[:row0], poison[:row0]) and np.array_equal(got[row0 + rows:], poison[row0 + rows:])
+        assert rel_fro(got[row0:row0 + rows], want) <= F16_TOL
+        if first is None:
+            first = got[row0:row0 + rows].view(np.uint16).copy()
+        assert np.array_equal(got[row0:row0 + rows].view(np.uint16), first)
+
+
+@pytest.mark.parametrize("n_peers", [1, 7])
+def test_emitted_fused_gather_into_loop_back_peers_f16(gpu, orc, n_peers):
+    # basalt_rt_launch_gather on the emitted tcgen05 kernel (two-SM entry), the "peers" being further
+    # result buffers on this GPU: same bits in every buffer, nothing outside the rank's rows touched,
+    # and the same bits as the plain launch.
+    M_all, N, K, rows, row0 = 1024, 512, 256, 256, 512
+    A = w.f16_normal01(w.SEEDS["matmul_f16"] + 21, rows * K).reshape(rows, K)
+    B = w.f16_normal01(w.SEEDS["matmul_f16"] + 22, K * N).reshape(K, N)
+    want = orc_matmul_f16_rows(orc, A, B, N, False, 0, rows)
+    dA, dB = dev(gpu, A), dev(gpu, B)
+    poison = np.full((M_all, N), -7.0, np.float16)
+    bufs = [dev(gpu, poison) for _ in range(1 + n_peers)]
+    fn = emitted(gpu, kb.matmul_f16(rows, N, K), "matmul_kernel")
+    go = fn.bind_gather((N // 128, rows // 128), 128, 0, [dA, dB, b.ptr(bufs[0].device_ptr() + row0 * N * 2)],
+                        [b_.device_ptr() + row0 * N * 2 for b_ in bufs[1:]])
+    for _ in range(2):
+        go()
+    gpu.synchronize()
+    assert fn.status() == 0
+    plain = dev(gpu, np.zeros((rows, N), np.float16))
+    fn.launch((N // 128, rows // 128), 128, 0, [dA, dB, plain])
+    first = plain.to_numpy(np.float16).reshape(rows, N).view(np.uint16)
+    for b_ in bufs:
+        got = b_.to_numpy(np.float16).reshape(M_all, N)
+        assert np.array_equal(got[:row0], poison[:row0]) and np.array_equal(got[row0 + rows:], poison[row0 + rows:])
+        assert rel_fro(got[row0:row0 + rows], want) <= F16_TOL
+        assert np.array_equal(got[row0:row0 + rows].view(np.uint16), first)
+
+
+@pytest.mark.parametrize("shape", [(256, 256, 64), (2560, 1920, 64)])
+def test_emitted_fused_gather_into_loop_back_peers_f32(gpu, shape):
+    # the FFMA matmul's gathering epilogue, whole tiles and the split tail wave (300 tiles: the last four
+    # are summed from K-parts by the part that finishes last, which then stores to every buffer)
+    rows, N, K = shape
+    A, B, _ = sgemm_fixture(rows, N, K)
+    want = (A.astype(np.int64) @ B.astype(np.int64)).astype(np.float32)
+    dA, dB = dev(gpu, A), dev(gpu, B)
+    row0, M_all = 128, rows + 256
+    poison = np.full((M_all, N), -7.0, np.float32)
+    bufs = [dev(gpu, poison) for _ in range(3)]
+    fn = emitted(gpu, kb.sgemm_cta128(rows, N, K), "sgemm_f32")
+    go = fn.bind_gather((N // 128, rows // 128), 256, 0, [dA, dB, b.ptr(bufs[0].device_ptr() + row0 * N * 4)],
+                        [b_.device_ptr() + row0 * N * 4 for b_ in bufs[1:]])
+    for _ in range(2):
+        go()
+    gpu.synchronize()
+    for b_ in bufs:
+        got = b_.to_numpy(np.float32).reshape(M_all, N)
+        assert np.array_equal(got[:row0], poison[:row0]) and np.array_equal(got[row0 + rows:], poison[row0 + rows:])
+        assert np.array_equal(got[row0:row0 + rows], want)
+
+
+def test_launch_gather_refuses_kernels_without_the_epilogue(gpu):
+    fn = emitted(gpu, kb.load("vadd_i32"), "vadd_i32")
+    x = dev(gpu, np.zeros(256, np.int32))
+    with pytest.raises(b.CudaError) as e:
+        fn.bind_gather(1, 256, 0, [x, x, x, b.i32(256)], [x.device_ptr()])()
+    assert e.value.kind == 4
+    odd = emitted(gpu, kb.matmul_f16(384, 256, 64), "matmul_kernel")     # three tile rows: only the one-SM entry can run it
+    c = dev(gpu, np.zeros((384, 256), np.float16))
+    with pytest.raises(b.CudaError) as e:
+        odd.bind_gather((2, 3), 128, 0, [dev(gpu, np.zeros((384, 64), np.float16)), dev(gpu, np.zeros((64, 256), np.float16)), c], [c.device_ptr()])()
+    assert e.value.kind == 4 and "even" in e.value.message

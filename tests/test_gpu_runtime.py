@@ -61,3 +61,27 @@ def test_async_launch_streams_events_and_pinned_memory(gpu):
     assert gpu.elapsed_ms(e0, e1) > 0
     assert np.array_equal(c, a + 7)
     gpu.destroy_event(e0); gpu.destroy_event(e1); gpu.destroy_stream(s)
+
+
+def test_peer_exchange_wait_runs_out_and_reports_it(gpu):
+    # The give-up path of the peer exchange, provoked without a second device and without a fault:
+    # a group of two whose second inbox is a zeroed buffer of THIS GPU that nothing ever writes.  The
+    # kernel stores its word into that inbox, polls its own inbox for rank 1's word for 1 ms, gives up,
+    # sets bit 1 of the status word and returns the maximum over the ranks that answered (itself).
+    import ctypes as C
+    from basalt_b200._lib import lib
+    words = 2 * 8
+    mine, silent = gpu.upload(np.zeros(words, np.uint64)), gpu.upload(np.zeros(words, np.uint64))
+    inboxes = (C.c_uint64 * 2)(mine.device_ptr(), silent.device_ptr())
+    partial, result = gpu.upload(np.array([1234567], np.int32)), gpu.upload(np.array([-1], np.int32))
+    status = gpu.upload(np.zeros(1, np.uint32))
+    for epoch in (1, 2):          # a second call gives up the same way: the context stays usable
+        rc = lib.basalt_k_peer_allreduce_max_i32(inboxes, 2, 0, epoch, C.c_void_p(partial.device_ptr()), C.c_void_p(result.device_ptr()),
+                                                 C.c_void_p(status.device_ptr()), 1_000_000, 0, 0, None)
+        assert rc == 0
+        gpu.synchronize()
+        assert status.to_numpy(np.uint32)[0] == 0b10
+        assert result.to_numpy(np.int32)[0] == 1234567
+        # this rank's word did reach the silent inbox (parity row, column = sender's rank)
+        assert silent.to_numpy(np.uint64)[(epoch & 1) * 8 + 0] == (epoch << 32 | 1234567)
+    assert np.array_equal(gpu.upload(np.arange(8, dtype=np.int32)).to_numpy(np.int32), np.arange(8))

@@ -144,3 +144,21 @@ def test_helper_chain_full_size(gpu, orc):
     kernels.helper_chain_u32(dx, dout, n)
     gpu.synchronize()
     assert np.array_equal(dout.to_numpy(np.uint32), want)
+
+
+@pytest.mark.parametrize("kind, host, dtype", [("u32", w.u32, np.uint32), ("i32_pm30", w.i32_pm30, np.int32), ("f32_pm1", w.f32_pm1, np.float32),
+                                               ("f16_normal01", w.f16_normal01, np.float16)])
+def test_device_generator_matches_the_host_generator(gpu, kind, host, dtype):
+    # bench.py makes its inputs on the device; they must be the bytes the host generator (and, by
+    # tests/test_golden.py, the oracle's generator) produces for the same seed, at any offset.
+    from basalt_b200 import kernels
+    n = (1 << 18) + 13
+    want = host(w.SEEDS["vadd_i32"] + 5, n)
+    buf = gpu.alloc(n * want.itemsize)
+    kernels.fill(kind, w.SEEDS["vadd_i32"] + 5, n, buf)
+    gpu.synchronize()
+    got = buf.to_numpy(dtype, n)
+    assert np.array_equal(got.view(np.uint8), want.view(np.uint8))
+    kernels.fill(kind, w.SEEDS["vadd_i32"] + 5, 1000, buf, start=777)
+    gpu.synchronize()
+    assert np.array_equal(buf.to_numpy(dtype, 1000).view(np.uint8), want[777:1777].view(np.uint8))
