@@ -66,6 +66,7 @@ def _load() -> C.CDLL:
         "basalt_rt_host_alloc": (C.c_int, [vp, sz, P(vp)]),
         "basalt_rt_host_free": (None, [vp, vp]),
         "basalt_rt_launch": (C.c_int, [vp, C.c_uint32 * 3, C.c_uint32 * 3, C.c_uint32, vp, P(vp)]),
+        "basalt_rt_function_tune": (C.c_int, [vp, C.c_char_p, C.c_int]),
         "basalt_rt_launch_gather": (C.c_int, [vp, C.c_uint32 * 3, C.c_uint32 * 3, C.c_uint32, vp, P(vp), P(u64), C.c_int]),
         "basalt_rt_planned_geometry": (C.c_int, [vp, P(vp), C.c_uint32 * 3, C.c_uint32 * 3, P(C.c_uint32)]),
         "basalt_rt_ctx_sync": (C.c_int, [vp]),
@@ -104,6 +105,10 @@ def _load() -> C.CDLL:
         "basalt_k_helper_chain_u32": (C.c_int, [vp, vp, i64, vp]),
         "basalt_k_imad_peak": (C.c_int, [vp, i64, C.c_int, P(C.c_int64), vp]),
         "basalt_k_sgemm_f32": (C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, vp]),
+        "basalt_k_sgemm_f32_variant": (C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, vp]),
+        "basalt_k_vadd_i32_waves": (C.c_int, [vp, vp, vp, i64, C.c_int, vp]),
+        "basalt_k_max_i32_waves": (C.c_int, [vp, i64, vp, C.c_int, vp]),
+        "basalt_k_helper_chain_u32_waves": (C.c_int, [vp, vp, i64, C.c_int, vp]),
         "basalt_k_sgemm_f32_static_workspace": (C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, vp]),
         "basalt_k_matmul_f16": (C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, vp, vp]),
         "basalt_k_matmul_f16_allgather": (C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, P(vp), C.c_int, vp, vp]),

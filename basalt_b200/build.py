@@ -20,7 +20,7 @@ LIB = os.path.join(HERE, "libbasalt_b200.so")
 CLI = os.path.join(HERE, "basalt-b200")
 CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 
-CXX_SOURCES = ["bir.cpp", "passes.cpp", "emit.cpp", "emit_mma.cpp", "frontend_c.cpp", "frontend_triton.cpp", "capi.cpp", "runtime.cpp"]
+CXX_SOURCES = ["bir.cpp", "passes.cpp", "emit.cpp", "emit_mma.cpp", "regbudget.cpp", "frontend_c.cpp", "frontend_triton.cpp", "capi.cpp", "runtime.cpp"]
 CU_SOURCES = ["kernels/common.cu", "kernels/streaming.cu", "kernels/sgemm.cu", "kernels/matmul_f16_tc.cu", "kernels/collective.cu", "kernels/workload_fill.cu"]
 HEADERS = ["bir.hpp", "passes.hpp", "emit.hpp", "frontend_c.hpp", "frontend_triton.hpp", "kernels/common.cuh", "../../include/basalt_b200.h",
            "../../include/basalt_b200_kernels.h"]

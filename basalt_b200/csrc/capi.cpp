@@ -37,9 +37,28 @@ static bool parse_or_diag(const char* bir, size_t len, Module* m, basalt_diag* d
 
 static bool opts_ok(const basalt_emit_opts* o, EmitOptions* e, basalt_diag* d) {
     if (!o) return true;
-    if (o->target_variant && *o->target_variant && strcmp(o->target_variant, "sm_100a") != 0) {
-        fill_diag(d, "E093", std::string("unknown target variant: ") + o->target_variant);
-        return false;
+    // "sm_100a", optionally followed by tuning keys: "sm_100a,max_unroll=2,regs=48"
+    if (o->target_variant && *o->target_variant) {
+        std::string v = o->target_variant;
+        size_t comma = v.find(',');
+        if (v.substr(0, comma) != "sm_100a") {
+            fill_diag(d, "E093", std::string("unknown target variant: ") + o->target_variant);
+            return false;
+        }
+        while (comma != std::string::npos) {
+            size_t next = v.find(',', comma + 1);
+            std::string kv = v.substr(comma + 1, next == std::string::npos ? std::string::npos : next - comma - 1);
+            size_t eq = kv.find('=');
+            int val = eq == std::string::npos ? 0 : atoi(kv.c_str() + eq + 1);
+            std::string key = kv.substr(0, eq);
+            if (key == "max_unroll" && val >= 1) e->max_unroll = val;
+            else if (key == "regs" && val >= 16 && val <= 255) e->reg_budget = val;
+            else {
+                fill_diag(d, "E093", std::string("unknown target variant: ") + o->target_variant);
+                return false;
+            }
+            comma = next;
+        }
     }
     e->opt_level = o->opt_level < 0 ? 0 : o->opt_level;
     return true;

@@ -87,6 +87,8 @@ struct FnEmitter {
     int label_n = 0, mma_n = 0;
     unsigned maxntid = 0, cluster = 0;
     bool pair_twin = false;   // emitting `<name>__pair`: the mma must take the two-SM lowering
+    int est_regs = 0, budget = 0;   // the register-budget pass's figures for this body (set by run)
+    bool capped = false;            // run emitted .maxnreg
     Diag diag;
     bool failed = false;
 
@@ -925,6 +927,21 @@ struct FnEmitter {
             if (mod.min_blocks) o += ".minnctapersm " + std::to_string(maxntid ? 1u : mod.min_blocks) + "\n";
         }
         if (cluster) o += ".reqnctapercluster " + std::to_string(cluster) + ", 1, 1\n";
+        // the register-budget pass: pressure of this body against the budget the launch bounds imply
+        std::vector<std::string> all_decls;
+        for (int c = 0; c < NCLS; c++)
+            if (counts[c]) all_decls.push_back(std::string("\t.reg ") + kClsDecl[c] + " " + kClsPrefix[c] + "<" + std::to_string(counts[c]) + ">;");
+        for (auto& d : decls) all_decls.push_back(d);
+        est_regs = ptx_register_pressure(all_decls, body);
+        const unsigned threads = maxntid ? maxntid : (mod.has_launch_bounds ? mod.max_threads : 0);
+        budget = register_budget(threads, maxntid ? 1u : mod.min_blocks);
+        // Launch bounds without a CTA count: the default residency is this backend's choice, so a body that
+        // overshoots its budget by a quarter at most is held to it (ptxas then trades a few registers for the
+        // residency); a larger overshoot is left alone rather than spilled.
+        if (mod.has_launch_bounds && !mod.min_blocks && !maxntid && est_regs > budget && 4 * est_regs <= 5 * budget) {
+            o += ".maxnreg " + std::to_string(budget) + "\n";
+            capped = true;
+        }
         o += "{\n";
         for (int c = 0; c < NCLS; c++)
             if (counts[c]) o += std::string("\t.reg ") + kClsDecl[c] + " " + kClsPrefix[c] + "<" + std::to_string(counts[c]) + ">;\n";
@@ -942,7 +959,14 @@ bool emit_ptx(const Module& in, const EmitOptions& opts, EmitResult* out, Diag* 
     if (!check_module(in, d)) return false;
     Module m = in;
     out->reports.clear();
-    optimize_module(m, opts.opt_level, opts.reg_budget, &out->reports);
+    // The vectorisers pick the largest unroll whose body, lowered by this emitter, stays inside the budget.
+    const int budget = opts.reg_budget > 0 ? opts.reg_budget : register_budget(m.has_launch_bounds ? m.max_threads : 0, m.min_blocks);
+    PressureFn measure = [](const Module& mm, const Function& fn) {
+        FnEmitter fe(mm, fn);
+        std::string ignored;
+        return fe.run(&ignored) ? fe.est_regs : (1 << 20);
+    };
+    optimize_module(m, opts.opt_level, budget, opts.max_unroll, measure, &out->reports);
     std::string why;
     if (!verify_module(m, &why)) {
         if (d) { d->code = "E400"; d->arg = "internal: optimised module failed verification: " + why; }
@@ -955,7 +979,13 @@ bool emit_ptx(const Module& in, const EmitOptions& opts, EmitResult* out, Diag* 
     for (size_t i = 0; i < m.funcs.size(); i++) {
         const Function& f = m.funcs[i];
         const OptReport& r = out->reports[i];
-        text += "// kernel " + f.name + ": est_regs=" + std::to_string(r.est_regs);
+        FnEmitter fe(m, f);
+        std::string fn_text;
+        if (!fe.run(&fn_text)) {
+            if (d) *d = fe.diag;
+            return false;
+        }
+        text += "// kernel " + f.name + ": est_regs=" + std::to_string(fe.est_regs) + " budget=" + std::to_string(fe.budget) + (fe.capped ? " maxnreg" : "");
         if (r.elementwise) text += " elementwise";
         if (r.reduction) text += " reduction";
         if (r.vec_lanes) text += " lanes=" + std::to_string(r.vec_lanes) + " unroll=" + std::to_string(r.unroll);
@@ -971,12 +1001,6 @@ bool emit_ptx(const Module& in, const EmitOptions& opts, EmitResult* out, Diag* 
             const int trips = arithmetic > 256 ? 4 : 1;
             text += "//!basalt.plan " + r.coarse_of + " coarse=" + f.name + " params=" + std::to_string(f.params.size() - 1) + " per_thread=" +
                     std::to_string(std::max(1, r.vec_lanes) * std::max(1, r.unroll) * trips) + "\n";
-        }
-        FnEmitter fe(m, f);
-        std::string fn_text;
-        if (!fe.run(&fn_text)) {
-            if (d) *d = fe.diag;
-            return false;
         }
         for (auto& p : fe.plan) text += p + "\n";
         for (auto& md : fe.module_decls)
@@ -996,6 +1020,7 @@ bool emit_ptx(const Module& in, const EmitOptions& opts, EmitResult* out, Diag* 
             }
             for (auto& md : fe2.module_decls)
                 if (std::find(module_decls.begin(), module_decls.end(), md) == module_decls.end()) module_decls.push_back(md);
+            text += "// kernel " + twin.name + ": est_regs=" + std::to_string(fe2.est_regs) + " budget=" + std::to_string(fe2.budget) + "\n";
             bodies += twin_text + "\n";
         }
     }

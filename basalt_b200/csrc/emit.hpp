@@ -11,7 +11,8 @@ namespace basalt {
 
 struct EmitOptions {
     int opt_level = 2;      // 0 = the reference's one-to-one lowering, >0 = run the BIR passes
-    int reg_budget = 64;    // 32-bit registers per thread the vectorisers may plan for
+    int reg_budget = 0;     // 32-bit registers per thread the vectorisers may plan for; 0 = from the module's launch bounds (register_budget)
+    int max_unroll = 4;     // cap on the vectorisers' unroll factor
     bool want_bir = false;  // also return the optimised BIR text
 };
 
@@ -20,6 +21,16 @@ struct EmitResult {
     std::string bir;   // optimised module, when requested
     std::vector<OptReport> reports;
 };
+
+// Registers per thread that keep `ctas_per_sm` CTAs of `threads_per_cta` threads resident on an SM of 65 536
+// registers (0 = the defaults: 256 threads, the reference's launch geometry; as many CTAs as give 1024 resident
+// threads, which is what a streaming kernel needs to saturate HBM), rounded down to the allocation unit of eight.
+int register_budget(unsigned threads_per_cta, unsigned ctas_per_sm);
+// Maximum number of 32-bit registers live at one point of an emitted function body: live intervals over the
+// linearised PTX (`decls`: its .reg declarations, `body`: its statements and labels), extended across loop back
+// edges -- steps 1-3 of the reference's linear-scan allocator (crates/basalt-passes/src/regalloc.rs:5-33) applied
+// to virtual PTX registers.  ptxas lands between this figure and two thirds of it on the benchmark kernels.
+int ptx_register_pressure(const std::vector<std::string>& decls, const std::vector<std::string>& body);
 
 // Deterministic: the same (module, options) always yields the same bytes.
 bool emit_ptx(const Module& m, const EmitOptions& opts, EmitResult* out, Diag* d);

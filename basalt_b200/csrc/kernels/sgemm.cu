@@ -204,8 +204,8 @@ TailWorkspace* tail_workspace(int slots) {
 void plan_tail(int tiles, int slots, int K, int* full, int* split) {
     *full = tiles;
     *split = 1;
-    const int tail = tiles % slots;
-    if (tiles < slots || tail == 0 || tail * 2 > slots) return;   // one wave or less, no tail, or a tail that is more than half full
+    const int tail = tiles % slots;                       // the whole problem, when it is less than one wave
+    if (tail == 0 || tail * 2 > slots) return;            // no tail, or a tail that is more than half full
     int s = slots / tail;
     if (s > 4) s = 4;
     while (s > 1 && (K % (s * BK) != 0)) s--;
@@ -217,6 +217,10 @@ void plan_tail(int tiles, int slots, int K, int* full, int* split) {
 }  // namespace
 
 extern "C" int basalt_k_sgemm_f32(const float* A, const float* B, float* C, int M, int N, int K, void* stream) {
+    return basalt_k_sgemm_f32_variant(A, B, C, M, N, K, 0, stream);
+}
+
+extern "C" int basalt_k_sgemm_f32_variant(const float* A, const float* B, float* C, int M, int N, int K, int flags, void* stream) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     if (M % BM || N % BN || K % BK) return basalt_k::record_msg(1, "sgemm_f32", "M and N must be multiples of 128 and K of 16");
     if (((uintptr_t)A | (uintptr_t)B | (uintptr_t)C) & 15) return basalt_k::record_msg(1, "sgemm_f32", "matrices must be 16-byte aligned");
@@ -224,15 +228,14 @@ extern "C" int basalt_k_sgemm_f32(const float* A, const float* B, float* C, int 
     if (!resident) resident = basalt_k::resident_ctas(sgemm_f32_kernel<true>, THREADS);
     const int tiles = (M / BM) * (N / BN), slots = resident * basalt_k::sm_count();
     int full = tiles, split = 1;
-    static const bool no_split = getenv("BASALT_K_SGEMM_NO_TAIL_SPLIT") != nullptr;   // for A/B timing of the tail-wave split
-    if (!no_split) plan_tail(tiles, slots, K, &full, &split);
+    if (!(flags & BASALT_K_SGEMM_NO_TAIL_SPLIT)) plan_tail(tiles, slots, K, &full, &split);
     TailWorkspace* w = nullptr;
     if (split > 1) {
         w = tail_workspace(slots);
         if (!w) { full = tiles; split = 1; }   // no workspace: the plain schedule is still correct
     }
     const int grid = full + (tiles - full) * split;
-    if (getenv("BASALT_K_SGEMM_CP_ASYNC"))   // A/B switch: the earlier staging with 4-byte cp.async copies
+    if (flags & BASALT_K_SGEMM_CP_ASYNC)   // the earlier staging with 4-byte cp.async copies
         sgemm_f32_kernel<false><<<grid, THREADS, 0, (cudaStream_t)stream>>>(A, B, C, M, N, K, full, split, w ? w->partials : nullptr, w ? w->tickets : nullptr);
     else sgemm_f32_kernel<true><<<grid, THREADS, 0, (cudaStream_t)stream>>>(A, B, C, M, N, K, full, split, w ? w->partials : nullptr, w ? w->tickets : nullptr);
     return basalt_k::record(cudaGetLastError(), "sgemm_f32");

@@ -132,7 +132,6 @@ bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
 // 2^28: 6.16 TB/s on one wave, 7.09 on up to 64; max_i32: 6.99 on one, 7.27 on 16, 5.05 on 64, where the CTAs' atomics pile up).
 template <class K>
 int grid_for(K kernel, int64_t work, int waves = 1) {
-    if (const char* w = getenv("BASALT_K_STREAM_WAVES")) waves = atoi(w) > 0 ? atoi(w) : 1;   // A/B switch
     const int64_t cap = (int64_t)basalt_k::sm_count() * basalt_k::resident_ctas(kernel, kThreads) * waves;
     int64_t need = (work + kThreads - 1) / kThreads;
     if (need < 1) need = 1;
@@ -143,32 +142,39 @@ int grid_for(K kernel, int64_t work, int waves = 1) {
 
 extern "C" {
 
-int basalt_k_vadd_i32(const int32_t* a, const int32_t* b, int32_t* c, int64_t n, void* stream) {
+int basalt_k_vadd_i32(const int32_t* a, const int32_t* b, int32_t* c, int64_t n, void* stream) { return basalt_k_vadd_i32_waves(a, b, c, n, 64, stream); }
+int basalt_k_max_i32(const int32_t* x, int64_t n, int32_t* out, void* stream) { return basalt_k_max_i32_waves(x, n, out, 16, stream); }
+int basalt_k_helper_chain_u32(const uint32_t* in, uint32_t* out, int64_t n, void* stream) { return basalt_k_helper_chain_u32_waves(in, out, n, 8, stream); }
+
+int basalt_k_vadd_i32_waves(const int32_t* a, const int32_t* b, int32_t* c, int64_t n, int waves, void* stream) {
     if (n <= 0) return 0;
+    if (waves < 1) waves = 1;
     cudaStream_t s = (cudaStream_t)stream;
     if (aligned16(a) && aligned16(b) && aligned16(c)) {
         const int64_t n4 = n / 4;
-        vadd_i32_kernel<<<grid_for(vadd_i32_kernel, (n4 + 1) / 2 + 4, 64), kThreads, 0, s>>>((const int4*)a, (const int4*)b, (int4*)c, n4, a, b, c, n);
+        vadd_i32_kernel<<<grid_for(vadd_i32_kernel, (n4 + 1) / 2 + 4, waves), kThreads, 0, s>>>((const int4*)a, (const int4*)b, (int4*)c, n4, a, b, c, n);
     } else vadd_i32_scalar_kernel<<<grid_for(vadd_i32_scalar_kernel, n), kThreads, 0, s>>>(a, b, c, n);
     return basalt_k::record(cudaGetLastError(), "vadd_i32");
 }
 
-int basalt_k_max_i32(const int32_t* x, int64_t n, int32_t* out, void* stream) {
+int basalt_k_max_i32_waves(const int32_t* x, int64_t n, int32_t* out, int waves, void* stream) {
     if (n <= 0) return 0;
+    if (waves < 1) waves = 1;
     cudaStream_t s = (cudaStream_t)stream;
     if (aligned16(x)) {
         const int64_t n4 = n / 4;
-        max_i32_kernel<<<grid_for(max_i32_kernel, (n4 + 3) / 4 + 4, 16), kThreads, 0, s>>>((const int4*)x, n4, x, n, out);
+        max_i32_kernel<<<grid_for(max_i32_kernel, (n4 + 3) / 4 + 4, waves), kThreads, 0, s>>>((const int4*)x, n4, x, n, out);
     } else max_i32_scalar_kernel<<<grid_for(max_i32_scalar_kernel, n), kThreads, 0, s>>>(x, n, out);
     return basalt_k::record(cudaGetLastError(), "max_i32");
 }
 
-int basalt_k_helper_chain_u32(const uint32_t* in, uint32_t* out, int64_t n, void* stream) {
+int basalt_k_helper_chain_u32_waves(const uint32_t* in, uint32_t* out, int64_t n, int waves, void* stream) {
     if (n <= 0) return 0;
+    if (waves < 1) waves = 1;
     cudaStream_t s = (cudaStream_t)stream;
     if (aligned16(in) && aligned16(out)) {
         const int64_t n4 = n / 4;
-        helper_chain_kernel<<<grid_for(helper_chain_kernel, (n4 + 1) / 2 + 4, 8), kThreads, 0, s>>>((const uint4*)in, (uint4*)out, n4, in, out, n);
+        helper_chain_kernel<<<grid_for(helper_chain_kernel, (n4 + 1) / 2 + 4, waves), kThreads, 0, s>>>((const uint4*)in, (uint4*)out, n4, in, out, n);
     } else helper_chain_scalar_kernel<<<grid_for(helper_chain_scalar_kernel, n), kThreads, 0, s>>>(in, out, n);
     return basalt_k::record(cudaGetLastError(), "helper_chain_u32");
 }

@@ -8,6 +8,7 @@
 // Every pass is BIR in, BIR out, so its result can be printed and run through the CPU oracle
 // interpreter in the tests.
 #pragma once
+#include <functional>
 #include <string>
 
 #include "bir.hpp"
@@ -80,6 +81,9 @@ int estimate_registers(const Function& f);
 
 // Runs the whole pipeline on a checked module: inline, simplify, fuse warp reductions, then the
 // vectorisers with the largest unroll whose register estimate stays inside `reg_budget`.
-void optimize_module(Module& m, int opt_level, int reg_budget, std::vector<OptReport>* reports);
+// `measure(module, function)` returns the register pressure of the function as it would be emitted (the emitter
+// passes ptx_register_pressure of its own lowering); when empty, the BIR-level estimate_registers is used.
+using PressureFn = std::function<int(const Module&, const Function&)>;
+void optimize_module(Module& m, int opt_level, int reg_budget, int max_unroll, const PressureFn& measure, std::vector<OptReport>* reports);
 
 }  // namespace basalt

@@ -138,6 +138,9 @@ struct basalt_rt_function {
     CUfunction coarse = nullptr;   // see Plan::coarse
     CUfunction pair = nullptr;     // see Plan::pair
     CUdeviceptr status = 0;        // see Plan::status
+    bool use_pair = true;          // basalt_rt_function_tune: take the two-SM entry when the grid allows it
+    bool tail_split = true;        //   split the K extent of a sparse last wave
+    unsigned coarse_waves = 0;     //   coarse entries: exactly this many resident waves (0 = one loop trip per thread)
     bool has_plan = false;
     Plan plan;
 };
@@ -409,7 +412,7 @@ int basalt_rt_get_function(basalt_rt_module* mod, const char* name, basalt_rt_fu
             if (!rc) rc = check(f, "cuMemcpyHtoD", f.cuMemcpyHtoD(h->status, &zero, 4));
             if (rc) { delete h; return rc; }
         }
-        if (!h->plan.pair.empty() && !getenv("BASALT_RT_NO_PAIR")) {
+        if (!h->plan.pair.empty()) {
             rc = check(f, "cuModuleGetFunction", f.cuModuleGetFunction(&h->pair, mod->mod, h->plan.pair.c_str()));
             if (rc) { delete h; return rc; }
         }
@@ -525,7 +528,7 @@ int launch_impl(basalt_rt_function* fn, const uint32_t grid[3], const uint32_t b
         uint64_t wave = (uint64_t)fn->mod->ctx->sm_count * (uint64_t)resident;
         uint64_t per_cta = (uint64_t)block[0] * (fn->plan.per_thread ? fn->plan.per_thread : 16);
         uint64_t want = (logical + per_cta - 1) / per_cta;
-        if (const char* w = getenv("BASALT_RT_COARSE_WAVES")) want = wave * (uint64_t)(atoi(w) > 0 ? atoi(w) : 1);   // A/B switch: a fixed number of waves
+        if (fn->coarse_waves) want = wave * (uint64_t)fn->coarse_waves;   // basalt_rt_function_tune: a fixed number of waves
         if (want < wave) want = wave;
         uint32_t phys = grid[0] < want ? grid[0] : (uint32_t)want;
         std::vector<void*> all(params, params + fn->plan.nparams);
@@ -552,8 +555,8 @@ int launch_impl(basalt_rt_function* fn, const uint32_t grid[3], const uint32_t b
         const uint32_t slots = (uint32_t)ctx->sm_count * (uint32_t)resident;
         uint32_t full = tiles, split = 1;
         const uint32_t tail = tiles % slots;
-        static const bool no_split = getenv("BASALT_RT_NO_TAIL_SPLIT") != nullptr;   // for A/B timing of the tail-wave split
-        if (!no_split && tiles >= slots && tail != 0 && tail * 2 <= slots) {
+        // a sparse last wave -- or a whole problem of less than half a wave -- runs as K-parts that fill the slots
+        if (fn->tail_split && tail != 0 && tail * 2 <= slots) {
             uint32_t sp = slots / tail;
             if (sp > 4) sp = 4;
             while (sp > 1 && p.tail_k % (sp * 16) != 0) sp--;
@@ -629,7 +632,7 @@ int launch_impl(basalt_rt_function* fn, const uint32_t grid[3], const uint32_t b
         uint64_t sms = (uint64_t)fn->mod->ctx->sm_count;
         g[0] = (uint32_t)(tiles < sms ? tiles : sms);
         g[1] = 1;
-        if (fn->pair && p.lgrid == 2 && lgx % 2 == 0 && lgy % 2 == 0 && sms >= 2) {
+        if (fn->pair && fn->use_pair && p.lgrid == 2 && lgx % 2 == 0 && lgy % 2 == 0 && sms >= 2) {
             // clusters of two CTAs (the entry's own .reqnctapercluster), each walking tiles of 2 x 2 logical CTAs
             uint64_t pair_tiles = (uint64_t)(lgx / 2) * (lgy / 2);
             uint64_t pairs = pair_tiles < sms / 2 ? pair_tiles : sms / 2;
@@ -649,6 +652,16 @@ int launch_impl(basalt_rt_function* fn, const uint32_t grid[3], const uint32_t b
     return check(f, "cuLaunchKernel", f.cuLaunchKernel(entry, g[0], g[1], g[2], p.block[0], p.block[1], p.block[2], sm, (CUstream)stream, all.data(), nullptr));
 }
 }  // namespace
+
+int basalt_rt_function_tune(basalt_rt_function* fn, const char* key, int value) {
+    if (!fn || !key) return set_err(4, 0, "basalt_rt_function_tune", "null argument");
+    const std::string k = key;
+    if (k == "pair") fn->use_pair = value != 0;
+    else if (k == "tail_split") fn->tail_split = value != 0;
+    else if (k == "coarse_waves") fn->coarse_waves = value > 0 ? (unsigned)value : 0;
+    else return set_err(4, 0, "basalt_rt_function_tune", "unknown key: " + k);
+    return 0;
+}
 
 int basalt_rt_occupancy(basalt_rt_function* fn, uint32_t block_threads, uint32_t shared_mem_bytes, int* ctas_per_sm, int* sm_count) {
     if (!fn || !ctas_per_sm) return set_err(4, 0, "basalt_rt_occupancy", "null argument");

@@ -292,6 +292,11 @@ class CudaFunction:
                 _check(1)
         return go
 
+    def tune(self, key: str, value: int) -> "CudaFunction":
+        """basalt_rt_function_tune: "pair" / "tail_split" (0 switches the policy off), "coarse_waves" (w > 0)."""
+        _check(lib.basalt_rt_function_tune(self._h, key.encode(), int(value)))
+        return self
+
     def bind_gather(self, grid, block, shared_mem_bytes: int, params: list, peer_out: list[int], stream=None):
         """`bind` for basalt_rt_launch_gather: the kernel's epilogue also stores every tile of its result,
         at the same offset, behind each address of `peer_out` (the output parameter's value on the other

@@ -180,6 +180,13 @@ int basalt_rt_planned_geometry(basalt_rt_function *fn, void **params, uint32_t g
  * counterpart in the reference, which leaves grid sizing to its tests. */
 int basalt_rt_occupancy(basalt_rt_function *fn, uint32_t block_threads, uint32_t shared_mem_bytes, int *ctas_per_sm,
                         int *sm_count);
+/* Switches one of the runtime's launch policies for this function handle, for A/B timing and tests; a
+ * handle starts with every policy on.  "pair" = 0: keep the one-SM entry of the tcgen05 matmul on
+ * grids that are even in x and y.  "tail_split" = 0: run every tile of the FFMA matmul whole.
+ * "coarse_waves" = w > 0: launch a coarsened one-element-per-thread kernel on exactly w resident
+ * waves instead of one loop trip per thread.  Unknown keys are refused (kind 4).  The state lives in
+ * the handle: nothing here reads the process environment.  No counterpart in the reference. */
+int basalt_rt_function_tune(basalt_rt_function *fn, const char *key, int value);
 /* Kernels with bounded device-side waits (the tcgen05 matmul) own a device status word; this
  * reads it after synchronising: 0 = every wait was satisfied, non-zero = a wait gave up and the
  * output of that launch is not valid. No counterpart: the reference's kernels never wait. */

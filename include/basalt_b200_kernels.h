@@ -34,6 +34,13 @@ int basalt_k_max_i32(const int32_t *x, int64_t n, int32_t *out, void *stream);
  * tests/kernels/device_helper_chain.cu (there 3 levels) at depth 32. */
 int basalt_k_helper_chain_u32(const uint32_t *in, uint32_t *out, int64_t n, void *stream);
 
+/* The three streaming kernels above with the grid capped at `waves` resident waves of CTAs instead of
+ * the defaults (64, 16 and 8), for A/B timing of the launch geometry: on this part several waves of
+ * short CTAs stream faster than one wave of long ones.  Same results.  No counterpart in the reference. */
+int basalt_k_vadd_i32_waves(const int32_t *a, const int32_t *b, int32_t *c, int64_t n, int waves, void *stream);
+int basalt_k_max_i32_waves(const int32_t *x, int64_t n, int32_t *out, int waves, void *stream);
+int basalt_k_helper_chain_u32_waves(const uint32_t *in, uint32_t *out, int64_t n, int waves, void *stream);
+
 /* Measures the INT32 pipe: one wave of CTAs, each thread running `iters` x 32 independent
  * multiply-adds (mod 2^32). *imads receives the number of multiply-adds executed; `out` (at least
  * out_elems uint32) receives one word per thread so the work cannot be optimised away. The
@@ -43,6 +50,13 @@ int basalt_k_imad_peak(uint32_t *out, int64_t out_elems, int iters, int64_t *ima
 /* C[MxN] = A[MxK] * B[KxN], row-major fp32, FFMA only (no TF32): the workload of
  * examples/cpu_launch_tiled_sgemm.c (there 32^3 with a C addend). M, N multiples of 128, K of 16. */
 int basalt_k_sgemm_f32(const float *A, const float *B, float *C, int M, int N, int K, void *stream);
+
+/* basalt_k_sgemm_f32 with parts of its schedule switched off, for A/B timing: NO_TAIL_SPLIT runs every
+ * tile whole (no split-K parts for a sparse last wave or for a problem smaller than one wave); CP_ASYNC
+ * stages the A slab with 4-byte cp.async copies instead of through registers.  flags = 0 is
+ * basalt_k_sgemm_f32.  No counterpart in the reference. */
+enum { BASALT_K_SGEMM_NO_TAIL_SPLIT = 1, BASALT_K_SGEMM_CP_ASYNC = 2 };
+int basalt_k_sgemm_f32_variant(const float *A, const float *B, float *C, int M, int N, int K, int flags, void *stream);
 
 /* basalt_k_sgemm_f32 with the split-K workspace of its tail wave in a static device array instead
  * of device memory allocated on first use: this entry point allocates nothing (no cudaMalloc,

@@ -206,14 +206,17 @@ def test_tiled_fp16_matmul_gets_a_two_sm_twin(ptx):
     for nk in (False, True):
         text = ptx.emit(kb.matmul_f16(512, 512, 256, nk)).text
         plans = [l for l in text.splitlines() if l.startswith("//!basalt.plan")]
-        assert len(plans) == 1 and " lgrid=2 " in plans[0] and plans[0].endswith("pair=matmul_kernel__pair")
+        assert len(plans) == 1 and " lgrid=2 " in plans[0] and " pair=matmul_kernel__pair " in plans[0] and plans[0].endswith("gather=2")   # output = parameter 2
         one, two = text.split(".visible .entry matmul_kernel__pair")
         assert ".visible .entry matmul_kernel(" in one and ".reqnctapercluster" not in one
         assert ".reqnctapercluster 2, 1, 1" in two and two.count("tcgen05.mma.cta_group::2.kind::f16") == 4
         assert "tcgen05.alloc.cta_group::2" in two and "tcgen05.dealloc.cta_group::2" in two and two.count("barrier.cluster.arrive") == 2
         # both entries take the same argument list: the runtime launches either with one set of tensor maps
         params = lambda t: [l.strip().rstrip(",").split()[-1].split("_", 2)[-1] for l in t.split(")")[0].splitlines() if ".param" in l]
-        assert params(one.split(".visible .entry matmul_kernel(")[1]) == [p.replace("_pair_", "", 1) if p.startswith("_pair_") else p for p in params(two)]
+        # (the twin takes two more: the peer table and count of the gathering epilogue)
+        two_params = [p.replace("_pair_", "", 1) if p.startswith("_pair_") else p for p in params(two)]
+        assert params(one.split(".visible .entry matmul_kernel(")[1]) == two_params[:-2] and "peers[56]" in two_params[-2] and "npeers" in two_params[-1]
+        assert "fence.acq_rel.sys" in two and two.count("st.global.v4.b32") == 16      # eight line stores locally, eight per peer
         # bulk-tensor loads never multicast: a cta_group::2 load names the leader's barrier by address instead
         for line in text.splitlines():
             if "cp.async.bulk" in line:

@@ -23,3 +23,7 @@ def test_reference_arm_prints_one_contract_line():
     assert cpu["kind"] == "port" and cpu["cores"] == 1 and cpu["value"] == d["value"] and "x86-regalloc" in cpu["sample"]
     assert d["e2e"] == {"value": d["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
     assert 0.05 < d["value"] < 50      # a single core streaming int32: well inside this bracket
+    # the device arm prints the same `config` object and honours the same warm-up floor
+    sys.path.insert(0, ROOT)
+    import bench
+    assert d["config"] == bench.headline_config(1 << 28, 1) and d["warmup"] == 3

@@ -98,12 +98,8 @@ def run_matmul_f16(gpu, how, A, B, N, b_is_nk):
         assert status.to_numpy(np.int32)[0] == 0, "a bounded wait inside the kernel expired"
     else:
         # "emitted" takes the two-SM entry whenever the grid is even in x and y; "emitted_one_sm" keeps the one-SM entry
-        if how == "emitted_one_sm":
-            os.environ["BASALT_RT_NO_PAIR"] = "1"
-        try:
-            fn = emitted(gpu, kb.matmul_f16(M, N, K, b_is_nk, per_cta=(how == "emitted_per_cta")), "matmul_kernel")
-        finally:
-            os.environ.pop("BASALT_RT_NO_PAIR", None)
+        fn = emitted(gpu, kb.matmul_f16(M, N, K, b_is_nk, per_cta=(how == "emitted_per_cta")), "matmul_kernel")
+        fn.tune("pair", 0 if how == "emitted_one_sm" else 1)
         fn.launch((N // 128, M // 128), 128, 0, [dA, dB, dC])
         assert fn.status() == 0, "a bounded wait inside the emitted kernel expired"
     return dC.to_numpy(np.float16).reshape(M, N)
