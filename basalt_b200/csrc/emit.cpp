@@ -85,7 +85,7 @@ struct FnEmitter {
     std::map<std::pair<int, int64_t>, std::string> cells; // (space, key) -> symbol
     std::vector<uint32_t> uses;
     int label_n = 0, mma_n = 0;
-    unsigned maxntid = 0, cluster = 0;
+    unsigned maxntid = 0, cluster = 0, tmem_cols = 0;
     bool pair_twin = false;   // emitting `<name>__pair`: the mma must take the two-SM lowering
     int est_regs = 0, budget = 0;   // the register-budget pass's figures for this body (set by run)
     bool capped = false;            // run emitted .maxnreg
@@ -712,6 +712,7 @@ struct FnEmitter {
         site.module_decls = &module_decls;
         site.pair_twin = pair_twin;
         site.cluster = &cluster;
+        site.tmem_cols = &tmem_cols;
         if (emit_mma_fast(site, &decls, &body, &plan)) return;
         if (pair_twin) { fail("E099", "internal: the two-SM twin of " + f.name + " has no lowering"); return; }
 
@@ -927,6 +928,13 @@ struct FnEmitter {
             if (mod.min_blocks) o += ".minnctapersm " + std::to_string(maxntid ? 1u : mod.min_blocks) + "\n";
         }
         if (cluster) o += ".reqnctapercluster " + std::to_string(cluster) + ", 1, 1\n";
+        // The tensor-memory budget beside the register budget: an SM has 512 columns, and every CTA resident on it
+        // allocates its own (a CTA that cannot get them would wait inside tcgen05.alloc for one that never leaves).
+        const unsigned resident_ctas = maxntid ? 1u : (mod.min_blocks ? mod.min_blocks : 1u);
+        if (tmem_cols * resident_ctas > 512) {
+            fail("E099", "internal: " + std::to_string(resident_ctas) + " resident CTAs x " + std::to_string(tmem_cols) + " tensor-memory columns exceed the SM's 512");
+            return false;
+        }
         // the register-budget pass: pressure of this body against the budget the launch bounds imply
         std::vector<std::string> all_decls;
         for (int c = 0; c < NCLS; c++)
@@ -985,7 +993,8 @@ bool emit_ptx(const Module& in, const EmitOptions& opts, EmitResult* out, Diag* 
             if (d) *d = fe.diag;
             return false;
         }
-        text += "// kernel " + f.name + ": est_regs=" + std::to_string(fe.est_regs) + " budget=" + std::to_string(fe.budget) + (fe.capped ? " maxnreg" : "");
+        text += "// kernel " + f.name + ": est_regs=" + std::to_string(fe.est_regs) + " budget=" + std::to_string(fe.budget) + (fe.capped ? " maxnreg" : "") +
+                (fe.tmem_cols ? " tmem_cols=" + std::to_string(fe.tmem_cols) : "");
         if (r.elementwise) text += " elementwise";
         if (r.reduction) text += " reduction";
         if (r.vec_lanes) text += " lanes=" + std::to_string(r.vec_lanes) + " unroll=" + std::to_string(r.unroll);
@@ -1020,7 +1029,8 @@ bool emit_ptx(const Module& in, const EmitOptions& opts, EmitResult* out, Diag* 
             }
             for (auto& md : fe2.module_decls)
                 if (std::find(module_decls.begin(), module_decls.end(), md) == module_decls.end()) module_decls.push_back(md);
-            text += "// kernel " + twin.name + ": est_regs=" + std::to_string(fe2.est_regs) + " budget=" + std::to_string(fe2.budget) + "\n";
+            text += "// kernel " + twin.name + ": est_regs=" + std::to_string(fe2.est_regs) + " budget=" + std::to_string(fe2.budget) +
+                    (fe2.tmem_cols ? " tmem_cols=" + std::to_string(fe2.tmem_cols) : "") + "\n";
             bodies += twin_text + "\n";
         }
     }

@@ -62,6 +62,7 @@ struct MmaSite {
     std::vector<std::string>* module_decls;   // receives module-scope declarations
     bool pair_twin = false;       // this is the `<name>__pair` twin of an entry: take the two-SM (cta_group::2) lowering or fail
     unsigned* cluster = nullptr;  // the entry's .reqnctapercluster x extent, which a lowering may set
+    unsigned* tmem_cols = nullptr;   // tensor-memory columns the lowering allocates per CTA (an SM has 512)
 };
 bool emit_mma_fast(const MmaSite& site, std::vector<std::string>* decls, std::vector<std::string>* lines,
                    std::vector<std::string>* plan);

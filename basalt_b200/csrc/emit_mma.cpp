@@ -473,6 +473,7 @@ bool matmul_tcgen05(const MmaSite& s, std::vector<std::string>* decls, std::vect
     o.label(L + "init_done");
     o("setp.eq.u32 %s, %s, 1;", r("w1").c_str(), r("warp").c_str());
     o("@!%s bra %salloc_done;", r("w1").c_str(), L.c_str());
+    if (s.tmem_cols) *s.tmem_cols = 128;
     o("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%s], 128;", r("slot").c_str());
     o("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
     o.label(L + "alloc_done");
@@ -755,6 +756,7 @@ bool matmul_tcgen05_persistent(const MmaSite& s, std::vector<std::string>* decls
     o.label(L + "init_done");
     o("setp.eq.u32 %s, %s, 1;", r("w1").c_str(), r("warp").c_str());
     o("@!%s bra %salloc_done;", r("w1").c_str(), L.c_str());
+    if (s.tmem_cols) *s.tmem_cols = 512;
     o("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%s], 512;", r("slot").c_str());
     o("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
     o.label(L + "alloc_done");
@@ -979,8 +981,11 @@ bool matmul_tcgen05_persistent(const MmaSite& s, std::vector<std::string>* decls
     o.label(L + "skip");
     char pl[640];
     snprintf(pl, sizeof pl,
-             "//!basalt.plan %s logical_block=128,1,1 block=192,1,1 smem=%u params=%u tmap=%d:2:%lld:%lld:64:128:128 tmap=%d:2:%lld:%lld:64:%d:128 status=1 lgrid=2 pair=%s__pair gather=%d",
-             s.kernel.c_str(), smem, s.nparams, s.a_param, lda, lda * 2, s.b_param, ldb, ldb * 2, b_nk ? 128 : 64, s.kernel.c_str(), s.d_param);
+             // an eighth tmap field gives the matrix's row count, so that the tensor map clamps: a constant, or the
+             // caller's grid extent in x or y times the tile rows (A has 128 rows per grid row; B stored [N x K] has
+             // 128 rows per grid column, B stored [K x N] has K rows)
+             "//!basalt.plan %s logical_block=128,1,1 block=192,1,1 smem=%u params=%u tmap=%d:2:%lld:%lld:64:128:128:y128 tmap=%d:2:%lld:%lld:64:%d:128:%s status=1 lgrid=2 pair=%s__pair gather=%d",
+             s.kernel.c_str(), smem, s.nparams, s.a_param, lda, lda * 2, s.b_param, ldb, ldb * 2, b_nk ? 128 : 64, b_nk ? "x128" : std::to_string(in.k).c_str(), s.kernel.c_str(), s.d_param);
     plan->push_back(pl);
     return true;
 }
@@ -1156,6 +1161,7 @@ bool matmul_tcgen05_pair(const MmaSite& s, std::vector<std::string>* decls, std:
     o.label(L + "init_done");
     o("setp.eq.u32 %s, %s, 1;", r("w1").c_str(), r("warp").c_str());
     o("@!%s bra %salloc_done;", r("w1").c_str(), L.c_str());
+    if (s.tmem_cols) *s.tmem_cols = 512;
     o("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%s], 512;", r("slot").c_str());   // the same warp of both CTAs allocates for the pair
     o("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;");
     o.label(L + "alloc_done");

@@ -17,6 +17,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <map>
+#include <mutex>
 #include <sstream>
 #include <string>
 #include <vector>
@@ -97,6 +98,12 @@ struct basalt_rt_ctx {
     // one ticket word per tile of a tail wave.  The kernels leave every ticket at zero.
     CUdeviceptr tail_partials = 0, tail_tickets = 0;
     unsigned tail_slots = 0;
+    // Every split launch of the context shares that workspace, so split launches are ordered one after another:
+    // each records `tail_done` on its stream, and a split launch on another stream first waits for it.
+    CUevent tail_done = nullptr;
+    CUstream tail_stream = nullptr;
+    bool tail_pending = false;
+    std::mutex mu;   // guards `staging` and the tail_* state: entry points may be called from several host threads
 };
 namespace {
 struct TmapSpec {
@@ -106,6 +113,8 @@ struct TmapSpec {
     uint64_t row_bytes = 0; // stride between rows
     unsigned box_inner = 0, box_outer = 0;
     unsigned swizzle = 0;   // bytes: 0, 32, 64, 128
+    char outer_axis = 0;    // rows of the matrix: 'x' / 'y' = the caller's grid extent on that axis times outer_mult,
+    uint64_t outer_mult = 0; //   0 = the constant outer_mult; both 0 = not known to the emitter (left wide open)
 };
 struct Plan {
     unsigned block[3] = {0, 0, 0};
@@ -247,9 +256,12 @@ void parse_plans(const char* ptx, std::map<std::string, Plan>* out) {
             else if (k == "tmap") {
                 TmapSpec t;
                 unsigned long long inner = 0, rowb = 0;
-                if (sscanf(v.c_str(), "%d:%u:%llu:%llu:%u:%u:%u", &t.param, &t.esz, &inner, &rowb, &t.box_inner, &t.box_outer, &t.swizzle) == 7) {
+                char outer[32] = {0};
+                if (sscanf(v.c_str(), "%d:%u:%llu:%llu:%u:%u:%u:%31s", &t.param, &t.esz, &inner, &rowb, &t.box_inner, &t.box_outer, &t.swizzle, outer) >= 7) {
                     t.inner = inner;
                     t.row_bytes = rowb;
+                    if (outer[0] == 'x' || outer[0] == 'y') { t.outer_axis = outer[0]; t.outer_mult = strtoull(outer + 1, nullptr, 10); }
+                    else if (outer[0]) t.outer_mult = strtoull(outer, nullptr, 10);
                     p.tmaps.push_back(t);
                 }
             }
@@ -346,6 +358,7 @@ void basalt_rt_ctx_destroy(basalt_rt_ctx* ctx) {
     for (auto& kv : ctx->staging) ctx->drv->f.cuMemFree(kv.second);
     if (ctx->tail_partials) ctx->drv->f.cuMemFree(ctx->tail_partials);
     if (ctx->tail_tickets) ctx->drv->f.cuMemFree(ctx->tail_tickets);
+    if (ctx->tail_done) ctx->drv->f.cuEventDestroy(ctx->tail_done);
     ctx->drv->f.cuDevicePrimaryCtxRelease(ctx->dev);
     delete ctx;
 }
@@ -562,6 +575,8 @@ int launch_impl(basalt_rt_function* fn, const uint32_t grid[3], const uint32_t b
             while (sp > 1 && p.tail_k % (sp * 16) != 0) sp--;
             if (sp >= 2) { full = tiles - tail; split = sp; }
         }
+        std::unique_lock<std::mutex> lock(ctx->mu, std::defer_lock);
+        if (split > 1) lock.lock();
         if (split > 1 && ctx->tail_slots < slots) {
             int rc = make_current(ctx);
             if (rc) return rc;
@@ -587,7 +602,23 @@ int launch_impl(basalt_rt_function* fn, const uint32_t grid[3], const uint32_t b
             all.push_back(peer_table);
             all.push_back(&peer_count);
         }
-        return check(f, "cuLaunchKernel", f.cuLaunchKernel(fn->fn, full + (tiles - full) * split, 1, 1, p.block[0], p.block[1], p.block[2], p.smem, (CUstream)stream, all.data(), nullptr));
+        if (split > 1) {
+            if (!ctx->tail_done) {
+                int rc = check(f, "cuEventCreate", f.cuEventCreate(&ctx->tail_done, CU_EVENT_DISABLE_TIMING));
+                if (rc) return rc;
+            }
+            if (ctx->tail_pending && ctx->tail_stream != (CUstream)stream) {
+                int rc = check(f, "cuStreamWaitEvent", f.cuStreamWaitEvent((CUstream)stream, ctx->tail_done, 0));
+                if (rc) return rc;
+            }
+        }
+        int rc = check(f, "cuLaunchKernel", f.cuLaunchKernel(fn->fn, full + (tiles - full) * split, 1, 1, p.block[0], p.block[1], p.block[2], p.smem, (CUstream)stream, all.data(), nullptr));
+        if (!rc && split > 1) {
+            rc = check(f, "cuEventRecord", f.cuEventRecord(ctx->tail_done, (CUstream)stream));
+            ctx->tail_stream = (CUstream)stream;
+            ctx->tail_pending = true;
+        }
+        return rc;
     }
     if (!fn->has_plan || fn->plan.tmaps.empty()) {
         if (fn->has_plan && fn->plan.block[0] && (block[0] != fn->plan.block[0] || block[1] != fn->plan.block[1] || block[2] != fn->plan.block[2]))
@@ -608,9 +639,16 @@ int launch_impl(basalt_rt_function* fn, const uint32_t grid[3], const uint32_t b
         uint64_t base = *(uint64_t*)params[t.param];
         if (base & 15) return set_err(4, 0, "cuTensorMapEncodeTiled", "matrix base address must be 16-byte aligned");
         CUtensorMapDataType dt = t.esz == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : t.esz == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
-        // The row count is not a kernel parameter; a kernel only requests boxes inside its own
-        // matrix, so the outer extent is left wide open.
-        cuuint64_t dims[2] = {t.inner, (cuuint64_t)1 << 24};
+        // The row count is not a kernel parameter: the plan derives it from the caller's grid (or names a
+        // constant), so that a box that reaches past the matrix is clamped and zero-filled by the copy engine
+        // instead of reading whatever lies behind the allocation; a kernel whose plan has no such field only
+        // requests boxes inside its own matrix, and the extent is left wide open.
+        cuuint64_t rows = (cuuint64_t)1 << 24;
+        if (t.outer_axis == 'x') rows = (cuuint64_t)grid[0] * t.outer_mult;
+        else if (t.outer_axis == 'y') rows = (cuuint64_t)grid[1] * t.outer_mult;
+        else if (t.outer_mult) rows = t.outer_mult;
+        if (rows == 0) return 0;
+        cuuint64_t dims[2] = {t.inner, rows};
         cuuint64_t strides[1] = {t.row_bytes};
         cuuint32_t box[2] = {t.box_inner, t.box_outer};
         cuuint32_t estr[2] = {1, 1};
@@ -716,16 +754,20 @@ int basalt_rt_cpu_launch(basalt_rt_ctx* ctx, basalt_rt_function* fn, const basal
     std::vector<uint64_t> dptrs(nargs, 0);
     std::vector<void*> params(nargs, nullptr);
     auto release = [&]() {
+        std::lock_guard<std::mutex> g(ctx->mu);
         for (auto& h : held) if (h.second) ctx->staging.insert(h);
     };
     for (int i = 0; i < nargs && !rc; i++) {
         const basalt_rt_arg& a = args[i];
         if (a.kind >= 4) {
             size_t bytes = a.bytes ? a.bytes : 1;
-            auto it = ctx->staging.find(bytes);
             CUdeviceptr p = 0;
-            if (it != ctx->staging.end()) { p = it->second; ctx->staging.erase(it); }
-            else rc = check(f, "cuMemAlloc", f.cuMemAlloc(&p, bytes));
+            {
+                std::lock_guard<std::mutex> g(ctx->mu);
+                auto it = ctx->staging.find(bytes);
+                if (it != ctx->staging.end()) { p = it->second; ctx->staging.erase(it); }
+            }
+            if (!p) rc = check(f, "cuMemAlloc", f.cuMemAlloc(&p, bytes));
             if (rc) break;
             held[i] = {bytes, p};
             // written-only buffers are uploaded too: the kernel may leave part of them untouched

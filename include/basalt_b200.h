@@ -154,7 +154,10 @@ void basalt_rt_host_free(basalt_rt_ctx *ctx, void *p);
  * kernel parameter, in the BIR parameter order. Unlike the reference it takes a stream and does
  * not synchronise; pass stream NULL and call basalt_rt_ctx_sync for the reference behaviour.
  * For a kernel with a launch plan, the tensor-map parameters are built from the pointer and size
- * parameters and appended here; the caller still passes only the BIR parameters. */
+ * parameters and appended here; the caller still passes only the BIR parameters.
+ * Launches of the FFMA matmul that split a sparse last wave along K share one workspace per
+ * context; the runtime orders them itself (each such launch waits, on its own stream, for the
+ * previous one wherever that ran), so callers may issue them from any streams and host threads. */
 int basalt_rt_launch(basalt_rt_function *fn, const uint32_t grid[3], const uint32_t block[3],
                      uint32_t shared_mem_bytes, void *stream, void **params);
 /* basalt_rt_launch for one rank of a row-sharded matmul whose result every rank wants whole: compute

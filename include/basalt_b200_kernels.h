@@ -48,7 +48,11 @@ int basalt_k_helper_chain_u32_waves(const uint32_t *in, uint32_t *out, int64_t n
 int basalt_k_imad_peak(uint32_t *out, int64_t out_elems, int iters, int64_t *imads, void *stream);
 
 /* C[MxN] = A[MxK] * B[KxN], row-major fp32, FFMA only (no TF32): the workload of
- * examples/cpu_launch_tiled_sgemm.c (there 32^3 with a C addend). M, N multiples of 128, K of 16. */
+ * examples/cpu_launch_tiled_sgemm.c (there 32^3 with a C addend). M, N multiples of 128, K of 16.
+ * A problem whose last wave of tiles is sparse runs those tiles as split-K parts through a workspace
+ * that is allocated on first use and shared by all calls on a device: such calls must not overlap in
+ * time on one device (issue them on one stream, or order the streams with events); calls on one
+ * stream never overlap. */
 int basalt_k_sgemm_f32(const float *A, const float *B, float *C, int M, int N, int K, void *stream);
 
 /* basalt_k_sgemm_f32 with parts of its schedule switched off, for A/B timing: NO_TAIL_SPLIT runs every
