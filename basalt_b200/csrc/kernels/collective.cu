@@ -62,7 +62,12 @@ __device__ __forceinline__ int exchange_max(const PeerTable& peers, int nranks, 
 
 __global__ void __launch_bounds__(32, 1) peer_allreduce_max_i32_kernel(PeerTable peers, int nranks, int rank, unsigned epoch, int* partial,
                                                                        int* __restrict__ result, unsigned* status, unsigned long long timeout_ns, int reset, int reset_value) {
-    const int v = exchange_max(peers, nranks, rank, epoch, *partial, status, timeout_ns);
+    // Launched with programmatic stream serialisation: this grid may be set up while the kernel before it
+    // on the stream (the reduction that produces *partial) is still draining, which hides its launch latency;
+    // nothing of that kernel's output is read before this wait, which returns once it has completed and its
+    // writes are visible.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int v = exchange_max(peers, nranks, rank, epoch, *reinterpret_cast<volatile int*>(partial), status, timeout_ns);
     if (threadIdx.x == 0) {
         *result = v;
         if (reset) *partial = reset_value;   // every lane has read it: ready for the next accumulation
@@ -130,8 +135,19 @@ extern "C" int basalt_k_peer_allreduce_max_i32(const uint64_t* inboxes, int nran
         if (!inboxes[r] || (inboxes[r] & 7)) return basalt_k::record_msg(1, "peer_allreduce_max_i32", "an inbox pointer is null or misaligned");
         t.inbox[r] = (unsigned long long*)(uintptr_t)inboxes[r];
     }
-    peer_allreduce_max_i32_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(t, nranks, rank, epoch, partial, result, status, timeout_ns, reset, reset_value);
-    return basalt_k::record(cudaGetLastError(), "peer_allreduce_max_i32");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1);
+    cfg.blockDim = dim3(32);
+    cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    unsigned long long timeout = timeout_ns;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, peer_allreduce_max_i32_kernel, t, nranks, rank, (unsigned)epoch, (int*)partial, (int*)result, (unsigned*)status, timeout, reset,
+                                       (int)reset_value);
+    return basalt_k::record(e != cudaSuccess ? e : cudaGetLastError(), "peer_allreduce_max_i32");
 }
 
 extern "C" int basalt_k_max_i32_allreduce(const int32_t* x, int64_t n, int32_t* partial, const uint64_t* inboxes, int nranks, int rank, uint32_t epoch,
