@@ -1678,6 +1678,112 @@ private:
         return select(t, c, a, b);
     }
 
+    // The per-thread fold of a reduction whose tile is `tl.load(p + pid * B + tl.arange(0, B), mask = offs < n)` over
+    // int32: the program's lanes are B consecutive words, so a thread reads them as 16-byte vectors (four in flight,
+    // lanes 4j .. 4j+3 for j = tid, tid + bdim, ...) instead of one masked word per lane -- integer max, min and
+    // wrapping add do not depend on the order of the fold.  The number of lanes the mask lets through is computed
+    // once per program (the mask is an upper bound on a unit-stride index, so they are a prefix); what is left
+    // after the vectors, and everything when the program's first word is not 16-byte aligned, goes through a scalar
+    // loop; the masked-off lanes contribute `other` (0 when absent, as in the lane-by-lane form) once.
+    // Returns false, having emitted nothing, when the tile is not of that shape.
+    bool fold_contiguous_i32(AtomOp op, const NP& x, Val identity, Val* acc_io) {
+        if (x->k != Node::Load || x->rank() != 1 || x->el != El::I32) return false;
+        const NP& p = x->in[0];
+        Aff ap = affine(p);
+        if (!ap.ok || ap.ci != 1 || !ap.ptr) return false;
+        NP lhs, rhs;
+        int64_t other = 0;
+        if (x->has_mask) {
+            const NP& m = x->in[1];
+            if (m->k != Node::Cmp || m->op != "<" || m->in[0]->rank() != 1 || m->in[1]->rank() != 0 || m->in[0]->el != El::I64 || m->in[1]->el != El::I64) return false;
+            Aff al = affine(m->in[0]);
+            if (!al.ok || al.ci != 1) return false;
+            lhs = m->in[0]; rhs = m->in[1];
+            if (x->has_other && (x->in[2]->rank() != 0 || !ceval(x->in[2], &other))) return false;
+            if (op == AtomOp::Add && other != 0) return false;   // a sum would need `other` once per masked-off lane
+        }
+        const Ty t = Ty::s(Scalar::I32), pg = Ty::p(Space::Global), v4 = Ty::vec(Scalar::I32, 4), i1 = Ty::s(Scalar::I1);
+        scopes_.emplace_back();
+        Val zero = ci(I64(), 0);
+        Val lanes = x->shape[0].sym >= 0 ? Val::P((uint32_t)x->shape[0].sym) : ci(I64(), x->shape[0].n);
+        Val p0 = gen(p, sub_idx(p, {zero}));
+        Val cnt = lanes;
+        if (x->has_mask) {
+            Val rem = bin(BinOp::Sub, I64(), gen(rhs, {}), gen(lhs, sub_idx(lhs, {zero})));
+            rem = select(I64(), icmp(ICmp::Slt, I64(), rem, zero), zero, rem);
+            cnt = select(I64(), icmp(ICmp::Slt, I64(), rem, lanes), rem, lanes);
+        }
+        Val aligned = icmp(ICmp::Eq, I64(), bin(BinOp::And, I64(), cast(CastOp::Bitcast, I64(), pg, p0), ci(I64(), 15)), zero);
+        Val nv = select(I64(), aligned, bin(BinOp::AShr, I64(), cnt, ci(I64(), 2)), zero);
+        Val tid = index(0), stride = index(6);
+        // ---- vectors: four per iteration, every load unconditional (a vector past the end re-reads the last one
+        // and its fold is dropped), so that the four are in flight together
+        uint32_t pre = cur_, vhead = new_block(), vbody = new_block(), vdone = new_block();
+        br(vhead);
+        cur_ = vhead;
+        Inst pj; pj.op = Opc::Phi; pj.ty = I64(); pj.ops = {tid}; pj.phi_blocks = {pre};
+        Val j = push(pj);
+        Inst pa; pa.op = Opc::Phi; pa.ty = t; pa.ops = {*acc_io}; pa.phi_blocks = {pre};
+        Val acc = push(pa);
+        condbr(icmp(ICmp::Slt, I64(), j, nv), vbody, vdone);
+        cur_ = vbody;
+        Val last = bin(BinOp::Sub, I64(), nv, ci(I64(), 1));
+        Val ju = j, cur = acc;
+        std::vector<Val> vecs, guards;
+        for (int u = 0; u < 4; u++) {
+            if (u) ju = bin(BinOp::Add, I64(), ju, stride);
+            Val g = u ? icmp(ICmp::Slt, I64(), ju, nv) : Val();
+            Val jc = u ? select(I64(), g, ju, last) : ju;
+            Inst ld; ld.op = Opc::Load; ld.ty = v4; ld.space = Space::Global; ld.align = 16;
+            ld.ops = {bin(BinOp::Add, pg, p0, bin(BinOp::Mul, I64(), jc, ci(I64(), 16)))};
+            vecs.push_back(push(ld));
+            guards.push_back(g);
+        }
+        for (int u = 0; u < 4; u++) {
+            Val e[4];
+            for (unsigned l = 0; l < 4; l++) { Inst ex; ex.op = Opc::VecExtract; ex.ty = t; ex.sub = (uint8_t)l; ex.ops = {vecs[u]}; e[l] = push(ex); }
+            Val m4 = combine(op, El::I32, combine(op, El::I32, e[0], e[1]), combine(op, El::I32, e[2], e[3]));
+            Val folded = combine(op, El::I32, cur, m4);
+            cur = u ? select(t, guards[u], folded, cur) : folded;
+        }
+        Val jnext = bin(BinOp::Add, I64(), ju, stride);
+        uint32_t vend = cur_;
+        br(vhead);
+        f_.insts[j.idx].ops.push_back(jnext); f_.insts[j.idx].phi_blocks.push_back(vend);
+        f_.insts[acc.idx].ops.push_back(cur); f_.insts[acc.idx].phi_blocks.push_back(vend);
+        // ---- what the vectors left: lanes 4 nv .. cnt-1, one word per trip
+        cur_ = vdone;
+        Val l0 = bin(BinOp::Add, I64(), bin(BinOp::Shl, I64(), nv, ci(I64(), 2)), tid);
+        uint32_t spre = cur_, shead = new_block(), sbody = new_block(), sdone = new_block();
+        br(shead);
+        cur_ = shead;
+        Inst pl; pl.op = Opc::Phi; pl.ty = I64(); pl.ops = {l0}; pl.phi_blocks = {spre};
+        Val l = push(pl);
+        Inst ps2; ps2.op = Opc::Phi; ps2.ty = t; ps2.ops = {acc}; ps2.phi_blocks = {spre};
+        Val sacc = push(ps2);
+        condbr(icmp(ICmp::Slt, I64(), l, cnt), sbody, sdone);
+        cur_ = sbody;
+        Inst ld; ld.op = Opc::Load; ld.ty = t; ld.space = Space::Global; ld.align = 4;
+        ld.ops = {bin(BinOp::Add, pg, p0, bin(BinOp::Mul, I64(), l, ci(I64(), 4)))};
+        Val w = push(ld);
+        Val snext_acc = combine(op, El::I32, sacc, w);
+        Val lnext = bin(BinOp::Add, I64(), l, stride);
+        uint32_t send = cur_;
+        br(shead);
+        f_.insts[l.idx].ops.push_back(lnext); f_.insts[l.idx].phi_blocks.push_back(send);
+        f_.insts[sacc.idx].ops.push_back(snext_acc); f_.insts[sacc.idx].phi_blocks.push_back(send);
+        cur_ = sdone;
+        Val out = sacc;
+        if (x->has_mask && op != AtomOp::Add) {   // max and min are idempotent: the masked-off lanes' value counts once
+            Val some_off = icmp(ICmp::Slt, I64(), cnt, lanes);
+            out = select(t, some_off, combine(op, El::I32, sacc, ci(t, other)), sacc);
+        }
+        (void)identity; (void)i1;
+        scopes_.pop_back();
+        *acc_io = out;
+        return true;
+    }
+
     void reduce_to_atomic(AtomOp op, const NP& ptr, const NP& x, int line) {
         El el = x->el;
         Ty t = Ty::s(scalar_of(el));
@@ -1693,7 +1799,8 @@ private:
                 if (lane.guarded) folded = select(t, lane.guard, folded, acc[0]);   // a lane past the tile contributes nothing
                 return std::vector<Val>{folded};
             };
-        lane_loop(x->shape, line, [&](const Lane& lane) { return std::vector<Val>{gen(x, sub_idx(x, lane.idx))}; }, nullptr, &carried, &fold);
+        if (!fold_contiguous_i32(op, x, identity, &carried[0]))
+            lane_loop(x->shape, line, [&](const Lane& lane) { return std::vector<Val>{gen(x, sub_idx(x, lane.idx))}; }, nullptr, &carried, &fold);
         // warp step, then the warps of the CTA through shared memory, then one atomic per program
         auto warp_combine = [&](Val v) {
             if (el == El::I32) {

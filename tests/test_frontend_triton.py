@@ -122,7 +122,8 @@ def test_int32_sources_wrap_and_reduce(ptx, orc, tmp_path):
     bir = checked(ptx, kt.max_i32())
     assert bir.count("warp.reduce.max i32") == 2 and bir.count("atomic.max i32 ptr.global") == 1 and "shuffle" not in bir
     assert "shared_obj 0 bytes 128 align 16" in bir and bir.count("barrier") == 1
-    assert bir.count("load i32 ptr.global") == 8      # eight independent loads per loop iteration (a reduction has one load per lane)
+    # the program's lanes are consecutive int32 words: four 16-byte loads per loop iteration, a one-word loop for the rest
+    assert bir.count("load v4i32 ptr.global") == 4 and bir.count("load i32 ptr.global") == 1
     assert "phi i32" in bir and "const.i i32 -2147483648" in bir
     text = ptx.emit(bir).text
     assert "redux.sync.max.s32" in text

@@ -97,3 +97,37 @@ def test_kernel_written_with_helper_functions(gpu, level):
         fn.launch(programs, 128, 0, [dev(gpu, x), dev(gpu, y), out, b.i64(n), b.i64(block)])
         got = out.to_numpy(np.float32)
         assert np.array_equal(got[:n], np.float32(2.5) * x + y) and np.all(got[n:] == -1.0), (n, level)
+
+
+@pytest.mark.parametrize("op, np_red, other, init", [("max", np.max, "-2147483648", -2**31), ("min", np.min, "2147483647", 2**31 - 1),
+                                                     ("max", np.max, "5", -2**31), ("add", None, "0", 0)])
+def test_int32_reduction_takes_vectors_and_stays_exact(gpu, op, np_red, other, init):
+    # int32 reductions read the program's consecutive lanes as 16-byte vectors.  Ragged sizes (a last program that
+    # is partly or wholly masked off), a base that is not 16-byte aligned (the one-word loop takes everything), a
+    # block that is not a multiple of four, an `other` that changes the answer when a lane is masked off, and a
+    # sum that wraps must all give the bits of the lane-by-lane definition.
+    red = "sum" if op == "add" else op
+    src = f"@triton.jit\ndef red(x_ptr, out_ptr, n, BLOCK: tl.constexpr):\n    offs = tl.program_id(0) * BLOCK + tl.arange(0, BLOCK)\n" \
+          f"    tl.atomic_{op}(out_ptr, tl.{red}(tl.load(x_ptr + offs, mask=offs < n, other={other}), axis=0))\n"
+    bir = b.compile_triton(src, pointee={"x_ptr": "i32", "out_ptr": "i32"})
+    assert "load v4i32 ptr.global" in bir
+    fn = emitted(gpu, bir, "red")
+    for n, block, threads, shift in [(1 << 20, 8192, 128, 0), (100003, 2048, 128, 0), (100003, 2048, 128, 1), (5, 64, 32, 0), (777, 100, 64, 0), (4096, 1024, 256, 3),
+                                     (9000, 4096, 128, 0)]:
+        x = w.u32(n + 17, n + 4).view(np.int32)
+        if op == "max" and other == "5":
+            x = np.minimum(x, -1)                    # every element is negative: a masked-off lane's 5 must win when there is one
+        dx = dev(gpu, x)
+        out = dev(gpu, np.array([init], np.int32))
+        programs = (n + block - 1) // block
+        fn.launch(programs, threads, 0, [b.ptr(dx.device_ptr() + 4 * shift), out, b.i64(n), b.i64(block)])
+        data = x[shift:shift + n]
+        if op == "add":
+            want = int(data.astype(np.int64).sum() & 0xffffffff)
+            got = int(out.to_numpy(np.int32)[0]) & 0xffffffff
+        else:
+            want = int(np_red(data))
+            if programs * block > n:
+                want = max(want, int(other)) if op == "max" else min(want, int(other))
+            got = int(out.to_numpy(np.int32)[0])
+        assert got == want, (n, block, threads, shift)
