@@ -387,7 +387,7 @@ constexpr int B_HALF_BYTES = HALF_N * BK * 2, STAGE_BYTES3 = A_BYTES + B_HALF_BY
 enum Epilogue { DIRECT = 0, LINES = 1, BULK = 2 };
 constexpr int PIECE_BYTES = 32 * 128;   // 32 rows x 64 columns of f16
 // ring depth of the K-slab stages and staging pieces per epilogue warp: everything fits 227 KB
-__host__ __device__ constexpr int stages_of(int epi, bool deep) { return epi == BULK && deep ? 5 : 6; }
+__host__ __device__ constexpr int stages_of(int epi, bool deep, int tn = 256) { return tn == 128 ? 8 : epi == BULK && deep ? 5 : 6; }   // 24 KB stages when the tile is 128 wide
 __host__ __device__ constexpr int pieces_of(int epi, bool deep) { return epi == DIRECT ? 0 : epi == LINES ? 1 : deep ? 4 : 2; }
 constexpr int GROUP_M = 8;
 constexpr uint32_t TMEM_COLS3 = 512;
@@ -457,11 +457,15 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t sr
 
 // Over NVLink the difference between LINES and DIRECT is a line-sized against a 16-byte write per request,
 // which is why the fused gather needs at least LINES; BULK also takes the copies off the warps.
-template <bool B_IS_NK, int EPI, bool DEEP>
+// TILE_N = 256: the 256 x 256 tile.  TILE_N = 128: a 256 x 128 tile (each CTA stages 128 rows of A and 64 columns of B
+// per K slab, 24 KB; MMA M256 N128 K16): half the work per tile, so a row shard of few tiles (the 8-GPU split) starts
+// handing finished tiles to its epilogue -- and, in the fused gather, to NVLink -- after half the time.
+template <bool B_IS_NK, int EPI, bool DEEP, int TILE_N>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS3, 1)
     matmul_f16_tc_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, __half* __restrict__ C, int M, int N, int K,
                        int32_t* status, const PeerRows peers, const __grid_constant__ StoreMaps out) {
-    constexpr int STAGES = stages_of(EPI, DEEP), PIECES = pieces_of(EPI, DEEP);
+    constexpr int TN = TILE_N, HALF_N = TILE_N / 2, STAGE_BYTES3 = A_BYTES + HALF_N * BK * 2;   // shadow the 256-wide constants of the namespace
+    constexpr int STAGES = stages_of(EPI, DEEP, TILE_N), PIECES = pieces_of(EPI, DEEP);
     constexpr bool STAGED = EPI == LINES;
     const bool PUSH = peers.n > 0;
     extern __shared__ uint8_t smem_raw[];
@@ -516,7 +520,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS3, 1)
                     if (B_IS_NK) tma_load_2d_pair(b_dst, &map_b, fb, kb * BK, n0);   // box 64 k x 128 n
                     else {
 #pragma unroll
-                        for (int h = 0; h < 2; h++) tma_load_2d_pair(b_dst + h * 8192, &map_b, fb, n0 + 64 * h, kb * BK);   // box 64 n x 64 k
+                        for (int h = 0; h < HALF_N / 64; h++) tma_load_2d_pair(b_dst + h * 8192, &map_b, fb, n0 + 64 * h, kb * BK);   // box 64 n x 64 k
                     }
                     if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
@@ -770,11 +774,11 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, __half* C, i
 }
 
 
-template <bool B_IS_NK, int EPI, bool DEEP>
+template <bool B_IS_NK, int EPI, bool DEEP, int TILE_N = 256>
 int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, __half* C, int M, int N, int K, int32_t* status, cudaStream_t s, const v3::PeerRows& peers,
                 const v3::StoreMaps& out) {
-    constexpr int smem = v3::stages_of(EPI, DEEP) * v3::STAGE_BYTES3 + 1024 + 4 * v3::pieces_of(EPI, DEEP) * v3::PIECE_BYTES;
-    auto kern = v3::matmul_f16_tc_pair<B_IS_NK, EPI, DEEP>;
+    constexpr int smem = v3::stages_of(EPI, DEEP, TILE_N) * (A_BYTES + TILE_N / 2 * BK * 2) + 1024 + 4 * v3::pieces_of(EPI, DEEP) * v3::PIECE_BYTES;
+    auto kern = v3::matmul_f16_tc_pair<B_IS_NK, EPI, DEEP, TILE_N>;
     static int max_pairs = 0;
     if (!max_pairs) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -788,7 +792,7 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, __half* C, int M, 
         if (e != cudaSuccess || n < 1) { (void)cudaGetLastError(); n = basalt_k::sm_count() / 2; }
         max_pairs = n;
     }
-    const int tiles = (M / v3::TM) * (N / v3::TN);
+    const int tiles = (M / v3::TM) * (N / TILE_N);
     const int pairs = tiles < max_pairs ? tiles : max_pairs;
     kern<<<2 * pairs, v3::THREADS3, smem, s>>>(ma, mb, C, M, N, K, status, peers, out);
     return basalt_k::record(cudaGetLastError(), "matmul_f16");
@@ -810,6 +814,7 @@ int launch_pair_variant(int variant, const CUtensorMap& ma, const CUtensorMap& m
     for (int i = 0; i < n_peers; i++) peers.c[i] = (__half*)peer_c[i];
     if (variant == BASALT_K_MATMUL_PAIR_DIRECT) return launch_pair<B_IS_NK, v3::DIRECT, false>(ma, mb, (__half*)C, M, N, K, status, s, peers, v3::StoreMaps{});
     if (variant == BASALT_K_MATMUL_PAIR_LINES) return launch_pair<B_IS_NK, v3::LINES, false>(ma, mb, (__half*)C, M, N, K, status, s, peers, v3::StoreMaps{});
+    if (variant == BASALT_K_MATMUL_PAIR_LINES_NARROW) return launch_pair<B_IS_NK, v3::LINES, false, 128>(ma, mb, (__half*)C, M, N, K, status, s, peers, v3::StoreMaps{});
     v3::StoreMaps out = {};
     int rc = make_store_maps(&out, C, peer_c, n_peers, M, N);
     if (rc) return rc;
@@ -832,7 +837,7 @@ int matmul_f16_any(const void* A, const void* B, void* C, int M, int N, int K, i
         else if (pair_shape) variant = BASALT_K_MATMUL_PAIR_LINES;
         else variant = N % v2::BN2 == 0 ? BASALT_K_MATMUL_ONE_SM_256 : BASALT_K_MATMUL_ONE_CTA_128;
     }
-    if (variant < BASALT_K_MATMUL_ONE_CTA_128 || variant > BASALT_K_MATMUL_PAIR_BULK_DEEP) return basalt_k::record_msg(1, who, "unknown variant");
+    if (variant < BASALT_K_MATMUL_ONE_CTA_128 || variant > BASALT_K_MATMUL_PAIR_LINES_NARROW) return basalt_k::record_msg(1, who, "unknown variant");
     const bool is_pair = variant >= BASALT_K_MATMUL_PAIR_DIRECT;
     if (is_pair && !pair_shape) return basalt_k::record_msg(1, who, "the CTA-pair kernels need M and N to be multiples of 256");
     if (!is_pair && n_peers) return basalt_k::record_msg(1, who, "only the CTA-pair kernels store to peers");
@@ -842,7 +847,8 @@ int matmul_f16_any(const void* A, const void* B, void* C, int M, int N, int K, i
     if (rc) return rc;
     cudaStream_t s = (cudaStream_t)stream;
     if (is_pair) {   // 256 x 256 tiles on pairs of SMs
-        rc = b_is_nk ? make_map(&mb, B, (uint64_t)N, (uint64_t)K, BK, v3::HALF_N) : make_map(&mb, B, (uint64_t)K, (uint64_t)N, 64, BK);
+        rc = b_is_nk ? make_map(&mb, B, (uint64_t)N, (uint64_t)K, BK, variant == BASALT_K_MATMUL_PAIR_LINES_NARROW ? 64 : v3::HALF_N)
+                     : make_map(&mb, B, (uint64_t)K, (uint64_t)N, 64, BK);
         if (rc) return rc;
         return b_is_nk ? launch_pair_variant<true>(variant, ma, mb, C, M, N, K, status, s, peer_c, n_peers)
                        : launch_pair_variant<false>(variant, ma, mb, C, M, N, K, status, s, peer_c, n_peers);

@@ -571,24 +571,29 @@ int launch_impl(basalt_rt_function* fn, const uint32_t grid[3], const uint32_t b
         // a sparse last wave -- or a whole problem of less than half a wave -- runs as K-parts that fill the slots
         if (fn->tail_split && tail != 0 && tail * 2 <= slots) {
             uint32_t sp = slots / tail;
-            if (sp > 4) sp = 4;
+            // With a gathering epilogue the parts are made as small as allowed even when they no longer fit one wave:
+            // the tiles of the first wave of parts are then complete, and on their way to the peers, while the second
+            // wave still computes.
+            if (sp > 4 || n_peers > 0) sp = 4;
             while (sp > 1 && p.tail_k % (sp * 16) != 0) sp--;
             if (sp >= 2) { full = tiles - tail; split = sp; }
         }
         std::unique_lock<std::mutex> lock(ctx->mu, std::defer_lock);
         if (split > 1) lock.lock();
-        if (split > 1 && ctx->tail_slots < slots) {
+        // one 64 KB partial tile per part (a wave of parts at least), one ticket per split tile
+        const uint32_t need = std::max(slots, (tiles - full) * split);
+        if (split > 1 && ctx->tail_slots < need) {
             int rc = make_current(ctx);
             if (rc) return rc;
             if (ctx->tail_partials) { f.cuMemFree(ctx->tail_partials); f.cuMemFree(ctx->tail_tickets); ctx->tail_partials = ctx->tail_tickets = 0; ctx->tail_slots = 0; }
-            rc = check(f, "cuMemAlloc", f.cuMemAlloc(&ctx->tail_partials, (size_t)slots * 65536));
+            rc = check(f, "cuMemAlloc", f.cuMemAlloc(&ctx->tail_partials, (size_t)need * 65536));
             if (rc) return rc;
-            rc = check(f, "cuMemAlloc", f.cuMemAlloc(&ctx->tail_tickets, (size_t)slots * 4));
+            rc = check(f, "cuMemAlloc", f.cuMemAlloc(&ctx->tail_tickets, (size_t)need * 4));
             if (rc) { f.cuMemFree(ctx->tail_partials); ctx->tail_partials = 0; return rc; }
-            std::vector<uint32_t> zeros(slots, 0);
-            rc = check(f, "cuMemcpyHtoD", f.cuMemcpyHtoD(ctx->tail_tickets, zeros.data(), (size_t)slots * 4));
+            std::vector<uint32_t> zeros(need, 0);
+            rc = check(f, "cuMemcpyHtoD", f.cuMemcpyHtoD(ctx->tail_tickets, zeros.data(), (size_t)need * 4));
             if (rc) return rc;
-            ctx->tail_slots = slots;
+            ctx->tail_slots = need;
         }
         std::vector<void*> all(params, params + p.nparams);
         uint64_t ws = (uint64_t)ctx->tail_partials, tk = (uint64_t)ctx->tail_tickets;

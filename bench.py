@@ -779,8 +779,8 @@ def cfg_sgemm(env: Env) -> dict:
     out.update({"value_1gpu": fl / ms_e / 1e9, "handwritten_tflops": fl / ms_h / 1e9, "emitted_over_handwritten": ms_h / ms_e, "parity_1gpu": par, "handwritten_parity": par_h,
                 "roofline": {"bound": "fp32 fma pipe", "achieved": fl / ms_e / 1e9, "peak": fp32_peak, "unit": "TFLOP/s", "frac": fl / ms_e / 1e9 / fp32_peak,
                              "peak_source": f"nominal: {sms} SMs x 128 FFMA x 2 flop x {env.peaks['sm_max_mhz']:.0f} MHz (MEASURED_PEAKS.json holds no fp32 figure)",
-                             "kernel": "sgemm_f32 (emitted)", "kernel_ms": ms_e, "flop_per_launch": fl, "traffic": traffic_from_profile("sgemm_f32", fl)[0],
-                             "traffic_source": traffic_from_profile("sgemm_f32", fl)[1]}})
+                             "kernel": "sgemm_f32 (emitted)", "kernel_ms": ms_e, "flop_per_launch": fl, "traffic": traffic_from_profile("sgemm_f32", 3.0 * M * N * 4)[0],
+                             "traffic_source": traffic_from_profile("sgemm_f32", 3.0 * M * N * 4)[1]}})
     out["value"] = out["value_1gpu"]
     out["parity"] = par["parity"] and par_h["parity"]
     if env.world == 1:
@@ -846,8 +846,8 @@ def cfg_matmul(env: Env) -> dict:
                     "emitted_frac_of_nominal_2250": med["emitted"] / 2250.0, "parity_1gpu": par, "handwritten_parity": par_h,
                     "roofline": {"bound": "tensor", "achieved": med["emitted"], "peak": peak, "unit": "TFLOP/s", "frac": med["emitted"] / peak,
                                  "peak_source": env.peaks["source"] + ": cuBLAS bf16 burst (best of 10) of MEASURED_PEAKS.json; the kernel is timed alone in short bursts",
-                                 "kernel": "matmul_kernel__pair (emitted)", "kernel_ms": ms_e, "flop_per_launch": fl, "traffic": traffic_from_profile("matmul_f16", fl)[0],
-                                 "traffic_source": traffic_from_profile("matmul_f16", fl)[1]}})
+                                 "kernel": "matmul_kernel__pair (emitted)", "kernel_ms": ms_e, "flop_per_launch": fl, "traffic": traffic_from_profile("matmul_f16", 3.0 * M * N * 2)[0],
+                                 "traffic_source": traffic_from_profile("matmul_f16", 3.0 * M * N * 2)[1]}})
         out["emitted_regimes"] = best_and_sustained(env, go, fl)
         out["handwritten_regimes"] = best_and_sustained(env, hand, fl)
         out["cublas_f16_same_operands_regimes"] = best_and_sustained(env, cands["cublas_f16_same_operands"], fl)
@@ -917,6 +917,25 @@ def profile_one(args):
         em = lambda: fn.launch((m // 128, m // 128), 128, 0, [dp(A), dp(B), dp(C)], stream=stream)
         hw = lambda: kernels.matmul_f16(A.data_ptr(), B.data_ptr(), C.data_ptr(), m, m, m, False, st.data_ptr(), stream)
         size = {"M=N=K": m}
+    if name == "matmul_f16_forms":
+        # every form of the hand-written kernel and the emitted entry, CUDA events, medians of 4 interleaved rounds of 5 launches
+        forms = {v: (lambda v=v: kernels.matmul_f16_variant(A.data_ptr(), B.data_ptr(), C.data_ptr(), m, m, m, v, status=st.data_ptr(), stream=stream))
+                 for v in ("one_sm_256", "pair_direct", "pair_lines", "pair_bulk", "pair_bulk_deep", "pair_lines_narrow")}
+        forms["emitted"] = em
+        forms["cublas_f16_same_operands"] = lambda: torch.matmul(A, B, out=C)
+        rounds = {k: [] for k in forms}
+        for _ in range(4):
+            for k, f in forms.items():
+                for _ in range(2):
+                    f()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(5):
+                    f()
+                e1.record(); e1.synchronize()
+                rounds[k].append(2.0 * m**3 * 5 / e0.elapsed_time(e1) / 1e9)
+        emit_line({"profiling": name, "size": size, "tflops_median_of_4_rounds_of_5": {k: statistics.median(v) for k, v in rounds.items()}, "status": int(st.item())})
+        return
     for f in (em, hw):
         for _ in range(reps):
             f()
@@ -949,8 +968,9 @@ def main():
     ap.add_argument("--elements", type=int, default=N_MAX, help="int32 elements per GPU (profiling runs use a smaller case)")
     ap.add_argument("--nccl-exchange", action="store_true", help="at N > 1 use ncclAllReduce for the 4-byte exchange instead of the peer-memory kernel")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer and CPU-baseline legs (profiling runs)")
-    ap.add_argument("--profile", default=None, choices=["max_i32", "vadd_i32", "helper_chain", "sgemm_f32", "matmul_f16"],
-                    help="run only this workload's emitted and hand-written kernels a few times on a small case (for ncu) and exit")
+    ap.add_argument("--profile", default=None, choices=["max_i32", "vadd_i32", "helper_chain", "sgemm_f32", "matmul_f16", "matmul_f16_forms"],
+                    help="run only this workload's emitted and hand-written kernels a few times on a small case (for ncu) and exit; "
+                         "matmul_f16_forms times every form of the fp16 matmul kernels with CUDA events instead")
     ap.add_argument("--size", type=int, default=0, help="problem size for --profile (elements, or the matrix dimension)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

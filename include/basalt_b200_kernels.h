@@ -141,7 +141,8 @@ enum {
     BASALT_K_MATMUL_PAIR_DIRECT = 3,
     BASALT_K_MATMUL_PAIR_LINES = 4,
     BASALT_K_MATMUL_PAIR_BULK = 5,
-    BASALT_K_MATMUL_PAIR_BULK_DEEP = 6
+    BASALT_K_MATMUL_PAIR_BULK_DEEP = 6,
+    BASALT_K_MATMUL_PAIR_LINES_NARROW = 7   /* PAIR_LINES on 256x128 tiles (MMA M256 N128 K16, eight 24 KB stages) */
 };
 int basalt_k_matmul_f16_variant(const void *A, const void *B, void *C, int M, int N, int K, int b_is_nk, int variant,
                                 void *const *peer_c, int n_peers, int32_t *status, void *stream);

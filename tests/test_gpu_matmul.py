@@ -166,7 +166,7 @@ def test_matmul_f16_full_size(gpu, orc, how):
     assert np.linalg.norm(lhs - rhs) / np.linalg.norm(rhs) <= F16_TOL
 
 
-PAIR_VARIANTS = ["pair_direct", "pair_lines", "pair_bulk", "pair_bulk_deep"]
+PAIR_VARIANTS = ["pair_direct", "pair_lines", "pair_bulk", "pair_bulk_deep", "pair_lines_narrow"]
 
 
 @pytest.mark.parametrize("b_is_nk", [True, False])
@@ -193,7 +193,7 @@ def test_matmul_f16_kernel_forms_agree(gpu, b_is_nk, shape):
         assert np.array_equal(got, results["one_cta_128"]), variant
 
 
-@pytest.mark.parametrize("variant", ["pair_direct", "pair_lines", "pair_bulk", "pair_bulk_deep", "auto"])
+@pytest.mark.parametrize("variant", ["pair_direct", "pair_lines", "pair_bulk", "pair_bulk_deep", "pair_lines_narrow", "auto"])
 @pytest.mark.parametrize("n_peers", [1, 7])
 def test_fused_gather_into_loop_back_peers(gpu, orc, variant, n_peers):
     # The fused matmul + gather on ONE GPU: the "peers" are further buffers of this GPU, so the peer
@@ -252,10 +252,11 @@ def test_emitted_fused_gather_into_loop_back_peers_f16(gpu, orc, n_peers):
         assert np.array_equal(got[row0:row0 + rows].view(np.uint16), first)
 
 
-@pytest.mark.parametrize("shape", [(256, 256, 64), (2560, 1920, 64)])
+@pytest.mark.parametrize("shape", [(256, 256, 64), (2560, 1920, 64), (512, 4096, 256)])
 def test_emitted_fused_gather_into_loop_back_peers_f32(gpu, shape):
     # the FFMA matmul's gathering epilogue, whole tiles and the split tail wave (300 tiles: the last four
-    # are summed from K-parts by the part that finishes last, which then stores to every buffer)
+    # are summed from K-parts by the part that finishes last, which then stores to every buffer); the third
+    # shape is an 8-GPU shard: 128 tiles, less than half a wave, run as 512 quarter-K parts (more than one wave)
     rows, N, K = shape
     A, B, _ = sgemm_fixture(rows, N, K)
     want = (A.astype(np.int64) @ B.astype(np.int64)).astype(np.float32)
