@@ -39,7 +39,13 @@ __device__ __forceinline__ void cp_async(void* smem_dst, const void* gmem_src) {
 
 constexpr int BM = 128, BN = 128, BK = 16, THREADS = 256;
 
-template <bool REG_STAGE>
+// WARP_ROWS: how the 128 x 128 tile is cut into per-thread 64-output blocks.  false: an 8 x 8 block as four 4 x 4
+// quadrants (rows ty*4 + {0..3} + {0, 64}, columns tx*4 + {0..3} + {0, 64}; a warp is 2 x 16 threads).  true: a 16 x 4
+// block -- warp w owns rows 16w .. 16w+15 of the tile over all 128 columns, lane l columns 4l .. 4l+3 -- so that the
+// four A fragments of a K step are the same address for the whole warp (pure broadcasts, one shared-memory wavefront
+// each) and the one B fragment is 512 contiguous bytes (four wavefronts): eight wavefronts per K step instead of
+// thirteen, and a warp's stores are whole 512-byte rows.
+template <bool REG_STAGE, bool WARP_ROWS>
 __global__ void __launch_bounds__(THREADS, 2) sgemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C,
                                                                int M, int N, int K, int full_tiles, int split, float* __restrict__ workspace,
                                                                unsigned* __restrict__ tickets) {
@@ -85,11 +91,16 @@ __global__ void __launch_bounds__(THREADS, 2) sgemm_f32_kernel(const float* __re
         Ag0 += BK; Ag1 += BK; Bg0 += b_step; Bg1 += b_step;
     };
 
-    float2 acc2[8][4];   // acc2[i][p] = (C[i][2p], C[i][2p+1]) of the thread's 8 x 8 block
+    constexpr int RI = WARP_ROWS ? 16 : 8, PJ = WARP_ROWS ? 2 : 4;
+    const int lane = tid & 31, wrp = tid >> 5;
+    float2 acc2[RI][PJ];   // acc2[i][p] = (C[i][2p], C[i][2p+1]) of the thread's block
 #pragma unroll
-    for (int i = 0; i < 8; i++)
+    for (int i = 0; i < RI; i++)
 #pragma unroll
-        for (int p = 0; p < 4; p++) acc2[i][p] = make_float2(0.0f, 0.0f);
+        for (int p = 0; p < PJ; p++) acc2[i][p] = make_float2(0.0f, 0.0f);
+    // position of output row i / first column of the thread's block inside the tile
+    auto out_row = [&](int i) { return WARP_ROWS ? wrp * 16 + i : ty * 4 + (i & 3) + (i >> 2) * 64; };
+    const int out_col = WARP_ROWS ? lane * 4 : tx * 4;
 
     // REG_STAGE: the next slab is loaded into four float4 registers before the multiply and stored to the other
     // half of the double buffer after it (the transposed A slab as eight 4-byte stores), instead of 4-byte cp.async
@@ -115,6 +126,23 @@ __global__ void __launch_bounds__(THREADS, 2) sgemm_f32_kernel(const float* __re
         if (kb + 1 < nk) { if (REG_STAGE) fetch(); else copy_slab(buf ^ 1); }   // lands while this slab is multiplied
 #pragma unroll
         for (int k = 0; k < BK; k++) {
+            if constexpr (WARP_ROWS) {
+                const int sw = ((k >> 2) & 3) << 3;
+                const float4 b0 = *reinterpret_cast<const float4*>(&Bs[buf][k][lane * 4]);
+                const float2 bp0 = make_float2(b0.x, b0.y), bp1 = make_float2(b0.z, b0.w);
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    const float4 aq = *reinterpret_cast<const float4*>(&As[buf][k][(wrp * 16 + q * 4) ^ sw]);
+                    const float a[4] = {aq.x, aq.y, aq.z, aq.w};
+#pragma unroll
+                    for (int r = 0; r < 4; r++) {
+                        const float2 ai = make_float2(a[r], a[r]);
+                        acc2[q * 4 + r][0] = __ffma2_rn(ai, bp0, acc2[q * 4 + r][0]);
+                        acc2[q * 4 + r][1] = __ffma2_rn(ai, bp1, acc2[q * 4 + r][1]);
+                    }
+                }
+                continue;
+            }
             const int m = (ty * 4) ^ (((k >> 2) & 3) << 3);
             const float4 a0 = *reinterpret_cast<const float4*>(&As[buf][k][m]);
             const float4 a1 = *reinterpret_cast<const float4*>(&As[buf][k][m + 64]);
@@ -122,11 +150,13 @@ __global__ void __launch_bounds__(THREADS, 2) sgemm_f32_kernel(const float* __re
             const float4 b1 = *reinterpret_cast<const float4*>(&Bs[buf][k][tx * 4 + 64]);
             const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
             const float2 b[4] = {make_float2(b0.x, b0.y), make_float2(b0.z, b0.w), make_float2(b1.x, b1.y), make_float2(b1.z, b1.w)};
+            if constexpr (!WARP_ROWS) {
 #pragma unroll
-            for (int i = 0; i < 8; i++) {
-                const float2 ai = make_float2(a[i], a[i]);
+                for (int i = 0; i < 8; i++) {
+                    const float2 ai = make_float2(a[i], a[i]);
 #pragma unroll
-                for (int p = 0; p < 4; p++) acc2[i][p] = __ffma2_rn(ai, b[p], acc2[i][p]);
+                    for (int p = 0; p < 4; p++) acc2[i][p] = __ffma2_rn(ai, b[p], acc2[i][p]);
+                }
             }
         }
         if (REG_STAGE) { if (kb + 1 < nk) stash(buf ^ 1); }
@@ -138,10 +168,10 @@ __global__ void __launch_bounds__(THREADS, 2) sgemm_f32_kernel(const float* __re
         const int t = tile - full_tiles;
         float* mine = workspace + ((size_t)t * parts + part) * (BM * BN);
 #pragma unroll
-        for (int i = 0; i < 8; i++) {
-            float* prow = mine + (ty * 4 + (i & 3) + (i >> 2) * 64) * BN + tx * 4;
+        for (int i = 0; i < RI; i++) {
+            float* prow = mine + out_row(i) * BN + out_col;
             *reinterpret_cast<float4*>(prow) = make_float4(acc2[i][0].x, acc2[i][0].y, acc2[i][1].x, acc2[i][1].y);
-            *reinterpret_cast<float4*>(prow + 64) = make_float4(acc2[i][2].x, acc2[i][2].y, acc2[i][3].x, acc2[i][3].y);
+            if constexpr (!WARP_ROWS) *reinterpret_cast<float4*>(prow + 64) = make_float4(acc2[i][PJ - 2].x, acc2[i][PJ - 2].y, acc2[i][PJ - 1].x, acc2[i][PJ - 1].y);
         }
         __threadfence();
         __syncthreads();
@@ -151,26 +181,25 @@ __global__ void __launch_bounds__(THREADS, 2) sgemm_f32_kernel(const float* __re
         __threadfence();
         const float* base = workspace + (size_t)t * parts * (BM * BN);
 #pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const int off = (ty * 4 + (i & 3) + (i >> 2) * 64) * BN + tx * 4;
-            float4 lo = __ldcg(reinterpret_cast<const float4*>(base + off)), hi = __ldcg(reinterpret_cast<const float4*>(base + off + 64));
+        for (int i = 0; i < RI; i++) {
+            const int off = out_row(i) * BN + out_col, hi_off = WARP_ROWS ? 0 : 64;
+            float4 lo = __ldcg(reinterpret_cast<const float4*>(base + off)), hi = __ldcg(reinterpret_cast<const float4*>(base + off + hi_off));
             for (int p = 1; p < parts; p++) {   // parts are added in index order, whichever finished last
                 const float4 l2 = __ldcg(reinterpret_cast<const float4*>(base + (size_t)p * (BM * BN) + off));
-                const float4 h2 = __ldcg(reinterpret_cast<const float4*>(base + (size_t)p * (BM * BN) + off + 64));
+                const float4 h2 = __ldcg(reinterpret_cast<const float4*>(base + (size_t)p * (BM * BN) + off + hi_off));
                 lo.x += l2.x; lo.y += l2.y; lo.z += l2.z; lo.w += l2.w;
                 hi.x += h2.x; hi.y += h2.y; hi.z += h2.z; hi.w += h2.w;
             }
             acc2[i][0] = make_float2(lo.x, lo.y); acc2[i][1] = make_float2(lo.z, lo.w);
-            acc2[i][2] = make_float2(hi.x, hi.y); acc2[i][3] = make_float2(hi.z, hi.w);
+            if constexpr (!WARP_ROWS) { acc2[i][PJ - 2] = make_float2(hi.x, hi.y); acc2[i][PJ - 1] = make_float2(hi.z, hi.w); }
         }
         if (tid == 0) tickets[t] = 0;   // ready for the next launch
     }
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
-        const int row = m0 + ty * 4 + (i & 3) + (i >> 2) * 64;
-        float* crow = C + (size_t)row * N + n0 + tx * 4;
+    for (int i = 0; i < RI; i++) {
+        float* crow = C + (size_t)(m0 + out_row(i)) * N + n0 + out_col;
         *reinterpret_cast<float4*>(crow) = make_float4(acc2[i][0].x, acc2[i][0].y, acc2[i][1].x, acc2[i][1].y);
-        *reinterpret_cast<float4*>(crow + 64) = make_float4(acc2[i][2].x, acc2[i][2].y, acc2[i][3].x, acc2[i][3].y);
+        if constexpr (!WARP_ROWS) *reinterpret_cast<float4*>(crow + 64) = make_float4(acc2[i][PJ - 2].x, acc2[i][PJ - 2].y, acc2[i][PJ - 1].x, acc2[i][PJ - 1].y);
     }
 }
 
@@ -225,7 +254,7 @@ extern "C" int basalt_k_sgemm_f32_variant(const float* A, const float* B, float*
     if (M % BM || N % BN || K % BK) return basalt_k::record_msg(1, "sgemm_f32", "M and N must be multiples of 128 and K of 16");
     if (((uintptr_t)A | (uintptr_t)B | (uintptr_t)C) & 15) return basalt_k::record_msg(1, "sgemm_f32", "matrices must be 16-byte aligned");
     static int resident = 0;
-    if (!resident) resident = basalt_k::resident_ctas(sgemm_f32_kernel<true>, THREADS);
+    if (!resident) resident = basalt_k::resident_ctas(sgemm_f32_kernel<true, false>, THREADS);
     const int tiles = (M / BM) * (N / BN), slots = resident * basalt_k::sm_count();
     int full = tiles, split = 1;
     if (!(flags & BASALT_K_SGEMM_NO_TAIL_SPLIT)) plan_tail(tiles, slots, K, &full, &split);
@@ -236,8 +265,10 @@ extern "C" int basalt_k_sgemm_f32_variant(const float* A, const float* B, float*
     }
     const int grid = full + (tiles - full) * split;
     if (flags & BASALT_K_SGEMM_CP_ASYNC)   // the earlier staging with 4-byte cp.async copies
-        sgemm_f32_kernel<false><<<grid, THREADS, 0, (cudaStream_t)stream>>>(A, B, C, M, N, K, full, split, w ? w->partials : nullptr, w ? w->tickets : nullptr);
-    else sgemm_f32_kernel<true><<<grid, THREADS, 0, (cudaStream_t)stream>>>(A, B, C, M, N, K, full, split, w ? w->partials : nullptr, w ? w->tickets : nullptr);
+        sgemm_f32_kernel<false, false><<<grid, THREADS, 0, (cudaStream_t)stream>>>(A, B, C, M, N, K, full, split, w ? w->partials : nullptr, w ? w->tickets : nullptr);
+    else if (flags & BASALT_K_SGEMM_WARP_ROWS)
+        sgemm_f32_kernel<true, true><<<grid, THREADS, 0, (cudaStream_t)stream>>>(A, B, C, M, N, K, full, split, w ? w->partials : nullptr, w ? w->tickets : nullptr);
+    else sgemm_f32_kernel<true, false><<<grid, THREADS, 0, (cudaStream_t)stream>>>(A, B, C, M, N, K, full, split, w ? w->partials : nullptr, w ? w->tickets : nullptr);
     return basalt_k::record(cudaGetLastError(), "sgemm_f32");
 }
 
@@ -271,7 +302,7 @@ extern "C" int basalt_k_sgemm_f32_static_workspace(const float* A, const float* 
         w.base = p;
     }
     static int resident = 0;
-    if (!resident) resident = basalt_k::resident_ctas(sgemm_f32_kernel<true>, THREADS);
+    if (!resident) resident = basalt_k::resident_ctas(sgemm_f32_kernel<true, false>, THREADS);
     const int tiles = (M / BM) * (N / BN), slots = resident * basalt_k::sm_count();
     int full = tiles, split = 1;
     plan_tail(tiles, slots, K, &full, &split);
@@ -289,6 +320,6 @@ extern "C" int basalt_k_sgemm_f32_static_workspace(const float* A, const float* 
         if (e != cudaSuccess) return basalt_k::record(e, "sgemm_f32_static_workspace (cudaMemsetAsync)");
     }
     const int grid = full + tail * split;
-    sgemm_f32_kernel<true><<<grid, THREADS, 0, (cudaStream_t)stream>>>(A, B, C, M, N, K, full, split, partials, tickets);
+    sgemm_f32_kernel<true, false><<<grid, THREADS, 0, (cudaStream_t)stream>>>(A, B, C, M, N, K, full, split, partials, tickets);
     return basalt_k::record(cudaGetLastError(), "sgemm_f32_static_workspace");
 }

@@ -84,6 +84,7 @@ def fill(kind: str, seed: int, n: int, out, start: int = 0, stream=None):
     _check(lib.basalt_k_fill(FILL_KINDS[kind], seed, start, n, _p(out), C.c_void_p(stream)))
 
 
-def sgemm_f32_variant(A, B, Cm, M: int, N: int, K: int, no_tail_split: bool = False, cp_async: bool = False, stream=None):
-    """basalt_k_sgemm_f32_variant: the hand-written SGEMM with parts of its schedule switched off (A/B timing)."""
-    _check(lib.basalt_k_sgemm_f32_variant(_p(A), _p(B), _p(Cm), M, N, K, (1 if no_tail_split else 0) | (2 if cp_async else 0), C.c_void_p(stream)))
+def sgemm_f32_variant(A, B, Cm, M: int, N: int, K: int, no_tail_split: bool = False, cp_async: bool = False, warp_rows: bool = False, stream=None):
+    """basalt_k_sgemm_f32_variant: the hand-written SGEMM with parts of its schedule switched (A/B timing)."""
+    flags = (1 if no_tail_split else 0) | (2 if cp_async else 0) | (4 if warp_rows else 0)
+    _check(lib.basalt_k_sgemm_f32_variant(_p(A), _p(B), _p(Cm), M, N, K, flags, C.c_void_p(stream)))

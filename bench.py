@@ -739,6 +739,31 @@ def sharded_gather_variants(env: Env, kind: str, M: int, N: int, K: int, A_full,
             pg.close()
             ms = variants[f"emitted_pushed_gather_bands{bands}"]["ms"]
             best = ms if best is None or ms < best else best
+        if world == 2 and M == 8192:
+            # The 8-GPU traffic between two GPUs: a 1024-row shard (what a rank owns at N = 8) whose every tile is stored
+            # seven times into the peer's buffer, so that each GPU sends and receives the 112 MiB it would at N = 8.
+            # Timing only (the seven copies land in row blocks that do not belong to either rank's real shard).
+            rows8 = M // 8
+            f8 = env.emitted(kb.matmul_f16(rows8, N, K), "matmul_kernel")
+            prm8 = [env.dp(A_full[rank * rows8:(rank + 1) * rows8]), env.dp(B_), b.ptr(Cbuf.device_ptr() + rank * rows8 * N * esz)]
+            blocks8 = [ptrs[1 - rank] + ((rank * 7 + i) % 8) * rows8 * N * esz for i in range(7)]
+            go8 = f8.bind((N // 128, rows8 // 128), 128, 0, prm8, stream=env.stream)
+            go8_gather = f8.bind_gather((N // 128, rows8 // 128), 128, 0, prm8, blocks8, stream=env.stream)
+
+            def fused8():
+                go8_gather()
+                barrier_kernel()
+
+            def push8():
+                for p_ in blocks8:
+                    ctx.copy_device_async(p_, prm8[2].value, rows8 * N * esz, env.stream)
+                barrier_kernel()
+            out["eight_gpu_volume_between_two_gpus"] = {"rows": rows8, "copies_to_the_peer": 7, "bytes_out_per_gpu": 7 * rows8 * N * esz,
+                                                        "compute_only_ms": env.timed(go8, 10), "emitted_fused_gather_ms": env.timed(fused8, 10),
+                                                        "copy_engine_push_only_ms": env.timed(push8, 10)}
+            e8 = out["eight_gpu_volume_between_two_gpus"]
+            e8["copy_engine_GBs_per_direction"] = e8["bytes_out_per_gpu"] / e8["copy_engine_push_only_ms"] / 1e6
+            e8["fused_GBs_per_direction_after_first_wave"] = e8["bytes_out_per_gpu"] / max(1e-9, e8["emitted_fused_gather_ms"] - e8["compute_only_ms"] / 2) / 1e6
     else:
         out["status"] = 0
     out["variants"] = variants

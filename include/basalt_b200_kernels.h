@@ -59,7 +59,7 @@ int basalt_k_sgemm_f32(const float *A, const float *B, float *C, int M, int N, i
  * tile whole (no split-K parts for a sparse last wave or for a problem smaller than one wave); CP_ASYNC
  * stages the A slab with 4-byte cp.async copies instead of through registers.  flags = 0 is
  * basalt_k_sgemm_f32.  No counterpart in the reference. */
-enum { BASALT_K_SGEMM_NO_TAIL_SPLIT = 1, BASALT_K_SGEMM_CP_ASYNC = 2 };
+enum { BASALT_K_SGEMM_NO_TAIL_SPLIT = 1, BASALT_K_SGEMM_CP_ASYNC = 2, BASALT_K_SGEMM_WARP_ROWS = 4 };
 int basalt_k_sgemm_f32_variant(const float *A, const float *B, float *C, int M, int N, int K, int flags, void *stream);
 
 /* basalt_k_sgemm_f32 with the split-K workspace of its tail wave in a static device array instead

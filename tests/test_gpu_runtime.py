@@ -85,3 +85,21 @@ def test_peer_exchange_wait_runs_out_and_reports_it(gpu):
         # this rank's word did reach the silent inbox (parity row, column = sender's rank)
         assert silent.to_numpy(np.uint64)[(epoch & 1) * 8 + 0] == (epoch << 32 | 1234567)
     assert np.array_equal(gpu.upload(np.arange(8, dtype=np.int32)).to_numpy(np.int32), np.arange(8))
+
+
+def test_launch_policies_are_switched_per_handle_not_by_environment(gpu, monkeypatch):
+    # basalt_rt_function_tune: the A/B switches are arguments; an unknown key is refused, and the
+    # environment variables earlier builds read change nothing
+    monkeypatch.setenv("BASALT_RT_COARSE_WAVES", "1")
+    fn = emitted(gpu, kb.load("vadd_i32"), "vadd_i32")
+    n = 100003
+    a, c = np.arange(n, dtype=np.int32), gpu.upload(np.zeros(n, np.int32))
+    da = gpu.upload(a)
+    for waves in (0, 1, 3):
+        fn.tune("coarse_waves", waves)
+        c.copy_from_host(np.zeros(n, np.int32))
+        fn.launch((n + 255) // 256, 256, 0, [da, da, c, b.i32(n)])
+        assert np.array_equal(c.to_numpy(np.int32), 2 * a), waves
+    with pytest.raises(b.CudaError) as e:
+        fn.tune("no_such_policy", 1)
+    assert e.value.kind == 4
