@@ -125,6 +125,12 @@ class RankGroup:
         handles = self.all_gather_bytes(buf.ipc_handle())
         return [buf.device_ptr() if r == self.rank else ctx.ipc_open(handles[r]) for r in range(self.world)]
 
+    def peer_order(self) -> list[int]:
+        """The other ranks, starting with the next one: rank + 1, rank + 2, ... (mod world).  A rank that sends
+        something to every peer in this order makes every step of the exchange a permutation -- at each moment
+        no two ranks send to the same receiver -- instead of all ranks starting on rank 0's ingress ports."""
+        return [(self.rank + k) % self.world for k in range(1, self.world)]
+
     def shard(self, total: int, align: int = 1) -> tuple[int, int]:
         return shard_range(total, self.world, self.rank, align)
 

@@ -672,7 +672,7 @@ def sharded_gather_variants(env: Env, kind: str, M: int, N: int, K: int, A_full,
         torch.cuda.synchronize(); group.barrier()
 
     mine = Cbuf.device_ptr() + r0 * N * esz
-    others = [ptrs[r] + r0 * N * esz for r in range(world) if r != rank]
+    others = [ptrs[r] + r0 * N * esz for r in group.peer_order()]      # rank + 1 first: every step of the gather is a permutation
     if kind == "sgemm":
         fn = env.emitted(kb.sgemm_cta128(Ml, N, K), "sgemm_f32"); block = 256
     else:
@@ -697,11 +697,23 @@ def sharded_gather_variants(env: Env, kind: str, M: int, N: int, K: int, A_full,
     out["compute_only_fraction_of_linear"] = compute_1gpu_ms / world / ms_compute if compute_1gpu_ms else None
 
     # copy-engine floor: the shard pushed to every peer by cuMemcpyDtoDAsync, nothing else running
-    def push_only():
-        for p_ in others:
-            ctx.copy_device_async(p_, mine, Ml * N * esz, env.stream)
+    push_streams = [ctx.create_stream() for _ in others]
+    push_start, push_done = ctx.create_event(), [ctx.create_event() for _ in others]
+
+    def push_only():      # every peer's copy on its own stream (its own copy engine and links), gathered back on the timing stream
+        ctx.record(push_start, env.stream)
+        for p_, s_, e_ in zip(others, push_streams, push_done):
+            ctx.stream_wait_event(s_, push_start)
+            ctx.copy_device_async(p_, mine, Ml * N * esz, s_)
+            ctx.record(e_, s_)
+            ctx.stream_wait_event(env.stream, e_)
         barrier_kernel()
     ms_push = env.timed(push_only, 10)
+    torch.cuda.synchronize()
+    for s_ in push_streams:
+        ctx.destroy_stream(s_)
+    for e_ in push_done + [push_start]:
+        ctx.destroy_event(e_)
     out["copy_engine_push_only_ms"] = ms_push
     out["copy_engine_push_GBs_out_per_gpu"] = (world - 1) * Ml * N * esz / ms_push / 1e6
 

@@ -167,7 +167,9 @@ int basalt_rt_launch(basalt_rt_function *fn, const uint32_t grid[3], const uint3
  * offset, behind each peer address over NVLink (plain line-sized stores from the SMs while the next
  * tile is being computed; no copy engine, no library collective), and ends with a system-scope
  * fence.  A stream-ordered basalt_rt_peer_allreduce_max_i32 afterwards is the barrier after which
- * every rank holds every rank's rows.  Only kernels the emitter lowered with a gathering epilogue
+ * every rank holds every rank's rows.  The peers are served in the order given: pass rank + 1,
+ * rank + 2, ... (mod the group size), so that at every moment no two ranks store into the same
+ * receiver.  Only kernels the emitter lowered with a gathering epilogue
  * take it (the fp32 FFMA matmul; the fp16 tcgen05 matmul through its two-SM entry, so the grid must
  * be even in x and y); any other kernel is refused (kind 4).  No counterpart in the reference, which
  * has no multi-GPU path (crates/basalt-runtime/src/ffi.rs:38-42). */

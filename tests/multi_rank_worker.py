@@ -139,7 +139,7 @@ def main():
     st, flag = ctx.upload(np.zeros(1, np.int32)), ctx.upload(np.zeros(2, np.int32))
     ptrs = group.map_peers(ctx, dC)
     group.barrier()      # every rank's buffer holds its NaN fill before anyone stores into it
-    others = [ptrs[r] + r0 * N * 2 for r in range(group.world) if r != group.rank]
+    others = [ptrs[r] + r0 * N * 2 for r in group.peer_order()]
     for _ in range(3):
         kernels.matmul_f16_allgather(dA, dB, dC.device_ptr() + r0 * N * 2, Ml, N, K, others, status=st)
         peers.allreduce_max_i32(flag.device_ptr(), flag.device_ptr() + 4, None)      # the barrier: all ranks' stores have landed
@@ -176,7 +176,7 @@ def main():
             fn = ctx.load_module(ptx.emit(kb.sgemm_cta128(Ml, N, K)).text).get_function("sgemm_f32")
             block = 256
         go = fn.bind_gather((N // 128, Ml // 128), block, 0, [dA, dB, b.ptr(dC.device_ptr() + r0 * N * esz)],
-                            [ptrs[r] + r0 * N * esz for r in range(group.world) if r != group.rank])
+                            [ptrs[r] + r0 * N * esz for r in group.peer_order()])
         for _ in range(3):
             go()
             peers.allreduce_max_i32(flag.device_ptr(), flag.device_ptr() + 4, None)      # the barrier: all ranks' stores have landed

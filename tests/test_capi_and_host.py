@@ -118,3 +118,13 @@ def test_cli_follows_the_reference_conventions(tmp_path):
     assert r.returncode == 1 and r.stderr.startswith("E100: ")
     r = subprocess.run([cli, "--ir", str(src)], capture_output=True, text=True)
     assert r.returncode == 0 and "load v4i32" in r.stdout
+
+
+def test_peer_order_makes_every_step_of_an_exchange_a_permutation():
+    from basalt_b200.sharding import RankGroup
+    for world in (2, 4, 8):
+        orders = [RankGroup(rank=r, world=world).peer_order() for r in range(world)]
+        for r, o in enumerate(orders):
+            assert sorted(o) == [x for x in range(world) if x != r]
+        for step in range(world - 1):       # at each step no two ranks address the same receiver
+            assert sorted(o[step] for o in orders) == list(range(world))
