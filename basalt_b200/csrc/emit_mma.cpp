@@ -984,7 +984,7 @@ bool matmul_tcgen05_persistent(const MmaSite& s, std::vector<std::string>* decls
              // an eighth tmap field gives the matrix's row count, so that the tensor map clamps: a constant, or the
              // caller's grid extent in x or y times the tile rows (A has 128 rows per grid row; B stored [N x K] has
              // 128 rows per grid column, B stored [K x N] has K rows)
-             "//!basalt.plan %s logical_block=128,1,1 block=192,1,1 smem=%u params=%u tmap=%d:2:%lld:%lld:64:128:128:y128 tmap=%d:2:%lld:%lld:64:%d:128:%s status=1 lgrid=2 pair=%s__pair gather=%d",
+             "//!basalt.plan %s logical_block=128,1,1 block=192,1,1 smem=%u params=%u tmap=%d:2:%lld:%lld:64:128:128:y128 tmap=%d:2:%lld:%lld:64:%d:128:%s status=1 lgrid=2 pair=%s__pair pair_block=256 gather=%d",
              s.kernel.c_str(), smem, s.nparams, s.a_param, lda, lda * 2, s.b_param, ldb, ldb * 2, b_nk ? 128 : 64, b_nk ? "x128" : std::to_string(in.k).c_str(), s.kernel.c_str(), s.d_param);
     plan->push_back(pl);
     return true;
@@ -1022,7 +1022,7 @@ bool matmul_tcgen05_pair(const MmaSite& s, std::vector<std::string>* decls, std:
     std::string b32 = "\t.reg .b32 ";
     for (const char* n : {"tid", "warp", "lane", "t", "u", "tiles", "bars", "slot", "gu", "tmem", "ok", "kb", "s", "ph", "par", "full", "empty", "fb", "adst", "bdst", "m0", "n0",
                           "x", "it", "g", "lgx", "lgy", "tm", "tn", "ntiles", "perband", "band", "first", "rows", "rr", "mi", "nj", "tile", "gstep", "local",
-                          "buf", "use", "bar2", "acc", "ew", "c", "src", "spin", "rank", "zero", "idesc", "np", "pi"})
+                          "buf", "use", "bar2", "acc", "ew", "c", "src", "spin", "rank", "zero", "idesc", "np", "pi", "ts", "want", "row"})
         b32 += P + n + ", ";
     b32 += P + "h<16>, " + P + "v<32>, " + P + "wo<8>, " + P + "ro<8>, " + P + "rb<32>;";
     decls->push_back(b32);
@@ -1032,13 +1032,13 @@ bool matmul_tcgen05_pair(const MmaSite& s, std::vector<std::string>* decls, std:
     decls->push_back(b64);
     decls->push_back("\t.reg .b16 " + P + "both;");
     std::string pr = "\t.reg .pred ";
-    for (const char* n : {"p", "q", "w0", "w1", "l0", "prod", "mma", "epi", "accp", "done", "all", "lead", "pk"}) pr += P + n + ", ";
+    for (const char* n : {"p", "q", "w0", "w1", "l0", "prod", "mma", "epi", "accp", "done", "all", "lead", "pk", "relay"}) pr += P + n + ", ";
     pr += P + "unused;";
     decls->push_back(pr);
     char d[256];
     snprintf(d, sizeof d, "\t.shared .align 8 .b8 __mq%d_bars[%d];", u, TEMPTY + 16);   // full[6], empty[6], tfull[2], tempty[2]
     decls->push_back(d);
-    snprintf(d, sizeof d, "\t.shared .align 4 .b8 __mq%d_misc[8];", u);
+    snprintf(d, sizeof d, "\t.shared .align 4 .b8 __mq%d_misc[12];", u);   // TMEM base, give-up flag, tiles stored by the epilogue warps
     decls->push_back(d);
     const std::string dyn = ".extern .shared .align 1024 .b8 __basalt_dyn_smem[];";
     if (std::find(s.module_decls->begin(), s.module_decls->end(), dyn) == s.module_decls->end()) s.module_decls->push_back(dyn);
@@ -1053,7 +1053,7 @@ bool matmul_tcgen05_pair(const MmaSite& s, std::vector<std::string>* decls, std:
     const std::string ppeers = s.kernel + "_peers", pnpeers = s.kernel + "_npeers";
     s.extra_params->push_back(".param .align 8 .b8 " + ppeers + "[56]");
     s.extra_params->push_back(".param .u32 " + pnpeers);
-    *s.maxntid = 192;
+    *s.maxntid = 256;   // warps 0-1 producer and MMA issuer, 2-5 epilogue, 6-7 relay the finished tiles to the peers
     *s.cluster = 2;
     Out o{lines};
     int wait_n = 0;
@@ -1121,7 +1121,7 @@ bool matmul_tcgen05_pair(const MmaSite& s, std::vector<std::string>* decls, std:
 
     o("// mma f16->f32->f16 128x128x%u over a tiled grid: TMA + tcgen05.cta_group::2, 256x256 tiles on pairs of SMs, %s B", in.k, b_nk ? "K-major" : "MN-major");
     o("mov.u32 %s, %%ntid.x;", r("t").c_str());
-    o("setp.ne.u32 %s, %s, 192;", r("p").c_str(), r("t").c_str());
+    o("setp.ne.u32 %s, %s, 256;", r("p").c_str(), r("t").c_str());
     o("@%s bra %sskip;", r("p").c_str(), L.c_str());
     o("ld.param.u64 %s, [%s];", r("status").c_str(), stp.c_str());
     o("ld.param.u32 %s, [%s];", r("lgx").c_str(), pgx.c_str());
@@ -1147,6 +1147,7 @@ bool matmul_tcgen05_pair(const MmaSite& s, std::vector<std::string>* decls, std:
     o("mov.u64 %s, __mq%d_misc;", r("w").c_str(), u);
     o("cvt.u32.u64 %s, %s;", r("slot").c_str(), r("w").c_str());
     o("add.u32 %s, %s, 4;", r("gu").c_str(), r("slot").c_str());
+    o("add.u32 %s, %s, 8;", r("ts").c_str(), r("slot").c_str());
     o("shr.u32 %s, %s, 1;", r("tn").c_str(), r("lgx").c_str());
     o("shr.u32 %s, %s, 1;", r("tm").c_str(), r("lgy").c_str());
     o("mul.lo.u32 %s, %s, %s;", r("ntiles").c_str(), r("tn").c_str(), r("tm").c_str());
@@ -1154,6 +1155,7 @@ bool matmul_tcgen05_pair(const MmaSite& s, std::vector<std::string>* decls, std:
     o("setp.ne.u32 %s, %s, 0;", r("p").c_str(), r("tid").c_str());
     o("@%s bra %sinit_done;", r("p").c_str(), L.c_str());
     o("st.volatile.shared.u32 [%s], 0;", r("gu").c_str());
+    o("st.volatile.shared.u32 [%s], 0;", r("ts").c_str());
     for (int i = 0; i < 2 * STAGES + 2; i++) o("mbarrier.init.shared::cta.b64 [%s+%d], 1;", r("bars").c_str(), 8 * i);   // full, empty, tfull
     for (int i = 0; i < 2; i++) o("mbarrier.init.shared::cta.b64 [%s+%d], 8;", r("bars").c_str(), TEMPTY + 8 * i);      // four epilogue warps in each CTA
     o("fence.mbarrier_init.release.cluster;");
@@ -1185,8 +1187,11 @@ bool matmul_tcgen05_pair(const MmaSite& s, std::vector<std::string>* decls, std:
     o("and.pred %s, %s, %s;", r("mma").c_str(), r("w1").c_str(), r("l0").c_str());
     o("and.pred %s, %s, %s;", r("mma").c_str(), r("mma").c_str(), r("lead").c_str());
     o("setp.ge.u32 %s, %s, 2;", r("epi").c_str(), r("warp").c_str());
+    o("setp.ge.u32 %s, %s, 6;", r("relay").c_str(), r("warp").c_str());
+    o("setp.ne.u32 %s, %s, 0;", r("pk").c_str(), r("np").c_str());           // pk: this launch gathers
     o("@%s bra %sp_tile;", r("prod").c_str(), L.c_str());
     o("@%s bra %sm_tile;", r("mma").c_str(), L.c_str());
+    o("@%s bra %sr_tile;", r("relay").c_str(), L.c_str());
     o("@%s bra %se_tile;", r("epi").c_str(), L.c_str());
     o("bra %send;", L.c_str());
 
@@ -1351,35 +1356,93 @@ bool matmul_tcgen05_pair(const MmaSite& s, std::vector<std::string>* decls, std:
         o("add.u64 %s, %s, %s;", r("z").c_str(), r("z").c_str(), r("crow").c_str());
         for (int i = 0; i < 8; i++)
             o("st.global.v4.b32 [%s+%lld], {%srb%d, %srb%d, %srb%d, %srb%d};", r("z").c_str(), 4ll * i * ldd * 2, P.c_str(), 4 * i, P.c_str(), 4 * i + 1, P.c_str(), 4 * i + 2, P.c_str(), 4 * i + 3);
-        // the fused gather: the same lines at the same offset behind every peer's base address, over NVLink,
-        // while the next tile's main loop runs on the tensor pipe
-        o("setp.eq.u32 %s, %s, 0;", r("pk").c_str(), r("np").c_str());
-        o("@%s bra %se_peers_done;", r("pk").c_str(), L.c_str());
-        o("sub.u64 %s, %s, %s;", r("pq").c_str(), r("z").c_str(), s.d_base.c_str());   // offset of this lane's first line in the result
-        o("mov.u32 %s, 0;", r("pi").c_str());
-        o("mov.b64 %s, %s;", r("pb").c_str(), ppeers.c_str());
-        o.label(L + "e_peer");
-        o("ld.param.u64 %s, [%s];", r("pz").c_str(), r("pb").c_str());
-        o("add.u64 %s, %s, %s;", r("pz").c_str(), r("pz").c_str(), r("pq").c_str());
-        for (int i = 0; i < 8; i++)
-            o("st.global.v4.b32 [%s+%lld], {%srb%d, %srb%d, %srb%d, %srb%d};", r("pz").c_str(), 4ll * i * ldd * 2, P.c_str(), 4 * i, P.c_str(), 4 * i + 1, P.c_str(), 4 * i + 2, P.c_str(), 4 * i + 3);
-        o("add.u64 %s, %s, 8;", r("pb").c_str(), r("pb").c_str());
-        o("add.u32 %s, %s, 1;", r("pi").c_str(), r("pi").c_str());
-        o("setp.lt.u32 %s, %s, %s;", r("pk").c_str(), r("pi").c_str(), r("np").c_str());
-        o("@%s bra %se_peer;", r("pk").c_str(), L.c_str());
-        o.label(L + "e_peers_done");
     }
     o("add.u32 %s, %s, 64;", r("c").c_str(), r("c").c_str());
     o("setp.lt.u32 %s, %s, 256;", r("p").c_str(), r("c").c_str());
     o("@%s bra %se_c;", r("p").c_str(), L.c_str());
     o("tcgen05.fence::before_thread_sync;");
+    o("@%s membar.gl;", r("pk").c_str());   // gathering: this lane's stores of the tile are visible device-wide before the warp counts itself
     o("bar.warp.sync 0xffffffff;");
     o("add.u32 %s, %s, %d;", r("bar2").c_str(), r("bar2").c_str(), TEMPTY - TFULL);   // tempty[buf] ...
     o("mapa.shared::cluster.u32 %s, %s, %s;", r("fb").c_str(), r("bar2").c_str(), r("zero").c_str());      // ... of the leader
     o("@%s mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%s];", r("l0").c_str(), r("fb").c_str());
+    o("and.pred %s, %s, %s;", r("q").c_str(), r("l0").c_str(), r("pk").c_str());
+    o("@%s red.shared.add.u32 [%s], 1;", r("q").c_str(), r("ts").c_str());   // one of the four epilogue warps has stored its rows of the tile
     o("add.u32 %s, %s, %s;", r("tile").c_str(), r("tile").c_str(), r("gstep").c_str());
     o("add.u32 %s, %s, 1;", r("local").c_str(), r("local").c_str());
     o("bra %se_tile;", L.c_str());
+
+    // ---- relay warps (6 and 7; only when the launch gathers): the fused gather.  The epilogue warps store a tile to this
+    // GPU's result only; these two warps read every finished tile of the CTA back (it is still in L2) and store it at the
+    // same offset behind every peer's base address, over NVLink, 64 rows each.  The epilogue therefore never waits on a
+    // link, and link back-pressure cannot hold an accumulator back from the MMA warp. ----
+    o.label(L + "r_tile");
+    o("@!%s bra %send;", r("pk").c_str(), L.c_str());
+    o("setp.ge.u32 %s, %s, %s;", r("p").c_str(), r("tile").c_str(), r("ntiles").c_str());
+    o("@%s bra %send;", r("p").c_str(), L.c_str());
+    coords();
+    // bounded wait until the four epilogue warps have counted this tile: tiles stored >= 4 * (local + 1)
+    o("mad.lo.u32 %s, %s, 4, 4;", r("want").c_str(), r("local").c_str());
+    o("mov.u64 %s, 0;", r("t0").c_str());
+    o("mov.u32 %s, 0;", r("spin").c_str());
+    o.label(L + "r_wait");
+    o("ld.volatile.shared.u32 %s, [%s];", r("g").c_str(), r("ts").c_str());
+    o("setp.ge.u32 %s, %s, %s;", r("done").c_str(), r("g").c_str(), r("want").c_str());
+    o("@%s bra %sr_ready;", r("done").c_str(), L.c_str());
+    o("ld.volatile.shared.u32 %s, [%s];", r("g").c_str(), r("gu").c_str());
+    o("setp.ne.u32 %s, %s, 0;", r("q").c_str(), r("g").c_str());
+    o("@%s bra %sr_fail;", r("q").c_str(), L.c_str());
+    o("add.u32 %s, %s, 1;", r("spin").c_str(), r("spin").c_str());
+    o("and.b32 %s, %s, 63;", r("g").c_str(), r("spin").c_str());
+    o("setp.ne.u32 %s, %s, 0;", r("q").c_str(), r("g").c_str());
+    o("@%s bra %sr_wait;", r("q").c_str(), L.c_str());
+    o("mov.u64 %s, %%globaltimer;", r("now").c_str());
+    o("setp.ne.u64 %s, %s, 0;", r("q").c_str(), r("t0").c_str());
+    o("@%s bra %sr_timed;", r("q").c_str(), L.c_str());
+    o("mov.u64 %s, %s;", r("t0").c_str(), r("now").c_str());
+    o("bra %sr_wait;", L.c_str());
+    o.label(L + "r_timed");
+    o("sub.u64 %s, %s, %s;", r("dt").c_str(), r("now").c_str(), r("t0").c_str());
+    o("setp.lt.u64 %s, %s, 200000000;", r("q").c_str(), r("dt").c_str());
+    o("@%s bra %sr_wait;", r("q").c_str(), L.c_str());
+    o("st.volatile.shared.u32 [%s], 1;", r("gu").c_str());
+    o.label(L + "r_fail");
+    o("mov.u32 %s, 0;", r("ok").c_str());
+    o("bra %send;", L.c_str());
+    o.label(L + "r_ready");
+    o("membar.gl;");
+    // this lane's 16 bytes of the warp's first row: D + ((m0 + 64 * (warp - 6)) * ldd + n0 + 8 * lane) * 2
+    o("sub.u32 %s, %s, 6;", r("t").c_str(), r("warp").c_str());
+    o("mad.lo.u32 %s, %s, 64, %s;", r("t").c_str(), r("t").c_str(), r("m0").c_str());
+    o("mul.wide.u32 %s, %s, %lld;", r("w").c_str(), r("t").c_str(), ldd * 2);
+    o("add.u64 %s, %s, %s;", r("z").c_str(), s.d_base.c_str(), r("w").c_str());
+    o("mul.wide.u32 %s, %s, 2;", r("w").c_str(), r("n0").c_str());
+    o("add.u64 %s, %s, %s;", r("z").c_str(), r("z").c_str(), r("w").c_str());
+    o("mul.wide.u32 %s, %s, 16;", r("w").c_str(), r("lane").c_str());
+    o("add.u64 %s, %s, %s;", r("z").c_str(), r("z").c_str(), r("w").c_str());
+    o("mov.u32 %s, 0;", r("row").c_str());
+    o.label(L + "r_rows");
+    for (int i = 0; i < 4; i++)
+        o("ld.global.cg.v4.b32 {%srb%d, %srb%d, %srb%d, %srb%d}, [%s+%lld];", P.c_str(), 4 * i, P.c_str(), 4 * i + 1, P.c_str(), 4 * i + 2, P.c_str(), 4 * i + 3, r("z").c_str(), (long long)i * ldd * 2);
+    o("sub.u64 %s, %s, %s;", r("pq").c_str(), r("z").c_str(), s.d_base.c_str());   // offset of these rows in the result
+    o("mov.u32 %s, 0;", r("pi").c_str());
+    o("mov.b64 %s, %s;", r("pb").c_str(), ppeers.c_str());
+    o.label(L + "r_peer");
+    o("ld.param.u64 %s, [%s];", r("pz").c_str(), r("pb").c_str());
+    o("add.u64 %s, %s, %s;", r("pz").c_str(), r("pz").c_str(), r("pq").c_str());
+    for (int i = 0; i < 4; i++)
+        o("st.global.v4.b32 [%s+%lld], {%srb%d, %srb%d, %srb%d, %srb%d};", r("pz").c_str(), (long long)i * ldd * 2, P.c_str(), 4 * i, P.c_str(), 4 * i + 1, P.c_str(), 4 * i + 2, P.c_str(), 4 * i + 3);
+    o("add.u64 %s, %s, 8;", r("pb").c_str(), r("pb").c_str());
+    o("add.u32 %s, %s, 1;", r("pi").c_str(), r("pi").c_str());
+    o("setp.lt.u32 %s, %s, %s;", r("q").c_str(), r("pi").c_str(), r("np").c_str());
+    o("@%s bra %sr_peer;", r("q").c_str(), L.c_str());
+    o("add.u64 %s, %s, %lld;", r("z").c_str(), r("z").c_str(), 4ll * ldd * 2);
+    o("add.u32 %s, %s, 4;", r("row").c_str(), r("row").c_str());
+    o("setp.lt.u32 %s, %s, 64;", r("q").c_str(), r("row").c_str());
+    o("@%s bra %sr_rows;", r("q").c_str(), L.c_str());
+    o("add.u32 %s, %s, %s;", r("tile").c_str(), r("tile").c_str(), r("gstep").c_str());
+    o("add.u32 %s, %s, 1;", r("local").c_str(), r("local").c_str());
+    o("bra %sr_tile;", L.c_str());
 
     o.label(L + "end");
     o("setp.ne.u32 %s, %s, 0;", r("p").c_str(), r("ok").c_str());

@@ -375,8 +375,7 @@ __global__ void __launch_bounds__(THREADS2, 1) matmul_f16_tc_persistent(const __
 // Every wait is bounded as in the other kernels; the pair meets at a cluster barrier before tensor
 // memory is released, so neither CTA leaves while the other may still name its barriers or memory.
 namespace v3 {
-constexpr int TM = 256, TN = 256, HALF_N = 128, THREADS3 = 192;
-constexpr int B_HALF_BYTES = HALF_N * BK * 2, STAGE_BYTES3 = A_BYTES + B_HALF_BYTES;   // 16 KB + 16 KB
+constexpr int TM = 256, TN = 256, HALF_N = 128;   // a stage is 16 KB of A + 16 KB of B per CTA
 // How the epilogue leaves the SM.
 //   DIRECT  16-byte pieces straight from the registers tcgen05.ld filled (a lane holds one row);
 //   LINES   each 32-row x 64-column piece is transposed through shared memory and stored by the warp as
@@ -384,11 +383,15 @@ constexpr int B_HALF_BYTES = HALF_N * BK * 2, STAGE_BYTES3 = A_BYTES + B_HALF_BY
 //   BULK    the piece is written to shared memory in the 128-byte-swizzled layout and one lane hands it
 //           to the copy engine of the SM as bulk-tensor stores (cp.async.bulk.tensor, shared -> global),
 //           one per destination: the warp goes straight back to tensor memory while the stores drain.
-enum Epilogue { DIRECT = 0, LINES = 1, BULK = 2 };
+//   RELAY   as LINES for this GPU's buffer; the copies for the peers are made by two further warps of the CTA that read each
+//           finished tile back (from L2) and store it behind every peer: the epilogue warps never wait on NVLink, so
+//           link back-pressure cannot hold an accumulator back from the MMA warp.
+enum Epilogue { DIRECT = 0, LINES = 1, BULK = 2, RELAY = 3 };
 constexpr int PIECE_BYTES = 32 * 128;   // 32 rows x 64 columns of f16
 // ring depth of the K-slab stages and staging pieces per epilogue warp: everything fits 227 KB
 __host__ __device__ constexpr int stages_of(int epi, bool deep, int tn = 256) { return tn == 128 ? 8 : epi == BULK && deep ? 5 : 6; }   // 24 KB stages when the tile is 128 wide
-__host__ __device__ constexpr int pieces_of(int epi, bool deep) { return epi == DIRECT ? 0 : epi == LINES ? 1 : deep ? 4 : 2; }
+__host__ __device__ constexpr int pieces_of(int epi, bool deep) { return epi == DIRECT ? 0 : (epi == LINES || epi == RELAY) ? 1 : deep ? 4 : 2; }
+__host__ __device__ constexpr int threads_of(int epi) { return epi == RELAY ? 256 : 192; }   // RELAY: warps 6 and 7 carry the tiles to the peers
 constexpr int GROUP_M = 8;
 constexpr uint32_t TMEM_COLS3 = 512;
 
@@ -461,13 +464,14 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t sr
 // per K slab, 24 KB; MMA M256 N128 K16): half the work per tile, so a row shard of few tiles (the 8-GPU split) starts
 // handing finished tiles to its epilogue -- and, in the fused gather, to NVLink -- after half the time.
 template <bool B_IS_NK, int EPI, bool DEEP, int TILE_N>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS3, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(threads_of(EPI), 1)
     matmul_f16_tc_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, __half* __restrict__ C, int M, int N, int K,
                        int32_t* status, const PeerRows peers, const __grid_constant__ StoreMaps out) {
     constexpr int TN = TILE_N, HALF_N = TILE_N / 2, STAGE_BYTES3 = A_BYTES + HALF_N * BK * 2;   // shadow the 256-wide constants of the namespace
     constexpr int STAGES = stages_of(EPI, DEEP, TILE_N), PIECES = pieces_of(EPI, DEEP);
-    constexpr bool STAGED = EPI == LINES;
-    const bool PUSH = peers.n > 0;
+    constexpr bool STAGED = EPI == LINES || EPI == RELAY;
+    const bool PUSH = EPI != RELAY && peers.n > 0;      // RELAY: the epilogue warps store locally only
+    __shared__ volatile uint32_t tiles_stored;          // RELAY: epilogue warps that have finished storing a tile (four per tile)
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], tfull_bar[2], tempty_bar[2];
     __shared__ uint32_t tmem_slot;
@@ -481,6 +485,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS3, 1)
 
     if (threadIdx.x == 0) {
         gave_up = 0;
+        tiles_stored = 0;
         for (int s = 0; s < STAGES; s++) {
             mbar_init(smem_u32(&full_bar[s]), 1);    // the leader's producer; bytes arrive from both CTAs
             mbar_init(smem_u32(&empty_bar[s]), 1);   // one commit from the leader's MMA warp
@@ -558,6 +563,44 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS3, 1)
                 }
                 umma_commit_pair(smem_u32(&tfull_bar[buf]));
             }
+        }
+    } else if (warp >= 6) {
+        // ---- RELAY: warps 6 and 7 carry every finished tile of this CTA (128 rows x TN columns) to the peers ----
+        if constexpr (EPI == RELAY) {
+            const int half = warp - 6;   // rows 64 half .. 64 half + 63 of the CTA's 128
+            uint32_t local = 0;
+            for (int t = pair; t < num_tiles && ok && peers.n > 0; t += pairs, local++) {
+                int mi, ni;
+                tile_coords(t, tiles_m, tiles_n, &mi, &ni);
+                // bounded wait for the four epilogue warps to have stored this tile (their stores are fenced before they count)
+                uint64_t t0 = 0;
+                for (uint32_t i = 0; tiles_stored < 4 * (local + 1); i++) {
+                    if (gave_up) { ok = false; break; }
+                    if ((i & 63) == 63) {
+                        const uint64_t now = global_ns();
+                        if (t0 == 0) t0 = now;
+                        else if (now - t0 > WAIT_LIMIT_NS) { gave_up = 1; ok = false; break; }
+                    }
+                }
+                if (!ok) break;
+                __threadfence();
+                const size_t first = (size_t)(mi * TM + (int)rank * BM + half * 64) * N + (size_t)ni * TN + 8 * lane;   // this lane's 16 bytes of the first row
+#pragma unroll 1
+                for (int r = 0; r < 64; r += 4) {
+                    uint4 v[4][TN / 256 ? TN / 256 : 1];
+#pragma unroll
+                    for (int i = 0; i < 4; i++)
+#pragma unroll
+                        for (int c = 0; c < TN / 256; c++) v[i][c] = __ldcg(reinterpret_cast<const uint4*>(C + first + (size_t)(r + i) * N + 256 * c));
+                    for (int p = 0; p < peers.n; p++) {
+#pragma unroll
+                        for (int i = 0; i < 4; i++)
+#pragma unroll
+                            for (int c = 0; c < TN / 256; c++) *reinterpret_cast<uint4*>(peers.c[p] + first + (size_t)(r + i) * N + 256 * c) = v[i][c];
+                    }
+                }
+            }
+            if (peers.n > 0) __threadfence_system();
         }
     } else {
         const int ew = warp & 3;
@@ -700,8 +743,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS3, 1)
             }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            if (EPI == RELAY) __threadfence();   // this lane's stores of the tile are visible device-wide before the warp counts itself
             __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[buf]), 0));
+            if (lane == 0) {
+                mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[buf]), 0));
+                if (EPI == RELAY) atomicAdd(const_cast<uint32_t*>(&tiles_stored), 1u);
+            }
         }
         if (EPI == BULK && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // every bulk store of this warp is complete
         if (PUSH) __threadfence_system();   // this thread's peer stores are performed before the kernel can end
@@ -785,7 +832,7 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, __half* C, int M, 
         if (e != cudaSuccess) return basalt_k::record(e, "matmul_f16 (shared memory size)");
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(2 * basalt_k::sm_count());
-        cfg.blockDim = dim3(v3::THREADS3);
+        cfg.blockDim = dim3(v3::threads_of(EPI));
         cfg.dynamicSmemBytes = smem;
         int n = 0;
         e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);   // the kernel's own __cluster_dims__ (2,1,1) applies
@@ -794,7 +841,7 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, __half* C, int M, 
     }
     const int tiles = (M / v3::TM) * (N / TILE_N);
     const int pairs = tiles < max_pairs ? tiles : max_pairs;
-    kern<<<2 * pairs, v3::THREADS3, smem, s>>>(ma, mb, C, M, N, K, status, peers, out);
+    kern<<<2 * pairs, v3::threads_of(EPI), smem, s>>>(ma, mb, C, M, N, K, status, peers, out);
     return basalt_k::record(cudaGetLastError(), "matmul_f16");
 }
 
@@ -814,6 +861,7 @@ int launch_pair_variant(int variant, const CUtensorMap& ma, const CUtensorMap& m
     for (int i = 0; i < n_peers; i++) peers.c[i] = (__half*)peer_c[i];
     if (variant == BASALT_K_MATMUL_PAIR_DIRECT) return launch_pair<B_IS_NK, v3::DIRECT, false>(ma, mb, (__half*)C, M, N, K, status, s, peers, v3::StoreMaps{});
     if (variant == BASALT_K_MATMUL_PAIR_LINES) return launch_pair<B_IS_NK, v3::LINES, false>(ma, mb, (__half*)C, M, N, K, status, s, peers, v3::StoreMaps{});
+    if (variant == BASALT_K_MATMUL_PAIR_RELAY) return launch_pair<B_IS_NK, v3::RELAY, false>(ma, mb, (__half*)C, M, N, K, status, s, peers, v3::StoreMaps{});
     if (variant == BASALT_K_MATMUL_PAIR_LINES_NARROW) return launch_pair<B_IS_NK, v3::LINES, false, 128>(ma, mb, (__half*)C, M, N, K, status, s, peers, v3::StoreMaps{});
     v3::StoreMaps out = {};
     int rc = make_store_maps(&out, C, peer_c, n_peers, M, N);
@@ -833,11 +881,11 @@ int matmul_f16_any(const void* A, const void* B, void* C, int M, int N, int K, i
     if (all & 15) return basalt_k::record_msg(1, who, "matrices must be 16-byte aligned");
     const bool pair_shape = M % v3::TM == 0 && N % v3::TN == 0;
     if (variant == BASALT_K_MATMUL_AUTO) {
-        if (n_peers) variant = BASALT_K_MATMUL_PAIR_BULK_DEEP;
+        if (n_peers) variant = BASALT_K_MATMUL_PAIR_RELAY;
         else if (pair_shape) variant = BASALT_K_MATMUL_PAIR_LINES;
         else variant = N % v2::BN2 == 0 ? BASALT_K_MATMUL_ONE_SM_256 : BASALT_K_MATMUL_ONE_CTA_128;
     }
-    if (variant < BASALT_K_MATMUL_ONE_CTA_128 || variant > BASALT_K_MATMUL_PAIR_LINES_NARROW) return basalt_k::record_msg(1, who, "unknown variant");
+    if (variant < BASALT_K_MATMUL_ONE_CTA_128 || variant > BASALT_K_MATMUL_PAIR_RELAY) return basalt_k::record_msg(1, who, "unknown variant");
     const bool is_pair = variant >= BASALT_K_MATMUL_PAIR_DIRECT;
     if (is_pair && !pair_shape) return basalt_k::record_msg(1, who, "the CTA-pair kernels need M and N to be multiples of 256");
     if (!is_pair && n_peers) return basalt_k::record_msg(1, who, "only the CTA-pair kernels store to peers");

@@ -132,6 +132,7 @@ struct Plan {
                             // two-row tile; launched instead when the caller's grid is even in x and y
     unsigned lgrid = 0;     // persistent kernel: the caller's grid goes in two trailing u32 parameters; lgrid logical CTAs
                             // along x form one tile, and min(SM count, tiles) CTAs are launched
+    unsigned pair_block = 0; // threads per CTA of the pair entry when they differ from block[0]
     int gather = -1;        // the kernel (its pair twin, for a persistent kernel) can also store its result behind peer base addresses:
                             // index of the output pointer parameter; two trailing parameters, a table of seven u64 and a u32 count
 };
@@ -253,6 +254,7 @@ void parse_plans(const char* ptx, std::map<std::string, Plan>* out) {
             else if (k == "lgrid") p.lgrid = (unsigned)strtoul(v.c_str(), nullptr, 10);
             else if (k == "tail") p.tail_k = (unsigned)strtoul(v.c_str(), nullptr, 10);
             else if (k == "gather") p.gather = (int)strtol(v.c_str(), nullptr, 10);
+            else if (k == "pair_block") p.pair_block = (unsigned)strtoul(v.c_str(), nullptr, 10);
             else if (k == "tmap") {
                 TmapSpec t;
                 unsigned long long inner = 0, rowb = 0;
@@ -692,7 +694,8 @@ int launch_impl(basalt_rt_function* fn, const uint32_t grid[3], const uint32_t b
     }
     if (n_peers && !(entry == fn->pair && p.gather >= 0))
         return set_err(4, 0, "basalt_rt_launch_gather", "the gathering epilogue is in the two-SM entry: the grid must be even in x and y");
-    return check(f, "cuLaunchKernel", f.cuLaunchKernel(entry, g[0], g[1], g[2], p.block[0], p.block[1], p.block[2], sm, (CUstream)stream, all.data(), nullptr));
+    const unsigned threads = entry == fn->pair && p.pair_block ? p.pair_block : p.block[0];
+    return check(f, "cuLaunchKernel", f.cuLaunchKernel(entry, g[0], g[1], g[2], threads, p.block[1], p.block[2], sm, (CUstream)stream, all.data(), nullptr));
 }
 }  // namespace
 

@@ -59,7 +59,7 @@ def matmul_f16_allgather(A, B, Cm, M: int, N: int, K: int, peer_ptrs, b_is_nk: b
                                              _p(status) if status is not None else None, C.c_void_p(stream)))
 
 
-MATMUL_VARIANTS = {"auto": 0, "one_cta_128": 1, "one_sm_256": 2, "pair_direct": 3, "pair_lines": 4, "pair_bulk": 5, "pair_bulk_deep": 6, "pair_lines_narrow": 7}
+MATMUL_VARIANTS = {"auto": 0, "one_cta_128": 1, "one_sm_256": 2, "pair_direct": 3, "pair_lines": 4, "pair_bulk": 5, "pair_bulk_deep": 6, "pair_lines_narrow": 7, "pair_relay": 8}
 
 
 def matmul_f16_variant(A, B, Cm, M: int, N: int, K: int, variant: str, peer_ptrs=(), b_is_nk: bool = False, status=None, stream=None):

@@ -163,10 +163,11 @@ int basalt_rt_launch(basalt_rt_function *fn, const uint32_t grid[3], const uint3
 /* basalt_rt_launch for one rank of a row-sharded matmul whose result every rank wants whole: compute
  * and gather in ONE kernel.  peer_out[i] (0 <= n_peers <= 7) is the value the kernel's output pointer
  * parameter has on another rank, as an address valid on this device (basalt_rt_ipc_open); the
- * kernel's epilogue stores every tile of its result at its own output pointer and, at the same
- * offset, behind each peer address over NVLink (plain line-sized stores from the SMs while the next
- * tile is being computed; no copy engine, no library collective), and ends with a system-scope
- * fence.  A stream-ordered basalt_rt_peer_allreduce_max_i32 afterwards is the barrier after which
+ * kernel stores every tile of its result at its own output pointer and, at the same offset, behind
+ * each peer address over NVLink (plain line-sized stores from the SMs while the next tiles are being
+ * computed -- in the tcgen05 matmul by two relay warps per CTA that read each finished tile back from
+ * L2, so that the epilogue never waits on a link; no copy engine, no library collective), and ends
+ * with a system-scope fence.  A stream-ordered basalt_rt_peer_allreduce_max_i32 afterwards is the barrier after which
  * every rank holds every rank's rows.  The peers are served in the order given: pass rank + 1,
  * rank + 2, ... (mod the group size), so that at every moment no two ranks store into the same
  * receiver.  Only kernels the emitter lowered with a gathering epilogue

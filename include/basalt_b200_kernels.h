@@ -112,19 +112,23 @@ int basalt_k_max_i32_allreduce(const int32_t *x, int64_t n, int32_t *partial, co
                                uint64_t timeout_ns, void *stream);
 
 /* The row-sharded fp16 matmul with its gather fused in: C = A * B for this rank's M rows as
- * basalt_k_matmul_f16 (CTA pairs, tcgen05.mma.cta_group::2), and the epilogue stores every piece of
- * every tile both to C and to the same position behind each of the n_peers pointers in peer_c (host
- * array; each entry the address, in this process, of the same rows of another rank's result buffer,
- * mapped with basalt_rt_ipc_open).  Each storing thread ends with a system-scope fence, so a
+ * basalt_k_matmul_f16 (CTA pairs, tcgen05.mma.cta_group::2), and every tile is stored both to C and
+ * to the same position behind each of the n_peers pointers in peer_c (host array; each entry the
+ * address, in this process, of the same rows of another rank's result buffer, mapped with
+ * basalt_rt_ipc_open): the epilogue warps store to C, two further warps of each CTA read the finished
+ * tile back from L2 and store it to the peers over NVLink while the next tiles are computed.  Each
+ * storing thread ends with a system-scope fence, so a
  * stream-ordered basalt_k_peer_allreduce_max_i32 after this kernel is the barrier after which every
- * rank holds the whole result.  M, N multiples of 256, K of 64, n_peers <= BASALT_K_MAX_PEERS - 1.
+ * rank holds the whole result.  The peers are served in the order given: pass rank + 1, rank + 2, ...
+ * (mod the group size) so that at no moment two ranks store into the same receiver.  M, N multiples of
+ * 256, K of 64, n_peers <= BASALT_K_MAX_PEERS - 1.
  * No counterpart in the reference, which has no multi-GPU path. */
 int basalt_k_matmul_f16_allgather(const void *A, const void *B, void *C, int M, int N, int K, int b_is_nk,
                                   void *const *peer_c, int n_peers, int32_t *status, void *stream);
 
 /* The same product through one named kernel form, for tests and A/B timing (basalt_k_matmul_f16 and
  * basalt_k_matmul_f16_allgather choose for themselves: the CTA-pair kernel with line-sized stores
- * when M and N are multiples of 256 and nothing is gathered, bulk-tensor stores for the gather).
+ * when M and N are multiples of 256 and nothing is gathered, the relay form for the gather).
  * ONE_CTA_128: one 128x128 tile per CTA of 128 threads.  ONE_SM_256: persistent, 128x256 tiles, one
  * SM each.  PAIR_*: 256x256 tiles on clusters of two SMs (tcgen05.mma.cta_group::2), differing in
  * how the epilogue leaves the SM: DIRECT = 16-byte pieces straight from the registers; LINES = each
@@ -142,7 +146,9 @@ enum {
     BASALT_K_MATMUL_PAIR_LINES = 4,
     BASALT_K_MATMUL_PAIR_BULK = 5,
     BASALT_K_MATMUL_PAIR_BULK_DEEP = 6,
-    BASALT_K_MATMUL_PAIR_LINES_NARROW = 7   /* PAIR_LINES on 256x128 tiles (MMA M256 N128 K16, eight 24 KB stages) */
+    BASALT_K_MATMUL_PAIR_LINES_NARROW = 7,  /* PAIR_LINES on 256x128 tiles (MMA M256 N128 K16, eight 24 KB stages) */
+    BASALT_K_MATMUL_PAIR_RELAY = 8          /* PAIR_LINES for this GPU's buffer; two further warps per CTA read each finished tile back
+                                               from L2 and store it behind every peer, so the epilogue never waits on NVLink */
 };
 int basalt_k_matmul_f16_variant(const void *A, const void *B, void *C, int M, int N, int K, int b_is_nk, int variant,
                                 void *const *peer_c, int n_peers, int32_t *status, void *stream);

@@ -216,10 +216,11 @@ def test_tiled_fp16_matmul_gets_a_two_sm_twin(ptx):
         # (the twin takes two more: the peer table and count of the gathering epilogue)
         two_params = [p.replace("_pair_", "", 1) if p.startswith("_pair_") else p for p in params(two)]
         assert params(one.split(".visible .entry matmul_kernel(")[1]) == two_params[:-2] and "peers[56]" in two_params[-2] and "npeers" in two_params[-1]
-        assert "fence.acq_rel.sys" in two and two.count("st.global.v4.b32") == 16      # eight line stores locally, eight per peer
+        assert "fence.acq_rel.sys" in two and two.count("st.global.v4.b32") == 12      # eight line stores locally, four rows per peer in the relay warps
+        assert ".maxntid 256" in two and " pair_block=256 " in plans[0] and two.count("ld.global.cg.v4.b32") == 4
         # bulk-tensor loads never multicast: a cta_group::2 load names the leader's barrier by address instead
         for line in text.splitlines():
             if "cp.async.bulk" in line:
                 assert "multicast" not in line, line
         # every wait in the twin is bounded: each try_wait loop reads the clock and can leave through the give-up flag
-        assert two.count("mbarrier.try_wait.parity") == two.count("setp.lt.u64") - 1    # + the 2 ms drain of the producer
+        assert two.count("mbarrier.try_wait.parity") == two.count("setp.lt.u64") - 2    # + the 2 ms drain of the producer and the relay warps' bounded wait for a stored tile

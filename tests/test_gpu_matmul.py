@@ -166,7 +166,7 @@ def test_matmul_f16_full_size(gpu, orc, how):
     assert np.linalg.norm(lhs - rhs) / np.linalg.norm(rhs) <= F16_TOL
 
 
-PAIR_VARIANTS = ["pair_direct", "pair_lines", "pair_bulk", "pair_bulk_deep", "pair_lines_narrow"]
+PAIR_VARIANTS = ["pair_direct", "pair_lines", "pair_bulk", "pair_bulk_deep", "pair_lines_narrow", "pair_relay"]
 
 
 @pytest.mark.parametrize("b_is_nk", [True, False])
@@ -193,7 +193,7 @@ def test_matmul_f16_kernel_forms_agree(gpu, b_is_nk, shape):
         assert np.array_equal(got, results["one_cta_128"]), variant
 
 
-@pytest.mark.parametrize("variant", ["pair_direct", "pair_lines", "pair_bulk", "pair_bulk_deep", "pair_lines_narrow", "auto"])
+@pytest.mark.parametrize("variant", ["pair_direct", "pair_lines", "pair_bulk", "pair_bulk_deep", "pair_lines_narrow", "pair_relay", "auto"])
 @pytest.mark.parametrize("n_peers", [1, 7])
 def test_fused_gather_into_loop_back_peers(gpu, orc, variant, n_peers):
     # The fused matmul + gather on ONE GPU: the "peers" are further buffers of this GPU, so the peer
