@@ -1361,13 +1361,17 @@ bool matmul_tcgen05_pair(const MmaSite& s, std::vector<std::string>* decls, std:
     o("setp.lt.u32 %s, %s, 256;", r("p").c_str(), r("c").c_str());
     o("@%s bra %se_c;", r("p").c_str(), L.c_str());
     o("tcgen05.fence::before_thread_sync;");
-    o("@%s membar.gl;", r("pk").c_str());   // gathering: this lane's stores of the tile are visible device-wide before the warp counts itself
     o("bar.warp.sync 0xffffffff;");
     o("add.u32 %s, %s, %d;", r("bar2").c_str(), r("bar2").c_str(), TEMPTY - TFULL);   // tempty[buf] ...
     o("mapa.shared::cluster.u32 %s, %s, %s;", r("fb").c_str(), r("bar2").c_str(), r("zero").c_str());      // ... of the leader
     o("@%s mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%s];", r("l0").c_str(), r("fb").c_str());
-    o("and.pred %s, %s, %s;", r("q").c_str(), r("l0").c_str(), r("pk").c_str());
-    o("@%s red.shared.add.u32 [%s], 1;", r("q").c_str(), r("ts").c_str());   // one of the four epilogue warps has stored its rows of the tile
+    // gathering: once every lane's stores of the tile are visible device-wide, the warp counts itself for the relay warps
+    // (after the accumulator has been handed back: the fence is not on the MMA warp's path)
+    o("@!%s bra %se_counted;", r("pk").c_str(), L.c_str());
+    o("membar.gl;");
+    o("bar.warp.sync 0xffffffff;");
+    o("@%s red.shared.add.u32 [%s], 1;", r("l0").c_str(), r("ts").c_str());
+    o.label(L + "e_counted");
     o("add.u32 %s, %s, %s;", r("tile").c_str(), r("tile").c_str(), r("gstep").c_str());
     o("add.u32 %s, %s, 1;", r("local").c_str(), r("local").c_str());
     o("bra %se_tile;", L.c_str());

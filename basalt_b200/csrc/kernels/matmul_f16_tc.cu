@@ -743,11 +743,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(threads_of(EPI), 1)
             }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            if (EPI == RELAY) __threadfence();   // this lane's stores of the tile are visible device-wide before the warp counts itself
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[buf]), 0));
-                if (EPI == RELAY) atomicAdd(const_cast<uint32_t*>(&tiles_stored), 1u);
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[buf]), 0));
+            if (EPI == RELAY && peers.n > 0) {   // after the accumulator is handed back: the fence is not on the MMA warp's path
+                __threadfence();                  // this lane's stores of the tile are visible device-wide before the warp counts itself
+                __syncwarp();
+                if (lane == 0) atomicAdd(const_cast<uint32_t*>(&tiles_stored), 1u);
             }
         }
         if (EPI == BULK && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // every bulk store of this warp is complete
