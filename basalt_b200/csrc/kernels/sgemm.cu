@@ -13,13 +13,15 @@
 //
 // Tail wave.  With R resident CTAs (2 per SM) and T tiles, the last T mod R tiles would run as a
 // mostly empty wave (4096^2 in 128x128 tiles: 1024 tiles on 296 slots is 3.46 waves, paid as 4).
-// When that tail is at most half a wave its tiles are split along K into s = min(4, R / tail)
-// parts, one CTA each, so the tail costs 1/s of a wave.  A part writes its 128x128 partial sums to
+// Its tiles are split along K into s = 2, 3 or 4 parts, one CTA each, when that shortens the
+// schedule: the parts take ceil(tail * s / R) / s of a tile's time instead of one (a tail of 136:
+// two parts, half a wave; a tail of 216: four parts, three waves of quarter tiles).  A part writes its 128x128 partial sums to
 // a workspace; the part that arrives last (a ticket counter per tile) adds the parts in index order
 // -- the result does not depend on arrival order -- stores the tile, and sets the counter back to
 // zero, so the workspace needs no clearing between launches.  The grid is one-dimensional: CTA c
 // below F (the full tiles) computes tile c over all of K; CTA F + s*t + p computes part p of tail
 // tile t.  CTAs are dispatched in index order, so the split parts form the last wave.
+#include <algorithm>
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
@@ -229,18 +231,24 @@ TailWorkspace* tail_workspace(int slots) {
     return &w;
 }
 
-// Chooses the split of the tail wave: tiles [0, *full) run whole, the rest in *split parts each.
-void plan_tail(int tiles, int slots, int K, int* full, int* split) {
+// Chooses the split of the tail wave: tiles [0, *full) run whole, the rest in *split parts each.  s parts of 1/s of
+// the work take ceil(tail * s / slots) / s of a tile's time instead of one; the traffic of the partial sums (64 KB
+// written and read per part, charged at 6 TB/s against a tile time of 0.17 us per K step) is set against that.
+// A split that needs more than `max_parts` partial tiles is not considered (0 = no limit).
+void plan_tail(int tiles, int slots, int K, int max_parts, int* full, int* split) {
     *full = tiles;
     *split = 1;
     const int tail = tiles % slots;                       // the whole problem, when it is less than one wave
-    if (tail == 0 || tail * 2 > slots) return;            // no tail, or a tail that is more than half full
-    int s = slots / tail;
-    if (s > 4) s = 4;
-    while (s > 1 && (K % (s * BK) != 0)) s--;
-    if (s < 2) return;
-    *full = tiles - tail;
-    *split = s;
+    if (tail == 0) return;
+    const double tile_us = 0.17 * (double)K;
+    double best = 1.0;
+    for (int s = 2; s <= 4; s++) {
+        if (K % (s * BK) != 0 || (max_parts > 0 && (long long)tail * s > max_parts)) continue;
+        const double waves = (double)(((long long)tail * s + slots - 1) / slots) / (double)s;
+        const double cost = waves + (double)tail * s * 131072.0 / 6.0e6 / tile_us;
+        if (cost < best - 1e-9) { best = cost; *split = s; }
+    }
+    if (*split > 1) *full = tiles - tail;
 }
 
 }  // namespace
@@ -257,10 +265,10 @@ extern "C" int basalt_k_sgemm_f32_variant(const float* A, const float* B, float*
     if (!resident) resident = basalt_k::resident_ctas(sgemm_f32_kernel<true, false>, THREADS);
     const int tiles = (M / BM) * (N / BN), slots = resident * basalt_k::sm_count();
     int full = tiles, split = 1;
-    if (!(flags & BASALT_K_SGEMM_NO_TAIL_SPLIT)) plan_tail(tiles, slots, K, &full, &split);
+    if (!(flags & BASALT_K_SGEMM_NO_TAIL_SPLIT)) plan_tail(tiles, slots, K, 0, &full, &split);
     TailWorkspace* w = nullptr;
     if (split > 1) {
-        w = tail_workspace(slots);
+        w = tail_workspace(std::max(slots, (tiles - full) * split));   // one partial tile per part, one ticket per tail tile
         if (!w) { full = tiles; split = 1; }   // no workspace: the plain schedule is still correct
     }
     const int grid = full + (tiles - full) * split;
@@ -275,7 +283,7 @@ extern "C" int basalt_k_sgemm_f32_variant(const float* A, const float* B, float*
 // ---- the same SGEMM with its tail workspace in a static device array: allocates nothing ----------
 namespace {
 constexpr int STATIC_MAX_PARTS = 304;    // partial tiles: one per resident CTA of a 148-SM part (296), rounded up
-constexpr int STATIC_MAX_TICKETS = 256;  // tail tiles (at most half a wave)
+constexpr int STATIC_MAX_TICKETS = 256;  // tail tiles (a split tail has at most STATIC_MAX_PARTS / 2)
 constexpr size_t STATIC_PARTIAL_BYTES = (size_t)STATIC_MAX_PARTS * BM * BN * sizeof(float);   // 19 MiB
 constexpr size_t STATIC_WS_BYTES = STATIC_PARTIAL_BYTES + STATIC_MAX_TICKETS * sizeof(unsigned);
 static __device__ __align__(256) unsigned char g_static_tail_ws[STATIC_WS_BYTES];
@@ -305,7 +313,7 @@ extern "C" int basalt_k_sgemm_f32_static_workspace(const float* A, const float* 
     if (!resident) resident = basalt_k::resident_ctas(sgemm_f32_kernel<true, false>, THREADS);
     const int tiles = (M / BM) * (N / BN), slots = resident * basalt_k::sm_count();
     int full = tiles, split = 1;
-    plan_tail(tiles, slots, K, &full, &split);
+    plan_tail(tiles, slots, K, STATIC_MAX_PARTS, &full, &split);   // a split that does not fit the array is not taken
     const int tail = tiles - full;
     if (split > 1 && ((size_t)tail * split > (size_t)STATIC_MAX_PARTS || tail > STATIC_MAX_TICKETS)) {
         char msg[200];

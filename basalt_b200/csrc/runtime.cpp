@@ -570,15 +570,23 @@ int launch_impl(basalt_rt_function* fn, const uint32_t grid[3], const uint32_t b
         const uint32_t slots = (uint32_t)ctx->sm_count * (uint32_t)resident;
         uint32_t full = tiles, split = 1;
         const uint32_t tail = tiles % slots;
-        // a sparse last wave -- or a whole problem of less than half a wave -- runs as K-parts that fill the slots
-        if (fn->tail_split && tail != 0 && tail * 2 <= slots) {
-            uint32_t sp = slots / tail;
-            // With a gathering epilogue the parts are made as small as allowed even when they no longer fit one wave:
-            // the tiles of the first wave of parts are then complete, and on their way to the peers, while the second
-            // wave still computes.
-            if (sp > 4 || n_peers > 0) sp = 4;
-            while (sp > 1 && p.tail_k % (sp * 16) != 0) sp--;
-            if (sp >= 2) { full = tiles - tail; split = sp; }
+        // The tiles of a last wave that does not fill the slots -- or a whole problem smaller than one wave -- run as
+        // s K-parts each when that shortens the schedule: s parts of 1/s of the work take ceil(tail * s / slots) / s of a
+        // tile's time instead of one (216 tail tiles on 296 slots: four parts each are three waves of quarter tiles,
+        // 0.75), against the traffic of the partial sums (64 KB written and read per part, charged at 6 TB/s against a
+        // tile time of 0.17 us per K step).  With a gathering epilogue the finest split wins ties: the tiles of the
+        // first wave of parts are then complete, and on their way to the peers, while the next wave still computes.
+        if (fn->tail_split && tail != 0) {
+            const double tile_us = 0.17 * (double)p.tail_k;
+            double best = 1.0;
+            for (uint32_t sp = 2; sp <= 4; sp++) {
+                if (p.tail_k % (sp * 16) != 0) continue;
+                const double waves = (double)(((uint64_t)tail * sp + slots - 1) / slots) / (double)sp;
+                const double traffic_us = (double)tail * sp * 131072.0 / 6.0e6;
+                const double cost = waves + traffic_us / tile_us - (n_peers > 0 ? 0.001 * sp : 0.0);
+                if (cost < best - 1e-9) { best = cost; split = sp; }
+            }
+            if (split > 1) full = tiles - tail;
         }
         std::unique_lock<std::mutex> lock(ctx->mu, std::defer_lock);
         if (split > 1) lock.lock();

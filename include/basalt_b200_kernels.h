@@ -65,8 +65,9 @@ int basalt_k_sgemm_f32_variant(const float *A, const float *B, float *C, int M, 
 /* basalt_k_sgemm_f32 with the split-K workspace of its tail wave in a static device array instead
  * of device memory allocated on first use: this entry point allocates nothing (no cudaMalloc,
  * cudaFree or allocating library call).  Same arguments and results.  The array holds 304 partial
- * 128x128 f32 tiles (19 MiB) and 256 tickets; a problem whose tail wave needs more is refused with
- * a message that says so (never on a 148-SM device, where a tail has at most 296 parts).  The first
+ * 128x128 f32 tiles (19 MiB) and 256 tickets; a split of the tail wave that would need more is not
+ * taken (the tail then runs whole, or in fewer parts, where basalt_k_sgemm_f32 would have split it
+ * further: the sums are then added in another order).  The first
  * call on each device looks the array's address up (cudaGetSymbolAddress) with that device current;
  * make that first call before any stream capture.  All calls on a device share the one array:
  * calls that overlap in time (different streams) race; calls on one stream do not.  Every call

@@ -74,10 +74,11 @@ def test_sgemm_full_size(gpu, orc, how):
 
 
 @pytest.mark.parametrize("how", ["hand", "cta128"])
-@pytest.mark.parametrize("shape", [(2560, 1920, 64), (2560, 1920, 48), (4096, 4736, 32), (2432, 2048, 16)])
+@pytest.mark.parametrize("shape", [(2560, 1920, 64), (2560, 1920, 48), (4096, 4736, 32), (2432, 2048, 16), (2048, 4096, 1024)])
 def test_sgemm_tail_wave(gpu, how, shape):
     # More tiles than resident CTAs with a sparse last wave: 300 tiles (tail 4, split in 4 or, for
-    # K = 48, in 3 parts), 1184 tiles (no tail on 296 slots), 304 tiles with K too short to split.
+    # K = 48, in 3 parts), 1184 tiles (no tail on 296 slots), 304 tiles with K too short to split,
+    # 512 tiles (a tail of 216, more than half a wave: four parts each, three waves of quarter tiles).
     # Small integers: every partial sum is exact, so any split of K must give the same bits; run
     # twice, since a split tail leaves its tickets behind for the next launch.
     M, N, K = shape
