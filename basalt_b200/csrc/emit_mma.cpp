@@ -52,9 +52,10 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
     const int u = s.uid, nk = (int)(in.k / 16);
     // Tail-wave form: when the kernel is nothing but this op on a tiled grid (operand pointers are the
     // parameters plus constant multiples of the block indices), the CTA decodes its tile from a linear
-    // index instead, so that the launch runtime can issue whole tiles first and the tiles of a sparse
-    // last wave as K-parts that fill one wave (the parts are summed in index order by the part that
-    // finishes last; see kernels/sgemm.cu for the same scheme in CUDA).
+    // index instead, so that the launch runtime can issue whole tiles first and have the tiles of a sparse
+    // last wave worked off by stream units: CTA full + u takes K slabs [u * per, (u + 1) * per) of the tail
+    // tiles' slabs laid end to end, segment by segment (a segment ends with its tile); the segments of a tile
+    // are summed in unit order by the one that finishes last (see kernels/sgemm.cu for the same scheme in CUDA).
     const bool tail = s.affine && s.pure_kernel && s.sole_mma && s.extra_params && s.a_c0 == 0 && s.a_cx == 0 && s.a_cy == 128 * lda * 4 && s.b_c0 == 0 &&
                       s.b_cy == 0 && s.b_cx == 512 && s.d_c0 == 0 && s.d_cx == 512 && s.d_cy == 128 * ldd * 4 && in.k < (1u << 30);
     // The generator also has a 128-thread form in which a thread owns 16 x 8 outputs (four groups of four rows, 32
@@ -85,8 +86,8 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
     snprintf(d, sizeof d, "\t.reg .pred %%mm%d_more, %%mm%d_bad;", u, u);
     decls->push_back(d);
     if (tail) {
-        snprintf(d, sizeof d, "\t.reg .b32 %%mm%d_cid, %%mm%d_full, %%mm%d_split, %%mm%d_tile, %%mm%d_part, %%mm%d_parts, %%mm%d_lgx, %%mm%d_bx, %%mm%d_by, %%mm%d_klen, %%mm%d_kbeg, %%mm%d_nk, %%mm%d_tt, %%mm%d_tk, %%mm%d_p;",
-                 u, u, u, u, u, u, u, u, u, u, u, u, u, u, u);
+        snprintf(d, sizeof d, "\t.reg .b32 %%mm%d_cid, %%mm%d_full, %%mm%d_per, %%mm%d_tile, %%mm%d_k0, %%mm%d_it0, %%mm%d_it1, %%mm%d_lgx, %%mm%d_bx, %%mm%d_by, %%mm%d_uf, %%mm%d_kbeg, %%mm%d_nk, %%mm%d_tt, %%mm%d_tk, %%mm%d_p;",
+                 u, u, u, u, u, u, u, u, u, u, u, u, u, u, u, u);
         decls->push_back(d);
         snprintf(d, sizeof d, "\t.reg .b64 %%mm%d_ta, %%mm%d_tb, %%mm%d_td, %%mm%d_ws, %%mm%d_tkp, %%mm%d_pp;", u, u, u, u, u, u);
         decls->push_back(d);
@@ -97,7 +98,7 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
         s.extra_params->push_back(".param .u32 " + s.kernel + "_lgrid_x");
         s.extra_params->push_back(".param .u32 " + s.kernel + "_lgrid_y");
         s.extra_params->push_back(".param .u32 " + s.kernel + "_full_tiles");
-        s.extra_params->push_back(".param .u32 " + s.kernel + "_split");
+        s.extra_params->push_back(".param .u32 " + s.kernel + "_per");
         s.extra_params->push_back(".param .u64 " + s.kernel + "_workspace");
         s.extra_params->push_back(".param .u64 " + s.kernel + "_tickets");
         // the fused gather: the result matrix's base address on up to seven peers, and how many are set
@@ -115,6 +116,7 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
     snprintf(d, sizeof d, "\t.shared .align 16 .b8 __mm%d_bs[16384];", u);
     decls->push_back(d);
     std::string l_loop = "$mm" + std::to_string(u) + "_loop", l_done = "$mm" + std::to_string(u) + "_done", l_skip = "$mm" + std::to_string(u) + "_skip";
+    std::string l_next = "$mm" + std::to_string(u) + "_next";
     Out o{lines};
     const std::string tid = R("tid"), tx = R("tx"), ty = R("ty"), t = R("t"), arow = R("arow"), acol = R("acol"), brow = R("brow"), bcol = R("bcol");
     const std::string asst = R("asst"), bsst = R("bsst"), asrd = R("asrd"), bsrd = R("bsrd"), as = R("as"), bs = R("bs"), kb = R("kb"), kb1 = R("kb1"), off = R("off");
@@ -140,26 +142,47 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
     o("shl.b32 %s, %s, 2;", bcol.c_str(), t.c_str());
     std::string abase = s.a, bbase = s.b, dbase = s.d;
     if (tail) {
-        const std::string cid = R("cid"), full = R("full"), split = R("split"), tile = R("tile"), part = R("part"), parts = R("parts"), lgx = R("lgx"), bx = R("bx"), by = R("by");
-        const std::string klen = R("klen"), kbeg = R("kbeg"), nkr = R("nk"), whole = R("whole"), ta = R("ta"), tb = R("tb"), td = R("td");
+        const std::string cid = R("cid"), full = R("full"), per = R("per"), tile = R("tile"), k0 = R("k0"), it0 = R("it0"), it1 = R("it1"), lgx = R("lgx"), bx = R("bx"), by = R("by");
+        const std::string kbeg = R("kbeg"), nkr = R("nk"), whole = R("whole"), ta = R("ta"), tb = R("tb"), td = R("td");
+        std::string l_top = "$mm" + std::to_string(u) + "_top", l_have = "$mm" + std::to_string(u) + "_have";
         o("ld.param.u32 %s, [%s_lgrid_x];", lgx.c_str(), s.kernel.c_str());
         o("ld.param.u32 %s, [%s_full_tiles];", full.c_str(), s.kernel.c_str());
-        o("ld.param.u32 %s, [%s_split];", split.c_str(), s.kernel.c_str());
+        o("ld.param.u32 %s, [%s_per];", per.c_str(), s.kernel.c_str());
         o("mov.u32 %s, %%ctaid.x;", cid.c_str());
+        // it1 != 0 marks a stream unit with slabs [it0, it1) of the tail tiles still to do
+        o("mov.u32 %s, 0;", it0.c_str());
+        o("mov.u32 %s, 0;", it1.c_str());
+        o("mov.u32 %s, %s;", tile.c_str(), cid.c_str());
+        o("mov.u32 %s, 0;", k0.c_str());
+        o("mov.u32 %s, %d;", nkr.c_str(), nk);
         o("setp.lt.u32 %s, %s, %s;", whole.c_str(), cid.c_str(), full.c_str());
-        o("sub.u32 %s, %s, %s;", t.c_str(), cid.c_str(), full.c_str());
-        o("div.u32 %s, %s, %s;", tile.c_str(), t.c_str(), split.c_str());
-        o("rem.u32 %s, %s, %s;", part.c_str(), t.c_str(), split.c_str());
+        o("@%s bra %s;", whole.c_str(), l_top.c_str());
+        o("ld.param.u32 %s, [%s_lgrid_y];", t.c_str(), s.kernel.c_str());
+        o("mul.lo.u32 %s, %s, %s;", t.c_str(), t.c_str(), lgx.c_str());
+        o("sub.u32 %s, %s, %s;", t.c_str(), t.c_str(), full.c_str());
+        o("mul.lo.u32 %s, %s, %d;", t.c_str(), t.c_str(), nk);               // slabs of all tail tiles
+        o("sub.u32 %s, %s, %s;", it0.c_str(), cid.c_str(), full.c_str());
+        o("mul.lo.u32 %s, %s, %s;", it0.c_str(), it0.c_str(), per.c_str());
+        o("add.u32 %s, %s, %s;", it1.c_str(), it0.c_str(), per.c_str());
+        o("min.u32 %s, %s, %s;", it1.c_str(), it1.c_str(), t.c_str());
+        o("setp.ge.u32 %s, %s, %s;", whole.c_str(), it0.c_str(), it1.c_str());
+        o("@%s bra %s;", whole.c_str(), l_skip.c_str());                    // a unit past the end of the slabs
+        o.label(l_top);
+        o("setp.eq.u32 %s, %s, 0;", whole.c_str(), it1.c_str());
+        o("@%s bra %s;", whole.c_str(), l_have.c_str());
+        // the next segment of this unit: the rest of its range, up to the end of the tile it falls in
+        o("div.u32 %s, %s, %d;", tile.c_str(), it0.c_str(), nk);
+        o("rem.u32 %s, %s, %d;", k0.c_str(), it0.c_str(), nk);
         o("add.u32 %s, %s, %s;", tile.c_str(), tile.c_str(), full.c_str());
-        o("selp.u32 %s, %s, %s, %s;", tile.c_str(), cid.c_str(), tile.c_str(), whole.c_str());
-        o("selp.u32 %s, 0, %s, %s;", part.c_str(), part.c_str(), whole.c_str());
-        o("selp.u32 %s, 1, %s, %s;", parts.c_str(), split.c_str(), whole.c_str());
+        o("mov.u32 %s, %d;", nkr.c_str(), nk);
+        o("sub.u32 %s, %s, %s;", nkr.c_str(), nkr.c_str(), k0.c_str());
+        o("sub.u32 %s, %s, %s;", t.c_str(), it1.c_str(), it0.c_str());
+        o("min.u32 %s, %s, %s;", nkr.c_str(), nkr.c_str(), t.c_str());
+        o("add.u32 %s, %s, %s;", it0.c_str(), it0.c_str(), nkr.c_str());
+        o.label(l_have);
         o("div.u32 %s, %s, %s;", by.c_str(), tile.c_str(), lgx.c_str());
         o("rem.u32 %s, %s, %s;", bx.c_str(), tile.c_str(), lgx.c_str());
-        o("mov.u32 %s, %u;", klen.c_str(), in.k);
-        o("div.u32 %s, %s, %s;", klen.c_str(), klen.c_str(), parts.c_str());
-        o("mul.lo.u32 %s, %s, %s;", kbeg.c_str(), part.c_str(), klen.c_str());
-        o("shr.u32 %s, %s, 4;", nkr.c_str(), klen.c_str());
+        o("shl.b32 %s, %s, 4;", kbeg.c_str(), k0.c_str());
         // tile pointers: A + by*128*lda*4 + kbeg*4 ; B + bx*512 + kbeg*ldb*4 ; D + by*128*ldd*4 + bx*512
         o("mul.wide.u32 %s, %s, %lld;", w.c_str(), by.c_str(), 128 * lda * 4);
         o("add.u64 %s, %s, %s;", ta.c_str(), s.a_base.c_str(), w.c_str());
@@ -256,25 +279,27 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
     o("bra %s;", l_loop.c_str());
     o.label(l_done);
     if (tail) {
-        const std::string parts = R("parts"), part = R("part"), tile = R("tile"), full = R("full"), tt = R("tt"), tk = R("tk"), pv = R("p");
+        const std::string k0 = R("k0"), per = R("per"), cid = R("cid"), uf = R("uf"), tile = R("tile"), full = R("full"), tt = R("tt"), tk = R("tk"), pv = R("p");
         const std::string ws = R("ws"), tkp = R("tkp"), pp = R("pp"), one = R("one"), t0 = R("t0"), notlast = R("notlast"), pl = R("pl");
         std::string l_store = "$mm" + std::to_string(u) + "_store", l_sum = "$mm" + std::to_string(u) + "_sum";
-        o("setp.eq.u32 %s, %s, 1;", one.c_str(), parts.c_str());
-        o("@%s bra %s;", one.c_str(), l_store.c_str());
-        // this part's partial sums: workspace + ((tile - full) * parts + part) * 64 KB, laid out [128][128]
+        o("setp.eq.u32 %s, %s, %d;", one.c_str(), R("nk").c_str(), nk);
+        o("@%s bra %s;", one.c_str(), l_store.c_str());                     // a whole tile
+        // A segment that is not a whole tile leaves its partial sums in the workspace, [slot][128][128]: slot 2u + 1
+        // when it starts the tile (then it is the last segment of unit u), slot 2u otherwise (then it is the first).
         o("ld.param.u64 %s, [%s_workspace];", ws.c_str(), s.kernel.c_str());
         o("ld.param.u64 %s, [%s_tickets];", tkp.c_str(), s.kernel.c_str());
         o("sub.u32 %s, %s, %s;", tt.c_str(), tile.c_str(), full.c_str());
         o("mul.wide.u32 %s, %s, 4;", w.c_str(), tt.c_str());
         o("add.u64 %s, %s, %s;", tkp.c_str(), tkp.c_str(), w.c_str());
-        o("mul.lo.u32 %s, %s, %s;", t.c_str(), tt.c_str(), parts.c_str());
-        o("mul.wide.u32 %s, %s, 65536;", w.c_str(), t.c_str());
-        o("add.u64 %s, %s, %s;", ws.c_str(), ws.c_str(), w.c_str());       // the tile's first part
         o("mul.wide.u32 %s, %s, 2048;", w.c_str(), ty.c_str());             // row ty*4, 512 bytes per row
         o("add.u64 %s, %s, %s;", ws.c_str(), ws.c_str(), w.c_str());
         o("mul.wide.u32 %s, %s, 16;", w.c_str(), tx.c_str());
-        o("add.u64 %s, %s, %s;", ws.c_str(), ws.c_str(), w.c_str());       // + this thread's position inside a part
-        o("mul.wide.u32 %s, %s, 65536;", w.c_str(), part.c_str());
+        o("add.u64 %s, %s, %s;", ws.c_str(), ws.c_str(), w.c_str());       // + this thread's position inside a slot
+        o("sub.u32 %s, %s, %s;", t.c_str(), cid.c_str(), full.c_str());
+        o("shl.b32 %s, %s, 1;", t.c_str(), t.c_str());
+        o("setp.eq.u32 %s, %s, 0;", pl.c_str(), k0.c_str());
+        o("@%s add.u32 %s, %s, 1;", pl.c_str(), t.c_str(), t.c_str());
+        o("mul.wide.u32 %s, %s, 65536;", w.c_str(), t.c_str());
         o("add.u64 %s, %s, %s;", pp.c_str(), ws.c_str(), w.c_str());
         for (int i = 0; i < 4 * RG; i++) {
             int off = ((i & 3) + (i >> 2) * SP) * 512;
@@ -290,24 +315,33 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
         o("@%s st.shared.u32 [%s], %s;", t0.c_str(), x.c_str(), tk.c_str());
         o("bar.sync 0;");
         o("ld.shared.u32 %s, [%s];", tk.c_str(), x.c_str());
-        o("add.u32 %s, %s, 1;", tk.c_str(), tk.c_str());
-        o("setp.ne.u32 %s, %s, %s;", notlast.c_str(), tk.c_str(), parts.c_str());
-        o("@%s bra %s;", notlast.c_str(), l_skip.c_str());                  // another part finishes this tile
+        // the units that hold a segment of this tile: uf = tt * nk / per starts it, every later one up to
+        // ((tt + 1) * nk - 1) / per begins inside it
+        o("mul.lo.u32 %s, %s, %d;", t.c_str(), tt.c_str(), nk);
+        o("div.u32 %s, %s, %s;", uf.c_str(), t.c_str(), per.c_str());
+        o("add.u32 %s, %s, %d;", t.c_str(), t.c_str(), nk - 1);
+        o("div.u32 %s, %s, %s;", tt.c_str(), t.c_str(), per.c_str());       // tt now holds the last unit
+        o("sub.u32 %s, %s, %s;", t.c_str(), tt.c_str(), uf.c_str());
+        o("setp.ne.u32 %s, %s, %s;", notlast.c_str(), tk.c_str(), t.c_str());
+        o("@%s bra %s;", notlast.c_str(), l_next.c_str());                  // another segment finishes this tile
         o("membar.gl;");
-        // the last part to arrive adds every part in index order, so the bits do not depend on who was last
+        // the last segment to arrive adds every segment in unit order, so the bits do not depend on who was last
         for (int i = 0; i < 16 * RG; i++) o("mov.b64 %s, 0;", acc2(i).c_str());
-        o("mov.u32 %s, 0;", pv.c_str());
-        o("mov.u64 %s, %s;", pp.c_str(), ws.c_str());
+        o("mov.u32 %s, %s;", pv.c_str(), uf.c_str());
         o.label(l_sum);
+        o("shl.b32 %s, %s, 1;", t.c_str(), pv.c_str());
+        o("setp.eq.u32 %s, %s, %s;", pl.c_str(), pv.c_str(), uf.c_str());
+        o("@%s add.u32 %s, %s, 1;", pl.c_str(), t.c_str(), t.c_str());
+        o("mul.wide.u32 %s, %s, 65536;", w.c_str(), t.c_str());
+        o("add.u64 %s, %s, %s;", pp.c_str(), ws.c_str(), w.c_str());
         for (int i = 0; i < 4 * RG; i++) {
             int off = ((i & 3) + (i >> 2) * SP) * 512;
             o("ld.global.cg.v2.b64 {%s, %s}, [%s+%d];", bp(0).c_str(), bp(1).c_str(), pp.c_str(), off);
             o("ld.global.cg.v2.b64 {%s, %s}, [%s+%d];", bp(2).c_str(), bp(3).c_str(), pp.c_str(), off + 256);
             for (int j = 0; j < 4; j++) o("add.rn.f32x2 %s, %s, %s;", acc2(i * 4 + j).c_str(), acc2(i * 4 + j).c_str(), bp(j).c_str());
         }
-        o("add.u64 %s, %s, 65536;", pp.c_str(), pp.c_str());
         o("add.u32 %s, %s, 1;", pv.c_str(), pv.c_str());
-        o("setp.lt.u32 %s, %s, %s;", pl.c_str(), pv.c_str(), parts.c_str());
+        o("setp.le.u32 %s, %s, %s;", pl.c_str(), pv.c_str(), tt.c_str());
         o("@%s bra %s;", pl.c_str(), l_sum.c_str());
         o("@%s st.global.u32 [%s], 0;", t0.c_str(), tkp.c_str());           // the ticket is back at zero for the next launch
         o.label(l_store);
@@ -330,7 +364,7 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
         std::string l_peer = "$mm" + std::to_string(u) + "_peer";
         o("ld.param.u32 %s, [%s_npeers];", np.c_str(), s.kernel.c_str());
         o("setp.eq.u32 %s, %s, 0;", pk.c_str(), np.c_str());
-        o("@%s bra %s;", pk.c_str(), l_skip.c_str());
+        o("@%s bra %s;", pk.c_str(), l_next.c_str());
         o("sub.u64 %s, %s, %s;", pq.c_str(), cp.c_str(), s.d_base.c_str());
         o("mov.u32 %s, 0;", pi.c_str());
         o("mov.b64 %s, %s_peers;", pb.c_str(), s.kernel.c_str());
@@ -347,6 +381,12 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
         o("setp.lt.u32 %s, %s, %s;", pk.c_str(), pi.c_str(), np.c_str());
         o("@%s bra %s;", pk.c_str(), l_peer.c_str());
         o("fence.acq_rel.sys;");
+        // a stream unit with slabs left goes on to its next segment, once no warp still reads this one's slabs
+        o.label(l_next);
+        o("setp.ge.u32 %s, %s, %s;", pk.c_str(), R("it0").c_str(), R("it1").c_str());
+        o("@%s bra %s;", pk.c_str(), l_skip.c_str());
+        o("bar.sync 0;");
+        o("bra %s;", ("$mm" + std::to_string(u) + "_top").c_str());
     }
     o.label(l_skip);
     o("bar.sync 0;");

@@ -12,15 +12,18 @@
 // Two CTAs are resident per SM (32 KB shared each).
 //
 // Tail wave.  With R resident CTAs (2 per SM) and T tiles, the last T mod R tiles would run as a
-// mostly empty wave (4096^2 in 128x128 tiles: 1024 tiles on 296 slots is 3.46 waves, paid as 4).
-// Its tiles are split along K into s = 2, 3 or 4 parts, one CTA each, when that shortens the
-// schedule: the parts take ceil(tail * s / R) / s of a tile's time instead of one (a tail of 136:
-// two parts, half a wave; a tail of 216: four parts, three waves of quarter tiles).  A part writes its 128x128 partial sums to
-// a workspace; the part that arrives last (a ticket counter per tile) adds the parts in index order
-// -- the result does not depend on arrival order -- stores the tile, and sets the counter back to
-// zero, so the workspace needs no clearing between launches.  The grid is one-dimensional: CTA c
-// below F (the full tiles) computes tile c over all of K; CTA F + s*t + p computes part p of tail
-// tile t.  CTAs are dispatched in index order, so the split parts form the last wave.
+// mostly empty wave (4096^2 in 128x128 tiles: 1024 tiles on 296 slots is 3.46 waves, paid as 4; a
+// 1024-row shard of it is 256 tiles, 0.86 of a wave paid as one).  Those tail tiles are instead
+// worked off by R stream units: their K slabs (16 columns of A each) are laid end to end, tile after
+// tile, and unit u takes slabs [u * per, (u + 1) * per) with per = ceil(tail slabs / R), so every slot
+// is busy for per / (K / 16) of a tile's time.  A unit's range may end one tile and begin the next: a
+// segment that covers a whole tile is stored; any other segment leaves its 128x128 partial sums in
+// the workspace (two slots per unit) and takes a ticket of its tile; the segment that takes the
+// tile's last ticket adds all of the tile's segments in unit order -- the result does not depend on
+// arrival order -- stores the tile, and sets the ticket back to zero, so the workspace needs no
+// clearing between launches.  The grid is one-dimensional: CTA c below F (the full tiles) computes
+// tile c over all of K; CTA F + u is stream unit u.  CTAs are dispatched in index order, so the
+// units form the last wave.
 #include <algorithm>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -47,37 +50,26 @@ constexpr int BM = 128, BN = 128, BK = 16, THREADS = 256;
 // four A fragments of a K step are the same address for the whole warp (pure broadcasts, one shared-memory wavefront
 // each) and the one B fragment is 512 contiguous bytes (four wavefronts): eight wavefronts per K step instead of
 // thirteen, and a warp's stores are whole 512-byte rows.
+// One segment: K slabs [k0, k0 + nk) of tile `tile`, by the whole CTA.  A whole tile (nk == K / 16) is stored; any other
+// segment goes through the workspace as described above.  Not inlined: as a function of its own it is allocated
+// registers for its main loop alone (inlined at both call sites of the kernel it measured 55.0 against 57.9 TFLOP/s).
 template <bool REG_STAGE, bool WARP_ROWS>
-__global__ void __launch_bounds__(THREADS, 2) sgemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C,
-                                                               int M, int N, int K, int full_tiles, int split, float* __restrict__ workspace,
-                                                               unsigned* __restrict__ tickets) {
+__device__ __noinline__ void sgemm_segment(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C, int N, int K, int tile, int k0, int nk,
+                                           int full_tiles, int per, float* __restrict__ workspace, unsigned* __restrict__ tickets) {
     // As holds the A slab transposed ([k][m]) so a thread's 4 consecutive rows are one float4.
     __shared__ __align__(16) float As[2][BK][BM];
     __shared__ __align__(16) float Bs[2][BK][BN];
-    __shared__ unsigned ticket_s;
+    __shared__ unsigned ticket_word;
+    unsigned* const ticket_s = &ticket_word;
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
-    const int tiles_n = N / BN;
-    int tile = blockIdx.x, part = 0, parts = 1;
-    if (tile >= full_tiles) {
-        const int r = tile - full_tiles;
-        tile = full_tiles + r / split;
-        part = r % split;
-        parts = split;
-    }
-    const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
-    const int k_len = K / parts, k_begin = part * k_len;   // the launcher makes K / parts a multiple of BK
-    (void)M;
-
+    const int tiles_n = N / BN, nkt = K / BK;
     // global -> register staging: A slab is 128 rows x 16 floats (4 float4 per row), B slab is
     // 16 rows x 128 floats (32 float4 per row); two float4 of each per thread.
     const int a_row = tid >> 2, a_col = (tid & 3) * 4;   // rows a_row and a_row + 64
     const int a_sw = a_row ^ ((tid & 3) << 3);           // swizzled column of the transposed slab: rows a_col .. a_col+3 all have (k >> 2) & 3 == tid & 3
     const int b_row = tid >> 5, b_col = (tid & 31) * 4;  // rows b_row and b_row + 8
-    // four running pointers, advanced by one K slab per iteration
-    const float* Ag0 = A + (size_t)(m0 + a_row) * K + k_begin + a_col;
-    const float* Ag1 = Ag0 + (size_t)64 * K;
-    const float* Bg0 = B + (size_t)(k_begin + b_row) * N + n0 + b_col;
-    const float* Bg1 = Bg0 + (size_t)8 * N;
+    // four running pointers, advanced by one K slab per iteration; set at the start of every segment
+    const float *Ag0 = nullptr, *Ag1 = nullptr, *Bg0 = nullptr, *Bg1 = nullptr;
     const size_t b_step = (size_t)BK * N;
     // global -> shared with cp.async, no staging registers: A lands transposed as eight 4-byte
     // copies per thread, B as two 16-byte copies; one commit group per K slab.
@@ -96,10 +88,6 @@ __global__ void __launch_bounds__(THREADS, 2) sgemm_f32_kernel(const float* __re
     constexpr int RI = WARP_ROWS ? 16 : 8, PJ = WARP_ROWS ? 2 : 4;
     const int lane = tid & 31, wrp = tid >> 5;
     float2 acc2[RI][PJ];   // acc2[i][p] = (C[i][2p], C[i][2p+1]) of the thread's block
-#pragma unroll
-    for (int i = 0; i < RI; i++)
-#pragma unroll
-        for (int p = 0; p < PJ; p++) acc2[i][p] = make_float2(0.0f, 0.0f);
     // position of output row i / first column of the thread's block inside the tile
     auto out_row = [&](int i) { return WARP_ROWS ? wrp * 16 + i : ty * 4 + (i & 3) + (i >> 2) * 64; };
     const int out_col = WARP_ROWS ? lane * 4 : tx * 4;
@@ -119,10 +107,18 @@ __global__ void __launch_bounds__(THREADS, 2) sgemm_f32_kernel(const float* __re
         *reinterpret_cast<float4*>(&Bs[buf][b_row][b_col]) = rb0;
         *reinterpret_cast<float4*>(&Bs[buf][b_row + 8][b_col]) = rb1;
     };
+    const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+    Ag0 = A + (size_t)(m0 + a_row) * K + k0 * BK + a_col;
+    Ag1 = Ag0 + (size_t)64 * K;
+    Bg0 = B + (size_t)(k0 * BK + b_row) * N + n0 + b_col;
+    Bg1 = Bg0 + (size_t)8 * N;
+#pragma unroll
+    for (int i = 0; i < RI; i++)
+#pragma unroll
+        for (int p = 0; p < PJ; p++) acc2[i][p] = make_float2(0.0f, 0.0f);
     if (REG_STAGE) { fetch(); stash(0); }
     else { copy_slab(0); asm volatile("cp.async.wait_group 0;" ::: "memory"); }
     __syncthreads();
-    const int nk = k_len / BK;
     for (int kb = 0; kb < nk; kb++) {
         const int buf = kb & 1;
         if (kb + 1 < nk) { if (REG_STAGE) fetch(); else copy_slab(buf ^ 1); }   // lands while this slab is multiplied
@@ -165,35 +161,38 @@ __global__ void __launch_bounds__(THREADS, 2) sgemm_f32_kernel(const float* __re
         else asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
     }
-    if (parts > 1) {
-        // partial sums of this part: [tail tile][part][128][128]
-        const int t = tile - full_tiles;
-        float* mine = workspace + ((size_t)t * parts + part) * (BM * BN);
+    if (nk != nkt) {
+        // A segment that is not a whole tile leaves its partial sums in the workspace: slot 2u + 1 when it starts the
+        // tile (then it is the last segment of unit u), slot 2u otherwise (then it is the first): [slot][128][128].
+        const unsigned t = (unsigned)(tile - full_tiles), unit = blockIdx.x - (unsigned)full_tiles;
+        float* mine = workspace + (size_t)(2 * unit + (k0 == 0 ? 1u : 0u)) * (BM * BN);
 #pragma unroll
         for (int i = 0; i < RI; i++) {
             float* prow = mine + out_row(i) * BN + out_col;
             *reinterpret_cast<float4*>(prow) = make_float4(acc2[i][0].x, acc2[i][0].y, acc2[i][1].x, acc2[i][1].y);
             if constexpr (!WARP_ROWS) *reinterpret_cast<float4*>(prow + 64) = make_float4(acc2[i][PJ - 2].x, acc2[i][PJ - 2].y, acc2[i][PJ - 1].x, acc2[i][PJ - 1].y);
         }
+        // the units that hold a segment of this tile: the first starts the tile, every later one begins inside it
+        const unsigned u_first = t * (unsigned)nkt / (unsigned)per, u_last = ((t + 1) * (unsigned)nkt - 1) / (unsigned)per;
         __threadfence();
         __syncthreads();
-        if (tid == 0) ticket_s = atomicAdd(&tickets[t], 1u);
+        if (tid == 0) *ticket_s = atomicAdd(&tickets[t], 1u);
         __syncthreads();
-        if (ticket_s != (unsigned)(parts - 1)) return;   // not the last part of this tile to finish
+        if (*ticket_s != u_last - u_first) return;   // not the last segment of this tile to finish
         __threadfence();
-        const float* base = workspace + (size_t)t * parts * (BM * BN);
 #pragma unroll
-        for (int i = 0; i < RI; i++) {
-            const int off = out_row(i) * BN + out_col, hi_off = WARP_ROWS ? 0 : 64;
-            float4 lo = __ldcg(reinterpret_cast<const float4*>(base + off)), hi = __ldcg(reinterpret_cast<const float4*>(base + off + hi_off));
-            for (int p = 1; p < parts; p++) {   // parts are added in index order, whichever finished last
-                const float4 l2 = __ldcg(reinterpret_cast<const float4*>(base + (size_t)p * (BM * BN) + off));
-                const float4 h2 = __ldcg(reinterpret_cast<const float4*>(base + (size_t)p * (BM * BN) + off + hi_off));
-                lo.x += l2.x; lo.y += l2.y; lo.z += l2.z; lo.w += l2.w;
-                hi.x += h2.x; hi.y += h2.y; hi.z += h2.z; hi.w += h2.w;
+        for (int i = 0; i < RI; i++)
+#pragma unroll
+            for (int p = 0; p < PJ; p++) acc2[i][p] = make_float2(0.0f, 0.0f);
+        for (unsigned u = u_first; u <= u_last; u++) {   // segments are added in unit order, whichever finished last
+            const float* base = workspace + (size_t)(2 * u + (u == u_first ? 1u : 0u)) * (BM * BN);
+#pragma unroll
+            for (int i = 0; i < RI; i++) {
+                const int off = out_row(i) * BN + out_col, hi_off = WARP_ROWS ? 0 : 64;
+                const float4 lo = __ldcg(reinterpret_cast<const float4*>(base + off)), hi = __ldcg(reinterpret_cast<const float4*>(base + off + hi_off));
+                acc2[i][0].x += lo.x; acc2[i][0].y += lo.y; acc2[i][1].x += lo.z; acc2[i][1].y += lo.w;
+                if constexpr (!WARP_ROWS) { acc2[i][PJ - 2].x += hi.x; acc2[i][PJ - 2].y += hi.y; acc2[i][PJ - 1].x += hi.z; acc2[i][PJ - 1].y += hi.w; }
             }
-            acc2[i][0] = make_float2(lo.x, lo.y); acc2[i][1] = make_float2(lo.z, lo.w);
-            if constexpr (!WARP_ROWS) { acc2[i][PJ - 2] = make_float2(hi.x, hi.y); acc2[i][PJ - 1] = make_float2(hi.z, hi.w); }
         }
         if (tid == 0) tickets[t] = 0;   // ready for the next launch
     }
@@ -205,9 +204,31 @@ __global__ void __launch_bounds__(THREADS, 2) sgemm_f32_kernel(const float* __re
     }
 }
 
-// Split-K workspace of the tail wave, one per device, sized for the largest tail that is ever split
-// (half a wave of tiles times the parts that fill the wave: at most one partial tile per resident
-// CTA) plus one ticket per tail tile.  Allocated on first use and kept.
+template <bool REG_STAGE, bool WARP_ROWS>
+__global__ void __launch_bounds__(THREADS, 2) sgemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C,
+                                                               int M, int N, int K, int full_tiles, int per, float* __restrict__ workspace,
+                                                               unsigned* __restrict__ tickets) {
+    const int nkt = K / BK;
+    // CTA c < full_tiles computes tile c over all of K.
+    if ((int)blockIdx.x < full_tiles) {
+        sgemm_segment<REG_STAGE, WARP_ROWS>(A, B, C, N, K, (int)blockIdx.x, 0, nkt, full_tiles, per, workspace, tickets);
+        return;
+    }
+    // CTA full_tiles + u is stream unit u: it walks K slabs [u * per, (u + 1) * per) of the tail tiles' slabs laid end
+    // to end, segment by segment; a segment ends with the tile it falls in.
+    const unsigned total = (unsigned)((M / BM) * (N / BN) - full_tiles) * (unsigned)nkt;
+    unsigned it0 = (blockIdx.x - (unsigned)full_tiles) * (unsigned)per;
+    const unsigned it1 = min(it0 + (unsigned)per, total);
+    while (it0 < it1) {
+        const int tile = full_tiles + (int)(it0 / (unsigned)nkt), k0 = (int)(it0 % (unsigned)nkt), nk = min(nkt - k0, (int)(it1 - it0));
+        sgemm_segment<REG_STAGE, WARP_ROWS>(A, B, C, N, K, tile, k0, nk, full_tiles, per, workspace, tickets);
+        it0 += (unsigned)nk;
+        __syncthreads();   // the slabs of this segment are no longer read
+    }
+}
+
+// Workspace of the tail wave, one per device: two partial tiles per stream unit and one ticket per
+// tail tile (never more than the unit count).  Allocated on first use and kept.
 struct TailWorkspace {
     float* partials = nullptr;
     unsigned* tickets = nullptr;
@@ -231,24 +252,26 @@ TailWorkspace* tail_workspace(int slots) {
     return &w;
 }
 
-// Chooses the split of the tail wave: tiles [0, *full) run whole, the rest in *split parts each.  s parts of 1/s of
-// the work take ceil(tail * s / slots) / s of a tile's time instead of one; the traffic of the partial sums (64 KB
-// written and read per part, charged at 6 TB/s against a tile time of 0.17 us per K step) is set against that.
-// A split that needs more than `max_parts` partial tiles is not considered (0 = no limit).
-void plan_tail(int tiles, int slots, int K, int max_parts, int* full, int* split) {
+// Plans the tail wave: tiles [0, *full) run whole, the rest are worked off by *units stream units of *per K slabs
+// each.  The units take per / (K / 16) of a tile's time instead of one; the traffic of the partial sums (at most two
+// 64 KB tiles written and read per unit, charged at 6 TB/s against a tile time of 0.17 us per K step) is set
+// against that, and a gain of less than 3 % is not taken.  `max_units` bounds the unit count (0 = the slots).
+void plan_tail(int tiles, int slots, int K, int max_units, int* full, int* per, int* units) {
     *full = tiles;
-    *split = 1;
-    const int tail = tiles % slots;                       // the whole problem, when it is less than one wave
-    if (tail == 0) return;
-    const double tile_us = 0.17 * (double)K;
-    double best = 1.0;
-    for (int s = 2; s <= 4; s++) {
-        if (K % (s * BK) != 0 || (max_parts > 0 && (long long)tail * s > max_parts)) continue;
-        const double waves = (double)(((long long)tail * s + slots - 1) / slots) / (double)s;
-        const double cost = waves + (double)tail * s * 131072.0 / 6.0e6 / tile_us;
-        if (cost < best - 1e-9) { best = cost; *split = s; }
-    }
-    if (*split > 1) *full = tiles - tail;
+    *per = 0;
+    *units = 0;
+    const long long tail = tiles % slots, nkt = K / BK;   // the whole problem, when it is less than one wave
+    if (tail == 0 || tail * nkt >= (1ll << 31)) return;
+    long long u = slots;
+    if (max_units > 0 && u > max_units) u = max_units;
+    const long long p = (tail * nkt + u - 1) / u;
+    if (p >= nkt) return;                                 // no more units than tiles: nothing to gain
+    u = (tail * nkt + p - 1) / p;
+    const double cost = (double)p / (double)nkt + (double)(2 * u) * 131072.0 / 6.0e6 / (0.17 * (double)K);
+    if (cost > 0.97) return;
+    *full = tiles - (int)tail;
+    *per = (int)p;
+    *units = (int)u;
 }
 
 }  // namespace
@@ -264,26 +287,26 @@ extern "C" int basalt_k_sgemm_f32_variant(const float* A, const float* B, float*
     static int resident = 0;
     if (!resident) resident = basalt_k::resident_ctas(sgemm_f32_kernel<true, false>, THREADS);
     const int tiles = (M / BM) * (N / BN), slots = resident * basalt_k::sm_count();
-    int full = tiles, split = 1;
-    if (!(flags & BASALT_K_SGEMM_NO_TAIL_SPLIT)) plan_tail(tiles, slots, K, 0, &full, &split);
+    int full = tiles, per = 0, units = 0;
+    if (!(flags & BASALT_K_SGEMM_NO_TAIL_SPLIT)) plan_tail(tiles, slots, K, 0, &full, &per, &units);
     TailWorkspace* w = nullptr;
-    if (split > 1) {
-        w = tail_workspace(std::max(slots, (tiles - full) * split));   // one partial tile per part, one ticket per tail tile
-        if (!w) { full = tiles; split = 1; }   // no workspace: the plain schedule is still correct
+    if (units > 0) {
+        w = tail_workspace(2 * slots);   // two partial tiles per unit, one ticket per tail tile
+        if (!w) { full = tiles; per = units = 0; }   // no workspace: the plain schedule is still correct
     }
-    const int grid = full + (tiles - full) * split;
+    const int grid = full + units;
     if (flags & BASALT_K_SGEMM_CP_ASYNC)   // the earlier staging with 4-byte cp.async copies
-        sgemm_f32_kernel<false, false><<<grid, THREADS, 0, (cudaStream_t)stream>>>(A, B, C, M, N, K, full, split, w ? w->partials : nullptr, w ? w->tickets : nullptr);
+        sgemm_f32_kernel<false, false><<<grid, THREADS, 0, (cudaStream_t)stream>>>(A, B, C, M, N, K, full, per, w ? w->partials : nullptr, w ? w->tickets : nullptr);
     else if (flags & BASALT_K_SGEMM_WARP_ROWS)
-        sgemm_f32_kernel<true, true><<<grid, THREADS, 0, (cudaStream_t)stream>>>(A, B, C, M, N, K, full, split, w ? w->partials : nullptr, w ? w->tickets : nullptr);
-    else sgemm_f32_kernel<true, false><<<grid, THREADS, 0, (cudaStream_t)stream>>>(A, B, C, M, N, K, full, split, w ? w->partials : nullptr, w ? w->tickets : nullptr);
+        sgemm_f32_kernel<true, true><<<grid, THREADS, 0, (cudaStream_t)stream>>>(A, B, C, M, N, K, full, per, w ? w->partials : nullptr, w ? w->tickets : nullptr);
+    else sgemm_f32_kernel<true, false><<<grid, THREADS, 0, (cudaStream_t)stream>>>(A, B, C, M, N, K, full, per, w ? w->partials : nullptr, w ? w->tickets : nullptr);
     return basalt_k::record(cudaGetLastError(), "sgemm_f32");
 }
 
 // ---- the same SGEMM with its tail workspace in a static device array: allocates nothing ----------
 namespace {
-constexpr int STATIC_MAX_PARTS = 304;    // partial tiles: one per resident CTA of a 148-SM part (296), rounded up
-constexpr int STATIC_MAX_TICKETS = 256;  // tail tiles (a split tail has at most STATIC_MAX_PARTS / 2)
+constexpr int STATIC_MAX_PARTS = 304;    // partial tiles: two per stream unit, so at most 152 units
+constexpr int STATIC_MAX_TICKETS = 256;  // tail tiles (fewer than the units)
 constexpr size_t STATIC_PARTIAL_BYTES = (size_t)STATIC_MAX_PARTS * BM * BN * sizeof(float);   // 19 MiB
 constexpr size_t STATIC_WS_BYTES = STATIC_PARTIAL_BYTES + STATIC_MAX_TICKETS * sizeof(unsigned);
 static __device__ __align__(256) unsigned char g_static_tail_ws[STATIC_WS_BYTES];
@@ -312,22 +335,21 @@ extern "C" int basalt_k_sgemm_f32_static_workspace(const float* A, const float* 
     static int resident = 0;
     if (!resident) resident = basalt_k::resident_ctas(sgemm_f32_kernel<true, false>, THREADS);
     const int tiles = (M / BM) * (N / BN), slots = resident * basalt_k::sm_count();
-    int full = tiles, split = 1;
-    plan_tail(tiles, slots, K, STATIC_MAX_PARTS, &full, &split);   // a split that does not fit the array is not taken
+    int full = tiles, per = 0, units = 0;
+    plan_tail(tiles, slots, K, STATIC_MAX_PARTS / 2, &full, &per, &units);   // no more units than the array has slot pairs for
     const int tail = tiles - full;
-    if (split > 1 && ((size_t)tail * split > (size_t)STATIC_MAX_PARTS || tail > STATIC_MAX_TICKETS)) {
+    if (units > 0 && (2 * units > STATIC_MAX_PARTS || tail > STATIC_MAX_TICKETS)) {
         char msg[200];
-        snprintf(msg, sizeof msg, "the tail wave needs %zu bytes of workspace (%d partial tiles); the static workspace holds %zu bytes (%d partial tiles)",
-                 (size_t)tail * split * BM * BN * sizeof(float), tail * split, STATIC_PARTIAL_BYTES, STATIC_MAX_PARTS);
+        snprintf(msg, sizeof msg, "the tail wave needs %d partial tiles and %d tickets; the static workspace holds %d and %d", 2 * units, tail, STATIC_MAX_PARTS, STATIC_MAX_TICKETS);
         return basalt_k::record_msg(1, "sgemm_f32_static_workspace", msg);
     }
     float* partials = reinterpret_cast<float*>(w.base);
     unsigned* tickets = reinterpret_cast<unsigned*>(w.base + STATIC_PARTIAL_BYTES);
-    if (split > 1) {   // the tickets must start at zero; the kernel leaves them at zero again
+    if (units > 0) {   // the tickets must start at zero; the kernel leaves them at zero again
         e = cudaMemsetAsync(tickets, 0, (size_t)tail * sizeof(unsigned), (cudaStream_t)stream);
         if (e != cudaSuccess) return basalt_k::record(e, "sgemm_f32_static_workspace (cudaMemsetAsync)");
     }
-    const int grid = full + tail * split;
-    sgemm_f32_kernel<true, false><<<grid, THREADS, 0, (cudaStream_t)stream>>>(A, B, C, M, N, K, full, split, partials, tickets);
+    const int grid = full + units;
+    sgemm_f32_kernel<true, false><<<grid, THREADS, 0, (cudaStream_t)stream>>>(A, B, C, M, N, K, full, per, partials, tickets);
     return basalt_k::record(cudaGetLastError(), "sgemm_f32_static_workspace");
 }

@@ -94,12 +94,12 @@ struct basalt_rt_ctx {
     // Device buffers kept between basalt_rt_cpu_launch calls, keyed by size: cuMemAlloc and
     // cuMemFree of a gigabyte cost more than the kernel they serve. Released with the context.
     std::multimap<size_t, CUdeviceptr> staging;
-    // Workspace of kernels whose plan says `tail=`: one 128x128 f32 partial tile per resident CTA and
-    // one ticket word per tile of a tail wave.  The kernels leave every ticket at zero.
+    // Workspace of kernels whose plan says `tail=`: two 128x128 f32 partial tiles per resident CTA (a stream
+    // unit) and one ticket word per tile of a tail wave.  The kernels leave every ticket at zero.
     CUdeviceptr tail_partials = 0, tail_tickets = 0;
     unsigned tail_slots = 0;
-    // Every split launch of the context shares that workspace, so split launches are ordered one after another:
-    // each records `tail_done` on its stream, and a split launch on another stream first waits for it.
+    // Every launch of the context with stream units shares that workspace, so such launches are ordered one after
+    // another: each records `tail_done` on its stream, and the next one on another stream first waits for it.
     CUevent tail_done = nullptr;
     CUstream tail_stream = nullptr;
     bool tail_pending = false;
@@ -126,8 +126,8 @@ struct Plan {
     unsigned per_thread = 0; // coarse entry: elements a thread handles in one trip of its loop (vector lanes x unroll)
     bool status = false;    // the entry takes a u64 parameter: a device int32 set when a bounded wait gave up
     unsigned logical_block[3] = {0, 0, 0};   // block the caller must ask for when it differs from the block launched
-    unsigned tail_k = 0;    // FFMA matmul with a split-K tail wave (K extent): the caller's 2-D grid is re-issued as a 1-D grid of
-                            // whole tiles followed by K-parts of the tail tiles; six trailing parameters (see basalt_rt_launch)
+    unsigned tail_k = 0;    // FFMA matmul with a streamed tail wave (K extent): the caller's 2-D grid is re-issued as a 1-D grid of
+                            // whole tiles followed by stream units over the tail tiles; six trailing parameters (see basalt_rt_launch)
     std::string pair;       // persistent kernel only: the same kernel lowered for clusters of two CTAs that share a 2 x lgrid-wide,
                             // two-row tile; launched instead when the caller's grid is even in x and y
     unsigned lgrid = 0;     // persistent kernel: the caller's grid goes in two trailing u32 parameters; lgrid logical CTAs
@@ -149,7 +149,7 @@ struct basalt_rt_function {
     CUfunction pair = nullptr;     // see Plan::pair
     CUdeviceptr status = 0;        // see Plan::status
     bool use_pair = true;          // basalt_rt_function_tune: take the two-SM entry when the grid allows it
-    bool tail_split = true;        //   split the K extent of a sparse last wave
+    bool tail_split = true;        //   work a sparse last wave off with stream units
     unsigned coarse_waves = 0;     //   coarse entries: exactly this many resident waves (0 = one loop trip per thread)
     bool has_plan = false;
     Plan plan;
@@ -552,7 +552,7 @@ int launch_impl(basalt_rt_function* fn, const uint32_t grid[3], const uint32_t b
     }
     if (fn->has_plan && fn->plan.tail_k) {
         // 128x128 tiles, one per logical CTA (grid x = tile column, y = tile row).  Whole tiles first,
-        // then the tiles of a sparse last wave split along K so that their parts fill one wave.
+        // then the tiles of a sparse last wave as stream units that keep every slot busy.
         const Plan& p = fn->plan;
         basalt_rt_ctx* ctx = fn->mod->ctx;
         const unsigned* want = p.logical_block[0] ? p.logical_block : p.block;
@@ -568,31 +568,26 @@ int launch_impl(basalt_rt_function* fn, const uint32_t grid[3], const uint32_t b
         int resident = 0;
         if (f.cuOccupancyMaxActiveBlocksPerMultiprocessor(&resident, fn->fn, (int)p.block[0], p.smem) != CUDA_SUCCESS || resident < 1) resident = 1;
         const uint32_t slots = (uint32_t)ctx->sm_count * (uint32_t)resident;
-        uint32_t full = tiles, split = 1;
-        const uint32_t tail = tiles % slots;
-        // The tiles of a last wave that does not fill the slots -- or a whole problem smaller than one wave -- run as
-        // s K-parts each when that shortens the schedule: s parts of 1/s of the work take ceil(tail * s / slots) / s of a
-        // tile's time instead of one (216 tail tiles on 296 slots: four parts each are three waves of quarter tiles,
-        // 0.75), against the traffic of the partial sums (64 KB written and read per part, charged at 6 TB/s against a
-        // tile time of 0.17 us per K step).  With a gathering epilogue the finest split wins ties: the tiles of the
-        // first wave of parts are then complete, and on their way to the peers, while the next wave still computes.
-        if (fn->tail_split && tail != 0) {
-            const double tile_us = 0.17 * (double)p.tail_k;
-            double best = 1.0;
-            for (uint32_t sp = 2; sp <= 4; sp++) {
-                if (p.tail_k % (sp * 16) != 0) continue;
-                const double waves = (double)(((uint64_t)tail * sp + slots - 1) / slots) / (double)sp;
-                const double traffic_us = (double)tail * sp * 131072.0 / 6.0e6;
-                const double cost = waves + traffic_us / tile_us - (n_peers > 0 ? 0.001 * sp : 0.0);
-                if (cost < best - 1e-9) { best = cost; split = sp; }
+        uint32_t full = tiles, per = 0, units = 0;
+        const uint64_t tail = tiles % slots, nkt = p.tail_k / 16;
+        // The tiles of a last wave that does not fill the slots -- or a whole problem smaller than one wave -- are worked
+        // off by one stream unit per slot: the tail tiles' K slabs laid end to end, `per` = ceil(slabs / slots) to a
+        // unit, so every slot is busy for per / (K / 16) of a tile's time instead of one (256 tiles on 296 slots: 0.87;
+        // 136 on 296: 0.46).  Against that stands the traffic of the partial sums (at most two 64 KB tiles written and
+        // read per unit, charged at 6 TB/s against a tile time of 0.17 us per K step); a gain below 3 % is not taken.
+        if (fn->tail_split && tail != 0 && tail * nkt < (1ull << 31)) {
+            const uint64_t pr = (tail * nkt + slots - 1) / slots;
+            if (pr < nkt) {
+                const uint64_t un = (tail * nkt + pr - 1) / pr;
+                const double cost = (double)pr / (double)nkt + (double)(2 * un) * 131072.0 / 6.0e6 / (0.17 * (double)p.tail_k);
+                if (cost <= 0.97) { full = tiles - (uint32_t)tail; per = (uint32_t)pr; units = (uint32_t)un; }
             }
-            if (split > 1) full = tiles - tail;
         }
         std::unique_lock<std::mutex> lock(ctx->mu, std::defer_lock);
-        if (split > 1) lock.lock();
-        // one 64 KB partial tile per part (a wave of parts at least), one ticket per split tile
-        const uint32_t need = std::max(slots, (tiles - full) * split);
-        if (split > 1 && ctx->tail_slots < need) {
+        if (units) lock.lock();
+        // two 64 KB partial tiles per unit, one ticket per tail tile (fewer than the units)
+        const uint32_t need = 2 * slots;
+        if (units && ctx->tail_slots < need) {
             int rc = make_current(ctx);
             if (rc) return rc;
             if (ctx->tail_partials) { f.cuMemFree(ctx->tail_partials); f.cuMemFree(ctx->tail_tickets); ctx->tail_partials = ctx->tail_tickets = 0; ctx->tail_slots = 0; }
@@ -610,14 +605,14 @@ int launch_impl(basalt_rt_function* fn, const uint32_t grid[3], const uint32_t b
         all.push_back(&lgx);
         all.push_back(&lgy);
         all.push_back(&full);
-        all.push_back(&split);
+        all.push_back(&per);
         all.push_back(&ws);
         all.push_back(&tk);
         if (p.gather >= 0) {
             all.push_back(peer_table);
             all.push_back(&peer_count);
         }
-        if (split > 1) {
+        if (units) {
             if (!ctx->tail_done) {
                 int rc = check(f, "cuEventCreate", f.cuEventCreate(&ctx->tail_done, CU_EVENT_DISABLE_TIMING));
                 if (rc) return rc;
@@ -627,8 +622,8 @@ int launch_impl(basalt_rt_function* fn, const uint32_t grid[3], const uint32_t b
                 if (rc) return rc;
             }
         }
-        int rc = check(f, "cuLaunchKernel", f.cuLaunchKernel(fn->fn, full + (tiles - full) * split, 1, 1, p.block[0], p.block[1], p.block[2], p.smem, (CUstream)stream, all.data(), nullptr));
-        if (!rc && split > 1) {
+        int rc = check(f, "cuLaunchKernel", f.cuLaunchKernel(fn->fn, full + units, 1, 1, p.block[0], p.block[1], p.block[2], p.smem, (CUstream)stream, all.data(), nullptr));
+        if (!rc && units) {
             rc = check(f, "cuEventRecord", f.cuEventRecord(ctx->tail_done, (CUstream)stream));
             ctx->tail_stream = (CUstream)stream;
             ctx->tail_pending = true;

@@ -155,8 +155,8 @@ void basalt_rt_host_free(basalt_rt_ctx *ctx, void *p);
  * not synchronise; pass stream NULL and call basalt_rt_ctx_sync for the reference behaviour.
  * For a kernel with a launch plan, the tensor-map parameters are built from the pointer and size
  * parameters and appended here; the caller still passes only the BIR parameters.
- * Launches of the FFMA matmul that split a sparse last wave along K share one workspace per
- * context; the runtime orders them itself (each such launch waits, on its own stream, for the
+ * Launches of the FFMA matmul that work a sparse last wave off with stream units (partial sums
+ * along K) share one workspace per context; the runtime orders them itself (each such launch waits, on its own stream, for the
  * previous one wherever that ran), so callers may issue them from any streams and host threads. */
 int basalt_rt_launch(basalt_rt_function *fn, const uint32_t grid[3], const uint32_t block[3],
                      uint32_t shared_mem_bytes, void *stream, void **params);

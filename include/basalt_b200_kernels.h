@@ -49,25 +49,26 @@ int basalt_k_imad_peak(uint32_t *out, int64_t out_elems, int iters, int64_t *ima
 
 /* C[MxN] = A[MxK] * B[KxN], row-major fp32, FFMA only (no TF32): the workload of
  * examples/cpu_launch_tiled_sgemm.c (there 32^3 with a C addend). M, N multiples of 128, K of 16.
- * A problem whose last wave of tiles is sparse runs those tiles as split-K parts through a workspace
- * that is allocated on first use and shared by all calls on a device: such calls must not overlap in
+ * A problem whose last wave of tiles is sparse (or which is smaller than one wave) has those tiles
+ * worked off by stream units -- one per resident CTA, each an equal run of the tail tiles' K slabs,
+ * summed per tile in a fixed order -- through a workspace that is allocated on first use and shared by all calls on a device: such calls must not overlap in
  * time on one device (issue them on one stream, or order the streams with events); calls on one
  * stream never overlap. */
 int basalt_k_sgemm_f32(const float *A, const float *B, float *C, int M, int N, int K, void *stream);
 
 /* basalt_k_sgemm_f32 with parts of its schedule switched off, for A/B timing: NO_TAIL_SPLIT runs every
- * tile whole (no split-K parts for a sparse last wave or for a problem smaller than one wave); CP_ASYNC
+ * tile whole (no stream units for a sparse last wave or for a problem smaller than one wave); CP_ASYNC
  * stages the A slab with 4-byte cp.async copies instead of through registers.  flags = 0 is
  * basalt_k_sgemm_f32.  No counterpart in the reference. */
 enum { BASALT_K_SGEMM_NO_TAIL_SPLIT = 1, BASALT_K_SGEMM_CP_ASYNC = 2, BASALT_K_SGEMM_WARP_ROWS = 4 };
 int basalt_k_sgemm_f32_variant(const float *A, const float *B, float *C, int M, int N, int K, int flags, void *stream);
 
-/* basalt_k_sgemm_f32 with the split-K workspace of its tail wave in a static device array instead
+/* basalt_k_sgemm_f32 with the workspace of its tail wave in a static device array instead
  * of device memory allocated on first use: this entry point allocates nothing (no cudaMalloc,
  * cudaFree or allocating library call).  Same arguments and results.  The array holds 304 partial
- * 128x128 f32 tiles (19 MiB) and 256 tickets; a split of the tail wave that would need more is not
- * taken (the tail then runs whole, or in fewer parts, where basalt_k_sgemm_f32 would have split it
- * further: the sums are then added in another order).  The first
+ * 128x128 f32 tiles (19 MiB: two per stream unit of the tail wave, so at most 152 units where
+ * basalt_k_sgemm_f32 uses one per resident CTA) and 256 tickets; when the two entry points cut a
+ * tail wave differently, its sums are added in another order.  The first
  * call on each device looks the array's address up (cudaGetSymbolAddress) with that device current;
  * make that first call before any stream capture.  All calls on a device share the one array:
  * calls that overlap in time (different streams) race; calls on one stream do not.  Every call

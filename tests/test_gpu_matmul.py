@@ -74,16 +74,17 @@ def test_sgemm_full_size(gpu, orc, how):
 
 
 @pytest.mark.parametrize("how", ["hand", "cta128"])
-@pytest.mark.parametrize("shape", [(2560, 1920, 64), (2560, 1920, 48), (4096, 4736, 32), (2432, 2048, 16), (2048, 4096, 1024)])
+@pytest.mark.parametrize("shape", [(2560, 1920, 64), (2560, 1920, 48), (4096, 4736, 32), (2432, 2048, 16), (2048, 4096, 1024), (1024, 4096, 2048)])
 def test_sgemm_tail_wave(gpu, how, shape):
-    # More tiles than resident CTAs with a sparse last wave: 300 tiles (tail 4, split in 4 or, for
-    # K = 48, in 3 parts), 1184 tiles (no tail on 296 slots), 304 tiles with K too short to split,
-    # 512 tiles (a tail of 216, more than half a wave: four parts each, three waves of quarter tiles).
-    # Small integers: every partial sum is exact, so any split of K must give the same bits; run
-    # twice, since a split tail leaves its tickets behind for the next launch.
+    # A last wave that does not fill the 296 CTA slots is worked off by stream units over the tail tiles' K slabs:
+    # 300 tiles (tail 4: 16 units of one slab for K = 64, 12 for K = 48), 1184 tiles (no tail), 304 tiles with one
+    # slab per tile (nothing to stream), 512 tiles (tail 216: 295 units of 47 slabs, which cross tile boundaries at
+    # 64), 256 tiles (less than one wave: 293 units of 112 of a tile's 128 slabs).
+    # Small integers: every partial sum is exact, so any cut of K must give the same bits; run
+    # twice, since a streamed tail leaves its tickets behind for the next launch.
     M, N, K = shape
     A, B, _ = sgemm_fixture(M, N, K)
-    want = (A.astype(np.int64) @ B.astype(np.int64)).astype(np.float32)
+    want = (A.astype(np.float64) @ B.astype(np.float64)).astype(np.float32)   # exact: the sums stay far below 2^53
     for _ in range(2):
         assert np.array_equal(run_sgemm(gpu, how, A, B), want)
 
