@@ -150,6 +150,7 @@ struct basalt_rt_function {
     CUdeviceptr status = 0;        // see Plan::status
     bool use_pair = true;          // basalt_rt_function_tune: take the two-SM entry when the grid allows it
     bool tail_split = true;        //   work a sparse last wave off with stream units
+    unsigned tail_rounds = 0;      //   rounds of stream units (0 = one, two with a gathering epilogue)
     unsigned coarse_waves = 0;     //   coarse entries: exactly this many resident waves (0 = one loop trip per thread)
     bool has_plan = false;
     Plan plan;
@@ -575,18 +576,25 @@ int launch_impl(basalt_rt_function* fn, const uint32_t grid[3], const uint32_t b
         // unit, so every slot is busy for per / (K / 16) of a tile's time instead of one (256 tiles on 296 slots: 0.87;
         // 136 on 296: 0.46).  Against that stands the traffic of the partial sums (at most two 64 KB tiles written and
         // read per unit, charged at 6 TB/s against a tile time of 0.17 us per K step); a gain below 3 % is not taken.
+        // With a gathering epilogue the units come in two rounds of one per slot (CTAs start in index order): the tiles
+        // of the first round are complete, and on their way to the peers, while the second round computes; otherwise
+        // every tile of the tail would finish, and leave, at the very end.
+        uint32_t rounds = fn->tail_rounds ? fn->tail_rounds : (n_peers > 0 ? 2u : 1u);
         if (fn->tail_split && tail != 0 && tail * nkt < (1ull << 31)) {
-            const uint64_t pr = (tail * nkt + slots - 1) / slots;
+            while (rounds > 1 && (tail * nkt) / ((uint64_t)slots * rounds) < 16) rounds--;   // at least 16 slabs to a unit
+            const uint64_t want = (uint64_t)slots * rounds;
+            const uint64_t pr = (tail * nkt + want - 1) / want;
             if (pr < nkt) {
                 const uint64_t un = (tail * nkt + pr - 1) / pr;
-                const double cost = (double)pr / (double)nkt + (double)(2 * un) * 131072.0 / 6.0e6 / (0.17 * (double)p.tail_k);
+                const double waves = (double)((un + slots - 1) / slots) * (double)pr / (double)nkt;
+                const double cost = waves + (double)(2 * un) * 131072.0 / 6.0e6 / (0.17 * (double)p.tail_k);
                 if (cost <= 0.97) { full = tiles - (uint32_t)tail; per = (uint32_t)pr; units = (uint32_t)un; }
             }
         }
         std::unique_lock<std::mutex> lock(ctx->mu, std::defer_lock);
         if (units) lock.lock();
         // two 64 KB partial tiles per unit, one ticket per tail tile (fewer than the units)
-        const uint32_t need = 2 * slots;
+        const uint32_t need = std::max(2 * slots, 2 * units);
         if (units && ctx->tail_slots < need) {
             int rc = make_current(ctx);
             if (rc) return rc;
@@ -707,6 +715,7 @@ int basalt_rt_function_tune(basalt_rt_function* fn, const char* key, int value) 
     const std::string k = key;
     if (k == "pair") fn->use_pair = value != 0;
     else if (k == "tail_split") fn->tail_split = value != 0;
+    else if (k == "tail_rounds") fn->tail_rounds = value < 0 ? 0u : value > 8 ? 8u : (unsigned)value;
     else if (k == "coarse_waves") fn->coarse_waves = value > 0 ? (unsigned)value : 0;
     else return set_err(4, 0, "basalt_rt_function_tune", "unknown key: " + k);
     return 0;

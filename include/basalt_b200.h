@@ -189,6 +189,8 @@ int basalt_rt_occupancy(basalt_rt_function *fn, uint32_t block_threads, uint32_t
 /* Switches one of the runtime's launch policies for this function handle, for A/B timing and tests; a
  * handle starts with every policy on.  "pair" = 0: keep the one-SM entry of the tcgen05 matmul on
  * grids that are even in x and y.  "tail_split" = 0: run every tile of the FFMA matmul whole.
+ * "tail_rounds" = r (1 to 8; 0 = the default: one, or two under basalt_rt_launch_gather): the stream units
+ * that work the FFMA matmul's tail wave off come in r rounds of one unit per CTA slot.
  * "coarse_waves" = w > 0: launch a coarsened one-element-per-thread kernel on exactly w resident
  * waves instead of one loop trip per thread.  Unknown keys are refused (kind 4).  The state lives in
  * the handle: nothing here reads the process environment.  No counterpart in the reference. */

@@ -254,19 +254,21 @@ def test_emitted_fused_gather_into_loop_back_peers_f16(gpu, orc, n_peers):
         assert np.array_equal(got[row0:row0 + rows].view(np.uint16), first)
 
 
-@pytest.mark.parametrize("shape", [(256, 256, 64), (2560, 1920, 64), (512, 4096, 256)])
-def test_emitted_fused_gather_into_loop_back_peers_f32(gpu, shape):
-    # the FFMA matmul's gathering epilogue, whole tiles and the split tail wave (300 tiles: the last four
-    # are summed from K-parts by the part that finishes last, which then stores to every buffer); the third
-    # shape is an 8-GPU shard: 128 tiles, less than half a wave, run as 512 quarter-K parts (more than one wave)
+@pytest.mark.parametrize("shape,rounds", [((256, 256, 64), 0), ((2560, 1920, 64), 0), ((512, 4096, 256), 0), ((512, 4096, 2048), 0), ((512, 4096, 2048), 3)])
+def test_emitted_fused_gather_into_loop_back_peers_f32(gpu, shape, rounds):
+    # the FFMA matmul's gathering epilogue, whole tiles and the streamed tail wave (300 tiles: the last four are
+    # summed from one-slab segments by the segment that finishes last, which then stores to every buffer); the
+    # third and fourth shapes are 8-GPU shards: 128 tiles, less than half a wave, worked off by one round of stream
+    # units (K = 256: seven slabs to a unit) or, with enough slabs, by two rounds -- three when tuned so
     rows, N, K = shape
     A, B, _ = sgemm_fixture(rows, N, K)
-    want = (A.astype(np.int64) @ B.astype(np.int64)).astype(np.float32)
+    want = (A.astype(np.float64) @ B.astype(np.float64)).astype(np.float32)   # exact: small integers
     dA, dB = dev(gpu, A), dev(gpu, B)
     row0, M_all = 128, rows + 256
     poison = np.full((M_all, N), -7.0, np.float32)
     bufs = [dev(gpu, poison) for _ in range(3)]
     fn = emitted(gpu, kb.sgemm_cta128(rows, N, K), "sgemm_f32")
+    fn.tune("tail_rounds", rounds)
     go = fn.bind_gather((N // 128, rows // 128), 256, 0, [dA, dB, b.ptr(bufs[0].device_ptr() + row0 * N * 4)],
                         [b_.device_ptr() + row0 * N * 4 for b_ in bufs[1:]])
     for _ in range(2):
