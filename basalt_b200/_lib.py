@@ -72,6 +72,7 @@ def _load() -> C.CDLL:
         "basalt_rt_ctx_sync": (C.c_int, [vp]),
         "basalt_rt_kernel_status": (C.c_int, [vp, i32p]),
         "basalt_rt_occupancy": (C.c_int, [vp, C.c_uint32, C.c_uint32, P(C.c_int), P(C.c_int)]),
+        "basalt_rt_tail_plan": (None, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, P(C.c_uint32)]),
         "basalt_rt_stream_create": (C.c_int, [vp, P(vp)]),
         "basalt_rt_stream_destroy": (C.c_int, [vp, vp]),
         "basalt_rt_stream_sync": (C.c_int, [vp, vp]),

@@ -506,6 +506,33 @@ int basalt_rt_planned_geometry(basalt_rt_function* fn, void** params, uint32_t g
     return 0;
 }
 
+// The schedule of an FFMA matmul whose plan says `tail=`: out = {full, per, units}.  Tiles [0, full) run whole, one CTA
+// each.  The tiles of a last wave that does not fill the slots -- or a whole problem smaller than one wave -- are worked
+// off by stream units: the tail tiles' K slabs (16 columns of A each) laid end to end, `per` = ceil(slabs / (slots x
+// rounds)) to a unit, so every slot is busy for rounds x per / (K / 16) of a tile's time instead of one (256 tiles on 296
+// slots: 0.87; 136 on 296: 0.46).  Against that stands the traffic of the partial sums (at most two 64 KB tiles written
+// and read per unit, charged at 6 TB/s against a tile time of 0.17 us per K step); a gain below 3 % is not taken, and
+// then full = tiles, per = units = 0.  A pure function of its arguments.
+void basalt_rt_tail_plan(uint32_t tiles, uint32_t slots, uint32_t k_extent, uint32_t rounds, uint32_t out[3]) {
+    out[0] = tiles;
+    out[1] = out[2] = 0;
+    if (slots == 0 || k_extent < 16) return;
+    const uint64_t tail = tiles % slots, nkt = k_extent / 16;
+    if (tail == 0 || tail * nkt >= (1ull << 31)) return;
+    if (rounds < 1) rounds = 1;
+    while (rounds > 1 && (tail * nkt) / ((uint64_t)slots * rounds) < 16) rounds--;   // at least 16 slabs to a unit
+    const uint64_t want = (uint64_t)slots * rounds;
+    const uint64_t pr = (tail * nkt + want - 1) / want;
+    if (pr >= nkt) return;                                                            // no more units than tiles
+    const uint64_t un = (tail * nkt + pr - 1) / pr;
+    const double waves = (double)((un + slots - 1) / slots) * (double)pr / (double)nkt;
+    const double cost = waves + (double)(2 * un) * 131072.0 / 6.0e6 / (0.17 * (double)k_extent);
+    if (cost > 0.97) return;
+    out[0] = tiles - (uint32_t)tail;
+    out[1] = (uint32_t)pr;
+    out[2] = (uint32_t)un;
+}
+
 namespace {
 int launch_impl(basalt_rt_function* fn, const uint32_t grid[3], const uint32_t block[3], uint32_t shared_mem_bytes, void* stream, void** params,
                 const uint64_t* peer_out, int n_peers);
@@ -569,28 +596,12 @@ int launch_impl(basalt_rt_function* fn, const uint32_t grid[3], const uint32_t b
         int resident = 0;
         if (f.cuOccupancyMaxActiveBlocksPerMultiprocessor(&resident, fn->fn, (int)p.block[0], p.smem) != CUDA_SUCCESS || resident < 1) resident = 1;
         const uint32_t slots = (uint32_t)ctx->sm_count * (uint32_t)resident;
-        uint32_t full = tiles, per = 0, units = 0;
-        const uint64_t tail = tiles % slots, nkt = p.tail_k / 16;
-        // The tiles of a last wave that does not fill the slots -- or a whole problem smaller than one wave -- are worked
-        // off by one stream unit per slot: the tail tiles' K slabs laid end to end, `per` = ceil(slabs / slots) to a
-        // unit, so every slot is busy for per / (K / 16) of a tile's time instead of one (256 tiles on 296 slots: 0.87;
-        // 136 on 296: 0.46).  Against that stands the traffic of the partial sums (at most two 64 KB tiles written and
-        // read per unit, charged at 6 TB/s against a tile time of 0.17 us per K step); a gain below 3 % is not taken.
         // With a gathering epilogue the units come in two rounds of one per slot (CTAs start in index order): the tiles
         // of the first round are complete, and on their way to the peers, while the second round computes; otherwise
         // every tile of the tail would finish, and leave, at the very end.
-        uint32_t rounds = fn->tail_rounds ? fn->tail_rounds : (n_peers > 0 ? 2u : 1u);
-        if (fn->tail_split && tail != 0 && tail * nkt < (1ull << 31)) {
-            while (rounds > 1 && (tail * nkt) / ((uint64_t)slots * rounds) < 16) rounds--;   // at least 16 slabs to a unit
-            const uint64_t want = (uint64_t)slots * rounds;
-            const uint64_t pr = (tail * nkt + want - 1) / want;
-            if (pr < nkt) {
-                const uint64_t un = (tail * nkt + pr - 1) / pr;
-                const double waves = (double)((un + slots - 1) / slots) * (double)pr / (double)nkt;
-                const double cost = waves + (double)(2 * un) * 131072.0 / 6.0e6 / (0.17 * (double)p.tail_k);
-                if (cost <= 0.97) { full = tiles - (uint32_t)tail; per = (uint32_t)pr; units = (uint32_t)un; }
-            }
-        }
+        uint32_t plan3[3] = {tiles, 0, 0};
+        if (fn->tail_split) basalt_rt_tail_plan(tiles, slots, p.tail_k, fn->tail_rounds ? fn->tail_rounds : (n_peers > 0 ? 2u : 1u), plan3);
+        uint32_t full = plan3[0], per = plan3[1], units = plan3[2];
         std::unique_lock<std::mutex> lock(ctx->mu, std::defer_lock);
         if (units) lock.lock();
         // two 64 KB partial tiles per unit, one ticket per tail tile (fewer than the units)

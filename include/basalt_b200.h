@@ -186,6 +186,13 @@ int basalt_rt_planned_geometry(basalt_rt_function *fn, void **params, uint32_t g
  * counterpart in the reference, which leaves grid sizing to its tests. */
 int basalt_rt_occupancy(basalt_rt_function *fn, uint32_t block_threads, uint32_t shared_mem_bytes, int *ctas_per_sm,
                         int *sm_count);
+/* The schedule basalt_rt_launch gives an FFMA matmul whose plan says `tail=` (kernels/sgemm.cu describes the scheme):
+ * out = {full, per, units}.  Of `tiles` 128x128 tiles on `slots` resident CTAs, tiles [0, full) run whole, one CTA each;
+ * the rest are worked off by `units` stream units of `per` K slabs (16 columns of A) each, the tail tiles' slabs laid end
+ * to end, in `rounds` rounds of one unit per slot.  per = units = 0 and full = tiles when nothing would be gained.  A pure
+ * function (no context, no device): exported so that the index arithmetic of the units can be checked without a GPU.
+ * No counterpart in the reference. */
+void basalt_rt_tail_plan(uint32_t tiles, uint32_t slots, uint32_t k_extent, uint32_t rounds, uint32_t out[3]);
 /* Switches one of the runtime's launch policies for this function handle, for A/B timing and tests; a
  * handle starts with every policy on.  "pair" = 0: keep the one-SM entry of the tcgen05 matmul on
  * grids that are even in x and y.  "tail_split" = 0: run every tile of the FFMA matmul whole.
