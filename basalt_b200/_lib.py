@@ -68,6 +68,7 @@ def _load() -> C.CDLL:
         "basalt_rt_launch": (C.c_int, [vp, C.c_uint32 * 3, C.c_uint32 * 3, C.c_uint32, vp, P(vp)]),
         "basalt_rt_function_tune": (C.c_int, [vp, C.c_char_p, C.c_int]),
         "basalt_rt_launch_gather": (C.c_int, [vp, C.c_uint32 * 3, C.c_uint32 * 3, C.c_uint32, vp, P(vp), P(u64), C.c_int]),
+        "basalt_rt_launch_gather_multicast": (C.c_int, [vp, C.c_uint32 * 3, C.c_uint32 * 3, C.c_uint32, vp, P(vp), u64]),
         "basalt_rt_planned_geometry": (C.c_int, [vp, P(vp), C.c_uint32 * 3, C.c_uint32 * 3, P(C.c_uint32)]),
         "basalt_rt_ctx_sync": (C.c_int, [vp]),
         "basalt_rt_kernel_status": (C.c_int, [vp, i32p]),

@@ -108,7 +108,7 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
         decls->push_back(d);
         snprintf(d, sizeof d, "\t.reg .b64 %%mm%d_pb, %%mm%d_pz, %%mm%d_pq;", u, u, u);
         decls->push_back(d);
-        snprintf(d, sizeof d, "\t.reg .pred %%mm%d_pk;", u);
+        snprintf(d, sizeof d, "\t.reg .pred %%mm%d_pk, %%mm%d_mc;", u, u);
         decls->push_back(d);
     }
     snprintf(d, sizeof d, "\t.shared .align 16 .b8 __mm%d_as[16384];", u);
@@ -365,12 +365,17 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
         o("ld.param.u32 %s, [%s_npeers];", np.c_str(), s.kernel.c_str());
         o("setp.eq.u32 %s, %s, 0;", pk.c_str(), np.c_str());
         o("@%s bra %s;", pk.c_str(), l_next.c_str());
+        // bit 31 of the count: the first table entry is the result's address in an NVLink multicast mapping of the whole
+        // group, and the tile leaves with one multimem.st per 16 bytes
+        o("setp.ge.u32 %s, %s, 0x80000000;", R("mc").c_str(), np.c_str());
+        o("and.b32 %s, %s, 0x7fffffff;", np.c_str(), np.c_str());
         o("sub.u64 %s, %s, %s;", pq.c_str(), cp.c_str(), s.d_base.c_str());
         o("mov.u32 %s, 0;", pi.c_str());
         o("mov.b64 %s, %s_peers;", pb.c_str(), s.kernel.c_str());
         o.label(l_peer);
         o("ld.param.u64 %s, [%s];", pz.c_str(), pb.c_str());
         o("add.u64 %s, %s, %s;", pz.c_str(), pz.c_str(), pq.c_str());
+        o("@%s bra %s;", R("mc").c_str(), ("$mm" + std::to_string(u) + "_mcast").c_str());
         for (int i = 0; i < 4 * RG; i++) {
             long long rowoff = ((i & 3) + (i >> 2) * SP) * ldd * 4;
             o("st.global.v2.b64 [%s+%lld], {%s, %s};", pz.c_str(), rowoff, acc2(i * 4).c_str(), acc2(i * 4 + 1).c_str());
@@ -380,6 +385,17 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
         o("add.u32 %s, %s, 1;", pi.c_str(), pi.c_str());
         o("setp.lt.u32 %s, %s, %s;", pk.c_str(), pi.c_str(), np.c_str());
         o("@%s bra %s;", pk.c_str(), l_peer.c_str());
+        o("bra %s;", ("$mm" + std::to_string(u) + "_sent").c_str());
+        o.label("$mm" + std::to_string(u) + "_mcast");
+        for (int i = 0; i < 4 * RG; i++) {
+            long long rowoff = ((i & 3) + (i >> 2) * SP) * ldd * 4;
+            for (int h = 0; h < 2; h++) {   // the accumulator pairs as four f32 lanes
+                o("mov.b64 {%s, %s}, %s;", fa(0).c_str(), fa(1).c_str(), acc2(i * 4 + 2 * h).c_str());
+                o("mov.b64 {%s, %s}, %s;", fa(2).c_str(), fa(3).c_str(), acc2(i * 4 + 2 * h + 1).c_str());
+                o("multimem.st.weak.global.v4.f32 [%s+%lld], {%s, %s, %s, %s};", pz.c_str(), rowoff + 256 * h, fa(0).c_str(), fa(1).c_str(), fa(2).c_str(), fa(3).c_str());
+            }
+        }
+        o.label("$mm" + std::to_string(u) + "_sent");
         o("fence.acq_rel.sys;");
         // a stream unit with slabs left goes on to its next segment, once no warp still reads this one's slabs
         o.label(l_next);
@@ -1072,7 +1088,7 @@ bool matmul_tcgen05_pair(const MmaSite& s, std::vector<std::string>* decls, std:
     decls->push_back(b64);
     decls->push_back("\t.reg .b16 " + P + "both;");
     std::string pr = "\t.reg .pred ";
-    for (const char* n : {"p", "q", "w0", "w1", "l0", "prod", "mma", "epi", "accp", "done", "all", "lead", "pk", "relay"}) pr += P + n + ", ";
+    for (const char* n : {"p", "q", "w0", "w1", "l0", "prod", "mma", "epi", "accp", "done", "all", "lead", "pk", "relay", "mc"}) pr += P + n + ", ";
     pr += P + "unused;";
     decls->push_back(pr);
     char d[256];
@@ -1229,6 +1245,10 @@ bool matmul_tcgen05_pair(const MmaSite& s, std::vector<std::string>* decls, std:
     o("setp.ge.u32 %s, %s, 2;", r("epi").c_str(), r("warp").c_str());
     o("setp.ge.u32 %s, %s, 6;", r("relay").c_str(), r("warp").c_str());
     o("setp.ne.u32 %s, %s, 0;", r("pk").c_str(), r("np").c_str());           // pk: this launch gathers
+    // bit 31 of the count: the first table entry is the result's address in an NVLink multicast mapping that covers every
+    // GPU of the group, and a tile leaves with one multimem.st per 16 bytes, which the switch replicates
+    o("setp.ge.u32 %s, %s, 0x80000000;", r("mc").c_str(), r("np").c_str());
+    o("and.b32 %s, %s, 0x7fffffff;", r("np").c_str(), r("np").c_str());
     o("@%s bra %sp_tile;", r("prod").c_str(), L.c_str());
     o("@%s bra %sm_tile;", r("mma").c_str(), L.c_str());
     o("@%s bra %sr_tile;", r("relay").c_str(), L.c_str());
@@ -1474,12 +1494,18 @@ bool matmul_tcgen05_pair(const MmaSite& s, std::vector<std::string>* decls, std:
     o.label(L + "r_peer");
     o("ld.param.u64 %s, [%s];", r("pz").c_str(), r("pb").c_str());
     o("add.u64 %s, %s, %s;", r("pz").c_str(), r("pz").c_str(), r("pq").c_str());
+    o("@%s bra %sr_mcast;", r("mc").c_str(), L.c_str());
     for (int i = 0; i < 4; i++)
         o("st.global.v4.b32 [%s+%lld], {%srb%d, %srb%d, %srb%d, %srb%d};", r("pz").c_str(), (long long)i * ldd * 2, P.c_str(), 4 * i, P.c_str(), 4 * i + 1, P.c_str(), 4 * i + 2, P.c_str(), 4 * i + 3);
     o("add.u64 %s, %s, 8;", r("pb").c_str(), r("pb").c_str());
     o("add.u32 %s, %s, 1;", r("pi").c_str(), r("pi").c_str());
     o("setp.lt.u32 %s, %s, %s;", r("q").c_str(), r("pi").c_str(), r("np").c_str());
     o("@%s bra %sr_peer;", r("q").c_str(), L.c_str());
+    o("bra %sr_sent;", L.c_str());
+    o.label(L + "r_mcast");
+    for (int i = 0; i < 4; i++)
+        o("multimem.st.weak.global.v4.f32 [%s+%lld], {%srb%d, %srb%d, %srb%d, %srb%d};", r("pz").c_str(), (long long)i * ldd * 2, P.c_str(), 4 * i, P.c_str(), 4 * i + 1, P.c_str(), 4 * i + 2, P.c_str(), 4 * i + 3);
+    o.label(L + "r_sent");
     o("add.u64 %s, %s, %lld;", r("z").c_str(), r("z").c_str(), 4ll * ldd * 2);
     o("add.u32 %s, %s, 4;", r("row").c_str(), r("row").c_str());
     o("setp.lt.u32 %s, %s, 64;", r("q").c_str(), r("row").c_str());

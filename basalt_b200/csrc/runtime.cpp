@@ -552,13 +552,28 @@ int basalt_rt_launch_gather(basalt_rt_function* fn, const uint32_t grid[3], cons
     return launch_impl(fn, grid, block, shared_mem_bytes, stream, params, peer_out, n_peers);
 }
 
+int basalt_rt_launch_gather_multicast(basalt_rt_function* fn, const uint32_t grid[3], const uint32_t block[3], uint32_t shared_mem_bytes, void* stream, void** params,
+                                      uint64_t multicast_out) {
+    if (!fn || !grid || !block) return set_err(4, 0, "basalt_rt_launch_gather_multicast", "null argument");
+    if (!fn->has_plan || fn->plan.gather < 0) return set_err(4, 0, "basalt_rt_launch_gather_multicast", "this kernel was not emitted with a gathering epilogue");
+    if (!multicast_out || (multicast_out & 15)) return set_err(4, 0, "basalt_rt_launch_gather_multicast", "the multicast address is null or not 16-byte aligned");
+    return launch_impl(fn, grid, block, shared_mem_bytes, stream, params, &multicast_out, -1);
+}
+
 namespace {
+// n_peers = -1: peer_out[0] is the output's address in a multicast mapping of the whole group (the kernels see a count
+// of one with bit 31 set).
 int launch_impl(basalt_rt_function* fn, const uint32_t grid[3], const uint32_t block[3], uint32_t shared_mem_bytes, void* stream, void** params,
                 const uint64_t* peer_out, int n_peers) {
     const Fns& f = fn->mod->ctx->drv->f;
     uint64_t peer_table[7] = {0, 0, 0, 0, 0, 0, 0};
     uint32_t peer_count = (uint32_t)n_peers;
-    for (int i = 0; i < n_peers; i++) peer_table[i] = peer_out[i];
+    if (n_peers < 0) {
+        peer_table[0] = peer_out[0];
+        peer_count = 0x80000001u;
+        n_peers = 1;
+    } else
+        for (int i = 0; i < n_peers; i++) peer_table[i] = peer_out[i];
     if (fn->coarse && params && grid[1] == 1 && grid[2] == 1 && block[1] == 1 && block[2] == 1 && block[0] >= 32) {
         // One-element-per-thread kernel: the caller's launch names the logical threads.  They are run by CTAs whose
         // threads each make one trip of the vectorised loop (several 16-byte accesses in flight): many short CTAs

@@ -314,6 +314,22 @@ class CudaFunction:
                 _check(1)
         return go
 
+    def bind_gather_multicast(self, grid, block, shared_mem_bytes: int, params: list, multicast_out: int, stream=None):
+        """`bind` for basalt_rt_launch_gather_multicast: every finished tile also leaves once, with multimem.st,
+        for `multicast_out` (the output parameter's value inside an NVLink multicast mapping of the same result
+        buffer on every rank), and the switch replicates it."""
+        vals = [C.c_uint64(p.device_ptr()) if isinstance(p, DeviceBuffer) else p for p in params]
+        arr = (C.c_void_p * max(len(vals), 1))(*[C.cast(C.pointer(v), C.c_void_p) for v in vals])
+        g = (C.c_uint32 * 3)(*_dim3(grid))
+        b = (C.c_uint32 * 3)(*_dim3(block))
+        s = C.c_void_p(stream)
+        h, fn, mc = self._h, lib.basalt_rt_launch_gather_multicast, C.c_uint64(int(multicast_out))
+
+        def go(stream=None, _keep=(vals, arr, g, b)):
+            if fn(h, g, b, shared_mem_bytes, s if stream is None else C.c_void_p(stream), arr, mc):
+                _check(1)
+        return go
+
     def status(self) -> int:
         """The kernel's device status word (synchronous read): non-zero when a bounded wait inside
         the kernel gave up and the last output is not valid. Always 0 for kernels without waits."""

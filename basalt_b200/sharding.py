@@ -143,6 +143,54 @@ def reduce_max_sharded(group: RankGroup, local_slice: np.ndarray, reduce_local) 
     return group.max_i32_host(partial)
 
 
+class MulticastResult:
+    """One result buffer of `nbytes` per rank behind an NVLink multicast mapping (NVLS), for
+    basalt_rt_launch_gather_multicast: `local_ptr` is this rank's buffer, `multicast_ptr` the address through which
+    one multimem.st lands at the same offset in every rank's buffer, `peer_ptrs[r]` rank r's buffer mapped here.
+    The allocation, the handle exchange between the processes and the multicast object are
+    torch.distributed._symmetric_memory's (cuMemCreate / cuMulticastCreate / cuMulticastBindMem): plumbing.
+
+    `open` returns None with the reason in `MulticastResult.why_not` when the box or this torch build has no
+    multicast support.  Every rank must call `close` (collectively) before it exits: a rank that leaves while its
+    memory is bound to a multicast object other ranks still use faults their NVLink."""
+    why_not = ""
+
+    def __init__(self, tensor, handle, group: "RankGroup"):
+        self.tensor, self._handle, self._group = tensor, handle, group
+        off = int(getattr(handle, "offset", 0) or 0)
+        self.local_ptr = int(tensor.data_ptr())
+        self.multicast_ptr = int(handle.multicast_ptr) + off
+        self.peer_ptrs = [int(p) + off for p in handle.buffer_ptrs]
+
+    @staticmethod
+    def open(group: "RankGroup", nbytes: int, device_index: int) -> "MulticastResult | None":
+        import torch
+        import torch.distributed as dist
+        try:
+            import torch.distributed._symmetric_memory as symm
+            t = symm.empty(nbytes, dtype=torch.uint8, device=torch.device("cuda", device_index))
+            h = symm.rendezvous(t, dist.group.WORLD)
+            ok = int(h.multicast_ptr) != 0
+            reason = "" if ok else "the symmetric-memory handle carries no multicast address"
+        except Exception as e:   # no multicast support, or a torch build without symmetric memory
+            t = h = None
+            ok, reason = False, f"{type(e).__name__}: {e}"[:200]
+        # every rank takes the same branch: one that failed alone must not leave the others bound
+        if group.max_i32_host(0 if ok else 1) != 0:
+            MulticastResult.why_not = reason or "another rank has no multicast support"
+            del h, t
+            return None
+        return MulticastResult(t, h, group)
+
+    def close(self):
+        import torch
+        torch.cuda.synchronize()
+        self._group.barrier()
+        self._handle = None
+        self.tensor = None
+        self._group.barrier()
+
+
 class PushGather:
     """The gather of a row-sharded result, overlapped with the compute that produces it.
 

@@ -659,16 +659,16 @@ def sharded_gather_variants(env: Env, kind: str, M: int, N: int, K: int, A_full,
     def barrier_kernel():
         bg.allreduce_max_i32(flag.data_ptr(), flag.data_ptr() + 4, env.stream)
 
-    def snapshot():
+    def snapshot(ptr=None):
         torch.cuda.synchronize(); group.barrier()
-        ctx.copy_device_async(Cfull.data_ptr(), Cbuf.device_ptr(), M * N * esz, env.stream)
+        ctx.copy_device_async(Cfull.data_ptr(), ptr or Cbuf.device_ptr(), M * N * esz, env.stream)
         torch.cuda.synchronize()
         return Cfull
 
-    def clear():
+    def clear(ptr=None):
         torch.cuda.synchronize(); group.barrier()
         Cfull.fill_(float("nan"))
-        ctx.copy_device_async(Cbuf.device_ptr(), Cfull.data_ptr(), M * N * esz, env.stream)
+        ctx.copy_device_async(ptr or Cbuf.device_ptr(), Cfull.data_ptr(), M * N * esz, env.stream)
         torch.cuda.synchronize(); group.barrier()
 
     mine = Cbuf.device_ptr() + r0 * N * esz
@@ -683,11 +683,11 @@ def sharded_gather_variants(env: Env, kind: str, M: int, N: int, K: int, A_full,
     go_gather = fn.bind_gather(grid, block, 0, prm, others, stream=env.stream)
     variants = {}
 
-    def run_variant(name, step, reps=10):
-        clear()
+    def run_variant(name, step, reps=10, ptr=None):
+        clear(ptr)
         ms = env.timed(step, reps)
         res = {"ms": ms, "tflops_total": fl / ms / 1e9}
-        res.update(check(snapshot()))
+        res.update(check(snapshot(ptr)))
         if compute_1gpu_ms:
             res["fraction_of_linear"] = compute_1gpu_ms / world / ms
         variants[name] = res
@@ -727,6 +727,25 @@ def sharded_gather_variants(env: Env, kind: str, M: int, N: int, K: int, A_full,
         barrier_kernel()
     run_variant("emitted_fused_gather", fused_emitted)
     out["emitted_fused_gather_nvlink_GBs_out_per_gpu"] = (world - 1) * Ml * N * esz / variants["emitted_fused_gather"]["ms"] / 1e6
+
+    # the same kernel sending every tile once through an NVLink multicast mapping of the result (NVLS): the switch
+    # replicates it, so Ml * N * esz bytes leave each GPU instead of (world - 1) times that
+    from basalt_b200 import sharding as _sh
+    mcr = _sh.MulticastResult.open(group, M * N * esz, torch.cuda.current_device())
+    if mcr is None:
+        out["emitted_fused_gather_multimem"] = {"unavailable": _sh.MulticastResult.why_not}
+    else:
+        try:
+            mine_mc = mcr.local_ptr + r0 * N * esz
+            go_mc = fn.bind_gather_multicast(grid, block, 0, [env.dp(Al), env.dp(B_), b.ptr(mine_mc)], mcr.multicast_ptr + r0 * N * esz, stream=env.stream)
+
+            def fused_multimem():
+                go_mc()
+                barrier_kernel()
+            run_variant("emitted_fused_gather_multimem", fused_multimem, ptr=mcr.local_ptr)
+            variants["emitted_fused_gather_multimem"]["nvlink_GBs_in_per_gpu"] = (world - 1) * Ml * N * esz / variants["emitted_fused_gather_multimem"]["ms"] / 1e6
+        finally:
+            mcr.close()          # collectively, whatever happened: no rank leaves while its memory is bound
 
     if kind == "matmul":
         st2 = torch.zeros(1, dtype=torch.int32, device="cuda")

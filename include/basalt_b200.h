@@ -177,6 +177,16 @@ int basalt_rt_launch(basalt_rt_function *fn, const uint32_t grid[3], const uint3
 int basalt_rt_launch_gather(basalt_rt_function *fn, const uint32_t grid[3], const uint32_t block[3],
                             uint32_t shared_mem_bytes, void *stream, void **params, const uint64_t *peer_out,
                             int n_peers);
+/* basalt_rt_launch_gather through an NVLink multicast mapping (NVLS): multicast_out is the value the kernel's output
+ * pointer parameter would have inside a multicast mapping that covers the same result buffer on every GPU of the group,
+ * this one included (cuMulticastCreate / cuMulticastBindMem over buffers of one size; 16-byte aligned; the caller
+ * builds the mapping, e.g. torch.distributed._symmetric_memory's multicast_ptr).  The kernel still writes this GPU's
+ * result with plain stores and sends each finished tile once, with multimem.st, to be replicated by the switch: one
+ * copy leaves the GPU instead of one per peer.  Completion is the caller's barrier, as for basalt_rt_launch_gather.
+ * A rank must not exit while its memory is bound to a multicast object that other ranks still use.  No counterpart
+ * in the reference. */
+int basalt_rt_launch_gather_multicast(basalt_rt_function *fn, const uint32_t grid[3], const uint32_t block[3],
+                                      uint32_t shared_mem_bytes, void *stream, void **params, uint64_t multicast_out);
 /* Grid and block the emitter planned for this kernel (0 when the kernel has no plan and the
  * caller chooses, as with the reference). */
 int basalt_rt_planned_geometry(basalt_rt_function *fn, void **params, uint32_t grid[3], uint32_t block[3],

@@ -190,6 +190,53 @@ def main():
             if r != group.rank:
                 ctx.ipc_close(p)
 
+    # ---- the same epilogues through an NVLink multicast mapping (basalt_rt_launch_gather_multicast): one multimem.st
+    # per 16 bytes, replicated by the switch.  Nothing is asserted while the result is bound to the multicast object:
+    # verdicts are collected, the mapping is closed by all ranks together, then checked. ----
+    import torch
+    verdicts = []
+    for what in ("f16", "f32"):
+        if what == "f16":
+            M, N, K, esz = 512 * group.world, 512, 192, 2
+            A = w.f16_normal01(w.SEEDS["matmul_f16"] + 41, M * K).reshape(M, K); B = w.f16_normal01(w.SEEDS["matmul_f16"] + 42, K * N).reshape(K, N)
+            want, tol, dt = orc_matmul_f16_rows(orc, A, B, N, False, 0, M), 2e-3, np.float16
+        else:
+            M, N, K, esz = 256 * group.world, 384, 96, 4
+            A = w.f32_pm1(w.SEEDS["sgemm_f32"] + 41, M * K).reshape(M, K); B = w.f32_pm1(w.SEEDS["sgemm_f32"] + 42, K * N).reshape(K, N)
+            want, tol, dt = orc_sgemm_rows(orc, A, B, 0, M), 1e-4, np.float32
+        r0, r1 = group.shard(M, 256)
+        Ml = r1 - r0
+        mcr = sharding.MulticastResult.open(group, M * N * esz, torch.cuda.current_device())
+        if mcr is None:
+            print(f"rank {group.rank}: no multicast mapping ({sharding.MulticastResult.why_not}); multimem gather not run", flush=True)
+            break
+        try:
+            mcr.tensor.view(torch.float16 if what == "f16" else torch.float32).fill_(float("nan"))
+            torch.cuda.synchronize()
+            group.barrier()
+            dA, dB = ctx.upload(A[r0:r1]), ctx.upload(B)
+            flag = ctx.upload(np.zeros(2, np.int32))
+            if what == "f16":
+                fn = ctx.load_module(ptx.emit(kb.matmul_f16(Ml, N, K)).text).get_function("matmul_kernel"); block = 128
+            else:
+                fn = ctx.load_module(ptx.emit(kb.sgemm_cta128(Ml, N, K)).text).get_function("sgemm_f32"); block = 256
+            go = fn.bind_gather_multicast((N // 128, Ml // 128), block, 0, [dA, dB, b.ptr(mcr.local_ptr + r0 * N * esz)], mcr.multicast_ptr + r0 * N * esz)
+            for _ in range(2):
+                go()
+                peers.allreduce_max_i32(flag.device_ptr(), flag.device_ptr() + 4, None)      # the barrier: all ranks' tiles have landed
+                ctx.synchronize()
+                got = mcr.tensor.view(torch.float16 if what == "f16" else torch.float32).reshape(M, N).cpu().numpy()
+                verdicts.append((what, fn.status() == 0 and peers.status() == 0, bool(np.isfinite(got).all()), float(rel_fro(got, want)) if np.isfinite(got).all() else float("inf"), tol))
+                group.barrier()
+        except Exception as e:      # reported after the mapping is closed
+            verdicts.append((what, False, False, float("inf"), repr(e)))
+        finally:
+            mcr.close()
+    for what, status_ok, finite, err, tol in verdicts:
+        assert status_ok and finite and err <= tol, ("multimem gather", what, status_ok, finite, err, tol)
+    if verdicts:
+        print(f"rank {group.rank}: multimem gather checked {len(verdicts)} times", flush=True)
+
     group.barrier()
     peers.destroy()
     comm.destroy()

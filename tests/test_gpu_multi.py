@@ -20,3 +20,4 @@ def test_sharded_workloads_on_all_gpus(gpu):
                         "--master-port", "29731", os.path.join(HERE, "multi_rank_worker.py")], capture_output=True, text=True, env=env, timeout=900)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-4000:]
     assert r.stdout.count(" ok") == world
+    print("\n".join(l for l in r.stdout.splitlines() if "multi" in l))      # whether the box had an NVLink multicast mapping to offer
