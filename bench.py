@@ -728,6 +728,14 @@ def sharded_gather_variants(env: Env, kind: str, M: int, N: int, K: int, A_full,
     run_variant("emitted_fused_gather", fused_emitted)
     out["emitted_fused_gather_nvlink_GBs_out_per_gpu"] = (world - 1) * Ml * N * esz / variants["emitted_fused_gather"]["ms"] / 1e6
 
+    if kind == "sgemm":
+        # rounds of stream units under the gathering launch (two by default): more rounds hide more of the gather
+        # behind compute and cost more partial sums
+        for rounds in (1, 3):
+            fn.tune("tail_rounds", rounds)
+            run_variant(f"emitted_fused_gather_rounds{rounds}", fused_emitted, reps=5)
+        fn.tune("tail_rounds", 0)
+
     # the same kernel sending every tile once through an NVLink multicast mapping of the result (NVLS): the switch
     # replicates it, so Ml * N * esz bytes leave each GPU instead of (world - 1) times that
     from basalt_b200 import sharding as _sh
