@@ -97,6 +97,9 @@ struct basalt_rt_ctx {
     // Workspace of kernels whose plan says `tail=`: two 128x128 f32 partial tiles per resident CTA (a stream
     // unit) and one ticket word per tile of a tail wave.  The kernels leave every ticket at zero.
     CUdeviceptr tail_partials = 0, tail_tickets = 0;
+    // A launch that needs a larger workspace allocates a new one; the old one is kept until the context goes, because
+    // launches already issued -- or captured in a CUDA graph -- still name it.
+    std::vector<CUdeviceptr> tail_retired;
     unsigned tail_slots = 0;
     // Every launch of the context with stream units shares that workspace, so such launches are ordered one after
     // another: each records `tail_done` on its stream, and the next one on another stream first waits for it.
@@ -360,6 +363,7 @@ void basalt_rt_ctx_destroy(basalt_rt_ctx* ctx) {
     if (!ctx) return;
     for (auto& kv : ctx->staging) ctx->drv->f.cuMemFree(kv.second);
     if (ctx->tail_partials) ctx->drv->f.cuMemFree(ctx->tail_partials);
+    for (CUdeviceptr old : ctx->tail_retired) ctx->drv->f.cuMemFree(old);
     if (ctx->tail_tickets) ctx->drv->f.cuMemFree(ctx->tail_tickets);
     if (ctx->tail_done) ctx->drv->f.cuEventDestroy(ctx->tail_done);
     ctx->drv->f.cuDevicePrimaryCtxRelease(ctx->dev);
@@ -624,7 +628,12 @@ int launch_impl(basalt_rt_function* fn, const uint32_t grid[3], const uint32_t b
         if (units && ctx->tail_slots < need) {
             int rc = make_current(ctx);
             if (rc) return rc;
-            if (ctx->tail_partials) { f.cuMemFree(ctx->tail_partials); f.cuMemFree(ctx->tail_tickets); ctx->tail_partials = ctx->tail_tickets = 0; ctx->tail_slots = 0; }
+            if (ctx->tail_partials) {
+                ctx->tail_retired.push_back(ctx->tail_partials);
+                ctx->tail_retired.push_back(ctx->tail_tickets);
+                ctx->tail_partials = ctx->tail_tickets = 0;
+                ctx->tail_slots = 0;
+            }
             rc = check(f, "cuMemAlloc", f.cuMemAlloc(&ctx->tail_partials, (size_t)need * 65536));
             if (rc) return rc;
             rc = check(f, "cuMemAlloc", f.cuMemAlloc(&ctx->tail_tickets, (size_t)need * 4));

@@ -156,7 +156,9 @@ void basalt_rt_host_free(basalt_rt_ctx *ctx, void *p);
  * For a kernel with a launch plan, the tensor-map parameters are built from the pointer and size
  * parameters and appended here; the caller still passes only the BIR parameters.
  * Launches of the FFMA matmul that work a sparse last wave off with stream units (partial sums
- * along K) share one workspace per context; the runtime orders them itself (each such launch waits, on its own stream, for the
+ * along K) share one workspace per context (two 64 KB tiles per unit; a launch that needs more than
+ * an earlier one did gets a new allocation, and the outgrown one lives until the context is destroyed,
+ * so that earlier launches and captured graphs stay valid); the runtime orders them itself (each such launch waits, on its own stream, for the
  * previous one wherever that ran), so callers may issue them from any streams and host threads. */
 int basalt_rt_launch(basalt_rt_function *fn, const uint32_t grid[3], const uint32_t block[3],
                      uint32_t shared_mem_bytes, void *stream, void **params);
