@@ -739,8 +739,10 @@ def sharded_gather_variants(env: Env, kind: str, M: int, N: int, K: int, A_full,
     # the same kernel sending every tile once through an NVLink multicast mapping of the result (NVLS): the switch
     # replicates it, so Ml * N * esz bytes leave each GPU instead of (world - 1) times that
     from basalt_b200 import sharding as _sh
-    mcr = _sh.MulticastResult.open(group, M * N * esz, torch.cuda.current_device())
-    if mcr is None:
+    mcr = None if env.args.no_multimem else _sh.MulticastResult.open(group, M * N * esz, torch.cuda.current_device())
+    if env.args.no_multimem:
+        out["emitted_fused_gather_multimem"] = {"unavailable": "switched off (--no-multimem)"}
+    elif mcr is None:
         out["emitted_fused_gather_multimem"] = {"unavailable": _sh.MulticastResult.why_not}
     else:
         try:
@@ -1028,6 +1030,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="basalt_b200", choices=["basalt_b200", "reference"])
     ap.add_argument("--no-others", action="store_true", help="headline only: skip the `configs` sections of the other four configurations")
+    ap.add_argument("--no-multimem", action="store_true", help="skip the gather variant that goes through an NVLink multicast mapping (torch symmetric memory)")
     ap.add_argument("--only", default=None, help="comma-separated subset of vadd_i32,helper_chain,sgemm_f32,matmul_f16 for the `configs` sections")
     ap.add_argument("--elements", type=int, default=N_MAX, help="int32 elements per GPU (profiling runs use a smaller case)")
     ap.add_argument("--nccl-exchange", action="store_true", help="at N > 1 use ncclAllReduce for the 4-byte exchange instead of the peer-memory kernel")
