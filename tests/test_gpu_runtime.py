@@ -30,6 +30,26 @@ def test_copies_are_bounds_checked(gpu):
     assert e.value.kind == 4
 
 
+@pytest.mark.parametrize("nbytes", [8 << 20, (37 << 20) + 12345, (64 << 20) + 4])
+def test_large_pageable_buffers_take_the_staged_copy_path(gpu, nbytes):
+    # Pageable host memory of 8 MiB or more is moved in 4 MiB chunks by several host threads through pinned buffers
+    # (chunk counts that are and are not multiples of the lane count, a ragged last chunk); the bytes must survive
+    # both directions, through the buffer API and through the CPU launch ABI.
+    rng = np.random.default_rng(nbytes)
+    x = rng.integers(0, 256, nbytes, dtype=np.uint8)
+    buf = gpu.alloc(nbytes)
+    buf.copy_from_host(x)
+    back = np.zeros(nbytes, np.uint8)
+    buf.copy_to_host(back)
+    assert np.array_equal(back, x)
+    n = nbytes // 4
+    a = x[:4 * n].view(np.int32) >> 2
+    bb = np.roll(a, 7)
+    c = np.full(n, -1, np.int32)
+    gpu.cpu_launch(gpu.load_module(b.Ptx().emit(kb.load("vadd_i32")).text).get_function("vadd_i32"), [a, bb, c, b.i32(n)], n)
+    assert np.array_equal(c, a + bb)
+
+
 def test_jit_failure_is_reported_not_fatal(gpu):
     with pytest.raises(b.CudaError) as e:
         gpu.load_module(".version 8.7\n.target sm_100a\n.address_size 64\n.visible .entry broken() { this is not ptx; }\n")
