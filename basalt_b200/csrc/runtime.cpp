@@ -493,7 +493,7 @@ uint64_t basalt_rt_buffer_ptr(const basalt_rt_buffer* buf) { return buf ? (uint6
 size_t basalt_rt_buffer_size(const basalt_rt_buffer* buf) { return buf ? buf->bytes : 0; }
 
 namespace {
-constexpr size_t kStageMin = 8u << 20;     // smaller host buffers go through the driver's own pageable path
+constexpr size_t kStageMin = 2u << 20;     // smaller host buffers go through the driver's own pageable path
 bool host_is_pinned(const Fns& f, const void* p);
 int staged_copy(basalt_rt_ctx* ctx, CUdeviceptr dev, void* host, size_t bytes, bool to_device);
 // A synchronous copy of a large pageable buffer: ordered after the work already in the NULL stream, like the
@@ -877,14 +877,15 @@ int staged_copy(basalt_rt_ctx* ctx, CUdeviceptr dev, void* host, size_t bytes, b
         }
         ctx->lanes = std::move(lanes);
     }
-    const size_t nchunks = (bytes + kStageChunk - 1) / kStageChunk;
-    const int nlanes = (int)ctx->lanes.size();
+    const size_t chunk = bytes >= (32u << 20) ? kStageChunk : (1u << 20);   // small buffers in 1 MiB pieces, so that several threads share them
+    const size_t nchunks = (bytes + chunk - 1) / chunk;
+    const int nlanes = (int)std::min<size_t>(ctx->lanes.size(), nchunks);
     std::atomic<int> failed{0};
     auto lane_work = [&](int li) {
         if (f.cuCtxSetCurrent(ctx->ctx) != CUDA_SUCCESS) { failed = 1; return; }
         auto& l = ctx->lanes[li];
         char* h = static_cast<char*>(host);
-        auto span = [&](size_t c, size_t* off, size_t* len) { *off = c * kStageChunk; *len = std::min(kStageChunk, bytes - *off); };
+        auto span = [&](size_t c, size_t* off, size_t* len) { *off = c * chunk; *len = std::min(chunk, bytes - *off); };
         size_t off, len;
         if (to_device) {
             int k = 0;

@@ -236,8 +236,8 @@ int basalt_rt_event_elapsed_ms(basalt_rt_ctx *ctx, void *start, void *end, float
  * kernel, 5 = pointer written, 6 = both (host address in `host`, extent in `bytes`). The call
  * takes device buffers (kept with the context between calls and reused by size), copies inputs,
  * launches ceil(nthreads/block) blocks of `block` threads (the reference's grid for a flat launch)
- * and copies outputs back.  Host buffers of 8 MiB or more that are not page-locked -- what a caller
- * of the reference's ABI passes -- are moved in 4 MiB chunks by up to eight host threads through pinned
+ * and copies outputs back.  Host buffers of 2 MiB or more that are not page-locked -- what a caller
+ * of the reference's ABI passes -- are moved in chunks (4 MiB; 1 MiB below 32 MiB) by up to eight host threads through pinned
  * staging buffers, each thread feeding the copy engine on its own stream, instead of through the
  * driver's own pageable path; page-locked buffers (basalt_rt_host_alloc) are copied directly.  The
  * synchronous forms of basalt_rt_copy_from_host / basalt_rt_copy_to_host (stream NULL) do the same. */

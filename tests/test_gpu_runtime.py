@@ -30,9 +30,9 @@ def test_copies_are_bounds_checked(gpu):
     assert e.value.kind == 4
 
 
-@pytest.mark.parametrize("nbytes", [8 << 20, (37 << 20) + 12345, (64 << 20) + 4])
+@pytest.mark.parametrize("nbytes", [(3 << 20) + 76, 8 << 20, (37 << 20) + 12344, (64 << 20) + 4])
 def test_large_pageable_buffers_take_the_staged_copy_path(gpu, nbytes):
-    # Pageable host memory of 8 MiB or more is moved in 4 MiB chunks by several host threads through pinned buffers
+    # Pageable host memory of 2 MiB or more is moved in 1 or 4 MiB chunks by several host threads through pinned buffers
     # (chunk counts that are and are not multiples of the lane count, a ragged last chunk); the bytes must survive
     # both directions, through the buffer API and through the CPU launch ABI.
     rng = np.random.default_rng(nbytes)
