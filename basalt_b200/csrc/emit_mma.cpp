@@ -396,7 +396,11 @@ bool sgemm_ffma(const MmaSite& s, std::vector<std::string>* decls, std::vector<s
             }
         }
         o.label("$mm" + std::to_string(u) + "_sent");
-        o("fence.acq_rel.sys;");
+        // One thread fences for the CTA: the barrier orders every thread's peer stores before it, and the fence is
+        // cumulative.  A system-scope fence in each of the 256 threads measured 1 % slower at four GPUs.
+        o("setp.eq.u32 %s, %s, 0;", pk.c_str(), tid.c_str());
+        o("bar.sync 0;");
+        o("@%s fence.acq_rel.sys;", pk.c_str());
         // a stream unit with slabs left goes on to its next segment, once no warp still reads this one's slabs
         o.label(l_next);
         o("setp.ge.u32 %s, %s, %s;", pk.c_str(), R("it0").c_str(), R("it1").c_str());
@@ -1520,8 +1524,11 @@ bool matmul_tcgen05_pair(const MmaSite& s, std::vector<std::string>* decls, std:
     o("mov.u32 %s, 1;", r("t").c_str());
     o("atom.global.exch.b32 %s, [%s], %s;", r("g").c_str(), r("status").c_str(), r("t").c_str());
     o.label(L + "status_done");
+    // The relay warps' stores into peer memory are performed before the kernel can end.  Only they stored there: the
+    // same fence in every thread of the CTA cost 8 % of a gathering launch at four GPUs (0.284 against 0.263 ms).
     o("setp.ne.u32 %s, %s, 0;", r("pk").c_str(), r("np").c_str());
-    o("@%s fence.acq_rel.sys;", r("pk").c_str());   // this thread's stores into peer memory are performed before the kernel can end
+    o("and.pred %s, %s, %s;", r("q").c_str(), r("pk").c_str(), r("relay").c_str());
+    o("@%s fence.acq_rel.sys;", r("q").c_str());
     o("bar.warp.sync 0xffffffff;");
     o("tcgen05.fence::before_thread_sync;");
     o("bar.sync 0;");
