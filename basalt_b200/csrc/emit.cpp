@@ -928,6 +928,11 @@ struct FnEmitter {
             if (b.term.has_val && !b.term.val.param) uses[b.term.val.idx]++;
         }
         emit_param_loads();
+        // Programmatic dependent launch: the next kernel on the stream may be set up while this grid runs, and this grid --
+        // when it is itself launched that way -- touches memory only once the grids before it have completed and their
+        // writes are visible.  Both are no-ops under an ordinary launch.
+        line("griddepcontrol.launch_dependents;");
+        line("griddepcontrol.wait;");
         for (uint32_t b = 0; b < f.blocks.size(); b++) {
             label(blk(b));
             for (uint32_t id : f.blocks[b].insts) { lower_inst(id); if (failed) return false; }
@@ -1026,7 +1031,7 @@ bool emit_ptx(const Module& in, const EmitOptions& opts, EmitResult* out, Diag* 
             for (auto& in : f.insts) arithmetic += in.op == Opc::Bin;
             const int trips = arithmetic > 256 ? 4 : 1;
             text += "//!basalt.plan " + r.coarse_of + " coarse=" + f.name + " params=" + std::to_string(f.params.size() - 1) + " per_thread=" +
-                    std::to_string(std::max(1, r.vec_lanes) * std::max(1, r.unroll) * trips) + "\n";
+                    std::to_string(std::max(1, r.vec_lanes) * std::max(1, r.unroll) * trips) + " pdl=1\n";
         }
         for (auto& p : fe.plan) text += p + "\n";
         for (auto& md : fe.module_decls)

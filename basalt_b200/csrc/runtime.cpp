@@ -62,6 +62,7 @@ struct Fns {
     CUresult (*cuMemcpyHtoDAsync)(CUdeviceptr, const void*, size_t, CUstream);
     CUresult (*cuMemcpyDtoHAsync)(void*, CUdeviceptr, size_t, CUstream);
     CUresult (*cuPointerGetAttribute)(void*, CUpointer_attribute, CUdeviceptr);   // optional
+    CUresult (*cuLaunchKernelEx)(const CUlaunchConfig*, CUfunction, void**, void**);   // optional
     CUresult (*cuMemAllocHost)(void**, size_t);
     CUresult (*cuMemFreeHost)(void*);
     CUresult (*cuStreamCreate)(CUstream*, unsigned);
@@ -140,6 +141,7 @@ struct Plan {
     std::vector<TmapSpec> tmaps;
     std::string coarse;     // entry taking one more u64 parameter: the thread count the caller asked for
     unsigned per_thread = 0; // coarse entry: elements a thread handles in one trip of its loop (vector lanes x unroll)
+    bool pdl = false;        // coarse entry: starts with griddepcontrol.wait, so it may be launched with programmatic stream serialisation
     bool status = false;    // the entry takes a u64 parameter: a device int32 set when a bounded wait gave up
     unsigned logical_block[3] = {0, 0, 0};   // block the caller must ask for when it differs from the block launched
     unsigned tail_k = 0;    // FFMA matmul with a streamed tail wave (K extent): the caller's 2-D grid is re-issued as a 1-D grid of
@@ -168,6 +170,7 @@ struct basalt_rt_function {
     bool tail_split = true;        //   work a sparse last wave off with stream units
     unsigned tail_rounds = 0;      //   rounds of stream units (0 = one, two with a gathering epilogue)
     unsigned coarse_waves = 0;     //   coarse entries: exactly this many resident waves (0 = one loop trip per thread)
+    bool pdl = true;               //   coarse entries: launch with programmatic stream serialisation when the plan allows it
     bool has_plan = false;
     Plan plan;
 };
@@ -265,6 +268,7 @@ void parse_plans(const char* ptx, std::map<std::string, Plan>* out) {
             else if (k == "params") p.nparams = (unsigned)strtoul(v.c_str(), nullptr, 10);
             else if (k == "coarse") p.coarse = v;
             else if (k == "per_thread") p.per_thread = (unsigned)strtoul(v.c_str(), nullptr, 10);
+            else if (k == "pdl") p.pdl = v == "1";
             else if (k == "pair") p.pair = v;
             else if (k == "status") p.status = v != "0";
             else if (k == "logical_block") sscanf(v.c_str(), "%u,%u,%u", &p.logical_block[0], &p.logical_block[1], &p.logical_block[2]);
@@ -336,6 +340,7 @@ int basalt_rt_driver_load(basalt_rt_driver** out) {
               resolve(lib, &f.cuOccupancyMaxActiveBlocksPerMultiprocessor, {"cuOccupancyMaxActiveBlocksPerMultiprocessor"});
     if (!ok) { dlclose(lib); delete d; return 2; }
     f.cuPointerGetAttribute = reinterpret_cast<decltype(f.cuPointerGetAttribute)>(dlsym(lib, "cuPointerGetAttribute"));   // optional
+    f.cuLaunchKernelEx = reinterpret_cast<decltype(f.cuLaunchKernelEx)>(dlsym(lib, "cuLaunchKernelEx"));                  // optional
     int rc = check(f, "cuInit", f.cuInit(0));
     if (rc) { dlclose(lib); delete d; return rc; }
     *out = d;
@@ -630,6 +635,21 @@ int launch_impl(basalt_rt_function* fn, const uint32_t grid[3], const uint32_t b
         uint32_t phys = grid[0] < want ? grid[0] : (uint32_t)want;
         std::vector<void*> all(params, params + fn->plan.nparams);
         all.push_back(&logical);
+        if (fn->pdl && fn->plan.pdl && f.cuLaunchKernelEx) {
+            // The kernel's first instruction after its parameter loads is griddepcontrol.wait: its CTAs may be set up while
+            // the kernel before it on the stream drains, which hides the launch latency of back-to-back small launches.
+            CUlaunchConfig cfg = {};
+            cfg.gridDimX = phys; cfg.gridDimY = 1; cfg.gridDimZ = 1;
+            cfg.blockDimX = block[0]; cfg.blockDimY = 1; cfg.blockDimZ = 1;
+            cfg.sharedMemBytes = shared_mem_bytes;
+            cfg.hStream = (CUstream)stream;
+            CUlaunchAttribute attr = {};
+            attr.id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
+            attr.value.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = &attr;
+            cfg.numAttrs = 1;
+            return check(f, "cuLaunchKernelEx", f.cuLaunchKernelEx(&cfg, fn->coarse, all.data(), nullptr));
+        }
         return check(f, "cuLaunchKernel", f.cuLaunchKernel(fn->coarse, phys, 1, 1, block[0], 1, 1, shared_mem_bytes, (CUstream)stream, all.data(), nullptr));
     }
     if (fn->has_plan && fn->plan.tail_k) {
@@ -787,6 +807,7 @@ int basalt_rt_function_tune(basalt_rt_function* fn, const char* key, int value) 
     else if (k == "tail_split") fn->tail_split = value != 0;
     else if (k == "tail_rounds") fn->tail_rounds = value < 0 ? 0u : value > 8 ? 8u : (unsigned)value;
     else if (k == "coarse_waves") fn->coarse_waves = value > 0 ? (unsigned)value : 0;
+    else if (k == "pdl") fn->pdl = value != 0;
     else return set_err(4, 0, "basalt_rt_function_tune", "unknown key: " + k);
     return 0;
 }

@@ -208,6 +208,8 @@ void basalt_rt_tail_plan(uint32_t tiles, uint32_t slots, uint32_t k_extent, uint
 /* Switches one of the runtime's launch policies for this function handle, for A/B timing and tests; a
  * handle starts with every policy on.  "pair" = 0: keep the one-SM entry of the tcgen05 matmul on
  * grids that are even in x and y.  "tail_split" = 0: run every tile of the FFMA matmul whole.
+ * "pdl" = 0: launch a coarsened kernel with an ordinary launch instead of programmatic stream serialisation
+ * (the emitted kernels begin with griddepcontrol.wait, so the serialised form keeps stream order).
  * "tail_rounds" = r (1 to 8; 0 = the default: one, or two under basalt_rt_launch_gather): the stream units
  * that work the FFMA matmul's tail wave off come in r rounds of one unit per CTA slot.
  * "coarse_waves" = w > 0: launch a coarsened one-element-per-thread kernel on exactly w resident

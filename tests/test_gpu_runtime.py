@@ -123,3 +123,22 @@ def test_launch_policies_are_switched_per_handle_not_by_environment(gpu, monkeyp
     with pytest.raises(b.CudaError) as e:
         fn.tune("no_such_policy", 1)
     assert e.value.kind == 4
+
+
+@pytest.mark.parametrize("pdl", [1, 0])
+def test_dependent_coarse_launches_keep_stream_order(gpu, pdl):
+    # Coarse launches go out with programmatic stream serialisation: the next launch's CTAs are set up while the one
+    # before drains, and griddepcontrol.wait holds them off memory until it has completed.  Twenty launches that each
+    # read what the one before wrote (x + x -> y, y + y -> x, ...), issued back to back on one stream: 2^20 everywhere.
+    fn = gpu.load_module(b.Ptx().emit(kb.load("vadd_i32")).text).get_function("vadd_i32")
+    fn.tune("pdl", pdl)
+    n = (1 << 20) + 13
+    x, y = gpu.upload(np.ones(n, np.int32)), gpu.upload(np.zeros(n, np.int32))
+    s = gpu.create_stream()
+    for i in range(20):
+        src, dst = (x, y) if i % 2 == 0 else (y, x)
+        fn.launch((n + 255) // 256, 256, 0, [src, src, dst, b.i32(n)], stream=s)
+    gpu.stream_sync(s)
+    gpu.destroy_stream(s)
+    assert np.array_equal(x.to_numpy(np.int32), np.full(n, 1 << 20, np.int32))
+    assert np.array_equal(y.to_numpy(np.int32), np.full(n, 1 << 19, np.int32))
