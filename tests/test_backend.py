@@ -131,6 +131,24 @@ def test_optimised_lowering_uses_the_blackwell_forms(ptx):
     assert h0.count("mul.lo.s32") == 33 and "v4" not in h0   # 32 squarings plus the index product
 
 
+def test_power_of_two_products_are_shifts_and_entries_admit_dependent_launch(ptx):
+    # a multiply by a constant power of two is a shift (ptxas would keep mul.lo on the multiply-add pipe); any other
+    # constant, and a product of two values, stay multiplies
+    body = ("    %c16 = const.i i64 16\n    %c12 = const.i i64 12\n    %w = sext i64 i32 %arg1\n    %a = mul i64 %w, %c16\n    %b = mul i64 %c16, %w\n"
+            "    %c = mul i64 %w, %c12\n    %c8 = const.i i32 8\n    %d = mul i32 %arg1, %c8\n    %e = mul i32 %arg1, %arg2\n"
+            "    %s = add i64 %a, %b\n    %t = add i64 %s, %c\n    %p = add ptr.global %arg0, %t\n    %de = add i32 %d, %e\n    store i32 ptr.global %p, %de, align 4")
+    text = emit0(ptx, kernel(body))
+    assert text.count("shl.b64") == 2 and text.count("shl.b32") == 1 and text.count("mul.lo.s64") == 1 and text.count("mul.lo.s32") == 1
+    # every entry begins with the programmatic-dependent-launch pair, and only coarse entries are planned for it
+    v = ptx.emit(kb.load("vadd_i32")).text
+    assert v.count("griddepcontrol.launch_dependents;") == v.count(".entry") == v.count("griddepcontrol.wait;") == 2
+    plan = [l for l in v.splitlines() if l.startswith("//!basalt.plan")]
+    assert len(plan) == 1 and "coarse=vadd_i32__coarse" in plan[0] and plan[0].endswith("pdl=1")
+    for entry in v.split(".entry")[1:]:
+        first_access = min(entry.index(op) for op in ("ld.global", "st.global") if op in entry)
+        assert entry.index("griddepcontrol.wait;") < first_access
+
+
 def test_emit_is_deterministic(ptx):
     for src in (kb.load("max_i32"), kb.helper_chain(), kb.load("sgemm_tile16"), kb.matmul_f16(256, 256, 128)):
         assert ptx.emit(src).text == ptx.emit(src).text
