@@ -120,6 +120,13 @@ def test_cli_follows_the_reference_conventions(tmp_path):
     assert r.returncode == 0 and "load v4i32" in r.stdout
 
 
+def test_multicast_result_reports_why_it_is_unavailable():
+    # no CUDA device here: the helper must say so and return None on every rank instead of raising
+    from basalt_b200.sharding import MulticastResult, RankGroup
+    assert MulticastResult.open(RankGroup(), 4096, 0) is None
+    assert MulticastResult.why_not
+
+
 def test_peer_order_makes_every_step_of_an_exchange_a_permutation():
     from basalt_b200.sharding import RankGroup
     for world in (2, 4, 8):
