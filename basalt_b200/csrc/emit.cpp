@@ -1034,6 +1034,9 @@ bool emit_ptx(const Module& in, const EmitOptions& opts, EmitResult* out, Diag* 
                     std::to_string(std::max(1, r.vec_lanes) * std::max(1, r.unroll) * trips) + " pdl=1\n";
         }
         for (auto& p : fe.plan) text += p + "\n";
+        // a kernel with no other launch plan still says that it begins with griddepcontrol.wait (a coarse twin's line,
+        // which comes later and carries the same key, replaces this one)
+        if (fe.plan.empty() && r.coarse_of.empty() && f.is_kernel) text += "//!basalt.plan " + f.name + " pdl=1\n";
         for (auto& md : fe.module_decls)
             if (std::find(module_decls.begin(), module_decls.end(), md) == module_decls.end()) module_decls.push_back(md);
         bodies += fn_text + "\n";

@@ -66,6 +66,9 @@ __global__ void __launch_bounds__(32, 1) peer_allreduce_max_i32_kernel(PeerTable
     // on the stream (the reduction that produces *partial) is still draining, which hides its launch latency;
     // nothing of that kernel's output is read before this wait, which returns once it has completed and its
     // writes are visible.
+    // The kernel after this one on the stream (the next step's reduction, launched the same way) may be set up while
+    // this warp waits for its peers; it touches memory only after this grid has completed.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int v = exchange_max(peers, nranks, rank, epoch, *reinterpret_cast<volatile int*>(partial), status, timeout_ns);
     if (threadIdx.x == 0) {

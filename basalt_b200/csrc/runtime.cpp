@@ -732,6 +732,19 @@ int launch_impl(basalt_rt_function* fn, const uint32_t grid[3], const uint32_t b
         if (fn->has_plan && fn->plan.block[0] && (block[0] != fn->plan.block[0] || block[1] != fn->plan.block[1] || block[2] != fn->plan.block[2]))
             return set_err(4, 0, "cuLaunchKernel", "kernel was compiled for block (" + std::to_string(fn->plan.block[0]) + "," + std::to_string(fn->plan.block[1]) + "," + std::to_string(fn->plan.block[2]) + ")");
         uint32_t sm = shared_mem_bytes ? shared_mem_bytes : (fn->has_plan ? fn->plan.smem : 0);
+        if (fn->pdl && fn->has_plan && fn->plan.pdl && f.cuLaunchKernelEx) {   // the kernel begins with griddepcontrol.wait: see the coarse launch above
+            CUlaunchConfig cfg = {};
+            cfg.gridDimX = grid[0]; cfg.gridDimY = grid[1]; cfg.gridDimZ = grid[2];
+            cfg.blockDimX = block[0]; cfg.blockDimY = block[1]; cfg.blockDimZ = block[2];
+            cfg.sharedMemBytes = sm;
+            cfg.hStream = (CUstream)stream;
+            CUlaunchAttribute attr = {};
+            attr.id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
+            attr.value.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = &attr;
+            cfg.numAttrs = 1;
+            return check(f, "cuLaunchKernelEx", f.cuLaunchKernelEx(&cfg, fn->fn, params, nullptr));
+        }
         return check(f, "cuLaunchKernel", f.cuLaunchKernel(fn->fn, grid[0], grid[1], grid[2], block[0], block[1], block[2], sm, (CUstream)stream, params, nullptr));
     }
     const Plan& p = fn->plan;

@@ -143,7 +143,9 @@ def test_power_of_two_products_are_shifts_and_entries_admit_dependent_launch(ptx
     v = ptx.emit(kb.load("vadd_i32")).text
     assert v.count("griddepcontrol.launch_dependents;") == v.count(".entry") == v.count("griddepcontrol.wait;") == 2
     plan = [l for l in v.splitlines() if l.startswith("//!basalt.plan")]
-    assert len(plan) == 1 and "coarse=vadd_i32__coarse" in plan[0] and plan[0].endswith("pdl=1")
+    assert plan[0] == "//!basalt.plan vadd_i32 pdl=1" and len(plan) == 2      # the later line of the same kernel is the one the runtime keeps
+    assert "coarse=vadd_i32__coarse" in plan[1] and plan[1].endswith("pdl=1")
+    assert "//!basalt.plan max_i32 pdl=1" in ptx.emit(kb.load("max_i32")).text
     for entry in v.split(".entry")[1:]:
         first_access = min(entry.index(op) for op in ("ld.global", "st.global") if op in entry)
         assert entry.index("griddepcontrol.wait;") < first_access
