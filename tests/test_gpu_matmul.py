@@ -291,3 +291,14 @@ def test_launch_gather_refuses_kernels_without_the_epilogue(gpu):
     with pytest.raises(b.CudaError) as e:
         odd.bind_gather((2, 3), 128, 0, [dev(gpu, np.zeros((384, 64), np.float16)), dev(gpu, np.zeros((64, 256), np.float16)), c], [c.device_ptr()])()
     assert e.value.kind == 4 and "even" in e.value.message
+    # the multicast form refuses the same kernels, and an address that is null or not 16-byte aligned
+    with pytest.raises(b.CudaError) as e:
+        fn.bind_gather_multicast(1, 256, 0, [x, x, x, b.i32(256)], x.device_ptr())()
+    assert e.value.kind == 4
+    ok = emitted(gpu, kb.matmul_f16(256, 256, 64), "matmul_kernel")
+    c2 = dev(gpu, np.zeros((256, 256), np.float16))
+    prm = [dev(gpu, np.zeros((256, 64), np.float16)), dev(gpu, np.zeros((64, 256), np.float16)), c2]
+    for bad in (0, c2.device_ptr() + 2):
+        with pytest.raises(b.CudaError) as e:
+            ok.bind_gather_multicast((2, 2), 128, 0, prm, bad)()
+        assert e.value.kind == 4
