@@ -580,6 +580,28 @@ void basalt_rt_tail_plan(uint32_t tiles, uint32_t slots, uint32_t k_extent, uint
 namespace {
 int launch_impl(basalt_rt_function* fn, const uint32_t grid[3], const uint32_t block[3], uint32_t shared_mem_bytes, void* stream, void** params,
                 const uint64_t* peer_out, int n_peers);
+
+// One launch of `entry`.  When the function's plan says `pdl=1` -- the kernel's first instruction after its parameter
+// loads is griddepcontrol.wait -- it goes out with programmatic stream serialisation: its CTAs may be set up while the
+// kernel before it on the stream drains, and touch memory only once that kernel has completed, which hides the launch
+// latency of back-to-back launches and keeps stream order.  An ordinary launch otherwise.
+int launch_maybe_dependent(const Fns& f, const basalt_rt_function* fn, CUfunction entry, const uint32_t grid[3], const uint32_t block[3], uint32_t smem, void* stream,
+                           void** params) {
+    if (fn->pdl && fn->has_plan && fn->plan.pdl && f.cuLaunchKernelEx) {
+        CUlaunchConfig cfg = {};
+        cfg.gridDimX = grid[0]; cfg.gridDimY = grid[1]; cfg.gridDimZ = grid[2];
+        cfg.blockDimX = block[0]; cfg.blockDimY = block[1]; cfg.blockDimZ = block[2];
+        cfg.sharedMemBytes = smem;
+        cfg.hStream = (CUstream)stream;
+        CUlaunchAttribute attr = {};
+        attr.id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
+        attr.value.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        return check(f, "cuLaunchKernelEx", f.cuLaunchKernelEx(&cfg, entry, params, nullptr));
+    }
+    return check(f, "cuLaunchKernel", f.cuLaunchKernel(entry, grid[0], grid[1], grid[2], block[0], block[1], block[2], smem, (CUstream)stream, params, nullptr));
+}
 }
 int basalt_rt_launch(basalt_rt_function* fn, const uint32_t grid[3], const uint32_t block[3], uint32_t shared_mem_bytes, void* stream, void** params) {
     if (!fn || !grid || !block) return set_err(4, 0, "basalt_rt_launch", "null argument");
@@ -635,22 +657,8 @@ int launch_impl(basalt_rt_function* fn, const uint32_t grid[3], const uint32_t b
         uint32_t phys = grid[0] < want ? grid[0] : (uint32_t)want;
         std::vector<void*> all(params, params + fn->plan.nparams);
         all.push_back(&logical);
-        if (fn->pdl && fn->plan.pdl && f.cuLaunchKernelEx) {
-            // The kernel's first instruction after its parameter loads is griddepcontrol.wait: its CTAs may be set up while
-            // the kernel before it on the stream drains, which hides the launch latency of back-to-back small launches.
-            CUlaunchConfig cfg = {};
-            cfg.gridDimX = phys; cfg.gridDimY = 1; cfg.gridDimZ = 1;
-            cfg.blockDimX = block[0]; cfg.blockDimY = 1; cfg.blockDimZ = 1;
-            cfg.sharedMemBytes = shared_mem_bytes;
-            cfg.hStream = (CUstream)stream;
-            CUlaunchAttribute attr = {};
-            attr.id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
-            attr.value.programmaticStreamSerializationAllowed = 1;
-            cfg.attrs = &attr;
-            cfg.numAttrs = 1;
-            return check(f, "cuLaunchKernelEx", f.cuLaunchKernelEx(&cfg, fn->coarse, all.data(), nullptr));
-        }
-        return check(f, "cuLaunchKernel", f.cuLaunchKernel(fn->coarse, phys, 1, 1, block[0], 1, 1, shared_mem_bytes, (CUstream)stream, all.data(), nullptr));
+        const uint32_t one_d[3] = {phys, 1, 1}, blk[3] = {block[0], 1, 1};
+        return launch_maybe_dependent(f, fn, fn->coarse, one_d, blk, shared_mem_bytes, stream, all.data());
     }
     if (fn->has_plan && fn->plan.tail_k) {
         // 128x128 tiles, one per logical CTA (grid x = tile column, y = tile row).  Whole tiles first,
@@ -732,20 +740,7 @@ int launch_impl(basalt_rt_function* fn, const uint32_t grid[3], const uint32_t b
         if (fn->has_plan && fn->plan.block[0] && (block[0] != fn->plan.block[0] || block[1] != fn->plan.block[1] || block[2] != fn->plan.block[2]))
             return set_err(4, 0, "cuLaunchKernel", "kernel was compiled for block (" + std::to_string(fn->plan.block[0]) + "," + std::to_string(fn->plan.block[1]) + "," + std::to_string(fn->plan.block[2]) + ")");
         uint32_t sm = shared_mem_bytes ? shared_mem_bytes : (fn->has_plan ? fn->plan.smem : 0);
-        if (fn->pdl && fn->has_plan && fn->plan.pdl && f.cuLaunchKernelEx) {   // the kernel begins with griddepcontrol.wait: see the coarse launch above
-            CUlaunchConfig cfg = {};
-            cfg.gridDimX = grid[0]; cfg.gridDimY = grid[1]; cfg.gridDimZ = grid[2];
-            cfg.blockDimX = block[0]; cfg.blockDimY = block[1]; cfg.blockDimZ = block[2];
-            cfg.sharedMemBytes = sm;
-            cfg.hStream = (CUstream)stream;
-            CUlaunchAttribute attr = {};
-            attr.id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
-            attr.value.programmaticStreamSerializationAllowed = 1;
-            cfg.attrs = &attr;
-            cfg.numAttrs = 1;
-            return check(f, "cuLaunchKernelEx", f.cuLaunchKernelEx(&cfg, fn->fn, params, nullptr));
-        }
-        return check(f, "cuLaunchKernel", f.cuLaunchKernel(fn->fn, grid[0], grid[1], grid[2], block[0], block[1], block[2], sm, (CUstream)stream, params, nullptr));
+        return launch_maybe_dependent(f, fn, fn->fn, grid, block, sm, stream, params);
     }
     const Plan& p = fn->plan;
     const unsigned* want = p.logical_block[0] ? p.logical_block : p.block;
