@@ -192,9 +192,9 @@ def main():
 
     # ---- the same epilogues through an NVLink multicast mapping (basalt_rt_launch_gather_multicast): one multimem.st
     # per 16 bytes, replicated by the switch.  Nothing is asserted while the result is bound to the multicast object:
-    # verdicts are collected, the mapping is closed by all ranks together, then checked. ----
+    # outcomes are collected, the mapping is closed by all ranks together, then checked. ----
     import torch
-    verdicts = []
+    outcomes = []
     for what in ("f16", "f32"):
         if what == "f16":
             M, N, K, esz = 512 * group.world, 512, 192, 2
@@ -226,16 +226,16 @@ def main():
                 peers.allreduce_max_i32(flag.device_ptr(), flag.device_ptr() + 4, None)      # the barrier: all ranks' tiles have landed
                 ctx.synchronize()
                 got = mcr.tensor.view(torch.float16 if what == "f16" else torch.float32).reshape(M, N).cpu().numpy()
-                verdicts.append((what, fn.status() == 0 and peers.status() == 0, bool(np.isfinite(got).all()), float(rel_fro(got, want)) if np.isfinite(got).all() else float("inf"), tol))
+                outcomes.append((what, fn.status() == 0 and peers.status() == 0, bool(np.isfinite(got).all()), float(rel_fro(got, want)) if np.isfinite(got).all() else float("inf"), tol))
                 group.barrier()
         except Exception as e:      # reported after the mapping is closed
-            verdicts.append((what, False, False, float("inf"), repr(e)))
+            outcomes.append((what, False, False, float("inf"), repr(e)))
         finally:
             mcr.close()
-    for what, status_ok, finite, err, tol in verdicts:
+    for what, status_ok, finite, err, tol in outcomes:
         assert status_ok and finite and err <= tol, ("multimem gather", what, status_ok, finite, err, tol)
-    if verdicts:
-        print(f"rank {group.rank}: multimem gather checked {len(verdicts)} times", flush=True)
+    if outcomes:
+        print(f"rank {group.rank}: multimem gather checked {len(outcomes)} times", flush=True)
 
     group.barrier()
     peers.destroy()
